@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the block-quantized matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): BASELINE config 2, the Q4_0 decode-GEMV sweep with M = 1 over
+(N,K) in {(4096,4096),(11008,4096),(4096,11008),(32000,4096)}, W ~ N(0,0.02) quantized to
+Q4_0 by the library's GPU quantizer, x ~ N(0,1), seed 0.  One *step* is one pass over the
+four shapes (four kernel launches).  Every shape cycles through a ring of distinct copies of
+its weight matrix (>= 512 MiB per shape, four times the L2), so no launch finds its weights in
+cache.  Steps are recorded once into CUDA graphs and replayed; time is CUDA-event time on the
+launching stream.
+
+Printed line: metric = aggregate algorithmic GB/s of the sweep (weight blocks + x + y bytes
+per launch, divided by device time); `roofline` is the dominant kernel (the 32000x4096 GEMV)
+timed alone; `e2e` is the same sweep through cq_qmatmul_host with pinned HOST x and y (copies
+inside the timed region); `cpu_baseline` is the CPU oracle (a C port of candy's dequantize +
+naive f32 matmul, one thread as in candy) on a bounded sample.
+
+With N > 1 (torchrun) every rank runs the same sweep on its own GPU over its own row shard of
+an N-times taller layer (column-parallel linear: no exchange), weak scaling; the time is the
+max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # (N, K), M = 1
+RING_BYTES = 512 << 20
+GRAPH_STEPS = 100
+Q4_0, Q8_0 = 2, 8
+ORDER = 0  # the Go CPU path's element order
+
+
+def gemv_bytes(n, k, m=1, bb=18):
+    return n * (k // 32) * bb + 4 * m * k + 4 * m * n
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock, power and clock-event reasons through NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self.index, self.period = index, period_s
+        self._stop = threading.Event()
+        self._thread = None
+        self.error = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # no NVML: report it, do not guess
+            self.nv, self.error = None, repr(e)
+
+    def _once(self):
+        nv = self.nv
+        mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+        try:
+            r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+        except Exception:
+            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        self.samples.append(mhz)
+        names = {
+            "sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+            "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80, "applications_clocks_setting": 0x2,
+        }
+        for name, bit in names.items():
+            if r & bit:
+                self.reasons.add(name)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self._once()
+            except Exception as e:
+                self.error = repr(e)
+                return
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        if self.nv and not self.samples:
+            try:
+                self._once()
+            except Exception as e:
+                self.error = repr(e)
+
+    def summary(self):
+        out = {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.error:
+            out["error"] = self.error
+        return out
+
+
+class Workload:
+    def __init__(self, dev, shapes, seed=0, ring_bytes=RING_BYTES, rank=0):
+        from candy_b200.backend import QStorage, RawBuffer
+        self.dev = dev
+        self.shapes = shapes
+        self.rings, self.xs, self.ys, self.qs0 = [], [], [], []
+        rng = np.random.default_rng(seed + 1000 * rank)
+        for (n, k) in shapes:
+            w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+            x = rng.standard_normal((1, k), dtype=np.float32)
+            q = QStorage.quantize(dev, Q4_0, ORDER, w)
+            del w
+            nbytes = q.buf.nbytes
+            copies = max(2, -(-ring_bytes // nbytes))
+            ring = [q.buf]
+            for _ in range(copies - 1):
+                b = RawBuffer(dev, nbytes)
+                dev._check(dev._lib.cq_memcpy_d2d(dev.ctx, b.ptr, q.buf.ptr, nbytes), "ring copy")
+                ring.append(b)
+            self.rings.append(ring)
+            self.qs0.append(q)
+            self.xs.append(dev.storage_from_slice(x))
+            self.ys.append(dev.alloc(n))
+        dev.synchronize()
+        self.cursor = [0] * len(shapes)
+
+    def launch(self, i):
+        dev = self.dev
+        n, k = self.shapes[i]
+        ring = self.rings[i]
+        w = ring[self.cursor[i] % len(ring)]
+        self.cursor[i] += 1
+        dev._check(dev._lib.cq_qmatmul(dev.ctx, Q4_0, ORDER, 0, self.xs[i].ptr, 1, k, k, w.ptr, n, self.ys[i].ptr, n), "qmatmul")
+
+    def capture(self, steps, which=None):
+        """Records `steps` steps (or `steps` launches of shape `which`) into a CUDA graph."""
+        dev = self.dev
+        g = C.c_void_p()
+        dev._check(dev._lib.cq_capture_begin(dev.ctx), "capture begin")
+        for _ in range(steps):
+            for i in (range(len(self.shapes)) if which is None else [which]):
+                self.launch(i)
+        dev._check(dev._lib.cq_capture_end(dev.ctx, C.byref(g)), "capture end")
+        return g
+
+    def run_graph(self, g, times=1):
+        dev = self.dev
+        for _ in range(times):
+            dev._check(dev._lib.cq_graph_launch(dev.ctx, g), "graph launch")
+
+    def timed(self, fn):
+        dev = self.dev
+        ms = C.c_float()
+        dev.synchronize()
+        dev._check(dev._lib.cq_timer_start(dev.ctx), "timer start")
+        fn()
+        dev._check(dev._lib.cq_timer_stop(dev.ctx, C.byref(ms)), "timer stop")
+        dev.synchronize()
+        return ms.value
+
+
+def dist_setup(world, local_rank):
+    if world <= 1:
+        return None
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    return dist
+
+
+def dist_max(dist, value, local_rank):
+    if dist is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64, device=torch.device("cuda", local_rank))
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def dist_barrier(dist):
+    if dist is not None:
+        import torch
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
+def cpu_baseline(blocks_by_shape, xs, budget_s=12.0, threads=1):
+    """Times the CPU oracle (C port of candy's dequantize + naive matmul) on the sweep."""
+    from oracle import oracle_c as oc
+    oc.lib()
+    total_bytes, reps = sum(gemv_bytes(n, k) for n, k in SHAPES), 0
+    t0 = time.perf_counter()
+    while True:
+        for (n, k), blocks, x in zip(SHAPES, blocks_by_shape, xs):
+            oc.qmatmul(Q4_0, ORDER, x, blocks, n, nthreads=threads)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s or reps >= 20:
+            break
+    return {"value": total_bytes * reps / el / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{reps} full passes over the 4-shape Q4_0 M=1 sweep ({el:.1f} s); C port of candy's "
+                      f"dequantize + sequential f32 matmul, {threads} thread(s)",
+            "seconds_per_sweep": el / reps}
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    from candy_b200.backend import CudaDevice
+    dist = dist_setup(world, local_rank)
+    dev = CudaDevice(local_rank)
+    wl = Workload(dev, SHAPES, seed=0, rank=rank)
+    lib, ctx = dev._lib, dev.ctx
+    K, W = args.steps, args.warmup
+    for i in range(len(SHAPES)):  # first launches outside any capture (one-time kernel attribute setup)
+        wl.launch(i)
+    dev.synchronize()
+
+    g_main = wl.capture(GRAPH_STEPS) if K >= GRAPH_STEPS else None
+    g_tail = wl.capture(K % GRAPH_STEPS) if K % GRAPH_STEPS else None
+    g_warm = wl.capture(W)
+
+    def timed_region():
+        if g_main is not None:
+            wl.run_graph(g_main, K // GRAPH_STEPS)
+        if g_tail is not None:
+            wl.run_graph(g_tail, 1)
+
+    wl.run_graph(g_warm)
+    dev.synchronize()
+    dist_barrier(dist)
+    with ClockSampler(local_rank) as clocks:
+        ms = wl.timed(timed_region)
+    dist_barrier(dist)
+    ms = dist_max(dist, ms, local_rank)
+    sweep_bytes = sum(gemv_bytes(n, k) for n, k in SHAPES)
+    value = world * sweep_bytes * K / (ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+
+    # ---- per-kernel timing: each shape alone, same ring discipline ------------------------
+    per_shape = []
+    launches = max(200, min(2000, K))
+    for i, (n, k) in enumerate(SHAPES):
+        g = wl.capture(100, which=i)
+        wl.run_graph(g, 2)
+        t = wl.timed(lambda: wl.run_graph(g, launches // 100))
+        us = t * 1e3 / (launches // 100 * 100)
+        gbs = gemv_bytes(n, k) / (us * 1e-6) / 1e9
+        per_shape.append({"n": n, "k": k, "bytes": gemv_bytes(n, k), "us": round(us, 3), "gbs": round(gbs, 1),
+                          "frac_of_" + peak_kind: round(gbs / peak, 4), "frac_of_8000": round(gbs / 8000.0, 4),
+                          "ring_copies": len(wl.rings[i])})
+        lib.cq_graph_destroy(ctx, g)
+    dom = max(range(len(SHAPES)), key=lambda i: per_shape[i]["us"])
+    roofline = {"bound": "hbm", "kernel": f"gemv_stream_kernel<Q4_0> n={SHAPES[dom][0]} k={SHAPES[dom][1]} m=1",
+                "achieved": per_shape[dom]["gbs"], "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": round(per_shape[dom]["gbs"] / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
+                "algorithmic_bytes": per_shape[dom]["bytes"]}
+
+    # ---- end to end through the host-buffer entry point -----------------------------------
+    e2e_steps = max(3, min(K, 200))
+    hx, hy = [], []
+    for (n, k) in SHAPES:
+        px, py = C.c_void_p(), C.c_void_p()
+        dev._check(lib.cq_malloc_host(ctx, 4 * k, C.byref(px)), "pinned x")
+        dev._check(lib.cq_malloc_host(ctx, 4 * n, C.byref(py)), "pinned y")
+        C.memmove(px, np.random.default_rng(1).standard_normal(k, dtype=np.float32).ctypes.data, 4 * k)
+        hx.append(px)
+        hy.append(py)
+
+    def e2e_step():
+        for i, (n, k) in enumerate(SHAPES):
+            ring = wl.rings[i]
+            w = ring[wl.cursor[i] % len(ring)]
+            wl.cursor[i] += 1
+            dev._check(lib.cq_qmatmul_host(ctx, Q4_0, ORDER, 0, hx[i], 1, k, w.ptr, n, hy[i]), "qmatmul_host")
+
+    for _ in range(3):
+        e2e_step()
+    dist_barrier(dist)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_s = time.perf_counter() - t0
+    e2e_s = dist_max(dist, e2e_s, local_rank)
+    e2e = {"value": round(world * sweep_bytes * e2e_steps / e2e_s / 1e9, 2), "unit": "GB/s",
+           "h2d_bytes_per_step": sum(4 * k for _, k in SHAPES), "d2h_bytes_per_step": sum(4 * n for n, _ in SHAPES),
+           "steps": e2e_steps, "us_per_step": round(e2e_s / e2e_steps * 1e6, 1)}
+
+    line = {
+        "metric": "q4_0_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "BASELINE config 2: Q4_0 decode GEMV sweep, M=1, (N,K) in "
+                               "{(4096,4096),(11008,4096),(4096,11008),(32000,4096)}, W~N(0,0.02)->Q4_0, x~N(0,1), seed 0",
+                   "element_order": "go_interleaved", "actmode": "f32",
+                   "l2_defeat": f"inputs larger than L2: each shape cycles a ring of weight copies >= {RING_BYTES >> 20} MiB",
+                   "sharding": "none" if world == 1 else f"rows of an {world}x taller layer, one shard per GPU, no collective"},
+        "frac_of_peak": round(value / world / peak, 4), "frac_of_8000": round(value / world / 8000.0, 4),
+        "roofline": roofline, "per_shape": per_shape, "e2e": e2e, "gpu_launches": K * len(SHAPES),
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        blocks = [q.data() for q in wl.qs0]
+        xs = [x.data().reshape(1, -1) for x in wl.xs]
+        line["cpu_baseline"] = cpu_baseline(blocks, xs, threads=1)
+    elif rank == 0:
+        line["cpu_baseline"] = None
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture; see
+# profiles/.  None until a capture has been summarised there.
+NCU_TRAFFIC_BYTES = None
+
+
+def run_reference(args):
+    """Reference arm: candy's CPU algorithm for the same sweep (the C port in oracle/, since
+    the Go original cannot be built without a Go toolchain), on host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle_c as oc
+    oc.lib()
+    threads = 1  # candy's kernels start no goroutines: one core is all its path can use
+    rng = np.random.default_rng(0)
+    # bounded sample: the first `rows` rows of every shape, sized from a calibration pass so
+    # that steps + warmup finish in about two minutes
+    data = []
+    for (n, k) in SHAPES:
+        rows = min(n, 512)
+        w = rng.standard_normal((rows, k), dtype=np.float32) * np.float32(0.02)
+        x = rng.standard_normal((1, k), dtype=np.float32)
+        data.append((rows, k, oc.quantize(Q4_0, ORDER, w), x))
+    t0 = time.perf_counter()
+    for rows, k, blocks, x in data:
+        oc.qmatmul(Q4_0, ORDER, x, blocks, rows, nthreads=threads)
+    per_row_s = (time.perf_counter() - t0) / sum(d[0] for d in data)
+    total_steps = args.steps + args.warmup
+    frac = min(1.0, (120.0 / total_steps) / (per_row_s * sum(n for n, _ in SHAPES)))
+    sample = []
+    for (n, k) in SHAPES:
+        rows = max(32, int(n * frac))
+        w = rng.standard_normal((rows, k), dtype=np.float32) * np.float32(0.02)
+        x = rng.standard_normal((1, k), dtype=np.float32)
+        sample.append((rows, k, oc.quantize(Q4_0, ORDER, w), x))
+    step_bytes = sum(gemv_bytes(rows, k) for rows, k, _, _ in sample)
+
+    def step():
+        for rows, k, blocks, x in sample:
+            oc.qmatmul(Q4_0, ORDER, x, blocks, rows, nthreads=threads)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    el = time.perf_counter() - t0
+    value = step_bytes * args.steps / el / 1e9
+    desc = (f"first {frac:.4f} of the rows of each of the 4 shapes per step "
+            f"({', '.join(str(s[0]) for s in sample)} rows); C port of candy's dequantize + sequential f32 matmul")
+    line = {
+        "impl": "reference", "metric": "q4_0_gemv_hbm_gbs", "value": round(value, 4), "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BASELINE config 2: Q4_0 decode GEMV sweep, M=1 (bounded row sample per step)",
+                   "element_order": "go_interleaved", "actmode": "f32"},
+        "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "host_cores_available": os.cpu_count(),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = 20 if args.steps is None else args.steps
+        args.warmup = 3 if args.warmup is None else max(args.warmup, 0)
+        run_reference(args)
+    else:
+        args.steps = 20000 if args.steps is None else args.steps
+        args.warmup = 200 if args.warmup is None else max(args.warmup, 3)
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,103 @@
+"""ctypes binding of ``libcandyq.so`` -- one Python function per C entry point.
+
+This is the same surface a cgo file binds (see ``include/candyq.h``); it adds nothing but
+argument marshalling and turning a non-zero status into :class:`CandyqError`.  If the
+shared library is missing the import of this module fails: there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libcandyq.so"
+
+OK = 0
+ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NOMEM, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
+Q4_0, Q8_0 = 2, 8
+ORDER_GO_INTERLEAVED, ORDER_GGML_SPLIT = 0, 1
+ACT_F32, ACT_Q8_1, ACT_F16 = 0, 1, 2
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34}
+Q8_1_BYTES = 36
+
+
+class CandyqError(RuntimeError):
+    def __init__(self, status: int, where: str, detail: str = ""):
+        self.status = status
+        text = lib().cq_status_string(status).decode()
+        super().__init__(f"{where}: {text}" + (f": {detail}" if detail else ""))
+
+
+_lib = None
+
+_vp, _i64, _int, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
+
+# name -> argtypes (every entry returns cq_status unless listed in _OTHER_RESTYPE)
+SIGNATURES = {
+    "cq_device_count": [C.POINTER(C.c_int)],
+    "cq_ctx_create": [_int, C.POINTER(_vp)],
+    "cq_ctx_destroy": [_vp],
+    "cq_ctx_set_stream": [_vp, _vp],
+    "cq_ctx_set_option": [_vp, C.c_char_p, _i64],
+    "cq_malloc": [_vp, _sz, C.POINTER(_vp)],
+    "cq_free": [_vp, _vp],
+    "cq_malloc_host": [_vp, _sz, C.POINTER(_vp)],
+    "cq_free_host": [_vp, _vp],
+    "cq_memset": [_vp, _vp, _int, _sz],
+    "cq_memcpy_h2d": [_vp, _vp, _vp, _sz],
+    "cq_memcpy_d2h": [_vp, _vp, _vp, _sz],
+    "cq_memcpy_d2d": [_vp, _vp, _vp, _sz],
+    "cq_synchronize": [_vp],
+    "cq_quantize_rows": [_vp, _int, _int, _vp, _i64, _i64, _vp],
+    "cq_dequantize": [_vp, _int, _int, _vp, _i64, _vp],
+    "cq_quantize_q8_1": [_vp, _vp, _i64, _i64, _i64, _vp],
+    "cq_qmatmul": [_vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
+    "cq_qmatmul_host": [_vp, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _vp],
+    "cq_capture_begin": [_vp],
+    "cq_capture_end": [_vp, C.POINTER(_vp)],
+    "cq_graph_launch": [_vp, _vp],
+    "cq_graph_destroy": [_vp, _vp],
+    "cq_timer_start": [_vp],
+    "cq_timer_stop": [_vp, C.POINTER(C.c_float)],
+}
+_OTHER_RESTYPE = {
+    "cq_status_string": (C.c_char_p, [C.c_int32]),
+    "cq_last_error": (C.c_char_p, [_vp]),
+    "cq_version": (C.c_char_p, []),
+    "cq_blocks_bytes": (_sz, [_int, _i64, _i64]),
+}
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m candy_b200.build` (needs nvcc). "
+                "candy_b200 has no CPU or eager fallback.")
+        handle = C.CDLL(str(LIB_PATH))
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError here means header and library disagree
+            fn.restype = C.c_int32
+            fn.argtypes = argtypes
+        for name, (restype, argtypes) in _OTHER_RESTYPE.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(ctx, status: int, where: str) -> None:
+    if status != OK:
+        detail = lib().cq_last_error(ctx).decode() if ctx else ""
+        raise CandyqError(status, where, detail)
+
+
+def version() -> str:
+    return lib().cq_version().decode()
+
+
+def device_count() -> int:
+    n = C.c_int(0)
+    lib().cq_device_count(C.byref(n))
+    return n.value

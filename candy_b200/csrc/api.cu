@@ -1,0 +1,360 @@
+// libcandyq: context, memory and dispatch entry points of the C ABI (include/candyq.h).
+#include <cstring>
+
+#include "common.cuh"
+
+cq_status cq_fail(cq_ctx *ctx, cq_status s, const std::string &msg) {
+    if (ctx) ctx->last_error = msg;
+    return s;
+}
+
+cq_status cq_cuda_fail(cq_ctx *ctx, cudaError_t e, const char *what) {
+    std::string msg = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    return cq_fail(ctx, e == cudaErrorMemoryAllocation ? CQ_ERR_NOMEM : CQ_ERR_CUDA, msg);
+}
+
+cq_status cq_reserve_scratch(cq_ctx *ctx, size_t bytes) {
+    if (bytes <= ctx->scratch_bytes) return CQ_OK;
+    if (ctx->scratch) {
+        CQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        CQ_CUDA(ctx, cudaFree(ctx->scratch));
+        ctx->scratch = nullptr;
+        ctx->scratch_bytes = 0;
+    }
+    size_t want = (bytes + 0xFFFFF) & ~size_t(0xFFFFF);
+    CQ_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+    return CQ_OK;
+}
+
+extern "C" {
+
+const char *cq_status_string(cq_status s) {
+    switch (s) {
+        case CQ_OK: return "ok";
+        case CQ_ERR_INVALID_ARG: return "invalid argument";
+        case CQ_ERR_CUDA: return "CUDA runtime error";
+        case CQ_ERR_UNSUPPORTED: return "unsupported configuration";
+        case CQ_ERR_TIMEOUT: return "device-side wait timed out";
+        case CQ_ERR_NOMEM: return "out of memory";
+        case CQ_ERR_TOO_LARGE: return "size beyond the entry point's fixed limit";
+        default: return "unknown status";
+    }
+}
+
+const char *cq_last_error(const cq_ctx *ctx) { return ctx ? ctx->last_error.c_str() : ""; }
+
+const char *cq_version(void) { return "candyq 0.1 sm_100a"; }
+
+cq_status cq_device_count(int *count) {
+    if (!count) return CQ_ERR_INVALID_ARG;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *count = 0;
+        cudaGetLastError();
+        return CQ_ERR_CUDA;
+    }
+    *count = n;
+    return CQ_OK;
+}
+
+cq_status cq_ctx_create(int device, cq_ctx **out) {
+    if (!out) return CQ_ERR_INVALID_ARG;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return CQ_ERR_CUDA;  // no GPU: there is no CPU fallback
+    }
+    if (device < 0 || device >= n) return CQ_ERR_INVALID_ARG;
+    if (cudaSetDevice(device) != cudaSuccess) return CQ_ERR_CUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return CQ_ERR_CUDA;
+    if (prop.major != 10) return CQ_ERR_UNSUPPORTED;  // kernels are built for sm_100a only
+    cq_ctx *ctx = new cq_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return CQ_ERR_CUDA;
+    }
+    ctx->stream = ctx->own_stream;
+    if (cudaHostAlloc((void **)&ctx->dev_err, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void **)&ctx->dev_err_devptr, ctx->dev_err, 0) != cudaSuccess) {
+        cudaStreamDestroy(ctx->own_stream);
+        delete ctx;
+        return CQ_ERR_CUDA;
+    }
+    *ctx->dev_err = 0;
+    *out = ctx;
+    return CQ_OK;
+}
+
+cq_status cq_ctx_destroy(cq_ctx *ctx) {
+    if (!ctx) return CQ_ERR_INVALID_ARG;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->xfer_x) cudaFree(ctx->xfer_x);
+    if (ctx->xfer_y) cudaFree(ctx->xfer_y);
+    if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+    if (ctx->dev_err) cudaFreeHost(ctx->dev_err);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+    return CQ_OK;
+}
+
+cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream) {
+    if (!ctx) return CQ_ERR_INVALID_ARG;
+    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    return CQ_OK;
+}
+
+cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
+    if (!ctx || !key) return CQ_ERR_INVALID_ARG;
+    GemvTuning &t = ctx->tune;
+    if (!strcmp(key, "gemv_warps")) t.target_warps = (int)value;
+    else if (!strcmp(key, "gemv_stages")) t.stages = (int)value;
+    else if (!strcmp(key, "gemv_ctas_per_sm")) t.ctas_per_sm = (int)value;
+    else if (!strcmp(key, "gemv_force_simple")) t.force_simple = (int)value;
+    else if (!strcmp(key, "gemv_pdl")) t.pdl = (int)value;
+    else if (!strcmp(key, "gemm_variant")) t.gemm_variant = (int)value;
+    else return cq_fail(ctx, CQ_ERR_INVALID_ARG, std::string("unknown option ") + key);
+    return CQ_OK;
+}
+
+cq_status cq_malloc(cq_ctx *ctx, size_t bytes, void **dptr) {
+    CQ_ENTER(ctx);
+    if (!dptr) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_malloc: null out pointer");
+    *dptr = nullptr;
+    if (bytes == 0) return CQ_OK;
+    CQ_CUDA(ctx, cudaMalloc(dptr, bytes));
+    return CQ_OK;
+}
+
+cq_status cq_free(cq_ctx *ctx, void *dptr) {
+    CQ_ENTER(ctx);
+    if (!dptr) return CQ_OK;
+    CQ_CUDA(ctx, cudaFree(dptr));
+    return CQ_OK;
+}
+
+cq_status cq_malloc_host(cq_ctx *ctx, size_t bytes, void **hptr) {
+    CQ_ENTER(ctx);
+    if (!hptr) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_malloc_host: null out pointer");
+    *hptr = nullptr;
+    if (bytes == 0) return CQ_OK;
+    CQ_CUDA(ctx, cudaHostAlloc(hptr, bytes, cudaHostAllocDefault));
+    return CQ_OK;
+}
+
+cq_status cq_free_host(cq_ctx *ctx, void *hptr) {
+    CQ_ENTER(ctx);
+    if (!hptr) return CQ_OK;
+    CQ_CUDA(ctx, cudaFreeHost(hptr));
+    return CQ_OK;
+}
+
+cq_status cq_memset(cq_ctx *ctx, void *dptr, int byte, size_t bytes) {
+    CQ_ENTER(ctx);
+    if (!dptr && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memset: null pointer");
+    CQ_CUDA(ctx, cudaMemsetAsync(dptr, byte, bytes, ctx->stream));
+    return CQ_OK;
+}
+
+cq_status cq_memcpy_h2d(cq_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
+    CQ_ENTER(ctx);
+    if ((!dst_dev || !src_host) && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memcpy_h2d: null pointer");
+    CQ_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    CQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return CQ_OK;
+}
+
+cq_status cq_memcpy_d2h(cq_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes) {
+    CQ_ENTER(ctx);
+    if ((!dst_host || !src_dev) && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memcpy_d2h: null pointer");
+    CQ_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    CQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return CQ_OK;
+}
+
+cq_status cq_memcpy_d2d(cq_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes) {
+    CQ_ENTER(ctx);
+    if ((!dst_dev || !src_dev) && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memcpy_d2d: null pointer");
+    CQ_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_dev, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return CQ_OK;
+}
+
+cq_status cq_synchronize(cq_ctx *ctx) {
+    CQ_ENTER(ctx);
+    CQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    int e = *(volatile int *)ctx->dev_err;
+    if (e != 0) {
+        *ctx->dev_err = 0;
+        return cq_fail(ctx, CQ_ERR_TIMEOUT, "a kernel's bounded wait gave up (device error word " + std::to_string(e) + ")");
+    }
+    return CQ_OK;
+}
+
+size_t cq_blocks_bytes(int qtype, int64_t n, int64_t k) {
+    if (n <= 0 || k <= 0 || k % kQK != 0) return 0;
+    if (qtype == CQ_Q4_0) return (size_t)n * (size_t)(k / kQK) * kQ4Bytes;
+    if (qtype == CQ_Q8_0) return (size_t)n * (size_t)(k / kQK) * kQ8Bytes;
+    return 0;
+}
+
+static cq_status check_qtype_order(cq_ctx *ctx, int qtype, int order) {
+    if (qtype != CQ_Q4_0 && qtype != CQ_Q8_0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "qtype must be CQ_Q4_0 or CQ_Q8_0");
+    if (order != CQ_ORDER_GO_INTERLEAVED && order != CQ_ORDER_GGML_SPLIT)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "order must be 0 (interleaved) or 1 (split)");
+    return CQ_OK;
+}
+
+cq_status cq_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w_dev, int64_t n, int64_t k,
+                           void *blocks_dev) {
+    CQ_ENTER(ctx);
+    cq_status s = check_qtype_order(ctx, qtype, order);
+    if (s != CQ_OK) return s;
+    if (!w_dev || !blocks_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: null pointer");
+    if (n < 1 || k < kQK || k % kQK != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: need n >= 1, k >= 32, k % 32 == 0");
+    return launch_quantize_rows(ctx, qtype, order, w_dev, n * (k / kQK), blocks_dev);
+}
+
+cq_status cq_dequantize(cq_ctx *ctx, int qtype, int order, const void *blocks_dev, int64_t nblocks, float *y_dev) {
+    CQ_ENTER(ctx);
+    cq_status s = check_qtype_order(ctx, qtype, order);
+    if (s != CQ_OK) return s;
+    if (nblocks == 0) return CQ_OK;
+    if (!blocks_dev || !y_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_dequantize: null pointer");
+    if (nblocks < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_dequantize: negative block count");
+    return launch_dequantize(ctx, qtype, order, blocks_dev, nblocks, y_dev);
+}
+
+cq_status cq_quantize_q8_1(cq_ctx *ctx, const float *x_dev, int64_t m, int64_t k, int64_t ldx, void *q8_1_dev) {
+    CQ_ENTER(ctx);
+    if (!x_dev || !q8_1_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_q8_1: null pointer");
+    if (m < 1 || k < kQK || k % kQK != 0 || ldx < k)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_q8_1: need m >= 1, k >= 32, k % 32 == 0, ldx >= k");
+    return launch_quantize_q8_1(ctx, x_dev, m, k, ldx, q8_1_dev);
+}
+
+static cq_status check_matmul_args(cq_ctx *ctx, int qtype, int order, int actmode, const void *x, int64_t m, int64_t k,
+                                   int64_t ldx, const void *w, int64_t n, const void *y, int64_t ldy) {
+    cq_status s = check_qtype_order(ctx, qtype, order);
+    if (s != CQ_OK) return s;
+    if (actmode != CQ_ACT_F32 && actmode != CQ_ACT_Q8_1 && actmode != CQ_ACT_F16)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "actmode must be CQ_ACT_F32, CQ_ACT_Q8_1 or CQ_ACT_F16");
+    if (!x || !w || !y) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: null pointer");
+    if (m < 1 || n < 1) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: m and n must be >= 1");
+    if (k < kQK || k % kQK != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: k must be a positive multiple of 32");
+    if (ldx < k) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: ldx < k");
+    if (ldy < n) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: ldy < n");
+    if (m > (int64_t(1) << 24) || n > (int64_t(1) << 28) || k > (int64_t(1) << 24))
+        return cq_fail(ctx, CQ_ERR_TOO_LARGE, "cq_qmatmul: dimension beyond 2^24 (m, k) / 2^28 (n)");
+    return CQ_OK;
+}
+
+cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev, int64_t m, int64_t k,
+                     int64_t ldx, const void *w_blocks_dev, int64_t n, float *y_dev, int64_t ldy) {
+    CQ_ENTER(ctx);
+    cq_status s = check_matmul_args(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
+    if (s != CQ_OK) return s;
+    if (m <= 8 && actmode != CQ_ACT_F16) return launch_gemv(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
+    return launch_gemm(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
+}
+
+cq_status cq_qmatmul_host(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_host, int64_t m, int64_t k,
+                          const void *w_blocks_dev, int64_t n, float *y_host) {
+    CQ_ENTER(ctx);
+    cq_status s = check_matmul_args(ctx, qtype, order, actmode, x_host, m, k, k, w_blocks_dev, n, y_host, n);
+    if (s != CQ_OK) return s;
+    size_t xb = (size_t)m * k * sizeof(float), yb = (size_t)m * n * sizeof(float);
+    if (xb > ctx->xfer_x_bytes) {
+        if (ctx->xfer_x) CQ_CUDA(ctx, cudaFree(ctx->xfer_x));
+        ctx->xfer_x = nullptr, ctx->xfer_x_bytes = 0;
+        CQ_CUDA(ctx, cudaMalloc(&ctx->xfer_x, xb));
+        ctx->xfer_x_bytes = xb;
+    }
+    if (yb > ctx->xfer_y_bytes) {
+        if (ctx->xfer_y) CQ_CUDA(ctx, cudaFree(ctx->xfer_y));
+        ctx->xfer_y = nullptr, ctx->xfer_y_bytes = 0;
+        CQ_CUDA(ctx, cudaMalloc(&ctx->xfer_y, yb));
+        ctx->xfer_y_bytes = yb;
+    }
+    CQ_CUDA(ctx, cudaMemcpyAsync(ctx->xfer_x, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+    s = cq_qmatmul(ctx, qtype, order, actmode, (const float *)ctx->xfer_x, m, k, k, w_blocks_dev, n, (float *)ctx->xfer_y, n);
+    if (s != CQ_OK) return s;
+    CQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->xfer_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    return cq_synchronize(ctx);
+}
+
+struct cq_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+cq_status cq_capture_begin(cq_ctx *ctx) {
+    CQ_ENTER(ctx);
+    if (ctx->capturing) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_capture_begin: already capturing");
+    CQ_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return CQ_OK;
+}
+
+cq_status cq_capture_end(cq_ctx *ctx, cq_graph **out) {
+    CQ_ENTER(ctx);
+    if (!out) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_capture_end: null out pointer");
+    *out = nullptr;
+    if (!ctx->capturing) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_capture_end: not capturing");
+    ctx->capturing = false;
+    cq_graph *g = new cq_graph();
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+        if (g->graph) cudaGraphDestroy(g->graph);
+        delete g;
+        return cq_cuda_fail(ctx, e, "graph capture/instantiate");
+    }
+    *out = g;
+    return CQ_OK;
+}
+
+cq_status cq_graph_launch(cq_ctx *ctx, cq_graph *g) {
+    CQ_ENTER(ctx);
+    if (!g || !g->exec) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_graph_launch: null graph");
+    CQ_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    return CQ_OK;
+}
+
+cq_status cq_graph_destroy(cq_ctx *ctx, cq_graph *g) {
+    CQ_ENTER(ctx);
+    if (!g) return CQ_OK;
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    return CQ_OK;
+}
+
+cq_status cq_timer_start(cq_ctx *ctx) {
+    CQ_ENTER(ctx);
+    if (!ctx->ev_start) {
+        CQ_CUDA(ctx, cudaEventCreate(&ctx->ev_start));
+        CQ_CUDA(ctx, cudaEventCreate(&ctx->ev_stop));
+    }
+    CQ_CUDA(ctx, cudaEventRecord(ctx->ev_start, ctx->stream));
+    return CQ_OK;
+}
+
+cq_status cq_timer_stop(cq_ctx *ctx, float *ms) {
+    CQ_ENTER(ctx);
+    if (!ms || !ctx->ev_start) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_timer_stop: no running timer");
+    CQ_CUDA(ctx, cudaEventRecord(ctx->ev_stop, ctx->stream));
+    CQ_CUDA(ctx, cudaEventSynchronize(ctx->ev_stop));
+    CQ_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_start, ctx->ev_stop));
+    return CQ_OK;
+}
+
+}  // extern "C"

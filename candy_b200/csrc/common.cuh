@@ -1,0 +1,129 @@
+// Shared internals of libcandyq: context, error plumbing, small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "candyq.h"
+
+constexpr int kQK = 32;         // values per block
+constexpr int kQ4Bytes = 18;    // f16 d + 16 nibble bytes
+constexpr int kQ8Bytes = 34;    // f16 d + 32 int8
+constexpr int kQ81Bytes = 36;   // f16 d + f16 sum + 32 int8
+
+// Device-side error word codes (written by kernels whose bounded waits gave up).
+enum : int { kDevErrNone = 0, kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErrDrain = 3, kDevErrMma = 4 };
+
+struct GemvTuning {
+    int target_warps = 8;   // consumer warps per CTA the launcher aims for
+    int stages = 8;         // smem ring depth (clamped by capacity)
+    int ctas_per_sm = 1;
+    int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
+    int pdl = 1;            // programmatic dependent launch on the streaming kernel
+    int gemm_variant = 0;
+};
+
+struct cq_ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    int *dev_err = nullptr;       // mapped pinned host word the kernels can write
+    int *dev_err_devptr = nullptr;
+    void *scratch = nullptr;      // activation staging (Q8_1 blocks / f16 copies)
+    size_t scratch_bytes = 0;
+    void *xfer_x = nullptr;       // device staging used by cq_qmatmul_host
+    void *xfer_y = nullptr;
+    size_t xfer_x_bytes = 0, xfer_y_bytes = 0;
+    GemvTuning tune;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    bool capturing = false;
+    std::string last_error;
+};
+
+cq_status cq_fail(cq_ctx *ctx, cq_status s, const std::string &msg);
+cq_status cq_cuda_fail(cq_ctx *ctx, cudaError_t e, const char *what);
+// Grows ctx->scratch to at least `bytes` (never shrinks).
+cq_status cq_reserve_scratch(cq_ctx *ctx, size_t bytes);
+
+#define CQ_CUDA(ctx, call)                                              \
+    do {                                                                \
+        cudaError_t e__ = (call);                                       \
+        if (e__ != cudaSuccess) return cq_cuda_fail((ctx), e__, #call); \
+    } while (0)
+
+#define CQ_ENTER(ctx)                                                          \
+    do {                                                                       \
+        if ((ctx) == nullptr) return CQ_ERR_INVALID_ARG;                       \
+        cudaError_t e__ = cudaSetDevice((ctx)->device);                        \
+        if (e__ != cudaSuccess) return cq_cuda_fail((ctx), e__, "cudaSetDevice"); \
+    } while (0)
+
+// ---- launchers implemented in the kernel translation units -------------------------
+cq_status launch_dequantize(cq_ctx *ctx, int qtype, int order, const void *blocks, int64_t nblocks, float *y);
+cq_status launch_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w, int64_t nblocks, void *blocks);
+cq_status launch_quantize_q8_1(cq_ctx *ctx, const float *x, int64_t m, int64_t k, int64_t ldx, void *out);
+cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,
+                      int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
+cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,
+                      int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
+
+#ifdef __CUDACC__
+// binary16 bits -> f32 exactly as tensor/internal/cpu/kernels/quantized.go:149-173:
+// finite values through the hardware conversion (exact), inf/NaN by bit assembly so a
+// NaN keeps its payload (mantissa << 13) instead of being quieted.
+__device__ __forceinline__ float fp16_bits_to_f32(uint32_t h) {
+    h &= 0xFFFFu;
+    if ((h & 0x7C00u) == 0x7C00u) return __uint_as_float(((h & 0x8000u) << 16) | 0x7F800000u | ((h & 0x3FFu) << 13));
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls and returns false (callers record an error
+// word and leave; nothing in this library spins without a limit).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 1-D bulk async copy global -> this CTA's shared memory, completion on an mbarrier.
+// dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif  // __CUDACC__

@@ -1,0 +1,588 @@
+// Decode GEMV: y[m,n] = x[m,k] . W[n,k]^T for m <= 8 with Q4_0 / Q8_0 weights.
+//
+// Streaming kernel (the hot path, HBM-bound).  The weight matrix is one contiguous byte
+// stream of n rows x (k/32) blocks.  Each CTA owns a contiguous range of rows and pulls it
+// through a ring of shared-memory stages with 1-D bulk async copies (cp.async.bulk,
+// completion on mbarriers) issued by a dedicated producer warp; the consumer warps never
+// touch global memory for weights.  A consumer thread owns a fixed 64-value slice of k for
+// the whole kernel: its 64 activations live in registers (pre-scaled, see below) and every
+// pass it reads the two blocks of that slice for one row from shared memory as 32-bit
+// words at a lane stride of 9 (Q4_0) or 17 (Q8_0) words -- odd, hence bank-conflict-free.
+//
+// Nibble -> f32 without integer conversion or shifts: a nibble n at bit position 4p of a
+// word (p <= 4) is masked in place and OR-ed into the mantissa of 2^23, giving the float
+// 2^23 + n*16^p; subtracting 2^23 + 8*16^p leaves (n-8)*16^p exactly.  The power of 16 is
+// cancelled by scaling the thread's activation by 16^-p once, at kernel start (exact: a
+// power of two).  Positions 5..7 come from the same word shifted right by 16.  Per weight
+// this is one LOP3, one FADD and one FFMA, issued as packed f32x2 pairs.  Q8_0 bytes are
+// handled the same way with the sign bit flipped: (b ^ 0x80) is b+128 as an unsigned byte.
+//
+// Numerics (CQ_ACT_F32): every product x*(q-8) is formed exactly inside an FMA and summed
+// in f32 per block, then scaled by the block's f16 scale -- the values of candy's CPU path
+// (dequantize, then tensor/internal/cpu/kernels/conv.go:373-389) in a different summation
+// order; the relative difference is ~1e-6.
+//
+// Plain kernel: one warp per row, byte loads, any k % 32 == 0, any alignment, m <= 8.  It is
+// the route for shapes the streaming kernel does not take and a second implementation the
+// tests compare against.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kXPerThread = 64;  // activations a consumer thread keeps in registers
+constexpr int kPassUnroll = 8;   // passes whose partial sums are reduced together
+constexpr int kMaxStages = 16;
+
+struct GemvParams {
+    const uint8_t *w;
+    const float *x;
+    float *y;
+    int64_t n;
+    int nb;            // blocks per row
+    int row_bytes;     // nb * block bytes (multiple of 16)
+    int tpr;           // threads that cover one row (nb / 2)
+    int lanes_per_row; // lanes of a warp on one row: 32, or tpr when tpr < 32 (power of two)
+    int wpr;           // warps per row
+    int rpp;           // rows per pass
+    int cwarps;        // consumer warps
+    int stages;
+    int stage_bytes;
+    int *err;
+};
+
+// ---- compile-time description of where each value of a thread's two blocks sits --------
+// A thread's slice is 36 bytes (Q4_0) = 9 words: [dA:2][qsA:16][dB:2][qsB:16], or 68 bytes
+// (Q8_0) = 17 words: [dA:2][qA:32][dB:2][qB:32].
+struct Slot {
+    int word;   // which 32-bit word
+    int shift;  // 0: take from the word, 1: take from word >> 16
+    int pos;    // nibble (Q4_0) or byte (Q8_0) position inside the (shifted) word
+    int elem;   // index 0..63 of the activation it multiplies (block A: 0..31, block B: 32..63)
+    int blk;    // 0 = block A, 1 = block B
+};
+
+template <int ORDER>
+__host__ __device__ constexpr Slot q4_slot(int s) {
+    // s enumerates the 64 nibbles of the 32 data bytes in stream order: data byte = s/2.
+    const int db = s / 2, hi = s & 1;
+    const int blk = db / 16, j = db % 16;          // byte j of block blk
+    const int sbyte = (blk == 0) ? 2 + j : 20 + j; // byte offset inside the 36-byte slice
+    const int word = sbyte / 4;
+    const int nib = (sbyte % 4) * 2 + hi;          // nibble index 0..7 inside the word
+    const int e = (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j + hi : j + 16 * hi;
+    return Slot{word, nib >= 5 ? 1 : 0, nib >= 5 ? nib - 4 : nib, blk * 32 + e, blk};
+}
+
+__host__ __device__ constexpr Slot q8_slot(int s) {
+    const int blk = s / 32, j = s % 32;
+    const int sbyte = (blk == 0) ? 2 + j : 36 + j;
+    const int word = sbyte / 4, b = sbyte % 4;
+    return Slot{word, b >= 2 ? 1 : 0, b >= 2 ? b - 2 : b, blk * 32 + j, blk};
+}
+
+template <int QT, int ORDER>
+__host__ __device__ constexpr Slot slot_of(int s) {
+    return QT == CQ_Q4_0 ? q4_slot<ORDER>(s) : q8_slot(s);
+}
+
+__host__ __device__ constexpr float pow2i(int e) {  // 2^e for small |e|
+    float r = 1.0f;
+    for (int i = 0; i < (e < 0 ? -e : e); ++i) r = (e < 0) ? r * 0.5f : r * 2.0f;
+    return r;
+}
+
+template <int QT>
+__host__ __device__ constexpr int bits_per_pos() { return QT == CQ_Q4_0 ? 4 : 8; }
+
+// (v & mask) | magic for Q4_0, (v & mask) ^ (magic | signbit) for Q8_0: one LOP3 either way.
+template <int QT>
+__device__ __forceinline__ float magic_float(uint32_t v, int pos) {
+    if (QT == CQ_Q4_0) return __uint_as_float((v & (0xFu << (4 * pos))) | 0x4B000000u);
+    return __uint_as_float((v & (0xFFu << (8 * pos))) ^ (0x4B000000u | (0x80u << (8 * pos))));
+}
+// The constant to subtract: 2^23 + 8*16^pos (Q4_0) or 2^23 + 128*256^pos (Q8_0).
+template <int QT>
+__host__ __device__ constexpr float magic_bias(int pos) {
+    return 8388608.0f + (QT == CQ_Q4_0 ? 8.0f * pow2i(4 * pos) : 128.0f * pow2i(8 * pos));
+}
+
+template <int QT, int ORDER>
+__global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p) {
+    constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
+    constexpr int kDBWord = (QT == CQ_Q4_0) ? 4 : 8;  // word holding block B's scale in its high half
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bar_full[kMaxStages];
+    __shared__ uint64_t bar_empty[kMaxStages];
+    __shared__ float red[2][kPassUnroll][64];  // [buffer][pass][rsub * wpr + warp-in-row], rpp*wpr <= 64
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int cthreads = p.cwarps * 32;
+    const bool is_producer = warp == p.cwarps;
+
+    // Rows of this CTA: an even split of [0, n).
+    const int64_t row_begin = (p.n * (int64_t)blockIdx.x) / gridDim.x;
+    const int64_t row_end = (p.n * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+    const int nrows = (int)(row_end - row_begin);
+    const int npass = (nrows + p.rpp - 1) / p.rpp;
+
+    // Let the next kernel in the stream become resident as soon as every CTA of this one is:
+    // its producer warp may prefetch weights, everything else there waits for this grid.
+    pdl_launch_dependents();
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), p.cwarps);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    if (is_producer) {
+        // ---- producer warp: one lane streams this CTA's rows into the ring ---------------
+        // Weights do not depend on the previous kernel in the stream, so under programmatic
+        // dependent launch the ring starts filling while that kernel is still draining.
+        if (lane == 0) {
+            int issued = 0;
+            for (int ps = 0; ps < npass; ++ps) {
+                const int s = ps % p.stages;
+                if (ps >= p.stages) {
+                    if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
+                        atomicExch(p.err, kDevErrEmptyWait);
+                        atomicExch(&abort_flag, 1);
+                        break;
+                    }
+                }
+                const int r0 = ps * p.rpp;
+                const int rows = min(p.rpp, nrows - r0);
+                const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
+                mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
+                bulk_g2s(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
+                         smem_u32(&bar_full[s]));
+                issued = ps + 1;
+            }
+            // Do not leave while copies into this CTA's shared memory may still be in flight:
+            // wait (bounded) for the last use of every stage that was issued.
+            const int first = issued > p.stages ? issued - p.stages : 0;
+            for (int ps = first; ps < issued; ++ps) {
+                if (!mbar_wait_bounded(smem_u32(&bar_full[ps % p.stages]), (ps / p.stages) & 1)) {
+                    atomicExch(p.err, kDevErrDrain);
+                    break;
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumer warps ---------------------------------------------------------------------
+    // Thread -> (row inside a pass, 64-value slice of k).
+    const int rows_per_warp = 32 / p.lanes_per_row;
+    const int rsub = (warp / p.wpr) * rows_per_warp + lane / p.lanes_per_row;
+    const int wir = warp % p.wpr;  // warp index inside the row
+    const int pair = wir * 32 + (lane % p.lanes_per_row);
+    const bool active = pair < p.tpr;
+
+    // Activations depend on the previous kernel in the stream.
+    pdl_wait_prior();
+
+    float xr[kXPerThread];  // xr[s] multiplies slot s; already divided by 16^pos / 256^pos
+    {
+        float tmp[kXPerThread];
+        if (active) {
+            const float4 *xv = reinterpret_cast<const float4 *>(p.x + (int64_t)pair * kXPerThread);
+#pragma unroll
+            for (int i = 0; i < kXPerThread / 4; ++i) {
+                float4 t = __ldg(xv + i);
+                tmp[4 * i] = t.x, tmp[4 * i + 1] = t.y, tmp[4 * i + 2] = t.z, tmp[4 * i + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kXPerThread; ++i) tmp[i] = 0.0f;
+        }
+#pragma unroll
+        for (int s = 0; s < kXPerThread; ++s) {
+            constexpr int bpp = bits_per_pos<QT>();
+            const Slot sl = slot_of<QT, ORDER>(s);
+            xr[s] = tmp[sl.elem] * pow2i(-bpp * sl.pos);
+        }
+    }
+
+    const int word_off = rsub * (p.row_bytes >> 2) + pair * kWords;
+    int buf = 0;
+    bool dead = false;
+
+    for (int pbase = 0; pbase < npass; pbase += kPassUnroll) {
+        float part[kPassUnroll];
+#pragma unroll
+        for (int u = 0; u < kPassUnroll; ++u) {
+            part[u] = 0.0f;
+            const int ps = pbase + u;
+            if (ps < npass) {  // uniform across the CTA
+                const int s = ps % p.stages;
+                // A warp whose wait gave up keeps walking the loop without waiting or computing,
+                // so that every consumer still reaches the barriers below and the CTA can exit.
+                if (!dead && !mbar_wait_bounded(smem_u32(&bar_full[s]), (ps / p.stages) & 1)) {
+                    atomicExch(p.err, kDevErrFullWait);
+                    atomicExch(&abort_flag, 1);
+                }
+                if (*(volatile int *)&abort_flag) dead = true;
+                const int rows = min(p.rpp, nrows - ps * p.rpp);
+                if (!dead && active && rsub < rows) {
+                    const uint32_t *sw = reinterpret_cast<const uint32_t *>(smem + (size_t)s * p.stage_bytes) + word_off;
+                    uint32_t wv[kWords], ws[kWords];
+#pragma unroll
+                    for (int i = 0; i < kWords; ++i) wv[i] = sw[i];
+#pragma unroll
+                    for (int i = 0; i < kWords; ++i) ws[i] = wv[i] >> 16;
+                    float2 acc[2][2];
+                    acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = make_float2(0.0f, 0.0f);
+#pragma unroll
+                    for (int sidx = 0; sidx < kXPerThread; sidx += 2) {
+                        const Slot a = slot_of<QT, ORDER>(sidx), b = slot_of<QT, ORDER>(sidx + 1);
+                        // both slots of a pair come from the same data byte, hence the same block
+                        float2 f = make_float2(magic_float<QT>(a.shift ? ws[a.word] : wv[a.word], a.pos),
+                                               magic_float<QT>(b.shift ? ws[b.word] : wv[b.word], b.pos));
+                        f = __fadd2_rn(f, make_float2(-magic_bias<QT>(a.pos), -magic_bias<QT>(b.pos)));
+                        float2 &dst = acc[a.blk][(sidx >> 1) & 1];
+                        dst = __ffma2_rn(f, make_float2(xr[sidx], xr[sidx + 1]), dst);
+                    }
+                    const float dA = fp16_bits_to_f32(wv[0] & 0xFFFFu);
+                    const float dB = fp16_bits_to_f32(ws[kDBWord]);
+                    const float sA = (acc[0][0].x + acc[0][0].y) + (acc[0][1].x + acc[0][1].y);
+                    const float sB = (acc[1][0].x + acc[1][0].y) + (acc[1][1].x + acc[1][1].y);
+                    part[u] = fmaf(dA, sA, dB * sB);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+            }
+        }
+
+        // ---- reduce the 8 partials over the lanes of each row segment ---------------------
+        // Three exchange steps halve the number of live values (8 -> 4 -> 2 -> 1) while
+        // summing over the three highest lane bits of the segment; the remaining lane bits are
+        // a plain butterfly.  Afterwards a lane holds the total of pass index `vidx`.
+        const int L = p.lanes_per_row;
+        int vidx = 0;
+        float v1;
+        if (L >= 8) {
+            const int lr = lane % L;
+            float v4[4], v2[2];
+            {
+                const int off = L >> 1;
+                const bool up = (lr & off) != 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float keep = up ? part[i + 4] : part[i];
+                    const float send = up ? part[i] : part[i + 4];
+                    v4[i] = keep + __shfl_xor_sync(0xffffffffu, send, off, 32);
+                }
+                vidx = up ? 4 : 0;
+            }
+            {
+                const int off = L >> 2;
+                const bool up = (lr & off) != 0;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float keep = up ? v4[i + 2] : v4[i];
+                    const float send = up ? v4[i] : v4[i + 2];
+                    v2[i] = keep + __shfl_xor_sync(0xffffffffu, send, off, 32);
+                }
+                vidx += up ? 2 : 0;
+            }
+            {
+                const int off = L >> 3;
+                const bool up = (lr & off) != 0;
+                const float keep = up ? v2[1] : v2[0];
+                const float send = up ? v2[0] : v2[1];
+                v1 = keep + __shfl_xor_sync(0xffffffffu, send, off, 32);
+                vidx += up ? 1 : 0;
+            }
+            for (int off = L >> 4; off > 0; off >>= 1) v1 += __shfl_xor_sync(0xffffffffu, v1, off, 32);
+            const bool writer = (lr & ((L >> 3) - 1)) == 0;
+            if (writer) red[buf][vidx][rsub * p.wpr + wir] = v1;
+        } else {
+            // narrow rows (k <= 128): plain butterflies, lane 0 of the segment writes all eight
+#pragma unroll
+            for (int u = 0; u < kPassUnroll; ++u) {
+                float t = part[u];
+                for (int off = L >> 1; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off, 32);
+                if ((lane % L) == 0) red[buf][u][rsub * p.wpr + wir] = t;
+            }
+        }
+        // consumer-only barrier (the producer warp is not part of it)
+        asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+        for (int t = tid; t < kPassUnroll * p.rpp; t += cthreads) {
+            const int u = t / p.rpp, rs = t % p.rpp;
+            const int r = (pbase + u) * p.rpp + rs;
+            if (pbase + u < npass && r < nrows) {
+                float tot = 0.0f;
+                for (int w = 0; w < p.wpr; ++w) tot += red[buf][u][rs * p.wpr + w];
+                p.y[row_begin + r] = tot;
+            }
+        }
+        buf ^= 1;
+    }
+}
+
+// ---- plain kernel ------------------------------------------------------------------------
+template <int QT, int ORDER, int M>
+__global__ void __launch_bounds__(256) gemv_simple_kernel(const uint8_t *__restrict__ w, const float *__restrict__ x,
+                                                        float *__restrict__ y, int64_t n, int nb, int64_t ldx, int64_t ldy) {
+    constexpr int BB = (QT == CQ_Q4_0) ? kQ4Bytes : kQ8Bytes;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    float acc[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) acc[i] = 0.0f;
+    for (int b = lane; b < nb; b += 32) {
+        const uint8_t *blk = w + (row * nb + b) * BB;
+        const float d = fp16_bits_to_f32((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
+        const float *xb = x + (int64_t)b * kQK;
+        if (QT == CQ_Q4_0) {
+#pragma unroll 4
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t q = blk[2 + j];
+                const float w0 = d * (float)((int)(q & 0xF) - 8);
+                const float w1 = d * (float)((int)(q >> 4) - 8);
+                const int e0 = (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j : j;
+                const int e1 = (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j + 1 : j + 16;
+#pragma unroll
+                for (int i = 0; i < M; ++i) acc[i] = fmaf(w1, xb[i * ldx + e1], fmaf(w0, xb[i * ldx + e0], acc[i]));
+            }
+        } else {
+#pragma unroll 4
+            for (int j = 0; j < kQK; ++j) {
+                const float wv = d * (float)(int)(signed char)blk[2 + j];
+#pragma unroll
+                for (int i = 0; i < M; ++i) acc[i] = fmaf(wv, xb[i * ldx + j], acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < M; ++i) {
+        float t = acc[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off, 32);
+        if (lane == 0) y[i * ldy + row] = t;
+    }
+}
+
+// Q8_1 activations: per-block integer dots scaled in f32, the arithmetic of
+// tensor/internal/cuda/kernels/quantized.cu:1919-1941 (Q4_0) and :2058-2073 (Q8_0) with the
+// work split of mul_mat_vec_q (quantized.cu:2806-2824): a Q4_0 block is two half-block dots,
+// each d4 * (sumi * d8 - 4 * s8); a Q8_0 block is four quarter-block dots d8_0 * d8_1 * sumi.
+// One warp per row; lane handles blocks lane, lane+32, ...
+template <int QT, int ORDER, int M>
+__global__ void __launch_bounds__(256) gemv_q8_1_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act,
+                                                      float *__restrict__ y, int64_t n, int nb, int64_t ldy) {
+    constexpr int BB = (QT == CQ_Q4_0) ? kQ4Bytes : kQ8Bytes;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    float acc[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) acc[i] = 0.0f;
+    for (int b = lane; b < nb; b += 32) {
+        const uint8_t *blk = w + (row * nb + b) * BB;
+        const float dw = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+#pragma unroll
+        for (int i = 0; i < M; ++i) {
+            const uint8_t *ab = act + ((int64_t)i * nb + b) * kQ81Bytes;  // 4-byte aligned: 36 | base
+            const float d8 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(ab)));
+            const float s8 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(ab + 2)));
+            const signed char *q8 = reinterpret_cast<const signed char *>(ab + 4);
+            if (QT == CQ_Q4_0) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    int sumi = 0;
+#pragma unroll
+                    for (int j = 8 * half; j < 8 * half + 8; ++j) {
+                        const int q = blk[2 + j];
+                        const int e0 = (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j : j;
+                        const int e1 = (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j + 1 : j + 16;
+                        sumi += (q & 0xF) * q8[e0] + (q >> 4) * q8[e1];
+                    }
+                    acc[i] += __fmul_rn(dw, __fsub_rn(__fmul_rn((float)sumi, d8), __fmul_rn(4.0f, s8)));
+                }
+            } else {
+#pragma unroll
+                for (int part = 0; part < 4; ++part) {
+                    int sumi = 0;
+#pragma unroll
+                    for (int j = 8 * part; j < 8 * part + 8; ++j) sumi += (int)(signed char)blk[2 + j] * q8[j];
+                    acc[i] += __fmul_rn(__fmul_rn(dw, d8), (float)sumi);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < M; ++i) {
+        float t = acc[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off, 32);
+        if (lane == 0) y[i * ldy + row] = t;
+    }
+}
+
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// Chooses the streaming kernel's geometry; returns false when the shape must take the plain
+// kernel (row bytes not a multiple of 16, misaligned pointers, k > 32768, no room for 2 stages).
+bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, int64_t n, int64_t k, GemvParams &p,
+                 int &grid, int &threads, size_t &smem) {
+    const int bb = qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
+    const int64_t nb = k / kQK;
+    if (nb % 8 != 0) return false;  // row bytes % 16 == 0 and an even block count
+    if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
+    const int tpr = (int)(nb / 2);
+    int lanes, wpr;
+    if (tpr >= 32) {
+        lanes = 32;
+        wpr = (tpr + 31) / 32;
+    } else {
+        if (!is_pow2(tpr)) return false;
+        lanes = tpr;
+        wpr = 1;
+    }
+    if (wpr > 16) return false;
+    const int target = ctx->tune.target_warps < 1 ? 1 : (ctx->tune.target_warps > 16 ? 16 : ctx->tune.target_warps);
+    int row_groups = (target + wpr - 1) / wpr;  // warp groups, each covering 32/lanes rows
+    if (row_groups < 1) row_groups = 1;
+    while (row_groups > 1 && row_groups * wpr > 16) --row_groups;
+    int cwarps = row_groups * wpr;
+    int rpp = row_groups * (32 / lanes);
+    if (rpp * wpr > 64) {  // reduction scratch holds 64 entries per pass
+        rpp = 64 / wpr;
+        row_groups = rpp / (32 / lanes);
+        if (row_groups < 1) return false;
+        cwarps = row_groups * wpr;
+        rpp = row_groups * (32 / lanes);
+    }
+    const int64_t row_bytes = nb * bb;
+    const int64_t stage_bytes = (int64_t)rpp * row_bytes;
+    const size_t budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 8192 : 0;
+    int stages = ctx->tune.stages < 2 ? 2 : (ctx->tune.stages > kMaxStages ? kMaxStages : ctx->tune.stages);
+    if ((size_t)stage_bytes * 2 > budget) return false;
+    while ((size_t)stage_bytes * stages > budget) --stages;
+    p.n = n;
+    p.nb = (int)nb;
+    p.row_bytes = (int)row_bytes;
+    p.tpr = tpr;
+    p.lanes_per_row = lanes;
+    p.wpr = wpr;
+    p.rpp = rpp;
+    p.cwarps = cwarps;
+    p.stages = stages;
+    p.stage_bytes = (int)stage_bytes;
+    threads = (cwarps + 1) * 32;
+    smem = (size_t)stage_bytes * stages;
+    const int64_t max_ctas = (n + rpp - 1) / rpp;
+    int64_t g = (int64_t)ctx->sm_count * (ctx->tune.ctas_per_sm < 1 ? 1 : ctx->tune.ctas_per_sm);
+    if (g > max_ctas) g = max_ctas;
+    grid = (int)g;
+    return true;
+}
+
+template <int QT, int ORDER>
+cq_status run_stream(cq_ctx *ctx, GemvParams p, int grid, int threads, size_t smem) {
+    static thread_local int configured_device = -1;
+    auto kern = gemv_stream_kernel<QT, ORDER>;
+    if (configured_device != ctx->device) {
+        CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 8192)));
+        configured_device = ctx->device;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+    return CQ_OK;
+}
+
+template <int QT, int ORDER>
+cq_status run_simple(cq_ctx *ctx, const uint8_t *w, const float *x, float *y, int64_t m, int64_t n, int nb, int64_t ldx,
+                     int64_t ldy) {
+    const int threads = 256, rows_per_cta = threads / 32;
+    const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
+    switch (m) {
+#define CQ_CASE(MM)                                                                                            \
+    case MM:                                                                                                   \
+        gemv_simple_kernel<QT, ORDER, MM><<<grid, threads, 0, ctx->stream>>>(w, x, y, n, nb, ldx, ldy);        \
+        break;
+        CQ_CASE(1) CQ_CASE(2) CQ_CASE(3) CQ_CASE(4) CQ_CASE(5) CQ_CASE(6) CQ_CASE(7) CQ_CASE(8)
+#undef CQ_CASE
+        default: return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemv: m must be 1..8");
+    }
+    CQ_CUDA(ctx, cudaGetLastError());
+    return CQ_OK;
+}
+
+template <int QT, int ORDER>
+cq_status run_q8_1(cq_ctx *ctx, const uint8_t *w, const uint8_t *act, float *y, int64_t m, int64_t n, int nb, int64_t ldy) {
+    const int threads = 256, rows_per_cta = threads / 32;
+    const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
+    switch (m) {
+#define CQ_CASE(MM)                                                                                      \
+    case MM:                                                                                             \
+        gemv_q8_1_kernel<QT, ORDER, MM><<<grid, threads, 0, ctx->stream>>>(w, act, y, n, nb, ldy);       \
+        break;
+        CQ_CASE(1) CQ_CASE(2) CQ_CASE(3) CQ_CASE(4) CQ_CASE(5) CQ_CASE(6) CQ_CASE(7) CQ_CASE(8)
+#undef CQ_CASE
+        default: return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemv: m must be 1..8");
+    }
+    CQ_CUDA(ctx, cudaGetLastError());
+    return CQ_OK;
+}
+
+template <int QT, int ORDER>
+cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx, const uint8_t *w,
+                        int64_t n, float *y, int64_t ldy) {
+    const int nb = (int)(k / kQK);
+    if (actmode == CQ_ACT_Q8_1) {
+        const size_t bytes = (size_t)m * nb * kQ81Bytes;
+        cq_status s = cq_reserve_scratch(ctx, bytes);
+        if (s != CQ_OK) return s;
+        s = launch_quantize_q8_1(ctx, x, m, k, ldx, ctx->scratch);
+        if (s != CQ_OK) return s;
+        return run_q8_1<QT, ORDER>(ctx, w, static_cast<const uint8_t *>(ctx->scratch), y, m, n, nb, ldy);
+    }
+    GemvParams p{};
+    int grid = 0, threads = 0;
+    size_t smem = 0;
+    if (!ctx->tune.force_simple && plan_stream(ctx, QT, w, x, n, k, p, grid, threads, smem) && (ldx % 4 == 0)) {
+        p.w = w;
+        p.err = ctx->dev_err_devptr;
+        for (int64_t i = 0; i < m; ++i) {  // one pass over the weights per activation row
+            p.x = x + i * ldx;
+            p.y = y + i * ldy;
+            cq_status s = run_stream<QT, ORDER>(ctx, p, grid, threads, smem);
+            if (s != CQ_OK) return s;
+        }
+        return CQ_OK;
+    }
+    return run_simple<QT, ORDER>(ctx, w, x, y, m, n, nb, ldx, ldy);
+}
+
+}  // namespace
+
+cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx,
+                      const void *w, int64_t n, float *y, int64_t ldy) {
+    if ((reinterpret_cast<uintptr_t>(w) & 1) != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "weight blocks must be 2-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "x and y must be 4-byte aligned");
+    const uint8_t *wb = static_cast<const uint8_t *>(w);
+    if (qtype == CQ_Q4_0 && order == CQ_ORDER_GO_INTERLEAVED)
+        return gemv_dispatch<CQ_Q4_0, 0>(ctx, actmode, x, m, k, ldx, wb, n, y, ldy);
+    if (qtype == CQ_Q4_0) return gemv_dispatch<CQ_Q4_0, 1>(ctx, actmode, x, m, k, ldx, wb, n, y, ldy);
+    return gemv_dispatch<CQ_Q8_0, 0>(ctx, actmode, x, m, k, ldx, wb, n, y, ldy);
+}

@@ -1,0 +1,160 @@
+/*
+ * candyq.h -- C ABI of libcandyq: block-quantized (Q4_0 / Q8_0) matmul for gocnn/candy
+ * on NVIDIA B200 (sm_100a).
+ *
+ * The reference (gocnn/candy) has no FFI for its tensor backends: its CUDA backend is
+ * an empty Go package (tensor/internal/cuda/device.go:1, storage.go:1) beside unlaunched
+ * kernel sources and a registry of kernel names (tensor/internal/cuda/kernels/kernels.go:
+ * 482-631).  This header is the boundary a cgo file in tensor/internal/cuda binds to make
+ * that backend real for the quantized linear.  The only C-ABI precedent in the reference
+ * is llm/internal/flashattn/flash_api.h:71-117 (extern "C", raw device pointers, strides
+ * in elements); unlike it, every entry point here returns a status and never aborts.
+ *
+ * Conventions
+ *  - All pointers named *_dev are device pointers on the context's GPU; *_host are host
+ *    pointers.  Sizes are in elements unless the name says bytes.
+ *  - A weight matrix W[n,k] is n*k/32 blocks, row-major: row r = blocks r*k/32 ...
+ *    (r+1)*k/32-1 (same layout the reference kernels index, quantized.cu:1279, :2827).
+ *    Q4_0 block = 18 bytes {f16 d; u8 qs[16]}; Q8_0 block = 34 bytes {f16 d; i8 qs[32]}
+ *    (tensor/internal/cpu/kernels/quantized.go:8-11, :34-37).  Little-endian, no padding.
+ *  - Launches are asynchronous on the context's stream; cq_synchronize waits and reports
+ *    deferred device-side errors.  One context must not be used from two threads at once.
+ *  - The library has no CPU fallback: without a usable GPU every compute entry fails.
+ */
+#ifndef CANDYQ_H
+#define CANDYQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t cq_status;
+enum {
+    CQ_OK = 0,
+    CQ_ERR_INVALID_ARG = -1, /* null pointer, k % 32 != 0, ld too small, unknown enum ...   */
+    CQ_ERR_CUDA = -2,        /* a CUDA runtime call failed; cq_last_error has the text      */
+    CQ_ERR_UNSUPPORTED = -3, /* valid request this build has no kernel for                   */
+    CQ_ERR_TIMEOUT = -4,     /* a bounded device-side wait gave up (reported at synchronize) */
+    CQ_ERR_NOMEM = -5,
+    CQ_ERR_TOO_LARGE = -6    /* beyond a stated fixed limit of the entry point               */
+};
+
+typedef struct cq_ctx cq_ctx;
+
+/* Block formats; values follow the GGML type ids the reference's registry names use. */
+enum cq_qtype { CQ_Q4_0 = 2, CQ_Q8_0 = 8 };
+
+/* Which of the 32 values each Q4_0 nibble is.  The reference disagrees with itself:
+ * CQ_ORDER_GO_INTERLEAVED  byte j -> values 2j (low), 2j+1 (high)   quantized.go:87-92
+ * CQ_ORDER_GGML_SPLIT      byte j -> values j (low), j+16 (high)    quantized.cu:862-866
+ * Ignored for Q8_0. */
+enum cq_order { CQ_ORDER_GO_INTERLEAVED = 0, CQ_ORDER_GGML_SPLIT = 1 };
+
+/* How activations enter the dot products.
+ * CQ_ACT_F32   f32 activations, f32 accumulate: the arithmetic of candy's CPU path
+ *              (dequantize, then conv.go:373-389) up to summation order.
+ * CQ_ACT_Q8_1  activations quantized per 32 to int8 exactly as quantize_q8_1
+ *              (quantized.cu:3521-3558), integer dots scaled per block as
+ *              vec_dot_q4_0_q8_1 / vec_dot_q8_0_q8_1 (quantized.cu:1919-1941, :2058-2073).
+ * CQ_ACT_F16   activations and dequantized weights rounded to f16, f32 accumulate on
+ *              the tensor cores (prefill GEMM). */
+enum cq_actmode { CQ_ACT_F32 = 0, CQ_ACT_Q8_1 = 1, CQ_ACT_F16 = 2 };
+
+const char *cq_status_string(cq_status s);
+/* Text of the most recent failure on this context ("" if none).  Owned by the context. */
+const char *cq_last_error(const cq_ctx *ctx);
+/* Library build tag, e.g. "candyq sm_100a". */
+const char *cq_version(void);
+
+/* ---- device / memory: what candy.BackendDevice needs (device.go:49-82) -------------- */
+cq_status cq_device_count(int *count);
+cq_status cq_ctx_create(int device, cq_ctx **out);
+cq_status cq_ctx_destroy(cq_ctx *ctx);
+/* Run subsequent launches on a caller-owned cudaStream_t (0 restores the context's own). */
+cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream);
+/* Tuning knobs (launch geometry); unknown keys -> CQ_ERR_INVALID_ARG.  Results never
+ * depend on them beyond f32 summation order. */
+cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
+cq_status cq_malloc(cq_ctx *ctx, size_t bytes, void **dptr);     /* BackendDevice.Alloc   */
+cq_status cq_free(cq_ctx *ctx, void *dptr);
+cq_status cq_malloc_host(cq_ctx *ctx, size_t bytes, void **hptr); /* pinned host memory   */
+cq_status cq_free_host(cq_ctx *ctx, void *hptr);
+cq_status cq_memset(cq_ctx *ctx, void *dptr, int byte, size_t bytes);            /* Zeros */
+cq_status cq_memcpy_h2d(cq_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+                                                          /* BackendDevice.StorageFromSlice */
+cq_status cq_memcpy_d2h(cq_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+                                                          /* BackendStorage.Data, backend.go:9 */
+cq_status cq_memcpy_d2d(cq_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes);
+                                                          /* BackendStorage.Clone, backend.go:6 */
+cq_status cq_synchronize(cq_ctx *ctx);                    /* BackendDevice.Synchronize, device.go:80-81 */
+
+/* ---- block formats ------------------------------------------------------------------ */
+/* Bytes of n*k/32 blocks of `qtype`, or 0 for bad arguments. */
+size_t cq_blocks_bytes(int qtype, int64_t n, int64_t k);
+
+/* f32 W[n,k] (row-major, contiguous) -> blocks.  Replaces the reference's only weight
+ * quantizers, the Metal shaders kernel_cpy_f32_q4_0 / kernel_cpy_f32_q8_0
+ * (tensor/internal/metal/kernels/quantized.metal:4149-4214, :4091-4147).  For Q4_0,
+ * `order` picks the nibble packing so that cq_dequantize with the same order returns
+ * the values in source order. */
+cq_status cq_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w_dev, int64_t n,
+                           int64_t k, void *blocks_dev);
+
+/* blocks -> f32, bit-exact.  Replaces DequantizeBlockQ4_0F32 / DequantizeBlockQ8_0F32
+ * (tensor/internal/cpu/kernels/quantized.go:85-93, :131-136, f16 decode :149-173) and the
+ * kernels dequantize_block_q4_0_f32 / dequantize_block_q8_0_f32 (quantized.cu:838-867,
+ * :1149-1175). */
+cq_status cq_dequantize(cq_ctx *ctx, int qtype, int order, const void *blocks_dev,
+                        int64_t nblocks, float *y_dev);
+
+/* f32 x[m,k] (row stride ldx) -> m*k/32 Q8_1 blocks of 36 bytes {f16 d; f16 sum; i8 q[32]}.
+ * Replaces quantize_q8_1 (quantized.cu:3521-3558). */
+cq_status cq_quantize_q8_1(cq_ctx *ctx, const float *x_dev, int64_t m, int64_t k, int64_t ldx,
+                           void *q8_1_dev);
+
+/* ---- the hot path ------------------------------------------------------------------- */
+/* y[m,n] = x[m,k] . W[n,k]^T, f32 in / f32 out, row-major with row strides ldx, ldy.
+ * This is BackendStorage.MatMul (backend.go:77-78) for a quantized right-hand side, i.e.
+ * what nn.Linear.Forward (nn/linear.go:58-112) reaches through MatMulForward
+ * (tensor/ops.go:1238-1266) and, on the CPU, NaiveBatchedMatMulStridedF32
+ * (tensor/internal/cpu/kernels/conv.go:373-389) after dequantizing.  It also stands in
+ * for the reference's unlaunched CUDA entry points dequantize_mul_mat_vec_q4_0_cuda
+ * (quantized.cu:1323), mul_mat_vec_q4_0_q8_1_cuda1..8 (quantized.cu:2874-3519) and
+ * mul_mat_q4_0 / mul_mat_q8_0 (quantized.cu:4477, :4529).
+ * m <= 8 runs the decode GEMV, larger m the prefill GEMM.
+ * Preconditions: k % 32 == 0, k >= 32, m, n >= 1, ldx >= k, ldy >= n. */
+cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev,
+                     int64_t m, int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n,
+                     float *y_dev, int64_t ldy);
+
+/* Same product with HOST activations and HOST result: copies x up, runs cq_qmatmul, copies
+ * y back and waits.  Weights stay resident on the device (they are the layer's state).
+ * x_host / y_host should be pinned (cq_malloc_host) for full copy speed. */
+cq_status cq_qmatmul_host(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_host,
+                          int64_t m, int64_t k, const void *w_blocks_dev, int64_t n,
+                          float *y_host);
+
+/* ---- CUDA graphs and device timing ----------------------------------------------------
+ * Decode loops are launch-bound: a GEMV lasts a few microseconds.  These wrap stream capture
+ * so a host in any language can record a sequence of cq_* launches once and replay it.
+ * The reference has no counterpart (its CUDA backend never launches anything).
+ * Between begin and end only asynchronous entry points may be called on this context
+ * (no cq_memcpy_h2d/d2h, cq_synchronize, cq_qmatmul_host, nor a first call that has to grow
+ * the context's scratch memory). */
+typedef struct cq_graph cq_graph;
+cq_status cq_capture_begin(cq_ctx *ctx);
+cq_status cq_capture_end(cq_ctx *ctx, cq_graph **out);
+cq_status cq_graph_launch(cq_ctx *ctx, cq_graph *g);
+cq_status cq_graph_destroy(cq_ctx *ctx, cq_graph *g);
+/* CUDA-event stopwatch on the context's stream: stop waits for the stream and returns the
+ * device time in milliseconds between the two marks. */
+cq_status cq_timer_start(cq_ctx *ctx);
+cq_status cq_timer_stop(cq_ctx *ctx, float *ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CANDYQ_H */
