@@ -408,6 +408,22 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_kernel_only(args):
+    """A few plain launches of one GEMV shape over a small ring: the case ncu captures."""
+    from candy_b200.backend import CudaDevice
+    n, k = (int(v) for v in args.kernel_only.lower().split("x"))
+    dev = CudaDevice(int(os.environ.get("LOCAL_RANK", "0")))
+    nbytes = n * (k // 32) * 18
+    for kv in args.option:
+        key, val = kv.split("=")
+        dev.set_option(key, int(val))
+    wl = Workload(dev, [(n, k)], seed=0, ring_bytes=max(2 * nbytes, 160 << 20))
+    for _ in range(args.launches):
+        wl.launch(0)
+    dev.synchronize()
+    print(json.dumps({"kernel_only": [n, k], "launches": args.launches, "ring_copies": len(wl.rings[0])}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,7 +431,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--kernel-only", default=None, metavar="NxK", help="profiling aid: launch one GEMV shape a few times")
+    ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--option", action="append", default=[], metavar="KEY=INT", help="library tuning option (kernel-only mode)")
     args = ap.parse_args()
+    if args.kernel_only:
+        run_kernel_only(args)
+        return
     if args.impl == "reference":
         args.steps = 20 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else max(args.warmup, 0)

@@ -122,6 +122,10 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemv_force_simple")) t.force_simple = (int)value;
     else if (!strcmp(key, "gemv_pdl")) t.pdl = (int)value;
     else if (!strcmp(key, "gemm_variant")) t.gemm_variant = (int)value;
+    else if (!strcmp(key, "gemv_variant")) t.gemv_variant = (int)value;
+    else if (!strcmp(key, "gemv_probe")) t.gemv_probe = (int)value;
+    else if (!strcmp(key, "gemv_coop")) t.gemv_coop = (int)value;
+    else if (!strcmp(key, "gemv_rpt")) t.gemv_rpt = (int)value;
     else return cq_fail(ctx, CQ_ERR_INVALID_ARG, std::string("unknown option ") + key);
     return CQ_OK;
 }

