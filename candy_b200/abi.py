@@ -9,7 +9,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libcandyq.so"
+import os
+
+# CANDYQ_LIBRARY points the binding at another build of the same library (profiling builds).
+LIB_PATH = Path(os.environ.get("CANDYQ_LIBRARY") or Path(__file__).resolve().parent / "libcandyq.so")
 
 OK = 0
 ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NOMEM, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6

@@ -20,14 +20,14 @@ enum : int { kDevErrNone = 0, kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErr
 struct GemvTuning {
     int target_warps = 8;   // consumer warps per CTA the launcher aims for
     int stages = 8;         // smem ring depth (clamped by capacity)
-    int ctas_per_sm = 1;
+    int ctas_per_sm = 0;    // 0 = automatic
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;
     int gemv_rpt = 2;       // rows per thread and pass in the streaming kernel (1 or 2)
     int gemv_coop = 1;      // slice activations once per CTA through shared memory when rows share a CTA
     int gemv_probe = 0;     // profiling aid, see GemvParams::probe (results are wrong when non-zero)
-    int gemv_variant = 0;   // 0: two int8 activation slices (default), 1: f32 FMA decoder, 3: three slices
+    int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices
 };
 
 struct cq_ctx {
@@ -126,6 +126,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+
+// Same copy with an L2 eviction-priority hint (a policy word from make_l2_policy_*).
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst_smem),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t make_l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
 }
 
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -36,6 +36,17 @@
 // tests compare against.
 #include "common.cuh"
 
+#ifdef CQ_TRACE
+__device__ long long g_trace[64];
+__device__ int g_trace_on;
+#define TRACE(i) do { if (blockIdx.x == 0 && g_trace_on && (threadIdx.x == 0)) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_trace[i] = t_; } } while (0)
+#define TRACEP(i) do { if (blockIdx.x == 0 && g_trace_on) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_trace[i] = t_; } } while (0)
+extern "C" int cq_debug_trace(long long *out, int on) { cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64); cudaMemcpyToSymbol(g_trace_on, &on, sizeof(int)); return 0; }
+#else
+#define TRACE(i)
+#define TRACEP(i)
+#endif
+
 namespace {
 
 constexpr int kXPerThread = 64;  // activations a consumer thread keeps in registers
@@ -58,7 +69,7 @@ struct GemvParams {
     int stages;
     int stage_bytes;
     int coop_off;      // byte offset of the cooperative activation staging area in dynamic smem, or -1
-    int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers
+    int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers, 3 = empty kernel
     int *err;
 };
 
@@ -172,6 +183,180 @@ __host__ __device__ constexpr int act_elem(int wi, int t, int hi) {
     const int j = 4 * wi + t;  // data byte inside the block
     return (ORDER == CQ_ORDER_GO_INTERLEAVED) ? 2 * j + hi : j + 16 * hi;
 }
+
+// ---- default decoder: 16-bit block fixed point --------------------------------------------
+// Every 32-block of activations is scaled once to 16-bit integers,  X = rint(x * 32767 / amax),
+// |x - X * amax/32767| <= amax / 65534, and split into a signed high byte and an unsigned low
+// byte (X = 256 * hi + lo).  A block's dot product is then exact integer arithmetic,
+//     sum_i n_i X_i = 256 * dp4a(n, hi) + dp4a(n, lo),
+// four weights per instruction and byte plane, followed by one int -> float conversion and two
+// multiplies per block.  Against candy's CPU path the result differs by the 16-bit rounding
+// of the activations (about 1e-5 of max|y| on Gaussian data) and by summation order.
+// Setting the state up costs ~5 instructions per activation, a third of the slice decoder.
+template <int QT, int ORDER>
+struct DecQ16 {
+    static constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
+    static constexpr int kBlkWords = (QT == CQ_Q4_0) ? 4 : 8;
+    static constexpr int kVecs = (QT == CQ_Q4_0) ? 2 : 1;
+    static constexpr bool kCoop = true;
+    static constexpr int kStateWordsPerBlock = 20;  // 8 hi words, 8 lo words, scale, bias, 2 pad (16-byte multiple)
+    int qh[2][kBlkWords][kVecs];  // high bytes (signed), lane order matching the weight bytes
+    int ql[2][kBlkWords][kVecs];  // low bytes (unsigned)
+    float d16[2];                 // amax / 32767 per block
+    int bias[2];                  // -8 * sum X for Q4_0, 0 for Q8_0
+
+    // low 16 bits of each input = X (two's complement): returns the packed low / high bytes
+    __device__ __forceinline__ static void pack_planes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t &lo, uint32_t &hi) {
+        const uint32_t ab = __byte_perm(a, b, 0x5410), cd = __byte_perm(c, d, 0x5410);
+        lo = __byte_perm(ab, cd, 0x6420);
+        hi = __byte_perm(ab, cd, 0x7531);
+    }
+    __device__ __forceinline__ static int plane_sum(uint32_t lo, uint32_t hi) {  // sum of the four X
+        return 256 * __dp4a((int)hi, 0x01010101, 0) + (int)__dp4a(lo, 0x01010101u, 0u);
+    }
+    __device__ __forceinline__ static uint32_t to_fixed(float x, float inv) {
+        return __float_as_uint(fminf(x * inv, 32767.0f) + 12582912.0f);  // 1.5 * 2^23: rint into the mantissa
+    }
+
+    // Cooperative set-up: item = block * 4 + quarter, 8 activations per lane, four adjacent
+    // lanes make one block.  All 32 lanes of the warp must call this together.
+    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) {
+        const int blk = item >> 2, qd = item & 3;
+        float r[8];
+        if (valid) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item + 1);
+            r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = 0.0f;
+        }
+        int idxA, idxB;  // which of the block's 8 packed words this quarter fills
+        if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) idxA = 2 * qd, idxB = 2 * qd + 1;
+        else if (QT == CQ_Q4_0) idxA = (qd < 2) ? 4 * qd : 4 * (qd - 2) + 1, idxB = idxA + 2;
+        else idxA = 2 * qd, idxB = 2 * qd + 1;
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(r[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1, 32));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2, 32));
+        const float inv = amax > 0.0f ? __fdividef(32767.0f, amax) : 0.0f;
+        uint32_t xi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xi[i] = to_fixed(r[i], inv);
+        uint32_t la, ha, lb, hb;
+        if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) {
+            pack_planes(xi[0], xi[2], xi[4], xi[6], la, ha);  // low nibbles meet the even values
+            pack_planes(xi[1], xi[3], xi[5], xi[7], lb, hb);
+        } else {
+            pack_planes(xi[0], xi[1], xi[2], xi[3], la, ha);
+            pack_planes(xi[4], xi[5], xi[6], xi[7], lb, hb);
+        }
+        int xsum = plane_sum(la, ha) + plane_sum(lb, hb);
+        xsum += __shfl_xor_sync(0xffffffffu, xsum, 1, 32);
+        xsum += __shfl_xor_sync(0xffffffffu, xsum, 2, 32);
+        if (valid) {
+            uint32_t *dst = area + blk * kStateWordsPerBlock;
+            dst[idxA] = ha, dst[idxB] = hb;
+            dst[8 + idxA] = la, dst[8 + idxB] = lb;
+            if (qd == 0) {
+                dst[16] = __float_as_uint(amax * (1.0f / 32767.0f));
+                dst[17] = (QT == CQ_Q4_0) ? (uint32_t)(-8 * xsum) : 0u;
+            }
+        }
+    }
+
+    // src: this thread's two consecutive block states (16-byte aligned).
+    __device__ __forceinline__ void load(const uint32_t *src) {
+        uint32_t t[2 * kStateWordsPerBlock];
+#pragma unroll
+        for (int i = 0; i < 2 * kStateWordsPerBlock / 4; ++i) {
+            const uint4 v = reinterpret_cast<const uint4 *>(src)[i];
+            t[4 * i] = v.x, t[4 * i + 1] = v.y, t[4 * i + 2] = v.z, t[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                qh[blk][j / kVecs][j % kVecs] = (int)t[blk * kStateWordsPerBlock + j];
+                ql[blk][j / kVecs][j % kVecs] = (int)t[blk * kStateWordsPerBlock + 8 + j];
+            }
+            d16[blk] = __uint_as_float(t[blk * kStateWordsPerBlock + 16]);
+            bias[blk] = (int)t[blk * kStateWordsPerBlock + 17];
+        }
+    }
+
+    // Per-thread set-up from the thread's own 64 activations (used when rows do not share a CTA).
+    __device__ __forceinline__ void init(const float (&x)[kXPerThread]) {
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kQK; ++i) amax = fmaxf(amax, fabsf(x[blk * kQK + i]));
+            const float inv = amax > 0.0f ? __fdividef(32767.0f, amax) : 0.0f;
+            d16[blk] = amax * (1.0f / 32767.0f);
+            uint32_t xi[kQK];
+#pragma unroll
+            for (int i = 0; i < kQK; ++i) xi[i] = to_fixed(x[blk * kQK + i], inv);
+            int xsum = 0;
+#pragma unroll
+            for (int wi = 0; wi < kBlkWords; ++wi)
+#pragma unroll
+                for (int v = 0; v < kVecs; ++v) {
+                    uint32_t lo, hi;
+                    pack_planes(xi[act_elem<QT, ORDER>(wi, 0, v)], xi[act_elem<QT, ORDER>(wi, 1, v)],
+                                xi[act_elem<QT, ORDER>(wi, 2, v)], xi[act_elem<QT, ORDER>(wi, 3, v)], lo, hi);
+                    qh[blk][wi][v] = (int)hi;
+                    ql[blk][wi][v] = (int)lo;
+                    xsum += plane_sum(lo, hi);
+                }
+            bias[blk] = (QT == CQ_Q4_0) ? -8 * xsum : 0;
+        }
+    }
+
+    // weights (signed for Q8_0, small non-negative for Q4_0) times unsigned low bytes
+    __device__ __forceinline__ static int dp4a_wu(int w, int lo, int acc) {
+        int r;
+        asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(lo), "r"(acc));
+        return r;
+    }
+
+    __device__ __forceinline__ float pass(const uint32_t *sw) const {
+        uint32_t w[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = sw[i];
+        // data words of block A start 2 bytes into the slice: realign with funnel shifts
+        uint32_t dw[2][kBlkWords];
+#pragma unroll
+        for (int i = 0; i < kBlkWords; ++i) {
+            dw[0][i] = __funnelshift_r(w[i], w[i + 1], 16);
+            dw[1][i] = w[kBlkWords + 1 + i];
+        }
+        // plain hardware conversion: a NaN scale gives a NaN sum either way
+        const float scale[2] = {__half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu))),
+                                __half2float(__ushort_as_half((unsigned short)(w[kBlkWords] >> 16)))};
+        float total = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            int ah = 0, al = bias[blk];
+#pragma unroll
+            for (int wi = 0; wi < kBlkWords; ++wi) {
+                if (QT == CQ_Q4_0) {
+                    const int lo = (int)(dw[blk][wi] & 0x0F0F0F0Fu);
+                    const int hi = (int)((dw[blk][wi] >> 4) & 0x0F0F0F0Fu);
+                    ah = __dp4a(hi, qh[blk][wi][1], __dp4a(lo, qh[blk][wi][0], ah));
+                    al = dp4a_wu(hi, ql[blk][wi][1], dp4a_wu(lo, ql[blk][wi][0], al));
+                } else {
+                    ah = __dp4a((int)dw[blk][wi], qh[blk][wi][0], ah);
+                    al = dp4a_wu((int)dw[blk][wi], ql[blk][wi][0], al);
+                }
+            }
+            const float v = (float)(ah * 256 + al);  // |.| < 2^24: exact
+            total = fmaf(scale[blk] * d16[blk], v, total);
+        }
+        return total;
+    }
+};
 
 template <int QT, int ORDER, int S>
 struct DecSlices {
@@ -374,6 +559,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     const int rows_per_pass = p.rpp * RPT;
     const int npass = (nrows + rows_per_pass - 1) / rows_per_pass;
 
+    TRACE(0);
     // Let the next kernel in the stream become resident as soon as every CTA of this one is:
     // its producer warp may prefetch weights, everything else there waits for this grid.
     pdl_launch_dependents();
@@ -386,14 +572,18 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
         fence_proxy_async();
     }
     __syncthreads();
+    TRACE(1);
 
     if (is_producer) {
         // ---- producer warp: one lane streams this CTA's rows into the ring ---------------
         // Weights do not depend on the previous kernel in the stream, so under programmatic
         // dependent launch the ring starts filling while that kernel is still draining.
         if (lane == 0) {
+            // Weights are read exactly once: mark them evict-first so that the stream does not push
+            // the activations (re-read by every CTA) and the outputs out of L2.
+            const uint64_t policy = make_l2_policy_evict_first();
             int issued = 0;
-            for (int ps = 0; ps < (p.probe == 2 ? 0 : npass); ++ps) {
+            for (int ps = 0; ps < (p.probe >= 2 ? 0 : npass); ++ps) {
                 const int s = ps % p.stages;
                 if (ps >= p.stages) {
                     if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
@@ -404,11 +594,13 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 const int r0 = ps * rows_per_pass;
                 const int rows = min(rows_per_pass, nrows - r0);
                 const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
+                if (ps == 0) TRACEP(10);
                 mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
-                bulk_g2s(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
-                         smem_u32(&bar_full[s]));
+                bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
+                              smem_u32(&bar_full[s]), policy);
                 issued = ps + 1;
             }
+            TRACEP(11);
             // Do not leave while copies into this CTA's shared memory may still be in flight:
             // wait (bounded) for the last use of every stage that was issued.
             const int first = issued > p.stages ? issued - p.stages : 0;
@@ -432,6 +624,8 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
 
     // Activations depend on the previous kernel in the stream.
     pdl_wait_prior();
+    TRACE(2);
+    if (p.probe == 3) return;  // profiling aid: the cost of an empty kernel in the chain
 
     Dec dec;
     if (Dec::kCoop && p.coop_off >= 0) {
@@ -441,6 +635,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
             const int item = base + tid;
             Dec::stage_quarter(p.x, item, item < nitems, area);
         }
+        TRACE(3);
         asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
         if (active) dec.load(area + (size_t)pair * 2 * Dec::kStateWordsPerBlock);
         else dec.load(area);  // idle lanes: any valid state, their results are never used
@@ -460,6 +655,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
         dec.init(tmp);
     }
 
+    TRACE(4);
     // Loop state is kept incremental (stage index, phase bit, rows left): an integer divide or
     // modulo per pass costs more ALU-pipe slots than the pass's own mask instructions.
     const uint8_t *my_words = smem + 4 * (rsub * (p.row_bytes >> 2) + pair * kWords);
@@ -483,6 +679,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 atomicExch(p.err, kDevErrFullWait);
                 dead = true;
             }
+            if (pbase == 0 && u == 0) TRACE(5);
             float v[RPT];
 #pragma unroll
             for (int j = 0; j < RPT; ++j) v[j] = 0.0f;
@@ -505,6 +702,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 phase ^= 1;
             }
         }
+        if (pbase == 0) TRACE(6);
         float part[kPassUnroll];
 #pragma unroll
         for (int i = 0; i < kPassUnroll; ++i) part[i] = (i < ucount * RPT) ? stash[i * cthreads + tid] : 0.0f;
@@ -561,6 +759,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 if ((lane % L) == 0) red[buf][u][rsub * p.wpr + wir] = t;
             }
         }
+        if (pbase == 0) TRACE(7);
         // consumer-only barrier (the producer warp is not part of it)
         asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
         for (int t = tid; t < kPassUnroll * p.rpp; t += cthreads) {
@@ -573,8 +772,10 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 p.y[row_begin + r] = tot;
             }
         }
+        if (pbase == 0) TRACE(8);
         buf ^= 1;
     }
+    TRACE(9);
 }
 
 // ---- plain kernel ------------------------------------------------------------------------
@@ -723,7 +924,7 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     // Cooperative activation slicing pays off when several row groups share the CTA; its staging
     // area holds 10 words per block and slice (sized for three slices).
     size_t coop_bytes = (size_t)nb * 3 * 10 * sizeof(uint32_t);
-    if (rpp <= 1 || coop_bytes > 24576 || ctx->tune.gemv_coop == 0) coop_bytes = 0;
+    if (rpp <= 1 || coop_bytes > 49152 || ctx->tune.gemv_coop == 0) coop_bytes = 0;
     const size_t budget = per_cta > kStaticSmemReserve + stash_bytes + coop_bytes ? per_cta - kStaticSmemReserve - stash_bytes - coop_bytes : 0;
     int stages = ctx->tune.stages < 2 ? 2 : (ctx->tune.stages > kMaxStages ? kMaxStages : ctx->tune.stages);
     if ((size_t)stage_bytes * 2 > budget) return false;
@@ -741,7 +942,9 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     smem = (size_t)stage_bytes * stages + stash_bytes + coop_bytes;
     p.coop_off = coop_bytes ? (int)((size_t)stage_bytes * stages + stash_bytes) : -1;
     const int64_t max_ctas = (n + rpp * rpt - 1) / (rpp * rpt);
-    int64_t g = (int64_t)ctx->sm_count * (ctx->tune.ctas_per_sm < 1 ? 1 : ctx->tune.ctas_per_sm);
+    // 0 = automatic: geometries that fit two CTAs per SM use both slots (more warps in flight).
+    const int per_sm = ctx->tune.ctas_per_sm > 0 ? ctx->tune.ctas_per_sm : (two_per_sm ? 2 : 1);
+    int64_t g = (int64_t)ctx->sm_count * per_sm;
     if (g > max_ctas) g = max_ctas;
     grid = (int)g;
     return true;
@@ -840,7 +1043,8 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
             switch (ctx->tune.gemv_variant) {
                 case 1: s = run_stream<DecFma<QT, ORDER>>(ctx, p, rpt, grid, threads, smem); break;
                 case 3: s = run_stream<DecSlices<QT, ORDER, 3>>(ctx, p, rpt, grid, threads, smem); break;
-                default: s = run_stream<DecSlices<QT, ORDER, 2>>(ctx, p, rpt, grid, threads, smem); break;
+                case 2: s = run_stream<DecSlices<QT, ORDER, 2>>(ctx, p, rpt, grid, threads, smem); break;
+                default: s = run_stream<DecQ16<QT, ORDER>>(ctx, p, rpt, grid, threads, smem); break;
             }
             if (s != CQ_OK) return s;
         }

@@ -149,7 +149,7 @@ def test_gemv_f32_matches_cpu_path(device, qt, order, n, k):
     got = gpu_qmatmul(device, qt, order, x, blocks, n)
     err = rel_err(got, want)
     assert err <= REL_TOL
-    assert err < 1e-4, f"two int8 activation slices should stay near 1e-5, got {err}"
+    assert err < 1e-4, f"16-bit activations should stay near 1e-5, got {err}"
 
 
 @pytest.mark.parametrize("qt,order", QT_ORDERS)
@@ -189,11 +189,11 @@ def test_gemv_result_does_not_depend_on_launch_geometry(device, warps, stages, c
     finally:
         device.set_option("gemv_warps", 8)
         device.set_option("gemv_stages", 8)
-        device.set_option("gemv_ctas_per_sm", 1)
+        device.set_option("gemv_ctas_per_sm", 0)
     assert rel_err(got, want) < 1e-4
 
 
-@pytest.mark.parametrize("variant,bound", [(0, 1e-4), (1, 2e-5), (3, 2e-5)])
+@pytest.mark.parametrize("variant,bound", [(0, 1e-4), (1, 2e-5), (2, 1e-4), (3, 2e-5)])
 @pytest.mark.parametrize("qt,order", QT_ORDERS)
 @pytest.mark.parametrize("n,k", [(513, 4096), (200, 11008), (64, 256), (37, 1024)])
 def test_gemv_decoder_variants(device, variant, bound, qt, order, n, k):
