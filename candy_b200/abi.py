@@ -55,6 +55,7 @@ SIGNATURES = {
     "cq_quantize_q8_1": [_vp, _vp, _i64, _i64, _i64, _vp],
     "cq_qmatmul": [_vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
     "cq_qmatmul_host": [_vp, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _vp],
+    "cq_qmatmul_q8_1_static": [_vp, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
     "cq_capture_begin": [_vp],
     "cq_capture_end": [_vp, C.POINTER(_vp)],
     "cq_graph_launch": [_vp, _vp],

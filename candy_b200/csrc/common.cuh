@@ -73,6 +73,8 @@ cq_status launch_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w
 cq_status launch_quantize_q8_1(cq_ctx *ctx, const float *x, int64_t m, int64_t k, int64_t ldx, void *out);
 cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,
                       int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
+cq_status launch_gemv_q8_1_blocks(cq_ctx *ctx, int qtype, int order, const void *act_blocks, int64_t m, int64_t k,
+                                  const void *w, int64_t n, float *y, int64_t ldy);
 cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,
                       int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
 

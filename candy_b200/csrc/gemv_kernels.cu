@@ -1066,3 +1066,15 @@ cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     if (qtype == CQ_Q4_0) return gemv_dispatch<CQ_Q4_0, 1>(ctx, actmode, x, m, k, ldx, wb, n, y, ldy);
     return gemv_dispatch<CQ_Q8_0, 0>(ctx, actmode, x, m, k, ldx, wb, n, y, ldy);
 }
+
+// The Q8_1-activation GEMV on activation blocks the caller has already quantized (36-byte
+// blocks, m rows of k/32).  Same kernels as the CQ_ACT_Q8_1 branch above.
+cq_status launch_gemv_q8_1_blocks(cq_ctx *ctx, int qtype, int order, const void *act_blocks, int64_t m, int64_t k,
+                                  const void *w, int64_t n, float *y, int64_t ldy) {
+    const uint8_t *wb = static_cast<const uint8_t *>(w);
+    const uint8_t *ab = static_cast<const uint8_t *>(act_blocks);
+    const int nb = (int)(k / kQK);
+    if (qtype == CQ_Q4_0 && order == CQ_ORDER_GO_INTERLEAVED) return run_q8_1<CQ_Q4_0, 0>(ctx, wb, ab, y, m, n, nb, ldy);
+    if (qtype == CQ_Q4_0) return run_q8_1<CQ_Q4_0, 1>(ctx, wb, ab, y, m, n, nb, ldy);
+    return run_q8_1<CQ_Q8_0, 0>(ctx, wb, ab, y, m, n, nb, ldy);
+}

@@ -137,6 +137,22 @@ cq_status cq_qmatmul_host(cq_ctx *ctx, int qtype, int order, int actmode, const 
                           int64_t m, int64_t k, const void *w_blocks_dev, int64_t n,
                           float *y_host);
 
+/* Same product as cq_qmatmul(..., CQ_ACT_Q8_1, ...) for m <= 8, for callers that cannot let
+ * the library allocate: hosts that gave all device memory to their own arena at start-up, or
+ * language runtimes (cgo, JNI) whose GPU glue may not call the CUDA allocator.  It has no
+ * counterpart in the reference.  The quantized activations go to a fixed 294,912-byte array
+ * that is part of the library image on every GPU (held from load to process exit), so:
+ *  - limits: m <= 8 and k <= 32768, beyond which it returns CQ_ERR_TOO_LARGE;
+ *  - it never calls cudaMalloc / cudaFree or any allocating routine;
+ *  - the first call on each device looks the array's address up (cudaGetSymbolAddress) --
+ *    make that first call outside any stream capture;
+ *  - all calls on one GPU, from any context or stream, share the array: two calls that may
+ *    overlap on the GPU race on it.  Issue them on one stream, or order them yourself.
+ *    Every call overwrites the part of the array it reads, so no clearing is ever needed. */
+cq_status cq_qmatmul_q8_1_static(cq_ctx *ctx, int qtype, int order, const float *x_dev, int64_t m,
+                                 int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n,
+                                 float *y_dev, int64_t ldy);
+
 /* ---- CUDA graphs and device timing ----------------------------------------------------
  * Decode loops are launch-bound: a GEMV lasts a few microseconds.  These wrap stream capture
  * so a host in any language can record a sequence of cq_* launches once and replay it.
