@@ -1,0 +1,328 @@
+// Prefill GEMM (m > 8): Y[m,n] = X[m,k] . W[n,k]^T on the 5th-generation tensor cores.
+//
+// CQ_ACT_F16 numerics: activations rounded to f16, weights dequantized (exactly, in f32) and
+// rounded once to f16, products exact, accumulation in f32 inside the tensor core.  Against
+// candy's CPU path (f32 activations, conv.go:373-389) this differs by the two f16 roundings:
+// ~3e-4 of max|y| on the benchmark's distributions, inside the 1e-3 bar.  Why not int8 MMAs:
+// each 32-block carries its own scale on BOTH operands (d_w[n,b] * d_x[m,b]), a rank-1 factor per
+// block that no single int8 operand can absorb, so an int8 design has to drain the accumulator
+// every 32 values of k and rescale on CUDA cores -- about 4 CUDA-core instructions per 32 MACs,
+// which caps it near one eighth of the int8 pipe, below this f16 kernel, and single-slice int8
+// activations miss the 1e-3 bar against the CPU path (5.8e-3) anyway.
+//
+// Two steps.  (1) streaming conversion kernels write f16 copies of X [m,k] and W [n,k] into
+// context scratch (HBM-bound: 18/34 B in, 64 B out per block).  (2) gemm_f16_tn_kernel: one CTA
+// per 128 x 256 output tile; a producer lane feeds a 4-stage shared-memory ring with TMA tensor
+// loads (128-byte swizzle, K-major tiles of 64 values); one lane issues tcgen05.mma
+// (cta_group::1, kind::f16, M=128, N=256, K=16 x 4 per stage) into a 256-column f32 accumulator
+// in tensor memory; tcgen05.commit hands stages back to the producer and, at the end, the
+// accumulator to four epilogue warps that read it with tcgen05.ld and store f32 rows.
+// Every mbarrier wait is bounded; a give-up sets the context's error word and the CTA still
+// reaches the final barrier and frees its tensor memory.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int GEMM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int TMEM_COLS = 256;
+
+// ---- f16 conversion kernels -------------------------------------------------------------
+__global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                                                     __half *__restrict__ out) {
+    const int64_t total = m * (k / 4);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / (k / 4), c4 = i - row * (k / 4);
+        const float *src = x + row * ldx + c4 * 4;
+        __half2 a = __floats2half2_rn(src[0], src[1]), b = __floats2half2_rn(src[2], src[3]);
+        uint2 v;
+        v.x = *reinterpret_cast<uint32_t *>(&a);
+        v.y = *reinterpret_cast<uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(out + row * k + c4 * 4) = v;
+    }
+}
+
+// One thread converts 8 consecutive values of a block (one 16-byte store).  The f32 value
+// d*(q-8) (or d*q) is exact, so the only rounding is f32 -> f16, round-to-nearest-even.
+template <int QT, int ORDER>
+__global__ void __launch_bounds__(256) w_to_f16_kernel(const uint8_t *__restrict__ blocks, int64_t nblocks,
+                                                     __half *__restrict__ out) {
+    const int64_t total = nblocks * 4;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t blk = idx >> 2;
+        const int p = (int)(idx & 3);  // values 8p .. 8p+7
+        float v[8];
+        if (QT == CQ_Q4_0) {
+            const uint8_t *b = blocks + blk * kQ4Bytes;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b)));
+            if (ORDER == CQ_ORDER_GO_INTERLEAVED) {
+                const uint8_t *qs = b + 2 + 4 * p;  // bytes 4p..4p+3 -> values 8p..8p+7
+                const uint32_t four = *reinterpret_cast<const unsigned short *>(qs) |
+                                      ((uint32_t) * reinterpret_cast<const unsigned short *>(qs + 2) << 16);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = d * (float)((int)((four >> (4 * i)) & 0xF) - 8);
+            } else {
+                const uint8_t *qs = b + 2 + 8 * (p & 1);  // values 8p..8p+7 = low (p<2) or high nibbles of 8 bytes
+                const int sh = (p >= 2) ? 4 : 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = d * (float)((int)((qs[i] >> sh) & 0xF) - 8);
+            }
+        } else {
+            const uint8_t *b = blocks + blk * kQ8Bytes;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b)));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = d * (float)(int)(signed char)b[2 + 8 * p + i];
+        }
+        __half2 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(out + idx * 8) = *reinterpret_cast<uint4 *>(h);
+    }
+}
+
+// ---- tcgen05 / TMA wrappers -------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], f16 inputs, f32 accumulate.
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what a TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row atoms 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: D f32, A/B f16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t idesc_f16(int mm, int nn) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(nn >> 3) << 17) | ((uint32_t)(mm >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, float *__restrict__ y, int M,
+                       int N, int K, int64_t ldy, int *err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smA = smem;                              // [STAGES][A_BYTES]
+    uint8_t *smB = smem + (size_t)STAGES * A_BYTES;   // [STAGES][B_BYTES]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * (A_BYTES + B_BYTES));
+    uint64_t *full = bars, *empty = bars + STAGES, *acc_full = bars + 2 * STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int nk = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        mbar_init(smem_u32(acc_full), 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < nk; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ((kb / STAGES) - 1) & 1)) {
+                    atomicExch(err, kDevErrEmptyWait);
+                    break;
+                }
+                mbar_expect_tx(smem_u32(&full[s]), A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(smA + (size_t)s * A_BYTES), &tmA, kb * BK, tile_m * BM, smem_u32(&full[s]));
+                tma_load_2d(smem_u32(smB + (size_t)s * B_BYTES), &tmB, kb * BK, tile_n * BN, smem_u32(&full[s]));
+                issued = kb + 1;
+            }
+            // never leave with copies in flight into this CTA's shared memory
+            const int first = issued > STAGES ? issued - STAGES : 0;
+            for (int kb = first; kb < issued; ++kb)
+                if (!mbar_wait_bounded(smem_u32(&full[kb % STAGES]), (kb / STAGES) & 1)) {
+                    atomicExch(err, kDevErrDrain);
+                    break;
+                }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < nk && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait_bounded(smem_u32(&full[s]), (kb / STAGES) & 1)) {
+                    atomicExch(err, kDevErrFullWait);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(smA + (size_t)s * A_BYTES), b0 = smem_u32(smB + (size_t)s * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)  // 16 values of k = 32 bytes inside the 128-byte swizzled row
+                    tc_mma_f16(tmem_base, smem_desc_k128(a0 + 32 * k), smem_desc_k128(b0 + 32 * k), idesc, (kb | k) != 0);
+                tc_commit(smem_u32(&empty[s]));  // arrives when these MMAs have finished reading the stage
+            }
+            tc_commit(smem_u32(acc_full));  // arrives when every MMA issued so far has completed
+        }
+    } else {
+        // epilogue warps 2..5: warp w may touch TMEM lanes 32*(w%4) .. +31 only
+        const int q = warp & 3;
+        if (mbar_wait_bounded(smem_u32(acc_full), 0)) {
+            tc_fence_after();
+            const int64_t row = (int64_t)tile_m * BM + q * 32 + lane;
+            const int col0 = tile_n * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                const int col = col0 + c * 32;
+                if (row < M) {
+                    float *dst = y + row * ldy + col;
+                    if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col + i < N) dst[i] = __uint_as_float(r[i]);
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(err, kDevErrMma);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- host side ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// f16 [rows, k] row-major; box = 64 values of k x box_rows rows, 128-byte swizzle, zero fill outside.
+bool make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx,
+                      const void *w, int64_t n, float *y, int64_t ldy) {
+    if (actmode != CQ_ACT_F16) {
+        // f32 / Q8_1 activation numerics for m > 8: the decode kernels, eight rows at a time
+        // (weights are re-read once per eight rows; the tensor-core path is CQ_ACT_F16).
+        for (int64_t r = 0; r < m; r += 8) {
+            const int64_t rows = (m - r) < 8 ? (m - r) : 8;
+            cq_status s = launch_gemv(ctx, qtype, order, actmode, x + r * ldx, rows, k, ldx, w, n, y + r * ldy, ldy);
+            if (s != CQ_OK) return s;
+        }
+        return CQ_OK;
+    }
+    if ((reinterpret_cast<uintptr_t>(w) & 1) != 0 || (reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
+    if (m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
+    const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
+    const size_t w16_bytes = (size_t)n * k * 2;
+    cq_status s = cq_reserve_scratch(ctx, x16_bytes + w16_bytes);
+    if (s != CQ_OK) return s;
+    __half *x16 = static_cast<__half *>(ctx->scratch);
+    __half *w16 = reinterpret_cast<__half *>(static_cast<uint8_t *>(ctx->scratch) + x16_bytes);
+    const unsigned cap = (unsigned)ctx->sm_count * 16;
+    {
+        const int64_t total = m * (k / 4);
+        const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+        x_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(x, m, k, ldx, x16);
+    }
+    {
+        const int64_t nblocks = n * (k / kQK);
+        const int64_t total = nblocks * 4;
+        const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+        const uint8_t *wb = static_cast<const uint8_t *>(w);
+        if (qtype == CQ_Q4_0 && order == CQ_ORDER_GO_INTERLEAVED) w_to_f16_kernel<CQ_Q4_0, 0><<<grid, 256, 0, ctx->stream>>>(wb, nblocks, w16);
+        else if (qtype == CQ_Q4_0) w_to_f16_kernel<CQ_Q4_0, 1><<<grid, 256, 0, ctx->stream>>>(wb, nblocks, w16);
+        else w_to_f16_kernel<CQ_Q8_0, 0><<<grid, 256, 0, ctx->stream>>>(wb, nblocks, w16);
+    }
+    CQ_CUDA(ctx, cudaGetLastError());
+    CUtensorMap tmA, tmB;
+    if (!make_map(&tmA, x16, m, k, BM) || !make_map(&tmB, w16, n, k, BN))
+        return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
+    static thread_local int configured_device = -1;
+    if (configured_device != ctx->device) {
+        CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
+        configured_device = ctx->device;
+    }
+    dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+    gemm_f16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
+    CQ_CUDA(ctx, cudaGetLastError());
+    return CQ_OK;
+}

@@ -1,0 +1,70 @@
+"""Prefill GEMM (m > 8) on the tensor cores, CQ_ACT_F16, through the C ABI.
+
+Two checks per case: (1) against a NumPy emulation of the mode's own arithmetic -- activations and
+dequantized weights each rounded once to f16, products summed in f64 -- where only f32 accumulation
+order may differ (bound 2e-5); (2) against candy's CPU path (the oracle) under the stated bar,
+max|y - y_ref| / max|y_ref| <= 1e-3.  At the BASELINE config-3 sizes the CPU path is evaluated on a
+sample of activation rows (the scalar oracle needs ~1e11 operations for all of them)."""
+import numpy as np
+import pytest
+
+from helpers import REL_TOL, make_case, rel_err
+from oracle import oracle_c as oc
+
+pytestmark = pytest.mark.gpu
+ACT_F16 = 2
+
+
+def emulate_f16(qt, order, x, blocks, n):
+    k = x.shape[1]
+    w16 = oc.dequantize(qt, order, blocks).reshape(n, k).astype(np.float16).astype(np.float64)
+    x16 = x.astype(np.float16).astype(np.float64)
+    return x16 @ w16.T
+
+
+def run(device, qt, order, x, blocks, n, actmode=ACT_F16):
+    from candy_b200.backend import QStorage
+    m, k = x.shape
+    qs = QStorage.from_blocks(device, qt, order, n, k, blocks)
+    xs = device.storage_from_slice(x)
+    y = xs.matmul(qs, 1, m, n, k, actmode).data().reshape(m, n)
+    device.synchronize()
+    return y
+
+
+@pytest.mark.parametrize("qt,order", [(oc.Q4_0, 0), (oc.Q4_0, 1), (oc.Q8_0, 0)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (16, 300, 512), (130, 257, 96), (9, 40, 32),
+                                   (512, 1024, 4096), (300, 700, 1056)])
+def test_gemm_f16_small_and_ragged(device, qt, order, m, n, k):
+    w, x = make_case(5000 + m + n + k, n, k, m)
+    blocks = oc.quantize(qt, order, w)
+    got = run(device, qt, order, x, blocks, n)
+    assert rel_err(got, emulate_f16(qt, order, x, blocks, n)) < 2e-5
+    rows = np.linspace(0, m - 1, num=min(m, 6), dtype=int)
+    cpu = oc.qmatmul(qt, order, x[rows], blocks, n, nthreads=8)
+    assert rel_err(got[rows], cpu) <= REL_TOL
+
+
+@pytest.mark.parametrize("qt", [oc.Q4_0, oc.Q8_0])
+@pytest.mark.parametrize("m", [16, 128, 512, 2048])
+def test_config3_prefill_gemm(device, qt, m):
+    n, k = 11008, 4096
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    blocks = oc.quantize(qt, 0, w)
+    got = run(device, qt, 0, x, blocks, n)
+    assert rel_err(got, emulate_f16(qt, 0, x, blocks, n)) < 2e-5
+    rows = np.linspace(0, m - 1, num=4, dtype=int)
+    cpu = oc.qmatmul(qt, 0, x[rows], blocks, n, nthreads=8)
+    err = rel_err(got[rows], cpu)
+    assert err <= REL_TOL, f"f16-operand GEMM vs CPU path: {err}"
+
+
+@pytest.mark.parametrize("actmode", [0, 1])
+def test_wide_batches_in_f32_and_q8_1_modes_use_the_decode_kernels(device, actmode):
+    w, x = make_case(77, 96, 1024, 19)
+    blocks = oc.quantize(oc.Q4_0, 0, w)
+    got = run(device, oc.Q4_0, 0, x, blocks, 96, actmode=actmode)
+    want = oc.qmatmul(oc.Q4_0, 0, x, blocks, 96, nthreads=8, q8_1=bool(actmode))
+    assert rel_err(got, want) < 1e-4
