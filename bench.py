@@ -345,9 +345,9 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture; see
-# profiles/.  None until a capture has been summarised there.
-NCU_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) of one launch of the dominant kernel (n=32000, k=4096) from the ncu
+# capture summarised in profiles/gemv_q4_0_32000x4096.md: 73.79 MB read + 0.96 MB written.
+NCU_TRAFFIC_BYTES = 73787136 + 956160
 
 
 def run_reference(args):
@@ -424,6 +424,21 @@ def run_kernel_only(args):
     print(json.dumps({"kernel_only": [n, k], "launches": args.launches, "ring_copies": len(wl.rings[0])}))
 
 
+def run_gemm_only(args):
+    """A few plain launches of the prefill GEMM (CQ_ACT_F16) on one shape: the case ncu captures."""
+    from candy_b200.backend import CudaDevice, QStorage
+    m, n, k = (int(v) for v in args.gemm_only.lower().split("x"))
+    dev = CudaDevice(int(os.environ.get("LOCAL_RANK", "0")))
+    rng = np.random.default_rng(1)
+    q = QStorage.quantize(dev, Q4_0, ORDER, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
+    y = dev.alloc(m * n)
+    for _ in range(args.launches):
+        dev._check(dev._lib.cq_qmatmul(dev.ctx, Q4_0, ORDER, 2, x.ptr, m, k, k, q.buf.ptr, n, y.ptr, n), "qmatmul")
+    dev.synchronize()
+    print(json.dumps({"gemm_only": [m, n, k], "launches": args.launches}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -432,11 +447,15 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--kernel-only", default=None, metavar="NxK", help="profiling aid: launch one GEMV shape a few times")
+    ap.add_argument("--gemm-only", default=None, metavar="MxNxK", help="profiling aid: launch the prefill GEMM a few times")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--option", action="append", default=[], metavar="KEY=INT", help="library tuning option (kernel-only mode)")
     args = ap.parse_args()
     if args.kernel_only:
         run_kernel_only(args)
+        return
+    if args.gemm_only:
+        run_gemm_only(args)
         return
     if args.impl == "reference":
         args.steps = 20 if args.steps is None else args.steps

@@ -150,7 +150,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    // m-tiles vary fastest across the grid: a wave of CTAs then shares a handful of B tiles (and all
+    // of A), so the f16 weight copy crosses HBM about once instead of once per few m-tiles.
+    const int tile_m = blockIdx.x, tile_n = blockIdx.y;
     const int nk = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -321,7 +323,7 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
         CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
         configured_device = ctx->device;
     }
-    dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+    dim3 grid((unsigned)((m + BM - 1) / BM), (unsigned)((n + BN - 1) / BN));
     gemm_f16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
     CQ_CUDA(ctx, cudaGetLastError());
     return CQ_OK;
