@@ -56,6 +56,16 @@ SIGNATURES = {
     "cq_qmatmul": [_vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
     "cq_qmatmul_host": [_vp, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _vp],
     "cq_qmatmul_q8_1_static": [_vp, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
+    "cq_rand_normal": [_vp, _vp, _i64, C.c_float, C.c_float, C.c_uint64],
+    "cq_rand_uniform": [_vp, _vp, _i64, C.c_float, C.c_float, C.c_uint64],
+    "cq_rmsnorm": [_vp, _vp, _vp, _i64, _i64, C.c_float, _vp],
+    "cq_add_rmsnorm": [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _vp],
+    "cq_rope_store_kv": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int],
+    "cq_decode_attention": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _int, _vp, _vp],
+    "cq_silu_mul": [_vp, _vp, _i64, _i64, _vp],
+    "cq_argmax": [_vp, _vp, _i64, _i64, _vp],
+    "cq_embedding": [_vp, _vp, _i64, _i64, _vp, _i64, _vp],
+    "cq_add_int": [_vp, _vp, _int],
     "cq_capture_begin": [_vp],
     "cq_capture_end": [_vp, C.POINTER(_vp)],
     "cq_graph_launch": [_vp, _vp],
@@ -68,6 +78,7 @@ _OTHER_RESTYPE = {
     "cq_last_error": (C.c_char_p, [_vp]),
     "cq_version": (C.c_char_p, []),
     "cq_blocks_bytes": (_sz, [_int, _i64, _i64]),
+    "cq_decode_attention_scratch_floats": (_sz, [_i64, _int, _int, _int]),
 }
 
 

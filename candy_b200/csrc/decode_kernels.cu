@@ -1,0 +1,393 @@
+// The small kernels a decoder step needs around the quantized linears, each following the
+// arithmetic of candy's CPU kernels (paths inside a gocnn/candy checkout):
+//   RMSNorm        tensor/internal/cpu/kernels/reduce.go:3071-3092  (FastRmsNormF32)
+//   softmax        reduce.go:2855-2879 (FastSoftmaxF32), inside the decode-attention kernel
+//   RoPE           reduce.go:3987-4006 (RopeF32: half-split pairs (i, i + d/2), cos/sin tables)
+//   SiLU           tensor/internal/cpu/kernels/unary.go:3353-3365 (USiluF32, evaluated in f64)
+//   argmax         reduce.go:846-862 (FastArgmaxF32: strict >, the lowest index wins ties)
+//   embedding      tensor/internal/cpu/kernels/indexing.go:8-26 (index select of rows)
+// All are HBM- or latency-bound streaming kernels over a few KB..MB; none touches weights.
+// They take part in programmatic dependent launch like the GEMV: trigger the dependents at
+// entry, wait for the previous kernel before reading its output.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o, 32);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o, 32));
+    return v;
+}
+
+// Block-wide sum over blockDim.x threads (multiple of 32, <= 1024); result in every thread.
+__device__ __forceinline__ float block_sum(float v, float *sh) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float t = (lane < nw) ? sh[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+// y = x * rsqrt(mean(x^2) + eps) * alpha, one CTA per row; optionally x += delta first (the
+// residual add that precedes every norm in a decoder layer), written back to x.
+template <bool ADD>
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ delta,
+                                                     const float *__restrict__ alpha, int cols, float eps, float *__restrict__ y) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    float *xr = x + (int64_t)blockIdx.x * cols;
+    const float *dr = ADD ? delta + (int64_t)blockIdx.x * cols : nullptr;
+    float *yr = y + (int64_t)blockIdx.x * cols;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float v = xr[c];
+        if (ADD) {
+            v += dr[c];
+            xr[c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, sh);
+    const float mean = ss / (float)cols;
+    const float scale = 1.0f / sqrtf(mean + eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = xr[c];  // own writes above are visible to the same thread
+        yr[c] = alpha ? scale * v * alpha[c] : scale * v;
+    }
+}
+
+// qkv: [B, (nq + 2 nkv) * hd].  Rotates q in place and k (half-split pairs), then stores k and v
+// of every sequence at position *pos of its cache [B][max_ctx][nkv*hd].
+__global__ void __launch_bounds__(256) rope_store_kv_kernel(float *__restrict__ qkv, int nq, int nkv, int hd,
+                                                          const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                                          const int *__restrict__ pos_dev, float *__restrict__ kc,
+                                                          float *__restrict__ vc, int max_ctx) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int b = blockIdx.y;
+    const int pos = *pos_dev;
+    const int half = hd / 2;
+    const int row = (nq + 2 * nkv) * hd;
+    float *base = qkv + (int64_t)b * row;
+    const int npairs = (nq + nkv) * half;
+    const int64_t cache_row = ((int64_t)b * max_ctx + pos) * (int64_t)(nkv * hd);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < npairs + nkv * hd; i += gridDim.x * blockDim.x) {
+        if (i < npairs) {
+            const int head = i / half, d = i - head * half;  // heads 0..nq-1 are q, then nkv k heads
+            float *p = base + head * hd;
+            const float c = cos_t[(int64_t)pos * half + d], s = sin_t[(int64_t)pos * half + d];
+            const float a = p[d], bb = p[d + half];
+            const float r1 = a * c - bb * s, r2 = a * s + bb * c;
+            p[d] = r1;
+            p[d + half] = r2;
+            if (head >= nq) {
+                float *kdst = kc + cache_row + (head - nq) * hd;
+                kdst[d] = r1;
+                kdst[d + half] = r2;
+            }
+        } else {
+            const int j = i - npairs;  // v values
+            vc[cache_row + j] = base[(nq + nkv) * hd + j];
+        }
+    }
+}
+
+constexpr int kAttnChunk = 128;   // keys per CTA
+constexpr int kAttnThreads = 128;
+
+// One CTA per (query head, sequence, chunk of 128 keys): scores, chunk-local softmax numerators
+// and the weighted sum of V; writes (max, sum, acc[hd]) for the combine kernel.  hd <= 256.
+__global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float *__restrict__ qkv, int nq, int nkv, int hd,
+                                                                  const int *__restrict__ pos_dev, const float *__restrict__ kc,
+                                                                  const float *__restrict__ vc, int max_ctx, float scale,
+                                                                  float *__restrict__ part, int nchunks) {
+    __shared__ float q_s[256];
+    __shared__ float p_s[kAttnChunk];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int head = blockIdx.x, b = blockIdx.y, chunk = blockIdx.z;
+    const int nkeys = *pos_dev + 1;
+    const int t0 = chunk * kAttnChunk;
+    float *out = part + (((int64_t)b * nq + head) * nchunks + chunk) * (hd + 2);
+    if (t0 >= nkeys) {  // chunk beyond the current length: neutral element
+        if (threadIdx.x == 0) {
+            out[0] = -3.402823466e38f;
+            out[1] = 0.0f;
+        }
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) out[2 + d] = 0.0f;
+        return;
+    }
+    const int t1 = min(t0 + kAttnChunk, nkeys);
+    const int kvh = head / (nq / nkv);
+    const int row = (nq + 2 * nkv) * hd;
+    const float *q = qkv + (int64_t)b * row + head * hd;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) q_s[d] = q[d];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int64_t kv_stride = (int64_t)nkv * hd;
+    const float *kbase = kc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
+    const float *vbase = vc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
+    // scores: one warp per key, lanes stride the head dimension
+    for (int t = t0 + warp; t < t1; t += nw) {
+        const float *k = kbase + (int64_t)t * kv_stride;
+        float s = 0.0f;
+        for (int d = lane; d < hd; d += 32) s = fmaf(q_s[d], k[d], s);
+        s = warp_sum(s);
+        if (lane == 0) p_s[t - t0] = s * scale;
+    }
+    __syncthreads();
+    float m = -3.402823466e38f;
+    for (int i = threadIdx.x; i < t1 - t0; i += blockDim.x) m = fmaxf(m, p_s[i]);
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = (lane < nw) ? red[lane] : -3.402823466e38f;
+    m = warp_max(m);
+    float l = 0.0f;
+    for (int i = threadIdx.x; i < t1 - t0; i += blockDim.x) {
+        const float e = expf(p_s[i] - m);
+        p_s[i] = e;
+        l += e;
+    }
+    l = block_sum(l, red);  // also orders the p_s writes before the reads below
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int t = t0; t < t1; ++t) acc = fmaf(p_s[t - t0], vbase[(int64_t)t * kv_stride + d], acc);
+        out[2 + d] = acc;
+    }
+    if (threadIdx.x == 0) {
+        out[0] = m;
+        out[1] = l;
+    }
+}
+
+// Combines the chunk partials of one (head, sequence): out[b][head*hd + d].
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, int nq, int hd, int nchunks,
+                                                         float *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int head = blockIdx.x, b = blockIdx.y;
+    const float *p = part + (((int64_t)b * nq + head) * nchunks) * (hd + 2);
+    float m = -3.402823466e38f;
+    for (int c = 0; c < nchunks; ++c) m = fmaxf(m, p[(int64_t)c * (hd + 2)]);
+    float l = 0.0f;
+    for (int c = 0; c < nchunks; ++c) l += p[(int64_t)c * (hd + 2) + 1] * expf(p[(int64_t)c * (hd + 2)] - m);
+    const float inv = 1.0f / l;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = 0; c < nchunks; ++c) acc = fmaf(p[(int64_t)c * (hd + 2) + 2 + d], expf(p[(int64_t)c * (hd + 2)] - m), acc);
+        out[((int64_t)b * nq + head) * hd + d] = acc * inv;
+    }
+}
+
+// out[b][i] = silu(gu[b][i]) * gu[b][n + i]; silu evaluated in f64 like USiluF32.
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, int n, int64_t total, float *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / n, c = i - b * n;
+        const double g = (double)gu[b * 2 * n + c];
+        const float s = (float)(g / (1.0 + exp(-g)));
+        out[i] = s * gu[b * 2 * n + n + c];
+    }
+}
+
+// One CTA per row; the lowest index among equal maxima wins, as the sequential strict '>' does.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ x, int cols, uint32_t *__restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const float *xr = x + (int64_t)blockIdx.x * cols;
+    float best = -3.402823466e38f;
+    int bi = 0x7FFFFFFF;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = xr[c];
+        if (v > best) {
+            best = v;
+            bi = c;
+        }
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o, 32);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o, 32);
+        if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
+    }
+    if (lane == 0) sv[w] = best, si[w] = bi;
+    __syncthreads();
+    if (w == 0) {
+        best = (lane < nw) ? sv[lane] : -3.402823466e38f;
+        bi = (lane < nw) ? si[lane] : 0x7FFFFFFF;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o, 32);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o, 32);
+            if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
+        }
+        // every value <= -FLT_MAX (or NaN): the sequential loop never updates and returns index 0
+        if (lane == 0) out[blockIdx.x] = (bi == 0x7FFFFFFF) ? 0u : (uint32_t)bi;
+    }
+}
+
+__global__ void __launch_bounds__(256) embedding_kernel(const float *__restrict__ table, const uint32_t *__restrict__ ids, int dim,
+                                                      int64_t vocab, float *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int b = blockIdx.x;
+    int64_t id = ids[b];
+    if (id >= vocab) id = vocab - 1;  // never read outside the table
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) out[(int64_t)b * dim + c] = table[id * dim + c];
+}
+
+__global__ void add_int_kernel(int *p, int delta) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    if (threadIdx.x == 0 && blockIdx.x == 0) *p += delta;
+}
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+// Counter-based normal / uniform fill: value i depends only on (seed, i).
+__global__ void __launch_bounds__(256) rand_fill_kernel(float *__restrict__ out, int64_t n, uint64_t seed, float a, float b, int normal) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = mix64(seed * 0x9E3779B97F4A7C15ull + (uint64_t)i + 0x632BE59BD9B4E019ull);
+        const float u1 = ((float)(uint32_t)(r >> 40) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
+        const float u2 = (float)(uint32_t)((r >> 8) & 0xFFFFFF) * (1.0f / 16777216.0f);
+        if (normal) out[i] = a + b * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+        else out[i] = a + (b - a) * u2;
+    }
+}
+
+template <typename Kern, typename... Args>
+cq_status launch_pdl(cq_ctx *ctx, Kern kern, dim3 grid, dim3 block, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, args...));
+    return CQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+cq_status cq_rand_normal(cq_ctx *ctx, float *out_dev, int64_t n, float mean, float std, uint64_t seed) {
+    CQ_ENTER(ctx);
+    if (!out_dev || n < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rand_normal: bad arguments");
+    if (n == 0) return CQ_OK;
+    const unsigned grid = (unsigned)((n + 255) / 256 < (int64_t)ctx->sm_count * 32 ? (n + 255) / 256 : (int64_t)ctx->sm_count * 32);
+    rand_fill_kernel<<<grid, 256, 0, ctx->stream>>>(out_dev, n, seed, mean, std, 1);
+    CQ_CUDA(ctx, cudaGetLastError());
+    return CQ_OK;
+}
+
+cq_status cq_rand_uniform(cq_ctx *ctx, float *out_dev, int64_t n, float lo, float hi, uint64_t seed) {
+    CQ_ENTER(ctx);
+    if (!out_dev || n < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rand_uniform: bad arguments");
+    if (n == 0) return CQ_OK;
+    const unsigned grid = (unsigned)((n + 255) / 256 < (int64_t)ctx->sm_count * 32 ? (n + 255) / 256 : (int64_t)ctx->sm_count * 32);
+    rand_fill_kernel<<<grid, 256, 0, ctx->stream>>>(out_dev, n, seed, lo, hi, 0);
+    CQ_CUDA(ctx, cudaGetLastError());
+    return CQ_OK;
+}
+
+cq_status cq_rmsnorm(cq_ctx *ctx, const float *x_dev, const float *alpha_dev, int64_t rows, int64_t cols, float eps, float *y_dev) {
+    CQ_ENTER(ctx);
+    if (!x_dev || !y_dev || rows < 1 || cols < 1 || cols > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rmsnorm: bad arguments");
+    const int threads = cols >= 4096 ? 1024 : (cols >= 1024 ? 512 : 256);
+    return launch_pdl(ctx, rmsnorm_kernel<false>, dim3((unsigned)rows), dim3(threads), const_cast<float *>(x_dev), (const float *)nullptr,
+                      alpha_dev, (int)cols, eps, y_dev);
+}
+
+cq_status cq_add_rmsnorm(cq_ctx *ctx, float *x_dev, const float *delta_dev, const float *alpha_dev, int64_t rows, int64_t cols, float eps,
+                         float *y_dev) {
+    CQ_ENTER(ctx);
+    if (!x_dev || !delta_dev || !y_dev || rows < 1 || cols < 1 || cols > 0x7FFFFFFF)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm: bad arguments");
+    const int threads = cols >= 4096 ? 1024 : (cols >= 1024 ? 512 : 256);
+    return launch_pdl(ctx, rmsnorm_kernel<true>, dim3((unsigned)rows), dim3(threads), x_dev, delta_dev, alpha_dev, (int)cols, eps, y_dev);
+}
+
+cq_status cq_rope_store_kv(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim, const float *cos_dev,
+                           const float *sin_dev, const int *pos_dev, float *k_cache_dev, float *v_cache_dev, int max_ctx) {
+    CQ_ENTER(ctx);
+    if (!qkv_dev || !cos_dev || !sin_dev || !pos_dev || !k_cache_dev || !v_cache_dev)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rope_store_kv: null pointer");
+    if (batch < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 2 || head_dim % 2 != 0 || max_ctx < 1)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rope_store_kv: bad shape");
+    const int work = (n_q_heads + n_kv_heads) * head_dim / 2 + n_kv_heads * head_dim;
+    return launch_pdl(ctx, rope_store_kv_kernel, dim3((unsigned)((work + 255) / 256), (unsigned)batch), dim3(256), qkv_dev, n_q_heads,
+                      n_kv_heads, head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx);
+}
+
+size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head_dim, int max_ctx) {
+    const int nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+    return (size_t)batch * n_q_heads * nchunks * (head_dim + 2);
+}
+
+cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim,
+                              const int *pos_dev, const float *k_cache_dev, const float *v_cache_dev, int max_ctx, float *scratch_dev,
+                              float *out_dev) {
+    CQ_ENTER(ctx);
+    if (!qkv_dev || !pos_dev || !k_cache_dev || !v_cache_dev || !scratch_dev || !out_dev)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: null pointer");
+    if (batch < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 1 || head_dim > 256 || max_ctx < 1)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: bad shape (head_dim <= 256)");
+    const int nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    cq_status s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads),
+                             qkv_dev, n_q_heads, n_kv_heads, head_dim, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
+    if (s != CQ_OK) return s;
+    return launch_pdl(ctx, attn_combine_kernel, dim3((unsigned)n_q_heads, (unsigned)batch), dim3(128), (const float *)scratch_dev, n_q_heads,
+                      head_dim, nchunks, out_dev);
+}
+
+cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev) {
+    CQ_ENTER(ctx);
+    if (!gate_up_dev || !out_dev || rows < 1 || n < 1 || n > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_silu_mul: bad arguments");
+    const int64_t total = rows * n;
+    const unsigned grid = (unsigned)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
+    return launch_pdl(ctx, silu_mul_kernel, dim3(grid), dim3(256), gate_up_dev, (int)n, total, out_dev);
+}
+
+cq_status cq_argmax(cq_ctx *ctx, const float *x_dev, int64_t rows, int64_t cols, uint32_t *out_dev) {
+    CQ_ENTER(ctx);
+    if (!x_dev || !out_dev || rows < 1 || cols < 1 || cols > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_argmax: bad arguments");
+    return launch_pdl(ctx, argmax_kernel, dim3((unsigned)rows), dim3(1024), x_dev, (int)cols, out_dev);
+}
+
+cq_status cq_embedding(cq_ctx *ctx, const float *table_dev, int64_t vocab, int64_t dim, const uint32_t *ids_dev, int64_t rows, float *out_dev) {
+    CQ_ENTER(ctx);
+    if (!table_dev || !ids_dev || !out_dev || vocab < 1 || dim < 1 || rows < 1 || dim > 0x7FFFFFFF)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_embedding: bad arguments");
+    return launch_pdl(ctx, embedding_kernel, dim3((unsigned)rows), dim3(256), table_dev, ids_dev, (int)dim, vocab, out_dev);
+}
+
+cq_status cq_add_int(cq_ctx *ctx, int *value_dev, int delta) {
+    CQ_ENTER(ctx);
+    if (!value_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_int: null pointer");
+    return launch_pdl(ctx, add_int_kernel, dim3(1), dim3(32), value_dev, delta);
+}
+
+}  // extern "C"

@@ -1,0 +1,194 @@
+"""A Llama-shape decoder step built only from libcandyq calls: the caller of the quantized
+linear that BASELINE configs 4 and 5 measure (tokens/s of greedy decode; tensor-parallel layers).
+
+candy itself has no LLM code (llm/ holds a README and a FlashAttention binding), so this module
+is the host-side loop a candy user would write against the backend API: embedding gather, then
+per layer RMSNorm -> fused QKV linear -> RoPE + KV-cache write -> decode attention -> o linear ->
+residual + RMSNorm -> fused gate/up linear -> SiLU*mul -> down linear, then final norm, output
+linear and argmax.  Every operator is a kernel of the library; positions and token ids stay on
+the device, so one step can be captured into a CUDA graph and replayed once per token.
+
+Tensor parallelism (world > 1): QKV / gate / up are split by output rows (whole heads), o / down
+by input columns, and `allreduce` (supplied by the caller, e.g. NCCL through torch.distributed)
+sums the two row-parallel outputs of each layer.  Each rank creates only its own shards.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import numpy as np
+
+from . import abi
+from .backend import CudaDevice, QStorage, RawBuffer, Q4_0, ORDER_GO_INTERLEAVED, ACT_F32
+
+
+@dataclass
+class DecoderConfig:
+    n_layers: int = 32
+    dim: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    vocab: int = 32000
+    max_ctx: int = 384
+    eps: float = 1e-5
+    rope_theta: float = 10000.0
+    with_head: bool = True  # embedding + output linear + argmax (a bare layer stack otherwise)
+
+
+def shard_sizes(cfg: DecoderConfig, world: int):
+    """Per-rank sizes under tensor parallelism; raises if heads or ffn do not divide."""
+    if cfg.n_heads % world or cfg.n_kv_heads % world or cfg.ffn % world:
+        raise ValueError(f"tensor parallel degree {world} must divide heads ({cfg.n_heads}), kv heads ({cfg.n_kv_heads}) and ffn ({cfg.ffn})")
+    nq, nkv, ffn = cfg.n_heads // world, cfg.n_kv_heads // world, cfg.ffn // world
+    if (nq * cfg.head_dim) % 32 or ffn % 32:
+        raise ValueError("row-parallel shards must keep k a multiple of 32 so no block is cut")
+    return nq, nkv, ffn
+
+
+def rope_tables(cfg: DecoderConfig):
+    """cos/sin [max_ctx, head_dim/2] in f32 from f64 angles (the tables RopeF32 takes as inputs)."""
+    half = cfg.head_dim // 2
+    inv = 1.0 / (cfg.rope_theta ** (np.arange(half, dtype=np.float64) * 2.0 / cfg.head_dim))
+    ang = np.arange(cfg.max_ctx, dtype=np.float64)[:, None] * inv[None, :]
+    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+
+class QuantDecoder:
+    def __init__(self, dev: CudaDevice, cfg: DecoderConfig, seed: int = 0, batch: int = 1, qtype: int = Q4_0,
+                 order: int = ORDER_GO_INTERLEAVED, rank: int = 0, world: int = 1,
+                 allreduce: Optional[Callable[[object, int], None]] = None, actmode: int = ACT_F32):
+        self.dev, self.cfg, self.batch, self.qtype, self.order = dev, cfg, batch, qtype, order
+        self.rank, self.world, self.allreduce, self.actmode = rank, world, allreduce, actmode
+        if world > 1 and allreduce is None:
+            raise ValueError("tensor parallel decoder needs an allreduce callback")
+        self.nq, self.nkv, self.ffn = shard_sizes(cfg, world)
+        self.lib, self.ctx = dev._lib, dev.ctx
+        hd, dim = cfg.head_dim, cfg.dim
+        self.qkv_rows = (self.nq + 2 * self.nkv) * hd
+        self.kv_dim = self.nkv * hd
+        # ---- weights: generated and quantized on the device, shard by shard ------------------
+        biggest = max(self.qkv_rows * dim, dim * self.nq * hd, 2 * self.ffn * dim, dim * self.ffn,
+                      (cfg.vocab * dim) if cfg.with_head else 0)
+        tmp = dev.alloc(biggest)
+        self.layers = []
+        for l in range(cfg.n_layers):
+            s = (seed * 1000003 + l) * 16 + rank * 4099
+            self.layers.append({
+                "wqkv": self._rand_q(tmp, self.qkv_rows, dim, s + 1),
+                "wo": self._rand_q(tmp, dim, self.nq * hd, s + 2),
+                "wgu": self._rand_q(tmp, 2 * self.ffn, dim, s + 3),
+                "wdown": self._rand_q(tmp, dim, self.ffn, s + 4),
+                "attn_norm": dev.storage_from_slice(np.ones(dim, dtype=np.float32)),
+                "ffn_norm": dev.storage_from_slice(np.ones(dim, dtype=np.float32)),
+                "k": dev.zeros(batch * cfg.max_ctx * self.kv_dim),
+                "v": dev.zeros(batch * cfg.max_ctx * self.kv_dim),
+            })
+        if cfg.with_head:
+            self.embed = dev.alloc(cfg.vocab * dim)
+            self._check(self.lib.cq_rand_normal(self.ctx, self.embed.ptr, cfg.vocab * dim, 0.0, 0.02, seed * 7919 + 11), "rand")
+            self.wout = self._rand_q(tmp, cfg.vocab, dim, seed * 7919 + 13)
+            self.final_norm = dev.storage_from_slice(np.ones(dim, dtype=np.float32))
+            self.logits = dev.alloc(batch * cfg.vocab)
+        del tmp
+        cos, sin = rope_tables(cfg)
+        self.cos, self.sin = dev.storage_from_slice(cos), dev.storage_from_slice(sin)
+        # ---- activations --------------------------------------------------------------------
+        self.x = dev.zeros(batch * dim)
+        self.xn = dev.alloc(batch * dim)
+        self.qkv = dev.alloc(batch * self.qkv_rows)
+        self.att = dev.alloc(batch * self.nq * hd)
+        self.o = dev.alloc(batch * dim)
+        self.gu = dev.alloc(batch * 2 * self.ffn)
+        self.h = dev.alloc(batch * self.ffn)
+        self.d = dev.zeros(batch * dim)
+        self.att_scratch = dev.alloc(self.lib.cq_decode_attention_scratch_floats(batch, self.nq, hd, cfg.max_ctx))
+        self.ids = RawBuffer(dev, 4 * batch)
+        self.pos = RawBuffer(dev, 4)
+        self.set_state(np.zeros(batch, dtype=np.uint32), 0)
+        dev.synchronize()
+
+    # ---- helpers ----------------------------------------------------------------------------
+    def _check(self, st, where):
+        abi.check(self.ctx, st, where)
+
+    def _rand_q(self, tmp, n, k, seed) -> QStorage:
+        self._check(self.lib.cq_rand_normal(self.ctx, tmp.ptr, n * k, 0.0, 0.02, seed), "rand normal")
+        buf = RawBuffer(self.dev, n * (k // 32) * abi.BLOCK_BYTES[self.qtype])
+        self._check(self.lib.cq_quantize_rows(self.ctx, self.qtype, self.order, tmp.ptr, n, k, buf.ptr), "quantize")
+        return QStorage(self.dev, self.qtype, self.order, n, k, buf)
+
+    def _linear(self, w: QStorage, x, y):
+        self._check(self.lib.cq_qmatmul(self.ctx, w.qtype, w.order, self.actmode, x.ptr, self.batch, w.k, w.k, w.buf.ptr, w.n,
+                                        y.ptr, w.n), "qmatmul")
+
+    def set_state(self, ids: np.ndarray, pos: int):
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        p = np.array([pos], dtype=np.int32)
+        self._check(self.lib.cq_memcpy_h2d(self.ctx, self.ids.ptr, ids.ctypes.data_as(C.c_void_p), ids.nbytes), "ids")
+        self._check(self.lib.cq_memcpy_h2d(self.ctx, self.pos.ptr, p.ctypes.data_as(C.c_void_p), 4), "pos")
+
+    def weight_bytes_per_step(self) -> int:
+        """Quantized weight bytes one decode step streams on this rank."""
+        per_layer = sum(self.layers[0][k].buf.nbytes for k in ("wqkv", "wo", "wgu", "wdown"))
+        return per_layer * self.cfg.n_layers + (self.wout.buf.nbytes if self.cfg.with_head else 0)
+
+    def launches_per_step(self) -> int:
+        return self.cfg.n_layers * 10 + (5 if self.cfg.with_head else 1)
+
+    # ---- one decode step, enqueued on the context's stream -----------------------------------
+    def step(self, advance: bool = True):
+        lib, ctx, cfg, B = self.lib, self.ctx, self.cfg, self.batch
+        hd, dim = cfg.head_dim, cfg.dim
+        if cfg.with_head:
+            self._check(lib.cq_embedding(ctx, self.embed.ptr, cfg.vocab, dim, self.ids.ptr, B, self.x.ptr), "embedding")
+        first = True
+        for L in self.layers:
+            if first and cfg.with_head:  # x was just gathered from the embedding table
+                self._check(lib.cq_rmsnorm(ctx, self.x.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "rmsnorm")
+                first = False
+            else:  # residual of the previous feed-forward (previous layer, or previous step of a bare stack), then the norm
+                first = False
+                self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.d.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
+            self._linear(L["wqkv"], self.xn, self.qkv)
+            self._check(lib.cq_rope_store_kv(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.cos.ptr, self.sin.ptr, self.pos.ptr,
+                                             L["k"].ptr, L["v"].ptr, cfg.max_ctx), "rope")
+            self._check(lib.cq_decode_attention(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.pos.ptr, L["k"].ptr, L["v"].ptr,
+                                                cfg.max_ctx, self.att_scratch.ptr, self.att.ptr), "attention")
+            self._linear(L["wo"], self.att, self.o)
+            if self.world > 1:
+                self.allreduce(self.o, B * dim)
+            self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.o.ptr, L["ffn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
+            self._linear(L["wgu"], self.xn, self.gu)
+            self._check(lib.cq_silu_mul(ctx, self.gu.ptr, B, self.ffn, self.h.ptr), "silu*mul")
+            self._linear(L["wdown"], self.h, self.d)
+            if self.world > 1:
+                self.allreduce(self.d, B * dim)
+        if cfg.with_head:
+            self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.d.ptr, self.final_norm.ptr, B, dim, cfg.eps, self.xn.ptr), "final norm")
+            self._linear(self.wout, self.xn, self.logits)
+            self._check(lib.cq_argmax(ctx, self.logits.ptr, B, cfg.vocab, self.ids.ptr), "argmax")
+        if advance:
+            self._check(lib.cq_add_int(ctx, self.pos.ptr, 1), "advance")
+
+    def capture(self, steps: int = 1):
+        g = C.c_void_p()
+        self._check(self.lib.cq_capture_begin(self.ctx), "capture begin")
+        for _ in range(steps):
+            self.step()
+        self._check(self.lib.cq_capture_end(self.ctx, C.byref(g)), "capture end")
+        return g
+
+    def replay(self, g, times: int = 1):
+        for _ in range(times):
+            self._check(self.lib.cq_graph_launch(self.ctx, g), "graph launch")
+
+    def read_logits(self) -> np.ndarray:
+        return self.logits.data().reshape(self.batch, self.cfg.vocab)
+
+    def read_ids(self) -> np.ndarray:
+        return self.ids.data().view(np.uint32).copy()

@@ -153,6 +153,48 @@ cq_status cq_qmatmul_q8_1_static(cq_ctx *ctx, int qtype, int order, const float 
                                  int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n,
                                  float *y_dev, int64_t ldy);
 
+/* ---- the operators around the linears in a decoder step ---------------------------------
+ * f32, row-major, asynchronous on the context's stream.  Each follows candy's CPU kernel of the
+ * same name (file:line in tensor/internal/cpu/kernels/). */
+/* BackendDevice.RandNormal / RandUniform (device.go:60-66): counter-based, value i depends only
+ * on (seed, i).  The reference's CPU device cannot be seeded (cpu/device.go:48-51). */
+cq_status cq_rand_normal(cq_ctx *ctx, float *out_dev, int64_t n, float mean, float std, uint64_t seed);
+cq_status cq_rand_uniform(cq_ctx *ctx, float *out_dev, int64_t n, float lo, float hi, uint64_t seed);
+/* BackendStorage.FastRmsNorm (backend.go:158-159; FastRmsNormF32, reduce.go:3071-3092):
+ * y = x / sqrt(mean(x^2) + eps) * alpha over the last dimension; alpha may be NULL. */
+cq_status cq_rmsnorm(cq_ctx *ctx, const float *x_dev, const float *alpha_dev, int64_t rows, int64_t cols,
+                     float eps, float *y_dev);
+/* x += delta (BackendStorage.Add, backend.go:20), then y = rmsnorm(x): the residual add and the
+ * norm that follows it in a decoder layer, in one pass. */
+cq_status cq_add_rmsnorm(cq_ctx *ctx, float *x_dev, const float *delta_dev, const float *alpha_dev,
+                         int64_t rows, int64_t cols, float eps, float *y_dev);
+/* BackendStorage.Rope (backend.go:152-153; RopeF32, reduce.go:3987-4006: pairs (i, i + d/2), cos/sin
+ * tables [max_ctx, d/2]) applied at position *pos_dev to the q and k heads of
+ * qkv[batch, (n_q + 2 n_kv) * head_dim]; the rotated k and the v of every sequence are then
+ * stored at that position of the caches [batch][max_ctx][n_kv * head_dim]. */
+cq_status cq_rope_store_kv(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads,
+                           int head_dim, const float *cos_dev, const float *sin_dev, const int *pos_dev,
+                           float *k_cache_dev, float *v_cache_dev, int max_ctx);
+/* One query per sequence against keys 0..*pos_dev of its cache: scores q.k / sqrt(head_dim),
+ * softmax as FastSoftmaxF32 (reduce.go:2855-2879), weighted sum of v.  Grouped-query heads
+ * (n_q_heads a multiple of n_kv_heads), head_dim <= 256.  scratch_dev needs
+ * cq_decode_attention_scratch_floats(...) floats.  out[batch, n_q_heads * head_dim]. */
+size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head_dim, int max_ctx);
+cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, int n_q_heads,
+                              int n_kv_heads, int head_dim, const int *pos_dev, const float *k_cache_dev,
+                              const float *v_cache_dev, int max_ctx, float *scratch_dev, float *out_dev);
+/* out[r, i] = silu(gu[r, i]) * gu[r, n + i]: BackendStorage.Silu (USiluF32, unary.go:3353-3365,
+ * evaluated in f64) fused with the Mul of a SwiGLU feed-forward. */
+cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev);
+/* BackendStorage.FastArgmax (backend.go:128-129; FastArgmaxF32, reduce.go:846-862): the lowest
+ * index among equal maxima. */
+cq_status cq_argmax(cq_ctx *ctx, const float *x_dev, int64_t rows, int64_t cols, uint32_t *out_dev);
+/* Row gather, out[r, :] = table[ids[r], :] (index select; indexing.go:8-26). */
+cq_status cq_embedding(cq_ctx *ctx, const float *table_dev, int64_t vocab, int64_t dim,
+                       const uint32_t *ids_dev, int64_t rows, float *out_dev);
+/* *value_dev += delta on the stream (advances a decode position inside a captured graph). */
+cq_status cq_add_int(cq_ctx *ctx, int *value_dev, int delta);
+
 /* ---- CUDA graphs and device timing ----------------------------------------------------
  * Decode loops are launch-bound: a GEMV lasts a few microseconds.  These wrap stream capture
  * so a host in any language can record a sequence of cq_* launches once and replay it.

@@ -1,0 +1,86 @@
+"""NumPy restatement of one decoder step with candy's CPU arithmetic (test infrastructure).
+
+Linears go through the C oracle (dequantize + sequential f32 matmul); the operators between them
+follow the CPU kernels in tensor/internal/cpu/kernels/: FastRmsNormF32 (reduce.go:3071-3092),
+RopeF32 (reduce.go:3987-4006), FastSoftmaxF32 (reduce.go:2855-2879), USiluF32 (unary.go:3353-3365,
+f64 inside), FastArgmaxF32 (reduce.go:846-862).  Sums over a row are taken with np.float32
+accumulation; their order differs from the sequential Go loops by rounding only.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import oracle_c as oc
+
+f32 = np.float32
+
+
+def rmsnorm(x, alpha, eps):
+    mean = (x.astype(f32) ** 2).sum(dtype=f32) / f32(x.size)
+    scale = f32(1.0) / f32(np.sqrt(np.float64(mean + f32(eps))))
+    return (scale * x * alpha).astype(f32)
+
+
+def rope(v, cos, sin):
+    """v: [heads, head_dim]; pairs (i, i + d/2)."""
+    half = v.shape[1] // 2
+    a, b = v[:, :half].copy(), v[:, half:].copy()
+    out = np.empty_like(v)
+    out[:, :half] = a * cos - b * sin
+    out[:, half:] = a * sin + b * cos
+    return out
+
+
+def softmax(s):
+    m = s.max()
+    e = np.exp((s - m).astype(np.float64)).astype(f32)
+    return (e * (f32(1.0) / e.sum(dtype=f32))).astype(f32)
+
+
+def silu(x):
+    x64 = x.astype(np.float64)
+    return (x64 / (1.0 + np.exp(-x64))).astype(f32)
+
+
+class OracleDecoder:
+    """Single sequence.  `layers` is a list of dicts with the Q-blocks (uint8) of wqkv, wo, wgu, wdown."""
+
+    def __init__(self, cfg, qtype, order, layers, embed=None, wout=None, cos=None, sin=None, nq=None, nkv=None, ffn=None):
+        self.cfg, self.qt, self.order, self.layers = cfg, qtype, order, layers
+        self.embed, self.wout, self.cos, self.sin = embed, wout, cos, sin
+        self.nq = nq or cfg.n_heads
+        self.nkv = nkv or cfg.n_kv_heads
+        self.ffn = ffn or cfg.ffn
+        self.k = [np.zeros((cfg.max_ctx, self.nkv, cfg.head_dim), dtype=f32) for _ in layers]
+        self.v = [np.zeros((cfg.max_ctx, self.nkv, cfg.head_dim), dtype=f32) for _ in layers]
+
+    def lin(self, x, blocks, n):
+        return oc.qmatmul(self.qt, self.order, x.reshape(1, -1), blocks, n, nthreads=8)[0]
+
+    def step(self, token: int, pos: int):
+        cfg = self.cfg
+        hd, dim = cfg.head_dim, cfg.dim
+        x = self.embed[token].astype(f32).copy()
+        ones = np.ones(dim, dtype=f32)
+        for li, L in enumerate(self.layers):
+            xn = rmsnorm(x, ones, cfg.eps)
+            qkv = self.lin(xn, L["wqkv"], (self.nq + 2 * self.nkv) * hd)
+            q = rope(qkv[: self.nq * hd].reshape(self.nq, hd), self.cos[pos], self.sin[pos])
+            k = rope(qkv[self.nq * hd:(self.nq + self.nkv) * hd].reshape(self.nkv, hd), self.cos[pos], self.sin[pos])
+            v = qkv[(self.nq + self.nkv) * hd:].reshape(self.nkv, hd)
+            self.k[li][pos], self.v[li][pos] = k, v
+            att = np.empty((self.nq, hd), dtype=f32)
+            group = self.nq // self.nkv
+            for h in range(self.nq):
+                kh = self.k[li][: pos + 1, h // group]
+                s = (kh @ q[h]).astype(f32) * f32(1.0 / np.sqrt(hd))
+                p = softmax(s)
+                att[h] = (p[:, None] * self.v[li][: pos + 1, h // group]).sum(axis=0, dtype=f32)
+            x = x + self.lin(att.reshape(-1), L["wo"], dim)
+            xn = rmsnorm(x, ones, cfg.eps)
+            gu = self.lin(xn, L["wgu"], 2 * self.ffn)
+            h_ = silu(gu[: self.ffn]) * gu[self.ffn:]
+            x = x + self.lin(h_, L["wdown"], dim)
+        xn = rmsnorm(x, ones, cfg.eps)
+        logits = self.lin(xn, self.wout, cfg.vocab)
+        return logits
