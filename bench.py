@@ -332,9 +332,20 @@ def run_ours(args):
         "roofline": roofline, "per_shape": per_shape, "e2e": e2e, "gpu_launches": K * len(SHAPES),
         "clocks": clocks.summary(),
     }
+    cpu_inputs = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        blocks = [q.data() for q in wl.qs0]
-        xs = [x.data().reshape(1, -1) for x in wl.xs]
+        cpu_inputs = ([q.data() for q in wl.qs0], [x.data().reshape(1, -1) for x in wl.xs])
+    for g in (g_main, g_tail, g_warm):
+        if g is not None:
+            lib.cq_graph_destroy(ctx, g)
+    del wl  # free the rings before the secondary workloads
+    if not args.skip_extras:
+        from candy_b200 import bench_workloads as bw
+        if world == 1:
+            line["decode_7b"] = bw.decode_7b(dev, peak)
+        line["tp_layer_70b"] = bw.tp_layer_70b(dev, dist, rank, world, local_rank, peak)
+    if cpu_inputs is not None:
+        blocks, xs = cpu_inputs
         line["cpu_baseline"] = cpu_baseline(blocks, xs, threads=1)
     elif rank == 0:
         line["cpu_baseline"] = None
@@ -439,6 +450,23 @@ def run_gemm_only(args):
     print(json.dumps({"gemm_only": [m, n, k], "launches": args.launches}))
 
 
+def run_decode_only(args):
+    """A few un-captured decode steps of a shallow 7B-width model: the case ncu lists kernel by kernel."""
+    from candy_b200.backend import CudaDevice
+    from candy_b200.decoder import DecoderConfig, QuantDecoder
+    dev = CudaDevice(int(os.environ.get("LOCAL_RANK", "0")))
+    for kv in args.option:
+        key, val = kv.split("=")
+        dev.set_option(key, int(val))
+    cfg = DecoderConfig(n_layers=args.decode_only, dim=4096, n_heads=32, n_kv_heads=32, head_dim=128, ffn=11008, vocab=32000, max_ctx=384)
+    model = QuantDecoder(dev, cfg, seed=2)
+    model.set_state(np.array([1], dtype=np.uint32), 255)
+    for _ in range(args.launches):
+        model.step(advance=False)
+    dev.synchronize()
+    print(json.dumps({"decode_only_layers": args.decode_only, "steps": args.launches, "launches_per_step": model.launches_per_step()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -446,8 +474,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--skip-extras", action="store_true", help="skip the 7B decode and 70B tensor-parallel layer workloads")
     ap.add_argument("--kernel-only", default=None, metavar="NxK", help="profiling aid: launch one GEMV shape a few times")
     ap.add_argument("--gemm-only", default=None, metavar="MxNxK", help="profiling aid: launch the prefill GEMM a few times")
+    ap.add_argument("--decode-only", type=int, default=0, metavar="LAYERS", help="profiling aid: a few plain decode steps of a shallow 7B-width model")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--option", action="append", default=[], metavar="KEY=INT", help="library tuning option (kernel-only mode)")
     args = ap.parse_args()
@@ -456,6 +486,9 @@ def main():
         return
     if args.gemm_only:
         run_gemm_only(args)
+        return
+    if args.decode_only:
+        run_decode_only(args)
         return
     if args.impl == "reference":
         args.steps = 20 if args.steps is None else args.steps

@@ -1,0 +1,144 @@
+"""Secondary workloads of bench.py: the 7B-shape greedy decode (BASELINE config 4) and the
+70B-shape tensor-parallel layer stack (config 5).  Both drive candy_b200.decoder.QuantDecoder;
+timing is CUDA-event time on the launching stream, graph-replayed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import time
+
+import numpy as np
+
+from .decoder import DecoderConfig, QuantDecoder
+
+
+def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: int = 2, n_layers: int = 32):
+    """32 layers, d=4096, 32 heads x 128, SwiGLU 11008, vocab 32000, Q4_0, batch 1: processes `prompt`
+    uniform-random ids one token at a time (the decode path is the only path measured), then times
+    `decode` greedy tokens as replays of a one-step CUDA graph."""
+    cfg = DecoderConfig(n_layers=n_layers, dim=4096, n_heads=32, n_kv_heads=32, head_dim=128, ffn=11008, vocab=32000,
+                        max_ctx=prompt + decode)
+    t0 = time.perf_counter()
+    model = QuantDecoder(dev, cfg, seed=seed)
+    build_s = time.perf_counter() - t0
+    lib, ctx = dev._lib, dev.ctx
+    ids = np.random.default_rng(seed).integers(0, cfg.vocab, size=prompt)
+    model.set_state(np.array([ids[0]], dtype=np.uint32), 0)
+    model.step()  # first launches outside any capture
+    dev.synchronize()
+    for pos in range(prompt):
+        model.set_state(np.array([ids[pos]], dtype=np.uint32), pos)
+        model.step()
+    dev.synchronize()
+    model.set_state(model.read_ids(), prompt)  # continue from the model's own prediction
+    g = model.capture(1)
+    ms = C.c_float()
+    dev.synchronize()
+    lib.cq_timer_start(ctx)
+    model.replay(g, decode)
+    lib.cq_timer_stop(ctx, C.byref(ms))
+    dev.synchronize()
+    lib.cq_graph_destroy(ctx, g)
+    tok_s = decode / (ms.value * 1e-3)
+    wbytes = model.weight_bytes_per_step()
+    kv_bytes_mid = cfg.n_layers * 2 * (prompt + decode // 2) * cfg.n_heads * cfg.head_dim * 4
+    return {
+        "tok_s": round(tok_s, 1), "ms_per_token": round(ms.value / decode, 4), "prompt_tokens": prompt, "decode_tokens": decode,
+        "n_layers": n_layers, "weight_bytes_per_token": wbytes, "kv_bytes_per_token_mid": kv_bytes_mid,
+        "weight_gbs": round(wbytes * tok_s / 1e9, 1), "frac_of_peak": round(wbytes * tok_s / 1e9 / peak_gbs, 4),
+        "roofline_tok_s": round(peak_gbs * 1e9 / wbytes, 1), "launches_per_token": model.launches_per_step(),
+        "build_seconds": round(build_s, 1),
+    }
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ view of a device buffer, so torch can wrap it without a copy."""
+
+    def __init__(self, ptr: int, count: int):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+
+
+def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: float, batches=(1, 32), ctx_len: int = 2048,
+                 n_layers: int = 8, reps: int = 30, seed: int = 3):
+    """8 layers of d=8192, 64 q / 8 kv heads x 128, ffn 28672, Q4_0; QKV/gate/up split by rows,
+    o/down by columns with an NCCL all-reduce (torch.distributed) after each; decode at a fixed
+    context of `ctx_len` keys (caches pre-filled with noise).  Returns per-batch step times."""
+    cfg = DecoderConfig(n_layers=n_layers, dim=8192, n_heads=64, n_kv_heads=8, head_dim=128, ffn=28672, vocab=0,
+                        max_ctx=ctx_len, with_head=False)
+    lib, ctx = dev._lib, dev.ctx
+    out = {"world": world, "n_layers": n_layers, "ctx": ctx_len}
+    torch = None
+    if world > 1:
+        import torch
+    for batch in batches:
+        views = {}
+
+        def allreduce(buf, count):
+            key = buf.ptr.value
+            if key not in views:
+                views[key] = torch.as_tensor(_CudaArray(key, count), device=torch.device("cuda", local_rank))
+            dist.all_reduce(views[key])
+
+        model = QuantDecoder(dev, cfg, seed=seed, batch=batch, rank=rank, world=world, allreduce=allreduce if world > 1 else None,
+                             actmode=0 if batch <= 8 else 2)
+        for L in model.layers:  # noise in the caches, as if ctx_len tokens had been decoded
+            n = batch * cfg.max_ctx * model.kv_dim
+            lib.cq_rand_normal(ctx, L["k"].ptr, n, 0.0, 1.0, seed + 101)
+            lib.cq_rand_normal(ctx, L["v"].ptr, n, 0.0, 1.0, seed + 202)
+        lib.cq_rand_normal(ctx, model.x.ptr, batch * cfg.dim, 0.0, 1.0, seed + 303)
+        model.set_state(np.zeros(batch, dtype=np.uint32), ctx_len - 1)
+        dev.synchronize()
+        if world == 1:
+            model.step(advance=False)
+            dev.synchronize()
+            lib.cq_capture_begin(ctx)
+            model.step(advance=False)
+            g = C.c_void_p()
+            model._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
+            model.replay(g, 3)
+            ms = C.c_float()
+            dev.synchronize()
+            lib.cq_timer_start(ctx)
+            model.replay(g, reps)
+            lib.cq_timer_stop(ctx, C.byref(ms))
+            lib.cq_graph_destroy(ctx, g)
+            step_ms = ms.value / reps
+        else:
+            stream = torch.cuda.Stream(device=local_rank)
+            dev.set_stream(stream.cuda_stream)
+            with torch.cuda.stream(stream):
+                model.step(advance=False)  # warm-up: NCCL channels, one-time kernel attributes, scratch
+                model.step(advance=False)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                model.step(advance=False)
+            dist.barrier()
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    graph.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0.record(stream)
+                for _ in range(reps):
+                    graph.replay()
+                e1.record(stream)
+            e1.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=torch.device("cuda", local_rank))
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            step_ms = float(t.item())
+            dev.set_stream(0)
+            del graph
+        wbytes_all = model.weight_bytes_per_step() * world
+        out[f"batch{batch}"] = {
+            "ms_per_step": round(step_ms, 4), "layers_per_s": round(n_layers / (step_ms * 1e-3), 1),
+            "tokens_per_s": round(batch / (step_ms * 1e-3), 1), "weight_bytes_per_step_all_ranks": wbytes_all,
+            "weight_gbs_all_ranks": round(wbytes_all / (step_ms * 1e-3) / 1e9, 1),
+            "frac_of_peak_per_gpu": round(wbytes_all / world / (step_ms * 1e-3) / 1e9 / peak_gbs, 4),
+            "allreduce": "none" if world == 1 else f"NCCL sum of [{batch},8192] f32, twice per layer",
+            "linear_mode": "f32 activations (decode GEMV)" if batch <= 8 else "f16 operands (tensor-core GEMM)",
+        }
+        del model
+        dev.synchronize()
+    return out

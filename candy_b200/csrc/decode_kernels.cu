@@ -100,18 +100,18 @@ __global__ void __launch_bounds__(256) rope_store_kv_kernel(float *__restrict__ 
     }
 }
 
-constexpr int kAttnChunk = 128;   // keys per CTA
+constexpr int kAttnChunk = 32;    // keys per CTA: short chunks keep many CTAs in flight at small contexts
 constexpr int kAttnThreads = 128;
 
-// One CTA per (query head, sequence, chunk of 128 keys): scores, chunk-local softmax numerators
-// and the weighted sum of V; writes (max, sum, acc[hd]) for the combine kernel.  hd <= 256.
+// One CTA per (query head, sequence, chunk of 32 keys): scores, chunk-local softmax numerators
+// and the weighted sum of V; writes (max, sum, acc[hd]) for the combine kernel.  hd <= 256 and a
+// multiple of 4.  Latency-bound (a few hundred KB per CTA out of L2/HBM), so every loop keeps
+// eight independent loads in flight.
 __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float *__restrict__ qkv, int nq, int nkv, int hd,
                                                                   const int *__restrict__ pos_dev, const float *__restrict__ kc,
                                                                   const float *__restrict__ vc, int max_ctx, float scale,
                                                                   float *__restrict__ part, int nchunks) {
-    __shared__ float q_s[256];
     __shared__ float p_s[kAttnChunk];
-    __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait_prior();
     const int head = blockIdx.x, b = blockIdx.y, chunk = blockIdx.z;
@@ -127,42 +127,85 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
         return;
     }
     const int t1 = min(t0 + kAttnChunk, nkeys);
+    const int cnt = t1 - t0;
     const int kvh = head / (nq / nkv);
     const int row = (nq + 2 * nkv) * hd;
     const float *q = qkv + (int64_t)b * row + head * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) q_s[d] = q[d];
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t kv_stride = (int64_t)nkv * hd;
     const float *kbase = kc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
     const float *vbase = vc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
-    // scores: one warp per key, lanes stride the head dimension
-    for (int t = t0 + warp; t < t1; t += nw) {
-        const float *k = kbase + (int64_t)t * kv_stride;
-        float s = 0.0f;
-        for (int d = lane; d < hd; d += 32) s = fmaf(q_s[d], k[d], s);
-        s = warp_sum(s);
-        if (lane == 0) p_s[t - t0] = s * scale;
+    // Every global load of the CTA is issued before the first use: q, this warp's 8 keys, and (for
+    // hd <= 128) this thread's 32 values of V.  One memory round trip instead of one per phase.
+    float4 kreg[8][2];
+    float4 qreg[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        const int d = lane * 4 + 128 * h2;
+        qreg[h2] = (d < hd) ? *reinterpret_cast<const float4 *>(q + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int t = t0 + warp * 8 + j;
+            kreg[j][h2] = (t < t1 && d < hd) ? *reinterpret_cast<const float4 *>(kbase + (int64_t)t * kv_stride + d)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float vreg[kAttnChunk];
+    const bool v_in_regs = hd <= kAttnThreads;
+    if (v_in_regs) {
+#pragma unroll
+        for (int j = 0; j < kAttnChunk; ++j)
+            vreg[j] = (j < cnt && (int)threadIdx.x < hd) ? vbase[(int64_t)(t0 + j) * kv_stride + threadIdx.x] : 0.0f;
+    }
+    {
+        float s[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j] = 0.0f;
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2)
+                s[j] = fmaf(qreg[h2].x, kreg[j][h2].x,
+                            fmaf(qreg[h2].y, kreg[j][h2].y, fmaf(qreg[h2].z, kreg[j][h2].z, fmaf(qreg[h2].w, kreg[j][h2].w, s[j]))));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o, 32);
+        if (lane < 8) {
+            float v = s[0];
+#pragma unroll
+            for (int j = 1; j < 8; ++j) v = (lane == j) ? s[j] : v;
+            p_s[warp * 8 + lane] = v * scale;
+        }
     }
     __syncthreads();
-    float m = -3.402823466e38f;
-    for (int i = threadIdx.x; i < t1 - t0; i += blockDim.x) m = fmaxf(m, p_s[i]);
-    m = warp_max(m);
-    if (lane == 0) red[warp] = m;
+    // chunk softmax numerators: every warp computes the same max / sum over the 32 scores
+    const float sc = (lane < cnt) ? p_s[lane] : -3.402823466e38f;
+    const float m = warp_max(sc);
+    const float e = (lane < cnt) ? expf(sc - m) : 0.0f;
+    const float l = warp_sum(e);
     __syncthreads();
-    m = (lane < nw) ? red[lane] : -3.402823466e38f;
-    m = warp_max(m);
-    float l = 0.0f;
-    for (int i = threadIdx.x; i < t1 - t0; i += blockDim.x) {
-        const float e = expf(p_s[i] - m);
-        p_s[i] = e;
-        l += e;
-    }
-    l = block_sum(l, red);  // also orders the p_s writes before the reads below
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int t = t0; t < t1; ++t) acc = fmaf(p_s[t - t0], vbase[(int64_t)t * kv_stride + d], acc);
-        out[2 + d] = acc;
+    if (warp == 0) p_s[lane] = e;
+    __syncthreads();
+    if (v_in_regs) {
+        if ((int)threadIdx.x < hd) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < kAttnChunk; ++j) acc[j & 3] = fmaf(p_s[j], vreg[j], acc[j & 3]);
+            out[2 + threadIdx.x] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
+    } else {
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+            for (int tb = 0; tb < cnt; tb += 8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (tb + j < cnt) acc[j] = fmaf(p_s[tb + j], vbase[(int64_t)(t0 + tb + j) * kv_stride + d], acc[j]);
+            }
+            out[2 + d] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+        }
     }
     if (threadIdx.x == 0) {
         out[0] = m;
@@ -173,31 +216,50 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
 // Combines the chunk partials of one (head, sequence): out[b][head*hd + d].
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, int nq, int hd, int nchunks,
                                                          float *__restrict__ out) {
+    __shared__ float w_s[512];  // per-chunk weight exp(m_c - m) / l; nchunks <= 512 (context <= 16384)
+    __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait_prior();
     const int head = blockIdx.x, b = blockIdx.y;
-    const float *p = part + (((int64_t)b * nq + head) * nchunks) * (hd + 2);
+    const int stride = hd + 2;
+    const float *p = part + (((int64_t)b * nq + head) * nchunks) * stride;
     float m = -3.402823466e38f;
-    for (int c = 0; c < nchunks; ++c) m = fmaxf(m, p[(int64_t)c * (hd + 2)]);
+    for (int c = threadIdx.x; c < nchunks; c += blockDim.x) m = fmaxf(m, p[(int64_t)c * stride]);
+    m = warp_max(m);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = (lane < nw) ? red[lane] : -3.402823466e38f;
+    m = warp_max(m);
     float l = 0.0f;
-    for (int c = 0; c < nchunks; ++c) l += p[(int64_t)c * (hd + 2) + 1] * expf(p[(int64_t)c * (hd + 2)] - m);
+    for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+        const float w = expf(p[(int64_t)c * stride] - m);
+        w_s[c] = w;
+        l += w * p[(int64_t)c * stride + 1];
+    }
+    l = block_sum(l, red);
     const float inv = 1.0f / l;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int c = 0; c < nchunks; ++c) acc = fmaf(p[(int64_t)c * (hd + 2) + 2 + d], expf(p[(int64_t)c * (hd + 2)] - m), acc);
-        out[((int64_t)b * nq + head) * hd + d] = acc * inv;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c = 0; c < nchunks; c += 4) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c + j < nchunks) acc[j] = fmaf(p[(int64_t)(c + j) * stride + 2 + d], w_s[c + j], acc[j]);
+        }
+        out[((int64_t)b * nq + head) * hd + d] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * inv;
     }
 }
 
 // out[b][i] = silu(gu[b][i]) * gu[b][n + i]; silu evaluated in f64 like USiluF32.
-__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, int n, int64_t total, float *__restrict__ out) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, int n, int64_t total, float *__restrict__ out,
+                                                     int64_t ld_out) {
     pdl_launch_dependents();
     pdl_wait_prior();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t b = i / n, c = i - b * n;
         const double g = (double)gu[b * 2 * n + c];
         const float s = (float)(g / (1.0 + exp(-g)));
-        out[i] = s * gu[b * 2 * n + n + c];
+        out[b * ld_out + c] = s * gu[b * 2 * n + n + c];
     }
 }
 
@@ -210,11 +272,35 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
     const float *xr = x + (int64_t)blockIdx.x * cols;
     float best = -3.402823466e38f;
     int bi = 0x7FFFFFFF;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-        const float v = xr[c];
-        if (v > best) {
-            best = v;
-            bi = c;
+    if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0 && cols <= 8 * 4 * (int)blockDim.x) {
+        // up to 8 float4 per thread, all loads issued before the first compare; a thread's elements
+        // are visited in increasing index order, so strict '>' keeps the lowest index of its maxima
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = (i * blockDim.x + threadIdx.x) * 4;
+            v[i] = (c + 3 < cols) ? *reinterpret_cast<const float4 *>(xr + c) : make_float4(-3.402823466e38f, -3.402823466e38f, -3.402823466e38f, -3.402823466e38f);
+            if (c < cols && c + 3 >= cols) {  // ragged tail
+                v[i].x = xr[c];
+                if (c + 1 < cols) v[i].y = xr[c + 1];
+                if (c + 2 < cols) v[i].z = xr[c + 2];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = (i * blockDim.x + threadIdx.x) * 4;
+            if (v[i].x > best) best = v[i].x, bi = c;
+            if (v[i].y > best) best = v[i].y, bi = c + 1;
+            if (v[i].z > best) best = v[i].z, bi = c + 2;
+            if (v[i].w > best) best = v[i].w, bi = c + 3;
+        }
+    } else {
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float v = xr[c];
+            if (v > best) {
+                best = v;
+                bi = c;
+            }
         }
     }
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -352,8 +438,8 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
     CQ_ENTER(ctx);
     if (!qkv_dev || !pos_dev || !k_cache_dev || !v_cache_dev || !scratch_dev || !out_dev)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: null pointer");
-    if (batch < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 1 || head_dim > 256 || max_ctx < 1)
-        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: bad shape (head_dim <= 256)");
+    if (batch < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 4 || head_dim > 256 || head_dim % 4 != 0 || max_ctx < 1 || max_ctx > 512 * kAttnChunk)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: bad shape (head_dim <= 256 and a multiple of 4, max_ctx <= 16384)");
     const int nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
     const float scale = 1.0f / sqrtf((float)head_dim);
     cq_status s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads),
@@ -363,12 +449,13 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
                       head_dim, nchunks, out_dev);
 }
 
-cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev) {
+cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev, int64_t ld_out) {
     CQ_ENTER(ctx);
-    if (!gate_up_dev || !out_dev || rows < 1 || n < 1 || n > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_silu_mul: bad arguments");
+    if (!gate_up_dev || !out_dev || rows < 1 || n < 1 || n > 0x7FFFFFFF || ld_out < n)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_silu_mul: bad arguments");
     const int64_t total = rows * n;
     const unsigned grid = (unsigned)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
-    return launch_pdl(ctx, silu_mul_kernel, dim3(grid), dim3(256), gate_up_dev, (int)n, total, out_dev);
+    return launch_pdl(ctx, silu_mul_kernel, dim3(grid), dim3(256), gate_up_dev, (int)n, total, out_dev, ld_out);
 }
 
 cq_status cq_argmax(cq_ctx *ctx, const float *x_dev, int64_t rows, int64_t cols, uint32_t *out_dev) {

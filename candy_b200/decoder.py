@@ -71,8 +71,12 @@ class QuantDecoder:
         hd, dim = cfg.head_dim, cfg.dim
         self.qkv_rows = (self.nq + 2 * self.nkv) * hd
         self.kv_dim = self.nkv * hd
+        # The down projection's k (this rank's slice of the feed-forward width) is padded to a
+        # multiple of 256 so its rows stay 16-byte aligned for the streaming kernel; the padded
+        # activations are zero, so whatever the padded weight columns hold contributes nothing.
+        self.ffn_pad = -(-self.ffn // 256) * 256
         # ---- weights: generated and quantized on the device, shard by shard ------------------
-        biggest = max(self.qkv_rows * dim, dim * self.nq * hd, 2 * self.ffn * dim, dim * self.ffn,
+        biggest = max(self.qkv_rows * dim, dim * self.nq * hd, 2 * self.ffn * dim, dim * self.ffn_pad,
                       (cfg.vocab * dim) if cfg.with_head else 0)
         tmp = dev.alloc(biggest)
         self.layers = []
@@ -82,7 +86,7 @@ class QuantDecoder:
                 "wqkv": self._rand_q(tmp, self.qkv_rows, dim, s + 1),
                 "wo": self._rand_q(tmp, dim, self.nq * hd, s + 2),
                 "wgu": self._rand_q(tmp, 2 * self.ffn, dim, s + 3),
-                "wdown": self._rand_q(tmp, dim, self.ffn, s + 4),
+                "wdown": self._rand_q(tmp, dim, self.ffn_pad, s + 4),
                 "attn_norm": dev.storage_from_slice(np.ones(dim, dtype=np.float32)),
                 "ffn_norm": dev.storage_from_slice(np.ones(dim, dtype=np.float32)),
                 "k": dev.zeros(batch * cfg.max_ctx * self.kv_dim),
@@ -104,7 +108,7 @@ class QuantDecoder:
         self.att = dev.alloc(batch * self.nq * hd)
         self.o = dev.alloc(batch * dim)
         self.gu = dev.alloc(batch * 2 * self.ffn)
-        self.h = dev.alloc(batch * self.ffn)
+        self.h = dev.zeros(batch * self.ffn_pad)
         self.d = dev.zeros(batch * dim)
         self.att_scratch = dev.alloc(self.lib.cq_decode_attention_scratch_floats(batch, self.nq, hd, cfg.max_ctx))
         self.ids = RawBuffer(dev, 4 * batch)
@@ -164,7 +168,7 @@ class QuantDecoder:
                 self.allreduce(self.o, B * dim)
             self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.o.ptr, L["ffn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
             self._linear(L["wgu"], self.xn, self.gu)
-            self._check(lib.cq_silu_mul(ctx, self.gu.ptr, B, self.ffn, self.h.ptr), "silu*mul")
+            self._check(lib.cq_silu_mul(ctx, self.gu.ptr, B, self.ffn, self.h.ptr, self.ffn_pad), "silu*mul")
             self._linear(L["wdown"], self.h, self.d)
             if self.world > 1:
                 self.allreduce(self.d, B * dim)

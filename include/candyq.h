@@ -183,9 +183,11 @@ size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head
 cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, int n_q_heads,
                               int n_kv_heads, int head_dim, const int *pos_dev, const float *k_cache_dev,
                               const float *v_cache_dev, int max_ctx, float *scratch_dev, float *out_dev);
-/* out[r, i] = silu(gu[r, i]) * gu[r, n + i]: BackendStorage.Silu (USiluF32, unary.go:3353-3365,
- * evaluated in f64) fused with the Mul of a SwiGLU feed-forward. */
-cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev);
+/* out[r * ld_out + i] = silu(gu[r, i]) * gu[r, n + i]: BackendStorage.Silu (USiluF32,
+ * unary.go:3353-3365, evaluated in f64) fused with the Mul of a SwiGLU feed-forward.  ld_out >= n
+ * lets the result sit in rows padded for the next linear. */
+cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev,
+                      int64_t ld_out);
 /* BackendStorage.FastArgmax (backend.go:128-129; FastArgmaxF32, reduce.go:846-862): the lowest
  * index among equal maxima. */
 cq_status cq_argmax(cq_ctx *ctx, const float *x_dev, int64_t rows, int64_t cols, uint32_t *out_dev);

@@ -80,7 +80,10 @@ class OracleDecoder:
             xn = rmsnorm(x, ones, cfg.eps)
             gu = self.lin(xn, L["wgu"], 2 * self.ffn)
             h_ = silu(gu[: self.ffn]) * gu[self.ffn:]
-            x = x + self.lin(h_, L["wdown"], dim)
+            kpad = L["wdown"].size // dim // oc.BLOCK_BYTES[self.qt] * 32  # rows may be zero-padded in k
+            hp = np.zeros(kpad, dtype=f32)
+            hp[: self.ffn] = h_
+            x = x + self.lin(hp, L["wdown"], dim)
         xn = rmsnorm(x, ones, cfg.eps)
         logits = self.lin(xn, self.wout, cfg.vocab)
         return logits
