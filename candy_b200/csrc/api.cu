@@ -97,6 +97,7 @@ cq_status cq_ctx_destroy(cq_ctx *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (auto &kv : ctx->w16_cache) cudaFree(kv.second);
     if (ctx->xfer_x) cudaFree(ctx->xfer_x);
     if (ctx->xfer_y) cudaFree(ctx->xfer_y);
     if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
@@ -122,6 +123,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemv_force_simple")) t.force_simple = (int)value;
     else if (!strcmp(key, "gemv_pdl")) t.pdl = (int)value;
     else if (!strcmp(key, "gemm_variant")) t.gemm_variant = (int)value;
+    else if (!strcmp(key, "gemm_cache_weights")) t.gemm_cache_weights = (int)value;
     else if (!strcmp(key, "gemv_variant")) t.gemv_variant = (int)value;
     else if (!strcmp(key, "gemv_probe")) t.gemv_probe = (int)value;
     else if (!strcmp(key, "gemv_coop")) t.gemv_coop = (int)value;
@@ -142,6 +144,15 @@ cq_status cq_malloc(cq_ctx *ctx, size_t bytes, void **dptr) {
 cq_status cq_free(cq_ctx *ctx, void *dptr) {
     CQ_ENTER(ctx);
     if (!dptr) return CQ_OK;
+    // a cached f16 copy of weights that lived in this allocation dies with it
+    for (auto it = ctx->w16_cache.begin(); it != ctx->w16_cache.end();) {
+        if (std::get<0>(it->first) == dptr) {
+            cudaFree(it->second);
+            it = ctx->w16_cache.erase(it);
+        } else {
+            ++it;
+        }
+    }
     CQ_CUDA(ctx, cudaFree(dptr));
     return CQ_OK;
 }

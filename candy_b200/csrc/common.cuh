@@ -5,7 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
 #include <string>
+#include <tuple>
 
 #include "candyq.h"
 
@@ -24,6 +26,7 @@ struct GemvTuning {
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;
+    int gemm_cache_weights = 0;  // keep the f16 copy of every weight matrix the GEMM has seen (4x the Q4_0 bytes)
     int gemv_rpt = 2;       // rows per thread and pass in the streaming kernel (1 or 2)
     int gemv_coop = 1;      // slice activations once per CTA through shared memory when rows share a CTA
     int gemv_probe = 0;     // profiling aid, see GemvParams::probe (results are wrong when non-zero)
@@ -43,6 +46,10 @@ struct cq_ctx {
     void *xfer_x = nullptr;       // device staging used by cq_qmatmul_host
     void *xfer_y = nullptr;
     size_t xfer_x_bytes = 0, xfer_y_bytes = 0;
+    // f16 shadow copies of weight matrices for the prefill GEMM (option gemm_cache_weights):
+    // key = (blocks pointer, n, k, qtype * 2 + order) -> device allocation of n*k halfs.
+    std::map<std::tuple<const void *, int64_t, int64_t, int>, void *> w16_cache;
+    size_t w16_cache_bytes = 0;
     GemvTuning tune;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
     bool capturing = false;

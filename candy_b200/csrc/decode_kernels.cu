@@ -241,10 +241,13 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restri
     const float inv = 1.0f / l;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int c = 0; c < nchunks; c += 4) {
+        for (int c = 0; c < nchunks; c += 16) {
+            float a[16];  // sixteen independent loads in flight per thread
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (c + j < nchunks) acc[j] = fmaf(p[(int64_t)(c + j) * stride + 2 + d], w_s[c + j], acc[j]);
+            for (int j = 0; j < 16; ++j) a[j] = (c + j < nchunks) ? p[(int64_t)(c + j) * stride + 2 + d] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (c + j < nchunks) acc[j & 3] = fmaf(a[j], w_s[c + j], acc[j & 3]);
         }
         out[((int64_t)b * nq + head) * hd + d] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * inv;
     }

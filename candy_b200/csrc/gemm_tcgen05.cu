@@ -12,7 +12,7 @@
 //
 // Two steps.  (1) streaming conversion kernels write f16 copies of X [m,k] and W [n,k] into
 // context scratch (HBM-bound: 18/34 B in, 64 B out per block).  (2) gemm_f16_tn_kernel: one CTA
-// per 128 x 256 output tile; a producer lane feeds a 4-stage shared-memory ring with TMA tensor
+// per 128 x 256 (or, for m <= 64, 128 x 64) output tile; a producer lane feeds a shared-memory ring with TMA tensor
 // loads (128-byte swizzle, K-major tiles of 64 values); one lane issues tcgen05.mma
 // (cta_group::1, kind::f16, M=128, N=256, K=16 x 4 per stage) into a 256-column f32 accumulator
 // in tensor memory; tcgen05.commit hands stages back to the producer and, at the end, the
@@ -27,12 +27,18 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int GEMM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
-constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr int TMEM_COLS = 256;
+// Two tile shapes: 128 x 256 (4 stages) for wide batches, 128 x 64 (8 stages) for batches of at
+// most 64 rows, where the number of n-tiles is what fills the SMs.
+template <int BN>
+struct GemmCfg {
+    static constexpr int kStages = BN >= 256 ? 4 : 8;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static constexpr size_t kSmem = (size_t)kStages * (A_BYTES + kBBytes) + 1024 /* alignment slack */ + 256 /* barriers */;
+};
 
 // ---- f16 conversion kernels -------------------------------------------------------------
 __global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__ x, int64_t m, int64_t k, int64_t ldx,
@@ -138,9 +144,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, float *__restrict__ y, int M,
                        int N, int K, int64_t ldy, int *err) {
+    constexpr int STAGES = GemmCfg<BN>::kStages, B_BYTES = GemmCfg<BN>::kBBytes, TMEM_COLS = GemmCfg<BN>::kTmemCols;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smA = smem;                              // [STAGES][A_BYTES]
@@ -265,7 +273,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // f16 [rows, k] row-major; box = 64 values of k x box_rows rows, 128-byte swizzle, zero fill outside.
-bool make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k, int box_rows) {
+bool make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k, int box_rows) {  // box_rows <= 256
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
@@ -295,17 +303,35 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     if (m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
     const size_t w16_bytes = (size_t)n * k * 2;
-    cq_status s = cq_reserve_scratch(ctx, x16_bytes + w16_bytes);
+    // With gemm_cache_weights the f16 copy of a weight matrix is made once and kept (the caller
+    // promises not to rewrite those blocks in place): later calls skip the conversion kernel.
+    __half *w16 = nullptr;
+    bool need_convert = true;
+    const auto key = std::make_tuple(w, n, k, qtype * 2 + order);
+    if (ctx->tune.gemm_cache_weights) {
+        auto it = ctx->w16_cache.find(key);
+        if (it != ctx->w16_cache.end()) {
+            w16 = static_cast<__half *>(it->second);
+            need_convert = false;
+        } else {
+            void *p = nullptr;
+            CQ_CUDA(ctx, cudaMalloc(&p, w16_bytes));
+            ctx->w16_cache[key] = p;
+            ctx->w16_cache_bytes += w16_bytes;
+            w16 = static_cast<__half *>(p);
+        }
+    }
+    cq_status s = cq_reserve_scratch(ctx, x16_bytes + (w16 ? 0 : w16_bytes));
     if (s != CQ_OK) return s;
     __half *x16 = static_cast<__half *>(ctx->scratch);
-    __half *w16 = reinterpret_cast<__half *>(static_cast<uint8_t *>(ctx->scratch) + x16_bytes);
+    if (!w16) w16 = reinterpret_cast<__half *>(static_cast<uint8_t *>(ctx->scratch) + x16_bytes);
     const unsigned cap = (unsigned)ctx->sm_count * 16;
     {
         const int64_t total = m * (k / 4);
         const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
         x_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(x, m, k, ldx, x16);
     }
-    {
+    if (need_convert) {
         const int64_t nblocks = n * (k / kQK);
         const int64_t total = nblocks * 4;
         const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
@@ -316,15 +342,20 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     }
     CQ_CUDA(ctx, cudaGetLastError());
     CUtensorMap tmA, tmB;
-    if (!make_map(&tmA, x16, m, k, BM) || !make_map(&tmB, w16, n, k, BN))
+    const int bn = (m <= 64 && ctx->tune.gemm_variant != 1) ? 64 : 256;
+    if (!make_map(&tmA, x16, m, k, BM) || !make_map(&tmB, w16, n, k, bn))
         return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
+        CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_tn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<256>::kSmem));
+        CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_tn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<64>::kSmem));
         configured_device = ctx->device;
     }
-    dim3 grid((unsigned)((m + BM - 1) / BM), (unsigned)((n + BN - 1) / BN));
-    gemm_f16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
+    dim3 grid((unsigned)((m + BM - 1) / BM), (unsigned)((n + bn - 1) / bn));
+    if (bn == 64)
+        gemm_f16_tn_kernel<64><<<grid, GEMM_THREADS, GemmCfg<64>::kSmem, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
+    else
+        gemm_f16_tn_kernel<256><<<grid, GEMM_THREADS, GemmCfg<256>::kSmem, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
     CQ_CUDA(ctx, cudaGetLastError());
     return CQ_OK;
 }
