@@ -66,6 +66,11 @@ SIGNATURES = {
     "cq_argmax": [_vp, _vp, _i64, _i64, _vp],
     "cq_embedding": [_vp, _vp, _i64, _i64, _vp, _i64, _vp],
     "cq_add_int": [_vp, _vp, _int],
+    "cq_comm_create": [_vp, _int, _int, _i64, C.POINTER(_vp), _vp],
+    "cq_comm_connect": [_vp, _vp, _vp],
+    "cq_comm_destroy": [_vp, _vp],
+    "cq_qmatmul_push": [_vp, _vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64],
+    "cq_add_rmsnorm_reduce": [_vp, _vp, _int, _vp, _vp, _i64, _i64, C.c_float, _vp],
     "cq_capture_begin": [_vp],
     "cq_capture_end": [_vp, C.POINTER(_vp)],
     "cq_graph_launch": [_vp, _vp],

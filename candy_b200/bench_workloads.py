@@ -82,8 +82,19 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
                 views[key] = torch.as_tensor(_CudaArray(key, count), device=torch.device("cuda", local_rank))
             dist.all_reduce(views[key])
 
-        model = QuantDecoder(dev, cfg, seed=seed, batch=batch, rank=rank, world=world, allreduce=allreduce if world > 1 else None,
-                             actmode=0 if batch <= 8 else 2)
+        fused = world > 1 and batch <= 8
+        comm = None
+        if fused:  # exchange fused into the GEMV epilogue / residual-norm kernel over peer memory
+            comm = C.c_void_p()
+            handle = (C.c_char * 64)()
+            model_check = lambda st, what: __import__("candy_b200").abi.check(ctx, st, what)
+            model_check(lib.cq_comm_create(ctx, rank, world, batch * cfg.dim, C.byref(comm), handle), "comm create")
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw))
+            model_check(lib.cq_comm_connect(ctx, comm, b"".join(handles)), "comm connect")
+            dist.barrier()
+        model = QuantDecoder(dev, cfg, seed=seed, batch=batch, rank=rank, world=world,
+                             allreduce=allreduce if (world > 1 and not fused) else None, actmode=0 if batch <= 8 else 2, comm=comm)
         for L in model.layers:  # noise in the caches, as if ctx_len tokens had been decoded
             n = batch * cfg.max_ctx * model.kv_dim
             lib.cq_rand_normal(ctx, L["k"].ptr, n, 0.0, 1.0, seed + 101)
@@ -91,22 +102,30 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
         lib.cq_rand_normal(ctx, model.x.ptr, batch * cfg.dim, 0.0, 1.0, seed + 303)
         model.set_state(np.zeros(batch, dtype=np.uint32), ctx_len - 1)
         dev.synchronize()
-        if world == 1:
+
+        def time_own_graph():
+            model.step(advance=False)
             model.step(advance=False)
             dev.synchronize()
             lib.cq_capture_begin(ctx)
             model.step(advance=False)
             g = C.c_void_p()
             model._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
+            if dist is not None:
+                dist.barrier()
             model.replay(g, 3)
             ms = C.c_float()
             dev.synchronize()
+            if dist is not None:
+                dist.barrier()
             lib.cq_timer_start(ctx)
             model.replay(g, reps)
             lib.cq_timer_stop(ctx, C.byref(ms))
+            dev.synchronize()
             lib.cq_graph_destroy(ctx, g)
-            step_ms = ms.value / reps
-        else:
+            return ms.value / reps
+
+        def time_torch_graph():
             stream = torch.cuda.Stream(device=local_rank)
             dev.set_stream(stream.cuda_stream)
             with torch.cuda.stream(stream):
@@ -128,20 +147,40 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
                     graph.replay()
                 e1.record(stream)
             e1.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=torch.device("cuda", local_rank))
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            step_ms = float(t.item())
+            t_ms = e0.elapsed_time(e1) / reps
             dev.set_stream(0)
             del graph
+            return t_ms
+
+        def max_over_ranks(v):
+            if dist is None:
+                return v
+            t = torch.tensor([v], dtype=torch.float64, device=torch.device("cuda", local_rank))
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        nccl_ms = None
+        if world == 1 or fused:
+            step_ms = max_over_ranks(time_own_graph())
+            if fused:  # the same stack with NCCL all-reduces, for comparison
+                model.comm, model.allreduce = None, allreduce
+                nccl_ms = max_over_ranks(time_torch_graph())
+        else:
+            step_ms = max_over_ranks(time_torch_graph())
         wbytes_all = model.weight_bytes_per_step() * world
         out[f"batch{batch}"] = {
             "ms_per_step": round(step_ms, 4), "layers_per_s": round(n_layers / (step_ms * 1e-3), 1),
             "tokens_per_s": round(batch / (step_ms * 1e-3), 1), "weight_bytes_per_step_all_ranks": wbytes_all,
             "weight_gbs_all_ranks": round(wbytes_all / (step_ms * 1e-3) / 1e9, 1),
             "frac_of_peak_per_gpu": round(wbytes_all / world / (step_ms * 1e-3) / 1e9 / peak_gbs, 4),
-            "allreduce": "none" if world == 1 else f"NCCL sum of [{batch},8192] f32, twice per layer",
+            "allreduce": "none" if world == 1 else ("fused: peer stores from the GEMV epilogue + counters, summed inside the following residual+RMSNorm kernel"
+                                                    if fused else f"NCCL sum of [{batch},8192] f32, twice per layer"),
+            "nccl_ms_per_step": None if nccl_ms is None else round(nccl_ms, 4),
             "linear_mode": "f32 activations (decode GEMV)" if batch <= 8 else "f16 operands (tensor-core GEMM), f16 weight copies cached",
         }
         del model
         dev.synchronize()
+        if comm is not None:
+            dist.barrier()
+            lib.cq_comm_destroy(ctx, comm)
     return out

@@ -328,6 +328,7 @@ cq_status cq_capture_end(cq_ctx *ctx, cq_graph **out) {
     cq_graph *g = new cq_graph();
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
     if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e == cudaSuccess) e = cudaGraphUpload(g->exec, ctx->stream);  // so the first launch does not pay the upload
     if (e != cudaSuccess) {
         if (g->graph) cudaGraphDestroy(g->graph);
         delete g;

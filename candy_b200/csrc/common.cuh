@@ -33,6 +33,15 @@ struct GemvTuning {
     int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices
 };
 
+// Set by the tensor-parallel entry point around one GEMV launch (see comm.cu).
+struct PushSpec {
+    float *const *rx = nullptr;
+    unsigned *const *cnt = nullptr;
+    int world = 0;
+    int64_t row_stride = 0;
+    int64_t arrivals = 0;
+};
+
 struct cq_ctx {
     int device = 0;
     int sm_count = 0;
@@ -51,6 +60,7 @@ struct cq_ctx {
     std::map<std::tuple<const void *, int64_t, int64_t, int>, void *> w16_cache;
     size_t w16_cache_bytes = 0;
     GemvTuning tune;
+    PushSpec push;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
     bool capturing = false;
     std::string last_error;

@@ -213,6 +213,89 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
     }
 }
 
+// Grouped-query variant: one CTA per (kv head, sequence, chunk of 32 keys) serves all G = nq/nkv
+// query heads of the group, so a K/V chunk is read from memory once instead of G times.  K is
+// staged transposed in shared memory (lane = key, conflict-free), V row-major (thread = dim).
+// hd == 128, G <= 8.  Same partial layout as attn_partial_kernel.
+constexpr int kGqaMaxG = 8;
+__global__ void __launch_bounds__(128) attn_partial_gqa_kernel(const float *__restrict__ qkv, int nq, int nkv, const int *__restrict__ pos_dev,
+                                                             const float *__restrict__ kc, const float *__restrict__ vc, int max_ctx,
+                                                             float scale, float *__restrict__ part, int nchunks) {
+    constexpr int hd = 128;
+    __shared__ float kt_s[hd][kAttnChunk + 1];       // K transposed, padded
+    __shared__ float v_s[kAttnChunk][hd];
+    __shared__ float q_s[kGqaMaxG][hd];
+    __shared__ float p_s[kGqaMaxG][kAttnChunk];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int kvh = blockIdx.x, b = blockIdx.y, chunk = blockIdx.z;
+    const int G = nq / nkv;
+    const int nkeys = *pos_dev + 1;
+    const int t0 = chunk * kAttnChunk;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (t0 >= nkeys) {
+        for (int g = 0; g < G; ++g) {
+            float *out = part + (((int64_t)b * nq + kvh * G + g) * nchunks + chunk) * (hd + 2);
+            if (tid == 0) out[0] = -3.402823466e38f, out[1] = 0.0f;
+            out[2 + tid] = 0.0f;
+        }
+        return;
+    }
+    const int cnt = min(kAttnChunk, nkeys - t0);
+    const int row = (nq + 2 * nkv) * hd;
+    const int64_t kv_stride = (int64_t)nkv * hd;
+    const float *kbase = kc + ((int64_t)b * max_ctx + t0) * kv_stride + kvh * hd;
+    const float *vbase = vc + ((int64_t)b * max_ctx + t0) * kv_stride + kvh * hd;
+    // all global loads first: 32 K values and 32 V values per thread (thread = dim), plus q
+    float kreg[kAttnChunk], vreg[kAttnChunk];
+#pragma unroll
+    for (int t = 0; t < kAttnChunk; ++t) {
+        kreg[t] = (t < cnt) ? kbase[(int64_t)t * kv_stride + tid] : 0.0f;
+        vreg[t] = (t < cnt) ? vbase[(int64_t)t * kv_stride + tid] : 0.0f;
+    }
+    for (int g = 0; g < G; ++g) q_s[g][tid] = qkv[(int64_t)b * row + (kvh * G + g) * hd + tid];
+#pragma unroll
+    for (int t = 0; t < kAttnChunk; ++t) {
+        kt_s[tid][t] = kreg[t];
+        v_s[t][tid] = vreg[t];
+    }
+    __syncthreads();
+    // scores: warp w takes heads w, w+4; lane = key
+    for (int g = warp; g < G; g += 4) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 8
+        for (int d = 0; d < hd; d += 4) {
+            s0 = fmaf(q_s[g][d], kt_s[d][lane], s0);
+            s1 = fmaf(q_s[g][d + 1], kt_s[d + 1][lane], s1);
+            s2 = fmaf(q_s[g][d + 2], kt_s[d + 2][lane], s2);
+            s3 = fmaf(q_s[g][d + 3], kt_s[d + 3][lane], s3);
+        }
+        const float sc = (lane < cnt) ? ((s0 + s1) + (s2 + s3)) * scale : -3.402823466e38f;
+        const float m = warp_max(sc);
+        const float e = (lane < cnt) ? expf(sc - m) : 0.0f;
+        const float l = warp_sum(e);
+        p_s[g][lane] = e;
+        if (lane == 0) {
+            float *out = part + (((int64_t)b * nq + kvh * G + g) * nchunks + chunk) * (hd + 2);
+            out[0] = m;
+            out[1] = l;
+        }
+    }
+    __syncthreads();
+    // weighted V: thread = dim, all heads of the group from the same staged V
+    for (int g = 0; g < G; ++g) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int t = 0; t < kAttnChunk; t += 4) {
+            a0 = fmaf(p_s[g][t], v_s[t][tid], a0);
+            a1 = fmaf(p_s[g][t + 1], v_s[t + 1][tid], a1);
+            a2 = fmaf(p_s[g][t + 2], v_s[t + 2][tid], a2);
+            a3 = fmaf(p_s[g][t + 3], v_s[t + 3][tid], a3);
+        }
+        part[(((int64_t)b * nq + kvh * G + g) * nchunks + chunk) * (hd + 2) + 2 + tid] = (a0 + a1) + (a2 + a3);
+    }
+}
+
 // Combines the chunk partials of one (head, sequence): out[b][head*hd + d].
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, int nq, int hd, int nchunks,
                                                          float *__restrict__ out) {
@@ -445,8 +528,14 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: bad shape (head_dim <= 256 and a multiple of 4, max_ctx <= 16384)");
     const int nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
     const float scale = 1.0f / sqrtf((float)head_dim);
-    cq_status s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads),
-                             qkv_dev, n_q_heads, n_kv_heads, head_dim, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
+    const int group = n_q_heads / n_kv_heads;
+    cq_status s;
+    if (head_dim == 128 && group >= 2 && group <= kGqaMaxG)
+        s = launch_pdl(ctx, attn_partial_gqa_kernel, dim3((unsigned)n_kv_heads, (unsigned)batch, (unsigned)nchunks), dim3(128), qkv_dev, n_q_heads,
+                       n_kv_heads, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
+    else
+        s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads), qkv_dev,
+                       n_q_heads, n_kv_heads, head_dim, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
     if (s != CQ_OK) return s;
     return launch_pdl(ctx, attn_combine_kernel, dim3((unsigned)n_q_heads, (unsigned)batch), dim3(128), (const float *)scratch_dev, n_q_heads,
                       head_dim, nchunks, out_dev);

@@ -255,6 +255,144 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// Persistent variant of the 128 x 256 kernel: one CTA per SM walks tiles t = blockIdx.x, +gridDim.x, ...
+// (m-tiles fastest).  The shared-memory ring keeps running across tile boundaries and the
+// accumulator is double-buffered in tensor memory (2 x 256 columns), so the epilogue of tile i
+// overlaps the MMAs of tile i+1 and no tile pays the pipeline fill again.
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_f16_tn_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, float *__restrict__ y,
+                                  int M, int N, int K, int64_t ldy, int *err) {
+    constexpr int BN = 256;
+    constexpr int STAGES = GemmCfg<BN>::kStages, B_BYTES = GemmCfg<BN>::kBBytes;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smA = smem;
+    uint8_t *smB = smem + (size_t)STAGES * A_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * (A_BYTES + B_BYTES));
+    uint64_t *full = bars, *empty = bars + STAGES, *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mt = (M + BM - 1) / BM, nt = (N + BN - 1) / BN;
+    const int ntiles = mt * nt;
+    const int nk = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 4);  // one arrival per epilogue warp
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;  // k-blocks issued so far, across tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const int tile_m = t % mt, tile_n = t / mt;
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ((it / STAGES) - 1) & 1)) {
+                        atomicExch(err, kDevErrEmptyWait);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(smem_u32(&full[s]), A_BYTES + B_BYTES);
+                    tma_load_2d(smem_u32(smA + (size_t)s * A_BYTES), &tmA, kb * BK, tile_m * BM, smem_u32(&full[s]));
+                    tma_load_2d(smem_u32(smB + (size_t)s * B_BYTES), &tmB, kb * BK, tile_n * BN, smem_u32(&full[s]));
+                }
+            }
+            // never leave with copies in flight into this CTA's shared memory
+            const int first = it > STAGES ? it - STAGES : 0;
+            for (int i = first; i < it; ++i)
+                if (!mbar_wait_bounded(smem_u32(&full[i % STAGES]), (i / STAGES) & 1)) {
+                    atomicExch(err, kDevErrDrain);
+                    break;
+                }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(BM, BN);
+            int it = 0, ti = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++ti) {
+                const int buf = ti & 1;
+                if (ti >= 2 && !mbar_wait_bounded(smem_u32(&acc_empty[buf]), ((ti >> 1) - 1) & 1)) {  // epilogue done with this buffer
+                    atomicExch(err, kDevErrMma);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_bounded(smem_u32(&full[s]), (it / STAGES) & 1)) {
+                        atomicExch(err, kDevErrFullWait);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a0 = smem_u32(smA + (size_t)s * A_BYTES), b0 = smem_u32(smB + (size_t)s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma_f16(acc, smem_desc_k128(a0 + 32 * k), smem_desc_k128(b0 + 32 * k), idesc, (kb | k) != 0);
+                    tc_commit(smem_u32(&empty[s]));
+                }
+                tc_commit(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int ti = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++ti) {
+            const int buf = ti & 1;
+            const int tile_m = t % mt, tile_n = t / mt;
+            if (!mbar_wait_bounded(smem_u32(&acc_full[buf]), (ti >> 1) & 1)) {
+                if (lane == 0) atomicExch(err, kDevErrMma);
+                break;
+            }
+            tc_fence_after();
+            const int64_t row = (int64_t)tile_m * BM + q * 32 + lane;
+            const int col0 = tile_n * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
+                const int col = col0 + c * 32;
+                if (row < M) {
+                    float *dst = y + row * ldy + col;
+                    if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col + i < N) dst[i] = __uint_as_float(r[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));  // this warp's quarter of the buffer is free
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // ---- host side ----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -352,7 +490,17 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
         configured_device = ctx->device;
     }
     dim3 grid((unsigned)((m + BM - 1) / BM), (unsigned)((n + bn - 1) / bn));
-    if (bn == 64)
+    if (bn == 256 && ctx->tune.gemm_variant != 2) {
+        static thread_local int configured_p = -1;
+        if (configured_p != ctx->device) {
+            CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_tn_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<256>::kSmem));
+            configured_p = ctx->device;
+        }
+        const int64_t ntiles = (int64_t)grid.x * grid.y;
+        const unsigned ctas = (unsigned)(ntiles < ctx->sm_count ? ntiles : ctx->sm_count);
+        gemm_f16_tn_persistent_kernel<<<ctas, GEMM_THREADS, GemmCfg<256>::kSmem, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy,
+                                                                                               ctx->dev_err_devptr);
+    } else if (bn == 64)
         gemm_f16_tn_kernel<64><<<grid, GEMM_THREADS, GemmCfg<64>::kSmem, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
     else
         gemm_f16_tn_kernel<256><<<grid, GEMM_THREADS, GemmCfg<256>::kSmem, ctx->stream>>>(tmA, tmB, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);

@@ -69,6 +69,12 @@ struct GemvParams {
     int stages;
     int stage_bytes;
     int coop_off;      // byte offset of the cooperative activation staging area in dynamic smem, or -1
+    // Row-parallel tensor parallelism: instead of y, the results go straight into every rank's
+    // receive buffer (peer stores over NVLink), then one counter per peer is bumped per CTA.
+    float *const *push_rx;      // [world] this rank's slot in each peer's receive buffer
+    unsigned *const *push_cnt;  // [world] this rank's arrival counter on each peer
+    int push_world;             // 0 = ordinary launch
+    int64_t push_off;           // element offset of this activation row inside the slot
     int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers, 3 = empty kernel
     int *err;
 };
@@ -135,7 +141,10 @@ struct DecFma {
     static constexpr bool kCoop = false;
     static constexpr int kStateWordsPerBlock = 0;
     static constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
+    static constexpr bool kSplitStage = false;
     __device__ __forceinline__ static void stage_quarter(const float *, int, bool, uint32_t *) {}
+    __device__ __forceinline__ static void load_quarter(const float *, int, bool, float (&)[8]) {}
+    __device__ __forceinline__ static void stage_quarter_regs(const float (&)[8], int, bool, uint32_t *) {}
     __device__ __forceinline__ void load(const uint32_t *) {}
     static constexpr int kDBWord = (QT == CQ_Q4_0) ? 4 : 8;  // word whose high half is block B's scale
     float xr[kXPerThread];  // xr[s] multiplies slot s; already divided by 16^pos / 256^pos
@@ -199,6 +208,7 @@ struct DecQ16 {
     static constexpr int kBlkWords = (QT == CQ_Q4_0) ? 4 : 8;
     static constexpr int kVecs = (QT == CQ_Q4_0) ? 2 : 1;
     static constexpr bool kCoop = true;
+    static constexpr bool kSplitStage = true;
     static constexpr int kStateWordsPerBlock = 20;  // 8 hi words, 8 lo words, scale, bias, 2 pad (16-byte multiple)
     int qh[2][kBlkWords][kVecs];  // high bytes (signed), lane order matching the weight bytes
     int ql[2][kBlkWords][kVecs];  // low bytes (unsigned)
@@ -220,9 +230,7 @@ struct DecQ16 {
 
     // Cooperative set-up: item = block * 4 + quarter, 8 activations per lane, four adjacent
     // lanes make one block.  All 32 lanes of the warp must call this together.
-    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) {
-        const int blk = item >> 2, qd = item & 3;
-        float r[8];
+    __device__ __forceinline__ static void load_quarter(const float *x, int item, bool valid, float (&r)[8]) {
         if (valid) {
             const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item);
             const float4 b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item + 1);
@@ -231,6 +239,14 @@ struct DecQ16 {
 #pragma unroll
             for (int i = 0; i < 8; ++i) r[i] = 0.0f;
         }
+    }
+    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) {
+        float r[8];
+        load_quarter(x, item, valid, r);
+        stage_quarter_regs(r, item, valid, area);
+    }
+    __device__ __forceinline__ static void stage_quarter_regs(const float (&r)[8], int item, bool valid, uint32_t *area) {
+        const int blk = item >> 2, qd = item & 3;
         int idxA, idxB;  // which of the block's 8 packed words this quarter fills
         if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) idxA = 2 * qd, idxB = 2 * qd + 1;
         else if (QT == CQ_Q4_0) idxA = (qd < 2) ? 4 * qd : 4 * (qd - 2) + 1, idxB = idxA + 2;
@@ -373,7 +389,10 @@ struct DecSlices {
     // the owner threads need, and each thread then loads its two blocks' state.
     // Per block: S x 8 packed words, then S scales, then S biases.
     static constexpr bool kCoop = true;
+    static constexpr bool kSplitStage = false;
     static constexpr int kStateWordsPerBlock = S * 10;
+    __device__ __forceinline__ static void load_quarter(const float *, int, bool, float (&)[8]) {}
+    __device__ __forceinline__ static void stage_quarter_regs(const float (&)[8], int, bool, uint32_t *) {}
 
     __device__ __forceinline__ static uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
         return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
@@ -631,9 +650,21 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     if (Dec::kCoop && p.coop_off >= 0) {
         uint32_t *area = reinterpret_cast<uint32_t *>(smem + p.coop_off);
         const int nitems = p.nb * 4;
-        for (int base = 0; base < nitems; base += cthreads) {  // uniform trip count: the shuffles need whole warps
-            const int item = base + tid;
-            Dec::stage_quarter(p.x, item, item < nitems, area);
+        if (Dec::kSplitStage) {
+            // two items per trip with both loads issued first: one L2 round trip for k <= 16 * threads
+            for (int base = 0; base < nitems; base += 2 * cthreads) {  // uniform trip count: the shuffles need whole warps
+                const int i0 = base + tid, i1 = base + cthreads + tid;
+                float r0[8], r1[8];
+                Dec::load_quarter(p.x, i0, i0 < nitems, r0);
+                Dec::load_quarter(p.x, i1, i1 < nitems, r1);
+                Dec::stage_quarter_regs(r0, i0, i0 < nitems, area);
+                Dec::stage_quarter_regs(r1, i1, i1 < nitems, area);
+            }
+        } else {
+            for (int base = 0; base < nitems; base += cthreads) {
+                const int item = base + tid;
+                Dec::stage_quarter(p.x, item, item < nitems, area);
+            }
         }
         TRACE(3);
         asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
@@ -769,13 +800,23 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
             if (pbase + u < npass && r < nrows) {
                 float tot = 0.0f;
                 for (int w = 0; w < p.wpr; ++w) tot += red[buf][i][rs * p.wpr + w];
-                p.y[row_begin + r] = tot;
+                if (p.push_world > 0) {
+                    for (int pr = 0; pr < p.push_world; ++pr) p.push_rx[pr][p.push_off + row_begin + r] = tot;
+                } else {
+                    p.y[row_begin + r] = tot;
+                }
             }
         }
         if (pbase == 0) TRACE(8);
         buf ^= 1;
     }
     TRACE(9);
+    if (p.push_world > 0) {
+        // all of this CTA's peer stores are ordered before the counter bumps that announce them
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+        if (tid < p.push_world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push_cnt[tid]) : "memory");
+    }
 }
 
 // ---- plain kernel ------------------------------------------------------------------------
@@ -1036,9 +1077,14 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         p.w = w;
         p.err = ctx->dev_err_devptr;
         p.probe = ctx->tune.gemv_probe;
+        p.push_world = ctx->push.world;
+        p.push_rx = ctx->push.rx;
+        p.push_cnt = ctx->push.cnt;
+        ctx->push.arrivals = (int64_t)grid * m;  // counter bumps each peer will see from this rank
         for (int64_t i = 0; i < m; ++i) {  // one pass over the weights per activation row
             p.x = x + i * ldx;
             p.y = y + i * ldy;
+            p.push_off = i * ctx->push.row_stride;
             cq_status s;
             switch (ctx->tune.gemv_variant) {
                 case 1: s = run_stream<DecFma<QT, ORDER>>(ctx, p, rpt, grid, threads, smem); break;
@@ -1050,6 +1096,7 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         }
         return CQ_OK;
     }
+    if (ctx->push.world > 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "pushing GEMV needs a shape the streaming kernel takes (k % 256 == 0, aligned pointers)");
     return run_simple<QT, ORDER>(ctx, w, x, y, m, n, nb, ldx, ldy);
 }
 

@@ -61,11 +61,17 @@ def rope_tables(cfg: DecoderConfig):
 class QuantDecoder:
     def __init__(self, dev: CudaDevice, cfg: DecoderConfig, seed: int = 0, batch: int = 1, qtype: int = Q4_0,
                  order: int = ORDER_GO_INTERLEAVED, rank: int = 0, world: int = 1,
-                 allreduce: Optional[Callable[[object, int], None]] = None, actmode: int = ACT_F32):
+                 allreduce: Optional[Callable[[object, int], None]] = None, actmode: int = ACT_F32, comm=None):
         self.dev, self.cfg, self.batch, self.qtype, self.order = dev, cfg, batch, qtype, order
         self.rank, self.world, self.allreduce, self.actmode = rank, world, allreduce, actmode
-        if world > 1 and allreduce is None:
-            raise ValueError("tensor parallel decoder needs an allreduce callback")
+        # comm: a connected cq_comm handle -> the two all-reduces of a layer are fused into the GEMV
+        # before them and the residual+norm after them (batch <= 8 only); else `allreduce` is called
+        self.comm = comm
+        self._pending = [False, False]  # a push into set i awaits its reducing norm
+        if world > 1 and allreduce is None and comm is None:
+            raise ValueError("tensor parallel decoder needs an allreduce callback or a communicator")
+        if comm is not None and (batch > 8 or cfg.with_head):
+            raise ValueError("the fused exchange serves bare layer stacks with batch <= 8")
         self.nq, self.nkv, self.ffn = shard_sizes(cfg, world)
         self.lib, self.ctx = dev._lib, dev.ctx
         hd, dim = cfg.head_dim, cfg.dim
@@ -151,27 +157,42 @@ class QuantDecoder:
         if cfg.with_head:
             self._check(lib.cq_embedding(ctx, self.embed.ptr, cfg.vocab, dim, self.ids.ptr, B, self.x.ptr), "embedding")
         first = True
+        fused = self.comm is not None
         for L in self.layers:
             if first and cfg.with_head:  # x was just gathered from the embedding table
                 self._check(lib.cq_rmsnorm(ctx, self.x.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "rmsnorm")
-                first = False
+            elif fused and self._pending[1]:  # the down projection's partials are summed inside this norm
+                self._check(lib.cq_add_rmsnorm_reduce(ctx, self.comm, 1, self.x.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "reduce+rmsnorm")
+                self._pending[1] = False
+            elif fused:  # very first step of a fused stack: nothing has been pushed yet
+                self._check(lib.cq_rmsnorm(ctx, self.x.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "rmsnorm")
             else:  # residual of the previous feed-forward (previous layer, or previous step of a bare stack), then the norm
-                first = False
                 self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.d.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
+            first = False
             self._linear(L["wqkv"], self.xn, self.qkv)
             self._check(lib.cq_rope_store_kv(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.cos.ptr, self.sin.ptr, self.pos.ptr,
                                              L["k"].ptr, L["v"].ptr, cfg.max_ctx), "rope")
             self._check(lib.cq_decode_attention(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.pos.ptr, L["k"].ptr, L["v"].ptr,
                                                 cfg.max_ctx, self.att_scratch.ptr, self.att.ptr), "attention")
-            self._linear(L["wo"], self.att, self.o)
-            if self.world > 1:
-                self.allreduce(self.o, B * dim)
-            self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.o.ptr, L["ffn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
+            if fused:
+                w = L["wo"]
+                self._check(lib.cq_qmatmul_push(ctx, self.comm, 0, w.qtype, w.order, self.att.ptr, B, w.k, w.k, w.buf.ptr, w.n), "push o")
+                self._check(lib.cq_add_rmsnorm_reduce(ctx, self.comm, 0, self.x.ptr, L["ffn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "reduce+rmsnorm")
+            else:
+                self._linear(L["wo"], self.att, self.o)
+                if self.world > 1:
+                    self.allreduce(self.o, B * dim)
+                self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.o.ptr, L["ffn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
             self._linear(L["wgu"], self.xn, self.gu)
             self._check(lib.cq_silu_mul(ctx, self.gu.ptr, B, self.ffn, self.h.ptr, self.ffn_pad), "silu*mul")
-            self._linear(L["wdown"], self.h, self.d)
-            if self.world > 1:
-                self.allreduce(self.d, B * dim)
+            if fused:
+                w = L["wdown"]
+                self._check(lib.cq_qmatmul_push(ctx, self.comm, 1, w.qtype, w.order, self.h.ptr, B, w.k, w.k, w.buf.ptr, w.n), "push down")
+                self._pending[1] = True
+            else:
+                self._linear(L["wdown"], self.h, self.d)
+                if self.world > 1:
+                    self.allreduce(self.d, B * dim)
         if cfg.with_head:
             self._check(lib.cq_add_rmsnorm(ctx, self.x.ptr, self.d.ptr, self.final_norm.ptr, B, dim, cfg.eps, self.xn.ptr), "final norm")
             self._linear(self.wout, self.xn, self.logits)

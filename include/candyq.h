@@ -197,6 +197,29 @@ cq_status cq_embedding(cq_ctx *ctx, const float *table_dev, int64_t vocab, int64
 /* *value_dev += delta on the stream (advances a decode position inside a captured graph). */
 cq_status cq_add_int(cq_ctx *ctx, int *value_dev, int delta);
 
+/* ---- tensor-parallel exchange fused into the kernels around it ---------------------------
+ * One process per GPU.  A row-parallel linear (o / down projection split along k) needs the sum
+ * of every rank's partial output.  Instead of a collective call, cq_qmatmul_push makes the decode
+ * GEMV store its results directly into every rank's receive buffer (peer stores over NVLink) and
+ * bump a counter per peer; cq_add_rmsnorm_reduce, the residual-add + RMSNorm that follows the
+ * linear anyway, waits (bounded; CQ_ERR_TIMEOUT at the next cq_synchronize on give-up) for all
+ * ranks' counters, sums the partials from local memory in rank order (bit-identical on every
+ * rank), and re-arms the counters.  Use set 0 and set 1 alternately (o: 0, down: 1).  Every rank
+ * must issue the same sequence of calls.  The reference has no multi-device code; no counterpart.
+ *   create:  allocates this rank's buffers; handle64 receives a 64-byte CUDA IPC handle;
+ *   connect: takes all ranks' handles (world x 64 bytes, rank order) gathered by the host. */
+typedef struct cq_comm cq_comm;
+cq_status cq_comm_create(cq_ctx *ctx, int rank, int world, int64_t max_floats, cq_comm **out, void *handle64);
+cq_status cq_comm_connect(cq_ctx *ctx, cq_comm *comm, const void *all_handles);
+cq_status cq_comm_destroy(cq_ctx *ctx, cq_comm *comm);
+/* partial[m,n] = x[m,k] . W[n,k]^T (f32 activations, m <= 8), pushed into slot `rank` of `set` on
+ * every rank instead of being written locally.  m*n <= max_floats. */
+cq_status cq_qmatmul_push(cq_ctx *ctx, cq_comm *comm, int set, int qtype, int order, const float *x_dev,
+                          int64_t m, int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n);
+/* x[rows,cols] += sum over ranks of the partials pushed into `set`; y = rmsnorm(x) * alpha. */
+cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *comm, int set, float *x_dev, const float *alpha_dev,
+                                int64_t rows, int64_t cols, float eps, float *y_dev);
+
 /* ---- CUDA graphs and device timing ----------------------------------------------------
  * Decode loops are launch-bound: a GEMV lasts a few microseconds.  These wrap stream capture
  * so a host in any language can record a sequence of cq_* launches once and replay it.
