@@ -296,43 +296,80 @@ __global__ void __launch_bounds__(128) attn_partial_gqa_kernel(const float *__re
     }
 }
 
-// Combines the chunk partials of one (head, sequence): out[b][head*hd + d].
+// Combines the chunk partials of one (head, sequence): out[b][head*hd + d].  Lane = four
+// consecutive dims, the four warps take every fourth chunk; all loads of a batch of eight chunks
+// are unconditional (clamped index, zero weight past the end) so they are in flight together.
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, int nq, int hd, int nchunks,
                                                          float *__restrict__ out) {
-    __shared__ float w_s[512];  // per-chunk weight exp(m_c - m) / l; nchunks <= 512 (context <= 16384)
+    __shared__ float w_s[512];  // per-chunk weight exp(m_c - m); nchunks <= 512 (context <= 16384)
     __shared__ float red[32];
+    __shared__ float4 acc_s[4][64];  // per-warp partial sums, hd <= 256
     pdl_launch_dependents();
     pdl_wait_prior();
     const int head = blockIdx.x, b = blockIdx.y;
     const int stride = hd + 2;
     const float *p = part + (((int64_t)b * nq + head) * nchunks) * stride;
-    float m = -3.402823466e38f;
-    for (int c = threadIdx.x; c < nchunks; c += blockDim.x) m = fmaxf(m, p[(int64_t)c * stride]);
-    m = warp_max(m);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    // chunk maxima and sums: one (m, l) pair per thread per trip, both loads issued together
+    float m = -3.402823466e38f;
+    float mc[4], lc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 128;
+        const int cc = c < nchunks ? c : nchunks - 1;
+        mc[i] = p[(int64_t)cc * stride];
+        lc[i] = p[(int64_t)cc * stride + 1];
+        if (c >= nchunks) mc[i] = -3.402823466e38f, lc[i] = 0.0f;
+        m = fmaxf(m, mc[i]);
+    }
+    m = warp_max(m);
     if (lane == 0) red[warp] = m;
     __syncthreads();
     m = (lane < nw) ? red[lane] : -3.402823466e38f;
     m = warp_max(m);
+    __syncthreads();
     float l = 0.0f;
-    for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
-        const float w = expf(p[(int64_t)c * stride] - m);
-        w_s[c] = w;
-        l += w * p[(int64_t)c * stride + 1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 128;
+        const float w = (c < nchunks) ? expf(mc[i] - m) : 0.0f;
+        if (c < nchunks) w_s[c] = w;
+        l = fmaf(w, lc[i], l);
     }
-    l = block_sum(l, red);
+    l = block_sum(l, red);  // has the barriers that publish w_s
     const float inv = 1.0f / l;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int c = 0; c < nchunks; c += 16) {
-            float a[16];  // sixteen independent loads in flight per thread
+    for (int d0 = 0; d0 < hd; d0 += 128) {
+        const int d = d0 + lane * 4;
+        const bool live = d < hd;
+        const float *pd = p + 2 + (live ? d : 0);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c0 = warp; c0 < nchunks; c0 += 32) {
+            float a[8][4];
+            float w[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) a[j] = (c + j < nchunks) ? p[(int64_t)(c + j) * stride + 2 + d] : 0.0f;
+            for (int j = 0; j < 8; ++j) {
+                const int c = c0 + 4 * j;
+                const int cc = c < nchunks ? c : nchunks - 1;
+                const float *q = pd + (int64_t)cc * stride;  // rows start 8 bytes past a 16-byte boundary: two 8-byte loads
+                const float2 lo = *reinterpret_cast<const float2 *>(q), hi = *reinterpret_cast<const float2 *>(q + 2);
+                a[j][0] = lo.x, a[j][1] = lo.y, a[j][2] = hi.x, a[j][3] = hi.y;
+                w[j] = c < nchunks ? w_s[c] : 0.0f;
+            }
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (c + j < nchunks) acc[j & 3] = fmaf(a[j], w_s[c + j], acc[j & 3]);
+            for (int j = 0; j < 8; ++j) {
+                acc.x = fmaf(a[j][0], w[j], acc.x);
+                acc.y = fmaf(a[j][1], w[j], acc.y);
+                acc.z = fmaf(a[j][2], w[j], acc.z);
+                acc.w = fmaf(a[j][3], w[j], acc.w);
+            }
         }
-        out[((int64_t)b * nq + head) * hd + d] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * inv;
+        acc_s[warp][(d0 >> 2) + lane] = acc;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        const float *f = reinterpret_cast<const float *>(&acc_s[0][0]);
+        const float v = (f[d] + f[256 + d]) + (f[512 + d] + f[768 + d]);
+        out[((int64_t)b * nq + head) * hd + d] = v * inv;
     }
 }
 

@@ -19,11 +19,8 @@
 // accumulator to four epilogue warps that read it with tcgen05.ld and store f32 rows.
 // Every mbarrier wait is bounded; a give-up sets the context's error word and the CTA still
 // reaches the final barrier and frees its tensor memory.
-#include <cuda.h>
-
-#include <mutex>
-
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -91,57 +88,6 @@ __global__ void __launch_bounds__(256) w_to_f16_kernel(const uint8_t *__restrict
         for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
         *reinterpret_cast<uint4 *>(out + idx * 8) = *reinterpret_cast<uint4 *>(h);
     }
-}
-
-// ---- tcgen05 / TMA wrappers -------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
-        "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], f16 inputs, f32 accumulate.
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
-// swizzle (what a TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row atoms 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-           ((uint64_t)2 << 61);
-}
-// kind::f16 instruction descriptor: D f32, A/B f16, both K-major, M x N.
-__host__ __device__ constexpr uint32_t idesc_f16(int mm, int nn) {
-    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(nn >> 3) << 17) | ((uint32_t)(mm >> 4) << 24);
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 template <int BN>
@@ -394,22 +340,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 }
 
 // ---- host side ----------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
 // f16 [rows, k] row-major; box = 64 values of k x box_rows rows, 128-byte swizzle, zero fill outside.
 bool make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k, int box_rows) {  // box_rows <= 256
     EncodeTiledFn fn = encode_tiled_fn();
@@ -439,6 +369,9 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     if ((reinterpret_cast<uintptr_t>(w) & 1) != 0 || (reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
     if (m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
+    // narrow batches stream the raw blocks and dequantize into tensor memory: no f16 copy of W
+    if (ctx->tune.gemm_variant != 3 && !ctx->tune.gemm_cache_weights && qgemm_dequant_tmem_supported(qtype, m, k, w))
+        return launch_qgemm_dequant_tmem(ctx, order, x, m, k, ldx, w, n, y, ldy);
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
     const size_t w16_bytes = (size_t)n * k * 2;
     // With gemm_cache_weights the f16 copy of a weight matrix is made once and kept (the caller

@@ -68,3 +68,37 @@ def test_wide_batches_in_f32_and_q8_1_modes_use_the_decode_kernels(device, actmo
     got = run(device, oc.Q4_0, 0, x, blocks, 96, actmode=actmode)
     want = oc.qmatmul(oc.Q4_0, 0, x, blocks, 96, nthreads=8, q8_1=bool(actmode))
     assert rel_err(got, want) < 1e-4
+
+
+# ---- narrow batches (8 < m <= 64, Q4_0, k % 256 == 0): blocks dequantized into tensor memory ----
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(9, 128, 256), (16, 300, 512), (17, 129, 768), (32, 1000, 1024), (33, 4096, 4096), (64, 257, 2304),
+                                   (64, 11008, 4096), (12, 8192, 14336)])
+def test_narrow_batch_gemm_streams_raw_blocks(device, order, m, n, k):
+    w, x = make_case(9000 + m + n + k, n, k, m)
+    blocks = oc.quantize(oc.Q4_0, order, w)
+    got = run(device, oc.Q4_0, order, x, blocks, n)
+    assert rel_err(got, emulate_f16(oc.Q4_0, order, x, blocks, n)) < 2e-5
+    rows = np.linspace(0, m - 1, num=min(m, 4), dtype=int)
+    cpu = oc.qmatmul(oc.Q4_0, order, x[rows], blocks, n, nthreads=8)
+    assert rel_err(got[rows], cpu) <= REL_TOL
+    # the two-step path (f16 copy of W, then the wide kernel) computes from identical operands
+    device.set_option("gemm_variant", 3)
+    try:
+        two_step = run(device, oc.Q4_0, order, x, blocks, n)
+    finally:
+        device.set_option("gemm_variant", 0)
+    assert rel_err(got, two_step) < 2e-5  # f32 summation order differs (k split, tensor-core internals)
+
+
+def test_narrow_batch_gemm_edge_scales(device):
+    """Blocks whose scale is zero, subnormal or large: the f16 product d*(q-8) must still round once."""
+    n, k, m = 256, 512, 16
+    rng = np.random.default_rng(5)
+    blocks = rng.integers(0, 256, size=(n * k // 32, 18), dtype=np.uint8)
+    scales = np.array([0x0000, 0x8000, 0x0001, 0x03FF, 0x0400, 0x3C00, 0x57FF, 0xD000], dtype=np.uint16)
+    d = scales[rng.integers(0, len(scales), size=blocks.shape[0])]
+    blocks[:, 0], blocks[:, 1] = d & 0xFF, d >> 8
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    got = run(device, oc.Q4_0, 0, x, blocks.reshape(-1), n)
+    assert rel_err(got, emulate_f16(oc.Q4_0, 0, x, blocks.reshape(-1), n)) < 2e-5
