@@ -72,9 +72,10 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
         import torch
     for batch in batches:
         views = {}
-        # batch > 8 runs the tensor-core GEMM; its f16 weight copies are kept across steps (weights are
-        # static in a decode loop), trading 4x the Q4_0 bytes of device memory for no per-step conversion
-        dev.set_option("gemm_cache_weights", 1 if batch > 8 else 0)
+        # 8 < batch <= 64 runs the narrow tensor-core GEMM that streams the raw blocks; wider batches the
+        # f16 GEMM, whose f16 weight copies are then kept across steps (weights are static in a decode
+        # loop), trading 4x the Q4_0 bytes of device memory for no per-step conversion
+        dev.set_option("gemm_cache_weights", 1 if batch > 64 else 0)
 
         def allreduce(buf, count):
             key = buf.ptr.value
@@ -176,7 +177,9 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
             "allreduce": "none" if world == 1 else ("fused: peer stores from the GEMV epilogue + counters, summed inside the following residual+RMSNorm kernel"
                                                     if fused else f"NCCL sum of [{batch},8192] f32, twice per layer"),
             "nccl_ms_per_step": None if nccl_ms is None else round(nccl_ms, 4),
-            "linear_mode": "f32 activations (decode GEMV)" if batch <= 8 else "f16 operands (tensor-core GEMM), f16 weight copies cached",
+            "linear_mode": "f32 activations (decode GEMV)" if batch <= 8 else (
+                "f16 operands, raw blocks dequantized into tensor memory (narrow-batch tcgen05 GEMM)" if batch <= 64
+                else "f16 operands (tensor-core GEMM), f16 weight copies cached"),
         }
         del model
         dev.synchronize()

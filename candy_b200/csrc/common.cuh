@@ -138,6 +138,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Same, with a sleep between polls: a waiting warp then costs almost no issue slots (the plain
+// loop competes with working warps for the integer pipe).  About a second at most.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, uint32_t sleep_ns) {
+    const uint32_t limit = sleep_ns >= 512 ? (1u << 21) : (1u << 23);
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(sleep_ns);
+    }
+    return false;
+}
 __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

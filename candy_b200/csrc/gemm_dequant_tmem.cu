@@ -7,56 +7,78 @@
 // bytes, not by the tensor pipe.  Roles are swapped against the wide kernel: the WEIGHT rows are
 // the M side of the MMA (128 rows = 128 tensor-memory lanes) and the batch is the N side.
 //
-//   warp 0        TMA: per stage one [128 rows x 144 B] tile of raw blocks (256 values of k per
-//                 row; 2-D byte tensor map, no swizzle) and the matching [MPAD x 256] f16 slab of X
-//                 (four 64-wide boxes, 128-byte swizzle).
-//   warps 5-20    four groups of 128 threads, thread = (weight row, half a stage): nine 8-byte shared
-//                 loads fetch four blocks of the row, nibbles become f16 pairs with one mask-or each
-//                 (0x6400 | q = 1024 + q), one HSUB2/HFMA2 takes off the 1032 and one HMUL2
-//                 applies the block scale; the 64 packed registers go to tensor memory with
-//                 tcgen05.st as the A operand.  Two groups share a stage, pairs of groups alternate
-//                 stages; three A buffers.
-//   warps 1-4     one lane each issues tcgen05.mma (A from tensor memory, B = X slab through a
-//                 shared-memory descriptor), M=128, N=MPAD, K=16: four of a stage's sixteen steps
-//                 per issuer, each issuer into its own f32 accumulator (a single thread can start
-//                 an MMA only every ~90 cycles, too slow for narrow N); commits free the stage,
-//                 the A buffer and, at the end of a unit, hand the accumulators to the epilogue.
-//   warps 21-24   epilogue: tcgen05.ld of the four accumulators, add, store.  Lane = weight row, so for each batch row a warp
+// A CTA runs three (two for m > 32) independent pipes, one per 128-row tile of a group of tiles
+// that share each slab of X:
+//
+//   warp 0        TMA: per step one [MPAD x 256] f16 slab of X (four 64-wide boxes, 128-byte
+//                 swizzle) and, per pipe, one [128 rows x 144 B] tile of raw blocks (256 values of
+//                 k per row; 2-D byte tensor map, no swizzle).  Separate rings, so a stage of raw
+//                 blocks is free again as soon as it has been read into registers.
+//   4 warps/pipe  dequantize, thread = weight row: nine 16-byte shared loads fetch the row's eight
+//                 blocks (row pitch 144 B = 9 x 16 B, odd, so quarter-warps hit eight different
+//                 bank groups); nibbles become f16 pairs with one mask-or each (0x6400 | q =
+//                 1024 + q), one HSUB2/HFMA2 takes off the 1032 and one HMUL2 applies the block
+//                 scale; packed registers go to tensor memory with tcgen05.st as the A operand,
+//                 in two halves of 64 columns so the second half is converted while the first
+//                 is multiplied.
+//   1 lane/pipe   issues tcgen05.mma (A from tensor memory, B = X slab through a shared-memory
+//                 descriptor), M=128, N=MPAD, K=16, sixteen per item, into the pipe's own f32
+//                 accumulator.  A single thread can start an MMA only every ~90 cycles whatever
+//                 its shape -- far too slow for narrow N -- hence one issuer per pipe.
+//   4 warps       epilogue: tcgen05.ld, store.  Lane = weight row, so for each batch row a warp
 //                 writes 32 consecutive floats.
+//
+// Every mbarrier is waited on by the same threads for each of its phases, in order: a parity
+// wait cannot tell phase k from phase k-2, so no barrier is shared between alternating waiters.
 //
 // Inside a 32-block the nibble extraction yields the values in a fixed permuted order; X is
 // written to f16 scratch in the same order by the conversion pre-pass (a dot product does not
 // care), which also serves the ggml element order with a different table.
 //
-// A unit of work is (128-row tile, range of k).  k is split when the tiles alone would not fill
-// the SMs; partial sums then go to scratch and a small kernel adds them in a fixed order.  CTAs
-// are persistent: units u = blockIdx.x, +gridDim.x, ...; the stage ring, the A buffers and the
-// accumulators keep cycling across units.  Every wait is bounded.
+// Work is the list of (group of tiles, 256-wide chunk of k) steps, group-major; every CTA takes
+// an equal contiguous share, so the SMs finish together whatever n and k are.  A share is cut
+// into segments at group boundaries: a segment that spans a group's whole k range is written to
+// y, the others (at most two per CTA) go to scratch and a small kernel adds them in CTA order.
+// The rings, the A buffers and the accumulators keep cycling across segments.  Every wait is
+// bounded.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#ifdef CQ_TRACE
+// profiling aid (separate build): clock64 stamps of CTA 0's roles for 16 consecutive steps
+__device__ long long g_ft_trace[16 * 32];
+#define FT_TRACE(step, ev) do { if (blockIdx.x == 0 && (step) >= 8 && (step) < 24) g_ft_trace[((step) - 8) * 32 + (ev)] = clock64(); } while (0)
+extern "C" int cq_debug_trace_ft(long long *out) { return (int)cudaMemcpyFromSymbol(out, g_ft_trace, sizeof(long long) * 16 * 32); }
+#else
+#define FT_TRACE(step, ev)
+#endif
+
 namespace {
 
-constexpr int FT_ROWS = 128;                   // weight rows per unit
-constexpr int FT_KCHUNK = 256;                 // values of k per stage
-constexpr int FT_ROWCHUNK_Q4 = 8 * kQ4Bytes;   // 144 bytes of one row per stage
+constexpr int FT_ROWS = 128;                   // weight rows per tile = tensor-memory lanes
+constexpr int FT_KCHUNK = 256;                 // values of k per item
+constexpr int FT_ROWCHUNK_Q4 = 8 * kQ4Bytes;   // 144 bytes of one row per item
 constexpr int FT_WBYTES = FT_ROWS * FT_ROWCHUNK_Q4;  // 18432
-constexpr int FT_ACOLS = FT_KCHUNK / 2;        // 128 columns per A buffer
-constexpr int FT_ISSUERS = 4;                  // MMA-issuing warps, each with its own accumulator
-constexpr int FT_DQ_WARPS = 16;                // four groups of four warps (one per lane quarter)
-constexpr int FT_WARP_DQ0 = 1 + FT_ISSUERS;     // first dequantizing warp
-constexpr int FT_WARP_EP0 = FT_WARP_DQ0 + FT_DQ_WARPS;
-constexpr int FT_THREADS = 32 * (FT_WARP_EP0 + 4);
+constexpr int FT_ACOLS = FT_KCHUNK / 2;        // 128 columns of A per pipe (two halves of 64)
 
 template <int MPAD>
 struct FtCfg {
-    static constexpr int kXBytes = 4 * MPAD * 128;  // four 64-wide boxes of MPAD rows
-    static constexpr int kStageBytes = FT_WBYTES + kXBytes;
-    static constexpr int kStages = MPAD >= 64 ? 4 : (MPAD >= 32 ? 6 : 8);
-    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + 256;
-    // tensor memory: A buffers of 128 columns, then one accumulator of MPAD columns per issuing warp
-    static constexpr int kABufs = (512 - FT_ISSUERS * MPAD) / FT_ACOLS;  // 3 (MPAD <= 32) or 2 (MPAD = 64)
-    static constexpr int kDCol0 = kABufs * FT_ACOLS;
+    // Independent pipes per CTA, each = (tile of the group, a TMA warp, four dequantizing warps, two
+    // MMA-issuing lanes with an accumulator each, 128 columns of A in two halves).
+    static constexpr int kPipes = 2;
+    static constexpr int kGroupRows = kPipes * FT_ROWS;
+    static constexpr int kXBytes = 4 * MPAD * 128;  // one slab of X: four 64-wide boxes of MPAD rows
+    static constexpr int kXStages = MPAD >= 64 ? 2 : 3;
+    static constexpr int kWStages = 4;  // per pipe
+    static constexpr size_t kSmem = (size_t)kPipes * kWStages * FT_WBYTES + (size_t)kXStages * kXBytes + 1024 + 512;
+    // tensor memory: 128 columns of A per pipe, then two accumulators of MPAD columns per pipe
+    static constexpr int kDCol0 = kPipes * FT_ACOLS;
+    static constexpr int kWarpW0 = 2;                        // warps 0,1 load X; then one TMA warp per pipe
+    static constexpr int kWarpMma0 = kWarpW0 + kPipes;       // two issuing warps per pipe
+    static constexpr int kWarpDq0 = kWarpMma0 + 2 * kPipes;  // eight dequantizing warps per pipe: four per half of an item
+    static constexpr int kWarpEp0 = kWarpDq0 + 8 * kPipes;   // four epilogue warps
+    static constexpr int kThreads = 32 * (kWarpEp0 + 4);
+    static_assert(kDCol0 + 2 * kPipes * MPAD <= 512, "tensor memory");
 };
 
 // Position p of a block's 32 values, in the order the dequantizing threads emit them, holds
@@ -83,15 +105,31 @@ __global__ void __launch_bounds__(256) x_to_f16_perm_kernel(const float *__restr
     }
 }
 
-// y[m][j] = sum over splits of part[s][m][j], in split order.
-__global__ void __launch_bounds__(256) splitk_sum_kernel(const float *__restrict__ part, int splits, int64_t m, int64_t n, float *__restrict__ y,
-                                                       int64_t ldy) {
-    const int64_t total = m * n;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        float acc = part[i];
-        for (int s = 1; s < splits; ++s) acc += part[(int64_t)s * total + i];
-        const int64_t row = i / n;
-        y[row * ldy + (i - row * n)] = acc;
+// Groups of tiles whose k range was shared between CTAs: y[m][j] = sum of the CTAs' partials, in
+// CTA order.  CTA i owns steps [i*per_cta, (i+1)*per_cta); a group's steps are [t*nchunks, (t+1)*nchunks).
+// One block per (group, batch row), one thread per four columns.
+__global__ void __launch_bounds__(64) shared_group_sum_kernel(const float *__restrict__ part, int64_t m, int64_t n, int nchunks, int per_cta,
+                                                            float *__restrict__ y, int64_t ldy) {
+    constexpr int kGroupRows = 256;
+    const int t = blockIdx.x, row = blockIdx.y;
+    const int first = (t * nchunks) / per_cta, last = ((t + 1) * nchunks - 1) / per_cta;
+    if (first == last) return;  // one CTA had the group's whole k range and wrote y itself
+    const int r = threadIdx.x * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = first; c <= last; ++c) {
+        const int slot = 2 * c + (((c * per_cta) / nchunks == t) ? 0 : 1);
+        const float4 v = *reinterpret_cast<const float4 *>(part + ((int64_t)slot * m + row) * kGroupRows + r);
+        acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+    }
+    const int64_t j = (int64_t)t * kGroupRows + r;
+    float *dst = y + (int64_t)row * ldy + j;
+    if (j + 3 < n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<float4 *>(dst) = acc;
+    } else {
+        if (j < n) dst[0] = acc.x;
+        if (j + 1 < n) dst[1] = acc.y;
+        if (j + 2 < n) dst[2] = acc.z;
+        if (j + 3 < n) dst[3] = acc.w;
     }
 }
 
@@ -117,226 +155,289 @@ __device__ __forceinline__ void dequant_word(uint32_t n, __half2 d2, uint32_t *o
 }
 
 struct FtParams {
-    float *out;        // y, or the split partials [splits][m][n]
-    int64_t ld_out;    // row pitch of out in floats
-    int64_t split_stride;  // floats between two splits' partials (0 when not split)
-    int m, n, ntiles, nchunks, splits, chunks_per_split;
+    float *y;          // [m, n], row pitch ldy: groups whose whole k range one CTA owns are written here directly
+    int64_t ldy;
+    float *part;       // partial sums of groups shared between CTAs: [2 * ctas][m][group rows]
+    int m, n, nchunks;
+    int total, per_cta;  // (group, chunk) steps in all and per CTA
+    int probe;  // profiling aid: bit 0 = skip the dequantization arithmetic and stores, bit 1 = skip the MMAs
     int *err;
 };
 
 template <int MPAD>
-__global__ void __launch_bounds__(FT_THREADS, 1)
+__global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
     qgemm_q4_0_tmem_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const FtParams p) {
     using Cfg = FtCfg<MPAD>;
-    constexpr int STAGES = Cfg::kStages, FT_ABUFS = Cfg::kABufs, FT_DCOL0 = Cfg::kDCol0;
+    constexpr int WSP = Cfg::kWStages, XST = Cfg::kXStages, PIPES = Cfg::kPipes, DCOL0 = Cfg::kDCol0, GROUP_ROWS = Cfg::kGroupRows;
+    constexpr int NISS = 2 * PIPES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * Cfg::kStageBytes);
-    uint64_t *w_full = bars, *w_empty = bars + STAGES, *a_full = bars + 2 * STAGES, *a_empty = a_full + FT_ABUFS;
-    uint64_t *d_full = a_empty + FT_ABUFS, *d_empty = d_full + 1;
+    uint8_t *smem_w = smem;                                          // per pipe WSP stages of raw blocks
+    uint8_t *smem_x = smem + (size_t)PIPES * WSP * FT_WBYTES;        // XST slabs of X
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_x + (size_t)XST * Cfg::kXBytes);
+    uint64_t *w_full = bars, *w_empty = w_full + PIPES * WSP, *x_full = w_empty + PIPES * WSP, *x_empty = x_full + XST;
+    uint64_t *a_full = x_empty + XST, *a_empty = a_full + 2 * PIPES, *d_full = a_empty + 2 * PIPES, *d_empty = d_full + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nunits = p.ntiles * p.splits;
+    // this CTA's steps [g0, g1) of the (group, chunk) list: equal shares, so the SMs finish together
+    const int g0 = blockIdx.x * p.per_cta, g1 = min(g0 + p.per_cta, p.total);
+    const int nsteps = g1 - g0;
 
+    // Every barrier below is waited on by the same threads for each of its phases, in order
+    // (a parity wait cannot tell phase k from phase k-2).
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < PIPES * WSP; ++s) {
             mbar_init(smem_u32(&w_full[s]), 1);
-            mbar_init(smem_u32(&w_empty[s]), 8 + FT_ISSUERS);  // eight dequantizing warps + one commit per issuing warp
+            mbar_init(smem_u32(&w_empty[s]), 8);  // the pipe's eight dequantizing warps
         }
-        for (int b = 0; b < FT_ABUFS; ++b) {
-            mbar_init(smem_u32(&a_full[b]), 8);
-            mbar_init(smem_u32(&a_empty[b]), FT_ISSUERS);
+        for (int s = 0; s < XST; ++s) {
+            mbar_init(smem_u32(&x_full[s]), 2);   // the two X-loading warps
+            mbar_init(smem_u32(&x_empty[s]), NISS);
         }
-        mbar_init(smem_u32(&d_full[0]), FT_ISSUERS);
+        for (int b = 0; b < 2 * PIPES; ++b) {  // per pipe: one per half of an item
+            mbar_init(smem_u32(&a_full[b]), 4);
+            mbar_init(smem_u32(&a_empty[b]), 2);  // the pipe's two issuers
+        }
+        mbar_init(smem_u32(&d_full[0]), NISS);
         mbar_init(smem_u32(&d_empty[0]), 4);
         fence_mbar_init();
         fence_proxy_async();
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // unit -> (tile, first chunk, chunk count)
-    auto unit_chunks = [&](int u, int &tile, int &c0, int &cn) {
-        const int split = u / p.ntiles;
-        tile = u - split * p.ntiles;
-        c0 = split * p.chunks_per_split;
-        cn = min(p.chunks_per_split, p.nchunks - c0);
+    // the segment of the list that starts at step g: stays inside one group of tiles
+    auto segment = [&](int g, int &group, int &c0, int &cn) {
+        group = g / p.nchunks;
+        c0 = g - group * p.nchunks;
+        cn = min(p.nchunks - c0, g1 - g);
     };
 
-    if (warp == 0) {
+    // One thread can start a TMA copy or a tcgen05.mma only every few hundred / ~100 cycles, so
+    // both jobs are spread over several warps: two for X, one per pipe for the raw blocks, two
+    // issuers per pipe (each with its own accumulator: MMAs of different threads are unordered).
+    if (warp < Cfg::kWarpW0) {
+        // ---- TMA, X: warp 0 loads boxes 0,1 of every slab, warp 1 boxes 2,3 -------------------------
         if (lane == 0) {
-            int it = 0;
+            int step = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
-                int tile, c0, cn;
-                unit_chunks(u, tile, c0, cn);
-                for (int c = 0; c < cn; ++c, ++it) {
-                    const int s = it % STAGES;
-                    if (it >= STAGES && !mbar_wait_bounded(smem_u32(&w_empty[s]), ((it / STAGES) - 1) & 1)) {
+            for (int g = g0; g < g1 && ok;) {
+                int group, c0, cn;
+                segment(g, group, c0, cn);
+                g += cn;
+                for (int c = 0; c < cn; ++c, ++step) {
+                    const int xs = step % XST;
+                    if (warp == 0) FT_TRACE(step, 0);
+                    if (step >= XST && !mbar_wait_sleep(smem_u32(&x_empty[xs]), ((step / XST) - 1) & 1, 100)) {
                         atomicExch(p.err, kDevErrEmptyWait);
                         ok = false;
                         break;
                     }
-                    uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
-                    const uint32_t bar = smem_u32(&w_full[s]);
-                    mbar_expect_tx(bar, Cfg::kStageBytes);
-                    tma_load_2d(smem_u32(st), &tmW, (c0 + c) * FT_ROWCHUNK_Q4, tile * FT_ROWS, bar);
+                    const uint32_t xbar = smem_u32(&x_full[xs]);
+                    mbar_expect_tx(xbar, Cfg::kXBytes / 2);
 #pragma unroll
-                    for (int a = 0; a < 4; ++a)
-                        tma_load_2d(smem_u32(st + FT_WBYTES + a * MPAD * 128), &tmX, (c0 + c) * FT_KCHUNK + a * 64, 0, bar);
+                    for (int a = 2 * warp; a < 2 * warp + 2; ++a)
+                        tma_load_2d(smem_u32(smem_x + (size_t)xs * Cfg::kXBytes + a * MPAD * 128), &tmX, (c0 + c) * FT_KCHUNK + a * 64, 0, xbar);
+                    if (warp == 0) FT_TRACE(step, 1);
                 }
             }
-            const int first = it > STAGES ? it - STAGES : 0;
-            for (int i = first; i < it; ++i)
-                if (!mbar_wait_bounded(smem_u32(&w_full[i % STAGES]), (i / STAGES) & 1)) {
-                    atomicExch(p.err, kDevErrDrain);
-                    break;
-                }
+            if (ok)  // leave only when nothing is in flight into this CTA's shared memory
+                for (int i = step > XST ? step - XST : 0; i < step; ++i)
+                    if (!mbar_wait_sleep(smem_u32(&x_full[i % XST]), (i / XST) & 1, 100)) {
+                        atomicExch(p.err, kDevErrDrain);
+                        break;
+                    }
         }
-    } else if (warp < FT_WARP_DQ0) {
-        // ---- MMA: four issuing lanes (one per warp), each takes a quarter of a stage's sixteen
-        // K=16 steps into its own accumulator.  One thread can start a tcgen05.mma only every ~90
-        // cycles whatever its shape, so narrow MMAs need several issuers to keep the pipe fed.
+    } else if (warp < Cfg::kWarpMma0) {
+        // ---- TMA, raw blocks of pipe q: one [128 x 144 B] tile per step ------------------------------
+        if (lane == 0) {
+            const int q = warp - Cfg::kWarpW0;
+            int step = 0;
+            bool ok = true;
+            for (int g = g0; g < g1 && ok;) {
+                int group, c0, cn;
+                segment(g, group, c0, cn);
+                g += cn;
+                for (int c = 0; c < cn; ++c, ++step) {
+                    const int s = q * WSP + step % WSP;
+                    if (step >= WSP && !mbar_wait_sleep(smem_u32(&w_empty[s]), ((step / WSP) - 1) & 1, 100)) {
+                        atomicExch(p.err, kDevErrEmptyWait);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&w_full[s]);
+                    mbar_expect_tx(bar, FT_WBYTES);
+                    // tiles past the last row are outside the tensor: zero fill, no traffic
+                    tma_load_2d(smem_u32(smem_w + (size_t)s * FT_WBYTES), &tmW, (c0 + c) * FT_ROWCHUNK_Q4, (group * PIPES + q) * FT_ROWS, bar);
+                    if (q == 0) FT_TRACE(step, 2);
+                }
+            }
+            if (ok)
+                for (int i = step > WSP ? step - WSP : 0; i < step; ++i)
+                    if (!mbar_wait_sleep(smem_u32(&w_full[q * WSP + i % WSP]), (i / WSP) & 1, 100)) {
+                        atomicExch(p.err, kDevErrDrain);
+                        break;
+                    }
+        }
+    } else if (warp < Cfg::kWarpDq0) {
+        // ---- MMA: issuer (pipe q, parity e) takes every second K=16 step of both halves ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16(FT_ROWS, MPAD);
-            const int q = warp - 1;
-            int it = 0, ui = 0;
+            const int iss = warp - Cfg::kWarpMma0, q = iss >> 1, e = iss & 1;
+            int step = 0, seg = 0;
             bool ok = true;
-            const uint32_t acc = tmem_base + (uint32_t)(FT_DCOL0 + q * MPAD);
-            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++ui) {
-                int tile, c0, cn;
-                unit_chunks(u, tile, c0, cn);
-                if (ui >= 1 && !mbar_wait_bounded(smem_u32(&d_empty[0]), (ui - 1) & 1)) {  // epilogue has read the accumulators
+            const uint32_t acc = tmem_base + (uint32_t)(DCOL0 + iss * MPAD);
+            for (int g = g0; g < g1 && ok; ++seg) {
+                int group, c0, cn;
+                segment(g, group, c0, cn);
+                g += cn;
+                if (seg >= 1 && !mbar_wait_sleep(smem_u32(&d_empty[0]), (seg - 1) & 1, 100)) {  // epilogue has read the accumulators
                     atomicExch(p.err, kDevErrMma);
                     break;
                 }
                 tc_fence_after();
-                for (int c = 0; c < cn; ++c, ++it) {
-                    const int s = it % STAGES, ab = it % FT_ABUFS;
-                    if (!mbar_wait_bounded(smem_u32(&w_full[s]), (it / STAGES) & 1) ||
-                        !mbar_wait_bounded(smem_u32(&a_full[ab]), (it / FT_ABUFS) & 1)) {
+                for (int c = 0; c < cn && ok; ++c, ++step) {
+                    const int xs = step % XST;
+                    if (!mbar_wait_sleep(smem_u32(&x_full[xs]), (step / XST) & 1, 40)) {
                         atomicExch(p.err, kDevErrFullWait);
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
-                    // this issuer's 64 values of k: one 128-byte-swizzled box of X, 32 columns of A
-                    const uint64_t bdesc = smem_desc_k128(smem_u32(smem + (size_t)s * Cfg::kStageBytes + FT_WBYTES + q * (MPAD * 128)));
-                    const uint32_t a_t = tmem_base + (uint32_t)(ab * FT_ACOLS + q * 32);
+                    if (iss == 0) FT_TRACE(step, 16);
+                    const uint64_t bdesc = smem_desc_k128(smem_u32(smem_x + (size_t)xs * Cfg::kXBytes));
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) tc_mma_f16_ts(acc, a_t + 8 * j, bdesc + 2 * j, idesc, (c | j) != 0);
-                    tc_commit(smem_u32(&w_empty[s]));
-                    tc_commit(smem_u32(&a_empty[ab]));
+                    for (int h = 0; h < 2; ++h) {
+                        if (!mbar_wait_sleep(smem_u32(&a_full[2 * q + h]), step & 1, 20)) {
+                            atomicExch(p.err, kDevErrFullWait);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        if (iss == 0) FT_TRACE(step, 17 + 2 * h);
+                        const uint32_t a_t = tmem_base + (uint32_t)(q * FT_ACOLS + h * 64);
+                        if (!(p.probe & 2)) {
+#pragma unroll
+                            for (int j2 = 0; j2 < 4; ++j2) {
+                                const int j = 2 * j2 + e;  // K=16 step inside the half
+                                const int jj = 8 * h + j;  // ... inside the item: X box jj/4, 32-byte column jj%4
+                                tc_mma_f16_ts(acc, a_t + 8 * j, bdesc + (uint64_t)((jj >> 2) * (MPAD * 128 / 16) + (jj & 3) * 2), idesc, (c | h | j2) != 0);
+                            }
+                        }
+                        tc_commit(smem_u32(&a_empty[2 * q + h]));
+                        if (iss == 0) FT_TRACE(step, 18 + 2 * h);
+                    }
+                    tc_commit(smem_u32(&x_empty[xs]));
                 }
                 tc_commit(smem_u32(&d_full[0]));
             }
         }
-    } else if (warp < FT_WARP_EP0) {
-        // ---- dequantize: thread = (weight row, half of the stage's 256 values); a group of four
-        // warps covers the 128 rows, groups 0/1 take the two halves of even stages, 2/3 of odd ones
-        const int g = (warp - FT_WARP_DQ0) >> 2;
-        const int half = g & 1, parity = g >> 1;
+    } else if (warp < Cfg::kWarpEp0) {
+        // ---- dequantize: per pipe four warps for each half of an item, thread = weight row ----------
+        const int dw = warp - Cfg::kWarpDq0, q = dw >> 3, h = (dw >> 2) & 1;
         const int quarter = warp & 3;  // the tensor-memory lanes this warp may touch
         const int r = quarter * 32 + lane;
-        int it = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
-            int tile, c0, cn;
-            unit_chunks(u, tile, c0, cn);
-            for (int c = 0; c < cn; ++c, ++it) {
-                if ((it & 1) != parity) continue;
-                const int s = it % STAGES, ab = it % FT_ABUFS;
-                if (!mbar_wait_bounded(smem_u32(&w_full[s]), (it / STAGES) & 1)) {
-                    if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-                    ok = false;
-                    break;
-                }
-                uint32_t w[18];  // four blocks = 72 bytes, 8-byte aligned
-                const uint2 *src = reinterpret_cast<const uint2 *>(smem + (size_t)s * Cfg::kStageBytes + r * FT_ROWCHUNK_Q4 + half * 72);
-#pragma unroll
-                for (int i = 0; i < 9; ++i) {
-                    const uint2 t = src[i];
-                    w[2 * i] = t.x, w[2 * i + 1] = t.y;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&w_empty[s]));  // the raw blocks are in registers: the stage may be refilled
-                if (it >= FT_ABUFS && !mbar_wait_bounded(smem_u32(&a_empty[ab]), ((it / FT_ABUFS) - 1) & 1)) {
-                    if (lane == 0) atomicExch(p.err, kDevErrMma);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t a_t = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * FT_ACOLS + half * 64);
-#pragma unroll
-                for (int pr = 0; pr < 2; ++pr) {
-                    // two blocks in nine words: the first starts on a word, its nibbles two bytes in;
-                    // the second starts two bytes into word 4, its nibbles on word 5
-                    const uint32_t *q = w + 9 * pr;
-                    uint32_t o[16];
-                    {
-                        const __half dh = __ushort_as_half((unsigned short)(q[0] & 0xFFFFu));
-                        const __half2 d2 = __halves2half2(dh, dh);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) dequant_word(__funnelshift_r(q[j], q[j + 1], 16), d2, o + 4 * j);
-                        tmem_st16(a_t + (uint32_t)((2 * pr) * 16), o);
-                    }
-                    {
-                        const __half dh = __ushort_as_half((unsigned short)(q[4] >> 16));
-                        const __half2 d2 = __halves2half2(dh, dh);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) dequant_word(q[5 + j], d2, o + 4 * j);
-                        tmem_st16(a_t + (uint32_t)((2 * pr + 1) * 16), o);
-                    }
-                }
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&a_full[ab]));
+        const bool tracer = q == 0 && quarter == 0 && lane == 0;
+        for (int step = 0; step < nsteps; ++step) {
+            const int s = q * WSP + step % WSP;
+            if (!mbar_wait_sleep(smem_u32(&w_full[s]), (step / WSP) & 1, 60)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                break;
             }
-        }
-    } else {
-        // ---- epilogue: adds the issuers' accumulators, lane = weight row ----------------------
-        const int quarter = warp & 3;
-        int ui = 0;
-        for (int u = blockIdx.x; u < nunits; u += gridDim.x, ++ui) {
-            const int split = u / p.ntiles, tile = u - split * p.ntiles;
-            if (!mbar_wait_bounded(smem_u32(&d_full[0]), ui & 1)) {
+            if (tracer) FT_TRACE(step, 8 + 3 * h);
+            uint32_t w[18];  // four blocks = 72 bytes, 8-byte aligned
+            const uint2 *src = reinterpret_cast<const uint2 *>(smem_w + (size_t)s * FT_WBYTES + r * FT_ROWCHUNK_Q4 + h * 72);
+#pragma unroll
+            for (int i = 0; i < 9; ++i) {
+                const uint2 t = src[i];
+                w[2 * i] = t.x, w[2 * i + 1] = t.y;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&w_empty[s]));  // the raw blocks are in registers: the stage may be refilled
+            if (step >= 1 && !mbar_wait_sleep(smem_u32(&a_empty[2 * q + h]), (step - 1) & 1, 20)) {
                 if (lane == 0) atomicExch(p.err, kDevErrMma);
                 break;
             }
             tc_fence_after();
-            const int row = tile * FT_ROWS + quarter * 32 + lane;
-            float *dst = p.out + (int64_t)split * p.split_stride + row;
+            if (tracer) FT_TRACE(step, 9 + 3 * h);
+            const uint32_t a_t = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(q * FT_ACOLS + h * 64);
+            if (!(p.probe & 1)) {
+#pragma unroll
+                for (int pr = 0; pr < 2; ++pr) {
+                    // two blocks in nine words: the first starts on a word, its nibbles two bytes in;
+                    // the second starts two bytes into word 4, its nibbles on word 5
+                    const uint32_t *wq = w + 9 * pr;
+                    uint32_t o[16];
+                    {
+                        const __half dh = __ushort_as_half((unsigned short)(wq[0] & 0xFFFFu));
+                        const __half2 d2 = __halves2half2(dh, dh);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dequant_word(__funnelshift_r(wq[j], wq[j + 1], 16), d2, o + 4 * j);
+                        tmem_st16(a_t + (uint32_t)((2 * pr) * 16), o);
+                    }
+                    {
+                        const __half dh = __ushort_as_half((unsigned short)(wq[4] >> 16));
+                        const __half2 d2 = __halves2half2(dh, dh);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dequant_word(wq[5 + j], d2, o + 4 * j);
+                        tmem_st16(a_t + (uint32_t)((2 * pr + 1) * 16), o);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&a_full[2 * q + h]));
+            if (tracer) FT_TRACE(step, 10 + 3 * h);
+        }
+    } else {
+        // ---- epilogue: two accumulators per tile of the group, lane = weight row ---------------------
+        const int quarter = warp & 3;
+        int seg = 0;
+        for (int g = g0; g < g1; ++seg) {
+            int group, c0, cn;
+            segment(g, group, c0, cn);
+            const bool first_seg = g == g0;
+            g += cn;
+            if (!mbar_wait_sleep(smem_u32(&d_full[0]), seg & 1, 500)) {
+                if (lane == 0) atomicExch(p.err, kDevErrMma);
+                break;
+            }
+            tc_fence_after();
+            // whole k range -> y; otherwise one of this CTA's two partial slots (0: the segment its share starts with)
+            const bool direct = cn == p.nchunks;
+            const int64_t ld = direct ? p.ldy : GROUP_ROWS;
 #pragma unroll 1
-            for (int c = 0; c < MPAD / 16; ++c) {
-                float v[16];
+            for (int t = 0; t < PIPES; ++t) {
+                const int row_in_group = t * FT_ROWS + quarter * 32 + lane;
+                const int row = group * GROUP_ROWS + row_in_group;
+                float *dst = direct ? p.y + row : p.part + ((int64_t)(2 * blockIdx.x + (first_seg ? 0 : 1)) * p.m) * GROUP_ROWS + row_in_group;
+#pragma unroll 1
+                for (int c = 0; c < MPAD / 16; ++c) {
+                    uint32_t v0[16], v1[16];
+                    const uint32_t col = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(DCOL0 + 2 * t * MPAD + c * 16);
+                    tmem_ld16(col, v0);
+                    tmem_ld16(col + MPAD, v1);
+                    if (t == PIPES - 1 && c == MPAD / 16 - 1) {  // everything is in registers: the issuers may overwrite the accumulators
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&d_empty[0]));
+                    }
+                    if (row < p.n) {
 #pragma unroll
-                for (int q = 0; q < FT_ISSUERS; ++q) {
-                    uint32_t t[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(FT_DCOL0 + q * MPAD + c * 16), t);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = q == 0 ? __uint_as_float(t[i]) : v[i] + __uint_as_float(t[i]);
-                }
-                if (c == MPAD / 16 - 1) {  // everything is in registers: the issuers may overwrite the accumulators
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&d_empty[0]));
-                }
-                if (row < p.n) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (c * 16 + i < p.m) dst[(int64_t)(c * 16 + i) * p.ld_out] = v[i];
+                        for (int i = 0; i < 16; ++i)
+                            if (c * 16 + i < p.m) dst[(int64_t)(c * 16 + i) * ld] = __uint_as_float(v0[i]) + __uint_as_float(v1[i]);
+                    }
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
 bool make_w_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes) {
@@ -367,7 +468,7 @@ cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, co
         CQ_CUDA(ctx, cudaFuncSetAttribute(qgemm_q4_0_tmem_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FtCfg<MPAD>::kSmem));
         configured = ctx->device;
     }
-    qgemm_q4_0_tmem_kernel<MPAD><<<ctas, FT_THREADS, FtCfg<MPAD>::kSmem, ctx->stream>>>(tmW, tmX, p);
+    qgemm_q4_0_tmem_kernel<MPAD><<<ctas, FtCfg<MPAD>::kThreads, FtCfg<MPAD>::kSmem, ctx->stream>>>(tmW, tmX, p);
     CQ_CUDA(ctx, cudaGetLastError());
     return CQ_OK;
 }
@@ -383,45 +484,44 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int6
     if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
     if (n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
-    const int ntiles = (int)((n + FT_ROWS - 1) / FT_ROWS);
+    const int mpad = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    const int group_rows = FtCfg<32>::kGroupRows;
+    const int ngroups = (int)((n + group_rows - 1) / group_rows);
     const int nchunks = (int)(k / FT_KCHUNK);
-    // split k until the units cover the SMs about one and a half times, keeping at least two chunks per unit
-    int splits = 1;
-    while (ntiles * splits < ctx->sm_count * 3 / 2 && nchunks / (splits * 2) >= 2 && splits < 16) splits *= 2;
-    int cps = (nchunks + splits - 1) / splits;
-    splits = (nchunks + cps - 1) / cps;  // no empty split
+    const int64_t total = (int64_t)ngroups * nchunks;
+    if (total > 0x3FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: too many tiles");
+    // equal shares of the (group, chunk) list per CTA; at least two steps (eight tile-chunks) each
+    int64_t per_cta = (total + ctx->sm_count - 1) / ctx->sm_count;
+    if (per_cta < 2) per_cta = total < 2 ? total : 2;
+    const unsigned ctas = (unsigned)((total + per_cta - 1) / per_cta);
+    const bool shared_tiles = per_cta % nchunks != 0;
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
-    const size_t part_bytes = splits > 1 ? (size_t)splits * m * n * 4 : 0;
+    const size_t part_bytes = shared_tiles ? (size_t)2 * ctas * m * group_rows * 4 : 0;
     cq_status s = cq_reserve_scratch(ctx, x16_bytes + part_bytes);
     if (s != CQ_OK) return s;
     __half *x16 = static_cast<__half *>(ctx->scratch);
     float *part = reinterpret_cast<float *>(static_cast<uint8_t *>(ctx->scratch) + x16_bytes);
     {
-        const int64_t total = m * (k / 32);
+        const int64_t items = m * (k / 8);
         const unsigned cap = (unsigned)ctx->sm_count * 8;
-        const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+        const unsigned grid = (unsigned)((items + 255) / 256 < cap ? (items + 255) / 256 : cap);
         x_to_f16_perm_kernel<<<grid, 256, 0, ctx->stream>>>(x, m, k, ldx, order, x16);
     }
-    const int mpad = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
     CUtensorMap tmW, tmX;
     if (!make_w_map(&tmW, w, n, (k / 32) * kQ4Bytes) || !make_x_map(&tmX, x16, m, k, mpad))
         return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
     FtParams p;
-    p.out = splits > 1 ? part : y;
-    p.ld_out = splits > 1 ? n : ldy;
-    p.split_stride = splits > 1 ? m * n : 0;
-    p.m = (int)m, p.n = (int)n, p.ntiles = ntiles, p.nchunks = nchunks, p.splits = splits, p.chunks_per_split = cps;
+    p.y = y, p.ldy = ldy, p.part = part;
+    p.m = (int)m, p.n = (int)n, p.nchunks = nchunks, p.total = (int)total, p.per_cta = (int)per_cta;
     p.err = ctx->dev_err_devptr;
-    const int64_t nunits = (int64_t)ntiles * splits;
-    const unsigned ctas = (unsigned)(nunits < ctx->sm_count ? nunits : ctx->sm_count);
+    p.probe = ctx->tune.gemv_probe;
     if (mpad == 16) s = run_ft<16>(ctx, tmW, tmX, p, ctas);
     else if (mpad == 32) s = run_ft<32>(ctx, tmW, tmX, p, ctas);
     else s = run_ft<64>(ctx, tmW, tmX, p, ctas);
     if (s != CQ_OK) return s;
-    if (splits > 1) {
-        const int64_t total = m * n;
-        const unsigned grid = (unsigned)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
-        splitk_sum_kernel<<<grid, 256, 0, ctx->stream>>>(part, splits, m, n, y, ldy);
+    if (shared_tiles) {
+        static_assert(FtCfg<16>::kGroupRows == 256 && FtCfg<32>::kGroupRows == 256 && FtCfg<64>::kGroupRows == 256, "sum kernel layout");
+        shared_group_sum_kernel<<<dim3((unsigned)ngroups, (unsigned)m), 64, 0, ctx->stream>>>(part, m, n, nchunks, (int)per_cta, y, ldy);
         CQ_CUDA(ctx, cudaGetLastError());
     }
     return CQ_OK;
