@@ -1,19 +1,22 @@
 // Tensor-parallel exchange without a collective library: the row-parallel linear's all-reduce is
 // split between the kernel before it and the kernel after it.
 //
-//   producer  cq_qmatmul_push      the decode GEMV writes its partial results straight into every
-//                                  rank's receive buffer (plain peer stores over NVLink/NVSwitch) and,
-//                                  per CTA, bumps one counter on each peer (red.release.sys).
-//   consumer  cq_add_rmsnorm_reduce waits (bounded) until every rank's counter shows all of that
-//                                  rank's CTAs, sums the world partials from its OWN memory into the
-//                                  residual, applies RMSNorm, and re-arms the counters.
+//   producer  cq_qmatmul_push      the decode GEMV writes each partial result straight into every
+//                                  rank's receive buffer (plain peer stores over NVLink/NVSwitch) as
+//                                  one 8-byte pair (value bits, tag).
+//   consumer  cq_add_rmsnorm_reduce polls (bounded) each pair in its OWN memory until the tag is the
+//                                  one this exchange carries, sums the world partials in rank order,
+//                                  adds the sum to the residual, applies RMSNorm, and advances the tag.
 //
-// No extra kernel, no NCCL call, nothing loaded from a peer (data is pushed, then read locally).
+// Value and tag arrive together (an aligned 8-byte store is single-copy atomic), so the data is
+// usable one NVLink hop after it was produced: no fence, no separate flag, no extra kernel, no
+// NCCL call, nothing loaded from a peer.  The tag is a per-set counter kept in each rank's own
+// memory and advanced by the consumer, so a captured CUDA graph replays correctly.
 // Buffers come in two sets used alternately (o-projection: set 0, down-projection: set 1); a rank
 // can only push into a set again after it consumed the other set, which needs every rank's push
-// there, which every rank issues after consuming (and re-arming) this set -- so reuse is ordered
-// by the data flow itself.  One process per GPU; peers are mapped with CUDA IPC handles that the
-// host exchanges through whatever transport it has (torch.distributed object gather in bench.py).
+// there, which every rank issues after consuming this set -- so reuse is ordered by the data flow
+// itself.  One process per GPU; peers are mapped with CUDA IPC handles that the host exchanges
+// through whatever transport it has (torch.distributed object gather in the benchmark).
 // The reference has no multi-device code at all; nothing here has a counterpart in it.
 #include <vector>
 
@@ -24,70 +27,61 @@ constexpr int kMaxWorld = 16;
 struct cq_comm {
     int rank = 0, world = 1;
     size_t max_floats = 0;          // capacity of one slot
-    void *local = nullptr;          // [2 sets][world slots][max_floats] f32, then [2][kMaxWorld] u32 counters, then [2] u32 "done"
+    void *local = nullptr;          // [2 sets][world slots][max_floats] (value, tag) pairs, then [2] tags, then [2] "done" counters
     void *peer_base[kMaxWorld] = {};
     bool opened[kMaxWorld] = {};
-    float **d_push_rx[2] = {};      // device arrays [world]: my slot on each peer, per set
-    unsigned **d_push_cnt[2] = {};  // device arrays [world]: my counter on each peer, per set
-    int64_t expected[2] = {0, 0};   // arrivals per peer the consumer of each set waits for
+    uint2 **d_push_rx[2] = {};      // device arrays [world]: my slot on each rank, per set
+    bool pushed[2] = {false, false};
 };
 
 namespace {
 
-size_t comm_bytes(int world, size_t max_floats) { return 2 * (size_t)world * max_floats * 4 + 2 * kMaxWorld * 4 + 64; }
-float *slot_ptr(void *base, int world, size_t max_floats, int set, int slot) {
-    return reinterpret_cast<float *>(base) + ((size_t)set * world + slot) * max_floats;
+size_t comm_bytes(int world, size_t max_floats) { return 2 * (size_t)world * max_floats * 8 + 64; }
+uint2 *slot_ptr(void *base, int world, size_t max_floats, int set, int slot) {
+    return reinterpret_cast<uint2 *>(base) + ((size_t)set * world + slot) * max_floats;
 }
-unsigned *cnt_ptr(void *base, int world, size_t max_floats, int set, int slot) {
-    return reinterpret_cast<unsigned *>(reinterpret_cast<uint8_t *>(base) + 2 * (size_t)world * max_floats * 4) + set * kMaxWorld + slot;
+unsigned *seq_ptr(void *base, int world, size_t max_floats, int set) {
+    return reinterpret_cast<unsigned *>(reinterpret_cast<uint8_t *>(base) + 2 * (size_t)world * max_floats * 8) + set;
 }
-unsigned *done_ptr(void *base, int world, size_t max_floats, int set) {
-    return reinterpret_cast<unsigned *>(reinterpret_cast<uint8_t *>(base) + 2 * (size_t)world * max_floats * 4 + 2 * kMaxWorld * 4) + set;
-}
+unsigned *done_ptr(void *base, int world, size_t max_floats, int set) { return seq_ptr(base, world, max_floats, 0) + 2 + set; }
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_volatile_pair(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 
 // One CTA per row.  x[row] += sum over ranks of rx[rank][row]; y[row] = rmsnorm(x[row]) * alpha.
-__global__ void __launch_bounds__(1024) add_rmsnorm_reduce_kernel(float *__restrict__ x, const float *rx, int world, int64_t slot_stride,
-                                                                const unsigned *cnt, unsigned *cnt_rw, unsigned *done, unsigned expected,
-                                                                const float *__restrict__ alpha, int cols, float eps, float *__restrict__ y,
-                                                                int *err) {
+__global__ void __launch_bounds__(1024) add_rmsnorm_reduce_kernel(float *__restrict__ x, const uint2 *rx, int world, int64_t slot_stride,
+                                                                unsigned *seq, unsigned *done, const float *__restrict__ alpha, int cols,
+                                                                float eps, float *__restrict__ y, int *err) {
     __shared__ float sh[32];
-    __shared__ int ok_s;
     pdl_launch_dependents();
     pdl_wait_prior();
-    if (threadIdx.x == 0) ok_s = 1;
-    __syncthreads();
-    if ((int)threadIdx.x < world) {
-        // bounded wait for rank threadIdx.x's pushes (about two seconds at most, then give up)
-        bool ok = false;
-        for (unsigned it = 0; it < (1u << 22); ++it) {
-            if (ld_acquire_sys(cnt + threadIdx.x) >= expected) {
-                ok = true;
-                break;
-            }
-            __nanosleep(it < 64 ? 0 : 200);
-        }
-        if (!ok) {
-            atomicExch(err, kDevErrFullWait);
-            ok_s = 0;
-        }
-    }
-    __syncthreads();
+    const unsigned tag = *seq + 1u;  // advanced only after every CTA of this grid has read it (below)
     float *xr = x + (int64_t)blockIdx.x * cols;
     float *yr = y + (int64_t)blockIdx.x * cols;
-    const float *r0 = rx + (int64_t)blockIdx.x * cols;
+    const uint2 *r0 = rx + (int64_t)blockIdx.x * cols;
     float ss = 0.0f;
+    bool timed_out = false;
     for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-        float v = xr[c];
-        for (int r = 0; r < world; ++r) v += r0[(int64_t)r * slot_stride + c];  // rank order: identical sums on every rank
+        float d = 0.0f;  // partials first, in rank order (identical on every rank), then the residual: what an all-reduce would give
+        for (int r = 0; r < world; ++r) {
+            const uint2 *src = r0 + (int64_t)r * slot_stride + c;
+            uint2 v = ld_volatile_pair(src);
+            // bounded wait for this value (about a second at most, then give up and flag it)
+            for (unsigned it = 0; v.y != tag && it < (1u << 22) && !timed_out; ++it) {
+                if (it >= 32) __nanosleep(it < 1024 ? 100 : 400);
+                v = ld_volatile_pair(src);
+            }
+            if (v.y != tag) timed_out = true;
+            d = r == 0 ? __uint_as_float(v.x) : d + __uint_as_float(v.x);
+        }
+        const float v = xr[c] + d;
         xr[c] = v;
         ss = fmaf(v, v, ss);
     }
+    if (timed_out) atomicExch(err, kDevErrFullWait);
     // block sum
     {
         const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -101,14 +95,14 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_reduce_kernel(float *__restr
     }
     const float scale = 1.0f / sqrtf(ss / (float)cols + eps);
     for (int c = threadIdx.x; c < cols; c += blockDim.x) yr[c] = alpha ? scale * xr[c] * alpha[c] : scale * xr[c];
-    // the last row's CTA re-arms the counters for the next use of this set
+    // the last row's CTA advances the tag for the next use of this set
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         const unsigned prev = atomicAdd(done, 1u);
         if (prev == gridDim.x - 1) {
-            for (int r = 0; r < world; ++r) atomicSub(cnt_rw + r, expected);  // subtract, not clear: early arrivals of a later use survive
             atomicExch(done, 0u);
+            atomicExch(seq, tag);
         }
     }
 }
@@ -151,16 +145,10 @@ cq_status cq_comm_connect(cq_ctx *ctx, cq_comm *c, const void *all_handles) {
         c->opened[r] = true;
     }
     for (int set = 0; set < 2; ++set) {
-        std::vector<float *> rx(c->world);
-        std::vector<unsigned *> cnt(c->world);
-        for (int r = 0; r < c->world; ++r) {
-            rx[r] = slot_ptr(c->peer_base[r], c->world, c->max_floats, set, c->rank);
-            cnt[r] = cnt_ptr(c->peer_base[r], c->world, c->max_floats, set, c->rank);
-        }
-        CQ_CUDA(ctx, cudaMalloc((void **)&c->d_push_rx[set], sizeof(float *) * c->world));
-        CQ_CUDA(ctx, cudaMalloc((void **)&c->d_push_cnt[set], sizeof(unsigned *) * c->world));
-        CQ_CUDA(ctx, cudaMemcpy(c->d_push_rx[set], rx.data(), sizeof(float *) * c->world, cudaMemcpyHostToDevice));
-        CQ_CUDA(ctx, cudaMemcpy(c->d_push_cnt[set], cnt.data(), sizeof(unsigned *) * c->world, cudaMemcpyHostToDevice));
+        std::vector<uint2 *> rx(c->world);
+        for (int r = 0; r < c->world; ++r) rx[r] = slot_ptr(c->peer_base[r], c->world, c->max_floats, set, c->rank);
+        CQ_CUDA(ctx, cudaMalloc((void **)&c->d_push_rx[set], sizeof(uint2 *) * c->world));
+        CQ_CUDA(ctx, cudaMemcpy(c->d_push_rx[set], rx.data(), sizeof(uint2 *) * c->world, cudaMemcpyHostToDevice));
     }
     return CQ_OK;
 }
@@ -173,7 +161,6 @@ cq_status cq_comm_destroy(cq_ctx *ctx, cq_comm *c) {
         if (c->opened[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
     for (int set = 0; set < 2; ++set) {
         if (c->d_push_rx[set]) cudaFree(c->d_push_rx[set]);
-        if (c->d_push_cnt[set]) cudaFree(c->d_push_cnt[set]);
     }
     if (c->local) cudaFree(c->local);
     delete c;
@@ -190,12 +177,11 @@ cq_status cq_qmatmul_push(cq_ctx *ctx, cq_comm *c, int set, int qtype, int order
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul_push: need 1 <= m <= 8, k % 32 == 0, ldx >= k");
     if ((size_t)(m * n) > c->max_floats) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "cq_qmatmul_push: m*n exceeds the communicator's slot size");
     ctx->push.rx = c->d_push_rx[set];
-    ctx->push.cnt = c->d_push_cnt[set];
+    ctx->push.seq = seq_ptr(c->local, c->world, c->max_floats, set);
     ctx->push.world = c->world;
     ctx->push.row_stride = n;
-    ctx->push.arrivals = 0;
     cq_status s = launch_gemv(ctx, qtype, order, CQ_ACT_F32, x_dev, m, k, ldx, w_blocks_dev, n, /*y unused*/ const_cast<float *>(x_dev), n);
-    c->expected[set] = ctx->push.arrivals;
+    c->pushed[set] = s == CQ_OK;
     ctx->push = PushSpec();
     return s;
 }
@@ -206,7 +192,7 @@ cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *c, int set, float *x_dev, 
     if (!c || (set != 0 && set != 1) || !x_dev || !y_dev || rows < 1 || rows > 8 || cols < 1 || cols > 0x7FFFFFFF)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: bad arguments");
     if ((size_t)(rows * cols) > c->max_floats) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "cq_add_rmsnorm_reduce: rows*cols exceeds the slot size");
-    if (c->expected[set] <= 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: no cq_qmatmul_push was issued into this set");
+    if (!c->pushed[set]) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: no cq_qmatmul_push was issued into this set");
     const int threads = cols >= 4096 ? 1024 : (cols >= 1024 ? 512 : 256);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)rows);
@@ -217,11 +203,10 @@ cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *c, int set, float *x_dev, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
-    const float *rx = slot_ptr(c->local, c->world, c->max_floats, set, 0);
-    unsigned *cnt = cnt_ptr(c->local, c->world, c->max_floats, set, 0);
-    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, add_rmsnorm_reduce_kernel, x_dev, rx, c->world, (int64_t)c->max_floats, (const unsigned *)cnt, cnt,
-                                    done_ptr(c->local, c->world, c->max_floats, set), (unsigned)c->expected[set], alpha_dev, (int)cols, eps,
-                                    y_dev, ctx->dev_err_devptr));
+    const uint2 *rx = slot_ptr(c->local, c->world, c->max_floats, set, 0);
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, add_rmsnorm_reduce_kernel, x_dev, rx, c->world, (int64_t)c->max_floats,
+                                    seq_ptr(c->local, c->world, c->max_floats, set), done_ptr(c->local, c->world, c->max_floats, set), alpha_dev,
+                                    (int)cols, eps, y_dev, ctx->dev_err_devptr));
     return CQ_OK;
 }
 

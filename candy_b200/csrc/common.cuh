@@ -35,11 +35,10 @@ struct GemvTuning {
 
 // Set by the tensor-parallel entry point around one GEMV launch (see comm.cu).
 struct PushSpec {
-    float *const *rx = nullptr;
-    unsigned *const *cnt = nullptr;
+    uint2 *const *rx = nullptr;    // [world] this rank's slot in each rank's receive buffer: (value bits, tag) pairs
+    const unsigned *seq = nullptr; // local word: tag of the last completed exchange on this set
     int world = 0;
     int64_t row_stride = 0;
-    int64_t arrivals = 0;
 };
 
 struct cq_ctx {

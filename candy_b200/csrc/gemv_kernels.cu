@@ -71,8 +71,8 @@ struct GemvParams {
     int coop_off;      // byte offset of the cooperative activation staging area in dynamic smem, or -1
     // Row-parallel tensor parallelism: instead of y, the results go straight into every rank's
     // receive buffer (peer stores over NVLink), then one counter per peer is bumped per CTA.
-    float *const *push_rx;      // [world] this rank's slot in each peer's receive buffer
-    unsigned *const *push_cnt;  // [world] this rank's arrival counter on each peer
+    uint2 *const *push_rx;      // [world] this rank's slot in each rank's receive buffer: (value bits, tag)
+    const unsigned *push_seq;   // tag of the last completed exchange; this launch tags its values with +1
     int push_world;             // 0 = ordinary launch
     int64_t push_off;           // element offset of this activation row inside the slot
     int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers, 3 = empty kernel
@@ -696,6 +696,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     int rows_left = nrows;
     int buf = 0;
     bool dead = false;
+    const unsigned push_tag = p.push_world > 0 ? *p.push_seq + 1u : 0u;
 
     const int sub_bytes = p.rpp * p.row_bytes;  // distance between a thread's two rows of a pass
     for (int pbase = 0; pbase < npass; pbase += kPassGroup) {
@@ -801,7 +802,12 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 float tot = 0.0f;
                 for (int w = 0; w < p.wpr; ++w) tot += red[buf][i][rs * p.wpr + w];
                 if (p.push_world > 0) {
-                    for (int pr = 0; pr < p.push_world; ++pr) p.push_rx[pr][p.push_off + row_begin + r] = tot;
+                    // value and tag travel in one 8-byte store: the receiver polls the data itself, so
+                    // nothing but one NVLink hop lies between this store and its use (no fence, no flag)
+                    const uint2 v = make_uint2(__float_as_uint(tot), push_tag);
+                    for (int pr = 0; pr < p.push_world; ++pr)
+                        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.push_rx[pr] + p.push_off + row_begin + r), "r"(v.x), "r"(v.y)
+                                     : "memory");
                 } else {
                     p.y[row_begin + r] = tot;
                 }
@@ -811,12 +817,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
         buf ^= 1;
     }
     TRACE(9);
-    if (p.push_world > 0) {
-        // all of this CTA's peer stores are ordered before the counter bumps that announce them
-        __threadfence_system();
-        asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
-        if (tid < p.push_world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push_cnt[tid]) : "memory");
-    }
 }
 
 // ---- plain kernel ------------------------------------------------------------------------
@@ -1079,8 +1079,7 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         p.probe = ctx->tune.gemv_probe;
         p.push_world = ctx->push.world;
         p.push_rx = ctx->push.rx;
-        p.push_cnt = ctx->push.cnt;
-        ctx->push.arrivals = (int64_t)grid * m;  // counter bumps each peer will see from this rank
+        p.push_seq = ctx->push.seq;
         for (int64_t i = 0; i < m; ++i) {  // one pass over the weights per activation row
             p.x = x + i * ldx;
             p.y = y + i * ldy;
