@@ -123,6 +123,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemv_force_simple")) t.force_simple = (int)value;
     else if (!strcmp(key, "gemv_pdl")) t.pdl = (int)value;
     else if (!strcmp(key, "gemm_variant")) t.gemm_variant = (int)value;
+    else if (!strcmp(key, "attn_variant")) t.attn_variant = (int)value;
     else if (!strcmp(key, "gemm_cache_weights")) t.gemm_cache_weights = (int)value;
     else if (!strcmp(key, "gemv_variant")) t.gemv_variant = (int)value;
     else if (!strcmp(key, "gemv_probe")) t.gemv_probe = (int)value;

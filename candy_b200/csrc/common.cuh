@@ -26,6 +26,7 @@ struct GemvTuning {
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;
+    int attn_variant = 0;  // 1 = one CTA per 32-key chunk (the earlier grouped-query kernel) instead of split-context
     int gemm_cache_weights = 0;  // keep the f16 copy of every weight matrix the GEMM has seen (4x the Q4_0 bytes)
     int gemv_rpt = 2;       // rows per thread and pass in the streaming kernel (1 or 2)
     int gemv_coop = 1;      // slice activations once per CTA through shared memory when rows share a CTA

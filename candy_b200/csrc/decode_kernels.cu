@@ -296,6 +296,189 @@ __global__ void __launch_bounds__(128) attn_partial_gqa_kernel(const float *__re
     }
 }
 
+// Split-context grouped-query decode attention, hd == 128, G = nq/nkv <= 8.  One CTA per
+// (split of the context, kv head, sequence) walks its keys 64 at a time with a running softmax
+// and serves all G query heads of the group from one pass over K and V:
+//   load    64 keys and values into shared memory with 16-byte async copies (K rows padded to
+//           132 floats so that lane = key reads are conflict-free);
+//   scores  warp = quarter of the 128 dims, lane = keys (lane, lane+32): 2 x 8 accumulators,
+//           ten 16-byte shared loads per 64 FMAs; the four dim-quarters are summed through
+//           shared memory;
+//   softmax warp w owns heads 2w, 2w+1: running max and sum in registers, numerators and the
+//           rescaling factor to shared memory;
+//   values  warp = quarter of the 64 keys, lane = four dims: 8 x 4 accumulators kept in
+//           registers across the whole split, three 16-byte shared loads per 32 FMAs.
+// Writes (max, sum, acc[128]) per (head, split) in the layout the combine kernel reads.
+constexpr int kAttn2Keys = 64;
+constexpr int kAttn2KStride = 132;
+constexpr size_t kAttn2Smem = (size_t)kAttn2Keys * kAttn2KStride * 4 + (size_t)kAttn2Keys * 128 * 4  // K, V
+                              + 8 * 128 * 4                                                          // q
+                              + 4 * 8 * kAttn2Keys * 4                                               // score partials [warp][head][key]
+                              + kAttn2Keys * 8 * 4 + 64;                                             // numerators [key][head], factors
+__global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__restrict__ qkv, int nq, int nkv, const int *__restrict__ pos_dev,
+                                                           const float *__restrict__ kc, const float *__restrict__ vc, int max_ctx, float scale,
+                                                           float *__restrict__ part, int nsplits, int keys_per_split) {
+    constexpr int hd = 128;
+    extern __shared__ __align__(16) uint8_t attn_smem[];
+    float *Ks = reinterpret_cast<float *>(attn_smem);
+    float *Vs = Ks + kAttn2Keys * kAttn2KStride;
+    float *q_s = Vs + kAttn2Keys * hd;
+    float *sp_s = q_s + 8 * hd;                  // [4][8][64]
+    float *p_s = sp_s + 4 * 8 * kAttn2Keys;      // [64][8]
+    float *alpha_s = p_s + kAttn2Keys * 8;       // [8]
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int G = nq / nkv;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nkeys = *pos_dev + 1;
+    const int t_begin = split * keys_per_split;
+    const int t_end = min(t_begin + keys_per_split, nkeys);
+    const int stride = hd + 2;
+    if (t_begin >= t_end) {  // split beyond the current length: neutral element
+        for (int g = 0; g < G; ++g) {
+            float *out = part + (((int64_t)b * nq + kvh * G + g) * nsplits + split) * stride;
+            if (tid == 0) out[0] = -3.402823466e38f, out[1] = 0.0f;
+            out[2 + tid] = 0.0f;
+        }
+        return;
+    }
+    const int row = (nq + 2 * nkv) * hd;
+    const int64_t kv_stride = (int64_t)nkv * hd;
+    const float *kbase = kc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
+    const float *vbase = vc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
+    for (int i = tid; i < 8 * hd; i += 128) q_s[i] = (i / hd) < G ? qkv[(int64_t)b * row + (kvh * G + i / hd) * hd + (i % hd)] : 0.0f;
+
+    float m_run[2] = {-3.402823466e38f, -3.402823466e38f}, l_run[2] = {0.0f, 0.0f};  // heads 2*warp, 2*warp+1 (lane-uniform)
+    float acc[8][4];
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[g][i] = 0.0f;
+
+    // 64 rows of K (or V) starting at key t0 into shared memory, as one async-copy group; rows past
+    // the end become zeros, so that no stale NaN reaches a product with a zero weight.  A warp copies
+    // one 512-byte row per instruction.
+    auto load_rows = [&](const float *base, float *dst, int dst_stride, int t0) {
+        const int cnt = min(kAttn2Keys, t_end - t0);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int f = tid + 128 * j, r = f >> 5, c4 = f & 31;
+            float *d = dst + r * dst_stride + 4 * c4;
+            if (r < cnt) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(d)),
+                             "l"(base + (int64_t)(t0 + r) * kv_stride + 4 * c4)
+                             : "memory");
+            } else {
+                *reinterpret_cast<float4 *>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // Software pipeline over two buffers: K of the next chunk streams in during this chunk's softmax
+    // and value pass, V of the next chunk during the next chunk's scores.
+    load_rows(kbase, Ks, kAttn2KStride, t_begin);
+    load_rows(vbase, Vs, hd, t_begin);
+    for (int t0 = t_begin; t0 < t_end; t0 += kAttn2Keys) {
+        const int cnt = min(kAttn2Keys, t_end - t0);
+        const bool more = t0 + kAttn2Keys < t_end;
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // K of this chunk has landed (V may still be in flight)
+        __syncthreads();
+        // ---- scores: this warp's 32 dims, keys lane and lane+32, all eight heads --------------------
+        {
+            float s[2][8];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) s[0][g] = 0.0f, s[1][g] = 0.0f;
+            const float *k0 = Ks + lane * kAttn2KStride + 32 * warp, *k1 = k0 + 32 * kAttn2KStride;
+            const float *qw = q_s + 32 * warp;
+#pragma unroll
+            for (int d4 = 0; d4 < 8; ++d4) {
+                const float4 a = *reinterpret_cast<const float4 *>(k0 + 4 * d4), c = *reinterpret_cast<const float4 *>(k1 + 4 * d4);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 q = *reinterpret_cast<const float4 *>(qw + g * hd + 4 * d4);
+                    s[0][g] = fmaf(q.x, a.x, fmaf(q.y, a.y, fmaf(q.z, a.z, fmaf(q.w, a.w, s[0][g]))));
+                    s[1][g] = fmaf(q.x, c.x, fmaf(q.y, c.y, fmaf(q.z, c.z, fmaf(q.w, c.w, s[1][g]))));
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                sp_s[(warp * 8 + g) * kAttn2Keys + lane] = s[0][g];
+                sp_s[(warp * 8 + g) * kAttn2Keys + lane + 32] = s[1][g];
+            }
+        }
+        __syncthreads();
+        if (more) load_rows(kbase, Ks, kAttn2KStride, t0 + kAttn2Keys);  // K buffer is free
+        else asm volatile("cp.async.commit_group;" ::: "memory");         // keep the group count uniform
+        // ---- running softmax: warp w owns heads 2w and 2w+1 ------------------------------------------
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int g = 2 * warp + hh;
+            float sc[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int t = lane + 32 * half;
+                const float v = (sp_s[(0 * 8 + g) * kAttn2Keys + t] + sp_s[(1 * 8 + g) * kAttn2Keys + t]) +
+                                (sp_s[(2 * 8 + g) * kAttn2Keys + t] + sp_s[(3 * 8 + g) * kAttn2Keys + t]);
+                sc[half] = t < cnt ? v * scale : -3.402823466e38f;
+            }
+            const float m_new = fmaxf(m_run[hh], warp_max(fmaxf(sc[0], sc[1])));
+            const float e0 = lane < cnt ? expf(sc[0] - m_new) : 0.0f;
+            const float e1 = lane + 32 < cnt ? expf(sc[1] - m_new) : 0.0f;
+            const float a = expf(m_run[hh] - m_new);  // 0 on the first chunk
+            l_run[hh] = l_run[hh] * a + warp_sum(e0 + e1);
+            m_run[hh] = m_new;
+            p_s[lane * 8 + g] = e0;
+            p_s[(lane + 32) * 8 + g] = e1;
+            if (lane == 0) alpha_s[g] = a;
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // V of this chunk has landed (the next K may still be in flight)
+        __syncthreads();
+        // ---- values: this warp's 16 keys, dims 4*lane .. 4*lane+3, all eight heads ---------------------
+        {
+            const float4 a0 = *reinterpret_cast<const float4 *>(alpha_s), a1 = *reinterpret_cast<const float4 *>(alpha_s + 4);
+            const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[g][i] *= al[g];
+#pragma unroll 4
+            for (int tt = 0; tt < 16; ++tt) {
+                const int t = 16 * warp + tt;
+                const float4 v = *reinterpret_cast<const float4 *>(Vs + t * hd + 4 * lane);
+                const float4 p0 = *reinterpret_cast<const float4 *>(p_s + t * 8), p1 = *reinterpret_cast<const float4 *>(p_s + t * 8 + 4);
+                const float pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    acc[g][0] = fmaf(pw[g], v.x, acc[g][0]);
+                    acc[g][1] = fmaf(pw[g], v.y, acc[g][1]);
+                    acc[g][2] = fmaf(pw[g], v.z, acc[g][2]);
+                    acc[g][3] = fmaf(pw[g], v.w, acc[g][3]);
+                }
+            }
+        }
+        __syncthreads();
+        if (more) load_rows(vbase, Vs, hd, t0 + kAttn2Keys);  // V buffer is free
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // ---- the four key-quarters' accumulators are summed through shared memory (K region) ---------
+    __syncthreads();
+    float *red = Ks;  // [4][8][128]
+#pragma unroll
+    for (int g = 0; g < 8; ++g) *reinterpret_cast<float4 *>(red + (warp * 8 + g) * hd + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    if (lane == 0) {
+        alpha_s[2 * warp] = m_run[0], alpha_s[2 * warp + 1] = m_run[1];
+        p_s[2 * warp] = l_run[0], p_s[2 * warp + 1] = l_run[1];
+    }
+    __syncthreads();
+    for (int g = 0; g < G; ++g) {
+        float *out = part + (((int64_t)b * nq + kvh * G + g) * nsplits + split) * stride;
+        out[2 + tid] = (red[(0 * 8 + g) * hd + tid] + red[(1 * 8 + g) * hd + tid]) + (red[(2 * 8 + g) * hd + tid] + red[(3 * 8 + g) * hd + tid]);
+        if (tid == 0) out[0] = alpha_s[g], out[1] = p_s[g];
+    }
+}
+
 // Combines the chunk partials of one (head, sequence): out[b][head*hd + d].  Lane = four
 // consecutive dims, the four warps take every fourth chunk; all loads of a batch of eight chunks
 // are unconditional (clamped index, zero weight past the end) so they are in flight together.
@@ -563,11 +746,38 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: null pointer");
     if (batch < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 4 || head_dim > 256 || head_dim % 4 != 0 || max_ctx < 1 || max_ctx > 512 * kAttnChunk)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: bad shape (head_dim <= 256 and a multiple of 4, max_ctx <= 16384)");
-    const int nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+    int nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
     const float scale = 1.0f / sqrtf((float)head_dim);
     const int group = n_q_heads / n_kv_heads;
     cq_status s;
-    if (head_dim == 128 && group >= 2 && group <= kGqaMaxG)
+    if (head_dim == 128 && group >= 2 && group <= 8 && ctx->tune.attn_variant != 1) {
+        // splits of the context sized so that about four CTAs per SM exist, never under 64 keys each
+        const int64_t pairs = (int64_t)n_kv_heads * batch;
+        int64_t want = ((int64_t)ctx->sm_count * 4 + pairs - 1) / pairs;
+        const int max_splits = (max_ctx + kAttn2Keys - 1) / kAttn2Keys;
+        if (want > max_splits) want = max_splits;
+        if (want < 1) want = 1;
+        const int keys_per_split = (int)(((max_ctx + want - 1) / want + kAttn2Keys - 1) / kAttn2Keys) * kAttn2Keys;
+        nchunks = (max_ctx + keys_per_split - 1) / keys_per_split;
+        static thread_local int configured = -1;
+        if (configured != ctx->device) {
+            CQ_CUDA(ctx, cudaFuncSetAttribute(attn_split_gqa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttn2Smem));
+            configured = ctx->device;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)nchunks, (unsigned)n_kv_heads, (unsigned)batch);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = kAttn2Smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+        CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel, qkv_dev, n_q_heads, n_kv_heads, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale,
+                                        scratch_dev, nchunks, keys_per_split));
+        s = CQ_OK;
+    } else if (head_dim == 128 && group >= 2 && group <= kGqaMaxG)
         s = launch_pdl(ctx, attn_partial_gqa_kernel, dim3((unsigned)n_kv_heads, (unsigned)batch, (unsigned)nchunks), dim3(128), qkv_dev, n_q_heads,
                        n_kv_heads, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
     else

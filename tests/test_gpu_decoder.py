@@ -80,3 +80,42 @@ def test_7b_width_two_layers(device):
         device.synchronize()
         want = ref.step(tok, pos)
         assert rel_err(model.read_logits()[0], want) <= REL_TOL
+
+
+# ---- decode attention, operator level: every kernel route against the softmax(q.K^T/sqrt(d)).V of
+# candy's CPU path (reduce.go:2855-2879 restated in oracle.decoder_np.softmax) --------------------------
+@pytest.mark.parametrize("batch,nq,nkv,hd,max_ctx,pos", [
+    (1, 8, 8, 128, 96, 40),       # one query head per kv head: chunk kernel
+    (2, 16, 2, 128, 300, 257),    # groups of eight: split-context kernel, ragged last chunk
+    (3, 8, 4, 128, 64, 0),        # a single key
+    (2, 6, 3, 64, 80, 79),        # head_dim != 128: generic kernel
+    (1, 64, 8, 128, 2048, 2047),  # the 70B-shape group at full context
+])
+def test_decode_attention_routes(device, batch, nq, nkv, hd, max_ctx, pos):
+    import ctypes as C
+    from candy_b200 import abi
+    from oracle.decoder_np import softmax
+    lib, ctx = device._lib, device.ctx
+    rng = np.random.default_rng(batch * 1000 + nq + pos)
+    qkv = rng.standard_normal((batch, (nq + 2 * nkv) * hd), dtype=np.float32)
+    kc = rng.standard_normal((batch, max_ctx, nkv, hd), dtype=np.float32)
+    vc = rng.standard_normal((batch, max_ctx, nkv, hd), dtype=np.float32)
+    want = np.zeros((batch, nq, hd), dtype=np.float32)
+    G = nq // nkv
+    for b in range(batch):
+        for h in range(nq):
+            q = qkv[b, h * hd:(h + 1) * hd]
+            s = (kc[b, :pos + 1, h // G, :] @ q) / np.float32(np.sqrt(hd))
+            want[b, h] = softmax(s.astype(np.float32)) @ vc[b, :pos + 1, h // G, :]
+    d_qkv, d_k, d_v = device.storage_from_slice(qkv), device.storage_from_slice(kc), device.storage_from_slice(vc)
+    d_pos = device.upload_bytes(np.array([pos], dtype=np.int32))
+    scratch = device.alloc(lib.cq_decode_attention_scratch_floats(batch, nq, hd, max_ctx))
+    out = device.alloc(batch * nq * hd)
+    for variant in (0, 1):
+        device.set_option("attn_variant", variant)
+        try:
+            abi.check(ctx, lib.cq_decode_attention(ctx, d_qkv.ptr, batch, nq, nkv, hd, d_pos.ptr, d_k.ptr, d_v.ptr, max_ctx, scratch.ptr, out.ptr), "attention")
+            got = out.data().reshape(batch, nq, hd)
+        finally:
+            device.set_option("attn_variant", 0)
+        assert rel_err(got, want) < 2e-5, f"variant {variant}"
