@@ -58,6 +58,17 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def measured_peak_tflops():
+    """Dense bf16-class tensor peak for a kernel timed alone (burst figure), else the pool's earlier measurement."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"])
+        except Exception:
+            pass
+    return 1590.0
+
+
 class ClockSampler:
     """Samples SM clock, power and clock-event reasons through NVML while a region runs."""
 
@@ -342,6 +353,7 @@ def run_ours(args):
     if not args.skip_extras:
         from candy_b200 import bench_workloads as bw
         if world == 1:
+            line["prefill_gemm"] = bw.prefill_gemm(dev, peak, measured_peak_tflops())
             line["decode_7b"] = bw.decode_7b(dev, peak)
         line["tp_layer_70b"] = bw.tp_layer_70b(dev, dist, rank, world, local_rank, peak)
     if cpu_inputs is not None:

@@ -51,6 +51,75 @@ def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: 
     }
 
 
+def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512, 2048), n: int = 11008, k: int = 4096, seed: int = 1,
+                 calls: int = 16):
+    """BASELINE config 3: Y = X . W^T for M in {16,128,512,2048}, N=11008, K=4096, Q4_0 and Q8_0, CQ_ACT_F16.
+    Each figure is the whole cq_qmatmul call (activation conversion, any weight conversion, GEMM, partial-sum
+    kernel) timed as replays of a CUDA graph of `calls` calls that cycle through eight copies of the weights
+    (more than L2).  `frac_of_roofline` = max(algorithmic bytes / measured copy peak, flops / measured bf16
+    burst peak) / measured time."""
+    from .backend import QStorage
+    lib, ctx = dev._lib, dev.ctx
+    rng = np.random.default_rng(seed)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    out = []
+    for qt, name, bb in ((2, "q4_0", 18), (8, "q8_0", 34)):
+        first = QStorage.quantize(dev, qt, 0, w)
+        ring = [first]
+        for _ in range(7):
+            c = RawCopy(dev, first)
+            ring.append(c)
+        for m in ms_rows:
+            x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
+            y = dev.alloc(m * n)
+            cursor = [0]
+
+            def call():
+                q = ring[cursor[0] % len(ring)]
+                cursor[0] += 1
+                dev._check(lib.cq_qmatmul(ctx, qt, 0, 2, x.ptr, m, k, k, q.ptr if isinstance(q, RawCopy) else q.buf.ptr, n, y.ptr, n), "qmatmul")
+
+            call()
+            dev.synchronize()
+            lib.cq_capture_begin(ctx)
+            for _ in range(calls):
+                call()
+            g = C.c_void_p()
+            dev._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
+            for _ in range(2):
+                dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+            dev.synchronize()
+            ms = C.c_float()
+            reps = 5
+            lib.cq_timer_start(ctx)
+            for _ in range(reps):
+                dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+            lib.cq_timer_stop(ctx, C.byref(ms))
+            dev.synchronize()
+            lib.cq_graph_destroy(ctx, g)
+            t = ms.value * 1e-3 / (reps * calls)
+            flops = 2.0 * m * n * k
+            nbytes = n * (k // 32) * bb + 4 * m * k + 4 * m * n
+            t_hbm, t_tensor = nbytes / (peak_gbs * 1e9), flops / (peak_tflops * 1e12)
+            out.append({"qtype": name, "m": m, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
+                        "algorithmic_gbs": round(nbytes / t / 1e9, 1), "bound": "hbm" if t_hbm >= t_tensor else "tensor",
+                        "roofline_us": round(max(t_hbm, t_tensor) * 1e6, 2), "frac_of_roofline": round(max(t_hbm, t_tensor) / t, 4),
+                        "path": "raw blocks dequantized into tensor memory" if (qt == 2 and m <= 128) else "f16 copy of W, then f16 tcgen05 GEMM"})
+            del x, y
+        del ring, first
+    return {"n": n, "k": k, "peak_gbs": peak_gbs, "peak_tflops": peak_tflops, "l2_defeat": "ring of 8 weight copies", "cases": out}
+
+
+class RawCopy:
+    """A device copy of a QStorage's blocks (ring element)."""
+
+    def __init__(self, dev, q):
+        from .backend import RawBuffer
+        self.buf = RawBuffer(dev, q.buf.nbytes)
+        dev._check(dev._lib.cq_memcpy_d2d(dev.ctx, self.buf.ptr, q.buf.ptr, q.buf.nbytes), "copy")
+        self.ptr = self.buf.ptr
+
+
 class _CudaArray:
     """Minimal __cuda_array_interface__ view of a device buffer, so torch can wrap it without a copy."""
 

@@ -1,4 +1,4 @@
-// Quantized GEMM for narrow batches (8 < m <= 64, Q4_0): Y[m,n] = X[m,k] . W[n,k]^T with the
+// Quantized GEMM for narrow batches (8 < m <= 128, Q4_0): Y[m,n] = X[m,k] . W[n,k]^T with the
 // weights read from HBM once, as the 18-byte blocks they are stored in.
 //
 // Same CQ_ACT_F16 numerics as the wide GEMM (f16 activations, weights d*(q-8) rounded once to
@@ -68,17 +68,18 @@ struct FtCfg {
     static constexpr int kPipes = 2;
     static constexpr int kGroupRows = kPipes * FT_ROWS;
     static constexpr int kXBytes = 4 * MPAD * 128;  // one slab of X: four 64-wide boxes of MPAD rows
+    static constexpr int kIssuers = MPAD >= 128 ? 1 : 2;  // MMA-issuing lanes per pipe, an accumulator each
     static constexpr int kXStages = MPAD >= 64 ? 2 : 3;
-    static constexpr int kWStages = 4;  // per pipe
+    static constexpr int kWStages = MPAD >= 128 ? 2 : 4;  // per pipe
     static constexpr size_t kSmem = (size_t)kPipes * kWStages * FT_WBYTES + (size_t)kXStages * kXBytes + 1024 + 512;
     // tensor memory: 128 columns of A per pipe, then two accumulators of MPAD columns per pipe
     static constexpr int kDCol0 = kPipes * FT_ACOLS;
     static constexpr int kWarpW0 = 2;                        // warps 0,1 load X; then one TMA warp per pipe
     static constexpr int kWarpMma0 = kWarpW0 + kPipes;       // two issuing warps per pipe
-    static constexpr int kWarpDq0 = kWarpMma0 + 2 * kPipes;  // eight dequantizing warps per pipe: four per half of an item
+    static constexpr int kWarpDq0 = kWarpMma0 + kIssuers * kPipes;  // eight dequantizing warps per pipe: four per half of an item
     static constexpr int kWarpEp0 = kWarpDq0 + 8 * kPipes;   // four epilogue warps
     static constexpr int kThreads = 32 * (kWarpEp0 + 4);
-    static_assert(kDCol0 + 2 * kPipes * MPAD <= 512, "tensor memory");
+    static_assert(kDCol0 + kIssuers * kPipes * MPAD <= 512, "tensor memory");
 };
 
 // Position p of a block's 32 values, in the order the dequantizing threads emit them, holds
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
     qgemm_q4_0_tmem_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const FtParams p) {
     using Cfg = FtCfg<MPAD>;
     constexpr int WSP = Cfg::kWStages, XST = Cfg::kXStages, PIPES = Cfg::kPipes, DCOL0 = Cfg::kDCol0, GROUP_ROWS = Cfg::kGroupRows;
-    constexpr int NISS = 2 * PIPES;
+    constexpr int IPP = Cfg::kIssuers, NISS = IPP * PIPES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_w = smem;                                          // per pipe WSP stages of raw blocks
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
     uint64_t *w_full = bars, *w_empty = w_full + PIPES * WSP, *x_full = w_empty + PIPES * WSP, *x_empty = x_full + XST;
     uint64_t *a_full = x_empty + XST, *a_empty = a_full + 2 * PIPES, *d_full = a_empty + 2 * PIPES, *d_empty = d_full + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + 1);
+    uint32_t *sink = tmem_slot + 1;  // one word per warp: target of the stores that pin load completion (see the dequantizing warps)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // this CTA's steps [g0, g1) of the (group, chunk) list: equal shares, so the SMs finish together
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
         }
         for (int b = 0; b < 2 * PIPES; ++b) {  // per pipe: one per half of an item
             mbar_init(smem_u32(&a_full[b]), 4);
-            mbar_init(smem_u32(&a_empty[b]), 2);  // the pipe's two issuers
+            mbar_init(smem_u32(&a_empty[b]), IPP);  // the pipe's issuers
         }
         mbar_init(smem_u32(&d_full[0]), NISS);
         mbar_init(smem_u32(&d_empty[0]), 4);
@@ -287,7 +289,7 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
         // ---- MMA: issuer (pipe q, parity e) takes every second K=16 step of both halves ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16(FT_ROWS, MPAD);
-            const int iss = warp - Cfg::kWarpMma0, q = iss >> 1, e = iss & 1;
+            const int iss = warp - Cfg::kWarpMma0, q = iss / IPP, e = iss % IPP;
             int step = 0, seg = 0;
             bool ok = true;
             const uint32_t acc = tmem_base + (uint32_t)(DCOL0 + iss * MPAD);
@@ -321,8 +323,8 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
                         const uint32_t a_t = tmem_base + (uint32_t)(q * FT_ACOLS + h * 64);
                         if (!(p.probe & 2)) {
 #pragma unroll
-                            for (int j2 = 0; j2 < 4; ++j2) {
-                                const int j = 2 * j2 + e;  // K=16 step inside the half
+                            for (int j2 = 0; j2 < 8 / IPP; ++j2) {
+                                const int j = IPP * j2 + e;  // K=16 step inside the half
                                 const int jj = 8 * h + j;  // ... inside the item: X box jj/4, 32-byte column jj%4
                                 tc_mma_f16_ts(acc, a_t + 8 * j, bdesc + (uint64_t)((jj >> 2) * (MPAD * 128 / 16) + (jj & 3) * 2), idesc, (c | h | j2) != 0);
                             }
@@ -348,15 +350,25 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
                 break;
             }
             if (tracer) FT_TRACE(step, 8 + 3 * h);
-            uint32_t w[18];  // four blocks = 72 bytes, 8-byte aligned
-            const uint2 *src = reinterpret_cast<const uint2 *>(smem_w + (size_t)s * FT_WBYTES + r * FT_ROWCHUNK_Q4 + h * 72);
+            // Four blocks = 72 bytes, 8-byte aligned.
+            uint32_t w[18];
+            const uint32_t src = smem_u32(smem_w + (size_t)s * FT_WBYTES + r * FT_ROWCHUNK_Q4 + h * 72);
 #pragma unroll
-            for (int i = 0; i < 9; ++i) {
-                const uint2 t = src[i];
-                w[2 * i] = t.x, w[2 * i + 1] = t.y;
+            for (int i = 0; i < 9; ++i)
+                asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(src + 8 * i) : "memory");
+            // The stage may be refilled once the raw blocks are in registers -- really in registers.
+            // Neither the compiler nor the arrive waits for shared-memory loads that are still in
+            // flight (observed: rows read from a stage the next TMA copy was already overwriting), so
+            // an instruction that needs every loaded word, and that cannot be dropped, goes first:
+            // instructions issue in order, and this store cannot issue before its operand exists.
+            {
+                uint32_t all = w[0];
+#pragma unroll
+                for (int i = 1; i < 18; ++i) all ^= w[i];
+                asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem_u32(&sink[warp])), "r"(all) : "memory");
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&w_empty[s]));  // the raw blocks are in registers: the stage may be refilled
+            if (lane == 0) mbar_arrive(smem_u32(&w_empty[s]));
             if (step >= 1 && !mbar_wait_sleep(smem_u32(&a_empty[2 * q + h]), (step - 1) & 1, 20)) {
                 if (lane == 0) atomicExch(p.err, kDevErrMma);
                 break;
@@ -418,9 +430,14 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
 #pragma unroll 1
                 for (int c = 0; c < MPAD / 16; ++c) {
                     uint32_t v0[16], v1[16];
-                    const uint32_t col = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(DCOL0 + 2 * t * MPAD + c * 16);
+                    const uint32_t col = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(DCOL0 + IPP * t * MPAD + c * 16);
                     tmem_ld16(col, v0);
-                    tmem_ld16(col + MPAD, v1);
+                    if (IPP == 2) {
+                        tmem_ld16(col + MPAD, v1);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v1[i] = 0u;
+                    }
                     if (t == PIPES - 1 && c == MPAD / 16 - 1) {  // everything is in registers: the issuers may overwrite the accumulators
                         tc_fence_before();
                         __syncwarp();
@@ -476,7 +493,7 @@ cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, co
 }  // namespace
 
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w) {
-    return qtype == CQ_Q4_0 && m >= 1 && m <= 64 && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    return qtype == CQ_Q4_0 && m >= 1 && m <= 128 && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
 }
 
 cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y,
@@ -484,7 +501,7 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int6
     if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
     if (n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
-    const int mpad = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    const int mpad = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
     const int group_rows = FtCfg<32>::kGroupRows;
     const int ngroups = (int)((n + group_rows - 1) / group_rows);
     const int nchunks = (int)(k / FT_KCHUNK);
@@ -517,10 +534,11 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int6
     p.probe = ctx->tune.gemv_probe;
     if (mpad == 16) s = run_ft<16>(ctx, tmW, tmX, p, ctas);
     else if (mpad == 32) s = run_ft<32>(ctx, tmW, tmX, p, ctas);
-    else s = run_ft<64>(ctx, tmW, tmX, p, ctas);
+    else if (mpad == 64) s = run_ft<64>(ctx, tmW, tmX, p, ctas);
+    else s = run_ft<128>(ctx, tmW, tmX, p, ctas);
     if (s != CQ_OK) return s;
     if (shared_tiles) {
-        static_assert(FtCfg<16>::kGroupRows == 256 && FtCfg<32>::kGroupRows == 256 && FtCfg<64>::kGroupRows == 256, "sum kernel layout");
+        static_assert(FtCfg<16>::kGroupRows == 256 && FtCfg<64>::kGroupRows == 256 && FtCfg<128>::kGroupRows == 256, "sum kernel layout");
         shared_group_sum_kernel<<<dim3((unsigned)ngroups, (unsigned)m), 64, 0, ctx->stream>>>(part, m, n, nchunks, (int)per_cta, y, ldy);
         CQ_CUDA(ctx, cudaGetLastError());
     }

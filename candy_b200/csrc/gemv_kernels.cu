@@ -724,10 +724,14 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
             } else if (go && rsub < rows_left) {
                 v[0] = dec.pass(reinterpret_cast<const uint32_t *>(sw));
             }
+            // The partial sums are parked BEFORE the stage is released: these stores need every word
+            // the pass loaded, and instructions issue in order, so the release below cannot be issued
+            // while a shared-memory load of this stage is still in flight (the arrive by itself does
+            // not wait for such loads, and the producer would start overwriting the stage).
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_u32(&stash[(u * RPT + j) * cthreads + tid])), "f"(v[j]) : "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * stage);
-#pragma unroll
-            for (int j = 0; j < RPT; ++j) stash[(u * RPT + j) * cthreads + tid] = v[j];
             rows_left -= rows_per_pass;
             if (++stage == p.stages) {
                 stage = 0;
