@@ -200,12 +200,13 @@ cq_status cq_add_int(cq_ctx *ctx, int *value_dev, int delta);
 /* ---- tensor-parallel exchange fused into the kernels around it ---------------------------
  * One process per GPU.  A row-parallel linear (o / down projection split along k) needs the sum
  * of every rank's partial output.  Instead of a collective call, cq_qmatmul_push makes the decode
- * GEMV store its results directly into every rank's receive buffer (peer stores over NVLink) and
- * bump a counter per peer; cq_add_rmsnorm_reduce, the residual-add + RMSNorm that follows the
- * linear anyway, waits (bounded; CQ_ERR_TIMEOUT at the next cq_synchronize on give-up) for all
- * ranks' counters, sums the partials from local memory in rank order (bit-identical on every
- * rank), and re-arms the counters.  Use set 0 and set 1 alternately (o: 0, down: 1).  Every rank
- * must issue the same sequence of calls.  The reference has no multi-device code; no counterpart.
+ * GEMV store each result directly into every rank's receive buffer (peer stores over NVLink) as
+ * an 8-byte (value, tag) pair; cq_add_rmsnorm_reduce, the residual-add + RMSNorm that follows the
+ * linear anyway, polls (bounded; CQ_ERR_TIMEOUT at the next cq_synchronize on give-up) its own
+ * memory until every pair carries this exchange's tag, sums the partials in rank order
+ * (bit-identical on every rank), adds the sum to x, and advances the tag (kept on the device, so a
+ * captured graph replays).  Use set 0 and set 1 alternately (o: 0, down: 1).  Every rank must
+ * issue the same sequence of calls.  The reference has no multi-device code; no counterpart.
  *   create:  allocates this rank's buffers; handle64 receives a 64-byte CUDA IPC handle;
  *   connect: takes all ranks' handles (world x 64 bytes, rank order) gathered by the host. */
 typedef struct cq_comm cq_comm;
