@@ -32,6 +32,7 @@ class CandyqError(RuntimeError):
 
 _lib = None
 
+CQ_OK, CQ_ERR_INVALID_ARG, CQ_ERR_CUDA, CQ_ERR_UNSUPPORTED, CQ_ERR_TIMEOUT, CQ_ERR_NOMEM, CQ_ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
 _vp, _i64, _int, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
 
 # name -> argtypes (every entry returns cq_status unless listed in _OTHER_RESTYPE)
@@ -63,6 +64,7 @@ SIGNATURES = {
     "cq_rope_store_kv": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int],
     "cq_decode_attention": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _int, _vp, _vp],
     "cq_silu_mul": [_vp, _vp, _i64, _i64, _vp, _i64],
+    "cq_silu_mul_pairs": [_vp, _vp, _i64, _i64, _vp, _i64],
     "cq_argmax": [_vp, _vp, _i64, _i64, _vp],
     "cq_embedding": [_vp, _vp, _i64, _i64, _vp, _i64, _vp],
     "cq_add_int": [_vp, _vp, _int],
@@ -70,6 +72,7 @@ SIGNATURES = {
     "cq_comm_connect": [_vp, _vp, _vp],
     "cq_comm_destroy": [_vp, _vp],
     "cq_qmatmul_push": [_vp, _vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64],
+    "cq_qlinear_fused": [_vp, _int, _int, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp, _i64, _int, _vp, _i64],
     "cq_add_rmsnorm_reduce": [_vp, _vp, _int, _vp, _vp, _i64, _i64, C.c_float, _vp],
     "cq_capture_begin": [_vp],
     "cq_capture_end": [_vp, C.POINTER(_vp)],

@@ -282,6 +282,29 @@ cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float
     return launch_gemm(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
 }
 
+cq_status cq_qlinear_fused(cq_ctx *ctx, int qtype, int order, const float *x_dev, const float *delta_dev, const float *alpha_dev, float eps,
+                           float *x_out_dev, int64_t m, int64_t k, const void *w_blocks_dev, int64_t n, int epilogue, float *y_dev,
+                           int64_t ldy) {
+    CQ_ENTER(ctx);
+    const int64_t n_out = epilogue == 1 ? n / 2 : n;
+    const int64_t ldy_chk = ldy >= n_out ? (ldy < n ? n : ldy) : -1;  // the shared check wants ldy >= n; here n_out columns are written
+    cq_status s = check_matmul_args(ctx, qtype, order, CQ_ACT_F32, x_dev, m, k, k, w_blocks_dev, n, y_dev, ldy_chk);
+    if (s != CQ_OK) return s;
+    if (m > 8) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qlinear_fused: m must be 1..8 (the decode path)");
+    if (epilogue != 0 && epilogue != 1) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qlinear_fused: epilogue must be 0 or 1");
+    if (epilogue == 1 && (n & 1)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qlinear_fused: the pairing epilogue needs an even n");
+    if (x_out_dev && x_out_dev == x_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qlinear_fused: x_out must not alias x (other CTAs still read x)");
+    for (const void *q : {(const void *)x_dev, (const void *)delta_dev, (const void *)alpha_dev, (const void *)x_out_dev})
+        if (reinterpret_cast<uintptr_t>(q) & 15) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qlinear_fused: x, delta, alpha, x_out must be 16-byte aligned");
+    FuseSpec f;
+    f.on = true, f.delta = delta_dev, f.alpha = alpha_dev, f.x_out = x_out_dev, f.eps = eps, f.norm = alpha_dev != nullptr, f.epilogue = epilogue;
+    f.ld_delta = k, f.ld_xout = k;
+    ctx->fuse = f;
+    s = launch_gemv(ctx, qtype, order, CQ_ACT_F32, x_dev, m, k, k, w_blocks_dev, n, y_dev, ldy);
+    ctx->fuse = FuseSpec();
+    return s;
+}
+
 cq_status cq_qmatmul_host(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_host, int64_t m, int64_t k,
                           const void *w_blocks_dev, int64_t n, float *y_host) {
     CQ_ENTER(ctx);

@@ -21,7 +21,7 @@ enum : int { kDevErrNone = 0, kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErr
 
 struct GemvTuning {
     int target_warps = 8;   // consumer warps per CTA the launcher aims for
-    int stages = 8;         // smem ring depth (clamped by capacity)
+    int stages = 4;         // smem ring depth (clamped by capacity)
     int ctas_per_sm = 0;    // 0 = automatic
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
@@ -40,6 +40,19 @@ struct PushSpec {
     const unsigned *seq = nullptr; // local word: tag of the last completed exchange on this set
     int world = 0;
     int64_t row_stride = 0;
+};
+
+// Operator fusion around one decode GEMV launch (cq_qlinear_fused): residual add + RMSNorm in the
+// prologue, SiLU(gate)*up over adjacent output rows in the epilogue.
+struct FuseSpec {
+    bool on = false;
+    const float *delta = nullptr;  // added to x before the norm (nullable)
+    const float *alpha = nullptr;  // norm weights (nullable: no norm, only the add)
+    float *x_out = nullptr;        // receives x + delta (nullable); must not alias x
+    float eps = 0.0f;
+    bool norm = false;
+    int epilogue = 0;              // 0: y[r] = row r; 1: y[r/2] = silu(row r) * row r+1 for even r
+    int64_t ld_delta = 0, ld_xout = 0;
 };
 
 struct cq_ctx {
@@ -61,6 +74,7 @@ struct cq_ctx {
     size_t w16_cache_bytes = 0;
     GemvTuning tune;
     PushSpec push;
+    FuseSpec fuse;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
     bool capturing = false;
     std::string last_error;

@@ -569,6 +569,19 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__
     }
 }
 
+// The same on (gate, up) pairs: out[b][i] = silu(gu[b][2i]) * gu[b][2i + 1].
+__global__ void __launch_bounds__(256) silu_mul_pairs_kernel(const float *__restrict__ gu, int n, int64_t total, float *__restrict__ out,
+                                                           int64_t ld_out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / n, c = i - b * n;
+        const float2 v = *reinterpret_cast<const float2 *>(gu + b * 2 * n + 2 * c);
+        const double g = (double)v.x;
+        out[b * ld_out + c] = (float)(g / (1.0 + exp(-g))) * v.y;
+    }
+}
+
 // One CTA per row; the lowest index among equal maxima wins, as the sequential strict '>' does.
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ x, int cols, uint32_t *__restrict__ out) {
     __shared__ float sv[32];
@@ -795,6 +808,15 @@ cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64
     const int64_t total = rows * n;
     const unsigned grid = (unsigned)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
     return launch_pdl(ctx, silu_mul_kernel, dim3(grid), dim3(256), gate_up_dev, (int)n, total, out_dev, ld_out);
+}
+
+cq_status cq_silu_mul_pairs(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev, int64_t ld_out) {
+    CQ_ENTER(ctx);
+    if (!gate_up_dev || !out_dev || rows < 1 || n < 1 || n > 0x7FFFFFFF || ld_out < n || (reinterpret_cast<uintptr_t>(gate_up_dev) & 7))
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_silu_mul_pairs: bad arguments");
+    const int64_t total = rows * n;
+    const unsigned grid = (unsigned)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
+    return launch_pdl(ctx, silu_mul_pairs_kernel, dim3(grid), dim3(256), gate_up_dev, (int)n, total, out_dev, ld_out);
 }
 
 cq_status cq_argmax(cq_ctx *ctx, const float *x_dev, int64_t rows, int64_t cols, uint32_t *out_dev) {

@@ -75,6 +75,15 @@ struct GemvParams {
     const unsigned *push_seq;   // tag of the last completed exchange; this launch tags its values with +1
     int push_world;             // 0 = ordinary launch
     int64_t push_off;           // element offset of this activation row inside the slot
+    // Fused prologue / epilogue (0 / null = off): x' = x + delta (written to x_out by CTA 0), then
+    // x'' = rmsnorm(x') * alpha, kept in shared memory at xs_off; epilogue 1 pairs adjacent rows.
+    const float *delta;
+    const float *alpha;
+    float *x_out;
+    float eps;
+    int norm;
+    int xs_off;
+    int epilogue;
     int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers, 3 = empty kernel
     int *err;
 };
@@ -232,8 +241,9 @@ struct DecQ16 {
     // lanes make one block.  All 32 lanes of the warp must call this together.
     __device__ __forceinline__ static void load_quarter(const float *x, int item, bool valid, float (&r)[8]) {
         if (valid) {
-            const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item);
-            const float4 b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item + 1);
+            // plain loads: the source is global memory or, with a fused norm, this CTA's shared memory
+            const float4 a = reinterpret_cast<const float4 *>(x)[2 * item];
+            const float4 b = reinterpret_cast<const float4 *>(x)[2 * item + 1];
             r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
         } else {
 #pragma unroll
@@ -403,8 +413,9 @@ struct DecSlices {
         const int blk = item >> 2, qd = item & 3;
         float r[8];
         if (valid) {
-            const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item);
-            const float4 b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * item + 1);
+            // plain loads: the source is global memory or, with a fused norm, this CTA's shared memory
+            const float4 a = reinterpret_cast<const float4 *>(x)[2 * item];
+            const float4 b = reinterpret_cast<const float4 *>(x)[2 * item + 1];
             r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
         } else {
 #pragma unroll
@@ -572,8 +583,10 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     const bool is_producer = warp == p.cwarps;
 
     // Rows of this CTA: an even split of [0, n).
-    const int64_t row_begin = (p.n * (int64_t)blockIdx.x) / gridDim.x;
-    const int64_t row_end = (p.n * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+    // (with the pairing epilogue the split falls on even rows)
+    const int64_t unit = p.epilogue == 1 ? 2 : 1;
+    const int64_t row_begin = unit * (((p.n / unit) * (int64_t)blockIdx.x) / gridDim.x);
+    const int64_t row_end = unit * (((p.n / unit) * (int64_t)(blockIdx.x + 1)) / gridDim.x);
     const int nrows = (int)(row_end - row_begin);
     const int rows_per_pass = p.rpp * RPT;
     const int npass = (nrows + rows_per_pass - 1) / rows_per_pass;
@@ -646,6 +659,46 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     TRACE(2);
     if (p.probe == 3) return;  // profiling aid: the cost of an empty kernel in the chain
 
+    // Fused prologue: x' = x + delta (CTA 0 also stores it to x_out: the caller ping-pongs two residual
+    // buffers, every other CTA keeps reading the old one), x'' = x' / sqrt(mean(x'^2) + eps) * alpha.
+    // Every CTA computes the same numbers in the same order; the result lives in shared memory and
+    // the activation set-up below reads it from there.
+    const float *xsrc = p.x;
+    if (p.xs_off >= 0) {
+        float *xs = reinterpret_cast<float *>(smem + p.xs_off);
+        const int k4 = p.nb * 8;  // float4 groups in a row
+        float ss = 0.0f;
+        for (int i = tid; i < k4; i += cthreads) {
+            float4 v = __ldg(reinterpret_cast<const float4 *>(p.x) + i);
+            if (p.delta) {
+                const float4 d = __ldg(reinterpret_cast<const float4 *>(p.delta) + i);
+                v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+            }
+            if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[i] = v;
+            reinterpret_cast<float4 *>(xs)[i] = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        if (p.norm) {
+            // consumer-only block sum (the producer warp is not part of barrier 1)
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, 32);
+            if (lane == 0) red[0][0][warp] = ss;
+            asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+            float tot = 0.0f;
+            for (int w = 0; w < p.cwarps; ++w) tot += red[0][0][w];
+            asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");  // red is reused by the reduction below
+            const float scale = 1.0f / sqrtf(tot / (float)(p.nb * kQK) + p.eps);
+            for (int i = tid; i < k4; i += cthreads) {  // each thread rescales what it wrote itself
+                float4 v = reinterpret_cast<float4 *>(xs)[i];
+                const float4 a = __ldg(reinterpret_cast<const float4 *>(p.alpha) + i);
+                v.x = scale * v.x * a.x, v.y = scale * v.y * a.y, v.z = scale * v.z * a.z, v.w = scale * v.w * a.w;
+                reinterpret_cast<float4 *>(xs)[i] = v;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+        xsrc = xs;
+    }
+
     Dec dec;
     if (Dec::kCoop && p.coop_off >= 0) {
         uint32_t *area = reinterpret_cast<uint32_t *>(smem + p.coop_off);
@@ -655,15 +708,15 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
             for (int base = 0; base < nitems; base += 2 * cthreads) {  // uniform trip count: the shuffles need whole warps
                 const int i0 = base + tid, i1 = base + cthreads + tid;
                 float r0[8], r1[8];
-                Dec::load_quarter(p.x, i0, i0 < nitems, r0);
-                Dec::load_quarter(p.x, i1, i1 < nitems, r1);
+                Dec::load_quarter(xsrc, i0, i0 < nitems, r0);
+                Dec::load_quarter(xsrc, i1, i1 < nitems, r1);
                 Dec::stage_quarter_regs(r0, i0, i0 < nitems, area);
                 Dec::stage_quarter_regs(r1, i1, i1 < nitems, area);
             }
         } else {
             for (int base = 0; base < nitems; base += cthreads) {
                 const int item = base + tid;
-                Dec::stage_quarter(p.x, item, item < nitems, area);
+                Dec::stage_quarter(xsrc, item, item < nitems, area);
             }
         }
         TRACE(3);
@@ -673,10 +726,10 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     } else {
         float tmp[kXPerThread];
         if (active) {
-            const float4 *xv = reinterpret_cast<const float4 *>(p.x + (int64_t)pair * kXPerThread);
+            const float4 *xv = reinterpret_cast<const float4 *>(xsrc + (int64_t)pair * kXPerThread);
 #pragma unroll
             for (int i = 0; i < kXPerThread / 4; ++i) {
-                float4 t = __ldg(xv + i);
+                float4 t = xv[i];
                 tmp[4 * i] = t.x, tmp[4 * i + 1] = t.y, tmp[4 * i + 2] = t.z, tmp[4 * i + 3] = t.w;
             }
         } else {
@@ -805,7 +858,16 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
             if (pbase + u < npass && r < nrows) {
                 float tot = 0.0f;
                 for (int w = 0; w < p.wpr; ++w) tot += red[buf][i][rs * p.wpr + w];
-                if (p.push_world > 0) {
+                if (p.epilogue == 1) {
+                    // rows come in (gate, up) pairs: the even row's thread writes silu(gate) * up.  The
+                    // reference evaluates the sigmoid in double and rounds (unary.go:3353-3365); here it is
+                    // expf in f32 (within 2 ulp of that) because this sits on every consumer's critical path.
+                    if ((rs & 1) == 0) {
+                        float up = 0.0f;
+                        for (int w = 0; w < p.wpr; ++w) up += red[buf][i][(rs + 1) * p.wpr + w];
+                        p.y[(row_begin + r) >> 1] = tot / (1.0f + expf(-tot)) * up;
+                    }
+                } else if (p.push_world > 0) {
                     // value and tag travel in one 8-byte store: the receiver polls the data itself, so
                     // nothing but one NVLink hop lies between this store and its use (no fence, no flag)
                     const uint2 v = make_uint2(__float_as_uint(tot), push_tag);
@@ -970,7 +1032,12 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     // area holds 10 words per block and slice (sized for three slices).
     size_t coop_bytes = (size_t)nb * 3 * 10 * sizeof(uint32_t);
     if (rpp <= 1 || coop_bytes > 49152 || ctx->tune.gemv_coop == 0) coop_bytes = 0;
-    const size_t budget = per_cta > kStaticSmemReserve + stash_bytes + coop_bytes ? per_cta - kStaticSmemReserve - stash_bytes - coop_bytes : 0;
+    // the activations a fused prologue produces (nothing when only the epilogue is fused)
+    const bool prologue = ctx->fuse.on && (ctx->fuse.delta || ctx->fuse.alpha || ctx->fuse.x_out);
+    const size_t xs_bytes = prologue ? (size_t)k * sizeof(float) : 0;
+    const size_t budget = per_cta > kStaticSmemReserve + stash_bytes + coop_bytes + xs_bytes ? per_cta - kStaticSmemReserve - stash_bytes - coop_bytes - xs_bytes : 0;
+    // A prologue that would crowd the ring out of a half-SM launch is refused (the caller then runs
+    // the norm as its own kernel): one CTA per SM costs a large GEMV more than the fusion saves.
     int stages = ctx->tune.stages < 2 ? 2 : (ctx->tune.stages > kMaxStages ? kMaxStages : ctx->tune.stages);
     if ((size_t)stage_bytes * 2 > budget) return false;
     while ((size_t)stage_bytes * stages > budget) --stages;
@@ -984,10 +1051,15 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     p.cwarps = cwarps;
     p.stages = stages;
     p.stage_bytes = (int)stage_bytes;
-    smem = (size_t)stage_bytes * stages + stash_bytes + coop_bytes;
+    smem = (size_t)stage_bytes * stages + stash_bytes + coop_bytes + xs_bytes;
     p.coop_off = coop_bytes ? (int)((size_t)stage_bytes * stages + stash_bytes) : -1;
+    p.xs_off = xs_bytes ? (int)((size_t)stage_bytes * stages + stash_bytes + coop_bytes) : -1;
+    if (ctx->fuse.on && ctx->fuse.epilogue == 1 && ((rpp & 1) != 0 || (n & 1) != 0)) return false;  // pairs must share a pass
     const int64_t max_ctas = (n + rpp * rpt - 1) / (rpp * rpt);
     // 0 = automatic: geometries that fit two CTAs per SM use both slots (more warps in flight).
+    // (One CTA per SM is faster when the SAME small shape runs back to back -- the next launch
+    // becomes resident at once and prefetches during this one -- but slower in a real decode
+    // step, where small kernels sit between the GEMVs: 59 vs 56 us per 7B-shape layer.)
     const int per_sm = ctx->tune.ctas_per_sm > 0 ? ctx->tune.ctas_per_sm : (two_per_sm ? 2 : 1);
     int64_t g = (int64_t)ctx->sm_count * per_sm;
     if (g > max_ctas) g = max_ctas;
@@ -1084,9 +1156,16 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         p.push_world = ctx->push.world;
         p.push_rx = ctx->push.rx;
         p.push_seq = ctx->push.seq;
+        const FuseSpec &f = ctx->fuse;
+        p.norm = f.on && f.norm ? 1 : 0;
+        p.eps = f.eps;
+        p.epilogue = f.on ? f.epilogue : 0;
         for (int64_t i = 0; i < m; ++i) {  // one pass over the weights per activation row
             p.x = x + i * ldx;
             p.y = y + i * ldy;
+            p.delta = f.on && f.delta ? f.delta + i * f.ld_delta : nullptr;
+            p.alpha = f.on ? f.alpha : nullptr;
+            p.x_out = f.on && f.x_out ? f.x_out + i * f.ld_xout : nullptr;
             p.push_off = i * ctx->push.row_stride;
             cq_status s;
             switch (ctx->tune.gemv_variant) {
@@ -1100,6 +1179,7 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         return CQ_OK;
     }
     if (ctx->push.world > 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "pushing GEMV needs a shape the streaming kernel takes (k % 256 == 0, aligned pointers)");
+    if (ctx->fuse.on) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "fused linear needs a shape the streaming kernel takes (k % 256 == 0, aligned pointers, an even row-group count for the pairing epilogue)");
     return run_simple<QT, ORDER>(ctx, w, x, y, m, n, nb, ldx, ldy);
 }
 

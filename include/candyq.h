@@ -188,6 +188,8 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
  * lets the result sit in rows padded for the next linear. */
 cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev,
                       int64_t ld_out);
+/* The same with gate and up interleaved: out[r, i] = silu(gate_up[r, 2i]) * gate_up[r, 2i+1]. */
+cq_status cq_silu_mul_pairs(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev, int64_t ld_out);
 /* BackendStorage.FastArgmax (backend.go:128-129; FastArgmaxF32, reduce.go:846-862): the lowest
  * index among equal maxima. */
 cq_status cq_argmax(cq_ctx *ctx, const float *x_dev, int64_t rows, int64_t cols, uint32_t *out_dev);
@@ -196,6 +198,20 @@ cq_status cq_embedding(cq_ctx *ctx, const float *table_dev, int64_t vocab, int64
                        const uint32_t *ids_dev, int64_t rows, float *out_dev);
 /* *value_dev += delta on the stream (advances a decode position inside a captured graph). */
 cq_status cq_add_int(cq_ctx *ctx, int *value_dev, int delta);
+
+/* One decode linear with its neighbours fused in (m <= 8, f32 activations, shapes the streaming GEMV
+ * takes: k % 256 == 0; CQ_ERR_UNSUPPORTED otherwise, and the caller issues the separate operators):
+ *   prologue  x' = x + delta (delta nullable); x_out (nullable, must not alias x) receives x';
+ *             x'' = x' / sqrt(mean(x'^2) + eps) * alpha when alpha is given (RMSNorm, reduce.go:3071-3092);
+ *   linear    t[m,n] = x''[m,k] . W[n,k]^T;
+ *   epilogue  0: y[r, c] = t[r, c], n columns; 1: rows of W come in (gate, up) pairs and
+ *             y[r, c] = silu(t[r, 2c]) * t[r, 2c+1], n/2 columns (SiLU as unary.go:3353-3365, but expf in
+ *             f32: within 2 ulp of the reference's double evaluation).
+ * x, delta, x_out have row pitch k; y has row pitch ldy.  No reference counterpart: candy runs
+ * these operators one by one. */
+cq_status cq_qlinear_fused(cq_ctx *ctx, int qtype, int order, const float *x_dev, const float *delta_dev,
+                           const float *alpha_dev, float eps, float *x_out_dev, int64_t m, int64_t k,
+                           const void *w_blocks_dev, int64_t n, int epilogue, float *y_dev, int64_t ldy);
 
 /* ---- tensor-parallel exchange fused into the kernels around it ---------------------------
  * One process per GPU.  A row-parallel linear (o / down projection split along k) needs the sum

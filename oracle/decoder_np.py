@@ -45,12 +45,13 @@ def silu(x):
 class OracleDecoder:
     """Single sequence.  `layers` is a list of dicts with the Q-blocks (uint8) of wqkv, wo, wgu, wdown."""
 
-    def __init__(self, cfg, qtype, order, layers, embed=None, wout=None, cos=None, sin=None, nq=None, nkv=None, ffn=None):
+    def __init__(self, cfg, qtype, order, layers, embed=None, wout=None, cos=None, sin=None, nq=None, nkv=None, ffn=None, gu_interleaved=True):
         self.cfg, self.qt, self.order, self.layers = cfg, qtype, order, layers
         self.embed, self.wout, self.cos, self.sin = embed, wout, cos, sin
         self.nq = nq or cfg.n_heads
         self.nkv = nkv or cfg.n_kv_heads
         self.ffn = ffn or cfg.ffn
+        self.gu_interleaved = gu_interleaved  # rows of wgu: (gate_0, up_0, gate_1, up_1, ...) instead of all gates, then all ups
         self.k = [np.zeros((cfg.max_ctx, self.nkv, cfg.head_dim), dtype=f32) for _ in layers]
         self.v = [np.zeros((cfg.max_ctx, self.nkv, cfg.head_dim), dtype=f32) for _ in layers]
 
@@ -79,7 +80,7 @@ class OracleDecoder:
             x = x + self.lin(att.reshape(-1), L["wo"], dim)
             xn = rmsnorm(x, ones, cfg.eps)
             gu = self.lin(xn, L["wgu"], 2 * self.ffn)
-            h_ = silu(gu[: self.ffn]) * gu[self.ffn:]
+            h_ = silu(gu[0::2]) * gu[1::2] if self.gu_interleaved else silu(gu[: self.ffn]) * gu[self.ffn:]
             kpad = L["wdown"].size // dim // oc.BLOCK_BYTES[self.qt] * 32  # rows may be zero-padded in k
             hp = np.zeros(kpad, dtype=f32)
             hp[: self.ffn] = h_

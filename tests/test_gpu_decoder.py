@@ -119,3 +119,71 @@ def test_decode_attention_routes(device, batch, nq, nkv, hd, max_ctx, pos):
         finally:
             device.set_option("attn_variant", 0)
         assert rel_err(got, want) < 2e-5, f"variant {variant}"
+
+
+# ---- one decode linear with its neighbours fused in (cq_qlinear_fused) -----------------------------------
+@pytest.mark.parametrize("m,k,n,epilogue,with_delta,with_norm", [
+    (1, 4096, 12288, 0, True, True),     # QKV-like
+    (1, 4096, 22016, 1, True, True),     # gate/up with the pairing epilogue
+    (3, 4096, 512, 1, True, True),       # several rows, few output rows
+    (1, 8192, 7168, 1, True, True),      # 70B-shape shard: the prologue would crowd the ring -> refused, caller falls back
+    (1, 8192, 7168, 1, False, False),    # ... and fuses only the epilogue
+    (1, 11008, 4096, 0, True, True),     # k = 11008: the per-thread activation set-up
+    (2, 1024, 2048, 0, False, True),     # norm without the residual add
+    (1, 4096, 4096, 0, True, False),     # add only
+])
+def test_fused_linear_matches_separate_operators_and_oracle(device, m, k, n, epilogue, with_delta, with_norm):
+    import ctypes as C
+    from candy_b200 import abi
+    from candy_b200.backend import QStorage
+    from oracle.decoder_np import silu
+    lib, ctx = device._lib, device.ctx
+    rng = np.random.default_rng(m + k + n + epilogue)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    delta = rng.standard_normal((m, k), dtype=np.float32) * np.float32(0.3)
+    alpha = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    eps = 1e-5
+    blocks = oc.quantize(oc.Q4_0, 0, w)
+    qs = QStorage.from_blocks(device, oc.Q4_0, 0, n, k, blocks)
+    d_x, d_delta, d_alpha = device.storage_from_slice(x), device.storage_from_slice(delta), device.storage_from_slice(alpha)
+    d_xout = device.alloc(m * k)
+    n_out = n // 2 if epilogue else n
+    d_y = device.alloc(m * n_out)
+    st = lib.cq_qlinear_fused(ctx, oc.Q4_0, 0, d_x.ptr, d_delta.ptr if with_delta else None, d_alpha.ptr if with_norm else None, eps,
+                              d_xout.ptr if (with_delta or with_norm) else None, m, k, qs.buf.ptr, n, epilogue, d_y.ptr, n_out)
+    if k == 8192 and (with_delta or with_norm):
+        assert st == abi.CQ_ERR_UNSUPPORTED  # documented: the caller issues the separate operators
+        return
+    abi.check(ctx, st, "fused linear")
+    got = d_y.data().reshape(m, n_out)
+    xs = x + delta if with_delta else x
+    if with_delta or with_norm:
+        np.testing.assert_array_equal(d_xout.data().reshape(m, k), xs.astype(np.float32))
+    xn = xs
+    if with_norm:
+        ms = (xs.astype(np.float64) ** 2).mean(axis=1, keepdims=True)
+        xn = (xs / np.sqrt(ms + eps) * alpha).astype(np.float32)
+    t = oc.qmatmul(oc.Q4_0, 0, xn, blocks, n, nthreads=8)
+    want = (silu(t[:, 0::2]) * t[:, 1::2]) if epilogue else t
+    assert rel_err(got, want) < 1e-4
+    assert rel_err(got, want) <= REL_TOL
+
+
+def test_decoder_fused_and_unfused_agree(device):
+    """The same model stepped with fused linears and with the separate operators: same logits (norm sums differ in order only)."""
+    from candy_b200.decoder import DecoderConfig, QuantDecoder
+    cfg = DecoderConfig(n_layers=2, dim=1024, n_heads=8, n_kv_heads=4, head_dim=128, ffn=2816, vocab=2000, max_ctx=32)
+    outs = []
+    for fuse in (True, False):
+        model = QuantDecoder(device, cfg, seed=5, fuse=fuse)
+        assert model.fuse == fuse
+        ids = [3, 77, 1999, 5, 1024]
+        logits = []
+        for pos, tok in enumerate(ids):
+            model.set_state(np.array([tok], dtype=np.uint32), pos)
+            model.step()
+            logits.append(model.read_logits().copy())
+        outs.append(np.stack(logits))
+        del model
+    assert rel_err(outs[0], outs[1]) < 5e-5
