@@ -104,7 +104,7 @@ def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512
             out.append({"qtype": name, "m": m, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
                         "algorithmic_gbs": round(nbytes / t / 1e9, 1), "bound": "hbm" if t_hbm >= t_tensor else "tensor",
                         "roofline_us": round(max(t_hbm, t_tensor) * 1e6, 2), "frac_of_roofline": round(max(t_hbm, t_tensor) / t, 4),
-                        "path": "raw blocks dequantized into tensor memory" if (qt == 2 and m <= 128) else "f16 copy of W, then f16 tcgen05 GEMM"})
+                        "path": "raw blocks dequantized into tensor memory" if m <= (128 if qt == 2 else 64) else "f16 copy of W, then f16 tcgen05 GEMM"})
             del x, y
         del ring, first
     return {"n": n, "k": k, "peak_gbs": peak_gbs, "peak_tflops": peak_tflops, "l2_defeat": "ring of 8 weight copies", "cases": out}

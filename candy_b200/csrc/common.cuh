@@ -106,9 +106,9 @@ cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const floa
                       int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
 cq_status launch_gemv_q8_1_blocks(cq_ctx *ctx, int qtype, int order, const void *act_blocks, int64_t m, int64_t k,
                                   const void *w, int64_t n, float *y, int64_t ldy);
-// Narrow-batch Q4_0 GEMM that dequantizes into tensor memory (gemm_dequant_tmem.cu).
+// Narrow-batch GEMM that dequantizes raw blocks into tensor memory (gemm_dequant_tmem.cu).
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w);
-cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
+cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
                                     float *y, int64_t ldy);
 cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,
                       int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);

@@ -1,4 +1,4 @@
-// Quantized GEMM for narrow batches (8 < m <= 128, Q4_0): Y[m,n] = X[m,k] . W[n,k]^T with the
+// Quantized GEMM for narrow batches (8 < m <= 128 for Q4_0, <= 64 for Q8_0): Y[m,n] = X[m,k] . W[n,k]^T with the
 // weights read from HBM once, as the 18-byte blocks they are stored in.
 //
 // Same CQ_ACT_F16 numerics as the wide GEMM (f16 activations, weights d*(q-8) rounded once to
@@ -57,12 +57,14 @@ namespace {
 
 constexpr int FT_ROWS = 128;                   // weight rows per tile = tensor-memory lanes
 constexpr int FT_KCHUNK = 256;                 // values of k per item
-constexpr int FT_ROWCHUNK_Q4 = 8 * kQ4Bytes;   // 144 bytes of one row per item
-constexpr int FT_WBYTES = FT_ROWS * FT_ROWCHUNK_Q4;  // 18432
 constexpr int FT_ACOLS = FT_KCHUNK / 2;        // 128 columns of A per pipe (two halves of 64)
 
-template <int MPAD>
+template <int QT, int MPAD>
 struct FtCfg {
+    static constexpr int kBlockBytes = QT == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
+    static constexpr int kRowChunk = 8 * kBlockBytes;        // bytes of one row per item: 144 (Q4_0) / 272 (Q8_0)
+    static constexpr int kWBytes = FT_ROWS * kRowChunk;      // one stage of raw blocks: 18 432 / 34 816
+    static constexpr int kHalfWords = kRowChunk / 8;         // 32-bit words a thread loads: four blocks = 18 / 34
     // Independent pipes per CTA, each = (tile of the group, a TMA warp, four dequantizing warps, two
     // MMA-issuing lanes with an accumulator each, 128 columns of A in two halves).
     static constexpr int kPipes = 2;
@@ -70,8 +72,9 @@ struct FtCfg {
     static constexpr int kXBytes = 4 * MPAD * 128;  // one slab of X: four 64-wide boxes of MPAD rows
     static constexpr int kIssuers = MPAD >= 128 ? 1 : 2;  // MMA-issuing lanes per pipe, an accumulator each
     static constexpr int kXStages = MPAD >= 64 ? 2 : 3;
-    static constexpr int kWStages = MPAD >= 128 ? 2 : 4;  // per pipe
-    static constexpr size_t kSmem = (size_t)kPipes * kWStages * FT_WBYTES + (size_t)kXStages * kXBytes + 1024 + 512;
+    static constexpr int kWStages = (MPAD >= 128 || QT == CQ_Q8_0) ? 2 : 4;  // per pipe
+    static constexpr size_t kSmem = (size_t)kPipes * kWStages * kWBytes + (size_t)kXStages * kXBytes + 1024 + 512;
+    static_assert(kSmem <= 232448, "shared memory");
     // tensor memory: 128 columns of A per pipe, then two accumulators of MPAD columns per pipe
     static constexpr int kDCol0 = kPipes * FT_ACOLS;
     static constexpr int kWarpW0 = 2;                        // warps 0,1 load X; then one TMA warp per pipe
@@ -84,9 +87,11 @@ struct FtCfg {
 
 // Position p of a block's 32 values, in the order the dequantizing threads emit them, holds
 // original element kPerm[order][p].
-__constant__ uint8_t kPerm[2][32] = {
+__constant__ uint8_t kPerm[3][32] = {
     {0, 4, 1, 5, 2, 6, 3, 7, 8, 12, 9, 13, 10, 14, 11, 15, 16, 20, 17, 21, 18, 22, 19, 23, 24, 28, 25, 29, 26, 30, 27, 31},
-    {0, 2, 16, 18, 1, 3, 17, 19, 4, 6, 20, 22, 5, 7, 21, 23, 8, 10, 24, 26, 9, 11, 25, 27, 12, 14, 28, 30, 13, 15, 29, 31}};
+    {0, 2, 16, 18, 1, 3, 17, 19, 4, 6, 20, 22, 5, 7, 21, 23, 8, 10, 24, 26, 9, 11, 25, 27, 12, 14, 28, 30, 13, 15, 29, 31},
+    // Q8_0: bytes convert in place, natural order
+    {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25, 26, 27, 28, 29, 30, 31}};
 
 // X [m,k] f32 -> f16 with each 32-group permuted; one thread per eight output positions.
 __global__ void __launch_bounds__(256) x_to_f16_perm_kernel(const float *__restrict__ x, int64_t m, int64_t k, int64_t ldx, int order,
@@ -155,6 +160,20 @@ __device__ __forceinline__ void dequant_word(uint32_t n, __half2 d2, uint32_t *o
     out[3] = *reinterpret_cast<uint32_t *>(&q3);
 }
 
+// Four int8 of one word -> two f16 pairs d*q, natural order: q ^ 0x80 = q + 128 as an unsigned byte,
+// a byte permute puts it under a 0x64 high byte (1024 + 128 + q), one HSUB2 removes the 1152.
+__device__ __forceinline__ void dequant_word_q8(uint32_t n, __half2 d2, uint32_t *out) {
+    const __half2 k1152 = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+    const uint32_t u = n ^ 0x80808080u;
+    uint32_t t0 = __byte_perm(u, 0x64646464u, 0x4140);  // bytes: u0, 0x64, u1, 0x64
+    uint32_t t1 = __byte_perm(u, 0x64646464u, 0x4342);  // bytes: u2, 0x64, u3, 0x64
+    __half2 q0 = __hsub2(*reinterpret_cast<__half2 *>(&t0), k1152);
+    __half2 q1 = __hsub2(*reinterpret_cast<__half2 *>(&t1), k1152);
+    q0 = __hmul2(q0, d2), q1 = __hmul2(q1, d2);
+    out[0] = *reinterpret_cast<uint32_t *>(&q0);
+    out[1] = *reinterpret_cast<uint32_t *>(&q1);
+}
+
 struct FtParams {
     float *y;          // [m, n], row pitch ldy: groups whose whole k range one CTA owns are written here directly
     int64_t ldy;
@@ -165,10 +184,11 @@ struct FtParams {
     int *err;
 };
 
-template <int MPAD>
-__global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
-    qgemm_q4_0_tmem_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const FtParams p) {
-    using Cfg = FtCfg<MPAD>;
+template <int QT, int MPAD>
+__global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
+    qgemm_tmem_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const FtParams p) {
+    using Cfg = FtCfg<QT, MPAD>;
+    constexpr int FT_WBYTES = Cfg::kWBytes, ROWCHUNK = Cfg::kRowChunk, HW = Cfg::kHalfWords;
     constexpr int WSP = Cfg::kWStages, XST = Cfg::kXStages, PIPES = Cfg::kPipes, DCOL0 = Cfg::kDCol0, GROUP_ROWS = Cfg::kGroupRows;
     constexpr int IPP = Cfg::kIssuers, NISS = IPP * PIPES;
     extern __shared__ uint8_t smem_raw[];
@@ -274,7 +294,7 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
                     const uint32_t bar = smem_u32(&w_full[s]);
                     mbar_expect_tx(bar, FT_WBYTES);
                     // tiles past the last row are outside the tensor: zero fill, no traffic
-                    tma_load_2d(smem_u32(smem_w + (size_t)s * FT_WBYTES), &tmW, (c0 + c) * FT_ROWCHUNK_Q4, (group * PIPES + q) * FT_ROWS, bar);
+                    tma_load_2d(smem_u32(smem_w + (size_t)s * FT_WBYTES), &tmW, (c0 + c) * (ROWCHUNK / 2), (group * PIPES + q) * FT_ROWS, bar);  // x in 2-byte elements
                     if (q == 0) FT_TRACE(step, 2);
                 }
             }
@@ -350,11 +370,11 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
                 break;
             }
             if (tracer) FT_TRACE(step, 8 + 3 * h);
-            // Four blocks = 72 bytes, 8-byte aligned.
-            uint32_t w[18];
-            const uint32_t src = smem_u32(smem_w + (size_t)s * FT_WBYTES + r * FT_ROWCHUNK_Q4 + h * 72);
+            // Four blocks = 72 / 136 bytes, 8-byte aligned.
+            uint32_t w[HW];
+            const uint32_t src = smem_u32(smem_w + (size_t)s * FT_WBYTES + r * ROWCHUNK + h * (ROWCHUNK / 2));
 #pragma unroll
-            for (int i = 0; i < 9; ++i)
+            for (int i = 0; i < HW / 2; ++i)
                 asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(src + 8 * i) : "memory");
             // The stage may be refilled once the raw blocks are in registers -- really in registers.
             // Neither the compiler nor the arrive waits for shared-memory loads that are still in
@@ -364,7 +384,7 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
             {
                 uint32_t all = w[0];
 #pragma unroll
-                for (int i = 1; i < 18; ++i) all ^= w[i];
+                for (int i = 1; i < HW; ++i) all ^= w[i];
                 asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem_u32(&sink[warp])), "r"(all) : "memory");
             }
             __syncwarp();
@@ -379,22 +399,30 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
             if (!(p.probe & 1)) {
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr) {
-                    // two blocks in nine words: the first starts on a word, its nibbles two bytes in;
-                    // the second starts two bytes into word 4, its nibbles on word 5
-                    const uint32_t *wq = w + 9 * pr;
+                    // two blocks in 9 (Q4_0) / 17 (Q8_0) words: the first starts on a word, its values two
+                    // bytes in; the second starts two bytes into the middle word, its values on the next one
+                    constexpr int PW = HW / 2, VW = (PW - 1) / 2;  // words per pair, words of values per block
+                    const uint32_t *wq = w + PW * pr;
                     uint32_t o[16];
                     {
                         const __half dh = __ushort_as_half((unsigned short)(wq[0] & 0xFFFFu));
                         const __half2 d2 = __halves2half2(dh, dh);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) dequant_word(__funnelshift_r(wq[j], wq[j + 1], 16), d2, o + 4 * j);
+                        for (int j = 0; j < VW; ++j) {
+                            const uint32_t v = __funnelshift_r(wq[j], wq[j + 1], 16);
+                            if (QT == CQ_Q4_0) dequant_word(v, d2, o + 4 * j);
+                            else dequant_word_q8(v, d2, o + 2 * j);
+                        }
                         tmem_st16(a_t + (uint32_t)((2 * pr) * 16), o);
                     }
                     {
-                        const __half dh = __ushort_as_half((unsigned short)(wq[4] >> 16));
+                        const __half dh = __ushort_as_half((unsigned short)(wq[VW] >> 16));
                         const __half2 d2 = __halves2half2(dh, dh);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) dequant_word(wq[5 + j], d2, o + 4 * j);
+                        for (int j = 0; j < VW; ++j) {
+                            if (QT == CQ_Q4_0) dequant_word(wq[VW + 1 + j], d2, o + 4 * j);
+                            else dequant_word_q8(wq[VW + 1 + j], d2, o + 2 * j);
+                        }
                         tmem_st16(a_t + (uint32_t)((2 * pr + 1) * 16), o);
                     }
                 }
@@ -457,14 +485,16 @@ __global__ void __launch_bounds__(FtCfg<MPAD>::kThreads, 1)
     if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
-bool make_w_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes) {
+// The raw blocks as a 2-D tensor of 2-byte elements (a Q8_0 item is 272 bytes per row, more than the 256
+// elements a box may span in 1-byte elements): box = one item of 128 rows.
+bool make_w_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes, int row_chunk) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n};
+    cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 2), (cuuint64_t)n};
     cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    cuuint32_t box[2] = {(cuuint32_t)FT_ROWCHUNK_Q4, (cuuint32_t)FT_ROWS};
+    cuuint32_t box[2] = {(cuuint32_t)(row_chunk / 2), (cuuint32_t)FT_ROWS};
     cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 bool make_x_map(CUtensorMap *map, const void *x16, int64_t m, int64_t k, int box_rows) {
@@ -478,14 +508,14 @@ bool make_x_map(CUtensorMap *map, const void *x16, int64_t m, int64_t k, int box
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MPAD>
+template <int QT, int MPAD>
 cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, const FtParams &p, unsigned ctas) {
     static thread_local int configured = -1;
     if (configured != ctx->device) {
-        CQ_CUDA(ctx, cudaFuncSetAttribute(qgemm_q4_0_tmem_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FtCfg<MPAD>::kSmem));
+        CQ_CUDA(ctx, cudaFuncSetAttribute(qgemm_tmem_kernel<QT, MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FtCfg<QT, MPAD>::kSmem));
         configured = ctx->device;
     }
-    qgemm_q4_0_tmem_kernel<MPAD><<<ctas, FtCfg<MPAD>::kThreads, FtCfg<MPAD>::kSmem, ctx->stream>>>(tmW, tmX, p);
+    qgemm_tmem_kernel<QT, MPAD><<<ctas, FtCfg<QT, MPAD>::kThreads, FtCfg<QT, MPAD>::kSmem, ctx->stream>>>(tmW, tmX, p);
     CQ_CUDA(ctx, cudaGetLastError());
     return CQ_OK;
 }
@@ -493,16 +523,17 @@ cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, co
 }  // namespace
 
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w) {
-    return qtype == CQ_Q4_0 && m >= 1 && m <= 128 && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    // Q8_0 stages are twice as large: no room for the 128-row X slabs next to them
+    return m >= 1 && m <= (qtype == CQ_Q4_0 ? 128 : 64) && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
 }
 
-cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y,
+cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y,
                                     int64_t ldy) {
     if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
     if (n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
     const int mpad = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
-    const int group_rows = FtCfg<32>::kGroupRows;
+    const int group_rows = FtCfg<CQ_Q4_0, 32>::kGroupRows;
     const int ngroups = (int)((n + group_rows - 1) / group_rows);
     const int nchunks = (int)(k / FT_KCHUNK);
     const int64_t total = (int64_t)ngroups * nchunks;
@@ -522,23 +553,30 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int order, const float *x, int6
         const int64_t items = m * (k / 8);
         const unsigned cap = (unsigned)ctx->sm_count * 8;
         const unsigned grid = (unsigned)((items + 255) / 256 < cap ? (items + 255) / 256 : cap);
-        x_to_f16_perm_kernel<<<grid, 256, 0, ctx->stream>>>(x, m, k, ldx, order, x16);
+        x_to_f16_perm_kernel<<<grid, 256, 0, ctx->stream>>>(x, m, k, ldx, qtype == CQ_Q4_0 ? order : 2, x16);
     }
     CUtensorMap tmW, tmX;
-    if (!make_w_map(&tmW, w, n, (k / 32) * kQ4Bytes) || !make_x_map(&tmX, x16, m, k, mpad))
+    const int bb = qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
+    if (!make_w_map(&tmW, w, n, (k / 32) * bb, 8 * bb) || !make_x_map(&tmX, x16, m, k, mpad))
         return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
     FtParams p;
     p.y = y, p.ldy = ldy, p.part = part;
     p.m = (int)m, p.n = (int)n, p.nchunks = nchunks, p.total = (int)total, p.per_cta = (int)per_cta;
     p.err = ctx->dev_err_devptr;
     p.probe = ctx->tune.gemv_probe;
-    if (mpad == 16) s = run_ft<16>(ctx, tmW, tmX, p, ctas);
-    else if (mpad == 32) s = run_ft<32>(ctx, tmW, tmX, p, ctas);
-    else if (mpad == 64) s = run_ft<64>(ctx, tmW, tmX, p, ctas);
-    else s = run_ft<128>(ctx, tmW, tmX, p, ctas);
+    if (qtype == CQ_Q4_0) {
+        if (mpad == 16) s = run_ft<CQ_Q4_0, 16>(ctx, tmW, tmX, p, ctas);
+        else if (mpad == 32) s = run_ft<CQ_Q4_0, 32>(ctx, tmW, tmX, p, ctas);
+        else if (mpad == 64) s = run_ft<CQ_Q4_0, 64>(ctx, tmW, tmX, p, ctas);
+        else s = run_ft<CQ_Q4_0, 128>(ctx, tmW, tmX, p, ctas);
+    } else {
+        if (mpad == 16) s = run_ft<CQ_Q8_0, 16>(ctx, tmW, tmX, p, ctas);
+        else if (mpad == 32) s = run_ft<CQ_Q8_0, 32>(ctx, tmW, tmX, p, ctas);
+        else s = run_ft<CQ_Q8_0, 64>(ctx, tmW, tmX, p, ctas);
+    }
     if (s != CQ_OK) return s;
     if (shared_tiles) {
-        static_assert(FtCfg<16>::kGroupRows == 256 && FtCfg<64>::kGroupRows == 256 && FtCfg<128>::kGroupRows == 256, "sum kernel layout");
+        static_assert(FtCfg<CQ_Q4_0, 16>::kGroupRows == 256 && FtCfg<CQ_Q8_0, 64>::kGroupRows == 256 && FtCfg<CQ_Q4_0, 128>::kGroupRows == 256, "sum kernel layout");
         shared_group_sum_kernel<<<dim3((unsigned)ngroups, (unsigned)m), 64, 0, ctx->stream>>>(part, m, n, nchunks, (int)per_cta, y, ldy);
         CQ_CUDA(ctx, cudaGetLastError());
     }

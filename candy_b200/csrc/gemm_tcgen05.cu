@@ -371,7 +371,7 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     if (m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
     // narrow batches stream the raw blocks and dequantize into tensor memory: no f16 copy of W
     if (ctx->tune.gemm_variant != 3 && !ctx->tune.gemm_cache_weights && qgemm_dequant_tmem_supported(qtype, m, k, w))
-        return launch_qgemm_dequant_tmem(ctx, order, x, m, k, ldx, w, n, y, ldy);
+        return launch_qgemm_dequant_tmem(ctx, qtype, order, x, m, k, ldx, w, n, y, ldy);
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
     const size_t w16_bytes = (size_t)n * k * 2;
     // With gemm_cache_weights the f16 copy of a weight matrix is made once and kept (the caller

@@ -88,7 +88,7 @@ def test_narrow_batch_gemm_streams_raw_blocks(device, order, m, n, k):
         two_step = run(device, oc.Q4_0, order, x, blocks, n)
     finally:
         device.set_option("gemm_variant", 0)
-    assert rel_err(got, two_step) < 2e-5  # f32 summation order differs (k split, tensor-core internals)
+    assert rel_err(got, two_step) < 5e-5  # f32 summation order differs (k split, tensor-core internals)
 
 
 def test_narrow_batch_gemm_edge_scales(device):
@@ -102,3 +102,36 @@ def test_narrow_batch_gemm_edge_scales(device):
     x = rng.standard_normal((m, k), dtype=np.float32)
     got = run(device, oc.Q4_0, 0, x, blocks.reshape(-1), n)
     assert rel_err(got, emulate_f16(oc.Q4_0, 0, x, blocks.reshape(-1), n)) < 2e-5
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 128, 256), (16, 300, 512), (33, 4096, 4096), (64, 257, 2304), (64, 11008, 4096), (12, 8192, 14336),
+                                   (16, 11008, 4096)])
+def test_narrow_batch_gemm_q8_0(device, m, n, k):
+    w, x = make_case(9100 + m + n + k, n, k, m)
+    blocks = oc.quantize(oc.Q8_0, 0, w)
+    got = run(device, oc.Q8_0, 0, x, blocks, n)
+    assert rel_err(got, emulate_f16(oc.Q8_0, 0, x, blocks, n)) < 2e-5
+    rows = np.linspace(0, m - 1, num=min(m, 4), dtype=int)
+    cpu = oc.qmatmul(oc.Q8_0, 0, x[rows], blocks, n, nthreads=8)
+    assert rel_err(got[rows], cpu) <= REL_TOL
+    device.set_option("gemm_variant", 3)
+    try:
+        two_step = run(device, oc.Q8_0, 0, x, blocks, n)
+    finally:
+        device.set_option("gemm_variant", 0)
+    assert rel_err(got, two_step) < 5e-5  # f32 summation order differs
+
+
+def test_narrow_batch_gemm_q8_0_edge_values(device):
+    """Every int8 value and scale patterns incl. zero and subnormal scales."""
+    n, k, m = 256, 512, 16
+    rng = np.random.default_rng(6)
+    blocks = rng.integers(0, 256, size=(n * k // 32, 34), dtype=np.uint8)
+    blocks[0, 2:] = np.arange(32, dtype=np.uint8) * 8          # 0, 8, ..., 248 (as int8: 0..127, -128..-8)
+    blocks[1, 2:] = np.array([0x80, 0x7F, 0xFF, 0x01] * 8, dtype=np.uint8)
+    scales = np.array([0x0000, 0x8000, 0x0001, 0x03FF, 0x0400, 0x3C00, 0x2E00, 0xB000], dtype=np.uint16)
+    d = scales[rng.integers(0, len(scales), size=blocks.shape[0])]
+    blocks[:, 0], blocks[:, 1] = d & 0xFF, d >> 8
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    got = run(device, oc.Q8_0, 0, x, blocks.reshape(-1), n)
+    assert rel_err(got, emulate_f16(oc.Q8_0, 0, x, blocks.reshape(-1), n)) < 2e-5
