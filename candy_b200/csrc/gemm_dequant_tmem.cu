@@ -96,6 +96,8 @@ __constant__ uint8_t kPerm[3][32] = {
 // X [m,k] f32 -> f16 with each 32-group permuted; one thread per eight output positions.
 __global__ void __launch_bounds__(256) x_to_f16_perm_kernel(const float *__restrict__ x, int64_t m, int64_t k, int64_t ldx, int order,
                                                           __half *__restrict__ out) {
+    pdl_launch_dependents();  // the GEMM behind this kernel starts fetching weights meanwhile
+    pdl_wait_prior();         // x comes from the previous kernel; the scratch this writes may still be read by it
     const int64_t per_row = k / 8, total = m * per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t row = i / per_row, o8 = i - row * per_row;  // output positions 8*o8 .. 8*o8+7 of the row
@@ -117,6 +119,8 @@ __global__ void __launch_bounds__(256) x_to_f16_perm_kernel(const float *__restr
 __global__ void __launch_bounds__(64) shared_group_sum_kernel(const float *__restrict__ part, int64_t m, int64_t n, int nchunks, int per_cta,
                                                             float *__restrict__ y, int64_t ldy) {
     constexpr int kGroupRows = 256;
+    pdl_launch_dependents();
+    pdl_wait_prior();
     const int t = blockIdx.x, row = blockIdx.y;
     const int first = (t * nchunks) / per_cta, last = ((t + 1) * nchunks - 1) / per_cta;
     if (first == last) return;  // one CTA had the group's whole k range and wrote y itself
@@ -202,6 +206,10 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
     uint32_t *sink = tmem_slot + 1;  // one word per warp: target of the stores that pin load completion (see the dequantizing warps)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Chained launch: the next kernel may become resident now.  Here, only the warps that touch what
+    // earlier kernels produce or still read wait for them: the X loaders (X scratch) and the epilogue
+    // (y, partial sums).  The raw blocks are nobody's output, so their TMA warps start at once.
+    pdl_launch_dependents();
     // this CTA's steps [g0, g1) of the (group, chunk) list: equal shares, so the SMs finish together
     const int g0 = blockIdx.x * p.per_cta, g1 = min(g0 + p.per_cta, p.total);
     const int nsteps = g1 - g0;
@@ -245,6 +253,7 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
     if (warp < Cfg::kWarpW0) {
         // ---- TMA, X: warp 0 loads boxes 0,1 of every slab, warp 1 boxes 2,3 -------------------------
         if (lane == 0) {
+            pdl_wait_prior();
             int step = 0;
             bool ok = true;
             for (int g = g0; g < g1 && ok;) {
@@ -435,6 +444,7 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
         }
     } else {
         // ---- epilogue: two accumulators per tile of the group, lane = weight row ---------------------
+        pdl_wait_prior();
         const int quarter = warp & 3;
         int seg = 0;
         for (int g = g0; g < g1; ++seg) {
@@ -508,6 +518,24 @@ bool make_x_map(CUtensorMap *map, const void *x16, int64_t m, int64_t k, int box
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Launch with programmatic stream serialization: the kernel may become resident while its predecessor
+// is still running; whatever depends on earlier work waits with griddepcontrol.wait inside the kernel.
+template <typename Kern, typename... Args>
+cq_status launch_chained(cq_ctx *ctx, Kern kern, dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, args...));
+    return CQ_OK;
+}
+
 template <int QT, int MPAD>
 cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, const FtParams &p, unsigned ctas) {
     static thread_local int configured = -1;
@@ -515,9 +543,7 @@ cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, co
         CQ_CUDA(ctx, cudaFuncSetAttribute(qgemm_tmem_kernel<QT, MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FtCfg<QT, MPAD>::kSmem));
         configured = ctx->device;
     }
-    qgemm_tmem_kernel<QT, MPAD><<<ctas, FtCfg<QT, MPAD>::kThreads, FtCfg<QT, MPAD>::kSmem, ctx->stream>>>(tmW, tmX, p);
-    CQ_CUDA(ctx, cudaGetLastError());
-    return CQ_OK;
+    return launch_chained(ctx, qgemm_tmem_kernel<QT, MPAD>, dim3(ctas), dim3(FtCfg<QT, MPAD>::kThreads), FtCfg<QT, MPAD>::kSmem, tmW, tmX, p);
 }
 
 }  // namespace
@@ -553,7 +579,8 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const flo
         const int64_t items = m * (k / 8);
         const unsigned cap = (unsigned)ctx->sm_count * 8;
         const unsigned grid = (unsigned)((items + 255) / 256 < cap ? (items + 255) / 256 : cap);
-        x_to_f16_perm_kernel<<<grid, 256, 0, ctx->stream>>>(x, m, k, ldx, qtype == CQ_Q4_0 ? order : 2, x16);
+        s = launch_chained(ctx, x_to_f16_perm_kernel, dim3(grid), dim3(256), 0, x, m, k, ldx, qtype == CQ_Q4_0 ? order : 2, x16);
+        if (s != CQ_OK) return s;
     }
     CUtensorMap tmW, tmX;
     const int bb = qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
@@ -577,8 +604,8 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const flo
     if (s != CQ_OK) return s;
     if (shared_tiles) {
         static_assert(FtCfg<CQ_Q4_0, 16>::kGroupRows == 256 && FtCfg<CQ_Q8_0, 64>::kGroupRows == 256 && FtCfg<CQ_Q4_0, 128>::kGroupRows == 256, "sum kernel layout");
-        shared_group_sum_kernel<<<dim3((unsigned)ngroups, (unsigned)m), 64, 0, ctx->stream>>>(part, m, n, nchunks, (int)per_cta, y, ldy);
-        CQ_CUDA(ctx, cudaGetLastError());
+        s = launch_chained(ctx, shared_group_sum_kernel, dim3((unsigned)ngroups, (unsigned)m), dim3(64), 0, (const float *)part, m, n, nchunks, (int)per_cta, y, ldy);
+        if (s != CQ_OK) return s;
     }
     return CQ_OK;
 }
