@@ -100,6 +100,19 @@ __global__ void __launch_bounds__(256) rope_store_kv_kernel(float *__restrict__ 
     }
 }
 
+// Element d of head vector v (hd values) rotated to position `pos`, half-split pairs (d, d + hd/2),
+// the same expression as rope_store_kv_kernel; cos/sin tables are [max_ctx][hd/2].
+__device__ __forceinline__ float rope_elem(const float *__restrict__ v, int d, int hd, const float *__restrict__ cos_t,
+                                           const float *__restrict__ sin_t, int pos) {
+    const int half = hd >> 1;
+    if (d < half) {
+        const float c = cos_t[(int64_t)pos * half + d], s = sin_t[(int64_t)pos * half + d];
+        return v[d] * c - v[d + half] * s;
+    }
+    const float c = cos_t[(int64_t)pos * half + d - half], s = sin_t[(int64_t)pos * half + d - half];
+    return v[d - half] * s + v[d] * c;
+}
+
 constexpr int kAttnChunk = 32;    // keys per CTA: short chunks keep many CTAs in flight at small contexts
 constexpr int kAttnThreads = 128;
 
@@ -107,10 +120,14 @@ constexpr int kAttnThreads = 128;
 // and the weighted sum of V; writes (max, sum, acc[hd]) for the combine kernel.  hd <= 256 and a
 // multiple of 4.  Latency-bound (a few hundred KB per CTA out of L2/HBM), so every loop keeps
 // eight independent loads in flight.
+// With cos_t / sin_t given the kernel also does the rotary step: q is rotated as it is loaded, and the
+// newest key (position *pos, not yet in the cache) is taken from qkv -- rotated k, plain v -- by the
+// chunk that holds it; the first head of each kv group stores it to the caches (kc_w / vc_w).
 __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float *__restrict__ qkv, int nq, int nkv, int hd,
-                                                                  const int *__restrict__ pos_dev, const float *__restrict__ kc,
-                                                                  const float *__restrict__ vc, int max_ctx, float scale,
-                                                                  float *__restrict__ part, int nchunks) {
+                                                                  const int *__restrict__ pos_dev, const float *kc,
+                                                                  const float *vc, int max_ctx, float scale,
+                                                                  float *__restrict__ part, int nchunks, const float *__restrict__ cos_t,
+                                                                  const float *__restrict__ sin_t, float *kc_w, float *vc_w) {
     __shared__ float p_s[kAttnChunk];
     pdl_launch_dependents();
     pdl_wait_prior();
@@ -143,20 +160,36 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
     for (int h2 = 0; h2 < 2; ++h2) {
         const int d = lane * 4 + 128 * h2;
         qreg[h2] = (d < hd) ? *reinterpret_cast<const float4 *>(q + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cos_t && d < hd)
+            qreg[h2] = make_float4(rope_elem(q, d, hd, cos_t, sin_t, nkeys - 1), rope_elem(q, d + 1, hd, cos_t, sin_t, nkeys - 1),
+                                   rope_elem(q, d + 2, hd, cos_t, sin_t, nkeys - 1), rope_elem(q, d + 3, hd, cos_t, sin_t, nkeys - 1));
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int t = t0 + warp * 8 + j;
-            kreg[j][h2] = (t < t1 && d < hd) ? *reinterpret_cast<const float4 *>(kbase + (int64_t)t * kv_stride + d)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            const bool newest = cos_t && t == nkeys - 1;  // not in the cache yet: comes from qkv
+            kreg[j][h2] = (t < t1 && d < hd && !newest) ? *reinterpret_cast<const float4 *>(kbase + (int64_t)t * kv_stride + d)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (newest && d < hd) {
+                const float *kn = qkv + (int64_t)b * row + (nq + kvh) * hd;
+                kreg[j][h2] = make_float4(rope_elem(kn, d, hd, cos_t, sin_t, t), rope_elem(kn, d + 1, hd, cos_t, sin_t, t),
+                                          rope_elem(kn, d + 2, hd, cos_t, sin_t, t), rope_elem(kn, d + 3, hd, cos_t, sin_t, t));
+                if (head % (nq / nkv) == 0)
+                    *reinterpret_cast<float4 *>(kc_w + ((int64_t)b * max_ctx + t) * kv_stride + kvh * hd + d) = kreg[j][h2];
+            }
         }
     }
+    const float *vnew = qkv + (int64_t)b * row + (nq + nkv + kvh) * hd;  // newest value row, straight from qkv
     float vreg[kAttnChunk];
     const bool v_in_regs = hd <= kAttnThreads;
     if (v_in_regs) {
 #pragma unroll
-        for (int j = 0; j < kAttnChunk; ++j)
-            vreg[j] = (j < cnt && (int)threadIdx.x < hd) ? vbase[(int64_t)(t0 + j) * kv_stride + threadIdx.x] : 0.0f;
+        for (int j = 0; j < kAttnChunk; ++j) {
+            const bool newest = cos_t && t0 + j == nkeys - 1;
+            vreg[j] = (j < cnt && (int)threadIdx.x < hd) ? (newest ? vnew[threadIdx.x] : vbase[(int64_t)(t0 + j) * kv_stride + threadIdx.x]) : 0.0f;
+        }
     }
+    if (cos_t && t1 == nkeys && head % (nq / nkv) == 0)  // this chunk holds the newest key: its value row goes to the cache
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) vc_w[((int64_t)b * max_ctx + nkeys - 1) * kv_stride + kvh * hd + d] = vnew[d];
     {
         float s[8];
 #pragma unroll
@@ -202,7 +235,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
             for (int tb = 0; tb < cnt; tb += 8) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    if (tb + j < cnt) acc[j] = fmaf(p_s[tb + j], vbase[(int64_t)(t0 + tb + j) * kv_stride + d], acc[j]);
+                    if (tb + j < cnt)
+                        acc[j] = fmaf(p_s[tb + j], (cos_t && t0 + tb + j == nkeys - 1) ? vnew[d] : vbase[(int64_t)(t0 + tb + j) * kv_stride + d], acc[j]);
             }
             out[2 + d] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
         }
@@ -316,8 +350,10 @@ constexpr size_t kAttn2Smem = (size_t)kAttn2Keys * kAttn2KStride * 4 + (size_t)k
                               + 4 * 8 * kAttn2Keys * 4                                               // score partials [warp][head][key]
                               + kAttn2Keys * 8 * 4 + 64;                                             // numerators [key][head], factors
 __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__restrict__ qkv, int nq, int nkv, const int *__restrict__ pos_dev,
-                                                           const float *__restrict__ kc, const float *__restrict__ vc, int max_ctx, float scale,
-                                                           float *__restrict__ part, int nsplits, int keys_per_split) {
+                                                           const float *kc, const float *vc, int max_ctx, float scale,
+                                                           float *__restrict__ part, int nsplits, int keys_per_split,
+                                                           const float *__restrict__ cos_t, const float *__restrict__ sin_t, float *kc_w,
+                                                           float *vc_w) {
     constexpr int hd = 128;
     extern __shared__ __align__(16) uint8_t attn_smem[];
     float *Ks = reinterpret_cast<float *>(attn_smem);
@@ -347,7 +383,11 @@ __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__rest
     const int64_t kv_stride = (int64_t)nkv * hd;
     const float *kbase = kc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
     const float *vbase = vc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
-    for (int i = tid; i < 8 * hd; i += 128) q_s[i] = (i / hd) < G ? qkv[(int64_t)b * row + (kvh * G + i / hd) * hd + (i % hd)] : 0.0f;
+    // q of the group's heads (rotated here when the rotary step is fused in: cos_t given)
+    for (int i = tid; i < 8 * hd; i += 128) {
+        const float *qh = qkv + (int64_t)b * row + (kvh * G + i / hd) * hd;
+        q_s[i] = (i / hd) < G ? (cos_t ? rope_elem(qh, i % hd, hd, cos_t, sin_t, nkeys - 1) : qh[i % hd]) : 0.0f;
+    }
 
     float m_run[2] = {-3.402823466e38f, -3.402823466e38f}, l_run[2] = {0.0f, 0.0f};  // heads 2*warp, 2*warp+1 (lane-uniform)
     float acc[8][4];
@@ -365,7 +405,18 @@ __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__rest
         for (int j = 0; j < 16; ++j) {
             const int f = tid + 128 * j, r = f >> 5, c4 = f & 31;
             float *d = dst + r * dst_stride + 4 * c4;
-            if (r < cnt) {
+            if (cos_t && r < cnt && t0 + r == nkeys - 1) {
+                // the newest key is not in the cache yet: rotated k / plain v come from qkv, and this CTA
+                // (the only one of its kv head and sequence that sees this row) stores them to the cache
+                const bool is_k = base == kbase;
+                const float *src = qkv + (int64_t)b * row + (nq + (is_k ? 0 : nkv) + kvh) * hd;
+                float4 v4;
+                if (is_k) v4 = make_float4(rope_elem(src, 4 * c4, hd, cos_t, sin_t, t0 + r), rope_elem(src, 4 * c4 + 1, hd, cos_t, sin_t, t0 + r),
+                                           rope_elem(src, 4 * c4 + 2, hd, cos_t, sin_t, t0 + r), rope_elem(src, 4 * c4 + 3, hd, cos_t, sin_t, t0 + r));
+                else v4 = *reinterpret_cast<const float4 *>(src + 4 * c4);
+                *reinterpret_cast<float4 *>(d) = v4;
+                *reinterpret_cast<float4 *>((is_k ? kc_w : vc_w) + ((int64_t)b * max_ctx + t0 + r) * kv_stride + kvh * hd + 4 * c4) = v4;
+            } else if (r < cnt) {
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(d)),
                              "l"(base + (int64_t)(t0 + r) * kv_stride + 4 * c4)
                              : "memory");
@@ -751,10 +802,14 @@ size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head
     return (size_t)batch * n_q_heads * nchunks * (head_dim + 2);
 }
 
-cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim,
-                              const int *pos_dev, const float *k_cache_dev, const float *v_cache_dev, int max_ctx, float *scratch_dev,
-                              float *out_dev) {
-    CQ_ENTER(ctx);
+}  // extern "C"
+
+namespace {
+// Decode attention; with cos_dev / sin_dev also the rotary step and the cache write of the newest position
+// (inside the attention kernels where they support it, as a separate kernel before them otherwise).
+cq_status attention_impl(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim, const float *cos_dev,
+                         const float *sin_dev, const int *pos_dev, float *k_cache_dev, float *v_cache_dev, int max_ctx, float *scratch_dev,
+                         float *out_dev) {
     if (!qkv_dev || !pos_dev || !k_cache_dev || !v_cache_dev || !scratch_dev || !out_dev)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention: null pointer");
     if (batch < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 4 || head_dim > 256 || head_dim % 4 != 0 || max_ctx < 1 || max_ctx > 512 * kAttnChunk)
@@ -763,7 +818,16 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
     const float scale = 1.0f / sqrtf((float)head_dim);
     const int group = n_q_heads / n_kv_heads;
     cq_status s;
-    if (head_dim == 128 && group >= 2 && group <= 8 && ctx->tune.attn_variant != 1) {
+    const bool split_route = head_dim == 128 && group >= 2 && group <= 8 && ctx->tune.attn_variant != 1;
+    const bool gqa_chunk_route = !split_route && head_dim == 128 && group >= 2 && group <= kGqaMaxG;
+    if (cos_dev && gqa_chunk_route) {  // this route has no fused rotary step: run it as its own kernel first
+        const int work = (n_q_heads + n_kv_heads) * head_dim / 2 + n_kv_heads * head_dim;
+        s = launch_pdl(ctx, rope_store_kv_kernel, dim3((unsigned)((work + 255) / 256), (unsigned)batch), dim3(256), qkv_dev, n_q_heads, n_kv_heads,
+                       head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx);
+        if (s != CQ_OK) return s;
+        cos_dev = sin_dev = nullptr;
+    }
+    if (split_route) {
         // splits of the context sized so that about four CTAs per SM exist, never under 64 keys each
         const int64_t pairs = (int64_t)n_kv_heads * batch;
         int64_t want = ((int64_t)ctx->sm_count * 4 + pairs - 1) / pairs;
@@ -787,18 +851,40 @@ cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
-        CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel, qkv_dev, n_q_heads, n_kv_heads, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale,
-                                        scratch_dev, nchunks, keys_per_split));
+        CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel, (const float *)qkv_dev, n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev,
+                                        (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks, keys_per_split, cos_dev, sin_dev,
+                                        k_cache_dev, v_cache_dev));
         s = CQ_OK;
-    } else if (head_dim == 128 && group >= 2 && group <= kGqaMaxG)
-        s = launch_pdl(ctx, attn_partial_gqa_kernel, dim3((unsigned)n_kv_heads, (unsigned)batch, (unsigned)nchunks), dim3(128), qkv_dev, n_q_heads,
-                       n_kv_heads, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
+    } else if (gqa_chunk_route)
+        s = launch_pdl(ctx, attn_partial_gqa_kernel, dim3((unsigned)n_kv_heads, (unsigned)batch, (unsigned)nchunks), dim3(128), (const float *)qkv_dev,
+                       n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev, (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
     else
-        s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads), qkv_dev,
-                       n_q_heads, n_kv_heads, head_dim, pos_dev, k_cache_dev, v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
+        s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads),
+                       (const float *)qkv_dev, n_q_heads, n_kv_heads, head_dim, pos_dev, (const float *)k_cache_dev, (const float *)v_cache_dev, max_ctx,
+                       scale, scratch_dev, nchunks, cos_dev, sin_dev, k_cache_dev, v_cache_dev);
     if (s != CQ_OK) return s;
     return launch_pdl(ctx, attn_combine_kernel, dim3((unsigned)n_q_heads, (unsigned)batch), dim3(128), (const float *)scratch_dev, n_q_heads,
                       head_dim, nchunks, out_dev);
+}
+}  // namespace
+
+extern "C" {
+
+cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim,
+                              const int *pos_dev, const float *k_cache_dev, const float *v_cache_dev, int max_ctx, float *scratch_dev,
+                              float *out_dev) {
+    CQ_ENTER(ctx);
+    return attention_impl(ctx, const_cast<float *>(qkv_dev), batch, n_q_heads, n_kv_heads, head_dim, nullptr, nullptr, pos_dev,
+                          const_cast<float *>(k_cache_dev), const_cast<float *>(v_cache_dev), max_ctx, scratch_dev, out_dev);
+}
+
+cq_status cq_decode_attention_rope(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim, const float *cos_dev,
+                                   const float *sin_dev, const int *pos_dev, float *k_cache_dev, float *v_cache_dev, int max_ctx,
+                                   float *scratch_dev, float *out_dev) {
+    CQ_ENTER(ctx);
+    if (!cos_dev || !sin_dev || head_dim % 2 != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_decode_attention_rope: cos / sin tables and an even head_dim are required");
+    return attention_impl(ctx, qkv_dev, batch, n_q_heads, n_kv_heads, head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx,
+                          scratch_dev, out_dev);
 }
 
 cq_status cq_silu_mul(cq_ctx *ctx, const float *gate_up_dev, int64_t rows, int64_t n, float *out_dev, int64_t ld_out) {

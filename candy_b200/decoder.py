@@ -152,7 +152,7 @@ class QuantDecoder:
         return per_layer * self.cfg.n_layers + (self.wout.buf.nbytes if self.cfg.with_head else 0)
 
     def launches_per_step(self) -> int:
-        per_layer = 7 if self.fuse else 10  # fused: QKV(+norm), rope, attention x2, o, gate-up(+norm, +SiLU*mul), down
+        per_layer = 6 if self.fuse else 10  # fused: QKV(+norm), attention x2 (+rotary step), o, gate-up(+norm, +SiLU*mul), down
         return self.cfg.n_layers * per_layer + ((3 if self.fuse else 5) if self.cfg.with_head else 0)
 
     # ---- one decode step, enqueued on the context's stream -----------------------------------
@@ -194,10 +194,14 @@ class QuantDecoder:
                     self._check(lib.cq_add_rmsnorm(ctx, xc.ptr, self.d.ptr, L["attn_norm"].ptr, B, dim, cfg.eps, self.xn.ptr), "add+rmsnorm")
                 self._linear(L["wqkv"], self.xn, self.qkv)
             first = False
-            self._check(lib.cq_rope_store_kv(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.cos.ptr, self.sin.ptr, self.pos.ptr,
-                                             L["k"].ptr, L["v"].ptr, cfg.max_ctx), "rope")
-            self._check(lib.cq_decode_attention(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.pos.ptr, L["k"].ptr, L["v"].ptr,
-                                                cfg.max_ctx, self.att_scratch.ptr, self.att.ptr), "attention")
+            if self.fuse:  # rotary step and cache write inside the attention kernels
+                self._check(lib.cq_decode_attention_rope(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.cos.ptr, self.sin.ptr, self.pos.ptr,
+                                                         L["k"].ptr, L["v"].ptr, cfg.max_ctx, self.att_scratch.ptr, self.att.ptr), "rope+attention")
+            else:
+                self._check(lib.cq_rope_store_kv(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.cos.ptr, self.sin.ptr, self.pos.ptr,
+                                                 L["k"].ptr, L["v"].ptr, cfg.max_ctx), "rope")
+                self._check(lib.cq_decode_attention(ctx, self.qkv.ptr, B, self.nq, self.nkv, hd, self.pos.ptr, L["k"].ptr, L["v"].ptr,
+                                                    cfg.max_ctx, self.att_scratch.ptr, self.att.ptr), "attention")
             done = False
             if fused:
                 w = L["wo"]

@@ -183,6 +183,13 @@ size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head
 cq_status cq_decode_attention(cq_ctx *ctx, const float *qkv_dev, int64_t batch, int n_q_heads,
                               int n_kv_heads, int head_dim, const int *pos_dev, const float *k_cache_dev,
                               const float *v_cache_dev, int max_ctx, float *scratch_dev, float *out_dev);
+/* cq_rope_store_kv followed by cq_decode_attention, with the rotary step done inside the attention
+ * kernels: q is rotated as it is loaded, the newest key / value (position *pos) are taken from qkv and
+ * stored to the caches by the CTA that consumes them.  qkv is left unrotated unless the shape takes the
+ * route without a fused rotary step (then it is rotated in place, as cq_rope_store_kv does). */
+cq_status cq_decode_attention_rope(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads, int head_dim,
+                                   const float *cos_dev, const float *sin_dev, const int *pos_dev, float *k_cache_dev,
+                                   float *v_cache_dev, int max_ctx, float *scratch_dev, float *out_dev);
 /* out[r * ld_out + i] = silu(gu[r, i]) * gu[r, n + i]: BackendStorage.Silu (USiluF32,
  * unary.go:3353-3365, evaluated in f64) fused with the Mul of a SwiGLU feed-forward.  ld_out >= n
  * lets the result sit in rows padded for the next linear. */

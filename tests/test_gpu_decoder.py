@@ -187,3 +187,43 @@ def test_decoder_fused_and_unfused_agree(device):
         outs.append(np.stack(logits))
         del model
     assert rel_err(outs[0], outs[1]) < 5e-5
+
+
+@pytest.mark.parametrize("batch,nq,nkv,hd,max_ctx,pos", [
+    (1, 8, 8, 128, 96, 40), (2, 16, 2, 128, 300, 257), (3, 8, 4, 128, 64, 0), (2, 6, 3, 64, 80, 79), (1, 8, 8, 128, 64, 31), (2, 16, 2, 128, 128, 63),
+])
+def test_attention_with_fused_rotary_step_equals_the_two_operators(device, batch, nq, nkv, hd, max_ctx, pos):
+    """cq_decode_attention_rope against cq_rope_store_kv + cq_decode_attention: same output, same cache rows."""
+    from candy_b200 import abi
+    lib, ctx = device._lib, device.ctx
+    rng = np.random.default_rng(7 * batch + nq + pos)
+    qkv = rng.standard_normal((batch, (nq + 2 * nkv) * hd), dtype=np.float32)
+    kc = rng.standard_normal((batch, max_ctx, nkv, hd), dtype=np.float32)
+    vc = rng.standard_normal((batch, max_ctx, nkv, hd), dtype=np.float32)
+    ang = rng.uniform(0, 6.28, size=(max_ctx, hd // 2))
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    d_cos, d_sin = device.storage_from_slice(cos), device.storage_from_slice(sin)
+    d_pos = device.upload_bytes(np.array([pos], dtype=np.int32))
+    scratch = device.alloc(lib.cq_decode_attention_scratch_floats(batch, nq, hd, max_ctx))
+    results = []
+    for fused in (False, True):
+        for variant in (0, 1):
+            d_qkv, d_k, d_v = device.storage_from_slice(qkv), device.storage_from_slice(kc), device.storage_from_slice(vc)
+            out = device.alloc(batch * nq * hd)
+            device.set_option("attn_variant", variant)
+            try:
+                if fused:
+                    abi.check(ctx, lib.cq_decode_attention_rope(ctx, d_qkv.ptr, batch, nq, nkv, hd, d_cos.ptr, d_sin.ptr, d_pos.ptr, d_k.ptr, d_v.ptr,
+                                                                max_ctx, scratch.ptr, out.ptr), "rope+attention")
+                else:
+                    abi.check(ctx, lib.cq_rope_store_kv(ctx, d_qkv.ptr, batch, nq, nkv, hd, d_cos.ptr, d_sin.ptr, d_pos.ptr, d_k.ptr, d_v.ptr, max_ctx), "rope")
+                    abi.check(ctx, lib.cq_decode_attention(ctx, d_qkv.ptr, batch, nq, nkv, hd, d_pos.ptr, d_k.ptr, d_v.ptr, max_ctx, scratch.ptr,
+                                                           out.ptr), "attention")
+            finally:
+                device.set_option("attn_variant", 0)
+            results.append((out.data().copy(), d_k.data().reshape(kc.shape)[:, pos].copy(), d_v.data().reshape(vc.shape)[:, pos].copy()))
+    ref = results[0]
+    for got in results[1:]:
+        assert rel_err(got[0], ref[0]) < 2e-6
+        np.testing.assert_allclose(got[1], ref[1], rtol=0, atol=1e-6)
+        np.testing.assert_array_equal(got[2], ref[2])
