@@ -45,7 +45,8 @@ def _worker(rank, world, port, out_dir):
     states = []
     for mode in ("host", "fused"):  # host first: every other kernel is loaded and warm before ranks wait on each other
         model = QuantDecoder(dev, cfg, seed=9, batch=batch, rank=rank, world=world,
-                             allreduce=host_allreduce if mode == "host" else None, comm=comm if mode == "fused" else None)
+                             allreduce=host_allreduce if mode == "host" else None, comm=comm if mode == "fused" else None,
+                             fuse=False)  # separate norm / SiLU kernels in both modes: only the exchange differs
         abi.check(ctx, lib.cq_rand_normal(ctx, model.x.ptr, batch * cfg.dim, 0.0, 1.0, 77), "x")
         model.set_state(np.zeros(batch, dtype=np.uint32), 0)
         for _ in range(3):
