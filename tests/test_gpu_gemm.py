@@ -72,7 +72,7 @@ def test_wide_batches_in_f32_and_q8_1_modes_use_the_decode_kernels(device, actmo
 
 # ---- narrow batches (8 < m <= 128, Q4_0, k % 256 == 0): blocks dequantized into tensor memory ----
 @pytest.mark.parametrize("order", [0, 1])
-@pytest.mark.parametrize("m,n,k", [(9, 128, 256), (16, 300, 512), (17, 129, 768), (32, 1000, 1024), (33, 4096, 4096), (64, 257, 2304),
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (2, 4096, 4096), (8, 11008, 4096), (9, 128, 256), (16, 300, 512), (17, 129, 768), (32, 1000, 1024), (33, 4096, 4096), (64, 257, 2304),
                                    (64, 11008, 4096), (12, 8192, 14336), (100, 300, 512), (128, 1000, 2048), (97, 5000, 4096)])
 def test_narrow_batch_gemm_streams_raw_blocks(device, order, m, n, k):
     w, x = make_case(9000 + m + n + k, n, k, m)
