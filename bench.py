@@ -375,8 +375,8 @@ def run_ours(args):
 
 
 # DRAM bytes (read + write) of one launch of the dominant kernel (n=32000, k=4096) from the ncu
-# capture summarised in profiles/gemv_q4_0_32000x4096.md: 73.79 MB read + 0.96 MB written.
-NCU_TRAFFIC_BYTES = 73787136 + 956160
+# capture summarised in profiles/gemv_q4_0_32000x4096.md: 73.80 MB read + 1.10 MB written.
+NCU_TRAFFIC_BYTES = 73804544 + 1099008
 
 
 def run_reference(args):
