@@ -45,14 +45,15 @@ unsigned *seq_ptr(void *base, int world, size_t max_floats, int set) {
 }
 unsigned *done_ptr(void *base, int world, size_t max_floats, int set) { return seq_ptr(base, world, max_floats, 0) + 2 + set; }
 
-__device__ __forceinline__ uint2 ld_volatile_pair(const uint2 *p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+// two adjacent (value, tag) pairs in one 16-byte load
+__device__ __forceinline__ uint4 ld_volatile_pair2(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
 // One CTA per row.  x[row] += sum over ranks of rx[rank][row]; y[row] = rmsnorm(x[row]) * alpha.
-__global__ void __launch_bounds__(1024) add_rmsnorm_reduce_kernel(float *__restrict__ x, const uint2 *rx, int world, int64_t slot_stride,
+__global__ void __launch_bounds__(512) add_rmsnorm_reduce_kernel(float *__restrict__ x, const uint2 *rx, int world, int64_t slot_stride,
                                                                 unsigned *seq, unsigned *done, const float *__restrict__ alpha, int cols,
                                                                 float eps, float *__restrict__ y, int *err) {
     __shared__ float sh[32];
@@ -64,22 +65,35 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_reduce_kernel(float *__restr
     const uint2 *r0 = rx + (int64_t)blockIdx.x * cols;
     float ss = 0.0f;
     bool timed_out = false;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-        float d = 0.0f;  // partials first, in rank order (identical on every rank), then the residual: what an all-reduce would give
-        for (int r = 0; r < world; ++r) {
-            const uint2 *src = r0 + (int64_t)r * slot_stride + c;
-            uint2 v = ld_volatile_pair(src);
-            // bounded wait for this value (about a second at most, then give up and flag it)
-            for (unsigned it = 0; v.y != tag && it < (1u << 22) && !timed_out; ++it) {
-                if (it >= 32) __nanosleep(it < 1024 ? 100 : 400);
-                v = ld_volatile_pair(src);
+    // Two adjacent columns per trip, and every rank's 16-byte (value, tag, value, tag) load issued before
+    // the first tag is looked at: `world` loads in flight per thread instead of one (a thread that polled
+    // its pairs one after the other paid a memory round trip per pair: 64 of them at 8 ranks, 8192 columns).
+    for (int cp = threadIdx.x; 2 * cp < cols; cp += blockDim.x) {
+        const int c = 2 * cp;
+        float d0 = 0.0f, d1 = 0.0f;  // partials first, in rank order (identical on every rank), then the residual: what an all-reduce would give
+        for (int rb = 0; rb < world; rb += 8) {  // eight ranks' loads in flight at a time
+            uint4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (rb + i < world) v[i] = ld_volatile_pair2(r0 + (int64_t)(rb + i) * slot_stride + c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (rb + i < world) {
+                    // bounded wait for this pair (about a second at most, then give up and flag it)
+                    for (unsigned it = 0; (v[i].y != tag || v[i].w != tag) && it < (1u << 22) && !timed_out; ++it) {
+                        if (it >= 32) __nanosleep(it < 1024 ? 100 : 400);
+                        v[i] = ld_volatile_pair2(r0 + (int64_t)(rb + i) * slot_stride + c);
+                    }
+                    if (v[i].y != tag || v[i].w != tag) timed_out = true;
+                    d0 = (rb + i) == 0 ? __uint_as_float(v[i].x) : d0 + __uint_as_float(v[i].x);
+                    d1 = (rb + i) == 0 ? __uint_as_float(v[i].z) : d1 + __uint_as_float(v[i].z);
+                }
             }
-            if (v.y != tag) timed_out = true;
-            d = r == 0 ? __uint_as_float(v.x) : d + __uint_as_float(v.x);
         }
-        const float v = xr[c] + d;
-        xr[c] = v;
-        ss = fmaf(v, v, ss);
+        const float2 xv = *reinterpret_cast<const float2 *>(xr + c);
+        const float v0 = xv.x + d0, v1 = xv.y + d1;
+        *reinterpret_cast<float2 *>(xr + c) = make_float2(v0, v1);
+        ss = fmaf(v0, v0, fmaf(v1, v1, ss));
     }
     if (timed_out) atomicExch(err, kDevErrFullWait);
     // block sum
@@ -192,8 +206,9 @@ cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *c, int set, float *x_dev, 
     if (!c || (set != 0 && set != 1) || !x_dev || !y_dev || rows < 1 || rows > 8 || cols < 1 || cols > 0x7FFFFFFF)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: bad arguments");
     if ((size_t)(rows * cols) > c->max_floats) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "cq_add_rmsnorm_reduce: rows*cols exceeds the slot size");
+    if ((cols & 1) || (reinterpret_cast<uintptr_t>(x_dev) & 7)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: cols must be even and x 8-byte aligned");
     if (!c->pushed[set]) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: no cq_qmatmul_push was issued into this set");
-    const int threads = cols >= 4096 ? 1024 : (cols >= 1024 ? 512 : 256);
+    const int threads = cols >= 1024 ? 512 : 256;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)rows);
     cfg.blockDim = dim3(threads);
