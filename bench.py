@@ -188,9 +188,16 @@ class Workload:
             dev._check(dev._lib.cq_graph_launch(dev.ctx, g), "graph launch")
 
     def timed(self, fn):
+        """CUDA-event time of fn() on the context's stream, synchronised on both sides.  An untimed
+        filler kernel (a 64 MiB random fill, which also sweeps L2) runs just before the start event, so
+        that the host has enqueued fn()'s launches by the time the GPU reaches the event: the timed region
+        then holds the GPU work only, not the host's launch latency after an idle GPU."""
         dev = self.dev
         ms = C.c_float()
+        if not hasattr(self, "_gate"):
+            self._gate = dev.alloc(16 << 20)
         dev.synchronize()
+        dev._check(dev._lib.cq_rand_uniform(dev.ctx, self._gate.ptr, 16 << 20, 0.0, 1.0, 1), "gate")
         dev._check(dev._lib.cq_timer_start(dev.ctx), "timer start")
         fn()
         dev._check(dev._lib.cq_timer_stop(dev.ctx, C.byref(ms)), "timer stop")
