@@ -562,6 +562,103 @@ struct DecSlices {
     }
 };
 
+// Q8_1 activations, the reference CUDA kernels' numerics (quantized.cu:3521-3558 quantizer, :1919-1941
+// and :2058-2073 dots): the activations arrive already quantized by quantize_q8_1 (36-byte blocks:
+// f16 d, f16 sum of the block's f32 values, 32 int8) and are only permuted here into the order of
+// the weight nibbles; a block contributes d4 * (sumi * d8 - 8 * s8) (Q4_0) or d8_0 * d8_1 * sumi
+// (Q8_0) with an exact integer dot sumi.  Cooperative set-up only (p.x points at the Q8_1 blocks).
+template <int QT, int ORDER>
+struct DecQ81 {
+    static constexpr int kWords = (QT == CQ_Q4_0) ? 9 : 17;
+    static constexpr int kBlkWords = (QT == CQ_Q4_0) ? 4 : 8;
+    static constexpr int kVecs = (QT == CQ_Q4_0) ? 2 : 1;
+    static constexpr bool kCoop = true;
+    static constexpr bool kSplitStage = false;
+    static constexpr int kStateWordsPerBlock = 10;  // 8 packed words, d8, s8
+    int q[2][kBlkWords][kVecs];
+    float d8[2], s8[2];
+
+    __device__ __forceinline__ static void load_quarter(const float *, int, bool, float (&)[8]) {}
+    __device__ __forceinline__ static void stage_quarter_regs(const float (&)[8], int, bool, uint32_t *) {}
+
+    // item = block * 4 + quarter: eight int8 of one Q8_1 block -> two packed words in weight order
+    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) {
+        if (!valid) return;
+        const int blk = item >> 2, qd = item & 3;
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(x) + (size_t)blk * kQ81Bytes);
+        const uint32_t w0 = src[1 + 2 * qd], w1 = src[2 + 2 * qd];  // values 8qd..8qd+3, 8qd+4..8qd+7
+        uint32_t wa, wb;
+        int idxA, idxB;
+        if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) {
+            wa = __byte_perm(w0, w1, 0x6420), wb = __byte_perm(w0, w1, 0x7531);  // low nibbles meet the even values
+            idxA = 2 * qd, idxB = 2 * qd + 1;
+        } else if (QT == CQ_Q4_0) {
+            wa = w0, wb = w1;
+            idxA = (qd < 2) ? 4 * qd : 4 * (qd - 2) + 1, idxB = idxA + 2;
+        } else {
+            wa = w0, wb = w1;
+            idxA = 2 * qd, idxB = 2 * qd + 1;
+        }
+        uint32_t *dst = area + blk * kStateWordsPerBlock;
+        dst[idxA] = wa;
+        dst[idxB] = wb;
+        if (qd == 0) {
+            dst[8] = __float_as_uint(__half2float(__ushort_as_half((unsigned short)(src[0] & 0xFFFFu))));
+            dst[9] = __float_as_uint(__half2float(__ushort_as_half((unsigned short)(src[0] >> 16))));
+        }
+    }
+
+    __device__ __forceinline__ void load(const uint32_t *src) {
+        uint32_t t[2 * kStateWordsPerBlock];
+#pragma unroll
+        for (int i = 0; i < 2 * kStateWordsPerBlock / 4; ++i) {
+            const uint4 v = reinterpret_cast<const uint4 *>(src)[i];
+            t[4 * i] = v.x, t[4 * i + 1] = v.y, t[4 * i + 2] = v.z, t[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[blk][j / kVecs][j % kVecs] = (int)t[blk * kStateWordsPerBlock + j];
+            d8[blk] = __uint_as_float(t[blk * kStateWordsPerBlock + 8]);
+            s8[blk] = __uint_as_float(t[blk * kStateWordsPerBlock + 9]);
+        }
+    }
+
+    __device__ __forceinline__ void init(const float (&)[kXPerThread]) {}  // never used: the planner insists on the cooperative set-up
+
+    __device__ __forceinline__ float pass(const uint32_t *sw) const {
+        uint32_t w[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = sw[i];
+        uint32_t dw[2][kBlkWords];
+#pragma unroll
+        for (int i = 0; i < kBlkWords; ++i) {
+            dw[0][i] = __funnelshift_r(w[i], w[i + 1], 16);
+            dw[1][i] = w[kBlkWords + 1 + i];
+        }
+        const float scale[2] = {__half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu))),
+                                __half2float(__ushort_as_half((unsigned short)(w[kBlkWords] >> 16)))};
+        float total = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            int acc = 0;
+#pragma unroll
+            for (int wi = 0; wi < kBlkWords; ++wi) {
+                if (QT == CQ_Q4_0) {
+                    const int lo = (int)(dw[blk][wi] & 0x0F0F0F0Fu);
+                    const int hi = (int)((dw[blk][wi] >> 4) & 0x0F0F0F0Fu);
+                    acc = __dp4a(hi, q[blk][wi][1], __dp4a(lo, q[blk][wi][0], acc));
+                } else {
+                    acc = __dp4a((int)dw[blk][wi], q[blk][wi][0], acc);
+                }
+            }
+            if (QT == CQ_Q4_0) total += __fmul_rn(scale[blk], __fsub_rn(__fmul_rn((float)acc, d8[blk]), __fmul_rn(8.0f, s8[blk])));
+            else total += __fmul_rn(__fmul_rn(scale[blk], d8[blk]), (float)acc);
+        }
+        return total;
+    }
+};
+
 // MAXT / MINB are launch bounds only: geometries of at most 288 threads are compiled to fit two
 // CTAs per SM, so that under programmatic dependent launch the next GEMV of the stream can be
 // resident (and prefetching its weights) while this one is still computing.
@@ -1144,6 +1241,25 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         if (s != CQ_OK) return s;
         s = launch_quantize_q8_1(ctx, x, m, k, ldx, ctx->scratch);
         if (s != CQ_OK) return s;
+        {   // the streaming kernel with the Q8_1 decoder, when the shape fits it and its cooperative set-up
+            GemvParams p{};
+            int rpt = 1, grid = 0, threads = 0;
+            size_t smem = 0;
+            const float *blocks = static_cast<const float *>(ctx->scratch);
+            if (!ctx->tune.force_simple && ctx->push.world == 0 && !ctx->fuse.on && plan_stream(ctx, QT, w, blocks, n, k, p, rpt, grid, threads, smem) &&
+                p.coop_off >= 0) {
+                p.w = w;
+                p.err = ctx->dev_err_devptr;
+                p.probe = 0;
+                for (int64_t i = 0; i < m; ++i) {
+                    p.x = reinterpret_cast<const float *>(static_cast<const uint8_t *>(ctx->scratch) + (size_t)i * nb * kQ81Bytes);
+                    p.y = y + i * ldy;
+                    s = run_stream<DecQ81<QT, ORDER>>(ctx, p, rpt, grid, threads, smem);
+                    if (s != CQ_OK) return s;
+                }
+                return CQ_OK;
+            }
+        }
         return run_q8_1<QT, ORDER>(ctx, w, static_cast<const uint8_t *>(ctx->scratch), y, m, n, nb, ldy);
     }
     GemvParams p{};

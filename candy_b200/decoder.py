@@ -22,7 +22,7 @@ from typing import Callable, Optional
 import numpy as np
 
 from . import abi
-from .backend import CudaDevice, QStorage, RawBuffer, Q4_0, ORDER_GO_INTERLEAVED, ACT_F32
+from .backend import CudaDevice, QStorage, RawBuffer, Q4_0, ORDER_GO_INTERLEAVED, ACT_F32, ACT_F16
 
 
 @dataclass
@@ -61,14 +61,18 @@ def rope_tables(cfg: DecoderConfig):
 class QuantDecoder:
     def __init__(self, dev: CudaDevice, cfg: DecoderConfig, seed: int = 0, batch: int = 1, qtype: int = Q4_0,
                  order: int = ORDER_GO_INTERLEAVED, rank: int = 0, world: int = 1,
-                 allreduce: Optional[Callable[[object, int], None]] = None, actmode: int = ACT_F32, comm=None, fuse: bool = True):
+                 allreduce: Optional[Callable[[object, int], None]] = None, actmode: Optional[int] = None, comm=None, fuse: bool = True):
         self.dev, self.cfg, self.batch, self.qtype, self.order = dev, cfg, batch, qtype, order
+        # actmode None: f32-activation GEMVs (one weight pass per row) up to two rows, the tensor-core
+        # kernel (f16 activations, one weight pass for the batch) for wider batches without a communicator
+        if actmode is None:
+            actmode = ACT_F32 if (batch <= 2 or comm is not None) else ACT_F16
         self.rank, self.world, self.allreduce, self.actmode = rank, world, allreduce, actmode
         # comm: a connected cq_comm handle -> the two all-reduces of a layer are fused into the GEMV
         # before them and the residual+norm after them (batch <= 8 only); else `allreduce` is called
         self.comm = comm
         # fuse: residual add + RMSNorm ride in the prologue of the QKV / gate-up / output GEMVs and
-        # SiLU(gate)*up in the gate-up GEMV's epilogue (cq_qlinear_fused); batch <= 8, no communicator
+        # SiLU(gate)*up in the gate-up GEMV's epilogue (cq_qlinear_fused); f32 activation mode, batch <= 8, no communicator
         self.fuse = bool(fuse) and comm is None and batch <= 8 and actmode == ACT_F32
         self._pending = [False, False]  # a push into set i awaits its reducing norm
         if world > 1 and allreduce is None and comm is None:

@@ -44,6 +44,31 @@ def test_small_decoder_logits_teacher_forced(device, qtype, order):
     assert agree >= 8  # greedy tokens agree except where the two top logits are within rounding
 
 
+def test_batch_of_four_rows_takes_the_tensor_core_linears(device):
+    """A batch of four sequences: the linears run as one narrow tensor-core launch each (f16
+    activations); every row's logits stay under the 1e-3 bar against its own oracle stream."""
+    from candy_b200.decoder import DecoderConfig, QuantDecoder, rope_tables
+    cfg = DecoderConfig(n_layers=2, dim=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=1000, max_ctx=48)
+    batch = 4
+    model = QuantDecoder(device, cfg, seed=3, batch=batch)
+    assert not model.fuse and model.actmode == 2
+    layers = [{k: L[k].data() for k in ("wqkv", "wo", "wgu", "wdown")} for L in model.layers]
+    cos, sin = rope_tables(cfg)
+    embed = model.embed.data().reshape(cfg.vocab, cfg.dim)
+    refs = [OracleDecoder(cfg, oc.Q4_0, 0, layers, embed=embed, wout=model.wout.data(), cos=cos, sin=sin) for _ in range(batch)]
+    rng = np.random.default_rng(4)
+    tokens = rng.integers(0, cfg.vocab, size=(40, batch))
+    for pos in range(tokens.shape[0]):
+        model.set_state(tokens[pos].astype(np.uint32), pos)
+        model.step()
+        device.synchronize()
+        got = model.read_logits()
+        for b in range(batch):
+            want = refs[b].step(int(tokens[pos, b]), pos)
+            if pos in (0, 1, 5, 33, 39):
+                assert rel_err(got[b], want) <= REL_TOL, f"row {b} position {pos}"
+
+
 def test_greedy_decode_graph_replay_matches_stepwise(device):
     """The captured one-step graph (token id and position on the device) replayed n times gives
     the same token stream as n individual steps."""
