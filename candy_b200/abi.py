@@ -16,10 +16,10 @@ LIB_PATH = Path(os.environ.get("CANDYQ_LIBRARY") or Path(__file__).resolve().par
 
 OK = 0
 ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NOMEM, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
-Q4_0, Q8_0 = 2, 8
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0 = 2, 3, 6, 7, 8
 ORDER_GO_INTERLEAVED, ORDER_GGML_SPLIT = 0, 1
 ACT_F32, ACT_Q8_1, ACT_F16 = 0, 1, 2
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34}
+BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34}
 Q8_1_BYTES = 36
 
 

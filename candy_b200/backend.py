@@ -17,9 +17,9 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import abi
-from .abi import (ACT_F16, ACT_F32, ACT_Q8_1, ORDER_GGML_SPLIT, ORDER_GO_INTERLEAVED, Q4_0, Q8_0, CandyqError)
+from .abi import (ACT_F16, ACT_F32, ACT_Q8_1, ORDER_GGML_SPLIT, ORDER_GO_INTERLEAVED, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, CandyqError)
 
-__all__ = ["CudaDevice", "CudaStorage", "QStorage", "QLinear", "Q4_0", "Q8_0", "ORDER_GO_INTERLEAVED",
+__all__ = ["CudaDevice", "CudaStorage", "QStorage", "QLinear", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "ORDER_GO_INTERLEAVED",
            "ORDER_GGML_SPLIT", "ACT_F32", "ACT_Q8_1", "ACT_F16", "CandyqError"]
 
 

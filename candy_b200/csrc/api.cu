@@ -219,13 +219,17 @@ size_t cq_blocks_bytes(int qtype, int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || k % kQK != 0) return 0;
     if (qtype == CQ_Q4_0) return (size_t)n * (size_t)(k / kQK) * kQ4Bytes;
     if (qtype == CQ_Q8_0) return (size_t)n * (size_t)(k / kQK) * kQ8Bytes;
+    if (cq_is_more_format(qtype)) return (size_t)n * (size_t)(k / kQK) * (size_t)cq_more_block_bytes(qtype);
     return 0;
 }
 
 static cq_status check_qtype_order(cq_ctx *ctx, int qtype, int order) {
-    if (qtype != CQ_Q4_0 && qtype != CQ_Q8_0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "qtype must be CQ_Q4_0 or CQ_Q8_0");
+    if (qtype != CQ_Q4_0 && qtype != CQ_Q8_0 && !cq_is_more_format(qtype))
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "qtype must be CQ_Q4_0, CQ_Q4_1, CQ_Q5_0, CQ_Q5_1 or CQ_Q8_0");
     if (order != CQ_ORDER_GO_INTERLEAVED && order != CQ_ORDER_GGML_SPLIT)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "order must be 0 (interleaved) or 1 (split)");
+    if (cq_is_more_format(qtype) && !cq_more_order_ok(qtype, order))
+        return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "Q5_0 / Q5_1 exist in the split order only");
     return CQ_OK;
 }
 
@@ -236,6 +240,7 @@ cq_status cq_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w_dev
     if (s != CQ_OK) return s;
     if (!w_dev || !blocks_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: null pointer");
     if (n < 1 || k < kQK || k % kQK != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: need n >= 1, k >= 32, k % 32 == 0");
+    if (cq_is_more_format(qtype)) return launch_quantize_rows_more(ctx, qtype, order, w_dev, n * (k / kQK), blocks_dev);
     return launch_quantize_rows(ctx, qtype, order, w_dev, n * (k / kQK), blocks_dev);
 }
 
@@ -246,6 +251,7 @@ cq_status cq_dequantize(cq_ctx *ctx, int qtype, int order, const void *blocks_de
     if (nblocks == 0) return CQ_OK;
     if (!blocks_dev || !y_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_dequantize: null pointer");
     if (nblocks < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_dequantize: negative block count");
+    if (cq_is_more_format(qtype)) return launch_dequantize_more(ctx, qtype, order, blocks_dev, nblocks, y_dev);
     return launch_dequantize(ctx, qtype, order, blocks_dev, nblocks, y_dev);
 }
 

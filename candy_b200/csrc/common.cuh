@@ -106,6 +106,15 @@ cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const floa
                       int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
 cq_status launch_gemv_q8_1_blocks(cq_ctx *ctx, int qtype, int order, const void *act_blocks, int64_t m, int64_t k,
                                   const void *w, int64_t n, float *y, int64_t ldy);
+// Q4_1 / Q5_0 / Q5_1 (more_formats.cu)
+bool cq_is_more_format(int qtype);
+int cq_more_block_bytes(int qtype);
+bool cq_more_order_ok(int qtype, int order);
+cq_status launch_dequantize_more(cq_ctx *ctx, int qtype, int order, const void *blocks, int64_t nblocks, float *y);
+cq_status launch_quantize_rows_more(cq_ctx *ctx, int qtype, int order, const float *w, int64_t nblocks, void *blocks);
+cq_status launch_w_to_f16_more(cq_ctx *ctx, int qtype, int order, const void *blocks, int64_t nblocks, void *out_f16);
+cq_status launch_gemv_more(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w,
+                           int64_t n, float *y, int64_t ldy);
 // Narrow-batch GEMM that dequantizes raw blocks into tensor memory (gemm_dequant_tmem.cu).
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w);
 cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,

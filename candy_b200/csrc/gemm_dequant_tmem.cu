@@ -550,7 +550,7 @@ cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, co
 
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w) {
     // Q8_0 stages are twice as large: no room for the 128-row X slabs next to them
-    return m >= 1 && m <= (qtype == CQ_Q4_0 ? 128 : 64) && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    return (qtype == CQ_Q4_0 || qtype == CQ_Q8_0) && m >= 1 && m <= (qtype == CQ_Q4_0 ? 128 : 64) && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
 }
 
 cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y,

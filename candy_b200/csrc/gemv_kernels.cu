@@ -1303,6 +1303,10 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
 
 cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx,
                       const void *w, int64_t n, float *y, int64_t ldy) {
+    if (cq_is_more_format(qtype)) {
+        if (ctx->fuse.on || ctx->push.world != 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "fused and multi-GPU GEMVs take Q4_0 / Q8_0 only");
+        return launch_gemv_more(ctx, qtype, order, actmode, x, m, k, ldx, w, n, y, ldy);
+    }
     if ((reinterpret_cast<uintptr_t>(w) & 1) != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "weight blocks must be 2-byte aligned");
     if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "x and y must be 4-byte aligned");
@@ -1317,6 +1321,7 @@ cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const floa
 // blocks, m rows of k/32).  Same kernels as the CQ_ACT_Q8_1 branch above.
 cq_status launch_gemv_q8_1_blocks(cq_ctx *ctx, int qtype, int order, const void *act_blocks, int64_t m, int64_t k,
                                   const void *w, int64_t n, float *y, int64_t ldy) {
+    if (cq_is_more_format(qtype)) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "Q8_1 activations take Q4_0 / Q8_0 weights only");
     const uint8_t *wb = static_cast<const uint8_t *>(w);
     const uint8_t *ab = static_cast<const uint8_t *>(act_blocks);
     const int nb = (int)(k / kQK);

@@ -1,4 +1,4 @@
-"""Weight files for the quantized linear: a GGUF tensor reader (F32 / F16 / Q4_0 / Q8_0) and NPZ.
+"""Weight files for the quantized linear: a GGUF tensor reader (F32 / F16 / Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0) and NPZ.
 
 GGUF is the container llama.cpp-family tools write; its Q4_0 / Q8_0 tensors are exactly the block
 streams this library consumes (18 / 34 bytes per 32 values, f16 scale first), with the Q4_0 nibbles
@@ -23,8 +23,8 @@ from typing import Dict, Tuple
 
 import numpy as np
 
-GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q8_0 = 0, 1, 2, 8
-_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34)}  # values per block, bytes per block
+GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q8_0 = 0, 1, 2, 3, 6, 7, 8
+_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q8_0: (32, 34)}  # values, bytes per block
 _ELEM = {GGML_F32: 4, GGML_F16: 2}
 
 # metadata value types of the GGUF specification
@@ -144,12 +144,12 @@ def read_gguf(path) -> Tuple[Dict[str, object], Dict[str, GGUFTensor]]:
 
 
 def load_linear(dev, t: GGUFTensor):
-    """A 2-D Q4_0 / Q8_0 tensor [n, k] as a device QStorage in the GGML split order, bytes unchanged."""
-    from .backend import QStorage, Q4_0, Q8_0, ORDER_GGML_SPLIT
+    """A 2-D Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 tensor [n, k] as a device QStorage in the GGML split order, bytes unchanged."""
+    from .backend import QStorage, ORDER_GGML_SPLIT
     if len(t.shape) != 2 or not t.is_quantized:
-        raise GGUFError(f"{t.name}: expected a 2-D Q4_0 / Q8_0 tensor, got type {t.ggml_type} shape {t.shape}")
+        raise GGUFError(f"{t.name}: expected a 2-D block-quantized tensor, got type {t.ggml_type} shape {t.shape}")
     n, k = t.shape
-    qtype = Q4_0 if t.ggml_type == GGML_Q4_0 else Q8_0
+    qtype = t.ggml_type  # the library's qtype ids are the GGML ids
     return QStorage.from_blocks(dev, qtype, ORDER_GGML_SPLIT, n, k, np.ascontiguousarray(t.data))
 
 

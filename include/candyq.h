@@ -45,7 +45,16 @@ enum {
 typedef struct cq_ctx cq_ctx;
 
 /* Block formats; values follow the GGML type ids the reference's registry names use. */
-enum cq_qtype { CQ_Q4_0 = 2, CQ_Q8_0 = 8 };
+enum cq_qtype {
+    CQ_Q4_0 = 2,
+    CQ_Q4_1 = 3, /* 20 bytes {f16 d; f16 m; u8 qs[16]}: d*q + m         quantized.go:13-17, :107-116        */
+    CQ_Q5_0 = 6, /* 22 bytes {f16 d; u32 qh; u8 qs[16]}: d*(q-16)       quantized.go:19-24, quantized.cu:749-771 */
+    CQ_Q5_1 = 7, /* 24 bytes {f16 d; f16 m; u32 qh; u8 qs[16]}: d*q + m quantized.go:26-31, quantized.cu:773-795 */
+    CQ_Q8_0 = 8
+};
+/* Q4_1 / Q5_0 / Q5_1: dequantize, quantize and matmul with CQ_ACT_F32 (a plain GEMV) or CQ_ACT_F16
+ * (tensor-core GEMM through an f16 copy); CQ_ACT_Q8_1 and the fused / multi-GPU entries answer
+ * CQ_ERR_UNSUPPORTED.  The 5-bit formats exist in the split order only. */
 
 /* Which of the 32 values each Q4_0 nibble is.  The reference disagrees with itself:
  * CQ_ORDER_GO_INTERLEAVED  byte j -> values 2j (low), 2j+1 (high)   quantized.go:87-92

@@ -200,6 +200,150 @@ void co_quantize_q8_0(const float *w, int64_t nblocks, uint8_t *blocks) {
     }
 }
 
+/* ---- Q4_1 / Q5_0 / Q5_1: the other 32-value formats of the reference's registry ------------
+ * Block layouts: tensor/internal/cpu/kernels/quantized.go:13-31.  qtype ids follow GGML:
+ * 3 = Q4_1 (20 bytes), 6 = Q5_0 (22 bytes), 7 = Q5_1 (24 bytes). */
+#define CO_Q4_1_BYTES 20
+#define CO_Q5_0_BYTES 22
+#define CO_Q5_1_BYTES 24
+
+static int64_t co_block_bytes(int qtype) {
+    switch (qtype) {
+    case 2: return CO_Q4_0_BYTES;
+    case 3: return CO_Q4_1_BYTES;
+    case 6: return CO_Q5_0_BYTES;
+    case 7: return CO_Q5_1_BYTES;
+    case 8: return CO_Q8_0_BYTES;
+    default: return 0;
+    }
+}
+
+/* Q4_1 -> f32.  order 0: tensor/internal/cpu/kernels/quantized.go:107-116 (y[2j] = d*lo + m,
+ * y[2j+1] = d*hi + m).  order 1: tensor/internal/cuda/kernels/quantized.cu:728-747 with the
+ * element placement of dequantize_block (y[j], y[j+16]).  d*q is exact, "+ m" rounds once. */
+void co_dequantize_q4_1(const uint8_t *blocks, int64_t nblocks, int order, float *y) {
+    for (int64_t b = 0; b < nblocks; ++b) {
+        const uint8_t *blk = blocks + b * CO_Q4_1_BYTES;
+        float d = co_fp16_to_f32(load_u16(blk));
+        float m = co_fp16_to_f32(load_u16(blk + 2));
+        const uint8_t *qs = blk + 4;
+        float *yb = y + b * CO_QK;
+        for (int j = 0; j < 16; ++j) {
+            float t1 = d * (float)(qs[j] & 0xF);
+            float t2 = d * (float)(qs[j] >> 4);
+            float v1 = t1 + m, v2 = t2 + m;
+            if (order == CO_ORDER_GO_INTERLEAVED) {
+                yb[2 * j] = v1;
+                yb[2 * j + 1] = v2;
+            } else {
+                yb[j] = v1;
+                yb[j + 16] = v2;
+            }
+        }
+    }
+}
+
+/* Q5_0 / Q5_1 -> f32, tensor/internal/cuda/kernels/quantized.cu:749-771 and :773-795: value j
+ * is the low nibble of qs[j] with bit j of qh as its fifth bit, value j+16 the high nibble
+ * with bit j+16.  Q5_0: (q - 16) * d;  Q5_1: q * d + m. */
+void co_dequantize_q5(int qtype, const uint8_t *blocks, int64_t nblocks, float *y) {
+    const int with_min = qtype == 7;
+    const int64_t bb = with_min ? CO_Q5_1_BYTES : CO_Q5_0_BYTES;
+    for (int64_t b = 0; b < nblocks; ++b) {
+        const uint8_t *blk = blocks + b * bb;
+        float d = co_fp16_to_f32(load_u16(blk));
+        float m = with_min ? co_fp16_to_f32(load_u16(blk + 2)) : 0.0f;
+        const uint8_t *qhp = blk + (with_min ? 4 : 2);
+        uint32_t qh = (uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24);
+        const uint8_t *qs = qhp + 4;
+        float *yb = y + b * CO_QK;
+        for (int j = 0; j < 16; ++j) {
+            int q0 = (qs[j] & 0xF) | (int)(((qh >> j) & 1u) << 4);
+            int q1 = (qs[j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+            if (with_min) {
+                float t0 = (float)q0 * d, t1 = (float)q1 * d;
+                yb[j] = t0 + m;
+                yb[j + 16] = t1 + m;
+            } else {
+                yb[j] = ((float)q0 - 16.0f) * d;
+                yb[j + 16] = ((float)q1 - 16.0f) * d;
+            }
+        }
+    }
+}
+
+/* f32 -> Q4_1 / Q5_0 / Q5_1, tensor/internal/metal/kernels/quantized.metal:4216-4280 (Q4_1:
+ * min and max of the block, d = (max - min) / 15, id = d ? 1/d : 0, q = min(15, (int8)((v - min)
+ * * id + 0.5))), :4282-4345 (Q5_0: first element of largest |v| gives max with its sign, d =
+ * max / -16, q = min(31, (int8)(v * id + 16.5))), :4347-4415 (Q5_1: d = (max - min) / 31, q =
+ * (uint8)((v - min) * id + 0.5), no clamp).  d and min are stored rounded to f16; id comes from
+ * the unrounded d.  The shaders pair value j with value j+16 in byte j (split order); for Q4_1
+ * `order` 0 pairs values 2j, 2j+1 instead so that the Go dequantizer returns source order. */
+void co_quantize_more(int qtype, const float *w, int64_t nblocks, int order, uint8_t *blocks) {
+    const int64_t bb = co_block_bytes(qtype);
+    const int interleaved = (qtype == 3 && order == CO_ORDER_GO_INTERLEAVED);
+    for (int64_t b = 0; b < nblocks; ++b) {
+        const float *src = w + b * CO_QK;
+        uint8_t *blk = blocks + b * bb;
+        float d, mn = 0.0f, off;
+        if (qtype == 6) {
+            float amax = 0.0f, max = 0.0f;
+            for (int j = 0; j < CO_QK; ++j)
+                if (amax < fabsf(src[j])) {
+                    amax = fabsf(src[j]);
+                    max = src[j];
+                }
+            d = max / -16.0f;
+            off = 16.5f;
+        } else {
+            float lo = src[0], hi = src[0];
+            for (int j = 1; j < CO_QK; ++j) {
+                lo = src[j] < lo ? src[j] : lo;
+                hi = src[j] > hi ? src[j] : hi;
+            }
+            float range = hi - lo;
+            d = range / (qtype == 3 ? 15.0f : 31.0f);
+            mn = lo;
+            off = 0.5f;
+        }
+        float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+        store_u16(blk, co_f32_to_fp16(d));
+        uint8_t *qs = blk + 2;
+        if (qtype != 6) {
+            store_u16(blk + 2, co_f32_to_fp16(mn));
+            qs += 2;
+        }
+        uint8_t *qhp = qs;
+        if (qtype != 3) qs += 4;
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            int i0 = interleaved ? 2 * j : j, i1 = interleaved ? 2 * j + 1 : j + 16;
+            float s0 = src[i0] - mn, s1 = src[i1] - mn;
+            float x0 = s0 * id, x1 = s1 * id;
+            float r0 = x0 + off, r1 = x1 + off;
+            int q0, q1;
+            if (qtype == 7) {
+                q0 = (int)(uint8_t)(int)r0;
+                q1 = (int)(uint8_t)(int)r1;
+            } else {
+                const int top = qtype == 3 ? 15 : 31;
+                q0 = (int)(int8_t)(int)r0;
+                q1 = (int)(int8_t)(int)r1;
+                q0 = q0 < top ? q0 : top;
+                q1 = q1 < top ? q1 : top;
+                q0 &= 0xFF;
+                q1 &= 0xFF;
+            }
+            qs[j] = (uint8_t)((q0 & 0xF) | ((q1 & 0xF) << 4));
+            qh |= (uint32_t)((q0 >> 4) & 1) << j;
+            qh |= (uint32_t)((q1 >> 4) & 1) << (j + 16);
+        }
+        if (qtype != 3) {
+            qhp[0] = (uint8_t)qh, qhp[1] = (uint8_t)(qh >> 8), qhp[2] = (uint8_t)(qh >> 16), qhp[3] = (uint8_t)(qh >> 24);
+        }
+    }
+}
+
 /* tensor/internal/cpu/kernels/conv.go:373-389 (NaiveBatchedMatMulStridedF32):
  * c[i,j] = sum over l = 0..k-1, in that order, of a*b with the product and the sum
  * each rounded to f32, starting from +0.  Strides are {batch,row,col} in elements. */
@@ -222,6 +366,10 @@ void co_matmul_strided_f32(int64_t bsize, int64_t m, int64_t n, int64_t k, const
 static void dequant_row(int qtype, int order, const uint8_t *row, int64_t nb, float *out) {
     if (qtype == 2)
         co_dequantize_q4_0(row, nb, order, out);
+    else if (qtype == 3)
+        co_dequantize_q4_1(row, nb, order, out);
+    else if (qtype == 6 || qtype == 7)
+        co_dequantize_q5(qtype, row, nb, out);
     else
         co_dequantize_q8_0(row, nb, out);
 }
@@ -231,15 +379,17 @@ static void dequant_row(int qtype, int order, const uint8_t *row, int64_t nb, fl
  * with rhs strides {0,1,K} -- the branch CpuStorage.MatMul takes for a transposed
  * weight view (tensor/internal/cpu/storage.go:892-909) as reached from
  * nn/linear.go:58-112.  Rows of W are dequantized one at a time into a scratch row;
- * the per-element arithmetic and its order are unchanged.  qtype: 2 = Q4_0, 8 = Q8_0.
+ * the per-element arithmetic and its order are unchanged.  qtype: 2 = Q4_0, 8 = Q8_0; 3 / 6 / 7 =
+ * Q4_1 / Q5_0 / Q5_1 follow the same rule (the reference's CPU side holds only their dequantizers).
  * nthreads > 1 splits the rows of W across OpenMP threads (each output element is
  * still one sequential sum, so results do not depend on nthreads). */
 int co_qmatmul(int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx,
                const uint8_t *wblocks, int64_t n, float *y, int64_t ldy, int nthreads) {
     if (k <= 0 || k % CO_QK != 0 || m <= 0 || n <= 0) return -1;
-    if (qtype != 2 && qtype != 8) return -2;
+    if (co_block_bytes(qtype) == 0) return -2;
+    if ((qtype == 6 || qtype == 7) && order != CO_ORDER_GGML_SPLIT) return -3;
     const int64_t nb = k / CO_QK;
-    const int64_t bpb = (qtype == 2) ? CO_Q4_0_BYTES : CO_Q8_0_BYTES;
+    const int64_t bpb = co_block_bytes(qtype);
     if (nthreads < 1) nthreads = 1;
 #pragma omp parallel num_threads(nthreads)
     {

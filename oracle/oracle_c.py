@@ -10,9 +10,9 @@ import numpy as np
 
 from . import build_oracle as _b
 
-Q4_0, Q8_0 = 2, 8
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0 = 2, 3, 6, 7, 8
 ORDER_GO, ORDER_SPLIT = 0, 1
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34}
+BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34}
 Q8_1_BYTES = 36
 
 _lib = None
@@ -32,6 +32,9 @@ def lib():
         _lib.co_quantize_q4_0.argtypes = [p, i64, C.c_int, p]
         _lib.co_quantize_q8_0.argtypes = [p, i64, p]
         _lib.co_quantize_q8_1.argtypes = [p, i64, p]
+        _lib.co_dequantize_q4_1.argtypes = [p, i64, C.c_int, p]
+        _lib.co_dequantize_q5.argtypes = [C.c_int, p, i64, p]
+        _lib.co_quantize_more.argtypes = [C.c_int, p, i64, C.c_int, p]
         _lib.co_matmul_strided_f32.argtypes = [i64, i64, i64, i64, p, p, p, p, p, p]
         for f in (_lib.co_qmatmul, _lib.co_qmatmul_q8_1):
             f.restype = C.c_int
@@ -57,6 +60,11 @@ def dequantize(qtype: int, order: int, blocks: np.ndarray) -> np.ndarray:
     y = np.empty(nb * 32, dtype=np.float32)
     if qtype == Q4_0:
         lib().co_dequantize_q4_0(_ptr(blocks), nb, order, _ptr(y))
+    elif qtype == Q4_1:
+        lib().co_dequantize_q4_1(_ptr(blocks), nb, order, _ptr(y))
+    elif qtype in (Q5_0, Q5_1):
+        assert order == ORDER_SPLIT, "the 5-bit formats exist in the split order only"
+        lib().co_dequantize_q5(qtype, _ptr(blocks), nb, _ptr(y))
     else:
         lib().co_dequantize_q8_0(_ptr(blocks), nb, _ptr(y))
     return y
@@ -69,6 +77,9 @@ def quantize(qtype: int, order: int, w: np.ndarray) -> np.ndarray:
     out = np.empty(nb * BLOCK_BYTES[qtype], dtype=np.uint8)
     if qtype == Q4_0:
         lib().co_quantize_q4_0(_ptr(w), nb, order, _ptr(out))
+    elif qtype in (Q4_1, Q5_0, Q5_1):
+        assert qtype == Q4_1 or order == ORDER_SPLIT, "the 5-bit formats exist in the split order only"
+        lib().co_quantize_more(qtype, _ptr(w), nb, order, _ptr(out))
     else:
         lib().co_quantize_q8_0(_ptr(w), nb, _ptr(out))
     return out

@@ -1,5 +1,5 @@
 """GGUF / NPZ weight files: the from-scratch GGUF reader against files written by the third-party
-`gguf` package (CPU), and a loaded Q4_0 / Q8_0 tensor through the quantized linear on the GPU."""
+`gguf` package (CPU), and a loaded block-quantized tensor through the quantized linear on the GPU."""
 import struct
 
 import numpy as np
@@ -92,7 +92,7 @@ def test_npz_round_trip(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("qname", ["Q4_0", "Q8_0"])
+@pytest.mark.parametrize("qname", ["Q4_0", "Q8_0", "Q4_1", "Q5_0", "Q5_1"])
 def test_gguf_tensor_through_the_quantized_linear(device, tmp_path, qname):
     gguf = pytest.importorskip("gguf")
     from gguf import quants
