@@ -562,6 +562,92 @@ struct DecSlices {
     }
 };
 
+// Q4_1 / Q5_0 / Q5_1 with the 16-bit block fixed point of DecQ16.  The nibble bytes of these formats
+// pair with the activations exactly like Q4_0's, so the activation state (and its cooperative set-up)
+// is DecQ16<CQ_Q4_0, ORDER>'s; only the slice layout and the per-block closing arithmetic differ:
+//   Q4_1, Q5_1:  sum_i (d q_i + m) x_i = d16 * (d * sum q_i X_i + m * sum X_i)
+//   Q5_0:        sum_i d (q_i - 16) x_i = d16 * d * (sum q_i X_i - 16 sum X_i)
+// with sum X_i recovered from DecQ16's Q4_0 bias (-8 sum X_i).  A fifth bit is spread from qh into
+// bit 4 of its byte before the dp4a.  Two consecutive blocks are 40 / 44 / 48 bytes: every field of
+// Q4_1 and Q5_1 is word aligned; Q5_0's first block sits 2 bytes off and is realigned by funnel shifts.
+template <int QT, int ORDER>
+struct DecMore {
+    using Base = DecQ16<CQ_Q4_0, ORDER>;
+    static constexpr int kBlockBytes = QT == CQ_Q4_1 ? 20 : (QT == CQ_Q5_0 ? 22 : 24);
+    static constexpr int kWords = kBlockBytes / 2;  // words of two blocks
+    static constexpr bool kCoop = true;
+    static constexpr bool kSplitStage = true;
+    static constexpr int kStateWordsPerBlock = Base::kStateWordsPerBlock;
+    Base b;
+
+    __device__ __forceinline__ static void load_quarter(const float *x, int item, bool valid, float (&r)[8]) { Base::load_quarter(x, item, valid, r); }
+    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) { Base::stage_quarter(x, item, valid, area); }
+    __device__ __forceinline__ static void stage_quarter_regs(const float (&r)[8], int item, bool valid, uint32_t *area) {
+        Base::stage_quarter_regs(r, item, valid, area);
+    }
+    __device__ __forceinline__ void load(const uint32_t *src) { b.load(src); }
+    __device__ __forceinline__ void init(const float (&x)[kXPerThread]) { b.init(x); }
+
+    // four qh bits -> bit 4 of four bytes
+    __device__ __forceinline__ static uint32_t spread4(uint32_t bits) { return (((bits & 0xFu) * 0x00204081u) & 0x01010101u) << 4; }
+
+    __device__ __forceinline__ float pass(const uint32_t *sw) const {
+        uint32_t w[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = sw[i];
+        uint32_t dw[2][4], qh[2] = {0u, 0u};
+        float d[2], mn[2] = {0.0f, 0.0f};
+        if (QT == CQ_Q4_1) {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                d[blk] = __half2float(__ushort_as_half((unsigned short)(w[5 * blk] & 0xFFFFu)));
+                mn[blk] = __half2float(__ushort_as_half((unsigned short)(w[5 * blk] >> 16)));
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dw[blk][i] = w[5 * blk + 1 + i];
+            }
+        } else if (QT == CQ_Q5_1) {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                d[blk] = __half2float(__ushort_as_half((unsigned short)(w[6 * blk] & 0xFFFFu)));
+                mn[blk] = __half2float(__ushort_as_half((unsigned short)(w[6 * blk] >> 16)));
+                qh[blk] = w[6 * blk + 1];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dw[blk][i] = w[6 * blk + 2 + i];
+            }
+        } else {  // Q5_0: block A at byte 0 (d 0-1, qh 2-5, qs 6-21), block B at byte 22 (d 22-23, qh 24-27, qs 28-43)
+            d[0] = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+            qh[0] = __funnelshift_r(w[0], w[1], 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dw[0][i] = __funnelshift_r(w[1 + i], w[2 + i], 16);
+            d[1] = __half2float(__ushort_as_half((unsigned short)(w[5] >> 16)));
+            qh[1] = w[6];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dw[1][i] = w[7 + i];
+        }
+        float total = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const int xsum = b.bias[blk] / -8;  // exact: the bias is -8 * sum X
+            int ah = 0, al = (QT == CQ_Q5_0) ? -16 * xsum : 0;
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                int lo = (int)(dw[blk][wi] & 0x0F0F0F0Fu);
+                int hi = (int)((dw[blk][wi] >> 4) & 0x0F0F0F0Fu);
+                if (QT != CQ_Q4_1) {
+                    lo |= (int)spread4(qh[blk] >> (4 * wi));
+                    hi |= (int)spread4(qh[blk] >> (16 + 4 * wi));
+                }
+                ah = __dp4a(hi, b.qh[blk][wi][1], __dp4a(lo, b.qh[blk][wi][0], ah));
+                al = Base::dp4a_wu(hi, b.ql[blk][wi][1], Base::dp4a_wu(lo, b.ql[blk][wi][0], al));
+            }
+            const float v = (float)(ah * 256 + al);
+            if (QT == CQ_Q5_0) total = fmaf(d[blk] * b.d16[blk], v, total);
+            else total = fmaf(b.d16[blk], fmaf(d[blk], v, mn[blk] * (float)xsum), total);
+        }
+        return total;
+    }
+};
+
 // Q8_1 activations, the reference CUDA kernels' numerics (quantized.cu:3521-3558 quantizer, :1919-1941
 // and :2058-2073 dots): the activations arrive already quantized by quantize_q8_1 (36-byte blocks:
 // f16 d, f16 sum of the block's f32 values, 32 int8) and are only permuted here into the order of
@@ -1089,7 +1175,7 @@ bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 // kernel (row bytes not a multiple of 16, misaligned pointers, k > 32768, no room for 2 stages).
 bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, int64_t n, int64_t k, GemvParams &p,
                  int &rpt, int &grid, int &threads, size_t &smem) {
-    const int bb = qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
+    const int bb = cq_is_more_format(qtype) ? cq_more_block_bytes(qtype) : (qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes);
     const int64_t nb = k / kQK;
     if (nb % 8 != 0) return false;  // row bytes % 16 == 0 and an even block count
     if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
@@ -1301,10 +1387,38 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
 
 }  // namespace
 
+// Q4_1 / Q5_0 / Q5_1 on the streaming kernel; false when the shape must take the plain kernel.
+template <int QT, int ORDER>
+bool try_stream_more(cq_ctx *ctx, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy, cq_status &s) {
+    GemvParams p{};
+    int rpt = 1, grid = 0, threads = 0;
+    size_t smem = 0;
+    if (ctx->tune.force_simple || (ldx % 4) != 0 || !plan_stream(ctx, QT, w, x, n, k, p, rpt, grid, threads, smem)) return false;
+    p.w = static_cast<const uint8_t *>(w);
+    p.err = ctx->dev_err_devptr;
+    p.probe = 0;
+    s = CQ_OK;
+    for (int64_t i = 0; i < m && s == CQ_OK; ++i) {
+        p.x = x + i * ldx;
+        p.y = y + i * ldy;
+        s = run_stream<DecMore<QT, ORDER>>(ctx, p, rpt, grid, threads, smem);
+    }
+    return true;
+}
+
 cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx,
                       const void *w, int64_t n, float *y, int64_t ldy) {
     if (cq_is_more_format(qtype)) {
         if (ctx->fuse.on || ctx->push.world != 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "fused and multi-GPU GEMVs take Q4_0 / Q8_0 only");
+        if (actmode == CQ_ACT_F32) {
+            cq_status s = CQ_OK;
+            bool taken;
+            if (qtype == CQ_Q4_1 && order == CQ_ORDER_GO_INTERLEAVED) taken = try_stream_more<CQ_Q4_1, 0>(ctx, x, m, k, ldx, w, n, y, ldy, s);
+            else if (qtype == CQ_Q4_1) taken = try_stream_more<CQ_Q4_1, 1>(ctx, x, m, k, ldx, w, n, y, ldy, s);
+            else if (qtype == CQ_Q5_0) taken = try_stream_more<CQ_Q5_0, 1>(ctx, x, m, k, ldx, w, n, y, ldy, s);
+            else taken = try_stream_more<CQ_Q5_1, 1>(ctx, x, m, k, ldx, w, n, y, ldy, s);
+            if (taken) return s;
+        }
         return launch_gemv_more(ctx, qtype, order, actmode, x, m, k, ldx, w, n, y, ldy);
     }
     if ((reinterpret_cast<uintptr_t>(w) & 1) != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "weight blocks must be 2-byte aligned");

@@ -14,9 +14,10 @@
 // rounding and the result does not depend on whether the compiler fuses the two.
 //
 // This file holds everything these formats need: blocks -> f32, f32 -> blocks, blocks -> f16
-// for the tensor-core GEMM, and a decode GEMV with f32 activations.  The GEMV is a plain
-// coalesced kernel (four lanes per block, one row per warp), about 1.0-1.5 TB/s on a B200;
-// it is not the tuned streaming kernel of Q4_0 / Q8_0.
+// for the tensor-core GEMM, and the plain decode GEMV with f32 activations (four lanes per block,
+// one row per warp, about 1.0-1.5 TB/s on a B200) that serves the shapes the streaming kernel
+// does not take (k % 256 != 0, misaligned pointers); the streaming decoder for these formats is
+// DecMore in gemv_kernels.cu.
 #include "common.cuh"
 
 namespace {

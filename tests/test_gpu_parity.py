@@ -308,7 +308,7 @@ def test_argument_errors_come_back_as_status_codes(device):
     assert lib.cq_qmatmul(ctx, 2, 0, 0, p, 1, 48, 48, p, 4, p, 4) == abi.ERR_INVALID_ARG  # k % 32
     assert lib.cq_qmatmul(ctx, 2, 0, 0, p, 1, 64, 32, p, 4, p, 4) == abi.ERR_INVALID_ARG  # ldx < k
     assert lib.cq_qmatmul(ctx, 2, 0, 0, p, 1, 64, 64, p, 4, p, 2) == abi.ERR_INVALID_ARG  # ldy < n
-    assert lib.cq_qmatmul(ctx, 3, 0, 0, p, 1, 64, 64, p, 4, p, 4) == abi.ERR_INVALID_ARG  # qtype
+    assert lib.cq_qmatmul(ctx, 5, 0, 0, p, 1, 64, 64, p, 4, p, 4) == abi.ERR_INVALID_ARG  # qtype (5 is no format of this library)
     assert lib.cq_qmatmul(ctx, 2, 7, 0, p, 1, 64, 64, p, 4, p, 4) == abi.ERR_INVALID_ARG  # order
     assert lib.cq_qmatmul(ctx, 2, 0, 9, p, 1, 64, 64, p, 4, p, 4) == abi.ERR_INVALID_ARG  # actmode
     assert b"ldy" in lib.cq_last_error(ctx) or b"actmode" in lib.cq_last_error(ctx)
