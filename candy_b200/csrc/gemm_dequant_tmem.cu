@@ -549,8 +549,9 @@ cq_status run_ft(cq_ctx *ctx, const CUtensorMap &tmW, const CUtensorMap &tmX, co
 }  // namespace
 
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w) {
-    // Q8_0 stages are twice as large: no room for the 128-row X slabs next to them
-    return (qtype == CQ_Q4_0 || qtype == CQ_Q8_0) && m >= 1 && m <= (qtype == CQ_Q4_0 ? 128 : 64) && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    // Q8_0 stages are twice as large: no room for the 128-row X slabs next to them, so a Q8_0 batch of
+    // 65..128 rows runs as two 64-row passes (the second pass finds the weights in L2)
+    return (qtype == CQ_Q4_0 || qtype == CQ_Q8_0) && m >= 1 && m <= 128 && k % FT_KCHUNK == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
 }
 
 cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y,
@@ -558,6 +559,11 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const flo
     if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 3) != 0)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
     if (n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
+    if (qtype == CQ_Q8_0 && m > 64) {
+        cq_status s = launch_qgemm_dequant_tmem(ctx, qtype, order, x, 64, k, ldx, w, n, y, ldy);
+        if (s != CQ_OK) return s;
+        return launch_qgemm_dequant_tmem(ctx, qtype, order, x + 64 * ldx, m - 64, k, ldx, w, n, y + 64 * ldy, ldy);
+    }
     const int mpad = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
     const int group_rows = FtCfg<CQ_Q4_0, 32>::kGroupRows;
     const int ngroups = (int)((n + group_rows - 1) / group_rows);

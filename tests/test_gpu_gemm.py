@@ -105,7 +105,7 @@ def test_narrow_batch_gemm_edge_scales(device):
 
 
 @pytest.mark.parametrize("m,n,k", [(9, 128, 256), (16, 300, 512), (33, 4096, 4096), (64, 257, 2304), (64, 11008, 4096), (12, 8192, 14336),
-                                   (16, 11008, 4096)])
+                                   (16, 11008, 4096), (65, 300, 512), (100, 1024, 2048), (128, 11008, 4096)])  # > 64 rows: two 64-row passes
 def test_narrow_batch_gemm_q8_0(device, m, n, k):
     w, x = make_case(9100 + m + n + k, n, k, m)
     blocks = oc.quantize(oc.Q8_0, 0, w)
