@@ -104,7 +104,8 @@ def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512
             out.append({"qtype": name, "m": m, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
                         "algorithmic_gbs": round(nbytes / t / 1e9, 1), "bound": "hbm" if t_hbm >= t_tensor else "tensor",
                         "roofline_us": round(max(t_hbm, t_tensor) * 1e6, 2), "frac_of_roofline": round(max(t_hbm, t_tensor) / t, 4),
-                        "path": "raw blocks dequantized into tensor memory" if m <= (128 if qt == 2 else 64) else "f16 copy of W, then f16 tcgen05 GEMM"})
+                        "path": ("raw blocks dequantized into tensor memory" + (" (two 64-row passes)" if qt != 2 and m > 64 else "")) if m <= 128
+                        else "f16 copy of W, then f16 tcgen05 GEMM"})
             del x, y
         del ring, first
     return {"n": n, "k": k, "peak_gbs": peak_gbs, "peak_tflops": peak_tflops, "l2_defeat": "ring of 8 weight copies", "cases": out}
@@ -243,7 +244,7 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
             "tokens_per_s": round(batch / (step_ms * 1e-3), 1), "weight_bytes_per_step_all_ranks": wbytes_all,
             "weight_gbs_all_ranks": round(wbytes_all / (step_ms * 1e-3) / 1e9, 1),
             "frac_of_peak_per_gpu": round(wbytes_all / world / (step_ms * 1e-3) / 1e9 / peak_gbs, 4),
-            "allreduce": "none" if world == 1 else ("fused: peer stores from the GEMV epilogue + counters, summed inside the following residual+RMSNorm kernel"
+            "allreduce": "none" if world == 1 else ("fused: tagged peer stores from the GEMV epilogue, summed inside the following residual+RMSNorm kernel"
                                                     if fused else f"NCCL sum of [{batch},8192] f32, twice per layer"),
             "nccl_ms_per_step": None if nccl_ms is None else round(nccl_ms, 4),
             "linear_mode": "f32 activations (decode GEMV)" if batch <= 8 else (
