@@ -461,6 +461,25 @@ def run_kernel_only(args):
     for kv in args.option:
         key, val = kv.split("=")
         dev.set_option(key, int(val))
+    if args.qtype != 2 or args.actmode != 0:
+        # another block format (3 = Q4_1, 6 = Q5_0, 7 = Q5_1, 8 = Q8_0) or activation mode (1 = Q8_1): same ring idea
+        import numpy as np
+        from candy_b200.backend import QStorage
+        from candy_b200.bench_workloads import RawCopy
+        rng = np.random.default_rng(0)
+        w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+        order = 1 if args.qtype in (6, 7) else 0
+        first = QStorage.quantize(dev, args.qtype, order, w)
+        copies = max(2, (160 << 20) // first.buf.nbytes + 1)
+        ring = [first.buf.ptr] + [RawCopy(dev, first) for _ in range(copies - 1)]
+        x = dev.storage_from_slice(rng.standard_normal((1, k), dtype=np.float32))
+        y = dev.alloc(n)
+        for i in range(args.launches):
+            q = ring[i % copies]
+            dev._check(dev._lib.cq_qmatmul(dev.ctx, args.qtype, order, args.actmode, x.ptr, 1, k, k, q if i % copies == 0 else q.ptr, n, y.ptr, n), "qmatmul")
+        dev.synchronize()
+        print(json.dumps({"kernel_only": [n, k], "qtype": args.qtype, "actmode": args.actmode, "launches": args.launches, "ring_copies": copies}))
+        return
     wl = Workload(dev, [(n, k)], seed=0, ring_bytes=max(2 * nbytes, 160 << 20))
     for _ in range(args.launches):
         wl.launch(0)
@@ -512,6 +531,8 @@ def main():
     ap.add_argument("--gemm-only", default=None, metavar="MxNxK", help="profiling aid: launch the prefill GEMM a few times")
     ap.add_argument("--decode-only", type=int, default=0, metavar="LAYERS", help="profiling aid: a few plain decode steps of a shallow 7B-width model")
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--qtype", type=int, default=2, help="kernel-only mode: block format id (2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0)")
+    ap.add_argument("--actmode", type=int, default=0, help="kernel-only mode: 0 f32 activations, 1 Q8_1 activations")
     ap.add_argument("--option", action="append", default=[], metavar="KEY=INT", help="library tuning option (kernel-only mode)")
     args = ap.parse_args()
     if args.kernel_only:
