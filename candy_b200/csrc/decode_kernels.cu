@@ -349,6 +349,7 @@ constexpr size_t kAttn2Smem = (size_t)kAttn2Keys * kAttn2KStride * 4 + (size_t)k
                               + 8 * 128 * 4                                                          // q
                               + 4 * 8 * kAttn2Keys * 4                                               // score partials [warp][head][key]
                               + kAttn2Keys * 8 * 4 + 64;                                             // numerators [key][head], factors
+template <bool ROPE>
 __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__restrict__ qkv, int nq, int nkv, const int *__restrict__ pos_dev,
                                                            const float *kc, const float *vc, int max_ctx, float scale,
                                                            float *__restrict__ part, int nsplits, int keys_per_split,
@@ -386,7 +387,7 @@ __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__rest
     // q of the group's heads (rotated here when the rotary step is fused in: cos_t given)
     for (int i = tid; i < 8 * hd; i += 128) {
         const float *qh = qkv + (int64_t)b * row + (kvh * G + i / hd) * hd;
-        q_s[i] = (i / hd) < G ? (cos_t ? rope_elem(qh, i % hd, hd, cos_t, sin_t, nkeys - 1) : qh[i % hd]) : 0.0f;
+        q_s[i] = (i / hd) < G ? (ROPE ? rope_elem(qh, i % hd, hd, cos_t, sin_t, nkeys - 1) : qh[i % hd]) : 0.0f;
     }
 
     float m_run[2] = {-3.402823466e38f, -3.402823466e38f}, l_run[2] = {0.0f, 0.0f};  // heads 2*warp, 2*warp+1 (lane-uniform)
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__rest
         for (int j = 0; j < 16; ++j) {
             const int f = tid + 128 * j, r = f >> 5, c4 = f & 31;
             float *d = dst + r * dst_stride + 4 * c4;
-            if (cos_t && r < cnt && t0 + r == nkeys - 1) {
+            if (ROPE && r < cnt && t0 + r == nkeys - 1) {
                 // the newest key is not in the cache yet: rotated k / plain v come from qkv, and this CTA
                 // (the only one of its kv head and sequence that sees this row) stores them to the cache
                 const bool is_k = base == kbase;
@@ -838,7 +839,8 @@ cq_status attention_impl(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_hea
         nchunks = (max_ctx + keys_per_split - 1) / keys_per_split;
         static thread_local int configured = -1;
         if (configured != ctx->device) {
-            CQ_CUDA(ctx, cudaFuncSetAttribute(attn_split_gqa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttn2Smem));
+            CQ_CUDA(ctx, cudaFuncSetAttribute(attn_split_gqa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttn2Smem));
+            CQ_CUDA(ctx, cudaFuncSetAttribute(attn_split_gqa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttn2Smem));
             configured = ctx->device;
         }
         cudaLaunchConfig_t cfg = {};
@@ -851,7 +853,12 @@ cq_status attention_impl(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_hea
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
-        CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel, (const float *)qkv_dev, n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev,
+        if (cos_dev)
+            CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel<true>, (const float *)qkv_dev, n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev,
+                                        (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks, keys_per_split, cos_dev, sin_dev,
+                                        k_cache_dev, v_cache_dev));
+        else
+            CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel<false>, (const float *)qkv_dev, n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev,
                                         (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks, keys_per_split, cos_dev, sin_dev,
                                         k_cache_dev, v_cache_dev));
         s = CQ_OK;
