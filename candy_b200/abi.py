@@ -42,6 +42,8 @@ SIGNATURES = {
     "cq_ctx_destroy": [_vp],
     "cq_ctx_set_stream": [_vp, _vp],
     "cq_ctx_set_option": [_vp, C.c_char_p, _i64],
+    "cq_reserve": [_vp, _sz],
+    "cq_invalidate_weight_cache": [_vp, _vp, _sz],
     "cq_malloc": [_vp, _sz, C.POINTER(_vp)],
     "cq_free": [_vp, _vp],
     "cq_malloc_host": [_vp, _sz, C.POINTER(_vp)],
@@ -55,6 +57,7 @@ SIGNATURES = {
     "cq_dequantize": [_vp, _int, _int, _vp, _i64, _vp],
     "cq_quantize_q8_1": [_vp, _vp, _i64, _i64, _i64, _vp],
     "cq_qmatmul": [_vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
+    "cq_qlinear": [_vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _i64],
     "cq_qmatmul_host": [_vp, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _vp],
     "cq_qmatmul_q8_1_static": [_vp, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64],
     "cq_rand_normal": [_vp, _vp, _i64, C.c_float, C.c_float, C.c_uint64],

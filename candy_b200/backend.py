@@ -231,6 +231,7 @@ class QLinear:
         self.b = None if b is None else np.ascontiguousarray(b, dtype=np.float32)
         if self.b is not None and self.b.shape != (w.n,):
             raise ValueError("linear: bias shape must be [out]")
+        self._b_dev = None if self.b is None else w.device().storage_from_slice(self.b)  # the bias lives on the device
 
     def forward(self, x: np.ndarray) -> np.ndarray:
         x = np.asarray(x, dtype=np.float32)
@@ -242,8 +243,10 @@ class QLinear:
         rows = int(np.prod(bs))
         dev = self.w.device()
         xs = dev.storage_from_slice(np.ascontiguousarray(x).reshape(rows, self.w.k))
-        ys = xs.matmul(self.w, 1, rows, self.w.n, self.w.k, self.actmode)
-        y = ys.data().reshape(*bs, self.w.n)
-        if self.b is not None:
-            y = y + self.b  # BroadcastAdd (nn/linear.go:105-110); bias is a host vector here
-        return y
+        if self._b_dev is None:
+            ys = xs.matmul(self.w, 1, rows, self.w.n, self.w.k, self.actmode)
+        else:  # BroadcastAdd (nn/linear.go:105-110) on the device, in the matmul's epilogue where its kernel has one
+            ys = dev.alloc(rows * self.w.n)
+            dev._check(dev._lib.cq_qlinear(dev.ctx, self.w.qtype, self.w.order, self.actmode, xs.ptr, rows, self.w.k, self.w.k,
+                                           self.w.buf.ptr, self.w.n, self._b_dev.ptr, ys.ptr, self.w.n), "linear")
+        return ys.data().reshape(*bs, self.w.n)

@@ -15,9 +15,15 @@ cq_status cq_cuda_fail(cq_ctx *ctx, cudaError_t e, const char *what) {
 
 cq_status cq_reserve_scratch(cq_ctx *ctx, size_t bytes) {
     if (bytes <= ctx->scratch_bytes) return CQ_OK;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (ctx->capturing || (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone))
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG,
+                       "this call needs " + std::to_string(bytes) + " bytes of context scratch but only " + std::to_string(ctx->scratch_bytes) +
+                           " are reserved, and scratch cannot grow during stream capture: call cq_reserve first, or run the call once before capturing");
     if (ctx->scratch) {
         CQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        CQ_CUDA(ctx, cudaFree(ctx->scratch));
+        if (ctx->graphs_alive > 0) ctx->retired_scratch.push_back(ctx->scratch);  // graphs may still point into it
+        else CQ_CUDA(ctx, cudaFree(ctx->scratch));
         ctx->scratch = nullptr;
         ctx->scratch_bytes = 0;
     }
@@ -25,6 +31,23 @@ cq_status cq_reserve_scratch(cq_ctx *ctx, size_t bytes) {
     CQ_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
     ctx->scratch_bytes = want;
     return CQ_OK;
+}
+
+void cq_w16_invalidate(cq_ctx *ctx, const void *begin, size_t bytes) {
+    if (ctx->w16_cache.empty() || !begin || bytes == 0) return;
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(begin), hi = lo + bytes;
+    bool synced = false;
+    for (auto it = ctx->w16_cache.begin(); it != ctx->w16_cache.end();) {
+        const uintptr_t w = reinterpret_cast<uintptr_t>(std::get<0>(it->first));
+        if (w >= lo && w < hi) {
+            if (!synced) cudaStreamSynchronize(ctx->stream), synced = true;  // a GEMM still reading the copy finishes first
+            cudaFree(it->second);
+            ctx->w16_cache_bytes -= (size_t)std::get<1>(it->first) * (size_t)std::get<2>(it->first) * 2;
+            it = ctx->w16_cache.erase(it);
+        } else {
+            ++it;
+        }
+    }
 }
 
 extern "C" {
@@ -97,6 +120,7 @@ cq_status cq_ctx_destroy(cq_ctx *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (void *p : ctx->retired_scratch) cudaFree(p);
     for (auto &kv : ctx->w16_cache) cudaFree(kv.second);
     if (ctx->xfer_x) cudaFree(ctx->xfer_x);
     if (ctx->xfer_y) cudaFree(ctx->xfer_y);
@@ -126,11 +150,18 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "attn_variant")) t.attn_variant = (int)value;
     else if (!strcmp(key, "gemm_cache_weights")) t.gemm_cache_weights = (int)value;
     else if (!strcmp(key, "gemv_variant")) t.gemv_variant = (int)value;
-    else if (!strcmp(key, "gemv_probe")) t.gemv_probe = (int)value;
+    else if (!strcmp(key, "comm_poll_limit")) t.comm_poll_limit = (int)value;
+    else if (!strcmp(key, "comm_cluster")) t.comm_cluster = (int)value;
+    else if (!strcmp(key, "gemv_multirow")) t.gemv_multirow = (int)value;
     else if (!strcmp(key, "gemv_coop")) t.gemv_coop = (int)value;
     else if (!strcmp(key, "gemv_rpt")) t.gemv_rpt = (int)value;
     else return cq_fail(ctx, CQ_ERR_INVALID_ARG, std::string("unknown option ") + key);
     return CQ_OK;
+}
+
+cq_status cq_reserve(cq_ctx *ctx, size_t bytes) {
+    CQ_ENTER(ctx);
+    return cq_reserve_scratch(ctx, bytes);
 }
 
 cq_status cq_malloc(cq_ctx *ctx, size_t bytes, void **dptr) {
@@ -139,22 +170,24 @@ cq_status cq_malloc(cq_ctx *ctx, size_t bytes, void **dptr) {
     *dptr = nullptr;
     if (bytes == 0) return CQ_OK;
     CQ_CUDA(ctx, cudaMalloc(dptr, bytes));
+    ctx->allocs[*dptr] = bytes;
     return CQ_OK;
 }
 
 cq_status cq_free(cq_ctx *ctx, void *dptr) {
     CQ_ENTER(ctx);
     if (!dptr) return CQ_OK;
-    // a cached f16 copy of weights that lived in this allocation dies with it
-    for (auto it = ctx->w16_cache.begin(); it != ctx->w16_cache.end();) {
-        if (std::get<0>(it->first) == dptr) {
-            cudaFree(it->second);
-            it = ctx->w16_cache.erase(it);
-        } else {
-            ++it;
-        }
-    }
+    // cached f16 copies of weights that lived anywhere in this allocation die with it
+    auto a = ctx->allocs.find(dptr);
+    cq_w16_invalidate(ctx, dptr, a != ctx->allocs.end() ? a->second : 1);
+    if (a != ctx->allocs.end()) ctx->allocs.erase(a);
     CQ_CUDA(ctx, cudaFree(dptr));
+    return CQ_OK;
+}
+
+cq_status cq_invalidate_weight_cache(cq_ctx *ctx, const void *blocks_dev, size_t bytes) {
+    CQ_ENTER(ctx);
+    cq_w16_invalidate(ctx, blocks_dev, bytes);
     return CQ_OK;
 }
 
@@ -177,6 +210,7 @@ cq_status cq_free_host(cq_ctx *ctx, void *hptr) {
 cq_status cq_memset(cq_ctx *ctx, void *dptr, int byte, size_t bytes) {
     CQ_ENTER(ctx);
     if (!dptr && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memset: null pointer");
+    cq_w16_invalidate(ctx, dptr, bytes);
     CQ_CUDA(ctx, cudaMemsetAsync(dptr, byte, bytes, ctx->stream));
     return CQ_OK;
 }
@@ -184,6 +218,7 @@ cq_status cq_memset(cq_ctx *ctx, void *dptr, int byte, size_t bytes) {
 cq_status cq_memcpy_h2d(cq_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
     CQ_ENTER(ctx);
     if ((!dst_dev || !src_host) && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memcpy_h2d: null pointer");
+    cq_w16_invalidate(ctx, dst_dev, bytes);
     CQ_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
     CQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return CQ_OK;
@@ -200,6 +235,7 @@ cq_status cq_memcpy_d2h(cq_ctx *ctx, void *dst_host, const void *src_dev, size_t
 cq_status cq_memcpy_d2d(cq_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes) {
     CQ_ENTER(ctx);
     if ((!dst_dev || !src_dev) && bytes) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_memcpy_d2d: null pointer");
+    cq_w16_invalidate(ctx, dst_dev, bytes);
     CQ_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_dev, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return CQ_OK;
 }
@@ -210,6 +246,8 @@ cq_status cq_synchronize(cq_ctx *ctx) {
     int e = *(volatile int *)ctx->dev_err;
     if (e != 0) {
         *ctx->dev_err = 0;
+        if (e == kDevErrPosition)
+            return cq_fail(ctx, CQ_ERR_INVALID_ARG, "a decode kernel found its device-resident position outside [0, max_ctx): it was clamped, the step's results are invalid");
         return cq_fail(ctx, CQ_ERR_TIMEOUT, "a kernel's bounded wait gave up (device error word " + std::to_string(e) + ")");
     }
     return CQ_OK;
@@ -240,6 +278,7 @@ cq_status cq_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w_dev
     if (s != CQ_OK) return s;
     if (!w_dev || !blocks_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: null pointer");
     if (n < 1 || k < kQK || k % kQK != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: need n >= 1, k >= 32, k % 32 == 0");
+    cq_w16_invalidate(ctx, blocks_dev, cq_blocks_bytes(qtype, n, k));
     if (cq_is_more_format(qtype)) return launch_quantize_rows_more(ctx, qtype, order, w_dev, n * (k / kQK), blocks_dev);
     return launch_quantize_rows(ctx, qtype, order, w_dev, n * (k / kQK), blocks_dev);
 }
@@ -286,6 +325,32 @@ cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float
     if (s != CQ_OK) return s;
     if (m <= 8 && actmode != CQ_ACT_F16) return launch_gemv(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
     return launch_gemm(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
+}
+
+// y[r, c] += bias[c] for the routes whose kernels have no bias epilogue (plain GEMV, tensor-core GEMMs).
+__global__ void __launch_bounds__(256) add_bias_kernel(float *__restrict__ y, const float *__restrict__ bias, int64_t rows, int64_t n, int64_t ldy) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / n, c = i - r * n;
+        y[r * ldy + c] += bias[c];
+    }
+}
+
+cq_status cq_qlinear(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev, int64_t m, int64_t k, int64_t ldx,
+                     const void *w_blocks_dev, int64_t n, const float *bias_dev, float *y_dev, int64_t ldy) {
+    CQ_ENTER(ctx);
+    ctx->bias = bias_dev;
+    ctx->bias_done = false;
+    cq_status s = cq_qmatmul(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
+    const bool done = ctx->bias_done;
+    ctx->bias = nullptr;
+    ctx->bias_done = false;
+    if (s != CQ_OK || !bias_dev || done) return s;
+    const int64_t total = m * n;
+    const unsigned cap = (unsigned)ctx->sm_count * 8;
+    const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+    add_bias_kernel<<<grid, 256, 0, ctx->stream>>>(y_dev, bias_dev, m, n, ldy);
+    CQ_CUDA(ctx, cudaGetLastError());
+    return CQ_OK;
 }
 
 cq_status cq_qlinear_fused(cq_ctx *ctx, int qtype, int order, const float *x_dev, const float *delta_dev, const float *alpha_dev, float eps,
@@ -365,6 +430,7 @@ cq_status cq_capture_end(cq_ctx *ctx, cq_graph **out) {
         return cq_cuda_fail(ctx, e, "graph capture/instantiate");
     }
     *out = g;
+    ++ctx->graphs_alive;
     return CQ_OK;
 }
 
@@ -381,6 +447,12 @@ cq_status cq_graph_destroy(cq_ctx *ctx, cq_graph *g) {
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
     delete g;
+    if (--ctx->graphs_alive <= 0) {  // nothing references the outgrown scratch blocks any more
+        ctx->graphs_alive = 0;
+        cudaStreamSynchronize(ctx->stream);
+        for (void *p : ctx->retired_scratch) cudaFree(p);
+        ctx->retired_scratch.clear();
+    }
     return CQ_OK;
 }
 

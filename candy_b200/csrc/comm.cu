@@ -8,7 +8,8 @@
 //                                  one this exchange carries, sums the world partials in rank order,
 //                                  adds the sum to the residual, applies RMSNorm, and advances the tag.
 //
-// Value and tag arrive together (an aligned 8-byte store is single-copy atomic), so the data is
+// Value and tag travel as ONE 64-bit element (st.relaxed.sys.b64 / ld.relaxed.sys.v2.b64: each 64-bit
+// element is single-copy atomic; a .v2.u32 access would be two 32-bit elements in no stated order), so the data is
 // usable one NVLink hop after it was produced: no fence, no separate flag, no extra kernel, no
 // NCCL call, nothing loaded from a peer.  The tag is a per-set counter kept in each rank's own
 // memory and advanced by the consumer, so a captured CUDA graph replays correctly.
@@ -18,9 +19,13 @@
 // itself.  One process per GPU; peers are mapped with CUDA IPC handles that the host exchanges
 // through whatever transport it has (torch.distributed object gather in the benchmark).
 // The reference has no multi-device code at all; nothing here has a counterpart in it.
+#include <cooperative_groups.h>
+
 #include <vector>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 constexpr int kMaxWorld = 16;
 
@@ -31,7 +36,8 @@ struct cq_comm {
     void *peer_base[kMaxWorld] = {};
     bool opened[kMaxWorld] = {};
     uint2 **d_push_rx[2] = {};      // device arrays [world]: my slot on each rank, per set
-    bool pushed[2] = {false, false};
+    bool pushed[2] = {false, false};  // a push into the set awaits its reducing norm
+    bool loopback = false;            // single-process stand-in: every "peer" is this rank's own buffer
 };
 
 namespace {
@@ -45,48 +51,55 @@ unsigned *seq_ptr(void *base, int world, size_t max_floats, int set) {
 }
 unsigned *done_ptr(void *base, int world, size_t max_floats, int set) { return seq_ptr(base, world, max_floats, 0) + 2 + set; }
 
-// two adjacent (value, tag) pairs in one 16-byte load
-__device__ __forceinline__ uint4 ld_volatile_pair2(const uint2 *p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+// two adjacent (value, tag) pairs in one 16-byte load; each pair is one 64-bit element (tag in the high half)
+__device__ __forceinline__ void ld_pair2(const uint2 *p, unsigned long long &a, unsigned long long &b) {
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
+__device__ __forceinline__ unsigned tag_of(unsigned long long v) { return (unsigned)(v >> 32); }
+__device__ __forceinline__ float val_of(unsigned long long v) { return __uint_as_float((unsigned)v); }
 
-// One CTA per row.  x[row] += sum over ranks of rx[rank][row]; y[row] = rmsnorm(x[row]) * alpha.
+// x[row] += sum over ranks of rx[rank][row]; y[row] = rmsnorm(x[row]) * alpha.
+// A row is shared by the CTAs of one thread-block cluster (1 or 8): each CTA polls, sums and stores its
+// slice of the columns, the sums of squares meet through distributed shared memory across one hardware
+// cluster barrier, and each CTA normalises its own slice.  With eight CTAs a thread of an 8192-column row
+// has one column pair and `world` 16-byte loads in flight at once: a single memory round trip.
 __global__ void __launch_bounds__(512) add_rmsnorm_reduce_kernel(float *__restrict__ x, const uint2 *rx, int world, int64_t slot_stride,
                                                                 unsigned *seq, unsigned *done, const float *__restrict__ alpha, int cols,
-                                                                float eps, float *__restrict__ y, int *err) {
+                                                                float eps, float *__restrict__ y, int *err, unsigned poll_limit) {
     __shared__ float sh[32];
+    __shared__ float cta_ss;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int row = blockIdx.x / csize;
     pdl_launch_dependents();
     pdl_wait_prior();
     const unsigned tag = *seq + 1u;  // advanced only after every CTA of this grid has read it (below)
-    float *xr = x + (int64_t)blockIdx.x * cols;
-    float *yr = y + (int64_t)blockIdx.x * cols;
-    const uint2 *r0 = rx + (int64_t)blockIdx.x * cols;
+    float *xr = x + (int64_t)row * cols;
+    float *yr = y + (int64_t)row * cols;
+    const uint2 *r0 = rx + (int64_t)row * cols;
+    const int slice = cols / csize, c_begin = crank * slice, c_end = c_begin + slice;  // slice is even (host checks)
     float ss = 0.0f;
     bool timed_out = false;
     // Two adjacent columns per trip, and every rank's 16-byte (value, tag, value, tag) load issued before
-    // the first tag is looked at: `world` loads in flight per thread instead of one (a thread that polled
-    // its pairs one after the other paid a memory round trip per pair: 64 of them at 8 ranks, 8192 columns).
-    for (int cp = threadIdx.x; 2 * cp < cols; cp += blockDim.x) {
-        const int c = 2 * cp;
+    // the first tag is looked at: `world` loads in flight per thread instead of one.
+    for (int c = c_begin + 2 * threadIdx.x; c < c_end; c += 2 * blockDim.x) {
         float d0 = 0.0f, d1 = 0.0f;  // partials first, in rank order (identical on every rank), then the residual: what an all-reduce would give
         for (int rb = 0; rb < world; rb += 8) {  // eight ranks' loads in flight at a time
-            uint4 v[8];
+            unsigned long long va[8], vb[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                if (rb + i < world) v[i] = ld_volatile_pair2(r0 + (int64_t)(rb + i) * slot_stride + c);
+                if (rb + i < world) ld_pair2(r0 + (int64_t)(rb + i) * slot_stride + c, va[i], vb[i]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 if (rb + i < world) {
-                    // bounded wait for this pair (about a second at most, then give up and flag it)
-                    for (unsigned it = 0; (v[i].y != tag || v[i].w != tag) && it < (1u << 22) && !timed_out; ++it) {
+                    // bounded wait for this pair, then give up and flag it
+                    for (unsigned it = 0; (tag_of(va[i]) != tag || tag_of(vb[i]) != tag) && it < poll_limit && !timed_out; ++it) {
                         if (it >= 32) __nanosleep(it < 1024 ? 100 : 400);
-                        v[i] = ld_volatile_pair2(r0 + (int64_t)(rb + i) * slot_stride + c);
+                        ld_pair2(r0 + (int64_t)(rb + i) * slot_stride + c, va[i], vb[i]);
                     }
-                    if (v[i].y != tag || v[i].w != tag) timed_out = true;
-                    d0 = (rb + i) == 0 ? __uint_as_float(v[i].x) : d0 + __uint_as_float(v[i].x);
-                    d1 = (rb + i) == 0 ? __uint_as_float(v[i].z) : d1 + __uint_as_float(v[i].z);
+                    if (tag_of(va[i]) != tag || tag_of(vb[i]) != tag) timed_out = true;
+                    d0 = (rb + i) == 0 ? val_of(va[i]) : d0 + val_of(va[i]);
+                    d1 = (rb + i) == 0 ? val_of(vb[i]) : d1 + val_of(vb[i]);
                 }
             }
         }
@@ -96,7 +109,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_reduce_kernel(float *__restri
         ss = fmaf(v0, v0, fmaf(v1, v1, ss));
     }
     if (timed_out) atomicExch(err, kDevErrFullWait);
-    // block sum
+    // CTA sum, then the cluster's sum in CTA-rank order (the same order, hence the same bits, on every rank)
     {
         const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
 #pragma unroll
@@ -106,10 +119,15 @@ __global__ void __launch_bounds__(512) add_rmsnorm_reduce_kernel(float *__restri
         ss = (lane < nw) ? sh[lane] : 0.0f;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, 32);
+        if (threadIdx.x == 0) cta_ss = ss;
     }
-    const float scale = 1.0f / sqrtf(ss / (float)cols + eps);
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) yr[c] = alpha ? scale * xr[c] * alpha[c] : scale * xr[c];
-    // the last row's CTA advances the tag for the next use of this set
+    cluster.sync();
+    float tot = 0.0f;
+    for (int r = 0; r < csize; ++r) tot += *cluster.map_shared_rank(&cta_ss, r);
+    cluster.sync();  // nobody leaves while a neighbour may still read its shared memory
+    const float scale = 1.0f / sqrtf(tot / (float)cols + eps);
+    for (int c = c_begin + threadIdx.x; c < c_end; c += blockDim.x) yr[c] = alpha ? scale * xr[c] * alpha[c] : scale * xr[c];
+    // the last CTA of the grid advances the tag for the next use of this set
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -148,10 +166,12 @@ cq_status cq_comm_create(cq_ctx *ctx, int rank, int world, int64_t max_floats, c
 // all_handles: world x 64 bytes, rank order (this rank's own entry is ignored).
 cq_status cq_comm_connect(cq_ctx *ctx, cq_comm *c, const void *all_handles) {
     CQ_ENTER(ctx);
-    if (!c || !all_handles) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_comm_connect: null pointer");
+    if (!c) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_comm_connect: null pointer");
+    if (c->d_push_rx[0]) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_comm_connect: already connected");
     const cudaIpcMemHandle_t *h = reinterpret_cast<const cudaIpcMemHandle_t *>(all_handles);
+    c->loopback = all_handles == nullptr;
     for (int r = 0; r < c->world; ++r) {
-        if (r == c->rank) {
+        if (r == c->rank || c->loopback) {
             c->peer_base[r] = c->local;
             continue;
         }
@@ -190,6 +210,9 @@ cq_status cq_qmatmul_push(cq_ctx *ctx, cq_comm *c, int set, int qtype, int order
     if (m < 1 || m > 8 || n < 1 || k < kQK || k % kQK != 0 || ldx < k)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul_push: need 1 <= m <= 8, k % 32 == 0, ldx >= k");
     if ((size_t)(m * n) > c->max_floats) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "cq_qmatmul_push: m*n exceeds the communicator's slot size");
+    if (!c->d_push_rx[set]) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul_push: communicator is not connected");
+    if (c->pushed[set])
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul_push: this set already holds a push that no cq_add_rmsnorm_reduce has consumed (it would reuse the tag and overwrite data peers may still read)");
     ctx->push.rx = c->d_push_rx[set];
     ctx->push.seq = seq_ptr(c->local, c->world, c->max_floats, set);
     ctx->push.world = c->world;
@@ -208,20 +231,27 @@ cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *c, int set, float *x_dev, 
     if ((size_t)(rows * cols) > c->max_floats) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "cq_add_rmsnorm_reduce: rows*cols exceeds the slot size");
     if ((cols & 1) || (reinterpret_cast<uintptr_t>(x_dev) & 7)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: cols must be even and x 8-byte aligned");
     if (!c->pushed[set]) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_add_rmsnorm_reduce: no cq_qmatmul_push was issued into this set");
-    const int threads = cols >= 1024 ? 512 : 256;
+    c->pushed[set] = false;
+    // eight CTAs (one cluster) per row when the row is long enough to share out in even slices
+    const int csize = (cols >= 2048 && cols % 16 == 0 && ctx->tune.comm_cluster != 1) ? 8 : 1;
+    const int slice = (int)cols / csize;
+    const int threads = slice >= 1024 ? 512 : 256;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)rows);
+    cfg.gridDim = dim3((unsigned)(rows * csize));
     cfg.blockDim = dim3(threads);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    cfg.numAttrs = ctx->tune.pdl ? 2 : 1;
     const uint2 *rx = slot_ptr(c->local, c->world, c->max_floats, set, 0);
+    const unsigned poll_limit = ctx->tune.comm_poll_limit > 0 ? (unsigned)ctx->tune.comm_poll_limit : (1u << 22);
     CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, add_rmsnorm_reduce_kernel, x_dev, rx, c->world, (int64_t)c->max_floats,
                                     seq_ptr(c->local, c->world, c->max_floats, set), done_ptr(c->local, c->world, c->max_floats, set), alpha_dev,
-                                    (int)cols, eps, y_dev, ctx->dev_err_devptr));
+                                    (int)cols, eps, y_dev, ctx->dev_err_devptr, poll_limit));
     return CQ_OK;
 }
 

@@ -8,6 +8,7 @@
 #include <map>
 #include <string>
 #include <tuple>
+#include <vector>
 
 #include "candyq.h"
 
@@ -17,7 +18,9 @@ constexpr int kQ8Bytes = 34;    // f16 d + 32 int8
 constexpr int kQ81Bytes = 36;   // f16 d + f16 sum + 32 int8
 
 // Device-side error word codes (written by kernels whose bounded waits gave up).
-enum : int { kDevErrNone = 0, kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErrDrain = 3, kDevErrMma = 4 };
+// 1..4: a bounded wait gave up (CQ_ERR_TIMEOUT at cq_synchronize); 5: a device-resident decode position
+// was outside [0, max_ctx) (CQ_ERR_INVALID_ARG at cq_synchronize).
+enum : int { kDevErrNone = 0, kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErrDrain = 3, kDevErrMma = 4, kDevErrPosition = 5 };
 
 struct GemvTuning {
     int target_warps = 8;   // consumer warps per CTA the launcher aims for
@@ -30,7 +33,9 @@ struct GemvTuning {
     int gemm_cache_weights = 0;  // keep the f16 copy of every weight matrix the GEMM has seen (4x the Q4_0 bytes)
     int gemv_rpt = 2;       // rows per thread and pass in the streaming kernel (1 or 2)
     int gemv_coop = 1;      // slice activations once per CTA through shared memory when rows share a CTA
-    int gemv_probe = 0;     // profiling aid, see GemvParams::probe (results are wrong when non-zero)
+    int comm_poll_limit = 0;  // polls before the reducing norm gives up on a (value, tag) pair; 0 = about a second
+    int comm_cluster = 0;     // 1: one CTA per row in the reducing norm instead of a cluster of eight
+    int gemv_multirow = 1;  // 0: one launch (one weight pass) per activation row even for m = 2..8
     int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices
 };
 
@@ -65,6 +70,8 @@ struct cq_ctx {
     int *dev_err_devptr = nullptr;
     void *scratch = nullptr;      // activation staging (Q8_1 blocks / f16 copies)
     size_t scratch_bytes = 0;
+    std::vector<void *> retired_scratch;  // outgrown blocks that instantiated graphs may still reference
+    int graphs_alive = 0;                 // graphs made by cq_capture_end and not yet destroyed
     void *xfer_x = nullptr;       // device staging used by cq_qmatmul_host
     void *xfer_y = nullptr;
     size_t xfer_x_bytes = 0, xfer_y_bytes = 0;
@@ -72,9 +79,12 @@ struct cq_ctx {
     // key = (blocks pointer, n, k, qtype * 2 + order) -> device allocation of n*k halfs.
     std::map<std::tuple<const void *, int64_t, int64_t, int>, void *> w16_cache;
     size_t w16_cache_bytes = 0;
+    std::map<const void *, size_t> allocs;  // cq_malloc'ed blocks -> bytes (so cq_free can drop cached copies of weights inside them)
     GemvTuning tune;
     PushSpec push;
     FuseSpec fuse;
+    const float *bias = nullptr;  // set by cq_qlinear around one matmul: the streaming GEMV adds it in its epilogue
+    bool bias_done = false;       // ... and says so here; other routes leave it to a small kernel afterwards
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
     bool capturing = false;
     std::string last_error;
@@ -82,8 +92,13 @@ struct cq_ctx {
 
 cq_status cq_fail(cq_ctx *ctx, cq_status s, const std::string &msg);
 cq_status cq_cuda_fail(cq_ctx *ctx, cudaError_t e, const char *what);
-// Grows ctx->scratch to at least `bytes` (never shrinks).
+// Grows ctx->scratch to at least `bytes` (never shrinks).  Refused while the stream is capturing (growth
+// would allocate and synchronise inside the capture); a block outgrown while graphs exist is kept until
+// the last graph is destroyed, because their kernel parameters and tensor maps point into it.
 cq_status cq_reserve_scratch(cq_ctx *ctx, size_t bytes);
+
+// Drops the cached f16 copies of every weight matrix whose blocks start inside [begin, begin + bytes).
+void cq_w16_invalidate(cq_ctx *ctx, const void *begin, size_t bytes);
 
 #define CQ_CUDA(ctx, call)                                              \
     do {                                                                \

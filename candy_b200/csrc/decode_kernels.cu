@@ -64,16 +64,29 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float *__restrict__ x, co
     }
 }
 
+// The decode position lives on the device (it is advanced inside captured graphs), so the host cannot
+// validate it: every kernel that indexes a cache or a rotary table with it goes through here.  A position
+// outside [0, max_ctx) is recorded in the context's error word (reported by cq_synchronize) and clamped,
+// so that no access ever leaves the caches or the tables; the step's results are then meaningless.
+__device__ __forceinline__ int checked_pos(const int *pos_dev, int max_ctx, int *err) {
+    const int pos = *pos_dev;
+    if (pos < 0 || pos >= max_ctx) {
+        if (threadIdx.x == 0) atomicExch(err, kDevErrPosition);
+        return pos < 0 ? 0 : max_ctx - 1;
+    }
+    return pos;
+}
+
 // qkv: [B, (nq + 2 nkv) * hd].  Rotates q in place and k (half-split pairs), then stores k and v
 // of every sequence at position *pos of its cache [B][max_ctx][nkv*hd].
 __global__ void __launch_bounds__(256) rope_store_kv_kernel(float *__restrict__ qkv, int nq, int nkv, int hd,
                                                           const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                                           const int *__restrict__ pos_dev, float *__restrict__ kc,
-                                                          float *__restrict__ vc, int max_ctx) {
+                                                          float *__restrict__ vc, int max_ctx, int *err) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const int b = blockIdx.y;
-    const int pos = *pos_dev;
+    const int pos = checked_pos(pos_dev, max_ctx, err);
     const int half = hd / 2;
     const int row = (nq + 2 * nkv) * hd;
     float *base = qkv + (int64_t)b * row;
@@ -127,12 +140,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
                                                                   const int *__restrict__ pos_dev, const float *kc,
                                                                   const float *vc, int max_ctx, float scale,
                                                                   float *__restrict__ part, int nchunks, const float *__restrict__ cos_t,
-                                                                  const float *__restrict__ sin_t, float *kc_w, float *vc_w) {
+                                                                  const float *__restrict__ sin_t, float *kc_w, float *vc_w, int *err) {
     __shared__ float p_s[kAttnChunk];
     pdl_launch_dependents();
     pdl_wait_prior();
     const int head = blockIdx.x, b = blockIdx.y, chunk = blockIdx.z;
-    const int nkeys = *pos_dev + 1;
+    const int nkeys = checked_pos(pos_dev, max_ctx, err) + 1;
     const int t0 = chunk * kAttnChunk;
     float *out = part + (((int64_t)b * nq + head) * nchunks + chunk) * (hd + 2);
     if (t0 >= nkeys) {  // chunk beyond the current length: neutral element
@@ -254,7 +267,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
 constexpr int kGqaMaxG = 8;
 __global__ void __launch_bounds__(128) attn_partial_gqa_kernel(const float *__restrict__ qkv, int nq, int nkv, const int *__restrict__ pos_dev,
                                                              const float *__restrict__ kc, const float *__restrict__ vc, int max_ctx,
-                                                             float scale, float *__restrict__ part, int nchunks) {
+                                                             float scale, float *__restrict__ part, int nchunks, int *err) {
     constexpr int hd = 128;
     __shared__ float kt_s[hd][kAttnChunk + 1];       // K transposed, padded
     __shared__ float v_s[kAttnChunk][hd];
@@ -264,7 +277,7 @@ __global__ void __launch_bounds__(128) attn_partial_gqa_kernel(const float *__re
     pdl_wait_prior();
     const int kvh = blockIdx.x, b = blockIdx.y, chunk = blockIdx.z;
     const int G = nq / nkv;
-    const int nkeys = *pos_dev + 1;
+    const int nkeys = checked_pos(pos_dev, max_ctx, err) + 1;
     const int t0 = chunk * kAttnChunk;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (t0 >= nkeys) {
@@ -354,7 +367,7 @@ __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__rest
                                                            const float *kc, const float *vc, int max_ctx, float scale,
                                                            float *__restrict__ part, int nsplits, int keys_per_split,
                                                            const float *__restrict__ cos_t, const float *__restrict__ sin_t, float *kc_w,
-                                                           float *vc_w) {
+                                                           float *vc_w, int *err) {
     constexpr int hd = 128;
     extern __shared__ __align__(16) uint8_t attn_smem[];
     float *Ks = reinterpret_cast<float *>(attn_smem);
@@ -368,7 +381,7 @@ __global__ void __launch_bounds__(128) attn_split_gqa_kernel(const float *__rest
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int G = nq / nkv;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nkeys = *pos_dev + 1;
+    const int nkeys = checked_pos(pos_dev, max_ctx, err) + 1;
     const int t_begin = split * keys_per_split;
     const int t_end = min(t_begin + keys_per_split, nkeys);
     const int stride = hd + 2;
@@ -795,7 +808,7 @@ cq_status cq_rope_store_kv(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_h
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rope_store_kv: bad shape");
     const int work = (n_q_heads + n_kv_heads) * head_dim / 2 + n_kv_heads * head_dim;
     return launch_pdl(ctx, rope_store_kv_kernel, dim3((unsigned)((work + 255) / 256), (unsigned)batch), dim3(256), qkv_dev, n_q_heads,
-                      n_kv_heads, head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx);
+                      n_kv_heads, head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx, ctx->dev_err_devptr);
 }
 
 size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head_dim, int max_ctx) {
@@ -824,7 +837,7 @@ cq_status attention_impl(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_hea
     if (cos_dev && gqa_chunk_route) {  // this route has no fused rotary step: run it as its own kernel first
         const int work = (n_q_heads + n_kv_heads) * head_dim / 2 + n_kv_heads * head_dim;
         s = launch_pdl(ctx, rope_store_kv_kernel, dim3((unsigned)((work + 255) / 256), (unsigned)batch), dim3(256), qkv_dev, n_q_heads, n_kv_heads,
-                       head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx);
+                       head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx, ctx->dev_err_devptr);
         if (s != CQ_OK) return s;
         cos_dev = sin_dev = nullptr;
     }
@@ -856,19 +869,19 @@ cq_status attention_impl(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_hea
         if (cos_dev)
             CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel<true>, (const float *)qkv_dev, n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev,
                                         (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks, keys_per_split, cos_dev, sin_dev,
-                                        k_cache_dev, v_cache_dev));
+                                        k_cache_dev, v_cache_dev, ctx->dev_err_devptr));
         else
             CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_split_gqa_kernel<false>, (const float *)qkv_dev, n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev,
                                         (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks, keys_per_split, cos_dev, sin_dev,
-                                        k_cache_dev, v_cache_dev));
+                                        k_cache_dev, v_cache_dev, ctx->dev_err_devptr));
         s = CQ_OK;
     } else if (gqa_chunk_route)
         s = launch_pdl(ctx, attn_partial_gqa_kernel, dim3((unsigned)n_kv_heads, (unsigned)batch, (unsigned)nchunks), dim3(128), (const float *)qkv_dev,
-                       n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev, (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks);
+                       n_q_heads, n_kv_heads, pos_dev, (const float *)k_cache_dev, (const float *)v_cache_dev, max_ctx, scale, scratch_dev, nchunks, ctx->dev_err_devptr);
     else
         s = launch_pdl(ctx, attn_partial_kernel, dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)nchunks), dim3(kAttnThreads),
                        (const float *)qkv_dev, n_q_heads, n_kv_heads, head_dim, pos_dev, (const float *)k_cache_dev, (const float *)v_cache_dev, max_ctx,
-                       scale, scratch_dev, nchunks, cos_dev, sin_dev, k_cache_dev, v_cache_dev);
+                       scale, scratch_dev, nchunks, cos_dev, sin_dev, k_cache_dev, v_cache_dev, ctx->dev_err_devptr);
     if (s != CQ_OK) return s;
     return launch_pdl(ctx, attn_combine_kernel, dim3((unsigned)n_q_heads, (unsigned)batch), dim3(128), (const float *)scratch_dev, n_q_heads,
                       head_dim, nchunks, out_dev);

@@ -44,14 +44,6 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
-#ifdef CQ_TRACE
-// profiling aid (separate build): clock64 stamps of CTA 0's roles for 16 consecutive steps
-__device__ long long g_ft_trace[16 * 32];
-#define FT_TRACE(step, ev) do { if (blockIdx.x == 0 && (step) >= 8 && (step) < 24) g_ft_trace[((step) - 8) * 32 + (ev)] = clock64(); } while (0)
-extern "C" int cq_debug_trace_ft(long long *out) { return (int)cudaMemcpyFromSymbol(out, g_ft_trace, sizeof(long long) * 16 * 32); }
-#else
-#define FT_TRACE(step, ev)
-#endif
 
 namespace {
 
@@ -184,7 +176,6 @@ struct FtParams {
     float *part;       // partial sums of groups shared between CTAs: [2 * ctas][m][group rows]
     int m, n, nchunks;
     int total, per_cta;  // (group, chunk) steps in all and per CTA
-    int probe;  // profiling aid: bit 0 = skip the dequantization arithmetic and stores, bit 1 = skip the MMAs
     int *err;
 };
 
@@ -262,7 +253,6 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
                 g += cn;
                 for (int c = 0; c < cn; ++c, ++step) {
                     const int xs = step % XST;
-                    if (warp == 0) FT_TRACE(step, 0);
                     if (step >= XST && !mbar_wait_sleep(smem_u32(&x_empty[xs]), ((step / XST) - 1) & 1, 100)) {
                         atomicExch(p.err, kDevErrEmptyWait);
                         ok = false;
@@ -273,7 +263,6 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
 #pragma unroll
                     for (int a = 2 * warp; a < 2 * warp + 2; ++a)
                         tma_load_2d(smem_u32(smem_x + (size_t)xs * Cfg::kXBytes + a * MPAD * 128), &tmX, (c0 + c) * FT_KCHUNK + a * 64, 0, xbar);
-                    if (warp == 0) FT_TRACE(step, 1);
                 }
             }
             if (ok)  // leave only when nothing is in flight into this CTA's shared memory
@@ -304,7 +293,6 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
                     mbar_expect_tx(bar, FT_WBYTES);
                     // tiles past the last row are outside the tensor: zero fill, no traffic
                     tma_load_2d(smem_u32(smem_w + (size_t)s * FT_WBYTES), &tmW, (c0 + c) * (ROWCHUNK / 2), (group * PIPES + q) * FT_ROWS, bar);  // x in 2-byte elements
-                    if (q == 0) FT_TRACE(step, 2);
                 }
             }
             if (ok)
@@ -338,7 +326,6 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
                         ok = false;
                         break;
                     }
-                    if (iss == 0) FT_TRACE(step, 16);
                     const uint64_t bdesc = smem_desc_k128(smem_u32(smem_x + (size_t)xs * Cfg::kXBytes));
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
@@ -348,9 +335,8 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
                             break;
                         }
                         tc_fence_after();
-                        if (iss == 0) FT_TRACE(step, 17 + 2 * h);
                         const uint32_t a_t = tmem_base + (uint32_t)(q * FT_ACOLS + h * 64);
-                        if (!(p.probe & 2)) {
+                        {
 #pragma unroll
                             for (int j2 = 0; j2 < 8 / IPP; ++j2) {
                                 const int j = IPP * j2 + e;  // K=16 step inside the half
@@ -359,7 +345,6 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
                             }
                         }
                         tc_commit(smem_u32(&a_empty[2 * q + h]));
-                        if (iss == 0) FT_TRACE(step, 18 + 2 * h);
                     }
                     tc_commit(smem_u32(&x_empty[xs]));
                 }
@@ -371,14 +356,12 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
         const int dw = warp - Cfg::kWarpDq0, q = dw >> 3, h = (dw >> 2) & 1;
         const int quarter = warp & 3;  // the tensor-memory lanes this warp may touch
         const int r = quarter * 32 + lane;
-        const bool tracer = q == 0 && quarter == 0 && lane == 0;
         for (int step = 0; step < nsteps; ++step) {
             const int s = q * WSP + step % WSP;
             if (!mbar_wait_sleep(smem_u32(&w_full[s]), (step / WSP) & 1, 60)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
                 break;
             }
-            if (tracer) FT_TRACE(step, 8 + 3 * h);
             // Four blocks = 72 / 136 bytes, 8-byte aligned.
             uint32_t w[HW];
             const uint32_t src = smem_u32(smem_w + (size_t)s * FT_WBYTES + r * ROWCHUNK + h * (ROWCHUNK / 2));
@@ -403,9 +386,8 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
                 break;
             }
             tc_fence_after();
-            if (tracer) FT_TRACE(step, 9 + 3 * h);
             const uint32_t a_t = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(q * FT_ACOLS + h * 64);
-            if (!(p.probe & 1)) {
+            {
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr) {
                     // two blocks in 9 (Q4_0) / 17 (Q8_0) words: the first starts on a word, its values two
@@ -440,7 +422,6 @@ __global__ void __launch_bounds__(FtCfg<QT, MPAD>::kThreads, 1)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&a_full[2 * q + h]));
-            if (tracer) FT_TRACE(step, 10 + 3 * h);
         }
     } else {
         // ---- epilogue: two accumulators per tile of the group, lane = weight row ---------------------
@@ -596,7 +577,6 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const flo
     p.y = y, p.ldy = ldy, p.part = part;
     p.m = (int)m, p.n = (int)n, p.nchunks = nchunks, p.total = (int)total, p.per_cta = (int)per_cta;
     p.err = ctx->dev_err_devptr;
-    p.probe = ctx->tune.gemv_probe;
     if (qtype == CQ_Q4_0) {
         if (mpad == 16) s = run_ft<CQ_Q4_0, 16>(ctx, tmW, tmX, p, ctas);
         else if (mpad == 32) s = run_ft<CQ_Q4_0, 32>(ctx, tmW, tmX, p, ctas);

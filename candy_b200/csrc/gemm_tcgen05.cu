@@ -385,6 +385,9 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
             w16 = static_cast<__half *>(it->second);
             need_convert = false;
         } else {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (ctx->capturing || (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone))
+                return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: the cached f16 copy of this weight matrix does not exist yet and cannot be allocated during stream capture: run the call once before capturing");
             void *p = nullptr;
             CQ_CUDA(ctx, cudaMalloc(&p, w16_bytes));
             ctx->w16_cache[key] = p;

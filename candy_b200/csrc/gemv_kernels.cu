@@ -9,43 +9,35 @@
 // pass it reads the two blocks of that slice for one row from shared memory as 32-bit
 // words at a lane stride of 9 (Q4_0) or 17 (Q8_0) words -- odd, hence bank-conflict-free.
 //
-// Nibble -> f32 without integer conversion or shifts: a nibble n at bit position 4p of a
-// word (p <= 4) is masked in place and OR-ed into the mantissa of 2^23, giving the float
-// 2^23 + n*16^p; subtracting 2^23 + 8*16^p leaves (n-8)*16^p exactly.  The power of 16 is
-// cancelled by scaling the thread's activation by 16^-p once, at kernel start (exact: a
-// power of two).  Positions 5..7 come from the same word shifted right by 16.  Per weight
-// this is one LOP3, one FADD and one FFMA, issued as packed f32x2 pairs.  Q8_0 bytes are
-// handled the same way with the sign bit flipped: (b ^ 0x80) is b+128 as an unsigned byte.
+// Decoders (how a consumer thread turns its 64 activations and its 9 / 17 words into a dot product):
 //
-// Numerics (CQ_ACT_F32): every product x*(q-8) is formed exactly inside an FMA and summed
-// in f32 per block, then scaled by the block's f16 scale -- the values of candy's CPU path
-// (dequantize, then tensor/internal/cpu/kernels/conv.go:373-389) in a different summation
-// order; the relative difference is ~1e-6.  (Decoder DecFma below.)
+// DecQ16, the default for CQ_ACT_F32: every 32-block of activations becomes 16-bit block fixed
+// point once per CTA (X = rint(x * 32767 / amax), split into a signed high and an unsigned low
+// byte plane), and a block's dot product is exact integer arithmetic on packed nibbles / bytes,
+// 256 * dp4a(n, hi) + dp4a(n, lo): four weights per instruction and plane, one int -> float
+// conversion and two multiplies per block.  Against candy's CPU path (dequantize, then
+// tensor/internal/cpu/kernels/conv.go:373-389) the result differs by the 16-bit rounding of the
+// activations (about 1e-5 of max|y| on Gaussian data) and by summation order.
 //
-// Default decoder (DecSlices): the FMA decoder costs ~5 issued instructions per weight, which
-// caps it far below HBM speed.  Instead each thread expands its 64 f32 activations, once, at
-// kernel start, into S = 3 int8 slices per 32-block:  x = d1*q1 + d2*q2 + d3*q3 + r,  each
-// slice quantizing the residual of the previous one (|r| <= 2^-23 of the block's largest
-// |x|, i.e. f32-level resolution against the block maximum).  The dot products are then
-// exact integer dp4a sums over packed nibbles (4 weights per instruction and slice), scaled
-// in f32 per block:  y += d_w * sum_s d_s * (sum_i n_i q_s,i - 8 sum_i q_s,i).  Versus the
-// CPU path this differs by the residual r and by summation order: ~1e-6 relative.
+// DecSlices<S> (option gemv_variant = 2 / 3): S int8 residual slices per block,
+// x = d1*q1 + d2*q2 (+ d3*q3) + r; three slices resolve x to f32 level (~1e-6 of max|y|).
+//
+// DecFma (gemv_variant = 1): plain f32.  A nibble n at bit position 4p of a word is masked in
+// place and OR-ed into the mantissa of 2^23, giving the float 2^23 + n*16^p; subtracting
+// 2^23 + 8*16^p leaves (n-8)*16^p exactly, and the power of 16 is cancelled by scaling the
+// thread's activation by 16^-p once.  Every product x*(q-8) is formed exactly inside an FMA and
+// summed in f32 per block: the values of the CPU path in another summation order (~1e-6).  About
+// five issued instructions per weight, which caps it near 1.8 TB/s.
+//
+// DecQ81 (CQ_ACT_Q8_1): activations already quantized by quantize_q8_1, exact integer dots scaled
+// per block as the reference's CUDA kernels do.  DecMore: Q4_1 / Q5_0 / Q5_1 on DecQ16's state.
 //
 // Plain kernel: one warp per row, byte loads, any k % 32 == 0, any alignment, m <= 8.  It is
 // the route for shapes the streaming kernel does not take and a second implementation the
 // tests compare against.
-#include "common.cuh"
+#include <type_traits>
 
-#ifdef CQ_TRACE
-__device__ long long g_trace[64];
-__device__ int g_trace_on;
-#define TRACE(i) do { if (blockIdx.x == 0 && g_trace_on && (threadIdx.x == 0)) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_trace[i] = t_; } } while (0)
-#define TRACEP(i) do { if (blockIdx.x == 0 && g_trace_on) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_trace[i] = t_; } } while (0)
-extern "C" int cq_debug_trace(long long *out, int on) { cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64); cudaMemcpyToSymbol(g_trace_on, &on, sizeof(int)); return 0; }
-#else
-#define TRACE(i)
-#define TRACEP(i)
-#endif
+#include "common.cuh"
 
 namespace {
 
@@ -84,7 +76,12 @@ struct GemvParams {
     int norm;
     int xs_off;
     int epilogue;
-    int probe;         // profiling aid: 1 = consumers skip the arithmetic, 2 = nobody touches memory barriers, 3 = empty kernel
+    // Multi-row launches (gemv_stream_mr_kernel): m activation rows against one pass over the weights.
+    int m;               // activation rows (<= MR * xg)
+    int xg;              // groups of warps that take the same weight rows against different activation rows
+    int64_t x_row_bytes; // distance between activation rows (f32 rows, or rows of Q8_1 blocks)
+    int64_t ldy;
+    const float *bias;   // added to every output row in the epilogue (nn.Linear's bias), or null
     int *err;
 };
 
@@ -379,6 +376,52 @@ struct DecQ16 {
             }
             const float v = (float)(ah * 256 + al);  // |.| < 2^24: exact
             total = fmaf(scale[blk] * d16[blk], v, total);
+        }
+        return total;
+    }
+
+    // The same arithmetic as pass(), split in two for the multi-row kernel: the weight words of a thread's
+    // two blocks are loaded and unpacked once (WBlk) and then meet the state of each activation row.
+    struct WBlk {
+        int a[2][kBlkWords];  // Q4_0: low nibbles, Q8_0: the signed bytes
+        int b[2][kBlkWords];  // Q4_0: high nibbles, Q8_0: unused
+        float scale[2];
+    };
+    __device__ __forceinline__ static void unpack(const uint32_t *sw, WBlk &o) {
+        uint32_t w[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = sw[i];
+#pragma unroll
+        for (int i = 0; i < kBlkWords; ++i) {
+            const uint32_t d0 = __funnelshift_r(w[i], w[i + 1], 16), d1 = w[kBlkWords + 1 + i];
+            if (QT == CQ_Q4_0) {
+                o.a[0][i] = (int)(d0 & 0x0F0F0F0Fu), o.b[0][i] = (int)((d0 >> 4) & 0x0F0F0F0Fu);
+                o.a[1][i] = (int)(d1 & 0x0F0F0F0Fu), o.b[1][i] = (int)((d1 >> 4) & 0x0F0F0F0Fu);
+            } else {
+                o.a[0][i] = (int)d0, o.a[1][i] = (int)d1;
+                o.b[0][i] = 0, o.b[1][i] = 0;
+            }
+        }
+        o.scale[0] = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+        o.scale[1] = __half2float(__ushort_as_half((unsigned short)(w[kBlkWords] >> 16)));
+    }
+    __device__ __forceinline__ float dot(const WBlk &wb) const {
+        float total = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            int ah = 0, al = bias[blk];
+#pragma unroll
+            for (int wi = 0; wi < kBlkWords; ++wi) {
+                if (QT == CQ_Q4_0) {
+                    ah = __dp4a(wb.b[blk][wi], qh[blk][wi][1], __dp4a(wb.a[blk][wi], qh[blk][wi][0], ah));
+                    al = dp4a_wu(wb.b[blk][wi], ql[blk][wi][1], dp4a_wu(wb.a[blk][wi], ql[blk][wi][0], al));
+                } else {
+                    ah = __dp4a(wb.a[blk][wi], qh[blk][wi][0], ah);
+                    al = dp4a_wu(wb.a[blk][wi], ql[blk][wi][0], al);
+                }
+            }
+            const float v = (float)(ah * 256 + al);  // |.| < 2^24: exact
+            total = fmaf(wb.scale[blk] * d16[blk], v, total);
         }
         return total;
     }
@@ -743,6 +786,46 @@ struct DecQ81 {
         }
         return total;
     }
+
+    // pass() split in two for the multi-row kernel (see DecQ16::WBlk).
+    struct WBlk {
+        int a[2][kBlkWords];
+        int b[2][kBlkWords];
+        float scale[2];
+    };
+    __device__ __forceinline__ static void unpack(const uint32_t *sw, WBlk &o) {
+        uint32_t w[kWords];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = sw[i];
+#pragma unroll
+        for (int i = 0; i < kBlkWords; ++i) {
+            const uint32_t d0 = __funnelshift_r(w[i], w[i + 1], 16), d1 = w[kBlkWords + 1 + i];
+            if (QT == CQ_Q4_0) {
+                o.a[0][i] = (int)(d0 & 0x0F0F0F0Fu), o.b[0][i] = (int)((d0 >> 4) & 0x0F0F0F0Fu);
+                o.a[1][i] = (int)(d1 & 0x0F0F0F0Fu), o.b[1][i] = (int)((d1 >> 4) & 0x0F0F0F0Fu);
+            } else {
+                o.a[0][i] = (int)d0, o.a[1][i] = (int)d1;
+                o.b[0][i] = 0, o.b[1][i] = 0;
+            }
+        }
+        o.scale[0] = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+        o.scale[1] = __half2float(__ushort_as_half((unsigned short)(w[kBlkWords] >> 16)));
+    }
+    __device__ __forceinline__ float dot(const WBlk &wb) const {
+        float total = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            int acc = 0;
+#pragma unroll
+            for (int wi = 0; wi < kBlkWords; ++wi) {
+                if (QT == CQ_Q4_0) acc = __dp4a(wb.b[blk][wi], q[blk][wi][1], __dp4a(wb.a[blk][wi], q[blk][wi][0], acc));
+                else acc = __dp4a(wb.a[blk][wi], q[blk][wi][0], acc);
+            }
+            if (QT == CQ_Q4_0) total += __fmul_rn(wb.scale[blk], __fsub_rn(__fmul_rn((float)acc, d8[blk]), __fmul_rn(8.0f, s8[blk])));
+            else total += __fmul_rn(__fmul_rn(wb.scale[blk], d8[blk]), (float)acc);
+        }
+        return total;
+    }
 };
 
 // MAXT / MINB are launch bounds only: geometries of at most 288 threads are compiled to fit two
@@ -774,7 +857,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     const int rows_per_pass = p.rpp * RPT;
     const int npass = (nrows + rows_per_pass - 1) / rows_per_pass;
 
-    TRACE(0);
     // Let the next kernel in the stream become resident as soon as every CTA of this one is:
     // its producer warp may prefetch weights, everything else there waits for this grid.
     pdl_launch_dependents();
@@ -787,7 +869,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
         fence_proxy_async();
     }
     __syncthreads();
-    TRACE(1);
 
     if (is_producer) {
         // ---- producer warp: one lane streams this CTA's rows into the ring ---------------
@@ -798,7 +879,7 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
             // the activations (re-read by every CTA) and the outputs out of L2.
             const uint64_t policy = make_l2_policy_evict_first();
             int issued = 0;
-            for (int ps = 0; ps < (p.probe >= 2 ? 0 : npass); ++ps) {
+            for (int ps = 0; ps < npass; ++ps) {
                 const int s = ps % p.stages;
                 if (ps >= p.stages) {
                     if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
@@ -809,13 +890,11 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 const int r0 = ps * rows_per_pass;
                 const int rows = min(rows_per_pass, nrows - r0);
                 const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
-                if (ps == 0) TRACEP(10);
                 mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
                 bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
                               smem_u32(&bar_full[s]), policy);
                 issued = ps + 1;
             }
-            TRACEP(11);
             // Do not leave while copies into this CTA's shared memory may still be in flight:
             // wait (bounded) for the last use of every stage that was issued.
             const int first = issued > p.stages ? issued - p.stages : 0;
@@ -839,8 +918,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
 
     // Activations depend on the previous kernel in the stream.
     pdl_wait_prior();
-    TRACE(2);
-    if (p.probe == 3) return;  // profiling aid: the cost of an empty kernel in the chain
 
     // Fused prologue: x' = x + delta (CTA 0 also stores it to x_out: the caller ping-pongs two residual
     // buffers, every other CTA keeps reading the old one), x'' = x' / sqrt(mean(x'^2) + eps) * alpha.
@@ -902,7 +979,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 Dec::stage_quarter(xsrc, item, item < nitems, area);
             }
         }
-        TRACE(3);
         asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
         if (active) dec.load(area + (size_t)pair * 2 * Dec::kStateWordsPerBlock);
         else dec.load(area);  // idle lanes: any valid state, their results are never used
@@ -922,7 +998,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
         dec.init(tmp);
     }
 
-    TRACE(4);
     // Loop state is kept incremental (stage index, phase bit, rows left): an integer divide or
     // modulo per pass costs more ALU-pipe slots than the pass's own mask instructions.
     const uint8_t *my_words = smem + 4 * (rsub * (p.row_bytes >> 2) + pair * kWords);
@@ -943,16 +1018,15 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
         for (int u = 0; u < ucount; ++u) {
             // A warp whose wait gave up keeps walking the loop without waiting or computing,
             // so that every consumer still reaches the barriers below and the CTA can exit.
-            if (!dead && p.probe != 2 && !mbar_wait_bounded(full0 + 8 * stage, phase)) {
+            if (!dead && !mbar_wait_bounded(full0 + 8 * stage, phase)) {
                 atomicExch(p.err, kDevErrFullWait);
                 dead = true;
             }
-            if (pbase == 0 && u == 0) TRACE(5);
             float v[RPT];
 #pragma unroll
             for (int j = 0; j < RPT; ++j) v[j] = 0.0f;
             const uint8_t *sw = my_words + stage * p.stage_bytes;
-            const bool go = !dead && active && p.probe != 1;
+            const bool go = !dead && active;
             if (RPT == 2 && go && rsub + p.rpp < rows_left) {
                 // both rows present: one basic block, so the two streams interleave
                 v[0] = dec.pass(reinterpret_cast<const uint32_t *>(sw));
@@ -974,7 +1048,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 phase ^= 1;
             }
         }
-        if (pbase == 0) TRACE(6);
         float part[kPassUnroll];
 #pragma unroll
         for (int i = 0; i < kPassUnroll; ++i) part[i] = (i < ucount * RPT) ? stash[i * cthreads + tid] : 0.0f;
@@ -1031,7 +1104,6 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 if ((lane % L) == 0) red[buf][u][rsub * p.wpr + wir] = t;
             }
         }
-        if (pbase == 0) TRACE(7);
         // consumer-only barrier (the producer warp is not part of it)
         asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
         for (int t = tid; t < kPassUnroll * p.rpp; t += cthreads) {
@@ -1053,19 +1125,225 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
                 } else if (p.push_world > 0) {
                     // value and tag travel in one 8-byte store: the receiver polls the data itself, so
                     // nothing but one NVLink hop lies between this store and its use (no fence, no flag)
-                    const uint2 v = make_uint2(__float_as_uint(tot), push_tag);
+                    // (one 64-bit element, tag in the high half: single-copy atomic, never seen torn)
+                    const unsigned long long v = ((unsigned long long)push_tag << 32) | (unsigned long long)__float_as_uint(tot);
                     for (int pr = 0; pr < p.push_world; ++pr)
-                        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.push_rx[pr] + p.push_off + row_begin + r), "r"(v.x), "r"(v.y)
-                                     : "memory");
+                        asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p.push_rx[pr] + p.push_off + row_begin + r), "l"(v) : "memory");
                 } else {
-                    p.y[row_begin + r] = tot;
+                    p.y[row_begin + r] = p.bias ? tot + p.bias[row_begin + r] : tot;
                 }
             }
         }
-        if (pbase == 0) TRACE(8);
         buf ^= 1;
     }
-    TRACE(9);
+}
+
+// ---- several activation rows per weight pass (m = 2..8) ------------------------------------
+// Same ring, producer and reduction as gemv_stream_kernel; a consumer thread keeps the state of MR
+// activation rows in registers, unpacks its two weight blocks once per pass and forms MR dot products
+// from them, so the weights cross HBM (and shared memory) once for all rows.  When MR rows of state do
+// not cover m, xg groups of warps take the same weight rows against different activation rows
+// (group g: rows g*MR .. g*MR+MR-1).  One weight row per thread and pass; no fused prologue / epilogue.
+template <class Dec, int MR>
+__global__ void __launch_bounds__(384, 1) gemv_stream_mr_kernel(const GemvParams p) {
+    constexpr int kWords = Dec::kWords;
+    constexpr int kPassGroup = kPassUnroll / MR;  // passes per reduction group (8 partial sums)
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bar_full[kMaxStages];
+    __shared__ uint64_t bar_empty[kMaxStages];
+    __shared__ float red[2][kPassUnroll][64];  // [buffer][partial][(group * rpp + rsub) * wpr + warp-in-row]
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int cthreads = p.cwarps * 32;
+    float *stash = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);  // [8][cthreads] partial sums
+    const bool is_producer = warp == p.cwarps;
+
+    const int64_t row_begin = (p.n * (int64_t)blockIdx.x) / gridDim.x;
+    const int64_t row_end = (p.n * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+    const int nrows = (int)(row_end - row_begin);
+    const int npass = (nrows + p.rpp - 1) / p.rpp;
+
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), p.cwarps);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    if (is_producer) {
+        if (lane == 0) {
+            const uint64_t policy = make_l2_policy_evict_first();
+            int issued = 0;
+            for (int ps = 0; ps < npass; ++ps) {
+                const int s = ps % p.stages;
+                if (ps >= p.stages) {
+                    if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
+                        atomicExch(p.err, kDevErrEmptyWait);
+                        break;
+                    }
+                }
+                const int r0 = ps * p.rpp;
+                const int rows = min(p.rpp, nrows - r0);
+                const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
+                mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
+                bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
+                              smem_u32(&bar_full[s]), policy);
+                issued = ps + 1;
+            }
+            // never leave with copies in flight into this CTA's shared memory
+            const int first = issued > p.stages ? issued - p.stages : 0;
+            for (int ps = first; ps < issued; ++ps) {
+                if (!mbar_wait_bounded(smem_u32(&bar_full[ps % p.stages]), (ps / p.stages) & 1)) {
+                    atomicExch(p.err, kDevErrDrain);
+                    break;
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumer warps: warp -> (row group, activation-row group, warp inside the row) ----
+    const int rows_per_warp = 32 / p.lanes_per_row;
+    const int wir = warp % p.wpr;
+    const int xgi = (warp / p.wpr) % p.xg;
+    const int rsub = (warp / (p.wpr * p.xg)) * rows_per_warp + lane / p.lanes_per_row;
+    const int pair = wir * 32 + (lane % p.lanes_per_row);
+    const bool active = pair < p.tpr;
+
+    pdl_wait_prior();  // activations depend on the previous kernel in the stream
+
+    // Activation state of all m rows, built once per CTA into shared memory (four lanes per block).
+    uint32_t *area = reinterpret_cast<uint32_t *>(smem + p.coop_off);
+    const int nitems = p.nb * 4;
+    const int row_words = p.nb * Dec::kStateWordsPerBlock;
+    const int total_items = p.m * nitems;
+    for (int base = 0; base < total_items; base += cthreads) {  // uniform trip count: the shuffles need whole warps
+        const int idx = base + tid;
+        const bool valid = idx < total_items;
+        const int r = valid ? idx / nitems : 0, item = valid ? idx - r * nitems : 0;
+        const float *xrow = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(p.x) + (int64_t)r * p.x_row_bytes);
+        Dec::stage_quarter(xrow, item, valid, area + (size_t)r * row_words);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+    Dec dec[MR];
+#pragma unroll
+    for (int r = 0; r < MR; ++r) {
+        const int xr = xgi * MR + r;
+        // rows beyond m and idle lanes: any valid state, their results are never stored
+        dec[r].load(area + (size_t)(xr < p.m ? xr : 0) * row_words + (size_t)(active ? pair : 0) * 2 * Dec::kStateWordsPerBlock);
+    }
+
+    const uint8_t *my_words = smem + 4 * (rsub * (p.row_bytes >> 2) + pair * kWords);
+    const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
+    int stage = 0;
+    uint32_t phase = 0;
+    int rows_left = nrows;
+    int buf = 0;
+    bool dead = false;
+    const int slots = p.rpp * p.xg;  // (group, weight row of the pass) pairs
+
+    for (int pbase = 0; pbase < npass; pbase += kPassGroup) {
+        const int ucount = min(kPassGroup, npass - pbase);
+#pragma unroll 1
+        for (int u = 0; u < ucount; ++u) {
+            // a warp whose wait gave up keeps walking the loop so that every consumer reaches the barriers below
+            if (!dead && !mbar_wait_bounded(full0 + 8 * stage, phase)) {
+                atomicExch(p.err, kDevErrFullWait);
+                dead = true;
+            }
+            float v[MR];
+#pragma unroll
+            for (int r = 0; r < MR; ++r) v[r] = 0.0f;
+            if (!dead && active && rsub < rows_left) {
+                typename Dec::WBlk wb;
+                Dec::unpack(reinterpret_cast<const uint32_t *>(my_words + stage * p.stage_bytes), wb);
+#pragma unroll
+                for (int r = 0; r < MR; ++r) v[r] = dec[r].dot(wb);
+            }
+            // parked BEFORE the stage is released: these stores need every word the pass loaded (an
+            // mbarrier arrive by itself does not wait for shared-memory loads still in flight)
+#pragma unroll
+            for (int r = 0; r < MR; ++r) asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_u32(&stash[(u * MR + r) * cthreads + tid])), "f"(v[r]) : "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+            rows_left -= p.rpp;
+            if (++stage == p.stages) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+        float part[kPassUnroll];
+#pragma unroll
+        for (int i = 0; i < kPassUnroll; ++i) part[i] = (i < ucount * MR) ? stash[i * cthreads + tid] : 0.0f;
+
+        // reduce the 8 partials over the lanes of each row segment (as in gemv_stream_kernel)
+        const int L = p.lanes_per_row;
+        const int slot = (xgi * p.rpp + rsub) * p.wpr + wir;
+        if (L >= 8) {
+            const int lr = lane % L;
+            int vidx = 0;
+            float v4[4], v2[2], v1;
+            {
+                const int off = L >> 1;
+                const bool up = (lr & off) != 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float keep = up ? part[i + 4] : part[i];
+                    const float send = up ? part[i] : part[i + 4];
+                    v4[i] = keep + __shfl_xor_sync(0xffffffffu, send, off, 32);
+                }
+                vidx = up ? 4 : 0;
+            }
+            {
+                const int off = L >> 2;
+                const bool up = (lr & off) != 0;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float keep = up ? v4[i + 2] : v4[i];
+                    const float send = up ? v4[i] : v4[i + 2];
+                    v2[i] = keep + __shfl_xor_sync(0xffffffffu, send, off, 32);
+                }
+                vidx += up ? 2 : 0;
+            }
+            {
+                const int off = L >> 3;
+                const bool up = (lr & off) != 0;
+                const float keep = up ? v2[1] : v2[0];
+                const float send = up ? v2[0] : v2[1];
+                v1 = keep + __shfl_xor_sync(0xffffffffu, send, off, 32);
+                vidx += up ? 1 : 0;
+            }
+            for (int off = L >> 4; off > 0; off >>= 1) v1 += __shfl_xor_sync(0xffffffffu, v1, off, 32);
+            const bool writer = (lr & ((L >> 3) - 1)) == 0;
+            if (writer) red[buf][vidx][slot] = v1;
+        } else {
+#pragma unroll
+            for (int u = 0; u < kPassUnroll; ++u) {
+                float t = part[u];
+                for (int off = L >> 1; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off, 32);
+                if ((lane % L) == 0) red[buf][u][slot] = t;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+        for (int t = tid; t < kPassUnroll * slots; t += cthreads) {
+            const int i = t / slots, sl = t - i * slots;   // i = pass-in-group * MR + activation row of the thread
+            const int g = sl / p.rpp, rs = sl - g * p.rpp;
+            const int u = i / MR, r = i - u * MR;
+            const int wrow = (pbase + u) * p.rpp + rs;
+            const int xr = g * MR + r;
+            if (u < ucount && wrow < nrows && xr < p.m) {
+                float tot = 0.0f;
+                for (int w = 0; w < p.wpr; ++w) tot += red[buf][i][sl * p.wpr + w];
+                p.y[(int64_t)xr * p.ldy + row_begin + wrow] = p.bias ? tot + p.bias[row_begin + wrow] : tot;
+            }
+        }
+        buf ^= 1;
+    }
 }
 
 // ---- plain kernel ------------------------------------------------------------------------
@@ -1250,6 +1528,125 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     return true;
 }
 
+// Geometry of the multi-row kernel for `m` activation rows with `mr` rows of state per thread; false when
+// the shape does not fit (then the caller falls back to one launch per row or per smaller group).
+bool plan_stream_mr(const cq_ctx *ctx, int qtype, const void *w, const void *x, int64_t n, int64_t k, int m, int mr, int state_words,
+                    GemvParams &p, int &grid, int &threads, size_t &smem) {
+    const int bb = qtype == CQ_Q4_0 ? kQ4Bytes : kQ8Bytes;
+    const int64_t nb = k / kQK;
+    if (nb % 8 != 0 || k > 32768) return false;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
+    const int tpr = (int)(nb / 2);
+    int lanes, wpr;
+    if (tpr >= 32) {
+        lanes = 32;
+        wpr = (tpr + 31) / 32;
+    } else {
+        if (!is_pow2(tpr)) return false;
+        lanes = tpr;
+        wpr = 1;
+    }
+    const int xg = (m + mr - 1) / mr;
+    constexpr int kMaxCWarps = 11;  // 11 consumer warps + the producer = 384 threads: 168 registers each
+    if (wpr * xg > kMaxCWarps) return false;
+    int row_groups = kMaxCWarps / (wpr * xg);
+    const int rows_per_warp = 32 / lanes;
+    while (row_groups > 1 && row_groups * rows_per_warp * xg * wpr > 64) --row_groups;  // reduction scratch: 64 slots per partial
+    if (row_groups * rows_per_warp * xg * wpr > 64) return false;
+    const int cwarps = row_groups * xg * wpr;
+    const int rpp = row_groups * rows_per_warp;
+    const int64_t row_bytes = nb * bb;
+    const int64_t stage_bytes = (int64_t)rpp * row_bytes;
+    threads = (cwarps + 1) * 32;
+    const size_t stash_bytes = (size_t)kPassUnroll * cwarps * 32 * sizeof(float);
+    const size_t coop_bytes = (size_t)m * nb * state_words * sizeof(uint32_t);
+    const size_t fixed = kStaticSmemReserve + stash_bytes + coop_bytes;
+    if (ctx->smem_optin < fixed + 2 * (size_t)stage_bytes) return false;
+    const size_t budget = ctx->smem_optin - fixed;
+    int stages = 8;
+    while ((size_t)stage_bytes * stages > budget) --stages;
+    p.n = n;
+    p.nb = (int)nb;
+    p.row_bytes = (int)row_bytes;
+    p.tpr = tpr;
+    p.lanes_per_row = lanes;
+    p.wpr = wpr;
+    p.rpp = rpp;
+    p.cwarps = cwarps;
+    p.stages = stages;
+    p.stage_bytes = (int)stage_bytes;
+    p.coop_off = (int)((size_t)stage_bytes * stages + stash_bytes);
+    p.xs_off = -1;
+    p.m = m;
+    p.xg = xg;
+    smem = (size_t)stage_bytes * stages + stash_bytes + coop_bytes;
+    const int64_t max_ctas = (n + rpp - 1) / rpp;
+    grid = (int)(max_ctas < ctx->sm_count ? max_ctas : ctx->sm_count);
+    return true;
+}
+
+template <class Dec, int MR>
+cq_status run_stream_mr(cq_ctx *ctx, const GemvParams &p, int grid, int threads, size_t smem) {
+    static thread_local int configured_device = -1;
+    auto kern = gemv_stream_mr_kernel<Dec, MR>;
+    if (configured_device != ctx->device) {
+        CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - kStaticSmemReserve)));
+        configured_device = ctx->device;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+    return CQ_OK;
+}
+
+// m (2..8) rows in as few weight passes as the register budget allows.  `x` is f32 rows (Q16 state, at
+// most 4 rows of state per thread, two warp groups for 5..8 rows when the row is short enough) or rows of
+// Q8_1 blocks (Q81 state, up to 8 rows per thread).  Returns how many leading rows were launched (0 when
+// the shape does not fit; a single left-over row is left to the one-row kernel).
+template <int QT, int ORDER, bool Q81>
+int64_t try_stream_mr(cq_ctx *ctx, const void *x, int64_t x_row_bytes, int64_t m, int64_t k, const uint8_t *w, int64_t n, float *y, int64_t ldy,
+                      cq_status &s) {
+    using Dec = typename std::conditional<Q81, DecQ81<QT, ORDER>, DecQ16<QT, ORDER>>::type;
+    s = CQ_OK;
+    if (ctx->tune.force_simple || ctx->tune.gemv_multirow == 0 || m < 2 || m > 8 || (x_row_bytes & 15) != 0) return 0;
+    int64_t r0 = 0;
+    while (m - r0 >= 2) {
+        GemvParams p{};
+        int grid = 0, threads = 0;
+        size_t smem = 0;
+        const uint8_t *xr = static_cast<const uint8_t *>(x) + r0 * x_row_bytes;
+        int rows = (int)(m - r0);
+        const int mr = Q81 ? (rows <= 2 ? 2 : (rows <= 4 ? 4 : 8)) : (rows <= 2 ? 2 : 4);
+        bool ok = plan_stream_mr(ctx, QT, w, xr, n, k, rows, mr, Dec::kStateWordsPerBlock, p, grid, threads, smem);
+        if (!ok && rows > mr) {  // not enough warps for two activation-row groups: mr rows now, the rest in another pass
+            rows = mr;
+            ok = plan_stream_mr(ctx, QT, w, xr, n, k, rows, mr, Dec::kStateWordsPerBlock, p, grid, threads, smem);
+        }
+        if (!ok) break;
+        p.w = w;
+        p.x = reinterpret_cast<const float *>(xr);
+        p.x_row_bytes = x_row_bytes;
+        p.y = y + r0 * ldy;
+        p.ldy = ldy;
+        p.err = ctx->dev_err_devptr;
+        p.bias = ctx->bias;
+        if (mr == 2) s = run_stream_mr<Dec, 2>(ctx, p, grid, threads, smem);
+        else if (mr == 4) s = run_stream_mr<Dec, 4>(ctx, p, grid, threads, smem);
+        else s = run_stream_mr<Dec, Q81 ? 8 : 4>(ctx, p, grid, threads, smem);
+        if (s != CQ_OK) return r0 + rows;
+        r0 += rows;
+    }
+    return r0;
+}
+
 template <class Dec, int RPT, int MAXT, int MINB>
 cq_status run_stream_b(cq_ctx *ctx, GemvParams p, int grid, int threads, size_t smem) {
     static thread_local int configured_device = -1;
@@ -1317,6 +1714,35 @@ cq_status run_q8_1(cq_ctx *ctx, const uint8_t *w, const uint8_t *act, float *y, 
     return CQ_OK;
 }
 
+// The Q8_1-activation GEMV on m rows of already quantized activation blocks (36 bytes each, 16-byte aligned
+// base): the streaming kernel with the Q8_1 decoder when the shape fits it (one weight pass for all rows),
+// else the plain one-warp-per-row kernel.  Allocates nothing.
+template <int QT, int ORDER>
+cq_status q8_1_on_blocks(cq_ctx *ctx, const void *act_blocks, int64_t m, int64_t k, const uint8_t *w, int64_t n, float *y, int64_t ldy) {
+    const int nb = (int)(k / kQK);
+    GemvParams p{};
+    int rpt = 1, grid = 0, threads = 0;
+    size_t smem = 0;
+    if (!ctx->tune.force_simple && ctx->push.world == 0 && !ctx->fuse.on &&
+        plan_stream(ctx, QT, w, static_cast<const float *>(act_blocks), n, k, p, rpt, grid, threads, smem) && p.coop_off >= 0) {
+        p.w = w;
+        p.err = ctx->dev_err_devptr;
+        p.bias = ctx->bias;
+        ctx->bias_done = true;
+        cq_status s = CQ_OK;
+        const int64_t done = try_stream_mr<QT, ORDER, true>(ctx, act_blocks, (int64_t)nb * kQ81Bytes, m, k, w, n, y, ldy, s);
+        if (s != CQ_OK) return s;
+        for (int64_t i = done; i < m; ++i) {
+            p.x = reinterpret_cast<const float *>(static_cast<const uint8_t *>(act_blocks) + (size_t)i * nb * kQ81Bytes);
+            p.y = y + i * ldy;
+            s = run_stream<DecQ81<QT, ORDER>>(ctx, p, rpt, grid, threads, smem);
+            if (s != CQ_OK) return s;
+        }
+        return CQ_OK;
+    }
+    return run_q8_1<QT, ORDER>(ctx, w, static_cast<const uint8_t *>(act_blocks), y, m, n, nb, ldy);
+}
+
 template <int QT, int ORDER>
 cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx, const uint8_t *w,
                         int64_t n, float *y, int64_t ldy) {
@@ -1327,26 +1753,7 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         if (s != CQ_OK) return s;
         s = launch_quantize_q8_1(ctx, x, m, k, ldx, ctx->scratch);
         if (s != CQ_OK) return s;
-        {   // the streaming kernel with the Q8_1 decoder, when the shape fits it and its cooperative set-up
-            GemvParams p{};
-            int rpt = 1, grid = 0, threads = 0;
-            size_t smem = 0;
-            const float *blocks = static_cast<const float *>(ctx->scratch);
-            if (!ctx->tune.force_simple && ctx->push.world == 0 && !ctx->fuse.on && plan_stream(ctx, QT, w, blocks, n, k, p, rpt, grid, threads, smem) &&
-                p.coop_off >= 0) {
-                p.w = w;
-                p.err = ctx->dev_err_devptr;
-                p.probe = 0;
-                for (int64_t i = 0; i < m; ++i) {
-                    p.x = reinterpret_cast<const float *>(static_cast<const uint8_t *>(ctx->scratch) + (size_t)i * nb * kQ81Bytes);
-                    p.y = y + i * ldy;
-                    s = run_stream<DecQ81<QT, ORDER>>(ctx, p, rpt, grid, threads, smem);
-                    if (s != CQ_OK) return s;
-                }
-                return CQ_OK;
-            }
-        }
-        return run_q8_1<QT, ORDER>(ctx, w, static_cast<const uint8_t *>(ctx->scratch), y, m, n, nb, ldy);
+        return q8_1_on_blocks<QT, ORDER>(ctx, ctx->scratch, m, k, w, n, y, ldy);
     }
     GemvParams p{};
     int rpt = 1, grid = 0, threads = 0;
@@ -1354,7 +1761,8 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
     if (!ctx->tune.force_simple && plan_stream(ctx, QT, w, x, n, k, p, rpt, grid, threads, smem) && (ldx % 4 == 0)) {
         p.w = w;
         p.err = ctx->dev_err_devptr;
-        p.probe = ctx->tune.gemv_probe;
+        p.bias = (ctx->push.world == 0 && !(ctx->fuse.on && ctx->fuse.epilogue == 1)) ? ctx->bias : nullptr;
+        ctx->bias_done = p.bias != nullptr;
         p.push_world = ctx->push.world;
         p.push_rx = ctx->push.rx;
         p.push_seq = ctx->push.seq;
@@ -1362,7 +1770,13 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         p.norm = f.on && f.norm ? 1 : 0;
         p.eps = f.eps;
         p.epilogue = f.on ? f.epilogue : 0;
-        for (int64_t i = 0; i < m; ++i) {  // one pass over the weights per activation row
+        int64_t done = 0;
+        if (!f.on && ctx->push.world == 0 && ctx->tune.gemv_variant == 0) {  // two or more plain rows: one weight pass for up to 4 (8) of them
+            cq_status s = CQ_OK;
+            done = try_stream_mr<QT, ORDER, false>(ctx, x, ldx * (int64_t)sizeof(float), m, k, w, n, y, ldy, s);
+            if (s != CQ_OK) return s;
+        }
+        for (int64_t i = done; i < m; ++i) {  // one pass over the weights per remaining activation row
             p.x = x + i * ldx;
             p.y = y + i * ldy;
             p.delta = f.on && f.delta ? f.delta + i * f.ld_delta : nullptr;
@@ -1396,7 +1810,6 @@ bool try_stream_more(cq_ctx *ctx, const float *x, int64_t m, int64_t k, int64_t 
     if (ctx->tune.force_simple || (ldx % 4) != 0 || !plan_stream(ctx, QT, w, x, n, k, p, rpt, grid, threads, smem)) return false;
     p.w = static_cast<const uint8_t *>(w);
     p.err = ctx->dev_err_devptr;
-    p.probe = 0;
     s = CQ_OK;
     for (int64_t i = 0; i < m && s == CQ_OK; ++i) {
         p.x = x + i * ldx;
@@ -1431,15 +1844,13 @@ cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     return gemv_dispatch<CQ_Q8_0, 0>(ctx, actmode, x, m, k, ldx, wb, n, y, ldy);
 }
 
-// The Q8_1-activation GEMV on activation blocks the caller has already quantized (36-byte
-// blocks, m rows of k/32).  Same kernels as the CQ_ACT_Q8_1 branch above.
+// The Q8_1-activation GEMV on activation blocks the caller has already quantized (36-byte blocks, m rows of
+// k/32, base 16-byte aligned for the streaming route).  The same routes as cq_qmatmul's CQ_ACT_Q8_1 mode; nothing is allocated.
 cq_status launch_gemv_q8_1_blocks(cq_ctx *ctx, int qtype, int order, const void *act_blocks, int64_t m, int64_t k,
                                   const void *w, int64_t n, float *y, int64_t ldy) {
     if (cq_is_more_format(qtype)) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "Q8_1 activations take Q4_0 / Q8_0 weights only");
     const uint8_t *wb = static_cast<const uint8_t *>(w);
-    const uint8_t *ab = static_cast<const uint8_t *>(act_blocks);
-    const int nb = (int)(k / kQK);
-    if (qtype == CQ_Q4_0 && order == CQ_ORDER_GO_INTERLEAVED) return run_q8_1<CQ_Q4_0, 0>(ctx, wb, ab, y, m, n, nb, ldy);
-    if (qtype == CQ_Q4_0) return run_q8_1<CQ_Q4_0, 1>(ctx, wb, ab, y, m, n, nb, ldy);
-    return run_q8_1<CQ_Q8_0, 0>(ctx, wb, ab, y, m, n, nb, ldy);
+    if (qtype == CQ_Q4_0 && order == CQ_ORDER_GO_INTERLEAVED) return q8_1_on_blocks<CQ_Q4_0, 0>(ctx, act_blocks, m, k, wb, n, y, ldy);
+    if (qtype == CQ_Q4_0) return q8_1_on_blocks<CQ_Q4_0, 1>(ctx, act_blocks, m, k, wb, n, y, ldy);
+    return q8_1_on_blocks<CQ_Q8_0, 0>(ctx, act_blocks, m, k, wb, n, y, ldy);
 }

@@ -35,6 +35,11 @@ cq_status static_scratch_address(cq_ctx *ctx, void **out) {
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "device ordinal beyond 63");
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
     if (g_scratch_addr[ctx->device] == nullptr) {
+        // The one-time lookup is a runtime call that must not land inside a stream capture.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (ctx->capturing || (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone))
+            return cq_fail(ctx, CQ_ERR_INVALID_ARG,
+                           "cq_qmatmul_q8_1_static: the first call on a device looks up the scratch array's address and must be made outside stream capture");
         void *ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&ptr, g_q8_1_scratch);
         if (e != cudaSuccess) return cq_cuda_fail(ctx, e, "cudaGetSymbolAddress(g_q8_1_scratch)");
@@ -68,7 +73,9 @@ extern "C" cq_status cq_qmatmul_q8_1_static(cq_ctx *ctx, int qtype, int order, c
     cq_status s = static_scratch_address(ctx, &scratch);
     if (s != CQ_OK) return s;
     // The quantizer rewrites every block the GEMV then reads (m * k/32 of them), so nothing left
-    // over from an earlier call is ever consumed and nothing needs clearing.
+    // over from an earlier call is ever consumed and nothing needs clearing.  The GEMV takes the same
+    // routes as cq_qmatmul's CQ_ACT_Q8_1 mode (streaming kernel when the shape fits, whose only working
+    // memory is shared memory; the plain kernel otherwise): neither allocates.
     s = launch_quantize_q8_1(ctx, x_dev, m, k, ldx, scratch);
     if (s != CQ_OK) return s;
     return launch_gemv_q8_1_blocks(ctx, qtype, order, scratch, m, k, w_blocks_dev, n, y_dev, ldy);

@@ -58,6 +58,33 @@ def rope_tables(cfg: DecoderConfig):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
+class PositionGuard:
+    """Host-side shadow of the device-resident decode position.
+
+    The position is advanced on the device (inside captured graphs), where the host cannot see it, so
+    the runner keeps its own count and refuses any step, replay or state that would index a KV cache
+    or rotary table at or beyond ``max_ctx``.  (The kernels clamp and flag such a position as well;
+    this check fails earlier and with the offending numbers.)"""
+
+    def __init__(self, max_ctx: int):
+        self.max_ctx = int(max_ctx)
+        self.pos = 0
+
+    def set(self, pos: int) -> None:
+        if not 0 <= int(pos) < self.max_ctx:
+            raise ValueError(f"decoder: position {pos} outside [0, {self.max_ctx})")
+        self.pos = int(pos)
+
+    def need(self, steps: int, what: str = "step") -> None:
+        """Raises unless `steps` more advancing steps fit: the last of them runs at pos + steps - 1."""
+        if steps > 0 and self.pos + steps > self.max_ctx:
+            raise ValueError(f"decoder: {what} of {steps} position(s) from {self.pos} runs past max_ctx {self.max_ctx}")
+
+    def advance(self, steps: int) -> None:
+        self.need(steps)
+        self.pos += int(steps)
+
+
 class QuantDecoder:
     def __init__(self, dev: CudaDevice, cfg: DecoderConfig, seed: int = 0, batch: int = 1, qtype: int = Q4_0,
                  order: int = ORDER_GO_INTERLEAVED, rank: int = 0, world: int = 1,
@@ -127,6 +154,9 @@ class QuantDecoder:
         self.att_scratch = dev.alloc(self.lib.cq_decode_attention_scratch_floats(batch, self.nq, hd, cfg.max_ctx))
         self.ids = RawBuffer(dev, 4 * batch)
         self.pos = RawBuffer(dev, 4)
+        self.guard = PositionGuard(cfg.max_ctx)
+        self._capturing = False
+        self._graph_steps = {}  # graph handle -> advancing steps recorded in it
         self.set_state(np.zeros(batch, dtype=np.uint32), 0)
         dev.synchronize()
 
@@ -145,6 +175,7 @@ class QuantDecoder:
                                         y.ptr, w.n), "qmatmul")
 
     def set_state(self, ids: np.ndarray, pos: int):
+        self.guard.set(pos)
         ids = np.ascontiguousarray(ids, dtype=np.uint32)
         p = np.array([pos], dtype=np.int32)
         self._check(self.lib.cq_memcpy_h2d(self.ctx, self.ids.ptr, ids.ctypes.data_as(C.c_void_p), ids.nbytes), "ids")
@@ -163,6 +194,8 @@ class QuantDecoder:
     def step(self, advance: bool = True):
         lib, ctx, cfg, B = self.lib, self.ctx, self.cfg, self.batch
         hd, dim = cfg.head_dim, cfg.dim
+        if not self._capturing:  # a recorded step runs at replay time: replay() accounts for it
+            self.guard.need(1)
         if cfg.with_head:
             self._check(lib.cq_embedding(ctx, self.embed.ptr, cfg.vocab, dim, self.ids.ptr, B, self.x.ptr), "embedding")
         first = True
@@ -241,16 +274,25 @@ class QuantDecoder:
             self._check(lib.cq_memcpy_d2d(ctx, self.x.ptr, xc.ptr, 4 * B * dim), "residual home")
         if advance:
             self._check(lib.cq_add_int(ctx, self.pos.ptr, 1), "advance")
+            if not self._capturing:
+                self.guard.advance(1)
 
     def capture(self, steps: int = 1):
         g = C.c_void_p()
         self._check(self.lib.cq_capture_begin(self.ctx), "capture begin")
-        for _ in range(steps):
-            self.step()
-        self._check(self.lib.cq_capture_end(self.ctx, C.byref(g)), "capture end")
+        self._capturing = True
+        try:
+            for _ in range(steps):
+                self.step()
+        finally:
+            self._capturing = False
+            self._check(self.lib.cq_capture_end(self.ctx, C.byref(g)), "capture end")
+        self._graph_steps[g.value] = steps
         return g
 
     def replay(self, g, times: int = 1):
+        """Launches a captured graph `times` times; refused when that would run past max_ctx."""
+        self.guard.advance(self._graph_steps.get(g.value, 0) * times)
         for _ in range(times):
             self._check(self.lib.cq_graph_launch(self.ctx, g), "graph launch")
 

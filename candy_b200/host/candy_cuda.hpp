@@ -213,17 +213,21 @@ class QLinear {
                                      std::to_string(w_.k));
         if (actmode < 0) actmode = rows > 8 ? CQ_ACT_F16 : CQ_ACT_F32;
         Storage xs = Storage::from_slice(w_.device(), x);
-        std::vector<float> y = xs.matmul(w_, 1, rows, w_.n, k, actmode).data();
-        if (!bias_.empty())
-            for (int64_t r = 0; r < rows; ++r)
-                for (int64_t c = 0; c < w_.n; ++c) y[r * w_.n + c] += bias_[c];  // BroadcastAdd (nn/linear.go:105-110)
-        return y;
+        if (bias_.empty()) return xs.matmul(w_, 1, rows, w_.n, k, actmode).data();
+        // BroadcastAdd (nn/linear.go:105-110) happens on the device, in the matmul's epilogue where its kernel has one
+        if (!bias_dev_) bias_dev_.reset(new Storage(Storage::from_slice(w_.device(), bias_)));
+        Storage out = Storage::alloc(w_.device(), (size_t)(rows * w_.n));
+        check(w_.device()->ctx(),
+              cq_qlinear(w_.device()->ctx(), w_.qtype, w_.order, actmode, xs.ptr(), rows, k, k, w_.ptr(), w_.n, bias_dev_->ptr(), out.ptr(), w_.n),
+              "linear: failed to matmul");
+        return out.data();
     }
     const QStorage &weight() const { return w_; }
 
   private:
     QStorage w_;
     std::vector<float> bias_;
+    mutable std::unique_ptr<Storage> bias_dev_;  // the bias, uploaded on first use
 };
 
 }  // namespace cuda

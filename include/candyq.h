@@ -63,8 +63,13 @@ enum cq_qtype {
 enum cq_order { CQ_ORDER_GO_INTERLEAVED = 0, CQ_ORDER_GGML_SPLIT = 1 };
 
 /* How activations enter the dot products.
- * CQ_ACT_F32   f32 activations, f32 accumulate: the arithmetic of candy's CPU path
- *              (dequantize, then conv.go:373-389) up to summation order.
+ * CQ_ACT_F32   f32 activations in, f32 out, no quantization the caller can see: the mode that
+ *              stands in for candy's CPU path (dequantize, then conv.go:373-389).  Inside the
+ *              decode GEMV each 32-block of activations is held as 16-bit block fixed point
+ *              (X = rint(x * 32767 / max|x|)), the dots are exact integers and blocks are summed
+ *              in f32: within about 1e-5 of max|y| of the CPU path (bar 1e-3).  The context
+ *              option gemv_variant = 3 (three int8 residual slices) or 1 (plain f32 FMAs)
+ *              resolves activations to f32 level, about 1e-6, at a lower rate.
  * CQ_ACT_Q8_1  activations quantized per 32 to int8 exactly as quantize_q8_1
  *              (quantized.cu:3521-3558), integer dots scaled per block as
  *              vec_dot_q4_0_q8_1 / vec_dot_q8_0_q8_1 (quantized.cu:1919-1941, :2058-2073).
@@ -84,9 +89,26 @@ cq_status cq_ctx_create(int device, cq_ctx **out);
 cq_status cq_ctx_destroy(cq_ctx *ctx);
 /* Run subsequent launches on a caller-owned cudaStream_t (0 restores the context's own). */
 cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream);
-/* Tuning knobs (launch geometry); unknown keys -> CQ_ERR_INVALID_ARG.  Results never
- * depend on them beyond f32 summation order. */
+/* Tuning knobs (launch geometry, decoder choice); unknown keys -> CQ_ERR_INVALID_ARG.  Results stay
+ * inside each activation mode's stated distance from the CPU path whatever the options are. */
 cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
+/* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl (launch geometry of the
+ * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
+ * row); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
+ * GEMM has seen: the weights must then stay unchanged, or be rewritten only through cq_* entry points, or
+ * cq_invalidate_weight_cache must be called); gemm_int8 (CQ_ACT_Q8_1 with m > 8: 1 = int8 tensor-core GEMM,
+ * default; 0 = decode kernels, eight rows a pass); attn_variant; comm_poll_limit (polls before the reducing
+ * norm gives up on a peer's data, default about one second's worth); comm_cluster. */
+/* Grows the context's scratch memory to at least `bytes` now, so that no later call has to (scratch cannot
+ * grow while the stream is being captured: such a call fails with CQ_ERR_INVALID_ARG and leaves the capture
+ * intact).  A block outgrown while graphs made by cq_capture_end exist is kept until the last of them is
+ * destroyed, because they point into it; graphs the caller captured by other means are the caller's to
+ * protect (reserve up front). */
+cq_status cq_reserve(cq_ctx *ctx, size_t bytes);
+/* Drops cached f16 copies (option gemm_cache_weights) of weight matrices whose blocks start inside
+ * [blocks_dev, blocks_dev + bytes): call after rewriting such blocks by any means other than cq_quantize_rows,
+ * cq_memcpy_h2d / _d2d or cq_memset, which do it themselves. */
+cq_status cq_invalidate_weight_cache(cq_ctx *ctx, const void *blocks_dev, size_t bytes);
 cq_status cq_malloc(cq_ctx *ctx, size_t bytes, void **dptr);     /* BackendDevice.Alloc   */
 cq_status cq_free(cq_ctx *ctx, void *dptr);
 cq_status cq_malloc_host(cq_ctx *ctx, size_t bytes, void **hptr); /* pinned host memory   */
@@ -138,6 +160,12 @@ cq_status cq_quantize_q8_1(cq_ctx *ctx, const float *x_dev, int64_t m, int64_t k
 cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev,
                      int64_t m, int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n,
                      float *y_dev, int64_t ldy);
+
+/* nn.Linear.Forward (nn/linear.go:58-112) on the device: y = x . W^T + bias, bias[n] broadcast over the
+ * rows (BroadcastAdd, nn/linear.go:105-110); bias_dev may be NULL.  The decode GEMV adds the bias in its
+ * epilogue; the other routes add it with a small kernel behind the matmul. */
+cq_status cq_qlinear(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev, int64_t m, int64_t k, int64_t ldx,
+                     const void *w_blocks_dev, int64_t n, const float *bias_dev, float *y_dev, int64_t ldy);
 
 /* Same product with HOST activations and HOST result: copies x up, runs cq_qmatmul, copies
  * y back and waits.  Weights stay resident on the device (they are the layer's state).
@@ -240,7 +268,11 @@ cq_status cq_qlinear_fused(cq_ctx *ctx, int qtype, int order, const float *x_dev
  * captured graph replays).  Use set 0 and set 1 alternately (o: 0, down: 1).  Every rank must
  * issue the same sequence of calls.  The reference has no multi-device code; no counterpart.
  *   create:  allocates this rank's buffers; handle64 receives a 64-byte CUDA IPC handle;
- *   connect: takes all ranks' handles (world x 64 bytes, rank order) gathered by the host. */
+ *   connect: takes all ranks' handles (world x 64 bytes, rank order) gathered by the host.  With
+ *            all_handles = NULL the communicator is a single-process stand-in: every "peer" is this rank's
+ *            own buffer, so pushes land only in this rank's slot and the other ranks' data never arrives
+ *            (how a missing peer looks; used to exercise the bounded wait on one GPU).
+ * A push into a set that still holds an unconsumed push is refused (CQ_ERR_INVALID_ARG). */
 typedef struct cq_comm cq_comm;
 cq_status cq_comm_create(cq_ctx *ctx, int rank, int world, int64_t max_floats, cq_comm **out, void *handle64);
 cq_status cq_comm_connect(cq_ctx *ctx, cq_comm *comm, const void *all_handles);

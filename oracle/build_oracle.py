@@ -5,7 +5,8 @@
 ``build_ref()`` compiles the reference project's own CUDA source for the quantized
 path (``tensor/internal/cuda/kernels/quantized.cu`` of a gocnn/candy checkout) into
 ``_ref/quantized_sm100a.cubin`` *from where it lies*; no reference source is copied.
-The checkout location comes from ``$CANDY_REFERENCE_DIR``.  The cubin is a test
+The checkout is looked for in ``$CANDY_REFERENCE_DIR``, else in a directory named
+``reference`` beside this repository.  The cubin is a test
 fixture: GPU tests load it with the CUDA driver API to pin this oracle against code
 the reference itself ships.  (The reference's Go CPU path cannot be built here: no Go
 toolchain.  Its Metal shaders cannot be built either.)
@@ -45,8 +46,8 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def reference_dir() -> Path | None:
-    d = os.environ.get("CANDY_REFERENCE_DIR", "/root/reference")
-    p = Path(d)
+    d = os.environ.get("CANDY_REFERENCE_DIR")
+    p = Path(d) if d else HERE.parent.parent / "reference"
     return p if (p / REF_SOURCE_REL).exists() else None
 
 

@@ -5,6 +5,8 @@ follow the CPU kernels in tensor/internal/cpu/kernels/: FastRmsNormF32 (reduce.g
 RopeF32 (reduce.go:3987-4006), FastSoftmaxF32 (reduce.go:2855-2879), USiluF32 (unary.go:3353-3365,
 f64 inside), FastArgmaxF32 (reduce.go:846-862).  Sums over a row are taken with np.float32
 accumulation; their order differs from the sequential Go loops by rounding only.
+Pinned by tests/test_decoder_oracle_pins.py to the known answers of the reference's own unit tests
+(reduce_test.go, unary_test.go; the literals are in tests/golden/reduce_unary_kats.json).
 """
 from __future__ import annotations
 
@@ -35,6 +37,15 @@ def softmax(s):
     m = s.max()
     e = np.exp((s - m).astype(np.float64)).astype(f32)
     return (e * (f32(1.0) / e.sum(dtype=f32))).astype(f32)
+
+
+def argmax(x):
+    """FastArgmaxF32 (reduce.go:846-862): strict '>', so the lowest index among equal maxima."""
+    best, bi = x[0], 0
+    for i in range(1, len(x)):
+        if x[i] > best:
+            best, bi = x[i], i
+    return bi
 
 
 def silu(x):

@@ -197,7 +197,7 @@ def test_gemv_result_does_not_depend_on_launch_geometry(device, warps, stages, c
 @pytest.mark.parametrize("qt,order", QT_ORDERS)
 @pytest.mark.parametrize("n,k", [(513, 4096), (200, 11008), (64, 256), (37, 1024)])
 def test_gemv_decoder_variants(device, variant, bound, qt, order, n, k):
-    """0: three int8 activation slices (default), 1: f32 FMA decoder, 2: two slices."""
+    """0: 16-bit block fixed point (default), 1: f32 FMA decoder, 2 / 3: two / three int8 slices."""
     w, x = make_case(4000 + n + k, n, k, 1)
     x[0, :32] *= 1e-4  # a block of small activations next to ordinary ones
     x[0, 40] = 37.5    # and one dominant value inside a block

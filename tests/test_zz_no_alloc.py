@@ -39,7 +39,7 @@ def test_static_scratch_matches_regular_entry_twice_in_a_row(device):
     for seed, qt, order, m, n, k in [(11, oc.Q4_0, 0, 3, 200, 4096), (12, oc.Q4_0, 1, 1, 96, 1024),
                                      (13, oc.Q8_0, 0, 8, 64, 2048), (14, oc.Q4_0, 0, 1, 130, 32768)]:
         a, b, want = _run_both(device, qt, order, seed, m, n, k)
-        assert rel_err(a, b) < 2e-5  # same kernels, same arithmetic
+        assert rel_err(a, b) < 2e-5  # same arithmetic, same routes
         assert rel_err(a, want) < 2e-5  # and the reference CUDA arithmetic of the oracle
 
 
