@@ -250,6 +250,105 @@ def cpu_baseline(blocks_by_shape, xs, budget_s=12.0, threads=1):
             "seconds_per_sweep": el / reps}
 
 
+def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3):
+    """Checker for BASELINE config 5, run before its timing: ONE reduced step -- one layer with the 70B
+    shard shapes (d 8192, 64 q / 8 kv heads x 128, ffn 28672, Q4_0), context of `ctx_len` keys -- on every
+    rank, through the fused exchange (batch 1), through NCCL all-reduces (batch 1 and 32) or, on one GPU,
+    with no exchange.  Rank 0 gathers every rank's weight blocks and caches and compares its residual stream
+    after the layer with the CPU oracle of the UNSHARDED layer (oracle/decoder_np.sharded_layer_step: candy's
+    CPU arithmetic, row-parallel partials summed in rank order).  The oracle is only the checker here; at
+    batch 32 it checks the first and the last sequence (each costs 0.86 G scalar multiply-adds)."""
+    import ctypes as C
+    from candy_b200 import abi
+    from candy_b200.bench_workloads import _CudaArray
+    from candy_b200.decoder import DecoderConfig, QuantDecoder, rope_tables
+    cfg = DecoderConfig(n_layers=1, dim=8192, n_heads=64, n_kv_heads=8, head_dim=128, ffn=28672, vocab=0, max_ctx=ctx_len, with_head=False)
+    lib, ctx = dev._lib, dev.ctx
+    cos, sin = rope_tables(cfg)
+    torch = None
+    if world > 1:
+        import torch
+    cases = [(1, "single"), (32, "single")] if world == 1 else [(1, "fused"), (1, "nccl"), (32, "nccl")]
+    out = {"bar": 1e-3, "ranks": world, "layer": "d 8192, 64/8 heads, ffn 28672, Q4_0", "ctx": ctx_len, "cases": []}
+    worst = 0.0
+    for batch, mode in cases:
+        views = {}
+
+        def allreduce(buf, count):
+            key = buf.ptr.value
+            if key not in views:
+                views[key] = torch.as_tensor(_CudaArray(key, count), device=torch.device("cuda", local_rank))
+            dist.all_reduce(views[key])
+
+        comm = None
+        if mode == "fused":
+            comm, handle = C.c_void_p(), (C.c_char * 64)()
+            abi.check(ctx, lib.cq_comm_create(ctx, rank, world, batch * cfg.dim, C.byref(comm), handle), "comm create")
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw))
+            abi.check(ctx, lib.cq_comm_connect(ctx, comm, b"".join(handles)), "comm connect")
+            dist.barrier()
+        model = QuantDecoder(dev, cfg, seed=seed, batch=batch, rank=rank, world=world, allreduce=allreduce if mode == "nccl" else None,
+                             actmode=0 if batch <= 8 else 2, comm=comm)
+        L = model.layers[0]
+        nkv_floats = batch * cfg.max_ctx * model.kv_dim
+        lib.cq_rand_normal(ctx, L["k"].ptr, nkv_floats, 0.0, 1.0, seed + 101 + rank)
+        lib.cq_rand_normal(ctx, L["v"].ptr, nkv_floats, 0.0, 1.0, seed + 202 + rank)
+        lib.cq_rand_normal(ctx, model.x.ptr, batch * cfg.dim, 0.0, 1.0, seed + 303)  # the same on every rank
+        pos = ctx_len - 1
+        model.set_state(np.zeros(batch, dtype=np.uint32), pos)
+        dev.synchronize()
+        x0 = model.x.data().reshape(batch, cfg.dim).copy()
+        kc = L["k"].data().reshape(batch, cfg.max_ctx, model.nkv, cfg.head_dim).copy()
+        vc = L["v"].data().reshape(batch, cfg.max_ctx, model.nkv, cfg.head_dim).copy()
+        if dist is not None:
+            torch.cuda.synchronize()
+            dist.barrier()
+        if mode == "nccl":  # the library's kernels and torch's NCCL calls share one stream
+            stream = torch.cuda.Stream(device=local_rank)
+            dev.set_stream(stream.cuda_stream)
+            with torch.cuda.stream(stream):
+                model.step(advance=False)
+            stream.synchronize()
+            dev.set_stream(0)
+        else:
+            model.step(advance=False)
+        if mode == "fused":  # fold in the down projection's partials, as the next layer's first norm would
+            abi.check(ctx, lib.cq_add_rmsnorm_reduce(ctx, comm, 1, model.x.ptr, L["attn_norm"].ptr, batch, cfg.dim, cfg.eps, model.xn.ptr), "final reduce")
+        if dist is not None:
+            torch.cuda.synchronize()
+        dev.synchronize()
+        x2 = model.x.data().reshape(batch, cfg.dim)
+        if mode != "fused":
+            x2 = x2 + model.d.data().reshape(batch, cfg.dim)
+        rows = sorted({0, batch - 1})
+        shard = {"wqkv": L["wqkv"].data(), "wo": L["wo"].data(), "wgu": L["wgu"].data(), "wdown": L["wdown"].data(),
+                 "k": kc[rows], "v": vc[rows], "nq": model.nq, "nkv": model.nkv, "ffn": model.ffn}
+        shards = [shard]
+        if dist is not None:
+            shards = [None] * world
+            dist.all_gather_object(shards, shard)
+        err = None
+        if rank == 0:
+            from oracle import decoder_np as dn  # the checker
+            err = 0.0
+            for i, b in enumerate(rows):
+                per_rank = [dict(s, k=s["k"][i], v=s["v"][i]) for s in shards]
+                want = dn.sharded_layer_step(cfg, model.qtype, model.order, per_rank, x0[b], pos, cos, sin)
+                err = max(err, float(np.abs(x2[b] - want).max() / np.abs(want).max()))
+            worst = max(worst, err)
+            out["cases"].append({"batch": batch, "exchange": mode, "rows_checked": rows, "max_rel_err": err,
+                                 "linear_mode": "f32 activations" if batch <= 8 else "f16 operands (tensor cores)"})
+        del model, shards, shard
+        dev.synchronize()
+        if comm is not None:
+            dist.barrier()
+            lib.cq_comm_destroy(ctx, comm)
+    out["max_rel_err"] = worst
+    out["pass"] = bool(worst <= out["bar"])
+    return out
+
+
 def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -368,7 +467,11 @@ def run_ours(args):
         if world == 1:
             extra("prefill_gemm", lambda: bw.prefill_gemm(dev, peak, measured_peak_tflops()))
             extra("decode_7b", lambda: bw.decode_7b(dev, peak))
+        if not args.no_cpu:  # parity of the config-5 layer against the CPU oracle, checked before it is timed
+            extra("tp_layer_70b_parity", lambda: tp_layer_parity(dev, dist, rank, world, local_rank))
         extra("tp_layer_70b", lambda: bw.tp_layer_70b(dev, dist, rank, world, local_rank, peak))
+        if isinstance(line.get("tp_layer_70b"), dict) and "tp_layer_70b_parity" in line:
+            line["tp_layer_70b"]["parity"] = line.pop("tp_layer_70b_parity")
     if cpu_inputs is not None:
         blocks, xs = cpu_inputs
         line["cpu_baseline"] = cpu_baseline(blocks, xs, threads=1)

@@ -82,6 +82,7 @@ SIGNATURES = {
     "cq_capture_end": [_vp, C.POINTER(_vp)],
     "cq_graph_launch": [_vp, _vp],
     "cq_graph_destroy": [_vp, _vp],
+    "cq_measure_i8_mma_peak": [_vp, _int, C.POINTER(C.c_double)],
     "cq_timer_start": [_vp],
     "cq_timer_stop": [_vp, C.POINTER(C.c_float)],
 }

@@ -152,6 +152,9 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemv_variant")) t.gemv_variant = (int)value;
     else if (!strcmp(key, "comm_poll_limit")) t.comm_poll_limit = (int)value;
     else if (!strcmp(key, "comm_cluster")) t.comm_cluster = (int)value;
+    else if (!strcmp(key, "gemm_int8")) t.gemm_int8 = (int)value;
+    else if (!strcmp(key, "i8_min_rows_f32")) t.i8_min_rows_f32 = (int)value;
+    else if (!strcmp(key, "i8_min_rows_q8_1")) t.i8_min_rows_q8_1 = (int)value;
     else if (!strcmp(key, "gemv_multirow")) t.gemv_multirow = (int)value;
     else if (!strcmp(key, "gemv_coop")) t.gemv_coop = (int)value;
     else if (!strcmp(key, "gemv_rpt")) t.gemv_rpt = (int)value;
@@ -323,6 +326,11 @@ cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float
     CQ_ENTER(ctx);
     cq_status s = check_matmul_args(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
     if (s != CQ_OK) return s;
+    // Integer dots on the tensor cores: one weight pass for the whole batch, in the activation mode's own numerics.
+    if (actmode != CQ_ACT_F16 && ctx->tune.gemm_int8 && !ctx->fuse.on && ctx->push.world == 0 && ctx->tune.gemv_variant == 0 &&
+        m >= (actmode == CQ_ACT_Q8_1 ? ctx->tune.i8_min_rows_q8_1 : ctx->tune.i8_min_rows_f32) &&
+        qgemm_i8_supported(qtype, k, w_blocks_dev, x_dev, ldx))
+        return launch_qgemm_i8(ctx, qtype, order, actmode == CQ_ACT_Q8_1 ? 1 : 0, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
     if (m <= 8 && actmode != CQ_ACT_F16) return launch_gemv(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
     return launch_gemm(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
 }

@@ -35,6 +35,9 @@ struct GemvTuning {
     int gemv_coop = 1;      // slice activations once per CTA through shared memory when rows share a CTA
     int comm_poll_limit = 0;  // polls before the reducing norm gives up on a (value, tag) pair; 0 = about a second
     int comm_cluster = 0;     // 1: one CTA per row in the reducing norm instead of a cluster of eight
+    int gemm_int8 = 1;        // 1: the int8 tensor-core kernel serves CQ_ACT_Q8_1 from i8_min_rows_q8_1 rows and CQ_ACT_F32 from i8_min_rows_f32 rows
+    int i8_min_rows_f32 = 3;
+    int i8_min_rows_q8_1 = 2;
     int gemv_multirow = 1;  // 0: one launch (one weight pass) per activation row even for m = 2..8
     int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices
 };
@@ -134,6 +137,10 @@ cq_status launch_gemv_more(cq_ctx *ctx, int qtype, int order, int actmode, const
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w);
 cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
                                     float *y, int64_t ldy);
+// Integer-dot GEMM on tcgen05.mma kind::i8 (gemm_i8_tmem.cu): mode 1 = Q8_1 activation columns, mode 0 = 15-bit planes.
+bool qgemm_i8_supported(int qtype, int64_t k, const void *w, const float *x, int64_t ldx);
+cq_status launch_qgemm_i8(cq_ctx *ctx, int qtype, int order, int mode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
+                          float *y, int64_t ldy);
 cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,
                       int64_t ldx, const void *w, int64_t n, float *y, int64_t ldy);
 

@@ -96,8 +96,9 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
  * row); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
  * GEMM has seen: the weights must then stay unchanged, or be rewritten only through cq_* entry points, or
- * cq_invalidate_weight_cache must be called); gemm_int8 (CQ_ACT_Q8_1 with m > 8: 1 = int8 tensor-core GEMM,
- * default; 0 = decode kernels, eight rows a pass); attn_variant; comm_poll_limit (polls before the reducing
+ * cq_invalidate_weight_cache must be called); gemm_int8 (1, default: batches of i8_min_rows_q8_1 (2) or more
+ * rows in CQ_ACT_Q8_1 and of i8_min_rows_f32 (3) or more in CQ_ACT_F32 run the int8 tensor-core kernel, one
+ * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant; comm_poll_limit (polls before the reducing
  * norm gives up on a peer's data, default about one second's worth); comm_cluster. */
 /* Grows the context's scratch memory to at least `bytes` now, so that no later call has to (scratch cannot
  * grow while the stream is being captured: such a call fails with CQ_ERR_INVALID_ARG and leaves the capture
@@ -155,7 +156,8 @@ cq_status cq_quantize_q8_1(cq_ctx *ctx, const float *x_dev, int64_t m, int64_t k
  * for the reference's unlaunched CUDA entry points dequantize_mul_mat_vec_q4_0_cuda
  * (quantized.cu:1323), mul_mat_vec_q4_0_q8_1_cuda1..8 (quantized.cu:2874-3519) and
  * mul_mat_q4_0 / mul_mat_q8_0 (quantized.cu:4477, :4529).
- * m <= 8 runs the decode GEMV, larger m the prefill GEMM.
+ * One row runs the streaming decode GEMV; small batches in CQ_ACT_F32 / CQ_ACT_Q8_1 run the int8 tensor-core
+ * kernel (integer dots per quant block, scaled per block as the mode says), CQ_ACT_F16 the f16 tensor-core GEMMs.
  * Preconditions: k % 32 == 0, k >= 32, m, n >= 1, ldx >= k, ldy >= n. */
 cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev,
                      int64_t m, int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n,
@@ -297,6 +299,11 @@ cq_status cq_capture_begin(cq_ctx *ctx);
 cq_status cq_capture_end(cq_ctx *ctx, cq_graph **out);
 cq_status cq_graph_launch(cq_ctx *ctx, cq_graph *g);
 cq_status cq_graph_destroy(cq_ctx *ctx, cq_graph *g);
+/* Measures the int8 tensor-pipe ceiling on this GPU: every SM issues `iters` x 4 back-to-back
+ * tcgen05.mma kind::i8 (s8 x s8 -> s32, M 128, N 256, K 32) on operands resident in shared memory, no
+ * global traffic and no epilogue.  *tera_ops receives 10^12 integer operations per second (2 per
+ * multiply-add).  A plain GEMM can only reach less; it is the denominator for the int8 prefill figures. */
+cq_status cq_measure_i8_mma_peak(cq_ctx *ctx, int iters, double *tera_ops);
 /* CUDA-event stopwatch on the context's stream: stop waits for the stream and returns the
  * device time in milliseconds between the two marks. */
 cq_status cq_timer_start(cq_ctx *ctx);

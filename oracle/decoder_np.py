@@ -99,3 +99,48 @@ class OracleDecoder:
         xn = rmsnorm(x, ones, cfg.eps)
         logits = self.lin(xn, self.wout, cfg.vocab)
         return logits
+
+
+def sharded_layer_step(cfg, qtype, order, shards, x, pos, cos, sin):
+    """One decoder layer for one sequence, computed from tensor-parallel SHARDS of its weights: the
+    unsharded layer's arithmetic with the row-parallel outputs summed in rank order, which is what an
+    all-reduce over the ranks yields.  `shards`: per rank a dict with the Q-blocks `wqkv` ([q heads; k heads;
+    v heads] of that rank), `wo`, `wgu` (gate/up rows interleaved), `wdown` (k zero-padded to a multiple of
+    256), the rank's key / value cache `k`, `v` as [ctx, nkv, head_dim] holding positions < pos, and its
+    `nq`, `nkv`, `ffn`.  Returns the residual stream after the layer (x + attention + feed-forward)."""
+    hd, dim = cfg.head_dim, cfg.dim
+    ones = np.ones(dim, dtype=f32)
+
+    def lin(v, blocks, n):
+        return oc.qmatmul(qtype, order, v.reshape(1, -1), blocks, n, nthreads=16)[0]
+
+    xn = rmsnorm(x.astype(f32), ones, cfg.eps)
+    o = None
+    for s in shards:
+        nq, nkv = s["nq"], s["nkv"]
+        qkv = lin(xn, s["wqkv"], (nq + 2 * nkv) * hd)
+        q = rope(qkv[: nq * hd].reshape(nq, hd), cos[pos], sin[pos])
+        k = rope(qkv[nq * hd:(nq + nkv) * hd].reshape(nkv, hd), cos[pos], sin[pos])
+        v = qkv[(nq + nkv) * hd:].reshape(nkv, hd)
+        K = np.concatenate([s["k"][:pos], k[None]], axis=0)
+        V = np.concatenate([s["v"][:pos], v[None]], axis=0)
+        att = np.empty((nq, hd), dtype=f32)
+        group = nq // nkv
+        for h in range(nq):
+            sc = (K[:, h // group] @ q[h]).astype(f32) * f32(1.0 / np.sqrt(hd))
+            p = softmax(sc)
+            att[h] = (p[:, None] * V[:, h // group]).sum(axis=0, dtype=f32)
+        part = lin(att.reshape(-1), s["wo"], dim)
+        o = part if o is None else (o + part).astype(f32)
+    x1 = (x + o).astype(f32)
+    xn = rmsnorm(x1, ones, cfg.eps)
+    d = None
+    for s in shards:
+        gu = lin(xn, s["wgu"], 2 * s["ffn"])
+        h_ = silu(gu[0::2]) * gu[1::2]
+        kpad = s["wdown"].size // dim // oc.BLOCK_BYTES[qtype] * 32
+        hp = np.zeros(kpad, dtype=f32)
+        hp[: s["ffn"]] = h_
+        part = lin(hp, s["wdown"], dim)
+        d = part if d is None else (d + part).astype(f32)
+    return (x1 + d).astype(f32)

@@ -252,3 +252,80 @@ def test_attention_with_fused_rotary_step_equals_the_two_operators(device, batch
         assert rel_err(got[0], ref[0]) < 2e-6
         np.testing.assert_allclose(got[1], ref[1], rtol=0, atol=1e-6)
         np.testing.assert_array_equal(got[2], ref[2])
+
+
+def test_7b_full_depth_three_positions(device):
+    """BASELINE config 4's model at its full 32 layers (d 4096, 32 heads x 128, SwiGLU 11008, vocab 32000,
+    Q4_0): logits of three teacher-forced positions against the CPU oracle, under the 1e-3 bar."""
+    from candy_b200.decoder import DecoderConfig
+    cfg = DecoderConfig(n_layers=32, dim=4096, n_heads=32, n_kv_heads=32, head_dim=128, ffn=11008, vocab=32000, max_ctx=8)
+    model, ref = build(device, cfg, seed=2)
+    assert model.fuse  # the fused norm / SiLU linears are the route a 7B decode takes
+    for pos, tok in enumerate([17, 31999, 4242]):
+        model.set_state(np.array([tok], dtype=np.uint32), pos)
+        model.step()
+        device.synchronize()
+        want = ref.step(tok, pos)
+        assert rel_err(model.read_logits()[0], want) <= REL_TOL, f"position {pos}"
+
+
+@pytest.mark.parametrize("batch", [1, 3, 12])
+def test_70b_shape_single_layer(device, batch):
+    """One layer of BASELINE config 5's shape (d 8192, 64 q / 8 kv heads x 128, ffn 28672, Q4_0), unsharded,
+    at a position inside a noise-filled cache: the residual stream after the layer against the CPU oracle.
+    Batch 1 runs the f32-activation GEMVs, batches 3 and 12 the narrow tensor-core linears (f16 operands),
+    as the decoder routes them."""
+    from candy_b200.decoder import DecoderConfig, QuantDecoder, rope_tables
+    from oracle.decoder_np import sharded_layer_step
+    cfg = DecoderConfig(n_layers=1, dim=8192, n_heads=64, n_kv_heads=8, head_dim=128, ffn=28672, vocab=0, max_ctx=24, with_head=False)
+    lib, ctx = device._lib, device.ctx
+    model = QuantDecoder(device, cfg, seed=3, batch=batch)
+    L = model.layers[0]
+    nkv_floats = batch * cfg.max_ctx * model.kv_dim
+    lib.cq_rand_normal(ctx, L["k"].ptr, nkv_floats, 0.0, 1.0, 11)
+    lib.cq_rand_normal(ctx, L["v"].ptr, nkv_floats, 0.0, 1.0, 12)
+    lib.cq_rand_normal(ctx, model.x.ptr, batch * cfg.dim, 0.0, 1.0, 13)
+    pos = 20
+    model.set_state(np.zeros(batch, dtype=np.uint32), pos)
+    device.synchronize()
+    x0 = model.x.data().reshape(batch, cfg.dim).copy()
+    kc = L["k"].data().reshape(batch, cfg.max_ctx, model.nkv, cfg.head_dim).copy()
+    vc = L["v"].data().reshape(batch, cfg.max_ctx, model.nkv, cfg.head_dim).copy()
+    model.step(advance=False)
+    device.synchronize()
+    got = model.x.data().reshape(batch, cfg.dim) + model.d.data().reshape(batch, cfg.dim)
+    cos, sin = rope_tables(cfg)
+    blocks = {k: L[k].data() for k in ("wqkv", "wo", "wgu", "wdown")}
+    for b in sorted({0, batch - 1}):
+        shard = dict(blocks, k=kc[b], v=vc[b], nq=model.nq, nkv=model.nkv, ffn=model.ffn)
+        want = sharded_layer_step(cfg, model.qtype, model.order, [shard], x0[b], pos, cos, sin)
+        assert rel_err(got[b], want) <= REL_TOL, f"row {b}"
+
+
+def test_position_outside_the_cache_is_clamped_and_reported(device):
+    """A device-resident position at or beyond max_ctx must not index outside the caches: the kernels clamp
+    it, flag it, and cq_synchronize answers CQ_ERR_INVALID_ARG; the next call is clean again."""
+    from candy_b200 import abi
+    from candy_b200.backend import CudaDevice, RawBuffer
+    dev = CudaDevice(0)  # its own context: the error word of the shared test device stays untouched
+    lib, ctx = dev._lib, dev.ctx
+    nq, nkv, hd, max_ctx = 2, 1, 128, 4
+    qkv = dev.storage_from_slice(np.ones((nq + 2 * nkv) * hd, dtype=np.float32))
+    cos, sin = dev.storage_from_slice(np.ones(max_ctx * hd // 2, dtype=np.float32)), dev.zeros(max_ctx * hd // 2)
+    kc, vc = dev.zeros(max_ctx * nkv * hd), dev.zeros(max_ctx * nkv * hd)
+    scratch = dev.alloc(lib.cq_decode_attention_scratch_floats(1, nq, hd, max_ctx))
+    out = dev.alloc(nq * hd)
+    pos = RawBuffer(dev, 4)
+    for bad in (max_ctx, 1000000, -3):
+        pv = np.array([bad], dtype=np.int32)
+        dev._check(lib.cq_memcpy_h2d(ctx, pos.ptr, pv.ctypes.data, 4), "pos")
+        assert lib.cq_rope_store_kv(ctx, qkv.ptr, 1, nq, nkv, hd, cos.ptr, sin.ptr, pos.ptr, kc.ptr, vc.ptr, max_ctx) == 0
+        assert lib.cq_synchronize(ctx) == abi.ERR_INVALID_ARG
+        assert b"max_ctx" in lib.cq_last_error(ctx)
+        assert lib.cq_decode_attention_rope(ctx, qkv.ptr, 1, nq, nkv, hd, cos.ptr, sin.ptr, pos.ptr, kc.ptr, vc.ptr, max_ctx, scratch.ptr, out.ptr) == 0
+        assert lib.cq_synchronize(ctx) == abi.ERR_INVALID_ARG
+    pv = np.array([max_ctx - 1], dtype=np.int32)
+    dev._check(lib.cq_memcpy_h2d(ctx, pos.ptr, pv.ctypes.data, 4), "pos")
+    assert lib.cq_rope_store_kv(ctx, qkv.ptr, 1, nq, nkv, hd, cos.ptr, sin.ptr, pos.ptr, kc.ptr, vc.ptr, max_ctx) == 0
+    assert lib.cq_synchronize(ctx) == 0
+    dev.close()

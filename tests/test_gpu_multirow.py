@@ -12,6 +12,14 @@ pytestmark = pytest.mark.gpu
 QT_ORDERS = [(oc.Q4_0, 0), (oc.Q4_0, 1), (oc.Q8_0, 0)]
 
 
+@pytest.fixture(autouse=True)
+def _decode_kernels_only(device):
+    """These tests are about the multi-row streaming GEMV: keep the int8 tensor-core kernel out of the way."""
+    device.set_option("gemm_int8", 0)
+    yield
+    device.set_option("gemm_int8", 1)
+
+
 def run(device, qt, order, x, blocks, n, actmode, ldx=None, ldy=None, bias=None):
     from candy_b200.backend import QStorage
     m, k = x.shape
