@@ -5,11 +5,11 @@
 
 Workload (N = 1): BASELINE config 2, the Q4_0 decode-GEMV sweep with M = 1 over
 (N,K) in {(4096,4096),(11008,4096),(4096,11008),(32000,4096)}, W ~ N(0,0.02) quantized to
-Q4_0 by the library's GPU quantizer, x ~ N(0,1), seed 0.  One *step* is one pass over the
-four shapes (four kernel launches).  Every shape cycles through a ring of distinct copies of
-its weight matrix (>= 512 MiB per shape, four times the L2), so no launch finds its weights in
-cache.  Steps are recorded once into CUDA graphs and replayed; time is CUDA-event time on the
-launching stream.
+Q4_0 by the library's GPU quantizer, x ~ N(0,1), seed 0.  One *step* is 400 passes over the
+four shapes (1600 kernel launches, about 16 ms), so that the driver's 20 steps make a timed region
+of a third of a second.  Every shape cycles through a ring of distinct copies of its weight matrix
+(>= 512 MiB per shape, four times the L2), so no launch finds its weights in cache.  Sweeps are
+recorded once into a CUDA graph and replayed; time is CUDA-event time on the launching stream.
 
 Printed line: metric = aggregate algorithmic GB/s of the sweep (weight blocks + x + y bytes
 per launch, divided by device time); `roofline` is the dominant kernel (the 32000x4096 GEMV)
@@ -39,9 +39,12 @@ sys.path.insert(0, str(ROOT))
 
 SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # (N, K), M = 1
 RING_BYTES = 512 << 20
-GRAPH_STEPS = 100
+SWEEPS_PER_STEP = 400   # one step = this many passes over the four shapes (1600 kernel launches, about 16 ms of device time)
+GRAPH_SWEEPS = 100      # sweeps recorded per CUDA graph; a step replays it SWEEPS_PER_STEP / GRAPH_SWEEPS times
 Q4_0, Q8_0 = 2, 8
 ORDER = 0  # the Go CPU path's element order
+WORKLOAD = ("BASELINE config 2: Q4_0 decode GEMV sweep, M=1, (N,K) in {(4096,4096),(11008,4096),(4096,11008),(32000,4096)}, "
+            "W~N(0,0.02)->Q4_0, x~N(0,1), seed 0")
 
 
 def gemv_bytes(n, k, m=1, bb=18):
@@ -250,7 +253,7 @@ def cpu_baseline(blocks_by_shape, xs, budget_s=12.0, threads=1):
             "seconds_per_sweep": el / reps}
 
 
-def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3):
+def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3, tp=None):
     """Checker for BASELINE config 5, run before its timing: ONE reduced step -- one layer with the 70B
     shard shapes (d 8192, 64 q / 8 kv heads x 128, ffn 28672, Q4_0), context of `ctx_len` keys -- on every
     rank, through the fused exchange (batch 1), through NCCL all-reduces (batch 1 and 32) or, on one GPU,
@@ -260,7 +263,6 @@ def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3):
     batch 32 it checks the first and the last sequence (each costs 0.86 G scalar multiply-adds)."""
     import ctypes as C
     from candy_b200 import abi
-    from candy_b200.bench_workloads import _CudaArray
     from candy_b200.decoder import DecoderConfig, QuantDecoder, rope_tables
     cfg = DecoderConfig(n_layers=1, dim=8192, n_heads=64, n_kv_heads=8, head_dim=128, ffn=28672, vocab=0, max_ctx=ctx_len, with_head=False)
     lib, ctx = dev._lib, dev.ctx
@@ -272,13 +274,8 @@ def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3):
     out = {"bar": 1e-3, "ranks": world, "layer": "d 8192, 64/8 heads, ffn 28672, Q4_0", "ctx": ctx_len, "cases": []}
     worst = 0.0
     for batch, mode in cases:
-        views = {}
-
-        def allreduce(buf, count):
-            key = buf.ptr.value
-            if key not in views:
-                views[key] = torch.as_tensor(_CudaArray(key, count), device=torch.device("cuda", local_rank))
-            dist.all_reduce(views[key])
+        def allreduce(buf, count):  # the library's NCCL all-reduce
+            abi.check(ctx, lib.cq_allreduce_sum_f32(ctx, tp, buf.ptr, count), "allreduce")
 
         comm = None
         if mode == "fused":
@@ -304,15 +301,7 @@ def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3):
         if dist is not None:
             torch.cuda.synchronize()
             dist.barrier()
-        if mode == "nccl":  # the library's kernels and torch's NCCL calls share one stream
-            stream = torch.cuda.Stream(device=local_rank)
-            dev.set_stream(stream.cuda_stream)
-            with torch.cuda.stream(stream):
-                model.step(advance=False)
-            stream.synchronize()
-            dev.set_stream(0)
-        else:
-            model.step(advance=False)
+        model.step(advance=False)
         if mode == "fused":  # fold in the down projection's partials, as the next layer's first norm would
             abi.check(ctx, lib.cq_add_rmsnorm_reduce(ctx, comm, 1, model.x.ptr, L["attn_norm"].ptr, batch, cfg.dim, cfg.eps, model.xn.ptr), "final reduce")
         if dist is not None:
@@ -349,6 +338,51 @@ def tp_layer_parity(dev, dist, rank, world, local_rank, ctx_len=32, seed=3):
     return out
 
 
+def reference_cuda_baseline(dev, wl, reps=40):
+    """A GPU-side anchor beside the CPU baseline: the reference's OWN decode kernels
+    (tensor/internal/cuda/kernels/quantized.cu compiled unchanged for sm_100a into oracle/_ref by
+    oracle/build_oracle.py) timed on the same box, same config-2 shapes, same rings of weight copies, with the
+    launch shapes the parity tests validated (oracle/ref_cuda.py): dequantize_mul_mat_vec_q4_0_cuda (f32
+    activations) and quantize_q8_1 + mul_mat_vec_q4_0_q8_1_cuda1.  The reference never launches them itself."""
+    from oracle import ref_cuda
+    if not ref_cuda.CUBIN.exists():
+        return {"unavailable": "oracle/_ref/quantized_sm100a.cubin not built (no reference checkout at build time)"}
+    from candy_b200.backend import RawBuffer
+    rk = ref_cuda.RefKernels(dev.ordinal)
+    out = {"kernels": "the reference's quantized.cu, unchanged, sm_100a", "shapes": []}
+    tot = {"dmmv": 0.0, "mmvq": 0.0}
+    for i, (n, k) in enumerate(wl.shapes):
+        ring = [b.ptr.value for b in wl.rings[i]]
+        x, y = wl.xs[i].ptr.value, wl.ys[i].ptr.value
+        act = RawBuffer(dev, (k // 32) * 36)
+        cur = [0]
+
+        def dmmv():
+            for _ in range(reps):
+                rk.dequantize_mul_mat_vec("q4_0", ring[cur[0] % len(ring)], x, y, k, n, sync=False)
+                cur[0] += 1
+
+        def mmvq():
+            for _ in range(reps):
+                rk.quantize_q8_1(x, act.ptr.value, k, 1, sync=False)
+                rk.mul_mat_vec_q8_1("q4_0", ring[cur[0] % len(ring)], act.ptr.value, y, k, n, sync=False)
+                cur[0] += 1
+
+        dev.synchronize()
+        dmmv()
+        t_d = rk.timed_ms(dmmv) / reps * 1e3
+        mmvq()
+        t_q = rk.timed_ms(mmvq) / reps * 1e3
+        tot["dmmv"] += t_d
+        tot["mmvq"] += t_q
+        out["shapes"].append({"n": n, "k": k, "dmmv_us": round(t_d, 2), "dmmv_gbs": round(gemv_bytes(n, k) / t_d / 1e3, 1),
+                              "q8_1_mmvq_us": round(t_q, 2), "q8_1_mmvq_gbs": round(gemv_bytes(n, k) / t_q / 1e3, 1)})
+    sweep = sum(gemv_bytes(n, k) for n, k in wl.shapes)
+    out["sweep_gbs_dmmv"] = round(sweep / tot["dmmv"] / 1e3, 1)
+    out["sweep_gbs_q8_1_mmvq"] = round(sweep / tot["mmvq"] / 1e3, 1)
+    return out
+
+
 def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -366,17 +400,13 @@ def run_ours(args):
         wl.launch(i)
     dev.synchronize()
 
-    g_main = wl.capture(GRAPH_STEPS) if K >= GRAPH_STEPS else None
-    g_tail = wl.capture(K % GRAPH_STEPS) if K % GRAPH_STEPS else None
-    g_warm = wl.capture(W)
+    g_main = wl.capture(GRAPH_SWEEPS)
+    replays_per_step = SWEEPS_PER_STEP // GRAPH_SWEEPS
 
     def timed_region():
-        if g_main is not None:
-            wl.run_graph(g_main, K // GRAPH_STEPS)
-        if g_tail is not None:
-            wl.run_graph(g_tail, 1)
+        wl.run_graph(g_main, K * replays_per_step)
 
-    wl.run_graph(g_warm)
+    wl.run_graph(g_main, W * replays_per_step)  # W untimed warm-up steps
     dev.synchronize()
     dist_barrier(dist)
     with ClockSampler(local_rank) as clocks:
@@ -384,12 +414,12 @@ def run_ours(args):
     dist_barrier(dist)
     ms = dist_max(dist, ms, local_rank)
     sweep_bytes = sum(gemv_bytes(n, k) for n, k in SHAPES)
-    value = world * sweep_bytes * K / (ms * 1e-3) / 1e9
+    value = world * sweep_bytes * K * SWEEPS_PER_STEP / (ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak_gbs()
 
     # ---- per-kernel timing: each shape alone, same ring discipline ------------------------
     per_shape = []
-    launches = max(200, min(2000, K))
+    launches = 2000
     for i, (n, k) in enumerate(SHAPES):
         g = wl.capture(100, which=i)
         wl.run_graph(g, 2)
@@ -407,7 +437,7 @@ def run_ours(args):
                 "algorithmic_bytes": per_shape[dom]["bytes"]}
 
     # ---- end to end through the host-buffer entry point -----------------------------------
-    e2e_steps = max(3, min(K, 200))
+    e2e_steps = 200  # host-buffer sweeps (a sweep = the four shapes once)
     hx, hy = [], []
     for (n, k) in SHAPES:
         px, py = C.c_void_p(), C.c_void_p()
@@ -440,21 +470,22 @@ def run_ours(args):
         "metric": "q4_0_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "BASELINE config 2: Q4_0 decode GEMV sweep, M=1, (N,K) in "
-                               "{(4096,4096),(11008,4096),(4096,11008),(32000,4096)}, W~N(0,0.02)->Q4_0, x~N(0,1), seed 0",
-                   "element_order": "go_interleaved", "actmode": "f32",
+        "config": {"workload": WORKLOAD, "element_order": "go_interleaved", "actmode": "f32",
+                   "step": f"{SWEEPS_PER_STEP} passes over the four shapes ({SWEEPS_PER_STEP * len(SHAPES)} launches); the driver's 20 steps time about a third of a second",
                    "l2_defeat": f"inputs larger than L2: each shape cycles a ring of weight copies >= {RING_BYTES >> 20} MiB",
                    "sharding": "none" if world == 1 else f"rows of an {world}x taller layer, one shard per GPU, no collective"},
         "frac_of_peak": round(value / world / peak, 4), "frac_of_8000": round(value / world / 8000.0, 4),
-        "roofline": roofline, "per_shape": per_shape, "e2e": e2e, "gpu_launches": K * len(SHAPES),
+        "roofline": roofline, "per_shape": per_shape, "e2e": e2e, "gpu_launches": K * SWEEPS_PER_STEP * len(SHAPES),
         "clocks": clocks.summary(),
     }
     cpu_inputs = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu_inputs = ([q.data() for q in wl.qs0], [x.data().reshape(1, -1) for x in wl.xs])
-    for g in (g_main, g_tail, g_warm):
-        if g is not None:
-            lib.cq_graph_destroy(ctx, g)
+        try:  # the reference's own CUDA kernels on the same box: a baseline leg like cpu_baseline, never the product path
+            line["ref_cuda_baseline"] = reference_cuda_baseline(dev, wl)
+        except Exception as e:  # noqa: BLE001
+            line["ref_cuda_baseline"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    lib.cq_graph_destroy(ctx, g_main)
     del wl  # free the rings before the secondary workloads
     if not args.skip_extras:
         from candy_b200 import bench_workloads as bw
@@ -467,9 +498,15 @@ def run_ours(args):
         if world == 1:
             extra("prefill_gemm", lambda: bw.prefill_gemm(dev, peak, measured_peak_tflops()))
             extra("decode_7b", lambda: bw.decode_7b(dev, peak))
+        tp = None
+        if world > 1:
+            try:
+                tp = bw.tp_connect(dev, dist, rank, world)
+            except Exception as e:  # noqa: BLE001
+                line["tp_connect_error"] = f"{type(e).__name__}: {e}"[:300]
         if not args.no_cpu:  # parity of the config-5 layer against the CPU oracle, checked before it is timed
-            extra("tp_layer_70b_parity", lambda: tp_layer_parity(dev, dist, rank, world, local_rank))
-        extra("tp_layer_70b", lambda: bw.tp_layer_70b(dev, dist, rank, world, local_rank, peak))
+            extra("tp_layer_70b_parity", lambda: tp_layer_parity(dev, dist, rank, world, local_rank, tp=tp))
+        extra("tp_layer_70b", lambda: bw.tp_layer_70b(dev, dist, rank, world, local_rank, peak, tp=tp))
         if isinstance(line.get("tp_layer_70b"), dict) and "tp_layer_70b_parity" in line:
             line["tp_layer_70b"]["parity"] = line.pop("tp_layer_70b_parity")
     if cpu_inputs is not None:
@@ -545,8 +582,8 @@ def run_reference(args):
         "impl": "reference", "metric": "q4_0_gemv_hbm_gbs", "value": round(value, 4), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BASELINE config 2: Q4_0 decode GEMV sweep, M=1 (bounded row sample per step)",
-                   "element_order": "go_interleaved", "actmode": "f32"},
+        "config": {"workload": WORKLOAD, "element_order": "go_interleaved", "actmode": "f32",
+                   "step": "one pass over the four shapes" + ("" if frac >= 1.0 else f", first {frac:.4f} of each shape's rows")},
         "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "host_cores_available": os.cpu_count(),
@@ -652,8 +689,8 @@ def main():
         args.warmup = 3 if args.warmup is None else max(args.warmup, 0)
         run_reference(args)
     else:
-        args.steps = 20000 if args.steps is None else args.steps
-        args.warmup = 200 if args.warmup is None else max(args.warmup, 3)
+        args.steps = 50 if args.steps is None else args.steps
+        args.warmup = 3 if args.warmup is None else max(args.warmup, 3)
         run_ours(args)
 
 

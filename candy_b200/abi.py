@@ -78,6 +78,11 @@ SIGNATURES = {
     "cq_qmatmul_push": [_vp, _vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64],
     "cq_qlinear_fused": [_vp, _int, _int, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp, _i64, _int, _vp, _i64],
     "cq_add_rmsnorm_reduce": [_vp, _vp, _int, _vp, _vp, _i64, _i64, C.c_float, _vp],
+    "cq_tp_unique_id": [_vp, _vp],
+    "cq_tp_init": [_vp, _int, _int, _vp, _sz, C.POINTER(_vp)],
+    "cq_tp_destroy": [_vp, _vp],
+    "cq_allreduce_sum_f32": [_vp, _vp, _vp, _i64],
+    "cq_tp_wait": [_vp, _vp, _int],
     "cq_capture_begin": [_vp],
     "cq_capture_end": [_vp, C.POINTER(_vp)],
     "cq_graph_launch": [_vp, _vp],

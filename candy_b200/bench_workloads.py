@@ -53,62 +53,74 @@ def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: 
 
 def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512, 2048), n: int = 11008, k: int = 4096, seed: int = 1,
                  calls: int = 16):
-    """BASELINE config 3: Y = X . W^T for M in {16,128,512,2048}, N=11008, K=4096, Q4_0 and Q8_0, CQ_ACT_F16.
-    Each figure is the whole cq_qmatmul call (activation conversion, any weight conversion, GEMM, partial-sum
-    kernel) timed as replays of a CUDA graph of `calls` calls that cycle through eight copies of the weights
-    (more than L2).  `frac_of_roofline` = max(algorithmic bytes / measured copy peak, flops / measured bf16
-    burst peak) / measured time."""
+    """BASELINE config 3: Y = X . W^T for M in {16,128,512,2048}, N=11008, K=4096, Q4_0 and Q8_0, in two
+    numerics: CQ_ACT_F16 (f16 operands, f32 accumulate, tcgen05 kind::f16) and CQ_ACT_Q8_1 (the reference CUDA
+    kernels' integer dots: Q8_1 activations, tcgen05 kind::i8, one MMA per quant block, per-block scaling on the
+    CUDA cores).  Each figure is the whole cq_qmatmul call (activation pre-pass, any weight conversion, GEMM,
+    partial-sum kernel) timed as replays of a CUDA graph of `calls` calls that cycle through eight copies of the
+    weights (more than L2).  `frac_of_roofline` = max(algorithmic bytes / measured copy peak, operations /
+    measured tensor peak) / measured time; the tensor peak is the measured bf16 burst figure for the f16 mode and
+    the int8 MMA issue peak measured here (cq_measure_i8_mma_peak) for the Q8_1 mode."""
     from .backend import QStorage
     lib, ctx = dev._lib, dev.ctx
     rng = np.random.default_rng(seed)
     w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
     out = []
+    tops = C.c_double()
+    dev._check(lib.cq_measure_i8_mma_peak(ctx, 4000, C.byref(tops)), "int8 peak")
+    int8_peak = float(tops.value)
     for qt, name, bb in ((2, "q4_0", 18), (8, "q8_0", 34)):
         first = QStorage.quantize(dev, qt, 0, w)
         ring = [first]
         for _ in range(7):
             c = RawCopy(dev, first)
             ring.append(c)
-        for m in ms_rows:
-            x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
-            y = dev.alloc(m * n)
-            cursor = [0]
+        for act, actname in ((2, "f16"), (1, "q8_1")):
+          for m in ms_rows:
+              x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
+              y = dev.alloc(m * n)
+              cursor = [0]
 
-            def call():
-                q = ring[cursor[0] % len(ring)]
-                cursor[0] += 1
-                dev._check(lib.cq_qmatmul(ctx, qt, 0, 2, x.ptr, m, k, k, q.ptr if isinstance(q, RawCopy) else q.buf.ptr, n, y.ptr, n), "qmatmul")
+              def call():
+                  q = ring[cursor[0] % len(ring)]
+                  cursor[0] += 1
+                  dev._check(lib.cq_qmatmul(ctx, qt, 0, act, x.ptr, m, k, k, q.ptr if isinstance(q, RawCopy) else q.buf.ptr, n, y.ptr, n), "qmatmul")
 
-            call()
-            dev.synchronize()
-            lib.cq_capture_begin(ctx)
-            for _ in range(calls):
-                call()
-            g = C.c_void_p()
-            dev._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
-            for _ in range(2):
-                dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
-            dev.synchronize()
-            ms = C.c_float()
-            reps = 5
-            lib.cq_timer_start(ctx)
-            for _ in range(reps):
-                dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
-            lib.cq_timer_stop(ctx, C.byref(ms))
-            dev.synchronize()
-            lib.cq_graph_destroy(ctx, g)
-            t = ms.value * 1e-3 / (reps * calls)
-            flops = 2.0 * m * n * k
-            nbytes = n * (k // 32) * bb + 4 * m * k + 4 * m * n
-            t_hbm, t_tensor = nbytes / (peak_gbs * 1e9), flops / (peak_tflops * 1e12)
-            out.append({"qtype": name, "m": m, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
-                        "algorithmic_gbs": round(nbytes / t / 1e9, 1), "bound": "hbm" if t_hbm >= t_tensor else "tensor",
-                        "roofline_us": round(max(t_hbm, t_tensor) * 1e6, 2), "frac_of_roofline": round(max(t_hbm, t_tensor) / t, 4),
-                        "path": ("raw blocks dequantized into tensor memory" + (" (two 64-row passes)" if qt != 2 and m > 64 else "")) if m <= 128
-                        else "f16 copy of W, then f16 tcgen05 GEMM"})
-            del x, y
+              call()
+              dev.synchronize()
+              lib.cq_capture_begin(ctx)
+              for _ in range(calls):
+                  call()
+              g = C.c_void_p()
+              dev._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
+              for _ in range(2):
+                  dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+              dev.synchronize()
+              ms = C.c_float()
+              reps = 5
+              lib.cq_timer_start(ctx)
+              for _ in range(reps):
+                  dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+              lib.cq_timer_stop(ctx, C.byref(ms))
+              dev.synchronize()
+              lib.cq_graph_destroy(ctx, g)
+              t = ms.value * 1e-3 / (reps * calls)
+              flops = 2.0 * m * n * k
+              nbytes = n * (k // 32) * bb + 4 * m * k + 4 * m * n
+              tensor_peak = peak_tflops if act == 2 else int8_peak
+              t_hbm, t_tensor = nbytes / (peak_gbs * 1e9), flops / (tensor_peak * 1e12)
+              out.append({"qtype": name, "actmode": actname, "m": m, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
+                          "algorithmic_gbs": round(nbytes / t / 1e9, 1), "bound": "hbm" if t_hbm >= t_tensor else "tensor",
+                          "roofline_us": round(max(t_hbm, t_tensor) * 1e6, 2), "frac_of_roofline": round(max(t_hbm, t_tensor) / t, 4),
+                          "tensor_peak_used": round(tensor_peak, 1),
+                          "path": "int8 tcgen05 (kind::i8), one MMA per quant block, per-block scaling in the epilogue" if act == 1 else (
+                              ("raw blocks dequantized into tensor memory" + (" (two 64-row passes)" if qt != 2 and m > 64 else "")) if m <= 128
+                              else "f16 copy of W, then f16 tcgen05 GEMM")})
+              del x, y
         del ring, first
-    return {"n": n, "k": k, "peak_gbs": peak_gbs, "peak_tflops": peak_tflops, "l2_defeat": "ring of 8 weight copies", "cases": out}
+    return {"n": n, "k": k, "peak_gbs": peak_gbs, "peak_tflops": peak_tflops, "int8_peak_measured": round(int8_peak, 1),
+            "int8_peak_note": "tcgen05.mma kind::i8 s8 x s8 -> s32, M128 N256 K32 back to back on every SM, operands in shared memory; nominal dense 4500",
+            "l2_defeat": "ring of 8 weight copies", "cases": out}
 
 
 class RawCopy:
@@ -121,18 +133,26 @@ class RawCopy:
         self.ptr = self.buf.ptr
 
 
-class _CudaArray:
-    """Minimal __cuda_array_interface__ view of a device buffer, so torch can wrap it without a copy."""
-
-    def __init__(self, ptr: int, count: int):
-        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+def tp_connect(dev, dist, rank: int, world: int):
+    """The library's own NCCL communicator (cq_tp_*): rank 0 makes the id, torch.distributed only carries it."""
+    from . import abi
+    lib, ctx = dev._lib, dev.ctx
+    ident = (C.c_char * 128)()
+    if rank == 0:
+        abi.check(ctx, lib.cq_tp_unique_id(ctx, ident), "tp unique id")
+    ids = [bytes(ident.raw)]
+    dist.broadcast_object_list(ids, src=0)
+    tp = C.c_void_p()
+    abi.check(ctx, lib.cq_tp_init(ctx, rank, world, ids[0], 128, C.byref(tp)), "tp init")
+    return tp
 
 
 def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: float, batches=(1, 32), ctx_len: int = 2048,
-                 n_layers: int = 8, reps: int = 30, seed: int = 3):
+                 n_layers: int = 8, reps: int = 30, seed: int = 3, tp=None):
     """8 layers of d=8192, 64 q / 8 kv heads x 128, ffn 28672, Q4_0; QKV/gate/up split by rows,
-    o/down by columns with an NCCL all-reduce (torch.distributed) after each; decode at a fixed
-    context of `ctx_len` keys (caches pre-filled with noise).  Returns per-batch step times."""
+    o/down by columns with an exchange after each: the fused peer-store exchange (batch <= 8) or the
+    library's NCCL all-reduce (cq_allreduce_sum_f32; torch.distributed is used for rendezvous only); decode at
+    a fixed context of `ctx_len` keys (caches pre-filled with noise).  Returns per-batch step times."""
     cfg = DecoderConfig(n_layers=n_layers, dim=8192, n_heads=64, n_kv_heads=8, head_dim=128, ffn=28672, vocab=0,
                         max_ctx=ctx_len, with_head=False)
     lib, ctx = dev._lib, dev.ctx
@@ -141,17 +161,13 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
     if world > 1:
         import torch
     for batch in batches:
-        views = {}
         # 8 < batch <= 64 runs the narrow tensor-core GEMM that streams the raw blocks; wider batches the
         # f16 GEMM, whose f16 weight copies are then kept across steps (weights are static in a decode
         # loop), trading 4x the Q4_0 bytes of device memory for no per-step conversion
         dev.set_option("gemm_cache_weights", 1 if batch > 64 else 0)
 
         def allreduce(buf, count):
-            key = buf.ptr.value
-            if key not in views:
-                views[key] = torch.as_tensor(_CudaArray(key, count), device=torch.device("cuda", local_rank))
-            dist.all_reduce(views[key])
+            dev._check(lib.cq_allreduce_sum_f32(ctx, tp, buf.ptr, count), "allreduce")
 
         fused = world > 1 and batch <= 8
         comm = None
@@ -196,33 +212,6 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
             lib.cq_graph_destroy(ctx, g)
             return ms.value / reps
 
-        def time_torch_graph():
-            stream = torch.cuda.Stream(device=local_rank)
-            dev.set_stream(stream.cuda_stream)
-            with torch.cuda.stream(stream):
-                model.step(advance=False)  # warm-up: NCCL channels, one-time kernel attributes, scratch
-                model.step(advance=False)
-            stream.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                model.step(advance=False)
-            dist.barrier()
-            with torch.cuda.stream(stream):
-                for _ in range(3):
-                    graph.replay()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                dist.barrier()
-                e0.record(stream)
-                for _ in range(reps):
-                    graph.replay()
-                e1.record(stream)
-            e1.synchronize()
-            t_ms = e0.elapsed_time(e1) / reps
-            dev.set_stream(0)
-            del graph
-            return t_ms
-
         def max_over_ranks(v):
             if dist is None:
                 return v
@@ -231,13 +220,10 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
             return float(t.item())
 
         nccl_ms = None
-        if world == 1 or fused:
-            step_ms = max_over_ranks(time_own_graph())
-            if fused:  # the same stack with NCCL all-reduces, for comparison
-                model.comm, model.allreduce = None, allreduce
-                nccl_ms = max_over_ranks(time_torch_graph())
-        else:
-            step_ms = max_over_ranks(time_torch_graph())
+        step_ms = max_over_ranks(time_own_graph())
+        if fused:  # the same stack with NCCL all-reduces, for comparison
+            model.comm, model.allreduce = None, allreduce
+            nccl_ms = max_over_ranks(time_own_graph())
         wbytes_all = model.weight_bytes_per_step() * world
         out[f"batch{batch}"] = {
             "ms_per_step": round(step_ms, 4), "layers_per_s": round(n_layers / (step_ms * 1e-3), 1),
@@ -245,7 +231,7 @@ def tp_layer_70b(dev, dist, rank: int, world: int, local_rank: int, peak_gbs: fl
             "weight_gbs_all_ranks": round(wbytes_all / (step_ms * 1e-3) / 1e9, 1),
             "frac_of_peak_per_gpu": round(wbytes_all / world / (step_ms * 1e-3) / 1e9 / peak_gbs, 4),
             "allreduce": "none" if world == 1 else ("fused: tagged peer stores from the GEMV epilogue, summed inside the following residual+RMSNorm kernel"
-                                                    if fused else f"NCCL sum of [{batch},8192] f32, twice per layer"),
+                                                    if fused else f"NCCL sum of [{batch},8192] f32 (cq_allreduce_sum_f32), twice per layer"),
             "nccl_ms_per_step": None if nccl_ms is None else round(nccl_ms, 4),
             "linear_mode": "f32 activations (decode GEMV)" if batch <= 8 else (
                 "f16 operands, raw blocks dequantized into tensor memory (narrow-batch tcgen05 GEMM)" if batch <= 64

@@ -65,7 +65,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         if o not in objs:
             o.unlink()
     if force or jobs or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB)] + [str(o) for o in objs] + ["-lcudart"]
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB)] + [str(o) for o in objs] + ["-lcudart", "-ldl"]
         subprocess.run(cmd, check=True)
     return LIB
 

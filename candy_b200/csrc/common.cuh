@@ -37,7 +37,7 @@ struct GemvTuning {
     int comm_cluster = 0;     // 1: one CTA per row in the reducing norm instead of a cluster of eight
     int gemm_int8 = 1;        // 1: the int8 tensor-core kernel serves CQ_ACT_Q8_1 from i8_min_rows_q8_1 rows and CQ_ACT_F32 from i8_min_rows_f32 rows
     int i8_min_rows_f32 = 3;
-    int i8_min_rows_q8_1 = 2;
+    int i8_min_rows_q8_1 = 3;
     int gemv_multirow = 1;  // 0: one launch (one weight pass) per activation row even for m = 2..8
     int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices
 };

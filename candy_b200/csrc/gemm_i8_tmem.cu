@@ -46,15 +46,18 @@ struct I8Cfg {
     static constexpr int kAStages = 2;
     static constexpr int kWScaleBytes = I8_BLOCKS * I8_ROWS * 4;  // f32 scale per (block, row)
     static constexpr int kBBytes = NC * I8_KCHUNK;                // activation columns: two [NC x 128 B] halves
-    static constexpr int kBStages = 2;
+    static constexpr int kBStages = NC <= 32 ? 4 : (NC <= 64 ? 3 : 2);  // the epilogue holds a stage (its scales) to the end of the chunk
     static constexpr int kXScaleBytes = I8_BLOCKS * NC * 8;       // float2 per (block, column) (plane mode uses half)
     static constexpr int kEpWarps = NC >= 128 ? 8 : 4;
     static constexpr int kColsPerWarp = NC / (kEpWarps / 4);
-    static constexpr int kSlots = (512 / NC) < 8 ? (512 / NC) : 8;  // rotating accumulator slots in tensor memory
+    // Accumulator slots in tensor memory, handed over in two groups: the MMAs of a group are committed once and
+    // the epilogue takes a whole group per barrier round (NC <= 32: a group is a chunk's eight blocks).
+    static constexpr int kSlots = (512 / NC) < 16 ? (512 / NC) : 16;
+    static constexpr int kGroup = kSlots / 2;
     static constexpr int kWarpUnpack0 = 4, kWarpEp0 = 8;
     static constexpr int kThreads = 32 * (kWarpEp0 + kEpWarps);
-    static constexpr size_t kSmem = (size_t)kWStages * kWBytes + (size_t)kAStages * (kABytes + kWScaleBytes + kXScaleBytes) +
-                                    (size_t)kBStages * kBBytes + 1024 /* alignment */ + 512 /* barriers */;
+    static constexpr size_t kSmem = (size_t)kWStages * kWBytes + (size_t)kAStages * (kABytes + kWScaleBytes) +
+                                    (size_t)kBStages * (kBBytes + kXScaleBytes) + 1024 /* alignment */ + 512 /* barriers */;
     static_assert(kSmem <= 232448, "shared memory");
 };
 
@@ -62,8 +65,7 @@ struct I8Params {
     float *y;            // [cols, n] with row pitch ldy (an activation row is a row of y)
     int64_t ldy;
     float *part;         // partial tiles: [2 * ctas][logical cols of this launch][128]
-    const float2 *xscale;  // [k/32][xs_pitch] per (block, logical column): Q8_1 (d8, s8); planes (amax/16383, bias)
-    int xs_pitch;        // logical columns in the whole pre-pass output
+    const float2 *xscale;  // this launch's activation scales, [chunk][8 blocks][logical columns of a launch]: Q8_1 (d8, s8); planes (amax/16383, bias)
     int col0;            // first logical column of this launch (column tile)
     int ncols;           // valid logical columns in this launch
     int n, nchunks;
@@ -72,97 +74,79 @@ struct I8Params {
 };
 
 // ---- activation pre-pass -------------------------------------------------------------------------------
-// Position p of a block's 32 values in the order the unpacking threads emit the weights: bytes 0..15 hold the
-// low nibbles of data bytes 0..15, bytes 16..31 the high nibbles.  Go order: data byte j = elements (2j, 2j+1).
-__device__ __forceinline__ int i8_src_elem(int p, int order) {
-    if (order == 0) return p < 16 ? 2 * p : 2 * (p - 16) + 1;  // Q4_0, interleaved
-    return p;                                                  // Q4_0 split order and Q8_0: natural
-}
-
-// One thread per (activation row, block).  MODE 1: Q8_1 columns.  MODE 0: hi / lo plane columns.
-// planes: int8 [rows_total][k]; scale: float2 [k/32][xs_pitch].  Rows >= m are zero (written here).
+// Eight lanes per (activation row, block), four values each.  MODE 1: Q8_1 columns.  MODE 0: hi / lo plane columns.
+// planes: int8 [rows_total][k]; scale: float2 [launch][chunk][8 blocks][ncl] (launch = row / ncl), so that the
+// scales one (launch, chunk) item needs are one contiguous run.  Rows >= m are zero (written here).
 template <int MODE>
-__global__ void __launch_bounds__(128) i8_prepass_kernel(const float *__restrict__ x, int m, int m_pad, int k, int64_t ldx, int order, int is_q4,
-                                                       int8_t *__restrict__ planes, float2 *__restrict__ scale, int xs_pitch) {
+__global__ void __launch_bounds__(256) i8_prepass_kernel(const float *__restrict__ x, int m, int m_pad, int k, int64_t ldx, int order, int is_q4,
+                                                       int8_t *__restrict__ planes, float2 *__restrict__ scale, int ncl) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const int nb = k / kQK;
-    const int64_t total = (int64_t)m_pad * nb;
+    const int64_t total = (int64_t)m_pad * nb * 8;  // a multiple of 8: the eight lanes of a block stay together
+    const int l = threadIdx.x & 7;                  // values 4l .. 4l+3 of the block
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int row = (int)(i / nb), b = (int)(i - (int64_t)row * nb);
-        uint32_t out0[8], out1[8];
+        const int64_t blk = i >> 3;
+        const int row = (int)(blk / nb), b = (int)(blk - (int64_t)row * nb);
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (row < m) v = reinterpret_cast<const float4 *>(x + (int64_t)row * ldx + (int64_t)b * kQK)[l];
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
+        int q[4];
         float2 sc = make_float2(0.0f, 0.0f);
-        if (row < m) {
-            float v[32];
-            const float4 *src = reinterpret_cast<const float4 *>(x + (int64_t)row * ldx + (int64_t)b * kQK);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 t = src[j];
-                v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
-            int q[32];
-            if (MODE == 1) {
-                // quantize_q8_1 (quantized.cu:3521-3558): d = amax / 127, q = round(x / d) by true division (0 when
-                // amax == 0); d and the sum of the block's f32 values are stored as f16 and read back rounded.  The
-                // sum follows the reference's xor butterfly (offsets 16, 8, 4, 2, 1), so the bits agree with it.
-                float t[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) t[j] = v[j];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                    for (int j = 0; j < off; ++j) t[j] = __fadd_rn(t[j], t[j + off]);
-                const float d = __fdiv_rn(amax, 127.0f);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) q[j] = amax == 0.0f ? 0 : (int)roundf(__fdiv_rn(v[j], d));
-                sc.x = __half2float(__float2half_rn(d));
-                sc.y = __half2float(__float2half_rn(t[0]));
-            } else {
-                const float inv = amax > 0.0f ? 16383.0f / amax : 0.0f;
-                int xsum = 0;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    q[j] = __float2int_rn(fminf(fmaxf(v[j] * inv, -16383.0f), 16383.0f));
-                    xsum += q[j];
-                }
-                sc.x = amax * (1.0f / 16383.0f);
-                sc.y = __int_as_float(is_q4 ? -8 * xsum : 0);  // an integer carried in the float2's second word
-            }
-#pragma unroll
-            for (int wd = 0; wd < 8; ++wd) {
-                uint32_t a = 0, bb = 0;
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int val = q[i8_src_elem(4 * wd + t, order)];
-                    if (MODE == 1) {
-                        a |= (uint32_t)(val & 0xFF) << (8 * t);
-                    } else {
-                        a |= (uint32_t)((val >> 7) & 0xFF) << (8 * t);  // hi: floor(X / 128), -128..127
-                        bb |= (uint32_t)(val & 0x7F) << (8 * t);        // lo: 0..127
-                    }
-                }
-                out0[wd] = a, out1[wd] = bb;
-            }
-        } else {
-#pragma unroll
-            for (int wd = 0; wd < 8; ++wd) out0[wd] = 0u, out1[wd] = 0u;
-        }
         if (MODE == 1) {
-            uint4 *dst = reinterpret_cast<uint4 *>(planes + (int64_t)row * k + (int64_t)b * kQK);
-            dst[0] = make_uint4(out0[0], out0[1], out0[2], out0[3]);
-            dst[1] = make_uint4(out0[4], out0[5], out0[6], out0[7]);
+            // quantize_q8_1 (quantized.cu:3521-3558): d = amax / 127, q = round(x / d) by true division (0 when
+            // amax == 0); d and the sum of the block's f32 values are stored as f16 and read back rounded.  The sum
+            // follows the reference's xor butterfly over the 32 values (offsets 16, 8, 4 across the lanes here, 2 and 1
+            // inside a lane), so its bits agree with the reference kernel's.
+            float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+                s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o, 8));
+                s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o, 8));
+                s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, o, 8));
+                s3 = __fadd_rn(s3, __shfl_xor_sync(0xffffffffu, s3, o, 8));
+            }
+            const float sum = __fadd_rn(__fadd_rn(s0, s2), __fadd_rn(s1, s3));
+            const float d = __fdiv_rn(amax, 127.0f);
+            q[0] = amax == 0.0f ? 0 : (int)roundf(__fdiv_rn(v.x, d));
+            q[1] = amax == 0.0f ? 0 : (int)roundf(__fdiv_rn(v.y, d));
+            q[2] = amax == 0.0f ? 0 : (int)roundf(__fdiv_rn(v.z, d));
+            q[3] = amax == 0.0f ? 0 : (int)roundf(__fdiv_rn(v.w, d));
+            sc.x = __half2float(__float2half_rn(d));
+            sc.y = __half2float(__float2half_rn(sum));
         } else {
-            uint4 *dh = reinterpret_cast<uint4 *>(planes + (int64_t)(2 * row) * k + (int64_t)b * kQK);
-            uint4 *dl = reinterpret_cast<uint4 *>(planes + (int64_t)(2 * row + 1) * k + (int64_t)b * kQK);
-            dh[0] = make_uint4(out0[0], out0[1], out0[2], out0[3]);
-            dh[1] = make_uint4(out0[4], out0[5], out0[6], out0[7]);
-            dl[0] = make_uint4(out1[0], out1[1], out1[2], out1[3]);
-            dl[1] = make_uint4(out1[4], out1[5], out1[6], out1[7]);
+            const float inv = amax > 0.0f ? 16383.0f / amax : 0.0f;
+            q[0] = __float2int_rn(fminf(fmaxf(v.x * inv, -16383.0f), 16383.0f));
+            q[1] = __float2int_rn(fminf(fmaxf(v.y * inv, -16383.0f), 16383.0f));
+            q[2] = __float2int_rn(fminf(fmaxf(v.z * inv, -16383.0f), 16383.0f));
+            q[3] = __float2int_rn(fminf(fmaxf(v.w * inv, -16383.0f), 16383.0f));
+            int xsum = q[0] + q[1] + q[2] + q[3];
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) xsum += __shfl_xor_sync(0xffffffffu, xsum, o, 8);
+            sc.x = amax * (1.0f / 16383.0f);
+            sc.y = __int_as_float(is_q4 ? -8 * xsum : 0);  // an integer carried in the float2's second word
         }
-        scale[(int64_t)b * xs_pitch + row] = sc;
+        // Where the four values go inside the block's 32 positions.  Natural order: positions 4l .. 4l+3.  Go
+        // (interleaved) order: the unpacking threads emit the low nibbles (even elements) as positions 0..15 and
+        // the high nibbles (odd elements) as positions 16..31, so elements 4l, 4l+2 land at 2l, 2l+1 and elements
+        // 4l+1, 4l+3 at 16+2l, 16+2l+1.
+        const int planes_per_row = MODE == 1 ? 1 : 2;
+#pragma unroll
+        for (int pl = 0; pl < planes_per_row; ++pl) {
+            uint32_t byte[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) byte[t] = MODE == 1 ? (uint32_t)(q[t] & 0xFF) : (pl == 0 ? (uint32_t)((q[t] >> 7) & 0xFF) : (uint32_t)(q[t] & 0x7F));
+            int8_t *dst = planes + (int64_t)(planes_per_row * row + pl) * k + (int64_t)b * kQK;
+            if (order == 0) {
+                *reinterpret_cast<uint16_t *>(dst + 2 * l) = (uint16_t)(byte[0] | (byte[2] << 8));
+                *reinterpret_cast<uint16_t *>(dst + 16 + 2 * l) = (uint16_t)(byte[1] | (byte[3] << 8));
+            } else {
+                *reinterpret_cast<uint32_t *>(dst + 4 * l) = byte[0] | (byte[1] << 8) | (byte[2] << 16) | (byte[3] << 24);
+            }
+        }
+        if (l == 0) scale[((int64_t)(row / ncl) * nb + b) * ncl + (row % ncl)] = sc;
     }
 }
 
@@ -196,18 +180,16 @@ __host__ __device__ constexpr uint32_t idesc_i8(int mm, int nn, bool a_signed) {
     return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(nn >> 3) << 17) | ((uint32_t)(mm >> 4) << 24);
 }
 
-// NW consecutive 32-bit words of a row that start at 16-bit unit `hw` (a compile-time constant after unrolling).
-template <int NW>
-__device__ __forceinline__ void row_words(const uint32_t *row, int hw, uint32_t (&out)[NW]) {
+// NW consecutive 32-bit words that start at 16-bit unit `hw` (a compile-time constant after unrolling) of a row
+// held in registers as 32-bit words.
+template <int NW, int ROWW>
+__device__ __forceinline__ void row_words(const uint32_t (&row)[ROWW], int hw, uint32_t (&out)[NW]) {
     if ((hw & 1) == 0) {
 #pragma unroll
         for (int i = 0; i < NW; ++i) out[i] = row[hw / 2 + i];
     } else {
-        uint32_t t[NW + 1];
 #pragma unroll
-        for (int i = 0; i <= NW; ++i) t[i] = row[(hw - 1) / 2 + i];
-#pragma unroll
-        for (int i = 0; i < NW; ++i) out[i] = __funnelshift_r(t[i], t[i + 1], 16);
+        for (int i = 0; i < NW; ++i) out[i] = __funnelshift_r(row[(hw - 1) / 2 + i], row[(hw - 1) / 2 + i + 1], 16);
     }
 }
 
@@ -216,7 +198,7 @@ template <int QT, int MODE, int NC>
 __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
     qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const I8Params p) {
     using Cfg = I8Cfg<QT, NC>;
-    constexpr int WST = Cfg::kWStages, AST = Cfg::kAStages, BST = Cfg::kBStages, SLOTS = Cfg::kSlots, EPW = Cfg::kEpWarps;
+    constexpr int WST = Cfg::kWStages, AST = Cfg::kAStages, BST = Cfg::kBStages, SLOTS = Cfg::kSlots, GROUP = Cfg::kGroup, EPW = Cfg::kEpWarps;
     constexpr int NCL = MODE == 1 ? NC : NC / 2;  // logical columns (activation rows) of the launch
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -224,11 +206,11 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
     uint8_t *sm_b = sm_a + (size_t)AST * Cfg::kABytes;               // BST activation tiles
     uint8_t *sm_w = sm_b + (size_t)BST * Cfg::kBBytes;               // WST raw weight stages
     float *sm_ws = reinterpret_cast<float *>(sm_w + (size_t)WST * Cfg::kWBytes);            // [AST][8][128]
-    float2 *sm_xs = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(sm_ws) + (size_t)AST * Cfg::kWScaleBytes);  // [AST][8][NCL]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sm_xs) + (size_t)AST * Cfg::kXScaleBytes);
+    float2 *sm_xs = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(sm_ws) + (size_t)AST * Cfg::kWScaleBytes);  // [BST][8][NCL]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sm_xs) + (size_t)BST * Cfg::kXScaleBytes);
     uint64_t *w_full = bars, *w_empty = w_full + WST, *a_full = w_empty + WST, *a_empty = a_full + AST, *b_full = a_empty + AST,
-             *b_empty = b_full + BST, *s_full = b_empty + BST, *s_empty = s_full + SLOTS;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_empty + SLOTS);
+             *b_empty = b_full + BST, *s_full = b_empty + BST, *s_empty = s_full + 2;  // one pair per group of slots
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -241,14 +223,14 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
         }
         for (int s = 0; s < AST; ++s) {
             mbar_init(smem_u32(&a_full[s]), 4);           // the unpacking warps
-            mbar_init(smem_u32(&a_empty[s]), 1 + EPW);    // the MMAs' commit + every epilogue warp (scales read)
+            mbar_init(smem_u32(&a_empty[s]), 1 + EPW);    // the MMAs' commit + every epilogue warp (weight scales read)
         }
         for (int s = 0; s < BST; ++s) {
             mbar_init(smem_u32(&b_full[s]), 1);
-            mbar_init(smem_u32(&b_empty[s]), 1);          // the MMAs' commit
+            mbar_init(smem_u32(&b_empty[s]), 1 + EPW);    // the MMAs' commit + every epilogue warp (activation scales read)
         }
-        for (int s = 0; s < SLOTS; ++s) {
-            mbar_init(smem_u32(&s_full[s]), 1);           // the block's MMA commit
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&s_full[s]), 1);           // the group's MMA commit
             mbar_init(smem_u32(&s_empty[s]), EPW);
         }
         fence_mbar_init();
@@ -312,7 +294,9 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(smem_u32(&b_full[s]), Cfg::kBBytes);
+                    constexpr uint32_t XS_BYTES = I8_BLOCKS * NCL * 8;
+                    mbar_expect_tx(smem_u32(&b_full[s]), Cfg::kBBytes + XS_BYTES);
+                    bulk_g2s(smem_u32(sm_xs + (size_t)s * (I8_BLOCKS * NCL)), p.xscale + (int64_t)(c0 + c) * (I8_BLOCKS * NCL), XS_BYTES, smem_u32(&b_full[s]));
                     const int row0 = (MODE == 1 ? p.col0 : 2 * p.col0);
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
@@ -330,7 +314,7 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
         // ---- MMA: one K = 32 instruction per quant block, each into its own tensor-memory slot ----------
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_i8(I8_ROWS, NC, QT == CQ_Q8_0);
-            int st = 0, bi = 0;
+            int st = 0, gi = 0;  // chunks and groups of blocks issued so far
             bool ok = true;
             for (int g = g0; g < g1 && ok; ++g, ++st) {
                 const int sa = st % AST, sb = st % BST;
@@ -341,18 +325,22 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
                 tc_fence_after();
                 const uint32_t a0 = smem_u32(sm_a + (size_t)sa * Cfg::kABytes), b0 = smem_u32(sm_b + (size_t)sb * Cfg::kBBytes);
 #pragma unroll 1
-                for (int j = 0; j < I8_BLOCKS; ++j, ++bi) {
-                    const int slot = bi % SLOTS;
-                    if (bi >= SLOTS && !mbar_wait_sleep(smem_u32(&s_empty[slot]), ((bi / SLOTS) - 1) & 1, 40)) {
+                for (int j0 = 0; j0 < I8_BLOCKS; j0 += GROUP, ++gi) {
+                    const int grp = gi & 1;
+                    if (gi >= 2 && !mbar_wait_sleep(smem_u32(&s_empty[grp]), ((gi >> 1) - 1) & 1, 40)) {  // the epilogue has drained this group's slots
                         atomicExch(p.err, kDevErrMma);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    // block j: half j/4 of the tile (a [rows x 128 B] swizzled slab), 32 bytes of k inside the 128-byte row
-                    tc_mma_i8(tmem_base + (uint32_t)(slot * NC), smem_desc_k128(a0 + (j >> 2) * (I8_ROWS * 128) + (j & 3) * 32),
-                              smem_desc_k128(b0 + (j >> 2) * (NC * 128) + (j & 3) * 32), idesc);
-                    tc_commit(smem_u32(&s_full[slot]));
+#pragma unroll
+                    for (int jg = 0; jg < GROUP; ++jg) {
+                        const int j = j0 + jg;
+                        // block j: half j/4 of the tile (a [rows x 128 B] swizzled slab), 32 bytes of k inside the 128-byte row
+                        tc_mma_i8(tmem_base + (uint32_t)((grp * GROUP + jg) * NC), smem_desc_k128(a0 + (j >> 2) * (I8_ROWS * 128) + (j & 3) * 32),
+                                  smem_desc_k128(b0 + (j >> 2) * (NC * 128) + (j & 3) * 32), idesc);
+                    }
+                    tc_commit(smem_u32(&s_full[grp]));  // arrives when the group's MMAs (and all before) have completed
                 }
                 if (!ok) break;
                 tc_commit(smem_u32(&a_empty[sa]));  // arrive when the chunk's MMAs have finished reading shared memory
@@ -362,10 +350,8 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
     } else if (warp >= Cfg::kWarpUnpack0 && warp < Cfg::kWarpEp0) {
         // ---- unpack: thread = weight row of the tile ----------------------------------------------------
         const int r = (warp - Cfg::kWarpUnpack0) * 32 + lane;
-        pdl_wait_prior();  // the activation scales copied below come from the pre-pass
         int st = 0;
-        for (int g = g0; g < g1; ++g, ++st) {
-            const int chunk = g % p.nchunks;
+        for (int g = g0; g < g1; ++g, ++st) {  // (weights are nobody's output: no wait for earlier kernels here)
             const int sw = st % WST, sa = st % AST;
             if (!mbar_wait_sleep(smem_u32(&w_full[sw]), (st / WST) & 1, 60)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
@@ -375,7 +361,18 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
                 if (lane == 0) atomicExch(p.err, kDevErrEmptyWait);
                 break;
             }
-            const uint32_t *row = reinterpret_cast<const uint32_t *>(sm_w + (size_t)sw * Cfg::kWBytes + (size_t)r * Cfg::kRowChunk);
+            // The thread's row of the stage, 144 / 272 bytes, in 16-byte loads: at this row pitch eight lanes' 16 bytes
+            // fall into distinct banks (32-bit loads would collide four ways).
+            constexpr int ROWW = Cfg::kRowChunk / 4;  // 36 / 68 words
+            uint32_t row[ROWW];
+            {
+                const uint4 *src = reinterpret_cast<const uint4 *>(sm_w + (size_t)sw * Cfg::kWBytes + (size_t)r * Cfg::kRowChunk);
+#pragma unroll
+                for (int i = 0; i < ROWW / 4; ++i) {
+                    const uint4 t = src[i];
+                    row[4 * i] = t.x, row[4 * i + 1] = t.y, row[4 * i + 2] = t.z, row[4 * i + 3] = t.w;
+                }
+            }
             uint8_t *a_tile = sm_a + (size_t)sa * Cfg::kABytes;
             float *ws = sm_ws + (size_t)sa * (I8_BLOCKS * I8_ROWS);
 #pragma unroll
@@ -387,23 +384,17 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
                 uint32_t o[8];
                 if (QT == CQ_Q4_0) {
                     uint32_t q[4];
-                    row_words<4>(row, HWB * j + 1, q);
+                    row_words<4, ROWW>(row, HWB * j + 1, q);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) o[i] = q[i] & 0x0F0F0F0Fu, o[4 + i] = (q[i] >> 4) & 0x0F0F0F0Fu;
                 } else {
-                    row_words<8>(row, HWB * j + 1, o);
+                    row_words<8, ROWW>(row, HWB * j + 1, o);
                 }
                 // block j -> bytes [32 (j & 3), +32) of the 128-byte row of half j >> 2; 16-byte chunk c sits at c ^ (r & 7)
                 uint8_t *dst = a_tile + (j >> 2) * (I8_ROWS * 128) + r * 128;
                 const int c = 2 * (j & 3);
                 *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 *reinterpret_cast<uint4 *>(dst + (((c + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-            }
-            // the chunk's activation scales: [8][NCL] float2 out of [k/32][xs_pitch]
-            float2 *xs = sm_xs + (size_t)sa * (I8_BLOCKS * NCL);
-            for (int i = r; i < I8_BLOCKS * NCL; i += 128) {
-                const int bl = i / NCL, c = i - bl * NCL;
-                xs[i] = p.xscale[(int64_t)(chunk * I8_BLOCKS + bl) * p.xs_pitch + p.col0 + c];
             }
             fence_proxy_async();  // the A tile is read by the tensor core's asynchronous proxy
             __syncwarp();
@@ -423,41 +414,41 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
         float acc[LPW];
 #pragma unroll
         for (int i = 0; i < LPW; ++i) acc[i] = 0.0f;
-        int st = 0, bi = 0;
+        int st = 0, gi = 0;  // chunks and groups of blocks drained so far
         bool ok = true, first_seg = true;
         for (int g = g0; g < g1 && ok;) {
             int tile, c0, cn;
             segment(g, tile, c0, cn);
             g += cn;
             for (int c = 0; c < cn && ok; ++c, ++st) {
-                const int sa = st % AST;
-                if (!mbar_wait_sleep(smem_u32(&a_full[sa]), (st / AST) & 1, 60)) {  // the scales of this chunk are in place
+                const int sa = st % AST, sb = st % BST;
+                // the weight scales (written by the unpacking warps) and the activation scales (bulk copy) of this chunk are in place
+                if (!mbar_wait_sleep(smem_u32(&a_full[sa]), (st / AST) & 1, 60) || !mbar_wait_sleep(smem_u32(&b_full[sb]), (st / BST) & 1, 60)) {
                     if (lane == 0) atomicExch(p.err, kDevErrFullWait);
                     ok = false;
                     break;
                 }
                 const float *ws = sm_ws + (size_t)sa * (I8_BLOCKS * I8_ROWS);
-                const float2 *xs = sm_xs + (size_t)sa * (I8_BLOCKS * NCL);
+                const float2 *xs = sm_xs + (size_t)sb * (I8_BLOCKS * NCL);
+                // A group of slots is drained in pieces of 16 columns, two register sets in turn: the load of the next
+                // piece is in flight while the current one is scaled and accumulated.
+                constexpr int PPB = CPW / 16;             // pieces per block
+                constexpr int PIECES = GROUP * PPB;       // pieces per group (even)
+                const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chalf * CPW);
 #pragma unroll 1
-                for (int j = 0; j < I8_BLOCKS; ++j, ++bi) {
-                    const int slot = bi % SLOTS;
-                    if (!mbar_wait_sleep(smem_u32(&s_full[slot]), (bi / SLOTS) & 1, 20)) {
+                for (int j0 = 0; j0 < I8_BLOCKS && ok; j0 += GROUP, ++gi) {
+                    const int grp = gi & 1;
+                    if (!mbar_wait_sleep(smem_u32(&s_full[grp]), (gi >> 1) & 1, 20)) {
                         if (lane == 0) atomicExch(p.err, kDevErrMma);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const float dw = ws[j * I8_ROWS + r];
-                    const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * NC + chalf * CPW);
-#pragma unroll
-                    for (int cb = 0; cb < CPW / 16; ++cb) {
-                        uint32_t v[16];
-                        tmem_ld16(t0 + cb * 16, v);
-                        if (cb == CPW / 16 - 1) {  // the slot is in registers: the next block's MMA may overwrite it
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(smem_u32(&s_empty[slot]));
-                        }
+                    const uint32_t gbase = lane_base + (uint32_t)(grp * GROUP * NC);
+                    auto fetch = [&](uint32_t (&dst)[16], int e) { tmem_ld16_async(gbase + (uint32_t)((e / PPB) * NC + (e % PPB) * 16), dst); };
+                    auto consume = [&](const uint32_t (&v)[16], int e) {
+                        const int j = j0 + e / PPB, cb = e % PPB;
+                        const float dw = ws[j * I8_ROWS + r];
                         if (MODE == 1) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
@@ -474,11 +465,30 @@ __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
                                 acc[cb * 8 + i] = fmaf(dw * sc.x, (float)t, acc[cb * 8 + i]);
                             }
                         }
+                    };
+                    uint32_t va[16], vb[16];
+                    fetch(va, 0);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int u = 0; u < PIECES / 2; ++u) {
+                        fetch(vb, 2 * u + 1);
+                        consume(va, 2 * u);
+                        tmem_wait_ld();
+                        if (2 * u + 2 < PIECES) fetch(va, 2 * u + 2);
+                        consume(vb, 2 * u + 1);
+                        tmem_wait_ld();
                     }
+                    // every piece of the group is in registers or already used: its slots may be overwritten
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&s_empty[grp]));
                 }
                 if (!ok) break;
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&a_empty[sa]));  // this warp has read the chunk's scales
+                if (lane == 0) {  // this warp has read the chunk's scales
+                    mbar_arrive(smem_u32(&a_empty[sa]));
+                    mbar_arrive(smem_u32(&b_empty[sb]));
+                }
             }
             if (!ok) break;
             // the segment is complete: whole k range -> y, otherwise one of this CTA's two partial slots
@@ -631,12 +641,12 @@ cq_status launch_qgemm_i8(cq_ctx *ctx, int qtype, int order, int mode, const flo
     float2 *scale = reinterpret_cast<float2 *>(static_cast<uint8_t *>(ctx->scratch) + planes_bytes);
     float *part = reinterpret_cast<float *>(static_cast<uint8_t *>(ctx->scratch) + planes_bytes + scale_bytes);
     {
-        const int64_t items = m_pad * nb;
+        const int64_t items = m_pad * nb * 8;
         const unsigned cap = (unsigned)ctx->sm_count * 8;
-        const unsigned grid = (unsigned)((items + 127) / 128 < cap ? (items + 127) / 128 : cap);
+        const unsigned grid = (unsigned)((items + 255) / 256 < cap ? (items + 255) / 256 : cap);
         const int ord = qtype == CQ_Q4_0 ? order : 1;
-        if (mode == 1) s = i8_launch_chained(ctx, i8_prepass_kernel<1>, dim3(grid), dim3(128), 0, x, (int)m, (int)m_pad, (int)k, ldx, ord, qtype == CQ_Q4_0 ? 1 : 0, planes, scale, (int)m_pad);
-        else s = i8_launch_chained(ctx, i8_prepass_kernel<0>, dim3(grid), dim3(128), 0, x, (int)m, (int)m_pad, (int)k, ldx, ord, qtype == CQ_Q4_0 ? 1 : 0, planes, scale, (int)m_pad);
+        if (mode == 1) s = i8_launch_chained(ctx, i8_prepass_kernel<1>, dim3(grid), dim3(256), 0, x, (int)m, (int)m_pad, (int)k, ldx, ord, qtype == CQ_Q4_0 ? 1 : 0, planes, scale, ncl);
+        else s = i8_launch_chained(ctx, i8_prepass_kernel<0>, dim3(grid), dim3(256), 0, x, (int)m, (int)m_pad, (int)k, ldx, ord, qtype == CQ_Q4_0 ? 1 : 0, planes, scale, ncl);
         if (s != CQ_OK) return s;
     }
     CUtensorMap tmW, tmX;
@@ -645,7 +655,7 @@ cq_status launch_qgemm_i8(cq_ctx *ctx, int qtype, int order, int mode, const flo
         return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
     for (int l = 0; l < launches; ++l) {
         I8Params p;
-        p.y = y + (int64_t)l * ncl * ldy, p.ldy = ldy, p.part = part, p.xscale = scale, p.xs_pitch = (int)m_pad;
+        p.y = y + (int64_t)l * ncl * ldy, p.ldy = ldy, p.part = part, p.xscale = scale + (int64_t)l * nb * ncl;
         p.col0 = l * ncl;
         p.ncols = (int)((m - (int64_t)l * ncl) < ncl ? (m - (int64_t)l * ncl) : ncl);
         p.n = (int)n, p.nchunks = nchunks, p.total = (int)total, p.per_cta = (int)per_cta;

@@ -380,6 +380,13 @@ struct DecQ16 {
         return total;
     }
 
+    // Set-up in two steps for the multi-row kernel, which issues several items' loads before using the first.
+    struct QRegs {
+        float r[8];
+    };
+    __device__ __forceinline__ static void qload(const float *x, int item, bool valid, QRegs &q) { load_quarter(x, item, valid, q.r); }
+    __device__ __forceinline__ static void qstage(const QRegs &q, int item, bool valid, uint32_t *area) { stage_quarter_regs(q.r, item, valid, area); }
+
     // The same arithmetic as pass(), split in two for the multi-row kernel: the weight words of a thread's
     // two blocks are loaded and unpacked once (WBlk) and then meet the state of each activation row.
     struct WBlk {
@@ -785,6 +792,44 @@ struct DecQ81 {
             else total += __fmul_rn(__fmul_rn(scale[blk], d8[blk]), (float)acc);
         }
         return total;
+    }
+
+    // Set-up in two steps for the multi-row kernel (loads of several items in flight together).
+    struct QRegs {
+        uint32_t w[3];  // the block's (d, s) word and the quarter's two data words
+    };
+    __device__ __forceinline__ static void qload(const float *x, int item, bool valid, QRegs &q) {
+        if (!valid) {
+            q.w[0] = q.w[1] = q.w[2] = 0u;
+            return;
+        }
+        const int blk = item >> 2, qd = item & 3;
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(x) + (size_t)blk * kQ81Bytes);
+        q.w[0] = src[0], q.w[1] = src[1 + 2 * qd], q.w[2] = src[2 + 2 * qd];
+    }
+    __device__ __forceinline__ static void qstage(const QRegs &q, int item, bool valid, uint32_t *area) {
+        if (!valid) return;
+        const int blk = item >> 2, qd = item & 3;
+        const uint32_t w0 = q.w[1], w1 = q.w[2];
+        uint32_t wa, wb;
+        int idxA, idxB;
+        if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) {
+            wa = __byte_perm(w0, w1, 0x6420), wb = __byte_perm(w0, w1, 0x7531);
+            idxA = 2 * qd, idxB = 2 * qd + 1;
+        } else if (QT == CQ_Q4_0) {
+            wa = w0, wb = w1;
+            idxA = (qd < 2) ? 4 * qd : 4 * (qd - 2) + 1, idxB = idxA + 2;
+        } else {
+            wa = w0, wb = w1;
+            idxA = 2 * qd, idxB = 2 * qd + 1;
+        }
+        uint32_t *dst = area + blk * kStateWordsPerBlock;
+        dst[idxA] = wa;
+        dst[idxB] = wb;
+        if (qd == 0) {
+            dst[8] = __float_as_uint(__half2float(__ushort_as_half((unsigned short)(q.w[0] & 0xFFFFu))));
+            dst[9] = __float_as_uint(__half2float(__ushort_as_half((unsigned short)(q.w[0] >> 16))));
+        }
     }
 
     // pass() split in two for the multi-row kernel (see DecQ16::WBlk).
@@ -1222,12 +1267,22 @@ __global__ void __launch_bounds__(384, 1) gemv_stream_mr_kernel(const GemvParams
     const int nitems = p.nb * 4;
     const int row_words = p.nb * Dec::kStateWordsPerBlock;
     const int total_items = p.m * nitems;
-    for (int base = 0; base < total_items; base += cthreads) {  // uniform trip count: the shuffles need whole warps
-        const int idx = base + tid;
-        const bool valid = idx < total_items;
-        const int r = valid ? idx / nitems : 0, item = valid ? idx - r * nitems : 0;
-        const float *xrow = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(p.x) + (int64_t)r * p.x_row_bytes);
-        Dec::stage_quarter(xrow, item, valid, area + (size_t)r * row_words);
+    // Four items per trip with all four loads issued before the first is used: a trip costs one L2 round trip, and
+    // 4 rows of k = 4096 take two trips instead of eight.  Uniform trip count: the shuffles inside need whole warps.
+    for (int base = 0; base < total_items; base += 4 * cthreads) {
+        typename Dec::QRegs q[4];
+        int rr[4], it[4];
+        bool vd[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int idx = base + u * cthreads + tid;
+            vd[u] = idx < total_items;
+            rr[u] = vd[u] ? idx / nitems : 0;
+            it[u] = vd[u] ? idx - rr[u] * nitems : 0;
+            Dec::qload(reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(p.x) + (int64_t)rr[u] * p.x_row_bytes), it[u], vd[u], q[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) Dec::qstage(q[u], it[u], vd[u], area + (size_t)rr[u] * row_words);
     }
     asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
     Dec dec[MR];

@@ -96,7 +96,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
  * row); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
  * GEMM has seen: the weights must then stay unchanged, or be rewritten only through cq_* entry points, or
- * cq_invalidate_weight_cache must be called); gemm_int8 (1, default: batches of i8_min_rows_q8_1 (2) or more
+ * cq_invalidate_weight_cache must be called); gemm_int8 (1, default: batches of i8_min_rows_q8_1 (3) or more
  * rows in CQ_ACT_Q8_1 and of i8_min_rows_f32 (3) or more in CQ_ACT_F32 run the int8 tensor-core kernel, one
  * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant; comm_poll_limit (polls before the reducing
  * norm gives up on a peer's data, default about one second's worth); comm_cluster. */
@@ -286,6 +286,25 @@ cq_status cq_qmatmul_push(cq_ctx *ctx, cq_comm *comm, int set, int qtype, int or
 /* x[rows,cols] += sum over ranks of the partials pushed into `set`; y = rmsnorm(x) * alpha. */
 cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *comm, int set, float *x_dev, const float *alpha_dev,
                                 int64_t rows, int64_t cols, float eps, float *y_dev);
+
+/* ---- NCCL all-reduce: the baseline exchange, and the one for batches beyond eight rows ---------
+ * No counterpart in the reference.  NCCL is opened at run time (libnccl.so.2; $CANDYQ_NCCL_LIBRARY
+ * overrides), not linked: without it these entries answer CQ_ERR_UNSUPPORTED and everything else works.
+ *   cq_tp_unique_id       rank 0 makes the 128-byte id and hands it to the other ranks by any means it has;
+ *   cq_tp_init            every rank joins (collective: returns when all `world` ranks have called it);
+ *   cq_allreduce_sum_f32  buf[count] = sum over ranks, in place, asynchronous on the context's stream
+ *                         (may be recorded into a graph between cq_capture_begin / _end);
+ *   cq_tp_wait            waits for the stream, at most timeout_ms: if the work has not finished by then (a
+ *                         rank is late or gone) or NCCL reports an asynchronous error, the communicator is
+ *                         aborted -- which releases the collective kernels still waiting on the GPU -- and
+ *                         CQ_ERR_TIMEOUT (or CQ_ERR_CUDA) comes back; the context stays usable, the
+ *                         communicator does not.  Use it instead of cq_synchronize wherever a peer may fail. */
+typedef struct cq_tp cq_tp;
+cq_status cq_tp_unique_id(cq_ctx *ctx, void *id128);
+cq_status cq_tp_init(cq_ctx *ctx, int rank, int world, const void *nccl_unique_id, size_t id_bytes, cq_tp **out);
+cq_status cq_tp_destroy(cq_ctx *ctx, cq_tp *tp);
+cq_status cq_allreduce_sum_f32(cq_ctx *ctx, cq_tp *tp, float *buf_dev, int64_t count);
+cq_status cq_tp_wait(cq_ctx *ctx, cq_tp *tp, int timeout_ms);
 
 /* ---- CUDA graphs and device timing ----------------------------------------------------
  * Decode loops are launch-bound: a GEMV lasts a few microseconds.  These wrap stream capture
