@@ -515,7 +515,7 @@ def run_ours(args):
     elif rank == 0:
         line["cpu_baseline"] = None
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        args.emit(json.dumps(line))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -659,6 +659,25 @@ def run_decode_only(args):
     print(json.dumps({"decode_only_layers": args.decode_only, "steps": args.launches, "launches_per_step": model.launches_per_step()}))
 
 
+class _QuietStdout:
+    """Everything libraries print to file descriptor 1 while the benchmark runs (NCCL announces its version
+    there) goes to stderr; the JSON line is written to the real stdout at the end, alone."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.real = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def emit(self, text: str):
+        os.write(self.real, (text + "\n").encode())
+
+    def __exit__(self, *a):
+        sys.stdout.flush()
+        os.dup2(self.real, 1)
+        os.close(self.real)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -691,7 +710,9 @@ def main():
     else:
         args.steps = 50 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else max(args.warmup, 3)
-        run_ours(args)
+        with _QuietStdout() as out:
+            args.emit = out.emit
+            run_ours(args)
 
 
 if __name__ == "__main__":
