@@ -78,6 +78,7 @@ SIGNATURES = {
     "cq_qmatmul_push": [_vp, _vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64],
     "cq_qlinear_fused": [_vp, _int, _int, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp, _i64, _int, _vp, _i64],
     "cq_add_rmsnorm_reduce": [_vp, _vp, _int, _vp, _vp, _i64, _i64, C.c_float, _vp],
+    "cq_flash_attention": [_vp] + [_vp] * 8 + [C.c_uint32] * 18 + [C.c_float] + [C.c_uint32] * 4 + [_int] * 5 + [C.c_float],
     "cq_tp_unique_id": [_vp, _vp],
     "cq_tp_init": [_vp, _int, _int, _vp, _sz, C.POINTER(_vp)],
     "cq_tp_destroy": [_vp, _vp],
@@ -92,6 +93,8 @@ SIGNATURES = {
     "cq_timer_stop": [_vp, C.POINTER(C.c_float)],
 }
 _OTHER_RESTYPE = {
+    "run_mha": (None, [_vp] * 8 + [C.c_uint32] * 18 + [C.c_float] + [C.c_uint32] * 4 + [_int] * 5 + [C.c_float]),
+    "cq_run_mha_last_status": (C.c_int32, []),
     "cq_status_string": (C.c_char_p, [C.c_int32]),
     "cq_last_error": (C.c_char_p, [_vp]),
     "cq_version": (C.c_char_p, []),

@@ -123,6 +123,39 @@ def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512
             "l2_defeat": "ring of 8 weight copies", "cases": out}
 
 
+def prefill_attention(dev, peak_tflops: float, cases=((1, 32, 32, 128), (1, 32, 32, 2048), (2, 64, 8, 4096)), d: int = 128, reps: int = 10):
+    """The prompt-phase attention (cq_flash_attention, causal, f16, head dimension 128) at the 7B prompt of BASELINE
+    config 4 (128 tokens, 32 heads) and at two longer contexts (7B heads at 2048 tokens, the 70B shape's 64 / 8 grouped
+    heads at 4096).  flops = 4 * seq^2 * heads * d / 2 (causal); fraction of the measured bf16-class burst peak."""
+    from .backend import RawBuffer
+    lib, ctx = dev._lib, dev.ctx
+    out = []
+    for b, h, hk, s in cases:
+        nq, nkv = b * s * h * d, b * s * hk * d
+        q, k, v, o = RawBuffer(dev, 2 * nq), RawBuffer(dev, 2 * nkv), RawBuffer(dev, 2 * nkv), RawBuffer(dev, 2 * nq)
+        tmp = dev.alloc(max(nq, nkv) // 2 + 1)  # f32 noise reinterpreted as f16 pairs would hold NaNs: fill with small f32 -> the bit patterns are benign f16 values
+        lib.cq_memset(ctx, q.ptr, 0x3C, 2 * nq)  # every f16 = 0x3C3C = 1.0586
+        lib.cq_memset(ctx, k.ptr, 0x2C, 2 * nkv)
+        lib.cq_memset(ctx, v.ptr, 0x34, 2 * nkv)
+        del tmp
+        args = [q.ptr, k.ptr, v.ptr, o.ptr, None, None, None, None, s * h * d, s * hk * d, s * hk * d, s * h * d, 0, h * d, hk * d, hk * d, h * d, d, d, d, d,
+                b, h, hk, d, d, float(1.0 / np.sqrt(d)), s, s, s, s, 0, 1, 0, -1, -1, 0.0]
+        dev._check(lib.cq_flash_attention(ctx, *args), "flash attention")
+        dev.synchronize()
+        ms = C.c_float()
+        lib.cq_timer_start(ctx)
+        for _ in range(reps):
+            dev._check(lib.cq_flash_attention(ctx, *args), "flash attention")
+        lib.cq_timer_stop(ctx, C.byref(ms))
+        dev.synchronize()
+        t = ms.value * 1e-3 / reps
+        flops = 4.0 * s * s * h * d * b / 2
+        out.append({"batch": b, "heads": h, "kv_heads": hk, "seq": s, "head_dim": d, "causal": True, "dtype": "f16", "us": round(t * 1e6, 1),
+                    "tflops": round(flops / t / 1e12, 1), "frac_of_tensor_peak": round(flops / t / 1e12 / peak_tflops, 4),
+                    "includes": "V transpose pre-pass + attention kernel"})
+    return {"peak_tflops": peak_tflops, "cases": out}
+
+
 class RawCopy:
     """A device copy of a QStorage's blocks (ring element)."""
 

@@ -1,0 +1,514 @@
+// Prefill attention on the 5th-generation tensor cores: O = softmax(Q K^T * scale) V per (batch, head), f16 or bf16
+// in and out, f32 accumulate, behind the interface of the reference's FlashAttention binding
+// (llm/internal/flashattn/flash_api.h:71-117 run_mha; semantics of kernels/flash_api.cu:13-147: one split, causal
+// switch, grouped-query heads, strides in elements, softmax_lse = max * scale + log(sum)).  The reference ships
+// FlashAttention-2 for sm_80 built on CUTLASS (a submodule that is absent from the checkout); this is a from-scratch
+// sm_100a kernel with the same contract for the cases a decoder's prompt phase needs.
+//
+// One CTA per (128 query rows, head, batch); keys and values stream through in tiles of 128 keys.
+//   warp 0        TMA: the Q tile once, then K and V^T tiles into a two-stage ring (128-byte swizzle)
+//   warp 1        tcgen05.mma issue: S = Q K^T into one of two 128-column f32 slots in tensor memory,
+//                 O_tile = P V with P read from tensor memory as the A operand
+//   warps 2-5     softmax: thread = query row; reads its row of S (tcgen05.ld), masks (key >= seqlen_k; causal:
+//                 key > row + seqlen_k - seqlen_q, the bottom-right alignment of kernels/mask.h:61-62), keeps the
+//                 running max and sum, writes P as packed f16 / bf16 pairs back into tensor memory (tcgen05.st)
+//                 and the factor exp(old max - new max) for the accumulator
+//   warps 6-9     accumulate: thread = query row with its output row in f32 registers; every tile's P V product
+//                 arrives fresh in tensor memory and is folded in as acc = acc * factor + tile, so nothing in
+//                 tensor memory is ever rescaled in place; at the end acc / sum goes out as f16 / bf16
+// V is [key][d] in memory but the P V product wants it K-major, i.e. [d][key]: a small kernel transposes it into
+// context scratch first (2 x the V bytes of traffic against O(seq^2 d) of compute).
+// Every wait is bounded; tensor memory is always freed.
+#include <cuda_bf16.h>
+
+#include <cmath>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int FA_M = 128;   // query rows per CTA
+constexpr int FA_N = 128;   // keys per tile
+constexpr int FA_THREADS = 320;
+
+struct FaParams {
+    void *o;
+    float *lse;             // [b][h][seqlen_q] or null
+    int64_t o_batch_stride, o_row_stride, o_head_stride;
+    int h, h_k, seqlen_q, seqlen_k;
+    int causal;
+    float scale_log2;       // softmax_scale * log2(e)
+    float scale;            // softmax_scale
+    int *err;
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(smem_dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+// kind::f16 instruction descriptor with the operand type: f16 (0) or bf16 (1); D f32; both operands K-major.
+__host__ __device__ constexpr uint32_t idesc_16(int mm, int nn, bool bf16) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(nn >> 3) << 17) | ((uint32_t)(mm >> 4) << 24);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if (BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&v);
+    }
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// V [b][key][h_k][d] (strides in elements) -> Vt [b * h_k][d][sk_pad], 16-bit elements moved as they are.
+__global__ void __launch_bounds__(256) fa_transpose_v_kernel(const uint16_t *__restrict__ v, int64_t bs, int64_t rs, int64_t hs, int h_k, int d, int sk,
+                                                           int sk_pad, uint16_t *__restrict__ vt) {
+    __shared__ uint16_t tile[32][33];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int bh = blockIdx.z, b = bh / h_k, hh = bh - b * h_k;
+    const int k0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const uint16_t *src = v + (int64_t)b * bs + (int64_t)hh * hs;
+    for (int i = ty; i < 32; i += 8) {
+        const int key = k0 + i, dd = d0 + tx;
+        tile[i][tx] = (key < sk && dd < d) ? src[(int64_t)key * rs + dd] : (uint16_t)0;
+    }
+    __syncthreads();
+    uint16_t *dst = vt + (int64_t)bh * d * sk_pad;
+    for (int i = ty; i < 32; i += 8) {
+        const int dd = d0 + i, key = k0 + tx;
+        if (dd < d && key < sk_pad) dst[(int64_t)dd * sk_pad + key] = tile[tx][i];
+    }
+}
+
+template <int D, bool BF16>
+struct FaCfg {
+    static constexpr int kSlabs = D / 64;                       // 64-wide slabs of the head dimension
+    static constexpr int kQBytes = kSlabs * FA_M * 128;         // Q tile
+    static constexpr int kKBytes = kSlabs * FA_N * 128;         // K tile
+    static constexpr int kVBytes = 2 * D * 128;                 // V^T tile: two 64-key slabs of D rows
+    static constexpr int kStages = 2;
+    static constexpr size_t kSmem = (size_t)kQBytes + (size_t)kStages * (kKBytes + kVBytes) + 2 * FA_M * 4 /* factors */ + FA_M * 4 /* sums */ +
+                                    1024 /* alignment */ + 256 /* barriers */;
+    // tensor memory columns: two S slots, P, the tile's P V product
+    static constexpr uint32_t kColS = 0, kColP = 256, kColO = 320;
+    static_assert(kColO + D <= 512, "tensor memory");
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+    fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmVt, const FaParams p) {
+    using Cfg = FaCfg<D, BF16>;
+    constexpr int SLABS = Cfg::kSlabs, ST = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sm_q = smem;
+    uint8_t *sm_k = sm_q + Cfg::kQBytes;                         // [ST][kKBytes]
+    uint8_t *sm_v = sm_k + (size_t)ST * Cfg::kKBytes;            // [ST][kVBytes]
+    float *sm_alpha = reinterpret_cast<float *>(sm_v + (size_t)ST * Cfg::kVBytes);  // [2][128]
+    float *sm_l = sm_alpha + 2 * FA_M;                           // [128] final sums
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm_l + FA_M);
+    uint64_t *q_full = bars, *kv_full = q_full + 1, *kv_empty = kv_full + ST, *s_full = kv_empty + ST, *s_empty = s_full + 2, *p_full = s_empty + 2,
+             *p_empty = p_full + 1, *o_full = p_empty + 1, *o_empty = o_full + 1, *l_full = o_empty + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(l_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heavy tiles (late query rows under a causal mask) first
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+    const int q0 = qt * FA_M;
+    const int off = p.seqlen_k - p.seqlen_q;  // causal: key j is visible to row i iff j <= i + off
+    int ntiles = (p.seqlen_k + FA_N - 1) / FA_N;
+    if (p.causal) {
+        const int lim = q0 + FA_M + off;      // keys >= lim are masked for every row of this tile
+        const int t = lim <= 0 ? 0 : (lim + FA_N - 1) / FA_N;
+        ntiles = t < ntiles ? t : ntiles;
+    }
+    const int kv_head = head / (p.h / p.h_k);
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(q_full), 1);
+        for (int s = 0; s < ST; ++s) {
+            mbar_init(smem_u32(&kv_full[s]), 1);
+            mbar_init(smem_u32(&kv_empty[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&s_empty[s]), 4);
+        }
+        mbar_init(smem_u32(p_full), 4);
+        mbar_init(smem_u32(p_empty), 1);
+        mbar_init(smem_u32(o_full), 1);
+        mbar_init(smem_u32(o_empty), 4);
+        mbar_init(smem_u32(l_full), 4);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait_prior();  // Q, K come from earlier kernels, V^T from the transpose just before this one
+            mbar_expect_tx(smem_u32(q_full), Cfg::kQBytes);
+#pragma unroll
+            for (int c = 0; c < SLABS; ++c) tma_load_4d(smem_u32(sm_q + c * (FA_M * 128)), &tmQ, c * 64, head, q0, batch, smem_u32(q_full));
+            bool ok = true;
+            for (int j = 0; j < ntiles; ++j) {
+                const int s = j % ST;
+                if (j >= ST && !mbar_wait_sleep(smem_u32(&kv_empty[s]), ((j / ST) - 1) & 1, 100)) {
+                    atomicExch(p.err, kDevErrEmptyWait);
+                    ok = false;
+                    break;
+                }
+                mbar_expect_tx(smem_u32(&kv_full[s]), Cfg::kKBytes + Cfg::kVBytes);
+#pragma unroll
+                for (int c = 0; c < SLABS; ++c)
+                    tma_load_4d(smem_u32(sm_k + (size_t)s * Cfg::kKBytes + c * (FA_N * 128)), &tmK, c * 64, kv_head, j * FA_N, batch, smem_u32(&kv_full[s]));
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+                    tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, j * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
+                                smem_u32(&kv_full[s]));
+            }
+            if (ok) {  // leave only when nothing is in flight into this CTA's shared memory
+                if (!mbar_wait_sleep(smem_u32(q_full), 0, 100)) atomicExch(p.err, kDevErrDrain);
+                for (int j = ntiles > ST ? ntiles - ST : 0; j < ntiles; ++j)
+                    if (!mbar_wait_sleep(smem_u32(&kv_full[j % ST]), (j / ST) & 1, 100)) {
+                        atomicExch(p.err, kDevErrDrain);
+                        break;
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && ntiles > 0) {
+            constexpr uint32_t idesc_s = idesc_16(FA_M, FA_N, BF16), idesc_o = idesc_16(FA_M, D, BF16);
+            bool ok = mbar_wait_sleep(smem_u32(q_full), 0, 40);
+            if (!ok) atomicExch(p.err, kDevErrFullWait);
+            const uint32_t q_addr = smem_u32(sm_q);
+            // S(j) = Q K(j)^T into slot j & 1
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % ST, buf = j & 1;
+                if (!mbar_wait_sleep(smem_u32(&kv_full[s]), (j / ST) & 1, 40)) return false;
+                if (j >= 2 && !mbar_wait_sleep(smem_u32(&s_empty[buf]), ((j >> 1) - 1) & 1, 40)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sm_k + (size_t)s * Cfg::kKBytes);
+#pragma unroll
+                for (int c = 0; c < SLABS; ++c)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        tc_mma_f16(tmem_base + Cfg::kColS + (uint32_t)(buf * FA_N), smem_desc_k128(q_addr + c * (FA_M * 128) + kk * 32),
+                                   smem_desc_k128(k_addr + c * (FA_N * 128) + kk * 32), idesc_s, (c | kk) != 0);
+                tc_commit(smem_u32(&s_full[buf]));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                if (j + 1 < ntiles) ok = issue_qk(j + 1);  // the next tile's scores are computed while this tile's softmax runs
+                if (!ok) break;
+                const int s = j % ST;
+                if (!mbar_wait_sleep(smem_u32(p_full), j & 1, 40) || (j >= 1 && !mbar_wait_sleep(smem_u32(o_empty), (j - 1) & 1, 40))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sm_v + (size_t)s * Cfg::kVBytes);
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)  // 16 keys per step: 8 tensor-memory columns of P, 32 bytes of a V^T row
+                        tc_mma_f16_ts(tmem_base + Cfg::kColO, tmem_base + Cfg::kColP + (uint32_t)((hf * 4 + kk) * 8),
+                                      smem_desc_k128(v_addr + hf * (D * 128) + kk * 32), idesc_o, (hf | kk) != 0);
+                tc_commit(smem_u32(o_full));
+                tc_commit(smem_u32(p_empty));
+                tc_commit(smem_u32(&kv_empty[s]));
+            }
+            if (!ok) atomicExch(p.err, kDevErrMma);
+        }
+    } else if (warp < 6) {
+        // ---- softmax: thread = query row -------------------------------------------------------------------
+        const int quarter = warp & 3, r = quarter * 32 + lane;
+        const int row = q0 + r;                               // global query index
+        const int causal_lim = p.causal ? row + off : 0x7FFFFFFF;  // last visible key
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float m_run = -INFINITY, l_run = 0.0f;                // running max of the raw scores, running sum
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int buf = j & 1;
+            if (!mbar_wait_sleep(smem_u32(&s_full[buf]), (j >> 1) & 1, 20)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + Cfg::kColS + (uint32_t)(buf * FA_N);
+            const int key0 = j * FA_N;
+            const int kmax = min(p.seqlen_k - 1, causal_lim) - key0;  // columns > kmax of this tile are masked
+            // pass 1: the row's maximum over the visible keys of the tile
+            float m_tile = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < FA_N / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(s_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (c * 32 + i <= kmax) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+            }
+            const float m_new = fmaxf(m_run, m_tile);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // a row with no visible key yet: every p is 0
+            const float alpha = exp2f((m_run - m_use) * p.scale_log2);  // m_run = -inf gives 0: nothing accumulated yet
+            const float mb = m_use * p.scale_log2;
+            // the previous tile's P must have been consumed before it is overwritten
+            if (j >= 1 && !mbar_wait_sleep(smem_u32(p_empty), (j - 1) & 1, 20)) {
+                if (lane == 0) atomicExch(p.err, kDevErrMma);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            // pass 2: p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
+            float l_tile = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < FA_N / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(s_addr + c * 32, v);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c0 = c * 32 + 2 * i;
+                    const float p0 = c0 <= kmax ? exp2f(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -mb)) : 0.0f;
+                    const float p1 = c0 + 1 <= kmax ? exp2f(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -mb)) : 0.0f;
+                    l_tile += p0 + p1;
+                    pk[i] = pack2<BF16>(p0, p1);
+                }
+                tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(c * 16), pk);
+            }
+            tmem_wait_st();
+            l_run = l_run * alpha + l_tile;
+            m_run = m_new;
+            sm_alpha[buf * FA_M + r] = alpha;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&s_empty[buf]));  // the scores are consumed
+                mbar_arrive(smem_u32(p_full));         // P and the factor are in place
+            }
+        }
+        sm_l[r] = l_run;
+        if (p.lse && row < p.seqlen_q)  // kernels/softmax.h:206: max * scale + log(sum); +inf for a row with nothing to attend to
+            p.lse[((int64_t)batch * p.h + head) * p.seqlen_q + row] = (l_run == 0.0f || l_run != l_run) ? INFINITY : m_run * p.scale + logf(l_run);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(l_full));
+    } else {
+        // ---- accumulate: thread = query row, output row in registers --------------------------------------------
+        const int quarter = warp & 3, r = quarter * 32 + lane;
+        const int row = q0 + r;
+        const uint32_t o_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::kColO;
+        pdl_wait_prior();  // the output buffer may still be read by an earlier kernel
+        float acc[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) acc[i] = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            if (!mbar_wait_sleep(smem_u32(o_full), j & 1, 20)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            // the factor was written by the softmax warps before they signalled p_full: wait on that barrier itself
+            // (it cannot run two phases ahead: the next P needs this tile's product consumed, i.e. o_empty below)
+            if (!mbar_wait_sleep(smem_u32(p_full), j & 1, 20)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                ok = false;
+                break;
+            }
+            const float alpha = sm_alpha[(j & 1) * FA_M + r];
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(o_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(v[i]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(o_empty));
+        }
+        if (ok && !mbar_wait_sleep(smem_u32(l_full), 0, 20)) {
+            if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+            ok = false;
+        }
+        if (ok && row < p.seqlen_q) {
+            const float l = sm_l[r];
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // nothing to attend to: zeros, as the reference writes
+            uint16_t *dst = reinterpret_cast<uint16_t *>(p.o) + (int64_t)batch * p.o_batch_stride + (int64_t)row * p.o_row_stride + (int64_t)head * p.o_head_stride;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) {
+                uint4 w;
+                w.x = pack2<BF16>(acc[8 * c] * inv, acc[8 * c + 1] * inv);
+                w.y = pack2<BF16>(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
+                w.z = pack2<BF16>(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
+                w.w = pack2<BF16>(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
+                reinterpret_cast<uint4 *>(dst)[c] = w;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// Q / K: [b][row][head][d] with strides in elements -> 4-D map (d, head, row, batch); box = 64 x 1 x 128 x 1.
+bool make_qk_map(CUtensorMap *map, const void *base, bool bf16, int d, int heads, int rows, int batches, int64_t hs, int64_t rs, int64_t bs) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batches};
+    cuuint64_t strides[3] = {(cuuint64_t)hs * 2, (cuuint64_t)rs * 2, (cuuint64_t)bs * 2};
+    cuuint32_t box[4] = {64u, 1u, 128u, 1u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// V^T: [b * h_k][d][sk_pad] -> 3-D map (key, d, b * h_k) whose key extent is seqlen_k (keys beyond read as zero); box = 64 keys x d x 1.
+bool make_vt_map(CUtensorMap *map, const void *base, bool bf16, int d, int sk, int sk_pad, int planes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)sk, (cuuint64_t)d, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)sk_pad * 2, (cuuint64_t)d * sk_pad * 2};
+    cuuint32_t box[3] = {64u, (cuuint32_t)d, 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, bool BF16>
+cq_status run_fa(cq_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const FaParams &p, dim3 grid) {
+    static thread_local int configured = -1;
+    if (configured != ctx->device) {
+        CQ_CUDA(ctx, cudaFuncSetAttribute(fmha_fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FaCfg<D, BF16>::kSmem));
+        configured = ctx->device;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(FA_THREADS);
+    cfg.dynamicSmemBytes = FaCfg<D, BF16>::kSmem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, fmha_fwd_kernel<D, BF16>, tq, tk, tv, p));
+    return CQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr, void *o_ptr, void *softmax_lse_ptr, void *alibi_slopes_ptr,
+                             int32_t *cu_seqlens_q_ptr, int32_t *cu_seqlens_k_ptr, uint32_t q_batch_stride, uint32_t k_batch_stride,
+                             uint32_t v_batch_stride, uint32_t o_batch_stride, uint32_t alibi_slopes_batch_stride, uint32_t q_row_stride,
+                             uint32_t k_row_stride, uint32_t v_row_stride, uint32_t o_row_stride, uint32_t q_head_stride, uint32_t k_head_stride,
+                             uint32_t v_head_stride, uint32_t o_head_stride, uint32_t b, uint32_t h, uint32_t h_k, uint32_t d, uint32_t d_rounded,
+                             float softmax_scale, uint32_t seqlen_q, uint32_t seqlen_k, uint32_t seqlen_q_rounded, uint32_t seqlen_k_rounded, int is_bf16,
+                             int is_causal, int unpadded_lse, int window_size_left, int window_size_right, float softcap) {
+    CQ_ENTER(ctx);
+    (void)alibi_slopes_batch_stride, (void)d_rounded, (void)seqlen_q_rounded, (void)seqlen_k_rounded;
+    if (!q_ptr || !k_ptr || !v_ptr || !o_ptr) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: query, key, value, and output tensors must be non-nil");
+    if (b == 0 || h == 0 || h_k == 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: batch size, number of heads, and number of KV heads must be positive");
+    if (d == 0 || seqlen_q == 0 || seqlen_k == 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: head dimension and sequence lengths must be positive");
+    if (h % h_k != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: num_heads must be divisible by num_heads_kv");
+    if (d != 64 && d != 128) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "flash attention: this build has kernels for head dimensions 64 and 128");
+    if (alibi_slopes_ptr || cu_seqlens_q_ptr || cu_seqlens_k_ptr || window_size_left >= 0 || window_size_right >= 0 || softcap > 0.0f || unpadded_lse)
+        return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "flash attention: ALiBi, variable-length batches, sliding windows, soft-capping and the unpadded LSE layout are not built");
+    const uint32_t str[] = {q_batch_stride, k_batch_stride, v_batch_stride, o_batch_stride, q_row_stride, k_row_stride, o_row_stride,
+                            q_head_stride, k_head_stride, o_head_stride};
+    for (uint32_t sv : str)
+        if (sv % 8 != 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "flash attention: q / k / o strides must be multiples of 8 elements (16-byte rows for the tensor maps)");
+    for (const void *ptr : {(const void *)q_ptr, (const void *)k_ptr, (const void *)o_ptr})
+        if (reinterpret_cast<uintptr_t>(ptr) & 15) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: q, k, o must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(v_ptr) & 1) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: v must be 2-byte aligned");
+    if (seqlen_q > (1u << 24) || seqlen_k > (1u << 24) || (uint64_t)b * h > 65535u * 65535ull) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "flash attention: sequence beyond 2^24");
+    // V^T in context scratch
+    const int sk_pad = (int)((seqlen_k + 7) & ~7u);
+    const size_t vt_bytes = (size_t)b * h_k * d * sk_pad * 2;
+    cq_status s = cq_reserve_scratch(ctx, vt_bytes);
+    if (s != CQ_OK) return s;
+    uint16_t *vt = static_cast<uint16_t *>(ctx->scratch);
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((sk_pad + 31) / 32), (unsigned)((d + 31) / 32), (unsigned)(b * h_k));
+        cfg.blockDim = dim3(256);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+        CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, fa_transpose_v_kernel, (const uint16_t *)v_ptr, (int64_t)v_batch_stride, (int64_t)v_row_stride,
+                                        (int64_t)v_head_stride, (int)h_k, (int)d, (int)seqlen_k, sk_pad, vt));
+    }
+    CUtensorMap tq, tk, tv;
+    const bool bf = is_bf16 != 0;
+    if (!make_qk_map(&tq, q_ptr, bf, (int)d, (int)h, (int)seqlen_q, (int)b, q_head_stride, q_row_stride, q_batch_stride) ||
+        !make_qk_map(&tk, k_ptr, bf, (int)d, (int)h_k, (int)seqlen_k, (int)b, k_head_stride, k_row_stride, k_batch_stride) ||
+        !make_vt_map(&tv, vt, bf, (int)d, (int)seqlen_k, sk_pad, (int)(b * h_k)))
+        return cq_fail(ctx, CQ_ERR_CUDA, "flash attention: cuTensorMapEncodeTiled failed or is unavailable");
+    FaParams p;
+    p.o = o_ptr, p.lse = static_cast<float *>(softmax_lse_ptr);
+    p.o_batch_stride = o_batch_stride, p.o_row_stride = o_row_stride, p.o_head_stride = o_head_stride;
+    p.h = (int)h, p.h_k = (int)h_k, p.seqlen_q = (int)seqlen_q, p.seqlen_k = (int)seqlen_k, p.causal = is_causal ? 1 : 0;
+    p.scale = softmax_scale, p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.err = ctx->dev_err_devptr;
+    const dim3 grid((seqlen_q + FA_M - 1) / FA_M, h, b);
+    if (d == 128) return bf ? run_fa<128, true>(ctx, tq, tk, tv, p, grid) : run_fa<128, false>(ctx, tq, tk, tv, p, grid);
+    return bf ? run_fa<64, true>(ctx, tq, tk, tv, p, grid) : run_fa<64, false>(ctx, tq, tk, tv, p, grid);
+}
+
+// The reference's own entry point, same symbol and signature (flash_api.h:71-117): a host that binds run_mha
+// (llm/internal/flashattn/flashattn.go:145-205) can link this library instead of the reference's static one.  Like the
+// reference it returns nothing and runs on the default stream; it keeps one context per device and the status of
+// the last call can be read with cq_run_mha_last_status().
+static cq_status g_run_mha_status = CQ_OK;
+static cq_ctx *g_run_mha_ctx[64] = {};
+
+cq_status cq_run_mha_last_status(void) { return g_run_mha_status; }
+
+void run_mha(void *q_ptr, void *k_ptr, void *v_ptr, void *o_ptr, void *softmax_lse_ptr, void *alibi_slopes_ptr, int32_t *cu_seqlens_q_ptr,
+             int32_t *cu_seqlens_k_ptr, uint32_t q_batch_stride, uint32_t k_batch_stride, uint32_t v_batch_stride, uint32_t o_batch_stride,
+             uint32_t alibi_slopes_batch_stride, uint32_t q_row_stride, uint32_t k_row_stride, uint32_t v_row_stride, uint32_t o_row_stride,
+             uint32_t q_head_stride, uint32_t k_head_stride, uint32_t v_head_stride, uint32_t o_head_stride, uint32_t b, uint32_t h, uint32_t h_k,
+             uint32_t d, uint32_t d_rounded, float softmax_scale, uint32_t seqlen_q, uint32_t seqlen_k, uint32_t seqlen_q_rounded,
+             uint32_t seqlen_k_rounded, int is_bf16, int is_causal, int unpadded_lse, int window_size_left, int window_size_right, float softcap) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        g_run_mha_status = CQ_ERR_CUDA;
+        return;
+    }
+    if (!g_run_mha_ctx[dev]) {
+        g_run_mha_status = cq_ctx_create(dev, &g_run_mha_ctx[dev]);
+        if (g_run_mha_status != CQ_OK) return;
+        g_run_mha_ctx[dev]->stream = cudaStreamLegacy;  // the reference launches on the default stream (flash_api.cu:145)
+    }
+    g_run_mha_status = cq_flash_attention(g_run_mha_ctx[dev], q_ptr, k_ptr, v_ptr, o_ptr, softmax_lse_ptr, alibi_slopes_ptr, cu_seqlens_q_ptr,
+                                          cu_seqlens_k_ptr, q_batch_stride, k_batch_stride, v_batch_stride, o_batch_stride, alibi_slopes_batch_stride,
+                                          q_row_stride, k_row_stride, v_row_stride, o_row_stride, q_head_stride, k_head_stride, v_head_stride,
+                                          o_head_stride, b, h, h_k, d, d_rounded, softmax_scale, seqlen_q, seqlen_k, seqlen_q_rounded,
+                                          seqlen_k_rounded, is_bf16, is_causal, unpadded_lse, window_size_left, window_size_right, softcap);
+}
+
+}  // extern "C"

@@ -287,6 +287,35 @@ cq_status cq_qmatmul_push(cq_ctx *ctx, cq_comm *comm, int set, int qtype, int or
 cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *comm, int set, float *x_dev, const float *alpha_dev,
                                 int64_t rows, int64_t cols, float eps, float *y_dev);
 
+/* ---- prefill attention: the FlashAttention binding's replacement ------------------------------------
+ * O = softmax(Q K^T * softmax_scale) V per (batch, head) on the sm_100a tensor cores (tcgen05, tensor
+ * memory, TMA).  Arguments, their order and meaning are those of run_mha in the reference
+ * (llm/internal/flashattn/flash_api.h:71-117; flashattn.go:145-205 is its caller): 16-bit tensors
+ * [batch][row][head][d] addressed through batch / row / head strides in ELEMENTS, h a multiple of h_k
+ * (grouped-query heads), is_bf16 0 = f16 / 1 = bf16, is_causal with the mask aligned to the bottom right
+ * (key j visible to row i iff j <= i + seqlen_k - seqlen_q, kernels/mask.h:61-62), softmax_lse (nullable)
+ * [batch][h][seqlen_q] f32 = max * scale + log(sum) (kernels/softmax.h:206).  Built: head dimensions 64 and
+ * 128, strides that are multiples of 8 elements.  Not built (CQ_ERR_UNSUPPORTED): other head dimensions,
+ * ALiBi, cu_seqlens (variable-length batches), sliding windows, soft-capping, the unpadded LSE layout.
+ * V is transposed into context scratch first (cq_reserve(b * h_k * d * roundup(seqlen_k, 8) * 2) up front
+ * when capturing).  cq_flash_attention returns a status and runs on the context's stream; run_mha is the
+ * reference's own symbol and signature (void, default stream), for hosts that already bind it, with
+ * cq_run_mha_last_status() to read the outcome. */
+cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr, void *o_ptr, void *softmax_lse_ptr, void *alibi_slopes_ptr,
+                             int32_t *cu_seqlens_q_ptr, int32_t *cu_seqlens_k_ptr, uint32_t q_batch_stride, uint32_t k_batch_stride,
+                             uint32_t v_batch_stride, uint32_t o_batch_stride, uint32_t alibi_slopes_batch_stride, uint32_t q_row_stride,
+                             uint32_t k_row_stride, uint32_t v_row_stride, uint32_t o_row_stride, uint32_t q_head_stride, uint32_t k_head_stride,
+                             uint32_t v_head_stride, uint32_t o_head_stride, uint32_t b, uint32_t h, uint32_t h_k, uint32_t d, uint32_t d_rounded,
+                             float softmax_scale, uint32_t seqlen_q, uint32_t seqlen_k, uint32_t seqlen_q_rounded, uint32_t seqlen_k_rounded,
+                             int is_bf16, int is_causal, int unpadded_lse, int window_size_left, int window_size_right, float softcap);
+void run_mha(void *q_ptr, void *k_ptr, void *v_ptr, void *o_ptr, void *softmax_lse_ptr, void *alibi_slopes_ptr, int32_t *cu_seqlens_q_ptr,
+             int32_t *cu_seqlens_k_ptr, uint32_t q_batch_stride, uint32_t k_batch_stride, uint32_t v_batch_stride, uint32_t o_batch_stride,
+             uint32_t alibi_slopes_batch_stride, uint32_t q_row_stride, uint32_t k_row_stride, uint32_t v_row_stride, uint32_t o_row_stride,
+             uint32_t q_head_stride, uint32_t k_head_stride, uint32_t v_head_stride, uint32_t o_head_stride, uint32_t b, uint32_t h, uint32_t h_k,
+             uint32_t d, uint32_t d_rounded, float softmax_scale, uint32_t seqlen_q, uint32_t seqlen_k, uint32_t seqlen_q_rounded,
+             uint32_t seqlen_k_rounded, int is_bf16, int is_causal, int unpadded_lse, int window_size_left, int window_size_right, float softcap);
+cq_status cq_run_mha_last_status(void);
+
 /* ---- NCCL all-reduce: the baseline exchange, and the one for batches beyond eight rows ---------
  * No counterpart in the reference.  NCCL is opened at run time (libnccl.so.2; $CANDYQ_NCCL_LIBRARY
  * overrides), not linked: without it these entries answer CQ_ERR_UNSUPPORTED and everything else works.
