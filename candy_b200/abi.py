@@ -19,7 +19,9 @@ ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NOMEM, ERR_TOO_LARG
 Q4_0, Q4_1, Q5_0, Q5_1, Q8_0 = 2, 3, 6, 7, 8
 ORDER_GO_INTERLEAVED, ORDER_GGML_SPLIT = 0, 1
 ACT_F32, ACT_Q8_1, ACT_F16 = 0, 1, 2
+Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 10, 11, 12, 13, 14
 BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34}
+K_BLOCK_BYTES = {Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210}  # per 256 values
 Q8_1_BYTES = 36
 
 

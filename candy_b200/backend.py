@@ -182,12 +182,13 @@ class QStorage:
     storage type that carries them behind the device API."""
 
     def __init__(self, device: CudaDevice, qtype: int, order: int, n: int, k: int, buf: RawBuffer):
-        if qtype not in abi.BLOCK_BYTES:
+        if qtype not in abi.BLOCK_BYTES and qtype not in abi.K_BLOCK_BYTES:
             raise ValueError(f"qstorage: unknown block format {qtype}")
-        if k <= 0 or k % 32 != 0:
-            raise ValueError(f"qstorage: k must be a positive multiple of 32, got {k}")
-        if buf.nbytes != n * (k // 32) * abi.BLOCK_BYTES[qtype]:
-            raise ValueError("qstorage: byte count does not match n*k/32 blocks")
+        per = 256 if qtype in abi.K_BLOCK_BYTES else 32  # values per block
+        if k <= 0 or k % per != 0:
+            raise ValueError(f"qstorage: k must be a positive multiple of {per}, got {k}")
+        if buf.nbytes != n * (k // per) * (abi.K_BLOCK_BYTES.get(qtype) or abi.BLOCK_BYTES[qtype]):
+            raise ValueError("qstorage: byte count does not match the block count")
         self._dev, self.qtype, self.order, self.n, self.k, self.buf = device, qtype, order, n, k, buf
 
     @classmethod
@@ -217,7 +218,8 @@ class QStorage:
     def dequantize(self) -> CudaStorage:
         d = self._dev
         out = d.alloc(self.n * self.k)
-        d._check(d._lib.cq_dequantize(d.ctx, self.qtype, self.order, self.buf.ptr, self.n * (self.k // 32), out.ptr), "dequantize")
+        per = 256 if self.qtype in abi.K_BLOCK_BYTES else 32
+        d._check(d._lib.cq_dequantize(d.ctx, self.qtype, self.order, self.buf.ptr, self.n * (self.k // per), out.ptr), "dequantize")
         return out
 
 

@@ -133,11 +133,9 @@ def prefill_attention(dev, peak_tflops: float, cases=((1, 32, 32, 128), (1, 32, 
     for b, h, hk, s in cases:
         nq, nkv = b * s * h * d, b * s * hk * d
         q, k, v, o = RawBuffer(dev, 2 * nq), RawBuffer(dev, 2 * nkv), RawBuffer(dev, 2 * nkv), RawBuffer(dev, 2 * nq)
-        tmp = dev.alloc(max(nq, nkv) // 2 + 1)  # f32 noise reinterpreted as f16 pairs would hold NaNs: fill with small f32 -> the bit patterns are benign f16 values
-        lib.cq_memset(ctx, q.ptr, 0x3C, 2 * nq)  # every f16 = 0x3C3C = 1.0586
+        lib.cq_memset(ctx, q.ptr, 0x3C, 2 * nq)  # constant fills (every f16 = 0x3C3C = 1.06 ...): the kernel's time does not depend on the values
         lib.cq_memset(ctx, k.ptr, 0x2C, 2 * nkv)
         lib.cq_memset(ctx, v.ptr, 0x34, 2 * nkv)
-        del tmp
         args = [q.ptr, k.ptr, v.ptr, o.ptr, None, None, None, None, s * h * d, s * hk * d, s * hk * d, s * h * d, 0, h * d, hk * d, hk * d, h * d, d, d, d, d,
                 b, h, hk, d, d, float(1.0 / np.sqrt(d)), s, s, s, s, 0, 1, 0, -1, -1, 0.0]
         dev._check(lib.cq_flash_attention(ctx, *args), "flash attention")

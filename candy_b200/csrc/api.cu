@@ -258,6 +258,7 @@ cq_status cq_synchronize(cq_ctx *ctx) {
 
 size_t cq_blocks_bytes(int qtype, int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || k % kQK != 0) return 0;
+    if (cq_is_k_format(qtype)) return k % 256 == 0 ? (size_t)n * (size_t)(k / 256) * (size_t)cq_k_block_bytes(qtype) : 0;
     if (qtype == CQ_Q4_0) return (size_t)n * (size_t)(k / kQK) * kQ4Bytes;
     if (qtype == CQ_Q8_0) return (size_t)n * (size_t)(k / kQK) * kQ8Bytes;
     if (cq_is_more_format(qtype)) return (size_t)n * (size_t)(k / kQK) * (size_t)cq_more_block_bytes(qtype);
@@ -265,12 +266,14 @@ size_t cq_blocks_bytes(int qtype, int64_t n, int64_t k) {
 }
 
 static cq_status check_qtype_order(cq_ctx *ctx, int qtype, int order) {
-    if (qtype != CQ_Q4_0 && qtype != CQ_Q8_0 && !cq_is_more_format(qtype))
-        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "qtype must be CQ_Q4_0, CQ_Q4_1, CQ_Q5_0, CQ_Q5_1 or CQ_Q8_0");
+    if (qtype != CQ_Q4_0 && qtype != CQ_Q8_0 && !cq_is_more_format(qtype) && !cq_is_k_format(qtype))
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "qtype must be CQ_Q4_0, CQ_Q4_1, CQ_Q5_0, CQ_Q5_1, CQ_Q8_0 or CQ_Q2_K .. CQ_Q6_K");
     if (order != CQ_ORDER_GO_INTERLEAVED && order != CQ_ORDER_GGML_SPLIT)
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "order must be 0 (interleaved) or 1 (split)");
     if (cq_is_more_format(qtype) && !cq_more_order_ok(qtype, order))
         return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "Q5_0 / Q5_1 exist in the split order only");
+    if (cq_is_k_format(qtype) && order != CQ_ORDER_GGML_SPLIT)
+        return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "the K formats have one element order, the reference CUDA kernels': pass CQ_ORDER_GGML_SPLIT");
     return CQ_OK;
 }
 
@@ -280,6 +283,7 @@ cq_status cq_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w_dev
     cq_status s = check_qtype_order(ctx, qtype, order);
     if (s != CQ_OK) return s;
     if (!w_dev || !blocks_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: null pointer");
+    if (cq_is_k_format(qtype)) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "cq_quantize_rows: the reference has no quantizer for the K formats and neither has this library; load such weights from a file");
     if (n < 1 || k < kQK || k % kQK != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_quantize_rows: need n >= 1, k >= 32, k % 32 == 0");
     cq_w16_invalidate(ctx, blocks_dev, cq_blocks_bytes(qtype, n, k));
     if (cq_is_more_format(qtype)) return launch_quantize_rows_more(ctx, qtype, order, w_dev, n * (k / kQK), blocks_dev);
@@ -293,6 +297,7 @@ cq_status cq_dequantize(cq_ctx *ctx, int qtype, int order, const void *blocks_de
     if (nblocks == 0) return CQ_OK;
     if (!blocks_dev || !y_dev) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_dequantize: null pointer");
     if (nblocks < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_dequantize: negative block count");
+    if (cq_is_k_format(qtype)) return launch_dequantize_k(ctx, qtype, blocks_dev, nblocks, y_dev);
     if (cq_is_more_format(qtype)) return launch_dequantize_more(ctx, qtype, order, blocks_dev, nblocks, y_dev);
     return launch_dequantize(ctx, qtype, order, blocks_dev, nblocks, y_dev);
 }
@@ -314,6 +319,7 @@ static cq_status check_matmul_args(cq_ctx *ctx, int qtype, int order, int actmod
     if (!x || !w || !y) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: null pointer");
     if (m < 1 || n < 1) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: m and n must be >= 1");
     if (k < kQK || k % kQK != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: k must be a positive multiple of 32");
+    if (cq_is_k_format(qtype) && k % 256 != 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: the K formats need k to be a multiple of 256");
     if (ldx < k) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: ldx < k");
     if (ldy < n) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_qmatmul: ldy < n");
     if (m > (int64_t(1) << 24) || n > (int64_t(1) << 28) || k > (int64_t(1) << 24))

@@ -133,6 +133,13 @@ cq_status launch_quantize_rows_more(cq_ctx *ctx, int qtype, int order, const flo
 cq_status launch_w_to_f16_more(cq_ctx *ctx, int qtype, int order, const void *blocks, int64_t nblocks, void *out_f16);
 cq_status launch_gemv_more(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w,
                            int64_t n, float *y, int64_t ldy);
+// K super-block formats, 256 values per block (kquants.cu)
+bool cq_is_k_format(int qtype);
+int cq_k_block_bytes(int qtype);
+cq_status launch_dequantize_k(cq_ctx *ctx, int qtype, const void *blocks, int64_t nblocks, float *y);
+cq_status launch_w_to_f16_k(cq_ctx *ctx, int qtype, const void *blocks, int64_t nblocks, void *out_f16);
+cq_status launch_gemv_k(cq_ctx *ctx, int qtype, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, float *y,
+                        int64_t ldy);
 // Narrow-batch GEMM that dequantizes raw blocks into tensor memory (gemm_dequant_tmem.cu).
 bool qgemm_dequant_tmem_supported(int qtype, int64_t m, int64_t k, const void *w);
 cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,

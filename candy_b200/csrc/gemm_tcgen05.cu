@@ -370,7 +370,7 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
         return cq_fail(ctx, CQ_ERR_INVALID_ARG, "gemm: misaligned pointer");
     if (m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "gemm: dimension beyond 2^31");
     // narrow batches stream the raw blocks and dequantize into tensor memory: no f16 copy of W
-    if (!cq_is_more_format(qtype) && ctx->tune.gemm_variant != 3 && !ctx->tune.gemm_cache_weights && qgemm_dequant_tmem_supported(qtype, m, k, w))
+    if (!cq_is_more_format(qtype) && !cq_is_k_format(qtype) && ctx->tune.gemm_variant != 3 && !ctx->tune.gemm_cache_weights && qgemm_dequant_tmem_supported(qtype, m, k, w))
         return launch_qgemm_dequant_tmem(ctx, qtype, order, x, m, k, ldx, w, n, y, ldy);
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
     const size_t w16_bytes = (size_t)n * k * 2;
@@ -410,7 +410,10 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
         const int64_t total = nblocks * 4;
         const unsigned grid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
         const uint8_t *wb = static_cast<const uint8_t *>(w);
-        if (cq_is_more_format(qtype)) {
+        if (cq_is_k_format(qtype)) {
+            cq_status s2 = launch_w_to_f16_k(ctx, qtype, w, n * (k / 256), w16);
+            if (s2 != CQ_OK) return s2;
+        } else if (cq_is_more_format(qtype)) {
             cq_status s2 = launch_w_to_f16_more(ctx, qtype, order, w, nblocks, w16);
             if (s2 != CQ_OK) return s2;
         } else if (qtype == CQ_Q4_0 && order == CQ_ORDER_GO_INTERLEAVED) w_to_f16_kernel<CQ_Q4_0, 0><<<grid, 256, 0, ctx->stream>>>(wb, nblocks, w16);

@@ -1876,6 +1876,10 @@ bool try_stream_more(cq_ctx *ctx, const float *x, int64_t m, int64_t k, int64_t 
 
 cq_status launch_gemv(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k, int64_t ldx,
                       const void *w, int64_t n, float *y, int64_t ldy) {
+    if (cq_is_k_format(qtype)) {
+        if (ctx->fuse.on || ctx->push.world != 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "fused and multi-GPU GEMVs take Q4_0 / Q8_0 only");
+        return launch_gemv_k(ctx, qtype, actmode, x, m, k, ldx, w, n, y, ldy);
+    }
     if (cq_is_more_format(qtype)) {
         if (ctx->fuse.on || ctx->push.world != 0) return cq_fail(ctx, CQ_ERR_UNSUPPORTED, "fused and multi-GPU GEMVs take Q4_0 / Q8_0 only");
         if (actmode == CQ_ACT_F32) {

@@ -1,4 +1,4 @@
-"""Weight files for the quantized linear: a GGUF tensor reader (F32 / F16 / Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0) and NPZ.
+"""Weight files for the quantized linear: a GGUF tensor reader (F32 / F16 / Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 / Q2_K .. Q6_K) and NPZ.
 
 GGUF is the container llama.cpp-family tools write; its Q4_0 / Q8_0 tensors are exactly the block
 streams this library consumes (18 / 34 bytes per 32 values, f16 scale first), with the Q4_0 nibbles
@@ -24,7 +24,9 @@ from typing import Dict, Tuple
 import numpy as np
 
 GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q8_0 = 0, 1, 2, 3, 6, 7, 8
-_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q8_0: (32, 34)}  # values, bytes per block
+GGML_Q2_K, GGML_Q3_K, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K = 10, 11, 12, 13, 14
+_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q8_0: (32, 34),
+          GGML_Q2_K: (256, 84), GGML_Q3_K: (256, 110), GGML_Q4_K: (256, 144), GGML_Q5_K: (256, 176), GGML_Q6_K: (256, 210)}  # values, bytes per block
 _ELEM = {GGML_F32: 4, GGML_F16: 2}
 
 # metadata value types of the GGUF specification
@@ -144,7 +146,7 @@ def read_gguf(path) -> Tuple[Dict[str, object], Dict[str, GGUFTensor]]:
 
 
 def load_linear(dev, t: GGUFTensor):
-    """A 2-D Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 tensor [n, k] as a device QStorage in the GGML split order, bytes unchanged."""
+    """A 2-D block-format tensor [n, k] (Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 / Q2_K .. Q6_K) as a device QStorage in the GGML order, bytes unchanged."""
     from .backend import QStorage, ORDER_GGML_SPLIT
     if len(t.shape) != 2 or not t.is_quantized:
         raise GGUFError(f"{t.name}: expected a 2-D block-quantized tensor, got type {t.ggml_type} shape {t.shape}")

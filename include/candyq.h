@@ -50,7 +50,15 @@ enum cq_qtype {
     CQ_Q4_1 = 3, /* 20 bytes {f16 d; f16 m; u8 qs[16]}: d*q + m         quantized.go:13-17, :107-116        */
     CQ_Q5_0 = 6, /* 22 bytes {f16 d; u32 qh; u8 qs[16]}: d*(q-16)       quantized.go:19-24, quantized.cu:749-771 */
     CQ_Q5_1 = 7, /* 24 bytes {f16 d; f16 m; u32 qh; u8 qs[16]}: d*q + m quantized.go:26-31, quantized.cu:773-795 */
-    CQ_Q8_0 = 8
+    CQ_Q8_0 = 8,
+    /* 256-value super-blocks, defined by the reference's CUDA dequantizers (quantized.cu:366-436 layouts, :899-1147):
+     * dequantize (bit-exact), decode GEMV with f32 activations, tensor-core GEMM through an f16 copy; no quantizer
+     * (the reference has none), k % 256 == 0, order CQ_ORDER_GGML_SPLIT only. */
+    CQ_Q2_K = 10, /* 84 bytes  */
+    CQ_Q3_K = 11, /* 110 bytes */
+    CQ_Q4_K = 12, /* 144 bytes */
+    CQ_Q5_K = 13, /* 176 bytes */
+    CQ_Q6_K = 14  /* 210 bytes */
 };
 /* Q4_1 / Q5_0 / Q5_1: dequantize, quantize and matmul with CQ_ACT_F32 (a plain GEMV) or CQ_ACT_F16
  * (tensor-core GEMM through an f16 copy); CQ_ACT_Q8_1 and the fused / multi-GPU entries answer
@@ -135,7 +143,7 @@ size_t cq_blocks_bytes(int qtype, int64_t n, int64_t k);
 cq_status cq_quantize_rows(cq_ctx *ctx, int qtype, int order, const float *w_dev, int64_t n,
                            int64_t k, void *blocks_dev);
 
-/* blocks -> f32, bit-exact.  Replaces DequantizeBlockQ4_0F32 / DequantizeBlockQ8_0F32
+/* blocks -> f32, bit-exact (nblocks counts 32-value blocks, or 256-value super-blocks for the K formats).  Replaces DequantizeBlockQ4_0F32 / DequantizeBlockQ8_0F32
  * (tensor/internal/cpu/kernels/quantized.go:85-93, :131-136, f16 decode :149-173) and the
  * kernels dequantize_block_q4_0_f32 / dequantize_block_q8_0_f32 (quantized.cu:838-867,
  * :1149-1175). */

@@ -412,6 +412,135 @@ int co_qmatmul(int qtype, int order, const float *x, int64_t m, int64_t k, int64
     return 0;
 }
 
+/* ---- K super-block formats (256 values), tensor/internal/cuda/kernels/quantized.cu:366-436 (layouts) and
+ * :899-1147 (dequantizers): the reference's only code for them is CUDA, restated here value by value, in
+ * value order, with each kernel's expression and operation order.  GGML type ids 10..14.  Pinned bit for bit
+ * against the third-party gguf package's dequantizers (tests/test_kquants.py). */
+static int64_t co_k_block_bytes(int qtype) {
+    switch (qtype) {
+    case 10: return 84;
+    case 11: return 110;
+    case 12: return 144;
+    case 13: return 176;
+    case 14: return 210;
+    default: return 0;
+    }
+}
+
+/* get_scale_min_k4, quantized.cu:994-1006 */
+static void co_scale_min_k4(int j, const uint8_t *q, int *d, int *m) {
+    if (j < 4) {
+        *d = q[j] & 63;
+        *m = q[j + 4] & 63;
+    } else {
+        *d = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+        *m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+void co_dequantize_k(int qtype, const uint8_t *blocks, int64_t nblocks, float *y) {
+    const int64_t bb = co_k_block_bytes(qtype);
+    for (int64_t ib = 0; ib < nblocks; ++ib) {
+        const uint8_t *b = blocks + ib * bb;
+        float *out = y + ib * 256;
+        if (qtype == 10) { /* dequantize_block_q2_K, quantized.cu:902-925 */
+            const float dall = co_fp16_to_f32(load_u16(b + 80)), dmin = co_fp16_to_f32(load_u16(b + 82));
+            const uint8_t *scales = b, *qs = b + 16;
+            for (int n = 0; n < 2; ++n)
+                for (int l = 0; l < 32; ++l) {
+                    const int is = 8 * n + l / 16;
+                    const uint8_t q = qs[32 * n + l];
+                    for (int j = 0; j < 4; ++j) {
+                        const uint8_t sc = scales[is + 2 * j];
+                        float t = dall * (float)(sc & 0xF);
+                        t = t * (float)((q >> (2 * j)) & 3);
+                        const float mn = dmin * (float)(sc >> 4);
+                        out[128 * n + 32 * j + l] = t - mn;
+                    }
+                }
+        } else if (qtype == 11) { /* dequantize_block_q3_K, quantized.cu:937-969 */
+            const uint8_t *hm = b, *qs = b + 32, *sc = b + 96;
+            const float d_all = co_fp16_to_f32(load_u16(b + 108));
+            for (int n = 0; n < 2; ++n)
+                for (int j = 0; j < 4; ++j)
+                    for (int is0 = 0; is0 < 2; ++is0) {
+                        const int is = 8 * n + 2 * j + is0;
+                        const int us = is < 4 ? (sc[is] & 0xF) | (((sc[is + 8] >> 0) & 3) << 4)
+                                     : is < 8 ? (sc[is] & 0xF) | (((sc[is + 4] >> 2) & 3) << 4)
+                                     : is < 12 ? (sc[is - 8] >> 4) | (((sc[is] >> 4) & 3) << 4)
+                                               : (sc[is - 8] >> 4) | (((sc[is - 4] >> 6) & 3) << 4);
+                        const float dl = d_all * (float)((int)(int8_t)us - 32);
+                        const uint8_t m = (uint8_t)(1 << (4 * n + j));
+                        for (int l = 16 * is0; l < 16 * is0 + 16; ++l)
+                            out[128 * n + 32 * j + l] = dl * (float)((int)(int8_t)((qs[32 * n + l] >> (2 * j)) & 3) - ((hm[l] & m) ? 0 : 4));
+                    }
+        } else if (qtype == 12 || qtype == 13) { /* dequantize_block_q4_K :1008-1042, _q5_K :1049-1082 */
+            const float dall = co_fp16_to_f32(load_u16(b)), dmin = co_fp16_to_f32(load_u16(b + 2));
+            const uint8_t *scales = b + 4;
+            const uint8_t *qh = b + 16;                         /* Q5_K only */
+            const uint8_t *qs = b + (qtype == 12 ? 16 : 48);
+            for (int il = 0; il < 4; ++il)
+                for (int h = 0; h < 2; ++h) {
+                    int sc, m;
+                    co_scale_min_k4(2 * il + h, scales, &sc, &m);
+                    const float d1 = dall * (float)sc, m1 = dmin * (float)m;
+                    for (int l = 0; l < 32; ++l) {
+                        int q = h ? (qs[32 * il + l] >> 4) : (qs[32 * il + l] & 0xF);
+                        if (qtype == 13) q += (qh[l] & (1 << (2 * il + h))) ? 16 : 0;
+                        const float t = d1 * (float)q;
+                        out[64 * il + 32 * h + l] = t - m1;
+                    }
+                }
+        } else { /* dequantize_block_q6_K, quantized.cu:1099-1123 */
+            const uint8_t *ql = b, *qh = b + 128;
+            const int8_t *sc = (const int8_t *)(b + 192);
+            const float d = co_fp16_to_f32(load_u16(b + 208));
+            for (int ip = 0; ip < 2; ++ip)
+                for (int il = 0; il < 32; ++il) {
+                    const int is = 8 * ip + il / 16;
+                    const uint8_t h = qh[32 * ip + il];
+                    const uint8_t *q = ql + 64 * ip + il;
+                    const int v[4] = {(int)(int8_t)((q[0] & 0xF) | (((h >> 0) & 3) << 4)) - 32, (int)(int8_t)((q[32] & 0xF) | (((h >> 2) & 3) << 4)) - 32,
+                                      (int)(int8_t)((q[0] >> 4) | (((h >> 4) & 3) << 4)) - 32, (int)(int8_t)((q[32] >> 4) | (((h >> 6) & 3) << 4)) - 32};
+                    for (int t = 0; t < 4; ++t) {
+                        const float ds = d * (float)sc[is + 2 * t];
+                        out[128 * ip + 32 * t + il] = ds * (float)v[t];
+                    }
+                }
+        }
+    }
+}
+
+/* y = x . W^T for a K-format W [n,k] (k % 256 == 0): dequantize each row, then the sequential f32 dot of
+ * candy's CPU matmul (conv.go:373-389), as co_qmatmul does for the 32-value formats. */
+int co_qmatmul_k(int qtype, const float *x, int64_t m, int64_t k, int64_t ldx, const uint8_t *wblocks, int64_t n, float *y, int64_t ldy,
+                 int nthreads) {
+    const int64_t bb = co_k_block_bytes(qtype);
+    if (bb == 0) return -2;
+    if (k <= 0 || k % 256 != 0 || m <= 0 || n <= 0) return -1;
+    const int64_t nsb = k / 256;
+    if (nthreads < 1) nthreads = 1;
+#pragma omp parallel num_threads(nthreads)
+    {
+        float *wrow = (float *)malloc((size_t)k * sizeof(float));
+#pragma omp for schedule(static)
+        for (int64_t j = 0; j < n; ++j) {
+            co_dequantize_k(qtype, wblocks + j * nsb * bb, nsb, wrow);
+            for (int64_t i = 0; i < m; ++i) {
+                float sum = 0.0f;
+                const float *xi = x + i * ldx;
+                for (int64_t l = 0; l < k; ++l) {
+                    float prod = xi[l] * wrow[l];
+                    sum = sum + prod;
+                }
+                y[i * ldy + j] = sum;
+            }
+        }
+        free(wrow);
+    }
+    return 0;
+}
+
 /* f32 activations -> Q8_1 blocks {half d; half sum; int8 q[32]},
  * tensor/internal/cuda/kernels/quantized.cu:3521-3558 (struct at :349-357):
  * d = amax/127; q = amax==0 ? 0 : roundf(x/d) (true division by the f32 d);

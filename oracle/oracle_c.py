@@ -14,6 +14,8 @@ Q4_0, Q4_1, Q5_0, Q5_1, Q8_0 = 2, 3, 6, 7, 8
 ORDER_GO, ORDER_SPLIT = 0, 1
 BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34}
 Q8_1_BYTES = 36
+Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 10, 11, 12, 13, 14
+K_BLOCK_BYTES = {Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210}  # per 256 values
 
 _lib = None
 
@@ -36,6 +38,9 @@ def lib():
         _lib.co_dequantize_q5.argtypes = [C.c_int, p, i64, p]
         _lib.co_quantize_more.argtypes = [C.c_int, p, i64, C.c_int, p]
         _lib.co_matmul_strided_f32.argtypes = [i64, i64, i64, i64, p, p, p, p, p, p]
+        _lib.co_dequantize_k.argtypes = [C.c_int, p, i64, p]
+        _lib.co_qmatmul_k.restype = C.c_int
+        _lib.co_qmatmul_k.argtypes = [C.c_int, p, i64, i64, i64, p, i64, p, i64, C.c_int]
         for f in (_lib.co_qmatmul, _lib.co_qmatmul_q8_1):
             f.restype = C.c_int
             f.argtypes = [C.c_int, C.c_int, p, i64, i64, i64, p, i64, p, i64, C.c_int]
@@ -67,6 +72,27 @@ def dequantize(qtype: int, order: int, blocks: np.ndarray) -> np.ndarray:
         lib().co_dequantize_q5(qtype, _ptr(blocks), nb, _ptr(y))
     else:
         lib().co_dequantize_q8_0(_ptr(blocks), nb, _ptr(y))
+    return y
+
+
+def dequantize_k(qtype: int, blocks: np.ndarray) -> np.ndarray:
+    """K super-block formats (256 values per block) -> f32."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    nb = blocks.size // K_BLOCK_BYTES[qtype]
+    y = np.empty(nb * 256, dtype=np.float32)
+    lib().co_dequantize_k(qtype, _ptr(blocks), nb, _ptr(y))
+    return y
+
+
+def qmatmul_k(qtype, x, wblocks, n, nthreads=1) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    wblocks = np.ascontiguousarray(wblocks, dtype=np.uint8).reshape(-1)
+    assert wblocks.size == n * (k // 256) * K_BLOCK_BYTES[qtype]
+    y = np.empty((m, n), dtype=np.float32)
+    rc = lib().co_qmatmul_k(qtype, _ptr(x), m, k, k, _ptr(wblocks), n, _ptr(y), n, nthreads)
+    if rc != 0:
+        raise ValueError(f"oracle qmatmul_k rejected its arguments (rc={rc})")
     return y
 
 
