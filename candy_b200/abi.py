@@ -80,6 +80,9 @@ SIGNATURES = {
     "cq_qmatmul_push": [_vp, _vp, _int, _int, _int, _vp, _i64, _i64, _i64, _vp, _i64],
     "cq_qlinear_fused": [_vp, _int, _int, _vp, _vp, _vp, C.c_float, _vp, _i64, _i64, _vp, _i64, _int, _vp, _i64],
     "cq_add_rmsnorm_reduce": [_vp, _vp, _int, _vp, _vp, _i64, _i64, C.c_float, _vp],
+    "cq_decoder_create": [_vp, _vp, C.POINTER(_vp)],
+    "cq_decoder_step": [_vp, _vp, _vp, _vp],
+    "cq_decoder_destroy": [_vp, _vp],
     "cq_flash_attention": [_vp] + [_vp] * 8 + [C.c_uint32] * 18 + [C.c_float] + [C.c_uint32] * 4 + [_int] * 5 + [C.c_float],
     "cq_tp_unique_id": [_vp, _vp],
     "cq_tp_init": [_vp, _int, _int, _vp, _sz, C.POINTER(_vp)],
@@ -97,12 +100,21 @@ SIGNATURES = {
 _OTHER_RESTYPE = {
     "run_mha": (None, [_vp] * 8 + [C.c_uint32] * 18 + [C.c_float] + [C.c_uint32] * 4 + [_int] * 5 + [C.c_float]),
     "cq_run_mha_last_status": (C.c_int32, []),
+    "cq_decoder_logits": (_vp, [_vp]),
     "cq_status_string": (C.c_char_p, [C.c_int32]),
     "cq_last_error": (C.c_char_p, [_vp]),
     "cq_version": (C.c_char_p, []),
     "cq_blocks_bytes": (_sz, [_int, _i64, _i64]),
     "cq_decode_attention_scratch_floats": (_sz, [_i64, _int, _int, _int]),
 }
+
+
+class DecoderDesc(C.Structure):
+    """cq_decoder_desc of include/candyq.h."""
+    _fields_ = [(n, C.c_int) for n in ("n_layers", "dim", "n_heads", "n_kv_heads", "head_dim", "ffn", "ffn_pad", "vocab", "max_ctx")] + \
+               [("eps", C.c_float), ("qtype", C.c_int), ("order", C.c_int)] + \
+               [(n, C.POINTER(C.c_void_p)) for n in ("wqkv", "wo", "wgu", "wdown", "attn_norm", "ffn_norm", "k_cache", "v_cache")] + \
+               [(n, C.c_void_p) for n in ("embed", "wout", "final_norm", "cos_table", "sin_table")]
 
 
 def lib() -> C.CDLL:

@@ -187,11 +187,53 @@ class QuantDecoder:
         return per_layer * self.cfg.n_layers + (self.wout.buf.nbytes if self.cfg.with_head else 0)
 
     def launches_per_step(self) -> int:
+        if getattr(self, "_pdec", None):
+            return 1
         per_layer = 6 if self.fuse else 10  # fused: QKV(+norm), attention x2 (+rotary step), o, gate-up(+norm, +SiLU*mul), down
         return self.cfg.n_layers * per_layer + ((3 if self.fuse else 5) if self.cfg.with_head else 0)
 
+    # ---- the whole step as one persistent kernel (batch 1, one GPU, with embedding and output linear) -------
+    def enable_persistent(self) -> bool:
+        """Switches step() to cq_decoder_step: one cooperative launch per token instead of ~200 small ones.
+        Returns False (and changes nothing) when the library has no persistent kernel for this model's shape."""
+        cfg = self.cfg
+        if self.batch != 1 or self.world != 1 or not cfg.with_head or self.comm is not None:
+            return False
+        n = cfg.n_layers
+
+        def arr(key):
+            return (C.c_void_p * n)(*[(L[key].buf.ptr.value if hasattr(L[key], "buf") else L[key].ptr.value) for L in self.layers])
+
+        self._pd_arrays = {k: arr(k) for k in ("wqkv", "wo", "wgu", "wdown", "attn_norm", "ffn_norm", "k", "v")}
+        d = abi.DecoderDesc()
+        d.n_layers, d.dim, d.n_heads, d.n_kv_heads, d.head_dim = n, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        d.ffn, d.ffn_pad, d.vocab, d.max_ctx, d.eps, d.qtype, d.order = cfg.ffn, self.ffn_pad, cfg.vocab, cfg.max_ctx, cfg.eps, self.qtype, self.order
+        for field, key in (("wqkv", "wqkv"), ("wo", "wo"), ("wgu", "wgu"), ("wdown", "wdown"), ("attn_norm", "attn_norm"), ("ffn_norm", "ffn_norm"),
+                           ("k_cache", "k"), ("v_cache", "v")):
+            setattr(d, field, C.cast(self._pd_arrays[key], C.POINTER(C.c_void_p)))
+        d.embed, d.wout, d.final_norm = self.embed.ptr.value, self.wout.buf.ptr.value, self.final_norm.ptr.value
+        d.cos_table, d.sin_table = self.cos.ptr.value, self.sin.ptr.value
+        handle = C.c_void_p()
+        st = self.lib.cq_decoder_create(self.ctx, C.byref(d), C.byref(handle))
+        if st == abi.CQ_ERR_UNSUPPORTED:
+            return False
+        self._check(st, "decoder create")
+        self._pdec = handle
+        return True
+
+    def _step_persistent(self, advance: bool):
+        if not advance:
+            raise ValueError("the persistent step always advances the position")
+        self._check(self.lib.cq_decoder_step(self.ctx, self._pdec, self.ids.ptr, self.pos.ptr), "decoder step")
+        if not self._capturing:
+            self.guard.advance(1)
+
     # ---- one decode step, enqueued on the context's stream -----------------------------------
     def step(self, advance: bool = True):
+        if getattr(self, "_pdec", None):
+            if not self._capturing:
+                self.guard.need(1)
+            return self._step_persistent(advance)
         lib, ctx, cfg, B = self.lib, self.ctx, self.cfg, self.batch
         hd, dim = cfg.head_dim, cfg.dim
         if not self._capturing:  # a recorded step runs at replay time: replay() accounts for it
@@ -297,7 +339,20 @@ class QuantDecoder:
             self._check(self.lib.cq_graph_launch(self.ctx, g), "graph launch")
 
     def read_logits(self) -> np.ndarray:
+        if getattr(self, "_pdec", None):
+            out = np.empty((1, self.cfg.vocab), dtype=np.float32)
+            src = self.lib.cq_decoder_logits(self._pdec)
+            self._check(self.lib.cq_memcpy_d2h(self.ctx, out.ctypes.data_as(C.c_void_p), src, out.nbytes), "logits")
+            return out
         return self.logits.data().reshape(self.batch, self.cfg.vocab)
+
+    def __del__(self):
+        try:
+            if getattr(self, "_pdec", None):
+                self.lib.cq_decoder_destroy(self.ctx, self._pdec)
+                self._pdec = None
+        except Exception:
+            pass
 
     def read_ids(self) -> np.ndarray:
         return self.ids.data().view(np.uint32).copy()

@@ -295,6 +295,40 @@ cq_status cq_qmatmul_push(cq_ctx *ctx, cq_comm *comm, int set, int qtype, int or
 cq_status cq_add_rmsnorm_reduce(cq_ctx *ctx, cq_comm *comm, int set, float *x_dev, const float *alpha_dev,
                                 int64_t rows, int64_t cols, float eps, float *y_dev);
 
+/* ---- a whole decode step as one persistent kernel (batch 1) --------------------------------------------
+ * Embedding row -> per layer [residual + RMSNorm -> QKV linear -> rotary step, KV-cache write, attention ->
+ * o linear -> residual + RMSNorm -> gate/up linear with SiLU(gate)*up -> down linear] -> final norm -> output
+ * linear -> arg-max, in ONE cooperative launch: every SM keeps one CTA for the whole step, a producer warp
+ * streams the weight rows of all linears through one shared-memory ring without stopping at phase boundaries,
+ * and the phases are separated by bounded grid-wide barriers (a wait that gives up -> CQ_ERR_TIMEOUT at
+ * cq_synchronize; the decoder must then be destroyed).  Numerics of each phase are those of the separate entry
+ * points (cq_qlinear_fused, cq_decode_attention_rope, cq_argmax).  No counterpart in the reference.
+ * The description's pointer arrays are host arrays of n_layers device pointers, read at create time only.
+ *   wqkv[l]  [(n_heads + 2 n_kv_heads) * 128, dim] blocks (q heads, then k heads, then v heads)
+ *   wo[l]    [dim, n_heads * 128]      wgu[l] [2 * ffn, dim], gate and up rows interleaved (g0, u0, g1, u1, ...)
+ *   wdown[l] [dim, ffn_pad], ffn_pad = ffn rounded up to 256 (padding columns multiply zeros)
+ *   k_cache[l], v_cache[l] f32 [max_ctx][n_kv_heads * 128]; cos / sin tables [max_ctx][64]; embed f32 [vocab][dim]
+ * Built for head_dim 128, Q4_0 / Q8_0, dim and n_heads * 128 multiples of 256, batch 1.
+ * cq_decoder_step consumes *ids_dev (the token to feed) at position *pos_dev and leaves the arg-max token in
+ * *ids_dev and the position advanced, so repeated launches (or one captured launch replayed) decode greedily;
+ * cq_decoder_logits is the step's logits row (f32 [vocab], device memory owned by the decoder). */
+typedef struct cq_decoder cq_decoder;
+typedef struct cq_decoder_desc {
+    int n_layers, dim, n_heads, n_kv_heads, head_dim, ffn, ffn_pad, vocab, max_ctx;
+    float eps;
+    int qtype, order;
+    const void *const *wqkv, *const *wo, *const *wgu, *const *wdown;
+    const float *const *attn_norm, *const *ffn_norm;
+    float *const *k_cache, *const *v_cache;
+    const float *embed;
+    const void *wout;
+    const float *final_norm, *cos_table, *sin_table;
+} cq_decoder_desc;
+cq_status cq_decoder_create(cq_ctx *ctx, const cq_decoder_desc *desc, cq_decoder **out);
+cq_status cq_decoder_step(cq_ctx *ctx, cq_decoder *dec, uint32_t *ids_dev, int *pos_dev);
+const float *cq_decoder_logits(const cq_decoder *dec);
+cq_status cq_decoder_destroy(cq_ctx *ctx, cq_decoder *dec);
+
 /* ---- prefill attention: the FlashAttention binding's replacement ------------------------------------
  * O = softmax(Q K^T * softmax_scale) V per (batch, head) on the sm_100a tensor cores (tcgen05, tensor
  * memory, TMA).  Arguments, their order and meaning are those of run_mha in the reference
