@@ -499,6 +499,7 @@ def run_ours(args):
             extra("prefill_gemm", lambda: bw.prefill_gemm(dev, peak, measured_peak_tflops()))
             extra("prefill_attention", lambda: bw.prefill_attention(dev, measured_peak_tflops()))
             extra("decode_7b", lambda: bw.decode_7b(dev, peak))
+            extra("decode_7b_persistent_kernel", lambda: bw.decode_7b(dev, peak, persistent=True))
         tp = None
         if world > 1:
             try:

@@ -12,16 +12,18 @@ import numpy as np
 from .decoder import DecoderConfig, QuantDecoder
 
 
-def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: int = 2, n_layers: int = 32):
+def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: int = 2, n_layers: int = 32, persistent: bool = False):
     """32 layers, d=4096, 32 heads x 128, SwiGLU 11008, vocab 32000, Q4_0, batch 1: processes `prompt`
     uniform-random ids one token at a time (the decode path is the only path measured), then times
-    `decode` greedy tokens as replays of a one-step CUDA graph."""
+    `decode` greedy tokens as replays of a one-step CUDA graph.  persistent: the step is ONE cooperative
+    kernel (cq_decoder_step); otherwise one launch per operator (~195 per token)."""
     cfg = DecoderConfig(n_layers=n_layers, dim=4096, n_heads=32, n_kv_heads=32, head_dim=128, ffn=11008, vocab=32000,
                         max_ctx=prompt + decode)
     t0 = time.perf_counter()
     model = QuantDecoder(dev, cfg, seed=seed)
     build_s = time.perf_counter() - t0
     lib, ctx = dev._lib, dev.ctx
+    is_persistent = bool(persistent) and model.enable_persistent()
     ids = np.random.default_rng(seed).integers(0, cfg.vocab, size=prompt)
     model.set_state(np.array([ids[0]], dtype=np.uint32), 0)
     model.step()  # first launches outside any capture
@@ -47,6 +49,7 @@ def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: 
         "n_layers": n_layers, "weight_bytes_per_token": wbytes, "kv_bytes_per_token_mid": kv_bytes_mid,
         "weight_gbs": round(wbytes * tok_s / 1e9, 1), "frac_of_peak": round(wbytes * tok_s / 1e9 / peak_gbs, 4),
         "roofline_tok_s": round(peak_gbs * 1e9 / wbytes, 1), "launches_per_token": model.launches_per_step(),
+        "path": "one persistent cooperative kernel per token (cq_decoder_step)" if is_persistent else "one launch per operator",
         "build_seconds": round(build_s, 1),
     }
 

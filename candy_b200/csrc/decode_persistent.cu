@@ -39,8 +39,12 @@ constexpr int PS_ATT_CHUNK = 64;         // keys per attention work item
 constexpr int PS_HD = 128;               // head dimension this kernel is built for
 
 enum : int { PS_LINEAR = 0, PS_ATTENTION = 1, PS_FINISH = 2 };
-enum : int { PS_PRO_PLAIN = 0, PS_PRO_ADD_NORM = 1, PS_PRO_ATT_COMBINE = 2, PS_PRO_EMBED_NORM = 3 };
-enum : int { PS_EPI_STORE = 0, PS_EPI_SILU_PAIRS = 1, PS_EPI_STORE_ARGMAX = 2 };
+// prologues: activations straight from global memory | RMSNorm of a residual whose sum of squares the previous
+// linear's epilogue left as per-CTA partials | attention partials combined | the token's embedding row, normed
+enum : int { PS_PRO_PLAIN = 0, PS_PRO_NORM = 1, PS_PRO_ATT_COMBINE = 2, PS_PRO_EMBED_NORM = 3 };
+// epilogues: store | SiLU(gate) * up over row pairs | store + arg-max partial | residual update: x_out = x_in + result,
+// with this CTA's share of sum(x_out^2) for the norm that follows
+enum : int { PS_EPI_STORE = 0, PS_EPI_SILU_PAIRS = 1, PS_EPI_STORE_ARGMAX = 2, PS_EPI_RESID = 3 };
 
 struct PsOp {
     int kind;
@@ -49,8 +53,10 @@ struct PsOp {
     int n, nb, row_bytes;
     int tpr, lanes, wpr, rpp, cwarps;   // consumer geometry: threads per row, lanes of a warp on one row, warps per row, rows per pass and row slot, active warps
     int prologue, epilogue;
-    const float *x, *delta, *alpha;
-    float *x_out, *y;
+    const float *x, *alpha;             // activations (or the residual to norm), norm weights
+    const float *x_in;                  // PS_EPI_RESID: the residual the result is added to
+    float *x_out, *y;                   // new residual (PS_EPI_RESID, PS_PRO_EMBED_NORM) / output vector
+    int ss_slot;                        // which of the two sum-of-squares partial arrays this phase writes (epilogue) or reads (prologue)
     // attention
     float *k_cache, *v_cache;
 };
@@ -64,6 +70,7 @@ struct PsParams {
     const float *embed, *cos_t, *sin_t;
     float *qkv, *part;                  // [(nq + 2 nkv) * 128], [nq][nch_max][130]
     float2 *argmax_part;                // per CTA (value, index bits)
+    float *ss_part;                     // [2][CTAs] partial sums of squares of a residual
     uint32_t *ids;                      // in: the token to feed; out: the arg-max token
     int *pos;                           // in: its position; out: + 1
     unsigned long long *bar_count;
@@ -167,7 +174,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_kernel(const PsPara
     const unsigned long long base = (unsigned long long)(*p.gen) * (unsigned long long)p.nops * (unsigned long long)G;
     bool dead = false;     // a bounded wait gave up: no more waiting, run to the end
     unsigned it = 0;       // passes consumed so far (mirrors the producer's counter)
-    float my_best = -INFINITY;
+    float my_best = -INFINITY, my_ss = 0.0f;
     uint32_t my_best_idx = 0xFFFFFFFFu;
 
     // all CTAs have finished phases 0 .. oi-1 (their global writes are visible after this)
@@ -190,10 +197,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_kernel(const PsPara
     // this CTA has finished the current phase
     auto grid_arrive = [&]() {
         consumer_sync();
-        if (ctid == 0) {
-            __threadfence();
-            atomicAdd(p.bar_count, 1ULL);
-        }
+        if (ctid == 0) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.bar_count) : "memory");
     };
 
     const int pos_raw = *p.pos;
@@ -317,18 +321,14 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_kernel(const PsPara
         const int npass = (nrows + rows_per_pass - 1) / rows_per_pass;
         const int k4 = op.nb * 8;  // float4 groups in an activation row
         const float *xsrc = op.x;
-        if (op.prologue == PS_PRO_ADD_NORM || op.prologue == PS_PRO_EMBED_NORM) {
-            // x' = x + delta (or the embedding row of the current token); CTA 0 stores it as the new residual;
-            // x'' = x' / sqrt(mean(x'^2) + eps) * alpha in shared memory.  Every CTA computes the same numbers in the same order.
-            const float *src = op.prologue == PS_PRO_EMBED_NORM ? p.embed + (int64_t)min(p.ids[0], (uint32_t)(p.vocab - 1)) * p.dim : op.x;
+        if (op.prologue == PS_PRO_EMBED_NORM) {
+            // x = the embedding row of the current token (CTA 0 stores it as the residual);
+            // x' = x / sqrt(mean(x^2) + eps) * alpha in shared memory.  Every CTA computes the same numbers in the same order.
+            const float *src = p.embed + (int64_t)min(p.ids[0], (uint32_t)(p.vocab - 1)) * p.dim;
             float ss = 0.0f;
             for (int i = ctid; i < k4; i += PS_CTHREADS) {
-                float4 v = reinterpret_cast<const float4 *>(src)[i];
-                if (op.delta) {
-                    const float4 d = reinterpret_cast<const float4 *>(op.delta)[i];
-                    v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
-                }
-                if (op.x_out && cta == 0) reinterpret_cast<float4 *>(op.x_out)[i] = v;
+                const float4 v = reinterpret_cast<const float4 *>(src)[i];
+                if (cta == 0) reinterpret_cast<float4 *>(op.x_out)[i] = v;
                 reinterpret_cast<float4 *>(xs)[i] = v;
                 ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
             }
@@ -348,20 +348,73 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_kernel(const PsPara
             }
             consumer_sync();
             xsrc = xs;
+        } else if (op.prologue == PS_PRO_NORM) {
+            // RMSNorm of the residual the previous linear's epilogue wrote (row by row, across the CTAs) together with each
+            // CTA's share of its sum of squares: everything this needs is issued as one batch of loads -- the residual, the
+            // norm weights and the partial sums -- so the prologue costs one round trip to L2.
+            constexpr int kMaxV = 6;  // float4 groups per thread: k <= 6 * 480 * 4 = 11520 activations
+            float4 v[kMaxV], a[kMaxV];
+#pragma unroll
+            for (int u = 0; u < kMaxV; ++u) {
+                const int i = ctid + u * PS_CTHREADS;
+                if (i < k4) {
+                    v[u] = reinterpret_cast<const float4 *>(op.x)[i];
+                    a[u] = __ldg(reinterpret_cast<const float4 *>(op.alpha) + i);
+                }
+            }
+            // the CTAs' partial sums in CTA order (the same order, hence the same bits, in every warp of every CTA)
+            const float *sp = p.ss_part + (size_t)op.ss_slot * G;
+            float part = 0.0f;
+            for (int c = lane; c < G; c += 32) part += sp[c];
+            float tot = 0.0f;
+            for (int l2 = 0; l2 < 32; ++l2) tot += __shfl_sync(0xffffffffu, part, l2, 32);
+            const float scale = 1.0f / sqrtf(tot / (float)(op.nb * kQK) + p.eps);
+#pragma unroll
+            for (int u = 0; u < kMaxV; ++u) {
+                const int i = ctid + u * PS_CTHREADS;
+                if (i < k4)
+                    reinterpret_cast<float4 *>(xs)[i] = make_float4(scale * v[u].x * a[u].x, scale * v[u].y * a[u].y, scale * v[u].z * a[u].z, scale * v[u].w * a[u].w);
+            }
+            consumer_sync();
+            xsrc = xs;
         } else if (op.prologue == PS_PRO_ATT_COMBINE) {
-            // attention output = chunks' partial sums rescaled to a common maximum (every CTA combines all heads)
+            // attention output = the chunks' partial sums rescaled to a common maximum; every CTA combines all heads.
+            // Weights first (one thread per (head, chunk) pair, then one per head), then the sums with their loads batched.
+            float *wgt = reinterpret_cast<float *>(area);  // [2][nq][nch_max]: the activation-state area is free until the set-up below
+            float *lsm = wgt + p.nq * p.nch_max;
+            for (int i = ctid; i < p.nq * p.nch_max; i += PS_CTHREADS) {
+                const int c = i % p.nch_max;
+                const float2 ml = c < nch ? *reinterpret_cast<const float2 *>(p.part + (int64_t)i * (PS_HD + 2)) : make_float2(-INFINITY, 0.0f);
+                wgt[i] = ml.x;  // chunk maximum
+                lsm[i] = ml.y;  // chunk sum
+            }
+            consumer_sync();
+            for (int head = ctid; head < p.nq; head += PS_CTHREADS) {
+                float M = -INFINITY;
+                for (int c = 0; c < nch; ++c) M = fmaxf(M, wgt[head * p.nch_max + c]);
+                float den = 0.0f;
+                for (int c = 0; c < nch; ++c) {
+                    const float e = expf(wgt[head * p.nch_max + c] - M);
+                    den = fmaf(e, lsm[head * p.nch_max + c], den);
+                    wgt[head * p.nch_max + c] = e;
+                }
+                const float inv = 1.0f / den;
+                for (int c = 0; c < nch; ++c) wgt[head * p.nch_max + c] *= inv;
+            }
+            consumer_sync();
             for (int idx = ctid; idx < p.nq * PS_HD; idx += PS_CTHREADS) {
                 const int head = idx >> 7, d = idx & (PS_HD - 1);
-                const float *pp = p.part + (int64_t)head * p.nch_max * (PS_HD + 2);
-                float M = -INFINITY;
-                for (int c = 0; c < nch; ++c) M = fmaxf(M, pp[c * (PS_HD + 2)]);
-                float num = 0.0f, den = 0.0f;
-                for (int c = 0; c < nch; ++c) {
-                    const float wgt = expf(pp[c * (PS_HD + 2)] - M);
-                    num = fmaf(wgt, pp[c * (PS_HD + 2) + 2 + d], num);
-                    den = fmaf(wgt, pp[c * (PS_HD + 2) + 1], den);
+                const float *pp = p.part + (int64_t)head * p.nch_max * (PS_HD + 2) + 2 + d;
+                const float *wh = wgt + head * p.nch_max;
+                float num = 0.0f;
+                for (int c0 = 0; c0 < nch; c0 += 8) {
+                    float t[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) t[j] = c0 + j < nch ? pp[(c0 + j) * (PS_HD + 2)] : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) num = fmaf(c0 + j < nch ? wh[c0 + j] : 0.0f, t[j], num);
                 }
-                xs[idx] = num * (1.0f / den);
+                xs[idx] = num;
             }
             consumer_sync();
             xsrc = xs;
@@ -479,6 +532,10 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_kernel(const PsPara
                             for (int w = 0; w < op.wpr; ++w) up += red[buf][i][(rs + 1) * op.wpr + w];
                             op.y[(row_begin + r) >> 1] = tot / (1.0f + expf(-tot)) * up;
                         }
+                    } else if (op.epilogue == PS_EPI_RESID) {
+                        const float xv = op.x_in[row_begin + r] + tot;
+                        op.x_out[row_begin + r] = xv;
+                        my_ss = fmaf(xv, xv, my_ss);
                     } else {
                         op.y[row_begin + r] = tot;
                         if (op.epilogue == PS_EPI_STORE_ARGMAX) {
@@ -489,6 +546,20 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_kernel(const PsPara
                 }
             }
             buf ^= 1;
+        }
+        if (op.epilogue == PS_EPI_RESID) {
+            // this CTA's share of sum(x_out^2), summed in a fixed order -> global, for the norm of the next phase
+            float t = my_ss;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o, 32);
+            if (lane == 0) best_val[cw] = t;
+            consumer_sync();
+            if (ctid == 0) {
+                float tot = 0.0f;
+                for (int w = 0; w < PS_CWARPS; ++w) tot += best_val[w];
+                p.ss_part[(size_t)op.ss_slot * G + cta] = tot;
+            }
+            my_ss = 0.0f;
         }
         if (op.epilogue == PS_EPI_STORE_ARGMAX) {
             // this CTA's best (value, lowest index) -> global
@@ -527,6 +598,7 @@ struct cq_decoder {
     PsOp *ops_dev = nullptr;
     float *qkv = nullptr, *part = nullptr, *xa = nullptr, *xb = nullptr, *o = nullptr, *h = nullptr, *dd = nullptr, *logits = nullptr;
     float2 *argmax_part = nullptr;
+    float *ss_part = nullptr;
     unsigned long long *bar_count = nullptr;
     unsigned *gen = nullptr;
     PsParams params;
@@ -627,41 +699,49 @@ cq_status cq_decoder_create(cq_ctx *ctx, const cq_decoder_desc *desc, cq_decoder
         (s = ps_alloc(ctx, dec, &dec->xa, (size_t)d.dim, true)) != CQ_OK || (s = ps_alloc(ctx, dec, &dec->xb, (size_t)d.dim, true)) != CQ_OK ||
         (s = ps_alloc(ctx, dec, &dec->o, (size_t)d.dim, true)) != CQ_OK || (s = ps_alloc(ctx, dec, &dec->h, (size_t)d.ffn_pad, true)) != CQ_OK ||
         (s = ps_alloc(ctx, dec, &dec->dd, (size_t)d.dim, true)) != CQ_OK || (s = ps_alloc(ctx, dec, &dec->logits, (size_t)d.vocab, true)) != CQ_OK ||
-        (s = ps_alloc(ctx, dec, &dec->argmax_part, (size_t)ctx->sm_count, true)) != CQ_OK || (s = ps_alloc(ctx, dec, &dec->bar_count, (size_t)1, true)) != CQ_OK ||
+        (s = ps_alloc(ctx, dec, &dec->argmax_part, (size_t)ctx->sm_count, true)) != CQ_OK ||
+        (s = ps_alloc(ctx, dec, &dec->ss_part, (size_t)2 * ctx->sm_count, true)) != CQ_OK || (s = ps_alloc(ctx, dec, &dec->bar_count, (size_t)1, true)) != CQ_OK ||
         (s = ps_alloc(ctx, dec, &dec->gen, (size_t)1, true)) != CQ_OK)
         return fail(s);
     // ---- the step as a list of phases ---------------------------------------------------------------------------
     bool ok = true;
     int max_stage = 0, max_nb = 0;
-    auto linear = [&](const void *w, int n, int k, int prologue, int epilogue, const float *x, const float *delta, const float *alpha, float *x_out, float *y) {
+    auto linear = [&](const void *w, int n, int k, int prologue, int epilogue, const float *x, const float *alpha, const float *x_in, float *x_out, float *y,
+                      int ss_slot) {
         PsOp op = {};
         op.kind = PS_LINEAR;
         op.w = static_cast<const uint8_t *>(w);
         ok = ok && w && ps_plan_linear(op, n, k, bb, epilogue == PS_EPI_SILU_PAIRS) && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
         if (epilogue == PS_EPI_SILU_PAIRS) ok = ok && (op.rpp % 2 == 0) && (n % 2 == 0);
-        op.prologue = prologue, op.epilogue = epilogue, op.x = x, op.delta = delta, op.alpha = alpha, op.x_out = x_out, op.y = y;
+        if (prologue == PS_PRO_NORM) ok = ok && k <= 6 * PS_CTHREADS * 4;
+        op.prologue = prologue, op.epilogue = epilogue, op.x = x, op.alpha = alpha, op.x_in = x_in, op.x_out = x_out, op.y = y, op.ss_slot = ss_slot;
         if (ok) {
             max_stage = std::max(max_stage, 2 * op.rpp * op.row_bytes);
             max_nb = std::max(max_nb, op.nb);
         }
         dec->ops.push_back(op);
     };
+    // The residual stream alternates between two buffers: a linear whose output is added to the stream reads one and
+    // writes the other, row by row, in its epilogue; the norm of the next phase reads the new one.
     float *cur = dec->xa, *other = dec->xb;
+    int slot = 0;
     for (int l = 0; l < d.n_layers; ++l) {
-        if (l == 0) linear(d.wqkv[l], qkv_rows, d.dim, PS_PRO_EMBED_NORM, PS_EPI_STORE, nullptr, nullptr, d.attn_norm[l], other, dec->qkv);
-        else linear(d.wqkv[l], qkv_rows, d.dim, PS_PRO_ADD_NORM, PS_EPI_STORE, cur, dec->dd, d.attn_norm[l], other, dec->qkv);
-        std::swap(cur, other);
+        if (l == 0) linear(d.wqkv[l], qkv_rows, d.dim, PS_PRO_EMBED_NORM, PS_EPI_STORE, nullptr, d.attn_norm[l], nullptr, cur, dec->qkv, 0);
+        else linear(d.wqkv[l], qkv_rows, d.dim, PS_PRO_NORM, PS_EPI_STORE, cur, d.attn_norm[l], nullptr, nullptr, dec->qkv, slot ^ 1);
         PsOp att = {};
         att.kind = PS_ATTENTION;
         att.k_cache = d.k_cache[l], att.v_cache = d.v_cache[l];
         ok = ok && att.k_cache && att.v_cache;
         dec->ops.push_back(att);
-        linear(d.wo[l], d.dim, att_dim, PS_PRO_ATT_COMBINE, PS_EPI_STORE, nullptr, nullptr, nullptr, nullptr, dec->o);
-        linear(d.wgu[l], 2 * d.ffn, d.dim, PS_PRO_ADD_NORM, PS_EPI_SILU_PAIRS, cur, dec->o, d.ffn_norm[l], other, dec->h);
+        linear(d.wo[l], d.dim, att_dim, PS_PRO_ATT_COMBINE, PS_EPI_RESID, nullptr, nullptr, cur, other, nullptr, slot);
         std::swap(cur, other);
-        linear(d.wdown[l], d.dim, d.ffn_pad, PS_PRO_PLAIN, PS_EPI_STORE, dec->h, nullptr, nullptr, nullptr, dec->dd);
+        linear(d.wgu[l], 2 * d.ffn, d.dim, PS_PRO_NORM, PS_EPI_SILU_PAIRS, cur, d.ffn_norm[l], nullptr, nullptr, dec->h, slot);
+        slot ^= 1;
+        linear(d.wdown[l], d.dim, d.ffn_pad, PS_PRO_PLAIN, PS_EPI_RESID, dec->h, nullptr, cur, other, nullptr, slot);
+        std::swap(cur, other);
+        slot ^= 1;
     }
-    linear(d.wout, d.vocab, d.dim, PS_PRO_ADD_NORM, PS_EPI_STORE_ARGMAX, cur, dec->dd, d.final_norm, nullptr, dec->logits);
+    linear(d.wout, d.vocab, d.dim, PS_PRO_NORM, PS_EPI_STORE_ARGMAX, cur, d.final_norm, nullptr, nullptr, dec->logits, slot ^ 1);
     PsOp fin = {};
     fin.kind = PS_FINISH;
     dec->ops.push_back(fin);
@@ -671,7 +751,8 @@ cq_status cq_decoder_create(cq_ctx *ctx, const cq_decoder_desc *desc, cq_decoder
     }
     // ---- shared memory: ring, partial sums, activation state, prologue activations --------------------------------
     const size_t stash_bytes = (size_t)8 * PS_CTHREADS * sizeof(float);
-    const size_t coop_bytes = (size_t)max_nb * DecQ16<CQ_Q4_0, 0>::kStateWordsPerBlock * sizeof(uint32_t);
+    size_t coop_bytes = (size_t)max_nb * DecQ16<CQ_Q4_0, 0>::kStateWordsPerBlock * sizeof(uint32_t);
+    coop_bytes = std::max(coop_bytes, (size_t)2 * d.n_heads * nch_max * sizeof(float));  // the attention combine's weights live there too
     const size_t xs_bytes = (size_t)std::max(d.dim, att_dim) * sizeof(float);
     const size_t cap = ctx->smem_optin - 8192;  // static shared memory of the kernel, rounded up
     const size_t stage_bytes = ((size_t)max_stage + 127) & ~size_t(127);
@@ -695,7 +776,7 @@ cq_status cq_decoder_create(cq_ctx *ctx, const cq_decoder_desc *desc, cq_decoder
     p.dim = d.dim, p.nq = d.n_heads, p.nkv = d.n_kv_heads, p.max_ctx = d.max_ctx, p.nch_max = nch_max, p.vocab = d.vocab;
     p.eps = d.eps, p.att_scale = 1.0f / sqrtf((float)d.head_dim);
     p.embed = d.embed, p.cos_t = d.cos_table, p.sin_t = d.sin_table;
-    p.qkv = dec->qkv, p.part = dec->part, p.argmax_part = dec->argmax_part;
+    p.qkv = dec->qkv, p.part = dec->part, p.argmax_part = dec->argmax_part, p.ss_part = dec->ss_part;
     p.bar_count = dec->bar_count, p.gen = dec->gen;
     p.err = ctx->dev_err_devptr;
     *out = dec;
