@@ -629,8 +629,26 @@ def run_kernel_only(args):
     print(json.dumps({"kernel_only": [n, k], "launches": args.launches, "ring_copies": len(wl.rings[0])}))
 
 
+def run_attn_only(args):
+    """A few plain launches of the prefill attention (f16, causal, head dimension 128) on one shape: the case ncu captures."""
+    from candy_b200.backend import CudaDevice, RawBuffer
+    b, h, hk, s = (int(v) for v in args.attn_only.lower().split("x"))
+    d = 128
+    dev = CudaDevice(int(os.environ.get("LOCAL_RANK", "0")))
+    lib, ctx = dev._lib, dev.ctx
+    q, k, v, o = (RawBuffer(dev, 2 * b * s * hh * d) for hh in (h, hk, hk, h))
+    for buf, byte in ((q, 0x3C), (k, 0x2C), (v, 0x34)):
+        lib.cq_memset(ctx, buf.ptr, byte, buf.nbytes)
+    a = [q.ptr, k.ptr, v.ptr, o.ptr, None, None, None, None, s * h * d, s * hk * d, s * hk * d, s * h * d, 0, h * d, hk * d, hk * d, h * d, d, d, d, d,
+         b, h, hk, d, d, float(1.0 / np.sqrt(d)), s, s, s, s, 0, 1, 0, -1, -1, 0.0]
+    for _ in range(args.launches):
+        dev._check(lib.cq_flash_attention(ctx, *a), "flash attention")
+    dev.synchronize()
+    print(json.dumps({"attn_only": [b, h, hk, s], "launches": args.launches}))
+
+
 def run_gemm_only(args):
-    """A few plain launches of the prefill GEMM (CQ_ACT_F16) on one shape: the case ncu captures."""
+    """A few plain launches of the prefill GEMM on one shape (--actmode 2: f16 operands, 1: Q8_1 / int8, 0: f32 mode): the case ncu captures."""
     from candy_b200.backend import CudaDevice, QStorage
     m, n, k = (int(v) for v in args.gemm_only.lower().split("x"))
     dev = CudaDevice(int(os.environ.get("LOCAL_RANK", "0")))
@@ -639,9 +657,9 @@ def run_gemm_only(args):
     x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
     y = dev.alloc(m * n)
     for _ in range(args.launches):
-        dev._check(dev._lib.cq_qmatmul(dev.ctx, Q4_0, ORDER, 2, x.ptr, m, k, k, q.buf.ptr, n, y.ptr, n), "qmatmul")
+        dev._check(dev._lib.cq_qmatmul(dev.ctx, Q4_0, ORDER, args.gemm_actmode, x.ptr, m, k, k, q.buf.ptr, n, y.ptr, n), "qmatmul")
     dev.synchronize()
-    print(json.dumps({"gemm_only": [m, n, k], "launches": args.launches}))
+    print(json.dumps({"gemm_only": [m, n, k], "actmode": args.gemm_actmode, "launches": args.launches}))
 
 
 def run_decode_only(args):
@@ -690,6 +708,8 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="skip the 7B decode and 70B tensor-parallel layer workloads")
     ap.add_argument("--kernel-only", default=None, metavar="NxK", help="profiling aid: launch one GEMV shape a few times")
     ap.add_argument("--gemm-only", default=None, metavar="MxNxK", help="profiling aid: launch the prefill GEMM a few times")
+    ap.add_argument("--gemm-actmode", type=int, default=2, help="gemm-only mode: 2 f16 operands, 1 Q8_1 activations (int8 tensor cores), 0 f32 mode")
+    ap.add_argument("--attn-only", default=None, metavar="BxHxHKxS", help="profiling aid: launch the prefill attention a few times")
     ap.add_argument("--decode-only", type=int, default=0, metavar="LAYERS", help="profiling aid: a few plain decode steps of a shallow 7B-width model")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--qtype", type=int, default=2, help="kernel-only mode: block format id (2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0)")
@@ -701,6 +721,9 @@ def main():
         return
     if args.gemm_only:
         run_gemm_only(args)
+        return
+    if args.attn_only:
+        run_attn_only(args)
         return
     if args.decode_only:
         run_decode_only(args)
