@@ -26,6 +26,10 @@ struct GemvTuning {
     int target_warps = 8;   // consumer warps per CTA the launcher aims for
     int stages = 4;         // smem ring depth (clamped by capacity)
     int ctas_per_sm = 0;    // 0 = automatic
+    // 1: the producer fills the ring before the CTA's first barrier.  Measured slower: the burst of a new CTA's
+    // ring fill delays the last loads of the previous kernel's CTAs still running (sweep of four shapes 40.3 us
+    // against 37.7), although the same shape back to back gains 0.1-0.2 us per launch.
+    int early = 0;
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;

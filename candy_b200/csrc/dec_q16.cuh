@@ -32,7 +32,9 @@ struct DecQ16 {
     static constexpr int kVecs = (QT == CQ_Q4_0) ? 2 : 1;
     static constexpr bool kCoop = true;
     static constexpr bool kSplitStage = true;
-    static constexpr int kStateWordsPerBlock = 20;  // 8 hi words, 8 lo words, scale, bias, 2 pad (16-byte multiple)
+    // 8 hi words, 8 lo words, scale, bias.  A thread's two blocks are 36 words: 16-byte aligned, and at this
+    // stride the eight lanes of a 128-bit shared-memory load phase fall on disjoint banks (40 words collide two ways).
+    static constexpr int kStateWordsPerBlock = 18;
     int qh[2][kBlkWords][kVecs];  // high bytes (signed), lane order matching the weight bytes
     int ql[2][kBlkWords][kVecs];  // low bytes (unsigned)
     float d16[2];                 // amax / 32767 per block

@@ -83,6 +83,7 @@ struct GemvParams {
     int64_t ldy;
     const float *bias;   // added to every output row in the epilogue (nn.Linear's bias), or null
     int *err;
+    int early;           // 1: the producer fills the ring before the CTA's first barrier
 };
 
 // ---- compile-time description of where each value of a thread's two blocks sits --------
@@ -652,8 +653,17 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     // Rows of this CTA: an even split of [0, n).
     // (with the pairing epilogue the split falls on even rows)
     const int64_t unit = p.epilogue == 1 ? 2 : 1;
-    const int64_t row_begin = unit * (((p.n / unit) * (int64_t)blockIdx.x) / gridDim.x);
-    const int64_t row_end = unit * (((p.n / unit) * (int64_t)(blockIdx.x + 1)) / gridDim.x);
+    int64_t row_begin, row_end;
+    {
+        const int64_t units = p.n / unit;
+        if (units * (int64_t)gridDim.x < (int64_t)1 << 32) {  // the usual case: 32-bit divisions (a 64-bit one is a long subroutine on the way to the first copy)
+            row_begin = unit * (int64_t)(((uint32_t)units * blockIdx.x) / gridDim.x);
+            row_end = unit * (int64_t)(((uint32_t)units * (blockIdx.x + 1)) / gridDim.x);
+        } else {
+            row_begin = unit * ((units * (int64_t)blockIdx.x) / gridDim.x);
+            row_end = unit * ((units * (int64_t)(blockIdx.x + 1)) / gridDim.x);
+        }
+    }
     const int nrows = (int)(row_end - row_begin);
     const int rows_per_pass = p.rpp * RPT;
     const int npass = (nrows + rows_per_pass - 1) / rows_per_pass;
@@ -661,40 +671,49 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     // Let the next kernel in the stream become resident as soon as every CTA of this one is:
     // its producer warp may prefetch weights, everything else there waits for this grid.
     pdl_launch_dependents();
-    if (tid == 0) {
+
+    // Weights are read exactly once: mark them evict-first so that the stream does not push
+    // the activations (re-read by every CTA) and the outputs out of L2.
+    uint64_t policy = 0;
+    int issued = 0;
+    auto issue_pass = [&](int ps) {
+        const int s = ps % p.stages;
+        const int r0 = ps * rows_per_pass;
+        const int rows = min(rows_per_pass, nrows - r0);
+        const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
+        mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
+        bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
+                      smem_u32(&bar_full[s]), policy);
+        issued = ps + 1;
+    };
+    // The producer lane initialises the barriers (and, with the `early` option, fills the ring before the CTA
+    // meets).  Weights do not depend on the previous kernel in the stream, so under programmatic dependent
+    // launch the ring fills while that kernel is still draining.
+    if (is_producer && lane == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), p.cwarps);
         }
         fence_mbar_init();
         fence_proxy_async();
+        policy = make_l2_policy_evict_first();
+        if (p.early) {
+            const int first = min(npass, p.stages);
+            for (int ps = 0; ps < first; ++ps) issue_pass(ps);
+        }
     }
     __syncthreads();
 
     if (is_producer) {
         // ---- producer warp: one lane streams this CTA's rows into the ring ---------------
-        // Weights do not depend on the previous kernel in the stream, so under programmatic
-        // dependent launch the ring starts filling while that kernel is still draining.
         if (lane == 0) {
-            // Weights are read exactly once: mark them evict-first so that the stream does not push
-            // the activations (re-read by every CTA) and the outputs out of L2.
-            const uint64_t policy = make_l2_policy_evict_first();
-            int issued = 0;
-            for (int ps = 0; ps < npass; ++ps) {
+            for (int ps = issued; ps < npass; ++ps) {
                 const int s = ps % p.stages;
-                if (ps >= p.stages) {
-                    if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
-                        atomicExch(p.err, kDevErrEmptyWait);
-                        break;
-                    }
+                if (ps >= p.stages && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
+                    atomicExch(p.err, kDevErrEmptyWait);
+                    break;
                 }
-                const int r0 = ps * rows_per_pass;
-                const int rows = min(rows_per_pass, nrows - r0);
-                const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
-                mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
-                bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes), p.w + (row_begin + r0) * (int64_t)p.row_bytes, bytes,
-                              smem_u32(&bar_full[s]), policy);
-                issued = ps + 1;
+                issue_pass(ps);
             }
             // Do not leave while copies into this CTA's shared memory may still be in flight:
             // wait (bounded) for the last use of every stage that was issued.
@@ -960,8 +979,14 @@ __global__ void __launch_bounds__(384, 1) gemv_stream_mr_kernel(const GemvParams
     float *stash = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);  // [8][cthreads] partial sums
     const bool is_producer = warp == p.cwarps;
 
-    const int64_t row_begin = (p.n * (int64_t)blockIdx.x) / gridDim.x;
-    const int64_t row_end = (p.n * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+    int64_t row_begin, row_end;
+    if (p.n * (int64_t)gridDim.x < (int64_t)1 << 32) {  // 32-bit divisions where they are exact (see gemv_stream_kernel)
+        row_begin = (int64_t)(((uint32_t)p.n * blockIdx.x) / gridDim.x);
+        row_end = (int64_t)(((uint32_t)p.n * (blockIdx.x + 1)) / gridDim.x);
+    } else {
+        row_begin = (p.n * (int64_t)blockIdx.x) / gridDim.x;
+        row_end = (p.n * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+    }
     const int nrows = (int)(row_end - row_begin);
     const int npass = (nrows + p.rpp - 1) / p.rpp;
 
@@ -1313,6 +1338,7 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     int stages = ctx->tune.stages < 2 ? 2 : (ctx->tune.stages > kMaxStages ? kMaxStages : ctx->tune.stages);
     if ((size_t)stage_bytes * 2 > budget) return false;
     while ((size_t)stage_bytes * stages > budget) --stages;
+    p.early = ctx->tune.early;
     p.n = n;
     p.nb = (int)nb;
     p.row_bytes = (int)row_bytes;
