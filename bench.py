@@ -523,9 +523,10 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one launch of the dominant kernel (n=32000, k=4096) from the ncu
-# capture summarised in profiles/gemv_q4_0_32000x4096.md: 73.80 MB read + 1.10 MB written.
-NCU_TRAFFIC_BYTES = 73804544 + 1099008
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel
+# (n=32000, k=4096) from an `ncu --set full -k regex:gemv_stream_kernel` capture of
+# `bench.py --kernel-only 32000x4096`: 73.81 MB read + 0.85 MB written.
+NCU_TRAFFIC_BYTES = 73805824 + 853248
 
 
 def run_reference(args):
