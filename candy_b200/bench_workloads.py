@@ -126,6 +126,57 @@ def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512
             "l2_defeat": "ring of 8 weight copies", "cases": out}
 
 
+def small_batch(dev, peak_gbs: float, ms_rows=(1, 2, 4, 8), n: int = 11008, k: int = 4096, seed: int = 3, calls: int = 40):
+    """Decode-side batches (m = 1 .. 8 activation rows against one Q4_0 weight, n = 11008, k = 4096) in the two
+    decode numerics, CQ_ACT_F32 and CQ_ACT_Q8_1: the whole cq_qmatmul call, timed as replays of a CUDA graph of
+    `calls` calls that cycle through eight copies of the weight.  One pass over the weights serves every row:
+    m = 1 the streaming GEMV, m = 2 its two-row form, m >= 3 the int8 tensor-core kernel (plane or Q8_1 columns)."""
+    from .backend import QStorage
+    lib, ctx = dev._lib, dev.ctx
+    rng = np.random.default_rng(seed)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    first = QStorage.quantize(dev, 2, 0, w)
+    ring = [first] + [RawCopy(dev, first) for _ in range(7)]
+    out = []
+    for act, actname in ((0, "f32"), (1, "q8_1")):
+        for m in ms_rows:
+            x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
+            y = dev.alloc(m * n)
+            cursor = [0]
+
+            def call():
+                q = ring[cursor[0] % len(ring)]
+                cursor[0] += 1
+                dev._check(lib.cq_qmatmul(ctx, 2, 0, act, x.ptr, m, k, k, q.ptr if isinstance(q, RawCopy) else q.buf.ptr, n, y.ptr, n), "qmatmul")
+
+            call()
+            dev.synchronize()
+            lib.cq_capture_begin(ctx)
+            for _ in range(calls):
+                call()
+            g = C.c_void_p()
+            dev._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
+            for _ in range(2):
+                dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+            dev.synchronize()
+            ms = C.c_float()
+            reps = 10
+            lib.cq_timer_start(ctx)
+            for _ in range(reps):
+                dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+            lib.cq_timer_stop(ctx, C.byref(ms))
+            dev.synchronize()
+            lib.cq_graph_destroy(ctx, g)
+            t = ms.value * 1e-3 / (reps * calls)
+            nbytes = n * (k // 32) * 18 + 4 * m * k + 4 * m * n
+            out.append({"actmode": actname, "m": m, "us": round(t * 1e6, 2), "algorithmic_gbs": round(nbytes / t / 1e9, 1),
+                        "frac_of_hbm_peak": round(nbytes / t / 1e9 / peak_gbs, 4),
+                        "path": "streaming GEMV" if m == 1 else ("two-row streaming GEMV" if m == 2 else "int8 tcgen05 kernel")})
+            del x, y
+    del ring, first
+    return {"n": n, "k": k, "qtype": "q4_0", "peak_gbs": peak_gbs, "l2_defeat": "ring of 8 weight copies", "cases": out}
+
+
 def prefill_attention(dev, peak_tflops: float, cases=((1, 32, 32, 128), (1, 32, 32, 2048), (2, 64, 8, 4096)), d: int = 128, reps: int = 10):
     """The prompt-phase attention (cq_flash_attention, causal, f16, head dimension 128) at the 7B prompt of BASELINE
     config 4 (128 tokens, 32 heads) and at two longer contexts (7B heads at 2048 tokens, the 70B shape's 64 / 8 grouped

@@ -339,6 +339,312 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+
+// ---- wide batches without an f16 copy of W (Q4_0) --------------------------------------------------
+// The persistent 128 x 256 kernel above with its B operand made in place: a TMA lane streams the RAW
+// blocks of the tile's 256 weight rows (144 bytes per row and 256 values of k) into a two-stage ring,
+// sixteen dequantize warps (two threads per weight row) turn each row's nibbles into f16 with exact arithmetic --
+// (1024 + n) assembled by one LOP3, minus 1032 (or times 1/16 minus 72 for the nibble four bits up)
+// gives n - 8 exactly, then one f16 multiply by the block's scale, the single rounding the f16 copy also
+// had -- and store them as the K-major, 128-byte-swizzled tile the MMA reads (the layout a TMA load with
+// CU_TENSOR_MAP_SWIZZLE_128B would have written).  A 32-bit word of nibbles yields the pairs
+// (n0,n4) (n1,n5) (n2,n6) (n3,n7): the values of k inside each group of eight are therefore stored
+// in that order, and the activation pre-pass writes X in the same order (a contraction does not care
+// how k is numbered as long as both operands agree).  W crosses HBM once (the CTAs that share a weight
+// tile run side by side); each CTA dequantizes the tile again for its own 128 activation rows, under
+// the MMAs of the previous stage.
+constexpr int FD_STAGES = 3;                       // MMA stages: A 16 KB + B 32 KB each
+constexpr int FD_RAW_STAGES = 2;
+constexpr int FD_RAW_ROW = 8 * kQ4Bytes;           // 144 bytes: one row's blocks for 256 values of k
+constexpr int FD_RAW_BYTES = 256 * FD_RAW_ROW;     // 36 KB
+constexpr int FD_B_BYTES = 256 * BK * 2;           // 32 KB
+constexpr int FD_DQ_WARPS = 16;                    // dequantize warps: thread = (weight row, one of its two blocks per 64 values of k)
+constexpr int FD_THREADS = (7 + FD_DQ_WARPS) * 32;  // warp 0 TMA(A), 1 MMA, 2-5 epilogue, 6 TMA(raw W), 7.. dequantize
+constexpr size_t FD_SMEM = (size_t)FD_STAGES * (A_BYTES + FD_B_BYTES) + (size_t)FD_RAW_STAGES * FD_RAW_BYTES + 1024 + 256;
+
+// Where value `slot` (0..7) of 16-byte chunk `cw` (0..3) of a 32-block sits in the block (see above).
+template <int ORDER>
+__host__ __device__ constexpr int fd_elem(int cw, int slot) {
+    // slots hold the nibbles (n0, n4, n1, n5, n2, n6, n3, n7) of word cw
+    const int nib = (slot & 1) * 4 + (slot >> 1);
+    const int byte = 4 * cw + (nib >> 1), hi = nib & 1;
+    return ORDER == CQ_ORDER_GO_INTERLEAVED ? 2 * byte + hi : byte + 16 * hi;
+}
+
+template <int ORDER>
+__global__ void __launch_bounds__(256) x_to_f16_perm_kernel(const float *__restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                                                          __half *__restrict__ out) {
+    const int64_t total = m * (k / 8);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / (k / 8), c8 = i - row * (k / 8);
+        const float *src = x + row * ldx + (c8 >> 2) * 32;
+        const int cw = (int)(c8 & 3);
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // selected at run time by cw only: the four candidates per slot are compile-time offsets
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (c == cw) a = src[fd_elem<ORDER>(c, 2 * j)], b = src[fd_elem<ORDER>(c, 2 * j + 1)];
+            h[j] = __floats2half2_rn(a, b);
+        }
+        *reinterpret_cast<uint4 *>(out + row * k + c8 * 8) = *reinterpret_cast<uint4 *>(h);
+    }
+}
+
+// eight nibbles of `w` times the scale pair d2 -> four f16 pairs in the order (n0,n4) (n1,n5) (n2,n6) (n3,n7)
+__device__ __forceinline__ uint4 fd_dequant_word(uint32_t w, __half2 d2) {
+    const uint32_t w8 = w >> 8;
+    uint32_t p0 = (w & 0x000F000Fu) | 0x64006400u, p1 = (w & 0x00F000F0u) | 0x64006400u;
+    uint32_t p2 = (w8 & 0x000F000Fu) | 0x64006400u, p3 = (w8 & 0x00F000F0u) | 0x64006400u;
+    const __half2 m1032 = __half2half2(__ushort_as_half((unsigned short)0xE408));  // -1032
+    const __half2 sixteenth = __half2half2(__ushort_as_half((unsigned short)0x2C00));  // 1/16
+    const __half2 m72 = __half2half2(__ushort_as_half((unsigned short)0xD480));  // -72
+    __half2 v0 = __hmul2(__hadd2(*reinterpret_cast<__half2 *>(&p0), m1032), d2);
+    __half2 v1 = __hmul2(__hfma2(*reinterpret_cast<__half2 *>(&p1), sixteenth, m72), d2);
+    __half2 v2 = __hmul2(__hadd2(*reinterpret_cast<__half2 *>(&p2), m1032), d2);
+    __half2 v3 = __hmul2(__hfma2(*reinterpret_cast<__half2 *>(&p3), sixteenth, m72), d2);
+    uint4 o;
+    o.x = *reinterpret_cast<uint32_t *>(&v0), o.y = *reinterpret_cast<uint32_t *>(&v1);
+    o.z = *reinterpret_cast<uint32_t *>(&v2), o.w = *reinterpret_cast<uint32_t *>(&v3);
+    return o;
+}
+
+__global__ void __launch_bounds__(FD_THREADS, 1)
+    gemm_f16_fused_dequant_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, float *__restrict__ y,
+                                  int M, int N, int K, int64_t ldy, int *err) {
+    constexpr int BN = 256;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smA = smem;                                        // [FD_STAGES][A_BYTES]
+    uint8_t *smB = smem + (size_t)FD_STAGES * A_BYTES;          // [FD_STAGES][FD_B_BYTES]
+    uint8_t *smR = smB + (size_t)FD_STAGES * FD_B_BYTES;        // [FD_RAW_STAGES][FD_RAW_BYTES]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smR + (size_t)FD_RAW_STAGES * FD_RAW_BYTES);
+    uint64_t *full = bars, *empty = full + FD_STAGES, *raw_full = empty + FD_STAGES, *raw_empty = raw_full + FD_RAW_STAGES;
+    uint64_t *acc_full = raw_empty + FD_RAW_STAGES, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mt = (M + BM - 1) / BM, nt = (N + BN - 1) / BN;
+    const int ntiles = mt * nt;
+    const int nk = K / BK;           // K % 256 == 0
+    const int nchunks = K / 256;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < FD_STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1 + FD_DQ_WARPS);  // the TMA lane's expect_tx arrival + one per dequantize warp
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int s = 0; s < FD_RAW_STAGES; ++s) {
+            mbar_init(smem_u32(&raw_full[s]), 1);
+            mbar_init(smem_u32(&raw_empty[s]), FD_DQ_WARPS);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 4);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- activation tiles ----
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const int tile_m = t % mt;
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % FD_STAGES;
+                    if (it >= FD_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ((it / FD_STAGES) - 1) & 1)) {
+                        atomicExch(err, kDevErrEmptyWait);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(smem_u32(&full[s]), A_BYTES);
+                    tma_load_2d(smem_u32(smA + (size_t)s * A_BYTES), &tmA, kb * BK, tile_m * BM, smem_u32(&full[s]));
+                }
+            }
+            // never leave with copies in flight into this CTA's shared memory: the MMA lane waits on every
+            // full barrier it uses, and it only skips one after an error; wait here for the last stages too
+            const int first = it > FD_STAGES ? it - FD_STAGES : 0;
+            for (int i = first; i < it && ok; ++i)
+                if (!mbar_wait_bounded(smem_u32(&full[i % FD_STAGES]), (i / FD_STAGES) & 1)) {
+                    atomicExch(err, kDevErrDrain);
+                    break;
+                }
+        }
+    } else if (warp == 6) {
+        // ---- raw weight blocks ----
+        if (lane == 0) {
+            int ic = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const int tile_n = t / mt;
+                for (int c = 0; c < nchunks; ++c, ++ic) {
+                    const int rs = ic % FD_RAW_STAGES;
+                    if (ic >= FD_RAW_STAGES && !mbar_wait_bounded(smem_u32(&raw_empty[rs]), ((ic / FD_RAW_STAGES) - 1) & 1)) {
+                        atomicExch(err, kDevErrEmptyWait);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(smem_u32(&raw_full[rs]), FD_RAW_BYTES);
+                    tma_load_2d(smem_u32(smR + (size_t)rs * FD_RAW_BYTES), &tmW, c * (FD_RAW_ROW / 2), tile_n * BN, smem_u32(&raw_full[rs]));
+                }
+            }
+            const int first = ic > FD_RAW_STAGES ? ic - FD_RAW_STAGES : 0;
+            for (int i = first; i < ic && ok; ++i)
+                if (!mbar_wait_bounded(smem_u32(&raw_full[i % FD_RAW_STAGES]), (i / FD_RAW_STAGES) & 1)) {
+                    atomicExch(err, kDevErrDrain);
+                    break;
+                }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(BM, BN);
+            int it = 0, ti = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++ti) {
+                const int buf = ti & 1;
+                if (ti >= 2 && !mbar_wait_bounded(smem_u32(&acc_empty[buf]), ((ti >> 1) - 1) & 1)) {
+                    atomicExch(err, kDevErrMma);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % FD_STAGES;
+                    if (!mbar_wait_bounded(smem_u32(&full[s]), (it / FD_STAGES) & 1)) {
+                        atomicExch(err, kDevErrFullWait);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a0 = smem_u32(smA + (size_t)s * A_BYTES), b0 = smem_u32(smB + (size_t)s * FD_B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma_f16(acc, smem_desc_k128(a0 + 32 * k), smem_desc_k128(b0 + 32 * k), idesc, (kb | k) != 0);
+                    tc_commit(smem_u32(&empty[s]));
+                }
+                if (ok) tc_commit(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else if (warp >= 7) {
+        // ---- dequantize: thread = (weight row of the tile, first or second block of each 64 values of k) ----
+        const int dw = warp - 7;
+        const int row = (dw & 7) * 32 + lane, half = dw >> 3;
+        const uint32_t sw = (uint32_t)(row & 7);
+        int it = 0, ic = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+            for (int c = 0; c < nchunks && ok; ++c, ++ic) {
+                const int rs = ic % FD_RAW_STAGES;
+                if (!mbar_wait_bounded(smem_u32(&raw_full[rs]), (ic / FD_RAW_STAGES) & 1)) {
+                    if (lane == 0) atomicExch(err, kDevErrFullWait);
+                    ok = false;
+                    break;
+                }
+                uint32_t R[36];
+                const uint4 *rp = reinterpret_cast<const uint4 *>(smR + (size_t)rs * FD_RAW_BYTES + (size_t)row * FD_RAW_ROW);
+#pragma unroll
+                for (int i = 0; i < 9; ++i) {
+                    const uint4 v = rp[i];
+                    R[4 * i] = v.x, R[4 * i + 1] = v.y, R[4 * i + 2] = v.z, R[4 * i + 3] = v.w;
+                }
+                // this thread's block of each of the four 64-value stages: scale pair and four aligned nibble words
+                uint32_t wq[4][4], dd[4];
+#pragma unroll
+                for (int sub = 0; sub < 4; ++sub) {
+                    const uint32_t *W9 = R + 9 * sub;  // [dA:2][qsA:16][dB:2][qsB:16]
+                    dd[sub] = half == 0 ? __byte_perm(W9[0], 0, 0x1010) : __byte_perm(W9[4], 0, 0x3232);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) wq[sub][i] = half == 0 ? __funnelshift_r(W9[i], W9[i + 1], 16) : W9[5 + i];
+                }
+                // the words are in registers: the raw stage can be refilled while they are converted
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+#pragma unroll
+                for (int sub = 0; sub < 4; ++sub, ++it) {
+                    const int s = it % FD_STAGES;
+                    if (ok && it >= FD_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ((it / FD_STAGES) - 1) & 1)) {
+                        if (lane == 0) atomicExch(err, kDevErrEmptyWait);
+                        ok = false;
+                    }
+                    if (ok) {
+                        const __half2 d2 = *reinterpret_cast<__half2 *>(&dd[sub]);
+                        uint8_t *brow = smB + (size_t)s * FD_B_BYTES + (size_t)row * 128;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *reinterpret_cast<uint4 *>(brow + (((uint32_t)(4 * half + i) ^ sw) << 4)) = fd_dequant_word(wq[sub][i], d2);
+                        fence_proxy_async();  // these generic-proxy stores are read by the tensor core (async proxy)
+                    }
+                    __syncwarp();
+                    if (lane == 0 && ok) mbar_arrive(smem_u32(&full[s]));
+                }
+            }
+        }
+    } else {
+        // ---- epilogue warps 2..5 (as in the kernel above) ----
+        const int q = warp & 3;
+        int ti = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++ti) {
+            const int buf = ti & 1;
+            const int tile_m = t % mt, tile_n = t / mt;
+            if (!mbar_wait_bounded(smem_u32(&acc_full[buf]), (ti >> 1) & 1)) {
+                if (lane == 0) atomicExch(err, kDevErrMma);
+                break;
+            }
+            tc_fence_after();
+            const int64_t row = (int64_t)tile_m * BM + q * 32 + lane;
+            const int col0 = tile_n * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
+                const int col = col0 + c * 32;
+                if (row < M) {
+                    float *dst = y + row * ldy + col;
+                    if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col + i < N) dst[i] = __uint_as_float(r[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// raw Q4_0 blocks [n rows][row_bytes]; box = 144 bytes (256 values of k) x 256 rows, no swizzle, zero fill outside
+bool make_raw_w_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 2), (cuuint64_t)n};
+    cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(FD_RAW_ROW / 2), 256u};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // ---- host side ----------------------------------------------------------------------------
 // f16 [rows, k] row-major; box = 64 values of k x box_rows rows, 128-byte swizzle, zero fill outside.
 bool make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k, int box_rows) {  // box_rows <= 256
@@ -373,6 +679,34 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
     if (!cq_is_more_format(qtype) && !cq_is_k_format(qtype) && ctx->tune.gemm_variant != 3 && !ctx->tune.gemm_cache_weights && qgemm_dequant_tmem_supported(qtype, m, k, w))
         return launch_qgemm_dequant_tmem(ctx, qtype, order, x, m, k, ldx, w, n, y, ldy);
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
+    // Q4_0, wide batch: no f16 copy of W at all (the dequantization happens inside the GEMM's producer)
+    // (taken up to 384 rows unless forced with gemm_fused_dequant = 2: beyond that the kernel is bound by shared-memory
+    // bandwidth -- the raw stage adds a quarter to the bytes each MMA stage moves -- and the two-step route is faster)
+    if (qtype == CQ_Q4_0 && (ctx->tune.gemm_fused_dequant == 2 || (ctx->tune.gemm_fused_dequant == 1 && m <= 384)) && !ctx->tune.gemm_cache_weights &&
+        ctx->tune.gemm_variant == 0 && k % 256 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        cq_status s = cq_reserve_scratch(ctx, x16_bytes);
+        if (s != CQ_OK) return s;
+        __half *x16 = static_cast<__half *>(ctx->scratch);
+        const unsigned cap = (unsigned)ctx->sm_count * 16;
+        const int64_t total = m * (k / 8);
+        const unsigned xgrid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+        if (order == CQ_ORDER_GO_INTERLEAVED) x_to_f16_perm_kernel<0><<<xgrid, 256, 0, ctx->stream>>>(x, m, k, ldx, x16);
+        else x_to_f16_perm_kernel<1><<<xgrid, 256, 0, ctx->stream>>>(x, m, k, ldx, x16);
+        CQ_CUDA(ctx, cudaGetLastError());
+        CUtensorMap tmA, tmW;
+        if (!make_map(&tmA, x16, m, k, BM) || !make_raw_w_map(&tmW, w, n, (k / kQK) * kQ4Bytes))
+            return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
+        static thread_local int configured_f = -1;
+        if (configured_f != ctx->device) {
+            CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_fused_dequant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM));
+            configured_f = ctx->device;
+        }
+        const int64_t ntiles = ((m + BM - 1) / BM) * ((n + 255) / 256);
+        const unsigned ctas = (unsigned)(ntiles < ctx->sm_count ? ntiles : ctx->sm_count);
+        gemm_f16_fused_dequant_kernel<<<ctas, FD_THREADS, FD_SMEM, ctx->stream>>>(tmA, tmW, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr);
+        CQ_CUDA(ctx, cudaGetLastError());
+        return CQ_OK;
+    }
     const size_t w16_bytes = (size_t)n * k * 2;
     // With gemm_cache_weights the f16 copy of a weight matrix is made once and kept (the caller
     // promises not to rewrite those blocks in place): later calls skip the conversion kernel.

@@ -135,3 +135,37 @@ def test_narrow_batch_gemm_q8_0_edge_values(device):
     x = rng.standard_normal((m, k), dtype=np.float32)
     got = run(device, oc.Q8_0, 0, x, blocks.reshape(-1), n)
     assert rel_err(got, emulate_f16(oc.Q8_0, 0, x, blocks.reshape(-1), n)) < 2e-5
+
+
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(129, 256, 256), (130, 257, 512), (300, 700, 1024), (512, 1000, 4096), (1000, 2048, 2304)])
+def test_wide_gemm_dequantizes_in_the_producer(device, order, m, n, k):
+    """m > 128, Q4_0, k % 256 == 0: no f16 copy of W; the raw blocks are dequantized inside the GEMM.  Same f16
+    values as the two-step route (exact n - 8, one rounding in the product with the scale), so the two agree to
+    summation order; ragged m and n exercise the zero-filled tile edges."""
+    w, x = make_case(7000 + m + n + k + order, n, k, m)
+    blocks = oc.quantize(oc.Q4_0, order, w)
+    device.set_option("gemm_fused_dequant", 2)  # at every batch size, not only where it is the faster route
+    try:
+        got = run(device, oc.Q4_0, order, x, blocks, n)
+        device.set_option("gemm_fused_dequant", 0)
+        two_step = run(device, oc.Q4_0, order, x, blocks, n)
+    finally:
+        device.set_option("gemm_fused_dequant", 1)
+    assert rel_err(got, emulate_f16(oc.Q4_0, order, x, blocks, n)) < 2e-5
+    assert rel_err(got, two_step) < 2e-5
+    rows = np.linspace(0, m - 1, num=4, dtype=int)
+    assert rel_err(got[rows], oc.qmatmul(oc.Q4_0, order, x[rows], blocks, n, nthreads=8)) <= REL_TOL
+
+
+def test_wide_gemm_edge_scales(device):
+    """Zero, negative-zero, subnormal, large and negative scales through the in-producer dequantizer."""
+    n, k, m = 512, 512, 160
+    rng = np.random.default_rng(6)
+    blocks = rng.integers(0, 256, size=(n * k // 32, 18), dtype=np.uint8)
+    scales = np.array([0x0000, 0x8000, 0x0001, 0x03FF, 0x0400, 0x3C00, 0x57FF, 0xD000], dtype=np.uint16)
+    d = scales[rng.integers(0, len(scales), size=blocks.shape[0])]
+    blocks[:, 0], blocks[:, 1] = d & 0xFF, d >> 8
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    got = run(device, oc.Q4_0, 0, x, blocks.reshape(-1), n)
+    assert rel_err(got, emulate_f16(oc.Q4_0, 0, x, blocks.reshape(-1), n)) < 2e-5
