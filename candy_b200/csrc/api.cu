@@ -144,6 +144,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     if (!strcmp(key, "gemv_warps")) t.target_warps = (int)value;
     else if (!strcmp(key, "gemv_stages")) t.stages = (int)value;
     else if (!strcmp(key, "gemv_ctas_per_sm")) t.ctas_per_sm = (int)value;
+    else if (!strcmp(key, "gemm_pair")) t.gemm_pair = value ? 1 : 0;
     else if (!strcmp(key, "gemm_fused_dequant")) t.gemm_fused_dequant = value < 0 ? 0 : (value > 2 ? 2 : (int)value);
     else if (!strcmp(key, "gemv_early")) t.early = value ? 1 : 0;
     else if (!strcmp(key, "gemv_force_simple")) t.force_simple = (int)value;
