@@ -792,271 +792,13 @@ __global__ void __launch_bounds__(FD_THREADS, 1)
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-// ---- both together: CTA pairs whose B halves are dequantized in place (Q4_0, m > 128) ---------------------
-// Each CTA of a pair streams the raw blocks of ITS 128 weight rows of the 256-row tile, dequantizes them into
-// its half of the B operand (sixteen warps, each serving one of the four stages of a 256-value chunk) and loads its own 128 activation rows; per MMA
-// stage an SM then takes 16 KB of activations and 4.5 KB of raw blocks from L2 instead of 32 KB of f16.  The
-// leader's full barrier collects the activation bytes of both CTAs and one arrival per dequantize warp of both
-// that serves the stage (a cluster-scope release on the peer's arrivals, about a microsecond each, was measured
-// to halve the kernel's rate; the arrivals follow each warp's proxy fence in program order as in the one-CTA kernel).
-constexpr int FP_STAGES = 5;
-constexpr int FP_RAW_BYTES = 128 * FD_RAW_ROW;  // 18 KB: this CTA's 128 rows, 256 values of k
-constexpr int FP_DQ_WARPS = 16;
-constexpr int FP_THREADS = (7 + FP_DQ_WARPS) * 32;  // warp 0 TMA(A), 1 MMA, 2-5 epilogue, 6 TMA(raw W), 7-22 dequantize
-constexpr size_t FP_SMEM = (size_t)FP_STAGES * P2_STAGE_BYTES + (size_t)FD_RAW_STAGES * FP_RAW_BYTES + 1024 + 256;
-
-__global__ void __launch_bounds__(FP_THREADS, 1)
-    gemm_f16_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, float *__restrict__ y, int M,
-                               int N, int K, int64_t ldy, int *err) {
-    constexpr int BN = 256;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *smA = smem;                                       // [FP_STAGES][A_BYTES]
-    uint8_t *smB = smem + (size_t)FP_STAGES * A_BYTES;         // [FP_STAGES][P2_BH_BYTES]
-    uint8_t *smR = smB + (size_t)FP_STAGES * P2_BH_BYTES;      // [FD_RAW_STAGES][FP_RAW_BYTES]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smR + (size_t)FD_RAW_STAGES * FP_RAW_BYTES);
-    uint64_t *full = bars, *empty = full + FP_STAGES, *raw_full = empty + FP_STAGES, *raw_empty = raw_full + FD_RAW_STAGES;
-    uint64_t *acc_full = raw_empty + FD_RAW_STAGES, *acc_empty = acc_full + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();
-    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int mt = (M + 255) / 256, nt = (N + BN - 1) / BN;
-    const int ntiles = mt * nt;
-    const int nk = K / BK;  // K % 256 == 0
-    const int nchunks = K / 256;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < FP_STAGES; ++s) {
-            mbar_init(smem_u32(&full[s]), 1 + 2 * (FP_DQ_WARPS / 4));  // used in the leader only: its producer + four warps of each CTA per stage
-            mbar_init(smem_u32(&empty[s]), 1);
-        }
-        for (int s = 0; s < FD_RAW_STAGES; ++s) {
-            mbar_init(smem_u32(&raw_full[s]), 1);
-            mbar_init(smem_u32(&raw_empty[s]), FP_DQ_WARPS);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&acc_full[b]), 1);
-            mbar_init(smem_u32(&acc_empty[b]), 8);
-        }
-        fence_mbar_init();
-        fence_proxy_async();
-    }
-    __syncthreads();
-    cluster_sync_all();
-    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), 512);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        // ---- activation rows of this CTA ----
-        if (lane == 0) {
-            int it = 0;
-            bool ok = true;
-            for (int t = pair; t < ntiles && ok; t += npairs) {
-                const int tile_m = t % mt;
-                for (int kb = 0; kb < nk; ++kb, ++it) {
-                    const int s = it % FP_STAGES;
-                    if (it >= FP_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ((it / FP_STAGES) - 1) & 1)) {
-                        atomicExch(err, kDevErrEmptyWait);
-                        ok = false;
-                        break;
-                    }
-                    if (rank == 0) mbar_expect_tx(smem_u32(&full[s]), 2 * A_BYTES);
-                    tma_load_2d_pair(smem_u32(smA + (size_t)s * A_BYTES), &tmA, kb * BK, tile_m * 256 + (int)rank * 128,
-                                     mapa_shared(smem_u32(&full[s]), 0));
-                }
-            }
-            if (rank == 0 && ok) {
-                const int first = it > FP_STAGES ? it - FP_STAGES : 0;
-                for (int i = first; i < it; ++i)
-                    if (!mbar_wait_bounded(smem_u32(&full[i % FP_STAGES]), (i / FP_STAGES) & 1)) {
-                        atomicExch(err, kDevErrDrain);
-                        break;
-                    }
-            }
-        }
-    } else if (warp == 6) {
-        // ---- raw blocks of this CTA's 128 weight rows ----
-        if (lane == 0) {
-            int ic = 0;
-            bool ok = true;
-            for (int t = pair; t < ntiles && ok; t += npairs) {
-                const int tile_n = t / mt;
-                for (int c = 0; c < nchunks; ++c, ++ic) {
-                    const int rs = ic % FD_RAW_STAGES;
-                    if (ic >= FD_RAW_STAGES && !mbar_wait_bounded(smem_u32(&raw_empty[rs]), ((ic / FD_RAW_STAGES) - 1) & 1)) {
-                        atomicExch(err, kDevErrEmptyWait);
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(smem_u32(&raw_full[rs]), FP_RAW_BYTES);
-                    tma_load_2d(smem_u32(smR + (size_t)rs * FP_RAW_BYTES), &tmW, c * (FD_RAW_ROW / 2), tile_n * BN + (int)rank * 128,
-                                smem_u32(&raw_full[rs]));
-                }
-            }
-            const int first = ic > FD_RAW_STAGES ? ic - FD_RAW_STAGES : 0;
-            for (int i = first; i < ic && ok; ++i)
-                if (!mbar_wait_bounded(smem_u32(&raw_full[i % FD_RAW_STAGES]), (i / FD_RAW_STAGES) & 1)) {
-                    atomicExch(err, kDevErrDrain);
-                    break;
-                }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = idesc_f16(256, BN);
-            int it = 0, ti = 0;
-            bool ok = true;
-            for (int t = pair; t < ntiles && ok; t += npairs, ++ti) {
-                const int buf = ti & 1;
-                if (ti >= 2 && !mbar_wait_bounded(smem_u32(&acc_empty[buf]), ((ti >> 1) - 1) & 1)) {
-                    atomicExch(err, kDevErrMma);
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < nk; ++kb, ++it) {
-                    const int s = it % FP_STAGES;
-                    if (!mbar_wait_bounded(smem_u32(&full[s]), (it / FP_STAGES) & 1)) {
-                        atomicExch(err, kDevErrFullWait);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t a0 = smem_u32(smA + (size_t)s * A_BYTES), b0 = smem_u32(smB + (size_t)s * P2_BH_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_f16_pair(acc, smem_desc_k128(a0 + 32 * k), smem_desc_k128(b0 + 32 * k), idesc, (kb | k) != 0);
-                    tc_commit_pair(smem_u32(&empty[s]), 3);
-                }
-                if (ok) tc_commit_pair(smem_u32(&acc_full[buf]), 3);
-            }
-        }
-    } else if (warp >= 7) {
-        // ---- dequantize: warp = (one of the four 64-value stages of a 256-value chunk, 32 of this CTA's 128 weight rows) ----
-        // A warp touches one MMA stage per chunk: one barrier wait, sixteen stores per thread, one proxy fence and one
-        // arrival per 256 values of k (a warp that served every stage was bound by that chain, not by the arithmetic).
-        const int dw = warp - 7;
-        const int sub = dw & 3, row = (dw >> 2) * 32 + lane;
-        const uint32_t sw = (uint32_t)(row & 7);
-        const uint32_t lead_full0 = mapa_shared(smem_u32(&full[0]), 0);
-        int ic = 0;
-        bool ok = true;
-        for (int t = pair; t < ntiles && ok; t += npairs) {
-            for (int c = 0; c < nchunks && ok; ++c, ++ic) {
-                const int rs = ic % FD_RAW_STAGES;
-                if (!mbar_wait_bounded(smem_u32(&raw_full[rs]), (ic / FD_RAW_STAGES) & 1)) {
-                    if (lane == 0) atomicExch(err, kDevErrFullWait);
-                    ok = false;
-                    break;
-                }
-                uint32_t R[36];
-                const uint4 *rp = reinterpret_cast<const uint4 *>(smR + (size_t)rs * FP_RAW_BYTES + (size_t)row * FD_RAW_ROW);
-#pragma unroll
-                for (int i = 0; i < 9; ++i) {
-                    const uint4 v = rp[i];
-                    R[4 * i] = v.x, R[4 * i + 1] = v.y, R[4 * i + 2] = v.z, R[4 * i + 3] = v.w;
-                }
-                uint32_t W9[9];  // this warp's stage of the row: [dA:2][qsA:16][dB:2][qsB:16]
-                switch (sub) {  // warp-uniform; constant indices keep R in registers
-                    case 0:
-#pragma unroll
-                        for (int i = 0; i < 9; ++i) W9[i] = R[i];
-                        break;
-                    case 1:
-#pragma unroll
-                        for (int i = 0; i < 9; ++i) W9[i] = R[9 + i];
-                        break;
-                    case 2:
-#pragma unroll
-                        for (int i = 0; i < 9; ++i) W9[i] = R[18 + i];
-                        break;
-                    default:
-#pragma unroll
-                        for (int i = 0; i < 9; ++i) W9[i] = R[27 + i];
-                        break;
-                }
-                uint32_t wa[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) wa[i] = __funnelshift_r(W9[i], W9[i + 1], 16);
-                uint32_t da = __byte_perm(W9[0], 0, 0x1010), db = __byte_perm(W9[4], 0, 0x3232);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));  // the words are in registers
-                const int it = 4 * ic + sub;
-                const int s = it % FP_STAGES;
-                if (it >= FP_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ((it / FP_STAGES) - 1) & 1)) {
-                    if (lane == 0) atomicExch(err, kDevErrEmptyWait);
-                    ok = false;
-                    break;
-                }
-                const __half2 dA = *reinterpret_cast<__half2 *>(&da), dB = *reinterpret_cast<__half2 *>(&db);
-                uint8_t *brow = smB + (size_t)s * P2_BH_BYTES + (size_t)row * 128;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(brow + (((uint32_t)i ^ sw) << 4)) = fd_dequant_word(wa[i], dA);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(brow + (((uint32_t)(4 + i) ^ sw) << 4)) = fd_dequant_word(W9[5 + i], dB);
-                fence_proxy_async();  // these generic-proxy stores are read by the tensor core (async proxy)
-                __syncwarp();
-                if (lane == 0) {
-                    if (rank == 0) mbar_arrive(smem_u32(&full[s]));
-                    else mbar_arrive_cluster(lead_full0 + 8 * s);
-                }
-            }
-        }
-    } else {
-        const int q = warp & 3;
-        const uint32_t lead_acc_empty0 = mapa_shared(smem_u32(&acc_empty[0]), 0);
-        int ti = 0;
-        for (int t = pair; t < ntiles; t += npairs, ++ti) {
-            const int buf = ti & 1;
-            const int tile_m = t % mt, tile_n = t / mt;
-            if (!mbar_wait_bounded(smem_u32(&acc_full[buf]), (ti >> 1) & 1)) {
-                if (lane == 0) atomicExch(err, kDevErrMma);
-                break;
-            }
-            tc_fence_after();
-            const int64_t row = (int64_t)tile_m * 256 + (int)rank * 128 + q * 32 + lane;
-            const int col0 = tile_n * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
-                const int col = col0 + c * 32;
-                if (row < M) {
-                    float *dst = y + row * ldy + col;
-                    if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (col + i < N) dst[i] = __uint_as_float(r[i]);
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(lead_acc_empty0 + 8 * buf);
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();
-    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
-}
-
 // raw Q4_0 blocks [n rows][row_bytes]; box = 144 bytes (256 values of k) x 256 rows, no swizzle, zero fill outside
-bool make_raw_w_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes, int box_rows = 256) {
+bool make_raw_w_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 2), (cuuint64_t)n};
     cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    cuuint32_t box[2] = {(cuuint32_t)(FD_RAW_ROW / 2), (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)(FD_RAW_ROW / 2), 256u};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -1097,48 +839,10 @@ cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const floa
         return launch_qgemm_dequant_tmem(ctx, qtype, order, x, m, k, ldx, w, n, y, ldy);
     const size_t x16_bytes = (((size_t)m * k * 2) + 1023) & ~size_t(1023);
     // Q4_0, wide batch: no f16 copy of W at all (the dequantization happens inside the GEMM's producer)
-    // (taken up to 384 rows unless forced with gemm_fused_dequant = 2: beyond that the kernel is bound by shared-memory
-    // bandwidth -- the raw stage adds a quarter to the bytes each MMA stage moves -- and the two-step route is faster)
-    if (qtype == CQ_Q4_0 && ctx->tune.gemm_fused_dequant && ctx->tune.gemm_pair && !ctx->tune.gemm_cache_weights && ctx->tune.gemm_variant == 0 &&
-        k % 256 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
-        static thread_local int configured_fp = -1;
-        static thread_local int max_clusters_fp = 0;
-        cudaLaunchConfig_t cfg = {};
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr, cfg.numAttrs = 1;
-        cfg.blockDim = dim3(FP_THREADS);
-        cfg.dynamicSmemBytes = FP_SMEM;
-        cfg.stream = ctx->stream;
-        if (configured_fp != ctx->device) {
-            CQ_CUDA(ctx, cudaFuncSetAttribute(gemm_f16_fused_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FP_SMEM));
-            cfg.gridDim = dim3((unsigned)ctx->sm_count & ~1u);
-            int nc = 0;
-            CQ_CUDA(ctx, cudaOccupancyMaxActiveClusters(&nc, gemm_f16_fused_pair_kernel, &cfg));
-            max_clusters_fp = nc;
-            configured_fp = ctx->device;
-        }
-        if (max_clusters_fp > 0) {
-            cq_status s = cq_reserve_scratch(ctx, x16_bytes);
-            if (s != CQ_OK) return s;
-            __half *x16 = static_cast<__half *>(ctx->scratch);
-            const unsigned cap = (unsigned)ctx->sm_count * 16;
-            const int64_t total = m * (k / 8);
-            const unsigned xgrid = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
-            if (order == CQ_ORDER_GO_INTERLEAVED) x_to_f16_perm_kernel<0><<<xgrid, 256, 0, ctx->stream>>>(x, m, k, ldx, x16);
-            else x_to_f16_perm_kernel<1><<<xgrid, 256, 0, ctx->stream>>>(x, m, k, ldx, x16);
-            CQ_CUDA(ctx, cudaGetLastError());
-            CUtensorMap tmA, tmW;
-            if (!make_map(&tmA, x16, m, k, BM) || !make_raw_w_map(&tmW, w, n, (k / kQK) * kQ4Bytes, 128))
-                return cq_fail(ctx, CQ_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed or is unavailable");
-            const int64_t ntiles = ((m + 255) / 256) * ((n + 255) / 256);
-            const int64_t pairs = ntiles < max_clusters_fp ? ntiles : max_clusters_fp;
-            cfg.gridDim = dim3((unsigned)(2 * pairs));
-            CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_f16_fused_pair_kernel, tmA, tmW, y, (int)m, (int)n, (int)k, ldy, ctx->dev_err_devptr));
-            return CQ_OK;
-        }
-    }
+    // (taken up to 384 rows unless forced with gemm_fused_dequant = 2: beyond that the two-step route on CTA pairs is
+    // faster.  A CTA-pair form of this kernel -- each CTA dequantizing its half of the B tile -- was built and measured
+    // too: correct, but 207 us against 171 at m = 2048, and still 189 us with the conversion arithmetic removed, so it
+    // is not kept.)
     if (qtype == CQ_Q4_0 && (ctx->tune.gemm_fused_dequant == 2 || (ctx->tune.gemm_fused_dequant == 1 && m <= 384)) && !ctx->tune.gemm_cache_weights &&
         ctx->tune.gemm_variant == 0 && k % 256 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
         cq_status s = cq_reserve_scratch(ctx, x16_bytes);

@@ -169,3 +169,21 @@ def test_wide_gemm_edge_scales(device):
     x = rng.standard_normal((m, k), dtype=np.float32)
     got = run(device, oc.Q4_0, 0, x, blocks.reshape(-1), n)
     assert rel_err(got, emulate_f16(oc.Q4_0, 0, x, blocks.reshape(-1), n)) < 2e-5
+
+
+@pytest.mark.parametrize("qt", [oc.Q4_0, oc.Q8_0])
+@pytest.mark.parametrize("m,n,k", [(400, 700, 1056), (513, 1300, 2048), (1024, 4096, 4096)])
+def test_wide_gemm_on_cta_pairs_and_on_single_ctas(device, qt, m, n, k):
+    """m > 384: the f16 GEMM runs 256 x 256 tiles on CTA pairs (one MMA of M = 256 across two SMs); with the
+    option off it runs 128 x 256 tiles per CTA.  Both against the mode's own arithmetic, ragged edges included."""
+    w, x = make_case(8000 + m + n + k + qt, n, k, m)
+    blocks = oc.quantize(qt, 0, w)
+    want = emulate_f16(qt, 0, x, blocks, n)
+    got_pair = run(device, qt, 0, x, blocks, n)
+    device.set_option("gemm_pair", 0)
+    try:
+        got_single = run(device, qt, 0, x, blocks, n)
+    finally:
+        device.set_option("gemm_pair", 1)
+    assert rel_err(got_pair, want) < 2e-5
+    assert rel_err(got_single, want) < 2e-5
