@@ -54,9 +54,9 @@ def decode_7b(dev, peak_gbs: float, prompt: int = 128, decode: int = 256, seed: 
     }
 
 
-def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512, 2048), n: int = 11008, k: int = 4096, seed: int = 1,
+def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 256, 512, 2048), n: int = 11008, k: int = 4096, seed: int = 1,
                  calls: int = 16):
-    """BASELINE config 3: Y = X . W^T for M in {16,128,512,2048}, N=11008, K=4096, Q4_0 and Q8_0, in two
+    """BASELINE config 3: Y = X . W^T for M in {16,128,512,2048} (and 256, where the in-producer dequantization is the route), N=11008, K=4096, Q4_0 and Q8_0, in two
     numerics: CQ_ACT_F16 (f16 operands, f32 accumulate, tcgen05 kind::f16) and CQ_ACT_Q8_1 (the reference CUDA
     kernels' integer dots: Q8_1 activations, tcgen05 kind::i8, one MMA per quant block, per-block scaling on the
     CUDA cores).  Each figure is the whole cq_qmatmul call (activation pre-pass, any weight conversion, GEMM,
@@ -118,7 +118,8 @@ def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 512
                           "tensor_peak_used": round(tensor_peak, 1),
                           "path": "int8 tcgen05 (kind::i8), one MMA per quant block, per-block scaling in the epilogue" if act == 1 else (
                               ("raw blocks dequantized into tensor memory" + (" (two 64-row passes)" if qt != 2 and m > 64 else "")) if m <= 128
-                              else "f16 copy of W, then f16 tcgen05 GEMM")})
+                              else ("raw Q4_0 blocks dequantized inside the tcgen05 GEMM's producer (no f16 copy of W)" if qt == 2 and m <= 384
+                                    else "f16 copy of W, then f16 tcgen05 GEMM on CTA pairs (cta_group::2, 256 x 256 tiles)"))})
               del x, y
         del ring, first
     return {"n": n, "k": k, "peak_gbs": peak_gbs, "peak_tflops": peak_tflops, "int8_peak_measured": round(int8_peak, 1),

@@ -100,11 +100,14 @@ cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream);
 /* Tuning knobs (launch geometry, decoder choice); unknown keys -> CQ_ERR_INVALID_ARG.  Results stay
  * inside each activation mode's stated distance from the CPU path whatever the options are. */
 cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
-/* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl (launch geometry of the
+/* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl, gemv_early (launch geometry of the
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
  * row); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
  * GEMM has seen: the weights must then stay unchanged, or be rewritten only through cq_* entry points, or
- * cq_invalidate_weight_cache must be called); gemm_int8 (1, default: batches of i8_min_rows_q8_1 (3) or more
+ * cq_invalidate_weight_cache must be called); gemm_pair (1, default: CQ_ACT_F16 batches beyond 384 rows run 256 x 256
+ * tiles on CTA pairs; 0: 128 x 256 tiles per CTA); gemm_fused_dequant (1, default: Q4_0 batches of 129..384 rows in
+ * CQ_ACT_F16 dequantize the raw blocks inside the GEMM instead of making an f16 copy of W; 2: at every batch size;
+ * 0: never); gemm_int8 (1, default: batches of i8_min_rows_q8_1 (3) or more
  * rows in CQ_ACT_Q8_1 and of i8_min_rows_f32 (3) or more in CQ_ACT_F32 run the int8 tensor-core kernel, one
  * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant; comm_poll_limit (polls before the reducing
  * norm gives up on a peer's data, default about one second's worth); comm_cluster. */
