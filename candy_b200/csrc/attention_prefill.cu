@@ -60,6 +60,13 @@ __host__ __device__ constexpr uint32_t idesc_16(int mm, int nn, bool bf16) {
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(nn >> 3) << 17) | ((uint32_t)(mm >> 4) << 24);
 }
 
+// 2^x by the special-function unit (relative error about 2^-22; -inf gives 0)
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     if (BF16) {
@@ -98,29 +105,33 @@ struct FaCfg {
     static constexpr int kQBytes = kSlabs * FA_M * 128;         // Q tile
     static constexpr int kKBytes = kSlabs * FA_N * 128;         // K tile
     static constexpr int kVBytes = 2 * D * 128;                 // V^T tile: two 64-key slabs of D rows
-    static constexpr int kStages = 2;
-    static constexpr size_t kSmem = (size_t)kQBytes + (size_t)kStages * (kKBytes + kVBytes) + 2 * FA_M * 4 /* factors */ + FA_M * 4 /* sums */ +
+    // K and V^T have rings of their own: a K tile is free again as soon as its scores are computed, long before the
+    // same tile's V^T (needed only after the softmax) is; with one ring for both, the next K could not be fetched
+    // until the previous tile's second product had finished, and that load sat on the critical path of every tile.
+    static constexpr int kKStages = 3, kVStages = 2;
+    static constexpr size_t kSmem = (size_t)kQBytes + (size_t)kKStages * kKBytes + (size_t)kVStages * kVBytes + 4 * FA_M * 4 /* factors */ + FA_M * 4 /* sums */ +
                                     1024 /* alignment */ + 256 /* barriers */;
-    // tensor memory columns: two S slots, P, the tile's P V product
-    static constexpr uint32_t kColS = 0, kColP = 256, kColO = 320;
-    static_assert(kColO + D <= 512, "tensor memory");
+    // tensor memory columns: S (read into registers as soon as it is complete, so one slot is enough), two P slots
+    // (64 columns each: 128 16-bit values), two slots for the tile's P V product
+    static constexpr uint32_t kColS = 0, kColP = 128, kColO = 256;
+    static_assert(kColO + 2 * D <= 512, "tensor memory");
 };
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(FA_THREADS, 1)
     fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmVt, const FaParams p) {
     using Cfg = FaCfg<D, BF16>;
-    constexpr int SLABS = Cfg::kSlabs, ST = Cfg::kStages;
+    constexpr int SLABS = Cfg::kSlabs, KS = Cfg::kKStages, VS = Cfg::kVStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *sm_q = smem;
-    uint8_t *sm_k = sm_q + Cfg::kQBytes;                         // [ST][kKBytes]
-    uint8_t *sm_v = sm_k + (size_t)ST * Cfg::kKBytes;            // [ST][kVBytes]
-    float *sm_alpha = reinterpret_cast<float *>(sm_v + (size_t)ST * Cfg::kVBytes);  // [2][128]
-    float *sm_l = sm_alpha + 2 * FA_M;                           // [128] final sums
+    uint8_t *sm_k = sm_q + Cfg::kQBytes;                         // [KS][kKBytes]
+    uint8_t *sm_v = sm_k + (size_t)KS * Cfg::kKBytes;            // [VS][kVBytes]
+    float *sm_alpha = reinterpret_cast<float *>(sm_v + (size_t)VS * Cfg::kVBytes);  // [4][128]: tile j's factors in slot j % 4
+    float *sm_l = sm_alpha + 4 * FA_M;                           // [128] final sums
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm_l + FA_M);
-    uint64_t *q_full = bars, *kv_full = q_full + 1, *kv_empty = kv_full + ST, *s_full = kv_empty + ST, *s_empty = s_full + 2, *p_full = s_empty + 2,
-             *p_empty = p_full + 1, *o_full = p_empty + 1, *o_empty = o_full + 1, *l_full = o_empty + 1;
+    uint64_t *q_full = bars, *k_full = q_full + 1, *k_empty = k_full + KS, *v_full = k_empty + KS, *v_empty = v_full + VS, *s_full = v_empty + VS, *s_empty = s_full + 1, *p_full = s_empty + 1,
+             *p_empty = p_full + 2, *o_full = p_empty + 2, *o_empty = o_full + 2, *a_full = o_empty + 2, *l_full = a_full + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(l_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,18 +150,23 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(q_full), 1);
-        for (int s = 0; s < ST; ++s) {
-            mbar_init(smem_u32(&kv_full[s]), 1);
-            mbar_init(smem_u32(&kv_empty[s]), 1);
+        for (int s = 0; s < KS; ++s) {
+            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), 1);
         }
+        for (int s = 0; s < VS; ++s) {
+            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), 1);
+        }
+        mbar_init(smem_u32(s_full), 1);
+        mbar_init(smem_u32(s_empty), 4);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_empty[s]), 4);
+            mbar_init(smem_u32(&p_full[s]), 4);
+            mbar_init(smem_u32(&p_empty[s]), 1);
+            mbar_init(smem_u32(&o_full[s]), 1);
+            mbar_init(smem_u32(&o_empty[s]), 4);
         }
-        mbar_init(smem_u32(p_full), 4);
-        mbar_init(smem_u32(p_empty), 1);
-        mbar_init(smem_u32(o_full), 1);
-        mbar_init(smem_u32(o_empty), 4);
+        for (int s = 0; s < 4; ++s) mbar_init(smem_u32(&a_full[s]), 4);
         mbar_init(smem_u32(l_full), 4);
         fence_mbar_init();
         fence_proxy_async();
@@ -168,59 +184,85 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
             for (int c = 0; c < SLABS; ++c) tma_load_4d(smem_u32(sm_q + c * (FA_M * 128)), &tmQ, c * 64, head, q0, batch, smem_u32(q_full));
             bool ok = true;
-            for (int j = 0; j < ntiles; ++j) {
-                const int s = j % ST;
-                if (j >= ST && !mbar_wait_sleep(smem_u32(&kv_empty[s]), ((j / ST) - 1) & 1, 100)) {
+            auto load_k = [&](int t) {
+                const int s = t % KS;
+                if (t >= KS && !mbar_wait_sleep(smem_u32(&k_empty[s]), ((t / KS) - 1) & 1, 100)) {
                     atomicExch(p.err, kDevErrEmptyWait);
                     ok = false;
-                    break;
+                    return;
                 }
-                mbar_expect_tx(smem_u32(&kv_full[s]), Cfg::kKBytes + Cfg::kVBytes);
+                mbar_expect_tx(smem_u32(&k_full[s]), Cfg::kKBytes);
 #pragma unroll
                 for (int c = 0; c < SLABS; ++c)
-                    tma_load_4d(smem_u32(sm_k + (size_t)s * Cfg::kKBytes + c * (FA_N * 128)), &tmK, c * 64, kv_head, j * FA_N, batch, smem_u32(&kv_full[s]));
+                    tma_load_4d(smem_u32(sm_k + (size_t)s * Cfg::kKBytes + c * (FA_N * 128)), &tmK, c * 64, kv_head, t * FA_N, batch, smem_u32(&k_full[s]));
+            };
+            auto load_v = [&](int t) {
+                const int s = t % VS;
+                if (t >= VS && !mbar_wait_sleep(smem_u32(&v_empty[s]), ((t / VS) - 1) & 1, 100)) {
+                    atomicExch(p.err, kDevErrEmptyWait);
+                    ok = false;
+                    return;
+                }
+                mbar_expect_tx(smem_u32(&v_full[s]), Cfg::kVBytes);
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf)
-                    tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, j * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
-                                smem_u32(&kv_full[s]));
+                    tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, t * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
+                                smem_u32(&v_full[s]));
+            };
+            // K runs one tile ahead of V^T: K(0), K(1), V(0), K(2), V(1), ...
+            if (ntiles > 0) load_k(0);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                if (j + 1 < ntiles) load_k(j + 1);
+                if (ok) load_v(j);
             }
             if (ok) {  // leave only when nothing is in flight into this CTA's shared memory
                 if (!mbar_wait_sleep(smem_u32(q_full), 0, 100)) atomicExch(p.err, kDevErrDrain);
-                for (int j = ntiles > ST ? ntiles - ST : 0; j < ntiles; ++j)
-                    if (!mbar_wait_sleep(smem_u32(&kv_full[j % ST]), (j / ST) & 1, 100)) {
+                for (int j = ntiles > KS ? ntiles - KS : 0; j < ntiles && ok; ++j)
+                    if (!mbar_wait_sleep(smem_u32(&k_full[j % KS]), (j / KS) & 1, 100)) {
                         atomicExch(p.err, kDevErrDrain);
-                        break;
+                        ok = false;
+                    }
+                for (int j = ntiles > VS ? ntiles - VS : 0; j < ntiles && ok; ++j)
+                    if (!mbar_wait_sleep(smem_u32(&v_full[j % VS]), (j / VS) & 1, 100)) {
+                        atomicExch(p.err, kDevErrDrain);
+                        ok = false;
                     }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && ntiles > 0) {
             constexpr uint32_t idesc_s = idesc_16(FA_M, FA_N, BF16), idesc_o = idesc_16(FA_M, D, BF16);
-            bool ok = mbar_wait_sleep(smem_u32(q_full), 0, 40);
+            bool ok = mbar_wait_bounded(smem_u32(q_full), 0);
             if (!ok) atomicExch(p.err, kDevErrFullWait);
             const uint32_t q_addr = smem_u32(sm_q);
-            // S(j) = Q K(j)^T into slot j & 1
+            // S(j) = Q K(j)^T (one slot: the softmax warps free it as soon as they hold the scores in registers)
             auto issue_qk = [&](int j) -> bool {
-                const int s = j % ST, buf = j & 1;
-                if (!mbar_wait_sleep(smem_u32(&kv_full[s]), (j / ST) & 1, 40)) return false;
-                if (j >= 2 && !mbar_wait_sleep(smem_u32(&s_empty[buf]), ((j >> 1) - 1) & 1, 40)) return false;
+                const int s = j % KS;
+                if (!mbar_wait_bounded(smem_u32(&k_full[s]), (j / KS) & 1)) return false;
+                if (j >= 1 && !mbar_wait_bounded(smem_u32(s_empty), (j - 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sm_k + (size_t)s * Cfg::kKBytes);
 #pragma unroll
                 for (int c = 0; c < SLABS; ++c)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        tc_mma_f16(tmem_base + Cfg::kColS + (uint32_t)(buf * FA_N), smem_desc_k128(q_addr + c * (FA_M * 128) + kk * 32),
+                        tc_mma_f16(tmem_base + Cfg::kColS, smem_desc_k128(q_addr + c * (FA_M * 128) + kk * 32),
                                    smem_desc_k128(k_addr + c * (FA_N * 128) + kk * 32), idesc_s, (c | kk) != 0);
-                tc_commit(smem_u32(&s_full[buf]));
+                tc_commit(smem_u32(s_full));
+                tc_commit(smem_u32(&k_empty[s]));  // the K tile is free once these MMAs have read it
                 return true;
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < ntiles && ok; ++j) {
                 if (j + 1 < ntiles) ok = issue_qk(j + 1);  // the next tile's scores are computed while this tile's softmax runs
                 if (!ok) break;
-                const int s = j % ST;
-                if (!mbar_wait_sleep(smem_u32(p_full), j & 1, 40) || (j >= 1 && !mbar_wait_sleep(smem_u32(o_empty), (j - 1) & 1, 40))) {
+                const int s = j % VS;
+                if (!mbar_wait_bounded(smem_u32(&v_full[s]), (j / VS) & 1)) {
+                    ok = false;
+                    break;
+                }
+                // P(j) in place, and the product slot free (the accumulate warps have folded tile j - 2)
+                if (!mbar_wait_bounded(smem_u32(&p_full[j & 1]), (j >> 1) & 1) || (j >= 2 && !mbar_wait_bounded(smem_u32(&o_empty[j & 1]), ((j >> 1) - 1) & 1))) {
                     ok = false;
                     break;
                 }
@@ -230,11 +272,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)  // 16 keys per step: 8 tensor-memory columns of P, 32 bytes of a V^T row
-                        tc_mma_f16_ts(tmem_base + Cfg::kColO, tmem_base + Cfg::kColP + (uint32_t)((hf * 4 + kk) * 8),
+                        tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)((j & 1) * D), tmem_base + Cfg::kColP + (uint32_t)((j & 1) * 64 + (hf * 4 + kk) * 8),
                                       smem_desc_k128(v_addr + hf * (D * 128) + kk * 32), idesc_o, (hf | kk) != 0);
-                tc_commit(smem_u32(o_full));
-                tc_commit(smem_u32(p_empty));
-                tc_commit(smem_u32(&kv_empty[s]));
+                tc_commit(smem_u32(&o_full[j & 1]));
+                tc_commit(smem_u32(&p_empty[j & 1]));
+                tc_commit(smem_u32(&v_empty[s]));
             }
             if (!ok) atomicExch(p.err, kDevErrMma);
         }
@@ -248,62 +290,81 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {
             const int buf = j & 1;
-            if (!mbar_wait_sleep(smem_u32(&s_full[buf]), (j >> 1) & 1, 20)) {
+            if (!mbar_wait_bounded(smem_u32(s_full), j & 1)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + Cfg::kColS + (uint32_t)(buf * FA_N);
+            const uint32_t s_addr = lane_addr + Cfg::kColS;
             const int key0 = j * FA_N;
             const int kmax = min(p.seqlen_k - 1, causal_lim) - key0;  // columns > kmax of this tile are masked
-            // pass 1: the row's maximum over the visible keys of the tile
-            float m_tile = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < FA_N / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(s_addr + c * 32, v);
+            // The row's 128 scores are read out of tensor memory once (four loads in flight, one wait) and stay in
+            // registers for both steps.  Only a tile that the causal diagonal or the end of the keys cuts needs the
+            // per-column mask; every other tile takes the plain loops (one max, then one FMA, one ex2.approx, one
+            // add and half a pack per score -- the exponentials, 16 a clock and SM, are then what bounds this warp).
+            uint32_t sv[FA_N];
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (c * 32 + i <= kmax) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+            for (int c = 0; c < FA_N / 32; ++c) tmem_ld32_async(s_addr + c * 32, sv + c * 32);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(s_empty));  // the scores are in registers: the next tile's may be computed
+            const bool cut = kmax < FA_N - 1;
+            float m_tile = -INFINITY;
+            if (!cut) {
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < FA_N; i += 4) {
+                    m4[0] = fmaxf(m4[0], __uint_as_float(sv[i])), m4[1] = fmaxf(m4[1], __uint_as_float(sv[i + 1]));
+                    m4[2] = fmaxf(m4[2], __uint_as_float(sv[i + 2])), m4[3] = fmaxf(m4[3], __uint_as_float(sv[i + 3]));
+                }
+                m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < FA_N; ++i)
+                    if (i <= kmax) m_tile = fmaxf(m_tile, __uint_as_float(sv[i]));
             }
             const float m_new = fmaxf(m_run, m_tile);
             const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // a row with no visible key yet: every p is 0
-            const float alpha = exp2f((m_run - m_use) * p.scale_log2);  // m_run = -inf gives 0: nothing accumulated yet
+            const float alpha = fast_ex2((m_run - m_use) * p.scale_log2);  // m_run = -inf gives 0: nothing accumulated yet
             const float mb = m_use * p.scale_log2;
-            // the previous tile's P must have been consumed before it is overwritten
-            if (j >= 1 && !mbar_wait_sleep(smem_u32(p_empty), (j - 1) & 1, 20)) {
+            // P has two slots: the product that read this one (two tiles back) must have finished
+            if (j >= 2 && !mbar_wait_bounded(smem_u32(&p_empty[buf]), ((j >> 1) - 1) & 1)) {
                 if (lane == 0) atomicExch(p.err, kDevErrMma);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            // pass 2: p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
-            float l_tile = 0.0f;
-#pragma unroll 1
+            // p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
+            float l2[2] = {0.0f, 0.0f};
+#pragma unroll
             for (int c = 0; c < FA_N / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(s_addr + c * 32, v);
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int c0 = c * 32 + 2 * i;
-                    const float p0 = c0 <= kmax ? exp2f(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -mb)) : 0.0f;
-                    const float p1 = c0 + 1 <= kmax ? exp2f(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -mb)) : 0.0f;
-                    l_tile += p0 + p1;
+                    float p0 = fast_ex2(fmaf(__uint_as_float(sv[c0]), p.scale_log2, -mb));
+                    float p1 = fast_ex2(fmaf(__uint_as_float(sv[c0 + 1]), p.scale_log2, -mb));
+                    if (cut) {
+                        p0 = c0 <= kmax ? p0 : 0.0f;
+                        p1 = c0 + 1 <= kmax ? p1 : 0.0f;
+                    }
+                    l2[0] += p0, l2[1] += p1;
                     pk[i] = pack2<BF16>(p0, p1);
                 }
-                tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(c * 16), pk);
+                tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(buf * 64 + c * 16), pk);
             }
+            const float l_tile = l2[0] + l2[1];
             tmem_wait_st();
             l_run = l_run * alpha + l_tile;
             m_run = m_new;
-            sm_alpha[buf * FA_M + r] = alpha;
+            sm_alpha[(j & 3) * FA_M + r] = alpha;  // four slots: the softmax can be up to four tiles ahead of the accumulate warps
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(smem_u32(&s_empty[buf]));  // the scores are consumed
-                mbar_arrive(smem_u32(p_full));         // P and the factor are in place
+                mbar_arrive(smem_u32(&p_full[buf]));     // P is in place
+                mbar_arrive(smem_u32(&a_full[j & 3]));   // and so is the factor
             }
         }
         sm_l[r] = l_run;
@@ -322,32 +383,32 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         for (int i = 0; i < D; ++i) acc[i] = 0.0f;
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {
-            if (!mbar_wait_sleep(smem_u32(o_full), j & 1, 20)) {
+            // The factor: its barrier has four slots, and slot j & 3 cannot complete again (tile j + 4) before this warp
+            // has released tile j's product slot -- P(j + 4) waits for the product of tile j + 2, which waits for that.
+            if (!mbar_wait_bounded(smem_u32(&a_full[j & 3]), (j >> 2) & 1)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                ok = false;
+                break;
+            }
+            if (!mbar_wait_bounded(smem_u32(&o_full[j & 1]), (j >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            // the factor was written by the softmax warps before they signalled p_full: wait on that barrier itself
-            // (it cannot run two phases ahead: the next P needs this tile's product consumed, i.e. o_empty below)
-            if (!mbar_wait_sleep(smem_u32(p_full), j & 1, 20)) {
-                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-                ok = false;
-                break;
-            }
-            const float alpha = sm_alpha[(j & 1) * FA_M + r];
+            const float alpha = sm_alpha[(j & 3) * FA_M + r];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(o_addr + c * 32, v);
+                tmem_ld32(o_addr + (uint32_t)((j & 1) * D) + c * 32, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(v[i]));
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(o_empty));
+            if (lane == 0) mbar_arrive(smem_u32(&o_empty[j & 1]));
         }
-        if (ok && !mbar_wait_sleep(smem_u32(l_full), 0, 20)) {
+        if (ok && !mbar_wait_bounded(smem_u32(l_full), 0)) {
             if (lane == 0) atomicExch(p.err, kDevErrFullWait);
             ok = false;
         }
