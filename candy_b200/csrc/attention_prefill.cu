@@ -6,16 +6,25 @@
 // sm_100a kernel with the same contract for the cases a decoder's prompt phase needs.
 //
 // One CTA per (128 query rows, head, batch); keys and values stream through in tiles of 128 keys.
-//   warp 0        TMA: the Q tile once, then K and V^T tiles into a two-stage ring (128-byte swizzle)
-//   warp 1        tcgen05.mma issue: S = Q K^T into one of two 128-column f32 slots in tensor memory,
-//                 O_tile = P V with P read from tensor memory as the A operand
-//   warps 2-5     softmax: thread = query row; reads its row of S (tcgen05.ld), masks (key >= seqlen_k; causal:
-//                 key > row + seqlen_k - seqlen_q, the bottom-right alignment of kernels/mask.h:61-62), keeps the
-//                 running max and sum, writes P as packed f16 / bf16 pairs back into tensor memory (tcgen05.st)
-//                 and the factor exp(old max - new max) for the accumulator
-//   warps 6-9     accumulate: thread = query row with its output row in f32 registers; every tile's P V product
-//                 arrives fresh in tensor memory and is folded in as acc = acc * factor + tile, so nothing in
-//                 tensor memory is ever rescaled in place; at the end acc / sum goes out as f16 / bf16
+//   warp 0        TMA: the Q tile once, then K tiles into a three-stage ring and V^T tiles into a two-stage ring of
+//                 its own (128-byte swizzle); a K tile is free as soon as its scores exist, long before its V^T
+//   warp 1        tcgen05.mma issue: S = Q K^T into a 128-column f32 slot of tensor memory (one slot: the compute
+//                 warps release it once the scores sit in their registers), O_tile = P V with P read from tensor
+//                 memory as the A operand into one of two product slots; one commit per product
+//   warps 2-9     compute: thread = (query row, half of the columns): warps 2-5 take keys 0-63 of a tile and the first
+//                 half of the output row, warps 6-9 the other halves (two warps per tensor-memory lane quarter, two per
+//                 scheduler).  Softmax of the half: scores read once (tcgen05.ld, loads in flight together), masked
+//                 only on a tile the causal diagonal or the end of the keys cuts (key >= seqlen_k; causal: key > row +
+//                 seqlen_k - seqlen_q, the bottom-right alignment of kernels/mask.h:61-62); the two halves of a row
+//                 agree on the maximum through shared memory and a 64-thread named barrier; p = ex2.approx of the
+//                 scaled difference, written as packed f16 / bf16 pairs into one of two P slots (tcgen05.st).  Then the
+//                 previous tile's product is folded into f32 registers, acc = acc * factor + tile, so nothing in
+//                 tensor memory is ever rescaled in place and the factor never leaves its thread; at the end
+//                 acc / (sum of both halves) goes out as f16 / bf16
+// Measured per tile (clock64 counters in an instrumented build): the MMA lane is busy ~2400 of ~3600 cycles and the
+// compute warps wait for scores a third of the time -- the 128 x 128 x 16 MMAs of S read both operands from shared
+// memory at exactly its bandwidth, next to the TMA writes, so the tensor pipe paces the kernel at about a quarter
+// of its peak.
 // V is [key][d] in memory but the P V product wants it K-major, i.e. [d][key]: a small kernel transposes it into
 // context scratch first (2 x the V bytes of traffic against O(seq^2 d) of compute).
 // Every wait is bounded; tensor memory is always freed.
@@ -108,8 +117,8 @@ struct FaCfg {
     // K and V^T have rings of their own: a K tile is free again as soon as its scores are computed, long before the
     // same tile's V^T (needed only after the softmax) is; with one ring for both, the next K could not be fetched
     // until the previous tile's second product had finished, and that load sat on the critical path of every tile.
-    static constexpr int kKStages = 3, kVStages = 2;
-    static constexpr size_t kSmem = (size_t)kQBytes + (size_t)kKStages * kKBytes + (size_t)kVStages * kVBytes + 4 * FA_M * 4 /* factors */ + FA_M * 4 /* sums */ +
+    static constexpr int kKStages = 3, kVStages = 2;  // kVStages must stay 2 (see the V^T loads)
+    static constexpr size_t kSmem = (size_t)kQBytes + (size_t)kKStages * kKBytes + (size_t)kVStages * kVBytes + 4 * FA_M * 4 /* half-row maxima */ + 2 * FA_M * 4 /* half-row sums */ +
                                     1024 /* alignment */ + 256 /* barriers */;
     // tensor memory columns: S (read into registers as soon as it is complete, so one slot is enough), two P slots
     // (64 columns each: 128 16-bit values), two slots for the tile's P V product
@@ -127,12 +136,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     uint8_t *sm_q = smem;
     uint8_t *sm_k = sm_q + Cfg::kQBytes;                         // [KS][kKBytes]
     uint8_t *sm_v = sm_k + (size_t)KS * Cfg::kKBytes;            // [VS][kVBytes]
-    float *sm_alpha = reinterpret_cast<float *>(sm_v + (size_t)VS * Cfg::kVBytes);  // [4][128]: tile j's factors in slot j % 4
-    float *sm_l = sm_alpha + 4 * FA_M;                           // [128] final sums
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm_l + FA_M);
-    uint64_t *q_full = bars, *k_full = q_full + 1, *k_empty = k_full + KS, *v_full = k_empty + KS, *v_empty = v_full + VS, *s_full = v_empty + VS, *s_empty = s_full + 1, *p_full = s_empty + 1,
-             *p_empty = p_full + 2, *o_full = p_empty + 2, *o_empty = o_full + 2, *a_full = o_empty + 2, *l_full = a_full + 4;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(l_full + 1);
+    float *sm_mx = reinterpret_cast<float *>(sm_v + (size_t)VS * Cfg::kVBytes);  // [2 tile parities][2 halves][128]: maxima of half rows
+    float *sm_l = sm_mx + 4 * FA_M;                              // [2 halves][128] final sums
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm_l + 2 * FA_M);
+    uint64_t *q_full = bars, *k_full = q_full + 1, *k_empty = k_full + KS, *v_full = k_empty + KS, *s_full = v_full + VS, *s_empty = s_full + 1, *p_full = s_empty + 1,
+             *o_full = p_full + 2, *o_empty = o_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy tiles (late query rows under a causal mask) first
@@ -156,18 +165,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         }
         for (int s = 0; s < VS; ++s) {
             mbar_init(smem_u32(&v_full[s]), 1);
-            mbar_init(smem_u32(&v_empty[s]), 1);
         }
         mbar_init(smem_u32(s_full), 1);
-        mbar_init(smem_u32(s_empty), 4);
+        mbar_init(smem_u32(s_empty), 8);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&p_full[s]), 4);
-            mbar_init(smem_u32(&p_empty[s]), 1);
+            mbar_init(smem_u32(&p_full[s]), 8);
             mbar_init(smem_u32(&o_full[s]), 1);
-            mbar_init(smem_u32(&o_empty[s]), 4);
+            mbar_init(smem_u32(&o_empty[s]), 8);
         }
-        for (int s = 0; s < 4; ++s) mbar_init(smem_u32(&a_full[s]), 4);
-        mbar_init(smem_u32(l_full), 4);
         fence_mbar_init();
         fence_proxy_async();
     }
@@ -198,7 +203,9 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             };
             auto load_v = [&](int t) {
                 const int s = t % VS;
-                if (t >= VS && !mbar_wait_sleep(smem_u32(&v_empty[s]), ((t / VS) - 1) & 1, 100)) {
+                // a V^T stage is free when the product that read it has finished: the barrier the compute warps wait on
+                // for that product (one commit per tile serves all three uses; VS == 2 == the number of product slots)
+                if (t >= VS && !mbar_wait_sleep(smem_u32(&o_full[s]), ((t / VS) - 1) & 1, 100)) {
                     atomicExch(p.err, kDevErrEmptyWait);
                     ok = false;
                     return;
@@ -274,72 +281,99 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                     for (int kk = 0; kk < 4; ++kk)  // 16 keys per step: 8 tensor-memory columns of P, 32 bytes of a V^T row
                         tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)((j & 1) * D), tmem_base + Cfg::kColP + (uint32_t)((j & 1) * 64 + (hf * 4 + kk) * 8),
                                       smem_desc_k128(v_addr + hf * (D * 128) + kk * 32), idesc_o, (hf | kk) != 0);
-                tc_commit(smem_u32(&o_full[j & 1]));
-                tc_commit(smem_u32(&p_empty[j & 1]));
-                tc_commit(smem_u32(&v_empty[s]));
+                tc_commit(smem_u32(&o_full[j & 1]));  // product ready; its P slot and V^T stage free
             }
             if (!ok) atomicExch(p.err, kDevErrMma);
         }
-    } else if (warp < 6) {
-        // ---- softmax: thread = query row -------------------------------------------------------------------
-        const int quarter = warp & 3, r = quarter * 32 + lane;
-        const int row = q0 + r;                               // global query index
+    } else {
+        // ---- eight compute warps: thread = (query row, one half of the columns) ------------------------------------------
+        // Warps 2-5 take key columns 0-63 of a tile's scores and the first half of the output row, warps 6-9 the other
+        // halves (a warp may touch only the tensor-memory lanes of its quarter, warp & 3: two warps per quarter).
+        // Each does the softmax of its half -- the two halves of a row agree on the maximum through shared memory and
+        // a 64-thread named barrier -- and folds its half of the previous tile's P V product into registers
+        // (acc = acc * factor + tile).  Two warps per scheduler instead of one hide each other's latencies, and the
+        // factor never leaves the thread that computed it.
+        constexpr int HC = FA_N / 2, HD = D / 2;
+        const int quarter = warp & 3, half = (warp - 2) >> 2, r = quarter * 32 + lane;
+        const int row = q0 + r;                                    // global query index
         const int causal_lim = p.causal ? row + off : 0x7FFFFFFF;  // last visible key
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float m_run = -INFINITY, l_run = 0.0f;                // running max of the raw scores, running sum
+        float m_run = -INFINITY, l_run = 0.0f;  // running max of the raw scores (whole row), running sum (this half)
+        float alpha_prev = 0.0f;                // the factor of the tile whose product is folded next
+        float acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
         bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int buf = j & 1;
-            if (!mbar_wait_bounded(smem_u32(s_full), j & 1)) {
+        auto fold = [&](int jt, float alpha) -> bool {  // acc = acc * alpha + (P V)(jt), this thread's half of the columns
+            if (!mbar_wait_bounded(smem_u32(&o_full[jt & 1]), (jt >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-                ok = false;
-                break;
+                return false;
             }
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + Cfg::kColS;
-            const int key0 = j * FA_N;
-            const int kmax = min(p.seqlen_k - 1, causal_lim) - key0;  // columns > kmax of this tile are masked
-            // The row's 128 scores are read out of tensor memory once (four loads in flight, one wait) and stay in
-            // registers for both steps.  Only a tile that the causal diagonal or the end of the keys cuts needs the
-            // per-column mask; every other tile takes the plain loops (one max, then one FMA, one ex2.approx, one
-            // add and half a pack per score -- the exponentials, 16 a clock and SM, are then what bounds this warp).
-            uint32_t sv[FA_N];
+            const uint32_t o_addr = lane_addr + Cfg::kColO + (uint32_t)((jt & 1) * D + half * HD);
 #pragma unroll
-            for (int c = 0; c < FA_N / 32; ++c) tmem_ld32_async(s_addr + c * 32, sv + c * 32);
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(o_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(v[i]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&o_empty[jt & 1]));
+            return true;
+        };
+        for (int j = 0; j < ntiles; ++j) {
+            const int buf = j & 1;
+            // A warp whose wait gave up keeps walking the tiles without waiting or computing, so that its partner
+            // (the other half of the rows' columns) still finds it at the named barrier below.
+            if (ok && !mbar_wait_bounded(smem_u32(s_full), j & 1)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                ok = false;
+            }
+            if (!ok) {
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+                continue;
+            }
+            tc_fence_after();
+            const int kmax = min(p.seqlen_k - 1, causal_lim) - j * FA_N - half * HC;  // columns > kmax of this half are masked
+            // this half of the row's scores: read out of tensor memory once, kept in registers for both steps
+            uint32_t sv[HC];
+#pragma unroll
+            for (int c = 0; c < HC / 32; ++c) tmem_ld32_async(lane_addr + Cfg::kColS + (uint32_t)(half * HC + c * 32), sv + c * 32);
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(s_empty));  // the scores are in registers: the next tile's may be computed
-            const bool cut = kmax < FA_N - 1;
-            float m_tile = -INFINITY;
+            const bool cut = kmax < HC - 1;  // only a tile that the causal diagonal or the end of the keys cuts needs the mask
+            float m_half = -INFINITY;
             if (!cut) {
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < FA_N; i += 4) {
+                for (int i = 0; i < HC; i += 4) {
                     m4[0] = fmaxf(m4[0], __uint_as_float(sv[i])), m4[1] = fmaxf(m4[1], __uint_as_float(sv[i + 1]));
                     m4[2] = fmaxf(m4[2], __uint_as_float(sv[i + 2])), m4[3] = fmaxf(m4[3], __uint_as_float(sv[i + 3]));
                 }
-                m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                m_half = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             } else {
 #pragma unroll
-                for (int i = 0; i < FA_N; ++i)
-                    if (i <= kmax) m_tile = fmaxf(m_tile, __uint_as_float(sv[i]));
+                for (int i = 0; i < HC; ++i)
+                    if (i <= kmax) m_half = fmaxf(m_half, __uint_as_float(sv[i]));
             }
+            // the row's maximum over both halves
+            sm_mx[(buf * 2 + half) * FA_M + r] = m_half;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            const float m_tile = fmaxf(m_half, sm_mx[(buf * 2 + (half ^ 1)) * FA_M + r]);
             const float m_new = fmaxf(m_run, m_tile);
             const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // a row with no visible key yet: every p is 0
             const float alpha = fast_ex2((m_run - m_use) * p.scale_log2);  // m_run = -inf gives 0: nothing accumulated yet
             const float mb = m_use * p.scale_log2;
-            // P has two slots: the product that read this one (two tiles back) must have finished
-            if (j >= 2 && !mbar_wait_bounded(smem_u32(&p_empty[buf]), ((j >> 1) - 1) & 1)) {
-                if (lane == 0) atomicExch(p.err, kDevErrMma);
-                ok = false;
-                break;
-            }
-            tc_fence_after();
+            // P has two slots: the product that read this one (two tiles back) has finished -- this warp folded it
+            // at the end of the previous iteration.
             // p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
             float l2[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < FA_N / 32; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -353,71 +387,32 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                     l2[0] += p0, l2[1] += p1;
                     pk[i] = pack2<BF16>(p0, p1);
                 }
-                tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(buf * 64 + c * 16), pk);
+                tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(buf * (FA_N / 2) + half * (HC / 2) + c * 16), pk);
             }
-            const float l_tile = l2[0] + l2[1];
             tmem_wait_st();
-            l_run = l_run * alpha + l_tile;
+            l_run = l_run * alpha + (l2[0] + l2[1]);
             m_run = m_new;
-            sm_alpha[(j & 3) * FA_M + r] = alpha;  // four slots: the softmax can be up to four tiles ahead of the accumulate warps
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&p_full[buf]));     // P is in place
-                mbar_arrive(smem_u32(&a_full[j & 3]));   // and so is the factor
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));  // this warp's part of P is in place
+            // the previous tile's product, while the tensor core works on this tile's
+            if (j >= 1) ok = fold(j - 1, alpha_prev);
+            alpha_prev = alpha;
         }
-        sm_l[r] = l_run;
-        if (p.lse && row < p.seqlen_q)  // kernels/softmax.h:206: max * scale + log(sum); +inf for a row with nothing to attend to
-            p.lse[((int64_t)batch * p.h + head) * p.seqlen_q + row] = (l_run == 0.0f || l_run != l_run) ? INFINITY : m_run * p.scale + logf(l_run);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(l_full));
-    } else {
-        // ---- accumulate: thread = query row, output row in registers --------------------------------------------
-        const int quarter = warp & 3, r = quarter * 32 + lane;
-        const int row = q0 + r;
-        const uint32_t o_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::kColO;
-        pdl_wait_prior();  // the output buffer may still be read by an earlier kernel
-        float acc[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) acc[i] = 0.0f;
-        bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            // The factor: its barrier has four slots, and slot j & 3 cannot complete again (tile j + 4) before this warp
-            // has released tile j's product slot -- P(j + 4) waits for the product of tile j + 2, which waits for that.
-            if (!mbar_wait_bounded(smem_u32(&a_full[j & 3]), (j >> 2) & 1)) {
-                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-                ok = false;
-                break;
-            }
-            if (!mbar_wait_bounded(smem_u32(&o_full[j & 1]), (j >> 1) & 1)) {
-                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            const float alpha = sm_alpha[(j & 3) * FA_M + r];
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(o_addr + (uint32_t)((j & 1) * D) + c * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(v[i]));
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&o_empty[j & 1]));
-        }
-        if (ok && !mbar_wait_bounded(smem_u32(l_full), 0)) {
-            if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-            ok = false;
-        }
+        if (ok && ntiles > 0) ok = fold(ntiles - 1, alpha_prev);
+        // the row's sum over both halves (both used the same maxima)
+        sm_l[half * FA_M + r] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+        const float l = l_run + sm_l[(half ^ 1) * FA_M + r];
+        if (half == 0 && p.lse && row < p.seqlen_q)  // kernels/softmax.h:206: max * scale + log(sum); +inf for a row with nothing to attend to
+            p.lse[((int64_t)batch * p.h + head) * p.seqlen_q + row] = (l == 0.0f || l != l) ? INFINITY : m_run * p.scale + logf(l);
         if (ok && row < p.seqlen_q) {
-            const float l = sm_l[r];
+            pdl_wait_prior();  // the output buffer may still be read by an earlier kernel
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // nothing to attend to: zeros, as the reference writes
-            uint16_t *dst = reinterpret_cast<uint16_t *>(p.o) + (int64_t)batch * p.o_batch_stride + (int64_t)row * p.o_row_stride + (int64_t)head * p.o_head_stride;
+            uint16_t *dst = reinterpret_cast<uint16_t *>(p.o) + (int64_t)batch * p.o_batch_stride + (int64_t)row * p.o_row_stride + (int64_t)head * p.o_head_stride +
+                            half * HD;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
+            for (int c = 0; c < HD / 8; ++c) {
                 uint4 w;
                 w.x = pack2<BF16>(acc[8 * c] * inv, acc[8 * c + 1] * inv);
                 w.y = pack2<BF16>(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
