@@ -21,10 +21,11 @@
 //                 previous tile's product is folded into f32 registers, acc = acc * factor + tile, so nothing in
 //                 tensor memory is ever rescaled in place and the factor never leaves its thread; at the end
 //                 acc / (sum of both halves) goes out as f16 / bf16
-// Measured per tile (clock64 counters in an instrumented build): the MMA lane is busy ~2400 of ~3600 cycles and the
-// compute warps wait for scores a third of the time -- the 128 x 128 x 16 MMAs of S read both operands from shared
-// memory at exactly its bandwidth, next to the TMA writes, so the tensor pipe paces the kernel at about a quarter
-// of its peak.
+// Measured per tile (clock64 counters in an instrumented build): the MMA lane is busy ~2400 of ~3600 cycles (the
+// tensor pipe itself ~1450 by the profiler's count) and the compute warps wait for scores a third of the time.
+// Keeping Q in tensor memory as the A operand of S, so that only K is read from shared memory, changed nothing
+// (measured, not kept): the MMAs are not starved for operands; what is left is the hand-over chain of a tile --
+// scores complete -> read -> maximum -> exponentials -> P complete -> product -> fold -- with one S slot.
 // V is [key][d] in memory but the P V product wants it K-major, i.e. [d][key]: a small kernel transposes it into
 // context scratch first (2 x the V bytes of traffic against O(seq^2 d) of compute).
 // Every wait is bounded; tensor memory is always freed.
