@@ -24,8 +24,8 @@
 // Measured per tile (clock64 counters in an instrumented build): the MMA lane is busy ~2400 of ~3600 cycles (the
 // tensor pipe itself ~1450 by the profiler's count) and the compute warps wait for scores a third of the time.
 // Keeping Q in tensor memory as the A operand of S, so that only K is read from shared memory, changed nothing
-// (measured, not kept): the MMAs are not starved for operands; what is left is the hand-over chain of a tile --
-// scores complete -> read -> maximum -> exponentials -> P complete -> product -> fold -- with one S slot.
+// (measured, not kept), and so did two S slots with one product slot: the MMAs are neither starved for operands
+// nor held back by the S slot.
 // V is [key][d] in memory but the P V product wants it K-major, i.e. [d][key]: a small kernel transposes it into
 // context scratch first (2 x the V bytes of traffic against O(seq^2 d) of compute).
 // Every wait is bounded; tensor memory is always freed.
