@@ -67,6 +67,8 @@ SIGNATURES = {
     "cq_rmsnorm": [_vp, _vp, _vp, _i64, _i64, C.c_float, _vp],
     "cq_add_rmsnorm": [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _vp],
     "cq_rope_store_kv": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int],
+    "cq_rope_prefill": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _int],
+    "cq_cast16_to_f32": [_vp, _vp, _i64, _int, _vp],
     "cq_decode_attention": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _int, _vp, _vp],
     "cq_decode_attention_rope": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp],
     "cq_silu_mul": [_vp, _vp, _i64, _i64, _vp, _i64],

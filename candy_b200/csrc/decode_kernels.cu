@@ -9,6 +9,9 @@
 // All are HBM- or latency-bound streaming kernels over a few KB..MB; none touches weights.
 // They take part in programmatic dependent launch like the GEMV: trigger the dependents at
 // entry, wait for the previous kernel before reading its output.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace {
@@ -124,6 +127,66 @@ __device__ __forceinline__ float rope_elem(const float *__restrict__ v, int d, i
     }
     const float c = cos_t[(int64_t)pos * half + d - half], s = sin_t[(int64_t)pos * half + d - half];
     return v[d - half] * s + v[d] * c;
+}
+
+// ---- prompt phase: the rotary step for T consecutive positions of one sequence -----------------------------
+// qkv: [T, (nq + 2 nkv) * hd] f32, row t belongs to position pos0 + t.  The same arithmetic as
+// rope_store_kv_kernel per row: q and k rotated (half-split pairs), rotated k and plain v stored to the f32 caches
+// [max_ctx][nkv * hd] at their positions -- what the decode kernels read afterwards -- and, for the tensor-core
+// attention of the prompt itself, 16-bit copies (f16 or bf16, round to nearest even) of rotated q [T][nq * hd],
+// rotated k [T][nkv * hd] and v [T][nkv * hd].
+template <bool BF16>
+__device__ __forceinline__ uint16_t to16(float v) {
+    if (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    return __half_as_ushort(__float2half_rn(v));
+}
+template <bool BF16>
+__global__ void __launch_bounds__(256) rope_prefill_kernel(const float *__restrict__ qkv, int T, int nq, int nkv, int hd, const float *__restrict__ cos_t,
+                                                         const float *__restrict__ sin_t, int pos0, float *__restrict__ kc, float *__restrict__ vc,
+                                                         uint16_t *__restrict__ q16, uint16_t *__restrict__ k16, uint16_t *__restrict__ v16) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int t = blockIdx.y;
+    const int pos = pos0 + t;
+    const int half = hd / 2;
+    const int row = (nq + 2 * nkv) * hd;
+    const float *base = qkv + (int64_t)t * row;
+    const int npairs = (nq + nkv) * half;
+    const int64_t cache_row = (int64_t)pos * (int64_t)(nkv * hd);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < npairs + nkv * hd; i += gridDim.x * blockDim.x) {
+        if (i < npairs) {
+            const int head = i / half, d = i - head * half;  // heads 0..nq-1 are q, then nkv k heads
+            const float *p = base + head * hd;
+            const float c = cos_t[(int64_t)pos * half + d], s = sin_t[(int64_t)pos * half + d];
+            const float a = p[d], bb = p[d + half];
+            const float r1 = a * c - bb * s, r2 = a * s + bb * c;
+            if (head < nq) {
+                uint16_t *dst = q16 + ((int64_t)t * nq + head) * hd;
+                dst[d] = to16<BF16>(r1);
+                dst[d + half] = to16<BF16>(r2);
+            } else {
+                float *kdst = kc + cache_row + (head - nq) * hd;
+                kdst[d] = r1;
+                kdst[d + half] = r2;
+                uint16_t *dst = k16 + ((int64_t)t * nkv + (head - nq)) * hd;
+                dst[d] = to16<BF16>(r1);
+                dst[d + half] = to16<BF16>(r2);
+            }
+        } else {
+            const int j = i - npairs;  // v values
+            const float v = base[(nq + nkv) * hd + j];
+            vc[cache_row + j] = v;
+            v16[(int64_t)t * nkv * hd + j] = to16<BF16>(v);
+        }
+    }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) cast16_to_f32_kernel(const uint16_t *__restrict__ src, int64_t n, float *__restrict__ dst) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = BF16 ? __bfloat162float(__ushort_as_bfloat16(src[i])) : __half2float(__ushort_as_half(src[i]));
 }
 
 constexpr int kAttnChunk = 32;    // keys per CTA: short chunks keep many CTAs in flight at small contexts
@@ -809,6 +872,35 @@ cq_status cq_rope_store_kv(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_h
     const int work = (n_q_heads + n_kv_heads) * head_dim / 2 + n_kv_heads * head_dim;
     return launch_pdl(ctx, rope_store_kv_kernel, dim3((unsigned)((work + 255) / 256), (unsigned)batch), dim3(256), qkv_dev, n_q_heads,
                       n_kv_heads, head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx, ctx->dev_err_devptr);
+}
+
+cq_status cq_rope_prefill(cq_ctx *ctx, const float *qkv_dev, int64_t tokens, int n_q_heads, int n_kv_heads, int head_dim, const float *cos_dev,
+                          const float *sin_dev, int pos0, float *k_cache_dev, float *v_cache_dev, int max_ctx, void *q16_dev, void *k16_dev,
+                          void *v16_dev, int is_bf16) {
+    CQ_ENTER(ctx);
+    if (!qkv_dev || !cos_dev || !sin_dev || !k_cache_dev || !v_cache_dev || !q16_dev || !k16_dev || !v16_dev)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rope_prefill: null pointer");
+    if (tokens < 1 || tokens > 65535 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || head_dim < 2 || head_dim % 2 != 0 || max_ctx < 1)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rope_prefill: bad shape");
+    if (pos0 < 0 || (int64_t)pos0 + tokens > max_ctx)
+        return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_rope_prefill: positions pos0 .. pos0 + tokens - 1 must lie inside [0, max_ctx)");
+    const int work = (n_q_heads + n_kv_heads) * head_dim / 2 + n_kv_heads * head_dim;
+    const dim3 grid((unsigned)((work + 255) / 256), (unsigned)tokens);
+    if (is_bf16)
+        return launch_pdl(ctx, rope_prefill_kernel<true>, grid, dim3(256), qkv_dev, (int)tokens, n_q_heads, n_kv_heads, head_dim, cos_dev, sin_dev, pos0,
+                          k_cache_dev, v_cache_dev, static_cast<uint16_t *>(q16_dev), static_cast<uint16_t *>(k16_dev), static_cast<uint16_t *>(v16_dev));
+    return launch_pdl(ctx, rope_prefill_kernel<false>, grid, dim3(256), qkv_dev, (int)tokens, n_q_heads, n_kv_heads, head_dim, cos_dev, sin_dev, pos0,
+                      k_cache_dev, v_cache_dev, static_cast<uint16_t *>(q16_dev), static_cast<uint16_t *>(k16_dev), static_cast<uint16_t *>(v16_dev));
+}
+
+cq_status cq_cast16_to_f32(cq_ctx *ctx, const void *src16_dev, int64_t count, int is_bf16, float *dst_dev) {
+    CQ_ENTER(ctx);
+    if (!src16_dev || !dst_dev || count < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_cast16_to_f32: bad arguments");
+    if (count == 0) return CQ_OK;
+    const unsigned cap = (unsigned)ctx->sm_count * 8;
+    const unsigned grid = (unsigned)((count + 255) / 256 < cap ? (count + 255) / 256 : cap);
+    if (is_bf16) return launch_pdl(ctx, cast16_to_f32_kernel<true>, dim3(grid), dim3(256), static_cast<const uint16_t *>(src16_dev), count, dst_dev);
+    return launch_pdl(ctx, cast16_to_f32_kernel<false>, dim3(grid), dim3(256), static_cast<const uint16_t *>(src16_dev), count, dst_dev);
 }
 
 size_t cq_decode_attention_scratch_floats(int64_t batch, int n_q_heads, int head_dim, int max_ctx) {

@@ -319,6 +319,76 @@ class QuantDecoder:
             if not self._capturing:
                 self.guard.advance(1)
 
+
+    # ---- the prompt as one pass (batch 1, one GPU, with embedding and output linear) ---------------------------
+    def prefill(self, tokens, actmode: int = ACT_F16):
+        """Runs the whole prompt through the model in ONE pass instead of one decode step per token: the linears see
+        all positions at once (cq_qmatmul with m = len(tokens): tensor-core GEMMs in CQ_ACT_F16, the default here),
+        the rotary step and the KV-cache writes cover every position (cq_rope_prefill) and the causal attention of
+        the prompt runs on the tensor cores (cq_flash_attention, f16 operands).  Afterwards the caches, the position
+        and the next token are exactly where len(tokens) calls of step() would have left them (the token up to the
+        arg-max of logits that differ by the f16 roundings of this path), so step() / replay() continue from there.
+        The sequence must be empty (position 0).  Returns the number of kernel launches of the pass."""
+        cfg, lib, ctx, dev = self.cfg, self.lib, self.ctx, self.dev
+        if self.batch != 1 or self.world != 1 or not cfg.with_head or self.comm is not None:
+            raise ValueError("prefill serves a single sequence on one GPU with embedding and output linear")
+        if cfg.head_dim not in (64, 128):
+            raise ValueError("prefill attention is built for head dimensions 64 and 128")
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        T = int(toks.size)
+        if T < 1:
+            raise ValueError("prefill needs at least one token")
+        if self.guard.pos != 0:
+            raise ValueError("prefill starts an empty sequence (position 0)")
+        self.guard.need(T, "prefill")
+        hd, dim, nq, nkv = cfg.head_dim, cfg.dim, self.nq, self.nkv
+        bufs = getattr(self, "_prefill_bufs", None)
+        if bufs is None or bufs["T"] < T:
+            bufs = {"T": T, "ids": RawBuffer(dev, 4 * T), "x": dev.alloc(T * dim), "xn": dev.alloc(T * dim), "qkv": dev.alloc(T * self.qkv_rows),
+                    "q16": RawBuffer(dev, 2 * T * nq * hd), "k16": RawBuffer(dev, 2 * T * nkv * hd), "v16": RawBuffer(dev, 2 * T * nkv * hd),
+                    "o16": RawBuffer(dev, 2 * T * nq * hd), "att": dev.alloc(T * nq * hd), "o": dev.alloc(T * dim), "gu": dev.alloc(T * 2 * self.ffn),
+                    "h": dev.zeros(T * self.ffn_pad), "d": dev.alloc(T * dim), "lse": dev.alloc(nq * ((T + 127) // 128 * 128))}
+            self._prefill_bufs = bufs
+        P = bufs
+        self._check(lib.cq_memcpy_h2d(ctx, P["ids"].ptr, toks.ctypes.data_as(C.c_void_p), toks.nbytes), "prompt ids")
+        launches = 0
+
+        def linear(w, x, y):
+            self._check(lib.cq_qmatmul(ctx, w.qtype, w.order, actmode, x.ptr, T, w.k, w.k, w.buf.ptr, w.n, y.ptr, w.n), "prefill qmatmul")
+
+        self._check(lib.cq_embedding(ctx, self.embed.ptr, cfg.vocab, dim, P["ids"].ptr, T, P["x"].ptr), "embedding")
+        scale = 1.0 / float(np.sqrt(hd))
+        for li, L in enumerate(self.layers):
+            if li == 0:
+                self._check(lib.cq_rmsnorm(ctx, P["x"].ptr, L["attn_norm"].ptr, T, dim, cfg.eps, P["xn"].ptr), "rmsnorm")
+            else:
+                self._check(lib.cq_add_rmsnorm(ctx, P["x"].ptr, P["d"].ptr, L["attn_norm"].ptr, T, dim, cfg.eps, P["xn"].ptr), "add+rmsnorm")
+            linear(L["wqkv"], P["xn"], P["qkv"])
+            self._check(lib.cq_rope_prefill(ctx, P["qkv"].ptr, T, nq, nkv, hd, self.cos.ptr, self.sin.ptr, 0, L["k"].ptr, L["v"].ptr, cfg.max_ctx,
+                                            P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, 0), "rope prefill")
+            self._check(lib.cq_flash_attention(ctx, P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, P["o16"].ptr, P["lse"].ptr, None, None, None,
+                                               T * nq * hd, T * nkv * hd, T * nkv * hd, T * nq * hd, 0, nq * hd, nkv * hd, nkv * hd, nq * hd, hd, hd, hd, hd,
+                                               1, nq, nkv, hd, hd, scale, T, T, (T + 127) // 128 * 128, (T + 127) // 128 * 128, 0, 1, 0, -1, -1, 0.0),
+                        "prefill attention")
+            self._check(lib.cq_cast16_to_f32(ctx, P["o16"].ptr, T * nq * hd, 0, P["att"].ptr), "cast")
+            linear(L["wo"], P["att"], P["o"])
+            self._check(lib.cq_add_rmsnorm(ctx, P["x"].ptr, P["o"].ptr, L["ffn_norm"].ptr, T, dim, cfg.eps, P["xn"].ptr), "add+rmsnorm")
+            linear(L["wgu"], P["xn"], P["gu"])
+            self._check(lib.cq_silu_mul_pairs(ctx, P["gu"].ptr, T, self.ffn, P["h"].ptr, self.ffn_pad), "silu*mul")
+            linear(L["wdown"], P["h"], P["d"])
+            launches += 11
+        # the last position's row only: final norm, output linear (a GEMV), arg-max
+        last = 4 * (T - 1) * dim
+        x_last, d_last = C.c_void_p(P["x"].ptr.value + last), C.c_void_p(P["d"].ptr.value + last)
+        self._check(lib.cq_add_rmsnorm(ctx, x_last, d_last, self.final_norm.ptr, 1, dim, cfg.eps, self.xn.ptr), "final norm")
+        w = self.wout
+        self._check(lib.cq_qmatmul(ctx, w.qtype, w.order, ACT_F32, self.xn.ptr, 1, w.k, w.k, w.buf.ptr, w.n, self.logits.ptr, w.n), "output linear")
+        self._check(lib.cq_argmax(ctx, self.logits.ptr, 1, cfg.vocab, self.ids.ptr), "argmax")
+        pos = np.array([T], dtype=np.int32)
+        self._check(lib.cq_memcpy_h2d(ctx, self.pos.ptr, pos.ctypes.data_as(C.c_void_p), 4), "pos")
+        self.guard.pos = T
+        return launches + 5
+
     def capture(self, steps: int = 1):
         g = C.c_void_p()
         self._check(self.lib.cq_capture_begin(self.ctx), "capture begin")

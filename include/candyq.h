@@ -225,6 +225,16 @@ cq_status cq_add_rmsnorm(cq_ctx *ctx, float *x_dev, const float *delta_dev, cons
 cq_status cq_rope_store_kv(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_heads, int n_kv_heads,
                            int head_dim, const float *cos_dev, const float *sin_dev, const int *pos_dev,
                            float *k_cache_dev, float *v_cache_dev, int max_ctx);
+/* The rotary step for the prompt: rows t = 0 .. tokens-1 of qkv[tokens, (n_q + 2 n_kv) * head_dim] belong to positions
+ * pos0 + t of ONE sequence.  Same arithmetic as cq_rope_store_kv per row; rotated k and plain v go to the f32 caches
+ * [max_ctx][n_kv * head_dim] (what the decode entries read afterwards), and 16-bit copies (f16, or bf16 with is_bf16) of
+ * rotated q [tokens][n_q * head_dim], rotated k and v [tokens][n_kv * head_dim] are written for cq_flash_attention /
+ * run_mha.  pos0 is a host value: positions outside [0, max_ctx) are refused here.  qkv itself is left unrotated. */
+cq_status cq_rope_prefill(cq_ctx *ctx, const float *qkv_dev, int64_t tokens, int n_q_heads, int n_kv_heads, int head_dim, const float *cos_dev,
+                          const float *sin_dev, int pos0, float *k_cache_dev, float *v_cache_dev, int max_ctx, void *q16_dev, void *k16_dev,
+                          void *v16_dev, int is_bf16);
+/* f16 / bf16 -> f32, element by element (the attention output back into the f32 residual stream). */
+cq_status cq_cast16_to_f32(cq_ctx *ctx, const void *src16_dev, int64_t count, int is_bf16, float *dst_dev);
 /* One query per sequence against keys 0..*pos_dev of its cache: scores q.k / sqrt(head_dim),
  * softmax as FastSoftmaxF32 (reduce.go:2855-2879), weighted sum of v.  Grouped-query heads
  * (n_q_heads a multiple of n_kv_heads), head_dim <= 256.  scratch_dev needs
