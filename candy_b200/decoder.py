@@ -321,14 +321,15 @@ class QuantDecoder:
 
 
     # ---- the prompt as one pass (batch 1, one GPU, with embedding and output linear) ---------------------------
-    def prefill(self, tokens, actmode: int = ACT_F16):
+    def prefill(self, tokens, actmode: int = ACT_F16, bf16: bool = False):
         """Runs the whole prompt through the model in ONE pass instead of one decode step per token: the linears see
         all positions at once (cq_qmatmul with m = len(tokens): tensor-core GEMMs in CQ_ACT_F16, the default here),
         the rotary step and the KV-cache writes cover every position (cq_rope_prefill) and the causal attention of
         the prompt runs on the tensor cores (cq_flash_attention, f16 operands).  Afterwards the caches, the position
         and the next token are exactly where len(tokens) calls of step() would have left them (the token up to the
         arg-max of logits that differ by the f16 roundings of this path), so step() / replay() continue from there.
-        The sequence must be empty (position 0).  Returns the number of kernel launches of the pass."""
+        bf16: the attention operands are bf16 instead of f16.  The sequence must be empty (position 0).  Returns the
+        number of kernel launches of the pass."""
         cfg, lib, ctx, dev = self.cfg, self.lib, self.ctx, self.dev
         if self.batch != 1 or self.world != 1 or not cfg.with_head or self.comm is not None:
             raise ValueError("prefill serves a single sequence on one GPU with embedding and output linear")
@@ -365,12 +366,12 @@ class QuantDecoder:
                 self._check(lib.cq_add_rmsnorm(ctx, P["x"].ptr, P["d"].ptr, L["attn_norm"].ptr, T, dim, cfg.eps, P["xn"].ptr), "add+rmsnorm")
             linear(L["wqkv"], P["xn"], P["qkv"])
             self._check(lib.cq_rope_prefill(ctx, P["qkv"].ptr, T, nq, nkv, hd, self.cos.ptr, self.sin.ptr, 0, L["k"].ptr, L["v"].ptr, cfg.max_ctx,
-                                            P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, 0), "rope prefill")
+                                            P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, 1 if bf16 else 0), "rope prefill")
             self._check(lib.cq_flash_attention(ctx, P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, P["o16"].ptr, P["lse"].ptr, None, None, None,
                                                T * nq * hd, T * nkv * hd, T * nkv * hd, T * nq * hd, 0, nq * hd, nkv * hd, nkv * hd, nq * hd, hd, hd, hd, hd,
-                                               1, nq, nkv, hd, hd, scale, T, T, (T + 127) // 128 * 128, (T + 127) // 128 * 128, 0, 1, 0, -1, -1, 0.0),
+                                               1, nq, nkv, hd, hd, scale, T, T, (T + 127) // 128 * 128, (T + 127) // 128 * 128, 1 if bf16 else 0, 1, 0, -1, -1, 0.0),
                         "prefill attention")
-            self._check(lib.cq_cast16_to_f32(ctx, P["o16"].ptr, T * nq * hd, 0, P["att"].ptr), "cast")
+            self._check(lib.cq_cast16_to_f32(ctx, P["o16"].ptr, T * nq * hd, 1 if bf16 else 0, P["att"].ptr), "cast")
             linear(L["wo"], P["att"], P["o"])
             self._check(lib.cq_add_rmsnorm(ctx, P["x"].ptr, P["o"].ptr, L["ffn_norm"].ptr, T, dim, cfg.eps, P["xn"].ptr), "add+rmsnorm")
             linear(L["wgu"], P["xn"], P["gu"])

@@ -72,6 +72,19 @@ def test_prompt_in_one_pass(device, T, actmode, bar):
         assert rel_err(model.read_logits()[0], want_next) <= bar
 
 
+def test_prompt_in_one_pass_bf16_attention(device):
+    """bf16 attention operands (8 mantissa bits): the logits stay within 2e-2 of the oracle's."""
+    from candy_b200.decoder import DecoderConfig
+    cfg = DecoderConfig(n_layers=2, dim=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=1000, max_ctx=160)
+    model, ref = build(device, cfg, seed=6)
+    tokens = np.random.default_rng(9).integers(0, cfg.vocab, size=75)
+    for pos, tok in enumerate(tokens):
+        want = ref.step(int(tok), pos)
+    model.prefill(tokens, bf16=True)
+    device.synchronize()
+    assert rel_err(model.read_logits()[0], want) <= 2e-2
+
+
 def test_prefill_refuses_what_it_does_not_serve(device):
     from candy_b200.decoder import DecoderConfig
     cfg = DecoderConfig(n_layers=1, dim=256, n_heads=2, n_kv_heads=1, head_dim=128, ffn=512, vocab=100, max_ctx=16)
