@@ -69,6 +69,7 @@ SIGNATURES = {
     "cq_rope_store_kv": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int],
     "cq_rope_prefill": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _int],
     "cq_cast16_to_f32": [_vp, _vp, _i64, _int, _vp],
+    "cq_cast_f32_to_16": [_vp, _vp, _i64, _int, _vp],
     "cq_decode_attention": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _int, _vp, _vp],
     "cq_decode_attention_rope": [_vp, _vp, _i64, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp],
     "cq_silu_mul": [_vp, _vp, _i64, _i64, _vp, _i64],

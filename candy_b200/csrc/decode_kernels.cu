@@ -182,6 +182,13 @@ __global__ void __launch_bounds__(256) rope_prefill_kernel(const float *__restri
 }
 
 template <bool BF16>
+__global__ void __launch_bounds__(256) cast_f32_to_16_kernel(const float *__restrict__ src, int64_t n, uint16_t *__restrict__ dst) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = to16<BF16>(src[i]);
+}
+
+template <bool BF16>
 __global__ void __launch_bounds__(256) cast16_to_f32_kernel(const uint16_t *__restrict__ src, int64_t n, float *__restrict__ dst) {
     pdl_launch_dependents();
     pdl_wait_prior();
@@ -891,6 +898,16 @@ cq_status cq_rope_prefill(cq_ctx *ctx, const float *qkv_dev, int64_t tokens, int
                           k_cache_dev, v_cache_dev, static_cast<uint16_t *>(q16_dev), static_cast<uint16_t *>(k16_dev), static_cast<uint16_t *>(v16_dev));
     return launch_pdl(ctx, rope_prefill_kernel<false>, grid, dim3(256), qkv_dev, (int)tokens, n_q_heads, n_kv_heads, head_dim, cos_dev, sin_dev, pos0,
                       k_cache_dev, v_cache_dev, static_cast<uint16_t *>(q16_dev), static_cast<uint16_t *>(k16_dev), static_cast<uint16_t *>(v16_dev));
+}
+
+cq_status cq_cast_f32_to_16(cq_ctx *ctx, const float *src_dev, int64_t count, int is_bf16, void *dst16_dev) {
+    CQ_ENTER(ctx);
+    if (!src_dev || !dst16_dev || count < 0) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "cq_cast_f32_to_16: bad arguments");
+    if (count == 0) return CQ_OK;
+    const unsigned cap = (unsigned)ctx->sm_count * 8;
+    const unsigned grid = (unsigned)((count + 255) / 256 < cap ? (count + 255) / 256 : cap);
+    if (is_bf16) return launch_pdl(ctx, cast_f32_to_16_kernel<true>, dim3(grid), dim3(256), src_dev, count, static_cast<uint16_t *>(dst16_dev));
+    return launch_pdl(ctx, cast_f32_to_16_kernel<false>, dim3(grid), dim3(256), src_dev, count, static_cast<uint16_t *>(dst16_dev));
 }
 
 cq_status cq_cast16_to_f32(cq_ctx *ctx, const void *src16_dev, int64_t count, int is_bf16, float *dst_dev) {

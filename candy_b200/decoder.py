@@ -328,8 +328,9 @@ class QuantDecoder:
         the prompt runs on the tensor cores (cq_flash_attention, f16 operands).  Afterwards the caches, the position
         and the next token are exactly where len(tokens) calls of step() would have left them (the token up to the
         arg-max of logits that differ by the f16 roundings of this path), so step() / replay() continue from there.
-        bf16: the attention operands are bf16 instead of f16.  The sequence must be empty (position 0).  Returns the
-        number of kernel launches of the pass."""
+        bf16: the attention operands are bf16 instead of f16.  The pass may continue a sequence (a second prompt after
+        some decoding): the cached keys and values of the earlier positions are then cast to 16 bits for the attention.
+        Returns the number of kernel launches of the pass."""
         cfg, lib, ctx, dev = self.cfg, self.lib, self.ctx, self.dev
         if self.batch != 1 or self.world != 1 or not cfg.with_head or self.comm is not None:
             raise ValueError("prefill serves a single sequence on one GPU with embedding and output linear")
@@ -339,14 +340,14 @@ class QuantDecoder:
         T = int(toks.size)
         if T < 1:
             raise ValueError("prefill needs at least one token")
-        if self.guard.pos != 0:
-            raise ValueError("prefill starts an empty sequence (position 0)")
+        pos0 = int(self.guard.pos)
         self.guard.need(T, "prefill")
         hd, dim, nq, nkv = cfg.head_dim, cfg.dim, self.nq, self.nkv
+        ctx_len = pos0 + T  # keys the prompt's queries may see
         bufs = getattr(self, "_prefill_bufs", None)
-        if bufs is None or bufs["T"] < T:
-            bufs = {"T": T, "ids": RawBuffer(dev, 4 * T), "x": dev.alloc(T * dim), "xn": dev.alloc(T * dim), "qkv": dev.alloc(T * self.qkv_rows),
-                    "q16": RawBuffer(dev, 2 * T * nq * hd), "k16": RawBuffer(dev, 2 * T * nkv * hd), "v16": RawBuffer(dev, 2 * T * nkv * hd),
+        if bufs is None or bufs["T"] < T or bufs["C"] < ctx_len:
+            bufs = {"T": T, "C": ctx_len, "ids": RawBuffer(dev, 4 * T), "x": dev.alloc(T * dim), "xn": dev.alloc(T * dim), "qkv": dev.alloc(T * self.qkv_rows),
+                    "q16": RawBuffer(dev, 2 * T * nq * hd), "k16": RawBuffer(dev, 2 * ctx_len * nkv * hd), "v16": RawBuffer(dev, 2 * ctx_len * nkv * hd),
                     "o16": RawBuffer(dev, 2 * T * nq * hd), "att": dev.alloc(T * nq * hd), "o": dev.alloc(T * dim), "gu": dev.alloc(T * 2 * self.ffn),
                     "h": dev.zeros(T * self.ffn_pad), "d": dev.alloc(T * dim), "lse": dev.alloc(nq * ((T + 127) // 128 * 128))}
             self._prefill_bufs = bufs
@@ -365,11 +366,16 @@ class QuantDecoder:
             else:
                 self._check(lib.cq_add_rmsnorm(ctx, P["x"].ptr, P["d"].ptr, L["attn_norm"].ptr, T, dim, cfg.eps, P["xn"].ptr), "add+rmsnorm")
             linear(L["wqkv"], P["xn"], P["qkv"])
-            self._check(lib.cq_rope_prefill(ctx, P["qkv"].ptr, T, nq, nkv, hd, self.cos.ptr, self.sin.ptr, 0, L["k"].ptr, L["v"].ptr, cfg.max_ctx,
-                                            P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, 1 if bf16 else 0), "rope prefill")
+            if pos0 > 0:  # the earlier positions' keys and values, as the attention wants them
+                self._check(lib.cq_cast_f32_to_16(ctx, L["k"].ptr, pos0 * nkv * hd, 1 if bf16 else 0, P["k16"].ptr), "cast k")
+                self._check(lib.cq_cast_f32_to_16(ctx, L["v"].ptr, pos0 * nkv * hd, 1 if bf16 else 0, P["v16"].ptr), "cast v")
+            new16 = 2 * pos0 * nkv * hd  # this prompt's rows follow them
+            self._check(lib.cq_rope_prefill(ctx, P["qkv"].ptr, T, nq, nkv, hd, self.cos.ptr, self.sin.ptr, pos0, L["k"].ptr, L["v"].ptr, cfg.max_ctx,
+                                            P["q16"].ptr, C.c_void_p(P["k16"].ptr.value + new16), C.c_void_p(P["v16"].ptr.value + new16),
+                                            1 if bf16 else 0), "rope prefill")
             self._check(lib.cq_flash_attention(ctx, P["q16"].ptr, P["k16"].ptr, P["v16"].ptr, P["o16"].ptr, P["lse"].ptr, None, None, None,
-                                               T * nq * hd, T * nkv * hd, T * nkv * hd, T * nq * hd, 0, nq * hd, nkv * hd, nkv * hd, nq * hd, hd, hd, hd, hd,
-                                               1, nq, nkv, hd, hd, scale, T, T, (T + 127) // 128 * 128, (T + 127) // 128 * 128, 1 if bf16 else 0, 1, 0, -1, -1, 0.0),
+                                               T * nq * hd, ctx_len * nkv * hd, ctx_len * nkv * hd, T * nq * hd, 0, nq * hd, nkv * hd, nkv * hd, nq * hd, hd, hd, hd, hd,
+                                               1, nq, nkv, hd, hd, scale, T, ctx_len, (T + 127) // 128 * 128, (ctx_len + 127) // 128 * 128, 1 if bf16 else 0, 1, 0, -1, -1, 0.0),
                         "prefill attention")
             self._check(lib.cq_cast16_to_f32(ctx, P["o16"].ptr, T * nq * hd, 1 if bf16 else 0, P["att"].ptr), "cast")
             linear(L["wo"], P["att"], P["o"])
@@ -385,9 +391,9 @@ class QuantDecoder:
         w = self.wout
         self._check(lib.cq_qmatmul(ctx, w.qtype, w.order, ACT_F32, self.xn.ptr, 1, w.k, w.k, w.buf.ptr, w.n, self.logits.ptr, w.n), "output linear")
         self._check(lib.cq_argmax(ctx, self.logits.ptr, 1, cfg.vocab, self.ids.ptr), "argmax")
-        pos = np.array([T], dtype=np.int32)
+        pos = np.array([ctx_len], dtype=np.int32)
         self._check(lib.cq_memcpy_h2d(ctx, self.pos.ptr, pos.ctypes.data_as(C.c_void_p), 4), "pos")
-        self.guard.pos = T
+        self.guard.pos = ctx_len
         return launches + 5
 
     def capture(self, steps: int = 1):

@@ -233,7 +233,9 @@ cq_status cq_rope_store_kv(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_h
 cq_status cq_rope_prefill(cq_ctx *ctx, const float *qkv_dev, int64_t tokens, int n_q_heads, int n_kv_heads, int head_dim, const float *cos_dev,
                           const float *sin_dev, int pos0, float *k_cache_dev, float *v_cache_dev, int max_ctx, void *q16_dev, void *k16_dev,
                           void *v16_dev, int is_bf16);
-/* f16 / bf16 -> f32, element by element (the attention output back into the f32 residual stream). */
+/* f16 / bf16 -> f32, element by element (the attention output back into the f32 residual stream), and f32 -> f16 / bf16,
+ * round to nearest even (the cached keys and values of earlier positions, when a prompt continues a sequence). */
+cq_status cq_cast_f32_to_16(cq_ctx *ctx, const float *src_dev, int64_t count, int is_bf16, void *dst16_dev);
 cq_status cq_cast16_to_f32(cq_ctx *ctx, const void *src16_dev, int64_t count, int is_bf16, float *dst_dev);
 /* One query per sequence against keys 0..*pos_dev of its cache: scores q.k / sqrt(head_dim),
  * softmax as FastSoftmaxF32 (reduce.go:2855-2879), weighted sum of v.  Grouped-query heads

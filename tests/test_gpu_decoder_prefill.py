@@ -85,14 +85,42 @@ def test_prompt_in_one_pass_bf16_attention(device):
     assert rel_err(model.read_logits()[0], want) <= 2e-2
 
 
+def test_second_prompt_continues_the_sequence(device):
+    """A prompt, a few decoded tokens, then another prompt in one pass: the second pass attends to the cached keys and
+    values of everything before it (cast to f16) and leaves the state a token-by-token run would have."""
+    from candy_b200.decoder import DecoderConfig
+    cfg = DecoderConfig(n_layers=2, dim=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=1000, max_ctx=200)
+    model, ref = build(device, cfg, seed=7)
+    rng = np.random.default_rng(3)
+    first, second = rng.integers(0, cfg.vocab, size=50), rng.integers(0, cfg.vocab, size=90)
+    pos = 0
+    for tok in first:
+        ref.step(int(tok), pos)
+        pos += 1
+    model.prefill(first)
+    forced = rng.integers(0, cfg.vocab, size=5)
+    for tok in forced:  # a few decode steps, teacher-forced
+        model.set_state(np.array([tok], dtype=np.uint32), pos)
+        model.step()
+        ref.step(int(tok), pos)
+        pos += 1
+    for tok in second:
+        want = ref.step(int(tok), pos)
+        pos += 1
+    model.prefill(second)
+    device.synchronize()
+    assert model.guard.pos == pos
+    assert rel_err(model.read_logits()[0], want) <= 5e-3
+
+
 def test_prefill_refuses_what_it_does_not_serve(device):
     from candy_b200.decoder import DecoderConfig
     cfg = DecoderConfig(n_layers=1, dim=256, n_heads=2, n_kv_heads=1, head_dim=128, ffn=512, vocab=100, max_ctx=16)
     model, _ = build(device, cfg, seed=1)
     with pytest.raises(ValueError):
         model.prefill(np.arange(17))  # runs past max_ctx
-    model.set_state(np.array([1], dtype=np.uint32), 3)
+    model.set_state(np.array([1], dtype=np.uint32), 14)
     with pytest.raises(ValueError):
-        model.prefill(np.arange(4))  # the sequence is not empty
+        model.prefill(np.arange(4))  # 14 + 4 positions do not fit in 16
     with pytest.raises(ValueError):
         model.prefill(np.array([], dtype=np.uint32))
