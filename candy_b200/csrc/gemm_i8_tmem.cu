@@ -198,7 +198,7 @@ template <int QT, int MODE, int NC>
 __global__ void __launch_bounds__(I8Cfg<QT, NC>::kThreads, 1)
     qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const I8Params p) {
     using Cfg = I8Cfg<QT, NC>;
-    constexpr int WST = Cfg::kWStages, AST = Cfg::kAStages, BST = Cfg::kBStages, SLOTS = Cfg::kSlots, GROUP = Cfg::kGroup, EPW = Cfg::kEpWarps;
+    constexpr int WST = Cfg::kWStages, AST = Cfg::kAStages, BST = Cfg::kBStages, GROUP = Cfg::kGroup, EPW = Cfg::kEpWarps;
     constexpr int NCL = MODE == 1 ? NC : NC / 2;  // logical columns (activation rows) of the launch
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
