@@ -124,3 +124,61 @@ def test_prefill_refuses_what_it_does_not_serve(device):
         model.prefill(np.arange(4))  # 14 + 4 positions do not fit in 16
     with pytest.raises(ValueError):
         model.prefill(np.array([], dtype=np.uint32))
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_rope_prefill_equals_the_decode_rotary_step_position_by_position(device, bf16):
+    """cq_rope_prefill writes, for every prompt position, exactly the cache rows cq_rope_store_kv writes for that
+    position (bit for bit), and its 16-bit copies are the round-to-nearest-even images of the rotated f32 values."""
+    import ctypes as C
+    from candy_b200.backend import RawBuffer
+    from candy_b200.decoder import DecoderConfig, rope_tables
+    from oracle import attention_np as an
+    lib, ctx = device._lib, device.ctx
+    T, nq, nkv, hd, max_ctx, pos0 = 19, 4, 2, 128, 64, 7
+    cfg = DecoderConfig(n_layers=1, dim=nq * hd, n_heads=nq, n_kv_heads=nkv, head_dim=hd, ffn=256, vocab=10, max_ctx=max_ctx)
+    cos, sin = rope_tables(cfg)
+    dcos, dsin = device.storage_from_slice(cos), device.storage_from_slice(sin)
+    rng = np.random.default_rng(17)
+    row = (nq + 2 * nkv) * hd
+    qkv = rng.standard_normal((T, row)).astype(np.float32)
+    dqkv = device.storage_from_slice(qkv)
+    kc, vc = device.zeros(max_ctx * nkv * hd), device.zeros(max_ctx * nkv * hd)
+    q16, k16, v16 = RawBuffer(device, 2 * T * nq * hd), RawBuffer(device, 2 * T * nkv * hd), RawBuffer(device, 2 * T * nkv * hd)
+    assert lib.cq_rope_prefill(ctx, dqkv.ptr, T, nq, nkv, hd, dcos.ptr, dsin.ptr, pos0, kc.ptr, vc.ptr, max_ctx, q16.ptr, k16.ptr, v16.ptr,
+                               1 if bf16 else 0) == 0
+    device.synchronize()
+    got_k, got_v = kc.data().reshape(max_ctx, nkv * hd), vc.data().reshape(max_ctx, nkv * hd)
+    # the decode entry, one position at a time, on a copy
+    kc2, vc2 = device.zeros(max_ctx * nkv * hd), device.zeros(max_ctx * nkv * hd)
+    pos = RawBuffer(device, 4)
+    rot_q = np.empty((T, nq * hd), dtype=np.float32)
+    for t in range(T):
+        one = device.storage_from_slice(qkv[t])
+        p = np.array([pos0 + t], dtype=np.int32)
+        assert lib.cq_memcpy_h2d(ctx, pos.ptr, p.ctypes.data_as(C.c_void_p), 4) == 0
+        assert lib.cq_rope_store_kv(ctx, one.ptr, 1, nq, nkv, hd, dcos.ptr, dsin.ptr, pos.ptr, kc2.ptr, vc2.ptr, max_ctx) == 0
+        device.synchronize()
+        rot_q[t] = one.data()[: nq * hd]
+    want_k, want_v = kc2.data().reshape(max_ctx, nkv * hd), vc2.data().reshape(max_ctx, nkv * hd)
+    assert np.array_equal(got_k.view(np.uint32), want_k.view(np.uint32))
+    assert np.array_equal(got_v.view(np.uint32), want_v.view(np.uint32))
+
+    def bits16(a):
+        return an.to_bf16_bits(a) if bf16 else a.astype(np.float16).view(np.uint16)
+
+    assert np.array_equal(q16.data().view(np.uint16).reshape(T, nq * hd), bits16(rot_q))
+    assert np.array_equal(k16.data().view(np.uint16).reshape(T, nkv * hd), bits16(want_k[pos0:pos0 + T]))
+    assert np.array_equal(v16.data().view(np.uint16).reshape(T, nkv * hd), bits16(want_v[pos0:pos0 + T]))
+    # the casts: 16 -> 32 exact, 32 -> 16 round to nearest even
+    back = device.alloc(T * nkv * hd)
+    assert lib.cq_cast16_to_f32(ctx, k16.ptr, T * nkv * hd, 1 if bf16 else 0, back.ptr) == 0
+    again = RawBuffer(device, 2 * T * nkv * hd)
+    assert lib.cq_cast_f32_to_16(ctx, kc.ptr.value + 4 * pos0 * nkv * hd, T * nkv * hd, 1 if bf16 else 0, again.ptr) == 0
+    device.synchronize()
+    k_bits = k16.data().view(np.uint16)
+    want_back = an.from_bf16_bits(k_bits) if bf16 else k_bits.view(np.float16).astype(np.float32)
+    assert np.array_equal(back.data().view(np.uint32), want_back.view(np.uint32))
+    assert np.array_equal(again.data().view(np.uint16), k_bits)
+    # positions outside the cache are refused on the host
+    assert lib.cq_rope_prefill(ctx, dqkv.ptr, T, nq, nkv, hd, dcos.ptr, dsin.ptr, max_ctx - T + 1, kc.ptr, vc.ptr, max_ctx, q16.ptr, k16.ptr, v16.ptr, 0) != 0
