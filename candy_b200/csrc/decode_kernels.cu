@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace {
@@ -328,6 +330,126 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const float 
         out[0] = m;
         out[1] = l;
     }
+}
+
+// ---- decode attention in ONE launch for short contexts: a cluster of eight CTAs per (head, sequence) --------------
+// CTA `rank` of the cluster takes the 32-key chunks rank, rank + 8, ... of the context (the arithmetic of
+// attn_partial_kernel per chunk, merged into a running maximum / sum / weighted sum), leaves its partial in its own
+// shared memory, and after one cluster barrier rank 0 reads the eight partials through distributed shared memory,
+// merges them in rank order and writes the normalised output: no partials in global memory, no second kernel.
+// head_dim <= 128 (thread = dim).  With cos_t / sin_t the rotary step is fused as in attn_partial_kernel.
+constexpr int kAttnCluster = 8;
+__global__ void __launch_bounds__(kAttnThreads) attn_cluster_kernel(const float *__restrict__ qkv, int nq, int nkv, int hd,
+                                                                  const int *__restrict__ pos_dev, const float *kc, const float *vc, int max_ctx,
+                                                                  float scale, float *__restrict__ out, const float *__restrict__ cos_t,
+                                                                  const float *__restrict__ sin_t, float *kc_w, float *vc_w, int *err) {
+    namespace cg = cooperative_groups;
+    __shared__ float p_s[kAttnChunk];
+    __shared__ float part_s[kAttnThreads + 2];  // (max, sum, weighted sum per dim) of this CTA's chunks
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    cg::cluster_group cluster = cg::this_cluster();
+    const int head = blockIdx.x, b = blockIdx.y, rank = blockIdx.z;  // the cluster spans z
+    const int nkeys = checked_pos(pos_dev, max_ctx, err) + 1;
+    const int nchunks = (nkeys + kAttnChunk - 1) / kAttnChunk;
+    const int kvh = head / (nq / nkv);
+    const int row = (nq + 2 * nkv) * hd;
+    const float *q = qkv + (int64_t)b * row + head * hd;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t kv_stride = (int64_t)nkv * hd;
+    const float *kbase = kc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
+    const float *vbase = vc + ((int64_t)b * max_ctx) * kv_stride + kvh * hd;
+    const float *vnew = qkv + (int64_t)b * row + (nq + nkv + kvh) * hd;  // newest value row, straight from qkv
+    float4 qreg;
+    {
+        const int d = lane * 4;
+        qreg = (d < hd) ? *reinterpret_cast<const float4 *>(q + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cos_t && d < hd)
+            qreg = make_float4(rope_elem(q, d, hd, cos_t, sin_t, nkeys - 1), rope_elem(q, d + 1, hd, cos_t, sin_t, nkeys - 1),
+                               rope_elem(q, d + 2, hd, cos_t, sin_t, nkeys - 1), rope_elem(q, d + 3, hd, cos_t, sin_t, nkeys - 1));
+    }
+    float m_run = -3.402823466e38f, l_run = 0.0f, acc_run = 0.0f;
+    for (int chunk = rank; chunk < nchunks; chunk += kAttnCluster) {
+        const int t0 = chunk * kAttnChunk;
+        const int t1 = min(t0 + kAttnChunk, nkeys);
+        const int cnt = t1 - t0;
+        // every global load of the chunk is issued before the first use: this warp's 8 keys and this thread's 32 values of V
+        float4 kreg[8];
+        const int d4 = lane * 4;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int t = t0 + warp * 8 + j;
+            const bool newest = cos_t && t == nkeys - 1;  // not in the cache yet: comes from qkv
+            kreg[j] = (t < t1 && d4 < hd && !newest) ? *reinterpret_cast<const float4 *>(kbase + (int64_t)t * kv_stride + d4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (newest && d4 < hd) {
+                const float *kn = qkv + (int64_t)b * row + (nq + kvh) * hd;
+                kreg[j] = make_float4(rope_elem(kn, d4, hd, cos_t, sin_t, t), rope_elem(kn, d4 + 1, hd, cos_t, sin_t, t),
+                                      rope_elem(kn, d4 + 2, hd, cos_t, sin_t, t), rope_elem(kn, d4 + 3, hd, cos_t, sin_t, t));
+                if (head % (nq / nkv) == 0) *reinterpret_cast<float4 *>(kc_w + ((int64_t)b * max_ctx + t) * kv_stride + kvh * hd + d4) = kreg[j];
+            }
+        }
+        float vreg[kAttnChunk];
+#pragma unroll
+        for (int j = 0; j < kAttnChunk; ++j) {
+            const bool newest = cos_t && t0 + j == nkeys - 1;
+            vreg[j] = (j < cnt && (int)threadIdx.x < hd) ? (newest ? vnew[threadIdx.x] : vbase[(int64_t)(t0 + j) * kv_stride + threadIdx.x]) : 0.0f;
+        }
+        if (cos_t && t1 == nkeys && head % (nq / nkv) == 0)  // this chunk holds the newest key: its value row goes to the cache
+            for (int d = threadIdx.x; d < hd; d += blockDim.x) vc_w[((int64_t)b * max_ctx + nkeys - 1) * kv_stride + kvh * hd + d] = vnew[d];
+        {
+            float sc8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                sc8[j] = fmaf(qreg.x, kreg[j].x, fmaf(qreg.y, kreg[j].y, fmaf(qreg.z, kreg[j].z, qreg.w * kreg[j].w)));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sc8[j] += __shfl_xor_sync(0xffffffffu, sc8[j], o, 32);
+            if (lane < 8) {
+                float v = sc8[0];
+#pragma unroll
+                for (int j = 1; j < 8; ++j) v = (lane == j) ? sc8[j] : v;
+                p_s[warp * 8 + lane] = v * scale;
+            }
+        }
+        __syncthreads();
+        // chunk softmax numerators: every warp computes the same max / sum over the 32 scores
+        const float sc = (lane < cnt) ? p_s[lane] : -3.402823466e38f;
+        const float m = warp_max(sc);
+        const float e = (lane < cnt) ? expf(sc - m) : 0.0f;
+        const float l = warp_sum(e);
+        __syncthreads();
+        if (warp == 0) p_s[lane] = e;
+        __syncthreads();
+        float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < kAttnChunk; ++j) acc4[j & 3] = fmaf(p_s[j], vreg[j], acc4[j & 3]);
+        const float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+        // merge into the running partial
+        const float m_new = fmaxf(m_run, m);
+        const float f_old = expf(m_run - m_new), f_new = expf(m - m_new);
+        l_run = l_run * f_old + l * f_new;
+        acc_run = acc_run * f_old + acc * f_new;
+        m_run = m_new;
+        __syncthreads();  // p_s is rewritten by the next chunk
+    }
+    if (threadIdx.x == 0) part_s[0] = m_run, part_s[1] = l_run;
+    part_s[2 + threadIdx.x] = acc_run;
+    cluster.sync();
+    if (rank == 0 && (int)threadIdx.x < hd) {
+        float m = -3.402823466e38f, l = 0.0f, acc = 0.0f;
+        for (int r = 0; r < kAttnCluster; ++r) {
+            const float *ps = cluster.map_shared_rank(part_s, r);
+            const float mr = ps[0], lr = ps[1], ar = ps[2 + threadIdx.x];
+            const float m_new = fmaxf(m, mr);
+            const float f_old = expf(m - m_new), f_r = expf(mr - m_new);
+            l = l * f_old + lr * f_r;
+            acc = acc * f_old + ar * f_r;
+            m = m_new;
+        }
+        out[((int64_t)b * nq + head) * hd + threadIdx.x] = acc / l;
+    }
+    cluster.sync();  // the partials are read out of the other CTAs' shared memory: nobody leaves before that
 }
 
 // Grouped-query variant: one CTA per (kv head, sequence, chunk of 32 keys) serves all G = nq/nkv
@@ -949,6 +1071,24 @@ cq_status attention_impl(cq_ctx *ctx, float *qkv_dev, int64_t batch, int n_q_hea
                        head_dim, cos_dev, sin_dev, pos_dev, k_cache_dev, v_cache_dev, max_ctx, ctx->dev_err_devptr);
         if (s != CQ_OK) return s;
         cos_dev = sin_dev = nullptr;
+    }
+    // Short contexts, one launch: a cluster of eight CTAs per (head, sequence) splits the chunks and combines through
+    // distributed shared memory (at most four chunks per CTA; longer contexts want more CTAs than that gives).
+    if (!split_route && !gqa_chunk_route && head_dim <= kAttnThreads && max_ctx <= 4 * kAttnCluster * kAttnChunk && ctx->tune.attn_variant != 2) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_q_heads, (unsigned)batch, (unsigned)kAttnCluster);
+        cfg.blockDim = dim3(kAttnThreads);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = kAttnCluster;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ctx->tune.pdl ? 2 : 1;
+        CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_cluster_kernel, (const float *)qkv_dev, n_q_heads, n_kv_heads, head_dim, pos_dev, (const float *)k_cache_dev,
+                                        (const float *)v_cache_dev, max_ctx, scale, out_dev, cos_dev, sin_dev, k_cache_dev, v_cache_dev, ctx->dev_err_devptr));
+        return CQ_OK;
     }
     if (split_route) {
         // splits of the context sized so that about four CTAs per SM exist, never under 64 keys each

@@ -189,7 +189,10 @@ class QuantDecoder:
     def launches_per_step(self) -> int:
         if getattr(self, "_pdec", None):
             return 1
-        per_layer = 6 if self.fuse else 10  # fused: QKV(+norm), attention x2 (+rotary step), o, gate-up(+norm, +SiLU*mul), down
+        # fused: QKV(+norm), attention (+rotary step; one cluster launch for contexts up to 1024 without grouped heads, else
+        # partial + combine), o, gate-up(+norm, +SiLU*mul), down
+        one_launch_attention = self.cfg.max_ctx <= 1024 and self.cfg.head_dim <= 128 and self.nq == self.nkv
+        per_layer = (5 if one_launch_attention else 6) if self.fuse else (9 if one_launch_attention else 10)
         return self.cfg.n_layers * per_layer + ((3 if self.fuse else 5) if self.cfg.with_head else 0)
 
     # ---- the whole step as one persistent kernel (batch 1, one GPU, with embedding and output linear) -------

@@ -109,7 +109,8 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
  * CQ_ACT_F16 dequantize the raw blocks inside the GEMM instead of making an f16 copy of W; 2: at every batch size;
  * 0: never); gemm_int8 (1, default: batches of i8_min_rows_q8_1 (3) or more
  * rows in CQ_ACT_Q8_1 and of i8_min_rows_f32 (3) or more in CQ_ACT_F32 run the int8 tensor-core kernel, one
- * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant; comm_poll_limit (polls before the reducing
+ * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant (decode attention: 1 = one CTA per 32-key chunk for grouped heads instead of split contexts, 2 = never the
+ * single-launch cluster kernel of short contexts); comm_poll_limit (polls before the reducing
  * norm gives up on a peer's data, default about one second's worth); comm_cluster. */
 /* Grows the context's scratch memory to at least `bytes` now, so that no later call has to (scratch cannot
  * grow while the stream is being captured: such a call fails with CQ_ERR_INVALID_ARG and leaves the capture
