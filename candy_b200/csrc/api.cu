@@ -144,6 +144,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     if (!strcmp(key, "gemv_warps")) t.target_warps = (int)value;
     else if (!strcmp(key, "gemv_stages")) t.stages = (int)value;
     else if (!strcmp(key, "gemv_ctas_per_sm")) t.ctas_per_sm = (int)value;
+    else if (!strcmp(key, "host_zero_copy")) t.host_zero_copy = value < 0 ? 0 : value;
     else if (!strcmp(key, "gemm_pair")) t.gemm_pair = value ? 1 : 0;
     else if (!strcmp(key, "gemm_fused_dequant")) t.gemm_fused_dequant = value < 0 ? 0 : (value > 2 ? 2 : (int)value);
     else if (!strcmp(key, "gemv_early")) t.early = value ? 1 : 0;
@@ -412,9 +413,20 @@ cq_status cq_qmatmul_host(cq_ctx *ctx, int qtype, int order, int actmode, const 
         ctx->xfer_y_bytes = yb;
     }
     CQ_CUDA(ctx, cudaMemcpyAsync(ctx->xfer_x, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
-    s = cq_qmatmul(ctx, qtype, order, actmode, (const float *)ctx->xfer_x, m, k, k, w_blocks_dev, n, (float *)ctx->xfer_y, n);
+    // A result buffer in pinned host memory is written by the kernel itself (it is addressable from the device):
+    // no copy out, one submission less.  Only for the row-streaming kernels (m <= 8), which store every result
+    // once and coalesced, and only for small results: the stores cross PCIe.
+    float *y_direct = nullptr;
+    if (m <= 8 && ctx->tune.host_zero_copy > 0 && yb <= (size_t)ctx->tune.host_zero_copy) {
+        cudaPointerAttributes pa;
+        if (cudaPointerGetAttributes(&pa, y_host) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer)
+            y_direct = static_cast<float *>(pa.devicePointer);
+        else
+            cudaGetLastError();
+    }
+    s = cq_qmatmul(ctx, qtype, order, actmode, (const float *)ctx->xfer_x, m, k, k, w_blocks_dev, n, y_direct ? y_direct : (float *)ctx->xfer_y, n);
     if (s != CQ_OK) return s;
-    CQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->xfer_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!y_direct) CQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->xfer_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
     return cq_synchronize(ctx);
 }
 

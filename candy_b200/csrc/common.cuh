@@ -40,6 +40,7 @@ struct GemvTuning {
     int comm_poll_limit = 0;  // polls before the reducing norm gives up on a (value, tag) pair; 0 = about a second
     int comm_cluster = 0;     // 1: one CTA per row in the reducing norm instead of a cluster of eight
     int gemm_int8 = 1;        // 1: the int8 tensor-core kernel serves CQ_ACT_Q8_1 from i8_min_rows_q8_1 rows and CQ_ACT_F32 from i8_min_rows_f32 rows
+    int64_t host_zero_copy = 256 << 10;  // cq_qmatmul_host, m <= 8: a result of up to this many bytes whose buffer is pinned host memory is written in place (0: always copy out)
     int gemm_pair = 1;           // m > 128: 256 x 256 tiles on CTA pairs (cta_group::2) instead of 128 x 256 per CTA
     int gemm_fused_dequant = 1;  // Q4_0, m > 128: dequantize inside the f16 GEMM's producer instead of making an f16 copy of W (1: up to 384 rows, 2: always)
     int i8_min_rows_f32 = 3;

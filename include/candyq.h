@@ -111,7 +111,8 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
  * rows in CQ_ACT_Q8_1 and of i8_min_rows_f32 (3) or more in CQ_ACT_F32 run the int8 tensor-core kernel, one
  * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant (decode attention: 1 = one CTA per 32-key chunk for grouped heads instead of split contexts, 2 = never the
  * single-launch cluster kernel of short contexts); comm_poll_limit (polls before the reducing
- * norm gives up on a peer's data, default about one second's worth); comm_cluster. */
+ * norm gives up on a peer's data, default about one second's worth); comm_cluster; host_zero_copy (see
+ * cq_qmatmul_host). */
 /* Grows the context's scratch memory to at least `bytes` now, so that no later call has to (scratch cannot
  * grow while the stream is being captured: such a call fails with CQ_ERR_INVALID_ARG and leaves the capture
  * intact).  A block outgrown while graphs made by cq_capture_end exist is kept until the last of them is
@@ -183,7 +184,9 @@ cq_status cq_qlinear(cq_ctx *ctx, int qtype, int order, int actmode, const float
 
 /* Same product with HOST activations and HOST result: copies x up, runs cq_qmatmul, copies
  * y back and waits.  Weights stay resident on the device (they are the layer's state).
- * x_host / y_host should be pinned (cq_malloc_host) for full copy speed. */
+ * x_host / y_host should be pinned (cq_malloc_host) for full copy speed.  With at most eight rows and a
+ * pinned y_host of up to host_zero_copy bytes (option, default 256 KiB; 0 turns it off) the kernel stores the
+ * result into y_host directly and nothing is copied back; the bits are the same either way. */
 cq_status cq_qmatmul_host(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_host,
                           int64_t m, int64_t k, const void *w_blocks_dev, int64_t n,
                           float *y_host);

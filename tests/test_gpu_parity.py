@@ -283,6 +283,32 @@ def test_qmatmul_host_buffers(device):
     assert rel_err(y, oc.qmatmul(oc.Q4_0, 0, x, blocks, 512)) < 1e-4
 
 
+@pytest.mark.parametrize("m,n", [(1, 4096), (4, 1024), (1, 80000), (16, 512)])
+def test_qmatmul_host_pinned_result_is_written_in_place(device, m, n):
+    """A pinned result buffer gets the same bits as a pageable one, whether the kernel writes it directly (small
+    results of the row-streaming kernels) or the call copies out (large results, m > 8, or the option off)."""
+    lib, ctx = device._lib, device.ctx
+    k = 1024
+    w, x = make_case(21, n, k, m)
+    blocks = oc.quantize(oc.Q4_0, 0, w)
+    wbuf = device.upload_bytes(blocks)
+    want = np.empty((m, n), dtype=np.float32)
+    assert lib.cq_qmatmul_host(ctx, oc.Q4_0, 0, 0, x.ctypes.data_as(C.c_void_p), m, k, wbuf.ptr, n,
+                               want.ctypes.data_as(C.c_void_p)) == 0
+    py = C.c_void_p()
+    assert lib.cq_malloc_host(ctx, 4 * m * n, C.byref(py)) == 0
+    try:
+        view = np.ctypeslib.as_array(C.cast(py, C.POINTER(C.c_float)), shape=(m, n))
+        for zero_copy in (256 << 10, 0):
+            assert lib.cq_ctx_set_option(ctx, b"host_zero_copy", zero_copy) == 0
+            view[:] = np.nan
+            assert lib.cq_qmatmul_host(ctx, oc.Q4_0, 0, 0, x.ctypes.data_as(C.c_void_p), m, k, wbuf.ptr, n, py) == 0
+            assert np.array_equal(view, want)
+    finally:
+        lib.cq_ctx_set_option(ctx, b"host_zero_copy", 256 << 10)
+        lib.cq_free_host(ctx, py)
+
+
 def test_qlinear_forward_flattens_batch_dims(device):
     from candy_b200.backend import QLinear, QStorage
     rng = np.random.default_rng(4)
