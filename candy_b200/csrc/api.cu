@@ -159,6 +159,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemm_int8")) t.gemm_int8 = (int)value;
     else if (!strcmp(key, "i8_min_rows_f32")) t.i8_min_rows_f32 = (int)value;
     else if (!strcmp(key, "i8_min_rows_q8_1")) t.i8_min_rows_q8_1 = (int)value;
+    else if (!strcmp(key, "gemv_mma")) t.gemv_mma = (int)value;
     else if (!strcmp(key, "gemv_multirow")) t.gemv_multirow = (int)value;
     else if (!strcmp(key, "gemv_coop")) t.gemv_coop = (int)value;
     else if (!strcmp(key, "gemv_rpt")) t.gemv_rpt = (int)value;
@@ -336,6 +337,13 @@ cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float
     CQ_ENTER(ctx);
     cq_status s = check_matmul_args(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
     if (s != CQ_OK) return s;
+    // Two to eight rows of CQ_ACT_F32 against Q4_0: the streaming kernel with tensor-core block dots, one launch.
+    if (actmode == CQ_ACT_F32 && ctx->tune.gemv_mma > 0 && m >= ctx->tune.gemv_mma && m <= 8 && !ctx->fuse.on && ctx->push.world == 0 &&
+        ctx->tune.gemv_variant == 0 && !ctx->tune.force_simple && gemv_mma_supported(ctx, qtype, m, k, n, w_blocks_dev, x_dev, ldx)) {
+        s = launch_gemv_mma(ctx, order, x_dev, m, k, ldx, w_blocks_dev, n, ctx->bias, y_dev, ldy);
+        if (s == CQ_OK && ctx->bias) ctx->bias_done = true;
+        return s;
+    }
     // Integer dots on the tensor cores: one weight pass for the whole batch, in the activation mode's own numerics.
     if (actmode != CQ_ACT_F16 && ctx->tune.gemm_int8 && !ctx->fuse.on && ctx->push.world == 0 && ctx->tune.gemv_variant == 0 &&
         m >= (actmode == CQ_ACT_Q8_1 ? ctx->tune.i8_min_rows_q8_1 : ctx->tune.i8_min_rows_f32) &&

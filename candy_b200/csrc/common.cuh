@@ -45,6 +45,7 @@ struct GemvTuning {
     int gemm_fused_dequant = 1;  // Q4_0, m > 128: dequantize inside the f16 GEMM's producer instead of making an f16 copy of W (1: up to 384 rows, 2: always)
     int i8_min_rows_f32 = 3;
     int i8_min_rows_q8_1 = 3;
+    int gemv_mma = 3;       // CQ_ACT_F32, Q4_0: batches of this many rows up to 8 take the single-launch mma.sync kernel (0: never)
     int gemv_multirow = 1;  // 0: one launch (one weight pass) per activation row even for m = 2..8
     int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices
 };
@@ -153,6 +154,10 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const flo
                                     float *y, int64_t ldy);
 // Integer-dot GEMM on tcgen05.mma kind::i8 (gemm_i8_tmem.cu): mode 1 = Q8_1 activation columns, mode 0 = 15-bit planes.
 bool qgemm_i8_supported(int qtype, int64_t k, const void *w, const float *x, int64_t ldx);
+// Q4_0, 2..8 activation rows, CQ_ACT_F32 numerics of small batches: one launch, one weight pass (gemv_mma.cu).
+bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx);
+cq_status launch_gemv_mma(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
+                          float *y, int64_t ldy);
 cq_status launch_qgemm_i8(cq_ctx *ctx, int qtype, int order, int mode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
                           float *y, int64_t ldy);
 cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,

@@ -1,0 +1,386 @@
+// Small batches (2..8 activation rows) against Q4_0 weights in ONE weight pass and ONE launch: the weights stream
+// through a shared-memory ring exactly as in the one-row kernel, and the dot products of a quant block against all
+// activation rows are one pair of integer tensor-core instructions (mma.sync m16n8k32, u8 x s8 -> s32) instead of
+// 32 x 8 multiply-adds on the CUDA cores, so the kernel stays bound by HBM at eight rows as it is at one.
+//
+// Numerics are those of the int8 tensor-core GEMM's plane columns (gemm_i8_tmem.cu): every activation block is
+// 15-bit block fixed point, X = rint(x * 16383 / amax) = 128 * hi + lo (hi in [-128, 127], lo in [0, 127]); with the
+// unsigned nibbles n of a weight block the block's term is (d_w * amax / 16383) * (128 * sum(n * hi) + sum(n * lo)
+// - 8 * sum(X)), integer sums exact.  The reference path is QMatMul's dequantize + f32 matmul
+// (tensor/cpu_backend.go:419-481); this lands about 2e-5 of max|y| from it.
+//
+// Shape of the work:
+//   * the CTAs of a cluster of `ks` (1, 2, 4 or 8) share a range of weight rows and split k between them, so that a
+//     CTA's part of every activation row fits its registers as ready-made B fragments (16 warps x BPW blocks);
+//   * a stage of the ring is 16 weight rows (the M of the instruction) by the CTA's k slice, one bulk copy per row
+//     into a pitch that keeps the eight rows a warp reads at once in different banks;
+//   * warp w owns blocks [w * BPW, (w + 1) * BPW) of the slice.  Lane (g = lane / 4, q = lane % 4) holds, per block,
+//     four nibble bytes of weight rows g and g + 8 (A fragment: low nibbles = k positions 4q.., high nibbles =
+//     16 + 4q..) and the matching eight activation values of activation row g (B fragment).  Which four bytes a lane
+//     takes is free as long as both operands agree: odd blocks start on a word boundary (bytes 4q .. 4q + 3), even
+//     blocks start two bytes past one, so there lanes 0..2 take bytes 2 + 4q .. 5 + 4q and lane 3 bytes 0, 1, 14, 15;
+//   * the accumulator of the low-plane instruction starts at (bias + 0x4B400000): after t = 128 * S_hi + S_lo the
+//     register read as a float is 12582912 + T exactly (|T| <= 8 * 16383 * 32 < 2^22), so the conversion is one
+//     subtraction and no int-to-float instruction is on the path;
+//   * the sixteen warps' partial 16 x 8 tiles are parked in shared memory and added in warp order by a warp of its
+//     own (deterministic; the workers only arrive at a named barrier and go on with the next stage), the cluster's
+//     k slices in rank order through distributed shared memory at the end.
+// Every wait is bounded and records an error word.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int MM_WARPS = 16;       // consumer warps
+constexpr int MM_ROWS = 16;        // weight rows per stage
+constexpr int MM_MAX_STAGES = 8;
+constexpr int MM_RED_BYTES = 2 * MM_WARPS * 128 * 4;
+constexpr int MM_COLSC_BYTES = MM_WARPS * 8 * 4 * 16;  // float4 per (warp, block, q)
+constexpr int MM_THREADS = (MM_WARPS + 2) * 32;   // workers, the producer warp, the reducer warp
+constexpr int kMagicBits = 0x4B400000;  // 1.5 * 2^23 as a float
+constexpr float kMagic = 12582912.0f;
+
+struct MmaGemvParams {
+    const uint8_t *w;
+    const float *x;
+    float *y;
+    const float *bias;
+    int64_t ldx, ldy, n;
+    int nb;        // blocks per weight row
+    int m;         // activation rows (<= 8)
+    int ks;        // CTAs per cluster = k slices
+    int ranges;    // row ranges = clusters
+    int order;     // 0: interleaved nibbles (elements 2j, 2j+1 in byte j), 1: split (elements j, j+16)
+    int stages, pitch, stage_bytes;
+    int ypart_off;  // byte offset of the cluster-reduction buffer in dynamic shared memory
+    int *err;
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+
+template <int BPW, int ORDER>
+__global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bar_full[MM_MAX_STAGES];
+    __shared__ uint64_t bar_empty[MM_MAX_STAGES];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ks = p.ks > 1 ? (int)(blockIdx.x % p.ks) : 0;  // rank in the cluster (clusters are consecutive CTAs)
+    const int range = (int)(blockIdx.x / p.ks);
+    const int64_t row_begin = p.n * range / p.ranges, row_end = p.n * (range + 1) / p.ranges;
+    const int nrows = (int)(row_end - row_begin);
+    const int npass = (nrows + MM_ROWS - 1) / MM_ROWS;
+    const int units = p.nb >> 3;  // slices are cut in units of eight blocks (144 bytes: copies stay 16-byte aligned)
+    const int u0 = units * ks / p.ks, u1 = units * (ks + 1) / p.ks;
+    const int sblocks = (u1 - u0) * 8;
+    const uint32_t slice_bytes = (uint32_t)sblocks * kQ4Bytes;
+    const int64_t row_bytes = (int64_t)p.nb * kQ4Bytes;
+    float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);
+    float4 *colsc = reinterpret_cast<float4 *>(smem + (size_t)p.stages * p.stage_bytes + MM_RED_BYTES);  // [warp][block][q]
+    float *ypart = reinterpret_cast<float *>(smem + p.ypart_off);
+
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), MM_WARPS);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    if (warp == MM_WARPS) {
+        // ---- producer: the weights do not depend on the previous kernel, so the ring fills at once ----
+        const uint64_t policy = make_l2_policy_evict_first();
+        const uint8_t *src0 = p.w + row_begin * row_bytes + (int64_t)u0 * (8 * kQ4Bytes);
+        int issued = 0;
+        for (int ps = 0; ps < npass; ++ps) {
+            const int s = ps % p.stages;
+            if (ps >= p.stages && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
+                if (lane == 0) atomicExch(p.err, kDevErrEmptyWait);
+                break;
+            }
+            const int rows = min(MM_ROWS, nrows - ps * MM_ROWS);
+            if (lane == 0) mbar_expect_tx(smem_u32(&bar_full[s]), (uint32_t)rows * slice_bytes);
+            __syncwarp();
+            if (lane < rows)
+                bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes + (size_t)lane * p.pitch), src0 + (int64_t)(ps * MM_ROWS + lane) * row_bytes,
+                              slice_bytes, smem_u32(&bar_full[s]), policy);
+            issued = ps + 1;
+        }
+        // never leave with copies in flight into this CTA's shared memory
+        for (int ps = issued > p.stages ? issued - p.stages : 0; ps < issued; ++ps) {
+            if (!mbar_wait_bounded(smem_u32(&bar_full[ps % p.stages]), (ps / p.stages) & 1)) {
+                if (lane == 0) atomicExch(p.err, kDevErrDrain);
+                break;
+            }
+        }
+    } else if (warp == MM_WARPS + 1) {
+        // ---- reducer: adds the sixteen partial tiles of a pass in warp order while the others work on the next ----
+        pdl_wait_prior();
+        for (int ps = 0; ps < npass; ++ps) {
+            const int buf = ps & 1;
+            asm volatile("bar.sync %0, %1;" ::"r"(2 + buf), "n"(MM_WARPS * 32 + 32) : "memory");  // the tile is parked
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = e * 32 + lane;  // value t of the tile: lane t / 4 of the fragment, register t % 4
+                float tot = 0.0f;
+#pragma unroll
+                for (int w = 0; w < MM_WARPS; ++w) tot += red[(buf * MM_WARPS + w) * 128 + t];
+                const int l = t >> 2, c = t & 3;
+                const int wrow = ps * MM_ROWS + (l >> 2) + ((c >> 1) << 3), col = 2 * (l & 3) + (c & 1);
+                if (wrow < nrows && col < p.m) {
+                    if (p.ks > 1) ypart[wrow * 8 + col] = tot;
+                    else p.y[(int64_t)col * p.ldy + row_begin + wrow] = p.bias ? tot + p.bias[row_begin + wrow] : tot;
+                }
+            }
+            if (ps + 2 < npass) asm volatile("bar.arrive %0, %1;" ::"r"(4 + buf), "n"(MM_WARPS * 32 + 32) : "memory");  // the buffer is free again
+        }
+    } else {
+        // ---- workers ----
+        const int g = lane >> 2, q = lane & 3;
+        pdl_wait_prior();  // the activations come from the previous kernel in the stream
+
+        // B fragments of this warp's blocks for activation row g, in registers; the scale and the accumulator seed of
+        // every (block, activation row) go to shared memory, where the lane that owns result columns 2q, 2q+1 finds them.
+        uint32_t bh[BPW][2], bl[BPW][2];
+        {
+            float v[BPW][8];  // 0..3: the elements under the low nibbles of the lane's four bytes, 4..7: under the high nibbles
+#pragma unroll
+            for (int j = 0; j < BPW; ++j) {  // every load first: one trip to L2 for the whole warp's share
+                const int lb = warp * BPW + j;
+                const bool live = lb < sblocks && g < p.m;
+                const float *xb = p.x + (int64_t)(live ? g : 0) * p.ldx + (int64_t)(u0 * 8 + (lb < sblocks ? lb : 0)) * kQK;
+                // the lane's four bytes are two byte pairs, starting at bytes b0 and b1 (both even)
+                const int b0 = (j & 1) ? 4 * q : (q < 3 ? 2 + 4 * q : 0), b1 = (j & 1) ? 4 * q + 2 : (q < 3 ? 4 + 4 * q : 14);
+                if (ORDER == 0) {  // byte b holds elements 2b (low nibble) and 2b + 1: a pair of bytes is four consecutive floats
+                    const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    const float4 f0 = live ? __ldg(reinterpret_cast<const float4 *>(xb + 2 * b0)) : z;
+                    const float4 f1 = live ? __ldg(reinterpret_cast<const float4 *>(xb + 2 * b1)) : z;
+                    v[j][0] = f0.x, v[j][4] = f0.y, v[j][1] = f0.z, v[j][5] = f0.w;
+                    v[j][2] = f1.x, v[j][6] = f1.y, v[j][3] = f1.z, v[j][7] = f1.w;
+                } else {  // byte b holds elements b (low nibble) and b + 16
+                    const float2 z = make_float2(0.0f, 0.0f);
+                    const float2 l0 = live ? __ldg(reinterpret_cast<const float2 *>(xb + b0)) : z;
+                    const float2 l1 = live ? __ldg(reinterpret_cast<const float2 *>(xb + b1)) : z;
+                    const float2 h0 = live ? __ldg(reinterpret_cast<const float2 *>(xb + 16 + b0)) : z;
+                    const float2 h1 = live ? __ldg(reinterpret_cast<const float2 *>(xb + 16 + b1)) : z;
+                    v[j][0] = l0.x, v[j][1] = l0.y, v[j][2] = l1.x, v[j][3] = l1.y;
+                    v[j][4] = h0.x, v[j][5] = h0.y, v[j][6] = h1.x, v[j][7] = h1.y;
+                }
+            }
+            float *sc = reinterpret_cast<float *>(colsc + (size_t)warp * BPW * 4);
+#pragma unroll
+            for (int j = 0; j < BPW; ++j) {
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float inv = amax > 0.0f ? 16383.0f / amax : 0.0f;
+                int xsum = 0;
+                uint32_t hi[2] = {0, 0}, lo[2] = {0, 0};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int t = __float2int_rn(fminf(fmaxf(v[j][i] * inv, -16383.0f), 16383.0f));
+                    xsum += t;
+                    hi[i >> 2] |= (uint32_t)((t >> 7) & 0xFF) << (8 * (i & 3));
+                    lo[i >> 2] |= (uint32_t)(t & 0x7F) << (8 * (i & 3));
+                }
+                xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
+                xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
+                bh[j][0] = hi[0], bh[j][1] = hi[1];
+                bl[j][0] = lo[0], bl[j][1] = lo[1];
+                // float4 (block j, q') = (scale of row 2q', scale of row 2q'+1, seed of row 2q', seed of row 2q'+1)
+                if (q == 0) {
+                    float *dst = sc + (j * 4 + (g >> 1)) * 4 + (g & 1);
+                    dst[0] = amax * (1.0f / 16383.0f);
+                    dst[2] = __int_as_float(kMagicBits - 8 * xsum);
+                }
+            }
+        }
+        __syncwarp();
+
+        const uint32_t sel = q < 3 ? 0x3210u : 0x5432u;  // lane 3 of an even block: the upper half of word 0 and the lower half of word 4
+        const int word_even = q < 3 ? 1 + q : 0, word_odd = 5 + q;
+        const float4 *mysc = colsc + (size_t)warp * BPW * 4 + q;
+        const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool dead = false;
+        for (int ps = 0; ps < npass; ++ps) {
+            const int buf = ps & 1;
+            // a warp whose wait gave up keeps walking the loop so that the reducer's barriers still fill up
+            if (!dead && !mbar_wait_bounded(full0 + 8 * stage, phase)) {
+                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                dead = true;
+            }
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
+            if (!dead) {
+                const uint8_t *r0 = smem + (size_t)stage * p.stage_bytes + (size_t)g * p.pitch + (size_t)warp * (BPW * kQ4Bytes);
+                const uint8_t *r1 = r0 + 8 * (size_t)p.pitch;
+#pragma unroll
+                for (int j = 0; j < BPW; j += 2) {
+                    if (warp * BPW + j < sblocks) {  // slices are multiples of eight blocks: a pair is whole or absent
+                        const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0 + j * kQ4Bytes);  // 36-byte pairs: word aligned
+                        const uint32_t *p1 = reinterpret_cast<const uint32_t *>(r1 + j * kQ4Bytes);
+                        const uint32_t h0 = p0[0], t0 = p0[4], e0 = p0[word_even], o0 = p0[word_odd];
+                        const uint32_t h1 = p1[0], t1 = p1[4], e1 = p1[word_even], o1 = p1[word_odd];
+                        const uint32_t wv[2][2] = {{__byte_perm(e0, t0, sel), __byte_perm(e1, t1, sel)}, {o0, o1}};
+                        const float dw[2][2] = {{__half2float(__ushort_as_half((unsigned short)(h0 & 0xFFFFu))),
+                                                 __half2float(__ushort_as_half((unsigned short)(h1 & 0xFFFFu)))},
+                                                {__half2float(__ushort_as_half((unsigned short)(t0 >> 16))),
+                                                 __half2float(__ushort_as_half((unsigned short)(t1 >> 16)))}};
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            const float4 cs = mysc[(j + b) * 4];
+                            const int s0 = __float_as_int(cs.z), s1 = __float_as_int(cs.w);
+                            const uint32_t a[4] = {wv[b][0] & 0x0F0F0F0Fu, wv[b][1] & 0x0F0F0F0Fu, (wv[b][0] >> 4) & 0x0F0F0F0Fu,
+                                                   (wv[b][1] >> 4) & 0x0F0F0F0Fu};
+                            int sh[4], sl[4];
+                            mma_u8s8(sh, a, bh[j + b][0], bh[j + b][1], 0, 0, 0, 0);
+                            mma_u8s8(sl, a, bl[j + b][0], bl[j + b][1], s0, s1, s0, s1);
+                            acc[0] = fmaf(dw[b][0] * cs.x, __int_as_float(sh[0] * 128 + sl[0]) - kMagic, acc[0]);
+                            acc[1] = fmaf(dw[b][0] * cs.y, __int_as_float(sh[1] * 128 + sl[1]) - kMagic, acc[1]);
+                            acc[2] = fmaf(dw[b][1] * cs.x, __int_as_float(sh[2] * 128 + sl[2]) - kMagic, acc[2]);
+                            acc[3] = fmaf(dw[b][1] * cs.y, __int_as_float(sh[3] * 128 + sl[3]) - kMagic, acc[3]);
+                        }
+                    }
+                }
+            }
+            // The tile of pass ps - 2 has left this buffer once the reducer says so.  The partial tile depends on every
+            // word read from the stage, so the stage can be released once it is parked.
+            if (ps >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + buf), "n"(MM_WARPS * 32 + 32) : "memory");
+            reinterpret_cast<float4 *>(red)[(buf * MM_WARPS + warp) * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+            asm volatile("bar.arrive %0, %1;" ::"r"(2 + buf), "n"(MM_WARPS * 32 + 32) : "memory");
+            if (++stage == p.stages) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+    }
+
+    if (p.ks > 1) {
+        // add the cluster's k slices in rank order; every rank finishes the rows r with r % ks == its rank
+        cg::cluster_group cluster = cg::this_cluster();
+        pdl_wait_prior();  // the producer warp writes results below and has not waited yet
+        cluster.sync();
+        for (int i = tid; i < nrows * 8; i += MM_THREADS) {
+            const int wrow = i >> 3, col = i & 7;
+            if (col < p.m && wrow % p.ks == ks) {
+                float tot = 0.0f;
+                for (int r = 0; r < p.ks; ++r) tot += cluster.map_shared_rank(ypart, r)[i];
+                p.y[(int64_t)col * p.ldy + row_begin + wrow] = p.bias ? tot + p.bias[row_begin + wrow] : tot;
+            }
+        }
+        cluster.sync();  // nobody leaves while its shared memory may still be read
+    }
+}
+
+template <int BPW, int ORDER>
+cq_status run_mma_o(cq_ctx *ctx, const MmaGemvParams &p, int grid, size_t smem) {
+    auto kern = gemv_mma_kernel<BPW, ORDER>;
+    static thread_local size_t configured = 0;
+    static thread_local int configured_dev = -1;
+    if (configured < smem || configured_dev != ctx->device) {
+        CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem, configured_dev = ctx->device;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(MM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (p.ks > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)p.ks, attr[na].val.clusterDim.y = 1, attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (ctx->tune.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+    return CQ_OK;
+}
+
+template <int BPW>
+cq_status run_mma(cq_ctx *ctx, const MmaGemvParams &p, int grid, size_t smem) {
+    return p.order == 0 ? run_mma_o<BPW, 0>(ctx, p, grid, smem) : run_mma_o<BPW, 1>(ctx, p, grid, smem);
+}
+
+struct MmaPlan {
+    int ks, bpw, ranges, stages, pitch, stage_bytes, ypart_off;
+    size_t smem;
+};
+
+bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, MmaPlan &pl) {
+    const int nb = (int)(k / kQK), units = nb / 8;
+    for (int ks = 1; ks <= 8; ks *= 2) {
+        if (ks > units) return false;
+        const int max_blocks = ((units + ks - 1) / ks) * 8;
+        if (max_blocks > MM_WARPS * 8) continue;
+        int bpw = (max_blocks + MM_WARPS - 1) / MM_WARPS;
+        bpw += bpw & 1;
+        const int ranges = ctx->sm_count / ks;
+        if (ranges < 1) return false;
+        // eight rows read at once must fall in different banks: pitch = 16 (mod 32) bytes
+        const int slice = max_blocks * kQ4Bytes;
+        const int pitch = (slice % 32 == 16) ? slice : slice + 16;
+        const int stage_bytes = MM_ROWS * pitch;
+        const int rows_max = (int)((n + ranges - 1) / ranges);
+        const int ypart = ks > 1 ? ((rows_max + MM_ROWS) * 8 * 4) : 0;
+        const int budget = 225 * 1024 - MM_RED_BYTES - MM_COLSC_BYTES - ypart;
+        int stages = budget / stage_bytes;
+        if (stages > MM_MAX_STAGES) stages = MM_MAX_STAGES;
+        if (stages < 2) return false;
+        pl.ks = ks, pl.bpw = bpw, pl.ranges = ranges, pl.stages = stages, pl.pitch = pitch, pl.stage_bytes = stage_bytes;
+        pl.ypart_off = stages * stage_bytes + MM_RED_BYTES + MM_COLSC_BYTES;
+        pl.smem = (size_t)pl.ypart_off + ypart;
+        return true;
+    }
+    return false;
+}
+
+}  // namespace
+
+bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx) {
+    MmaPlan pl;
+    return qtype == CQ_Q4_0 && m >= 2 && m <= 8 && k % 256 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 4 == 0 && plan_mma(ctx, k, n, pl);
+}
+
+cq_status launch_gemv_mma(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
+                          float *y, int64_t ldy) {
+    MmaPlan pl;
+    if (!plan_mma(ctx, k, n, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: shape not supported");
+    MmaGemvParams p;
+    p.w = static_cast<const uint8_t *>(w);
+    p.x = x, p.y = y, p.bias = bias;
+    p.ldx = ldx, p.ldy = ldy, p.n = n;
+    p.nb = (int)(k / kQK), p.m = (int)m, p.ks = pl.ks, p.ranges = pl.ranges, p.order = order == CQ_ORDER_GGML_SPLIT ? 1 : 0;
+    p.stages = pl.stages, p.pitch = pl.pitch, p.stage_bytes = pl.stage_bytes, p.ypart_off = pl.ypart_off;
+    p.err = ctx->dev_err_devptr;
+    const int grid = pl.ranges * pl.ks;
+    switch (pl.bpw) {
+    case 2: return run_mma<2>(ctx, p, grid, pl.smem);
+    case 4: return run_mma<4>(ctx, p, grid, pl.smem);
+    case 6: return run_mma<6>(ctx, p, grid, pl.smem);
+    default: return run_mma<8>(ctx, p, grid, pl.smem);
+    }
+}

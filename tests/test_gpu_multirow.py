@@ -14,10 +14,12 @@ QT_ORDERS = [(oc.Q4_0, 0), (oc.Q4_0, 1), (oc.Q8_0, 0)]
 
 @pytest.fixture(autouse=True)
 def _decode_kernels_only(device):
-    """These tests are about the multi-row streaming GEMV: keep the int8 tensor-core kernel out of the way."""
+    """These tests are about the multi-row streaming GEMV: keep the tensor-core kernels out of the way."""
     device.set_option("gemm_int8", 0)
+    device.set_option("gemv_mma", 0)
     yield
     device.set_option("gemm_int8", 1)
+    device.set_option("gemv_mma", 3)
 
 
 def run(device, qt, order, x, blocks, n, actmode, ldx=None, ldy=None, bias=None):
