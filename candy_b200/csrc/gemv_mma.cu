@@ -27,6 +27,7 @@
 //     k slices in rank order through distributed shared memory at the end.
 // Every wait is bounded and records an error word.
 #include <cooperative_groups.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
@@ -38,7 +39,7 @@ constexpr int MM_WARPS = 16;       // consumer warps
 constexpr int MM_ROWS = 16;        // weight rows per stage
 constexpr int MM_MAX_STAGES = 8;
 constexpr int MM_RED_BYTES = 2 * MM_WARPS * 128 * 4;
-constexpr int MM_COLSC_BYTES = MM_WARPS * 8 * 4 * 16;  // float4 per (warp, block, q)
+constexpr int MM_COLSC_BYTES = MM_WARPS * 8 * 4 * 32;  // per (warp, block, q): the accumulator seeds as a ready quad, then the two scales
 constexpr int MM_THREADS = (MM_WARPS + 2) * 32;   // workers, the producer warp, the reducer warp
 constexpr int kMagicBits = 0x4B400000;  // 1.5 * 2^23 as a float
 constexpr float kMagic = 12582912.0f;
@@ -65,6 +66,30 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], ui
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
 }
 
+// Packed pairs of f32 in a 64-bit register: sm_100 adds, multiplies and fuses two at a time.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t dup2(float v) { return pack2(v, v); }
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 template <int BPW, int ORDER>
 __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -83,7 +108,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
     const uint32_t slice_bytes = (uint32_t)sblocks * kQ4Bytes;
     const int64_t row_bytes = (int64_t)p.nb * kQ4Bytes;
     float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);
-    float4 *colsc = reinterpret_cast<float4 *>(smem + (size_t)p.stages * p.stage_bytes + MM_RED_BYTES);  // [warp][block][q]
+    float4 *colsc = reinterpret_cast<float4 *>(smem + (size_t)p.stages * p.stage_bytes + MM_RED_BYTES);  // [warp][block][q] entries of 32 bytes
     float *ypart = reinterpret_cast<float *>(smem + p.ypart_off);
 
     pdl_launch_dependents();
@@ -177,7 +202,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                     v[j][4] = h0.x, v[j][5] = h0.y, v[j][6] = h1.x, v[j][7] = h1.y;
                 }
             }
-            float *sc = reinterpret_cast<float *>(colsc + (size_t)warp * BPW * 4);
+            float *sc = reinterpret_cast<float *>(colsc) + (size_t)warp * BPW * 32;
 #pragma unroll
             for (int j = 0; j < BPW; ++j) {
                 float amax = 0.0f;
@@ -190,7 +215,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                 uint32_t hi[2] = {0, 0}, lo[2] = {0, 0};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int t = __float2int_rn(fminf(fmaxf(v[j][i] * inv, -16383.0f), 16383.0f));
+                    const int t = __float2int_rn(v[j][i] * inv);  // |v * inv| <= 16383 * (1 + 2^-23): never rounds to 16384
                     xsum += t;
                     hi[i >> 2] |= (uint32_t)((t >> 7) & 0xFF) << (8 * (i & 3));
                     lo[i >> 2] |= (uint32_t)(t & 0x7F) << (8 * (i & 3));
@@ -199,19 +224,21 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                 xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
                 bh[j][0] = hi[0], bh[j][1] = hi[1];
                 bl[j][0] = lo[0], bl[j][1] = lo[1];
-                // float4 (block j, q') = (scale of row 2q', scale of row 2q'+1, seed of row 2q', seed of row 2q'+1)
+                // entry (block j, q') of 8 words = (seed of row 2q', seed of row 2q'+1, the same two again: the accumulator
+                // quad of the low-plane instruction as one 16-byte load), (scale of row 2q', scale of row 2q'+1), padding
                 if (q == 0) {
-                    float *dst = sc + (j * 4 + (g >> 1)) * 4 + (g & 1);
-                    dst[0] = amax * (1.0f / 16383.0f);
-                    dst[2] = __int_as_float(kMagicBits - 8 * xsum);
+                    float *dst = sc + (j * 4 + (g >> 1)) * 8 + (g & 1);
+                    dst[0] = dst[2] = __int_as_float(kMagicBits - 8 * xsum);
+                    dst[4] = amax * (1.0f / 16383.0f);
                 }
             }
         }
         __syncwarp();
 
+        const uint64_t neg_magic = dup2(-kMagic);
         const uint32_t sel = q < 3 ? 0x3210u : 0x5432u;  // lane 3 of an even block: the upper half of word 0 and the lower half of word 4
         const int word_even = q < 3 ? 1 + q : 0, word_odd = 5 + q;
-        const float4 *mysc = colsc + (size_t)warp * BPW * 4 + q;
+        const float *mysc = reinterpret_cast<const float *>(colsc) + ((size_t)warp * BPW * 4 + q) * 8;
         const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
         int stage = 0;
         uint32_t phase = 0;
@@ -223,39 +250,47 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
                 dead = true;
             }
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
+            uint64_t acc01 = 0, acc23 = 0;  // packed f32 pairs: (row g, col 2q), (g, 2q+1) and (g+8, 2q), (g+8, 2q+1)
             if (!dead) {
-                const uint8_t *r0 = smem + (size_t)stage * p.stage_bytes + (size_t)g * p.pitch + (size_t)warp * (BPW * kQ4Bytes);
-                const uint8_t *r1 = r0 + 8 * (size_t)p.pitch;
+                // word pointers of weight rows g and g + 8 at this warp's first block: the head word of a pair of blocks
+                // (scale of the even block, its bytes 0, 1), the lane's word of the even block and of the odd block
+                const uint32_t *h0p = reinterpret_cast<const uint32_t *>(smem + (size_t)stage * p.stage_bytes + (size_t)g * p.pitch + (size_t)warp * (BPW * kQ4Bytes));
+                const uint32_t *h1p = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(h0p) + 8 * (size_t)p.pitch);
+                const uint32_t *e0p = h0p + word_even, *e1p = h1p + word_even, *o0p = h0p + word_odd, *o1p = h1p + word_odd;
 #pragma unroll
                 for (int j = 0; j < BPW; j += 2) {
                     if (warp * BPW + j < sblocks) {  // slices are multiples of eight blocks: a pair is whole or absent
-                        const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0 + j * kQ4Bytes);  // 36-byte pairs: word aligned
-                        const uint32_t *p1 = reinterpret_cast<const uint32_t *>(r1 + j * kQ4Bytes);
-                        const uint32_t h0 = p0[0], t0 = p0[4], e0 = p0[word_even], o0 = p0[word_odd];
-                        const uint32_t h1 = p1[0], t1 = p1[4], e1 = p1[word_even], o1 = p1[word_odd];
+                        constexpr int kPairWords = 2 * kQ4Bytes / 4;  // a pair of blocks is nine words
+                        const int wo = (j / 2) * kPairWords;
+                        const uint32_t h0 = h0p[wo], t0 = h0p[wo + 4], e0 = e0p[wo], o0 = o0p[wo];
+                        const uint32_t h1 = h1p[wo], t1 = h1p[wo + 4], e1 = e1p[wo], o1 = o1p[wo];
                         const uint32_t wv[2][2] = {{__byte_perm(e0, t0, sel), __byte_perm(e1, t1, sel)}, {o0, o1}};
-                        const float dw[2][2] = {{__half2float(__ushort_as_half((unsigned short)(h0 & 0xFFFFu))),
-                                                 __half2float(__ushort_as_half((unsigned short)(h1 & 0xFFFFu)))},
-                                                {__half2float(__ushort_as_half((unsigned short)(t0 >> 16))),
-                                                 __half2float(__ushort_as_half((unsigned short)(t1 >> 16)))}};
+                        // scales of (even block, odd block) x (row g, row g + 8), each twice in a register pair
+                        const uint64_t dw[2][2] = {{dup2(__low2float(*reinterpret_cast<const __half2 *>(&h0))),
+                                                    dup2(__low2float(*reinterpret_cast<const __half2 *>(&h1)))},
+                                                   {dup2(__high2float(*reinterpret_cast<const __half2 *>(&t0))),
+                                                    dup2(__high2float(*reinterpret_cast<const __half2 *>(&t1)))}};
 #pragma unroll
                         for (int b = 0; b < 2; ++b) {
-                            const float4 cs = mysc[(j + b) * 4];
-                            const int s0 = __float_as_int(cs.z), s1 = __float_as_int(cs.w);
+                            const int4 sd = *reinterpret_cast<const int4 *>(mysc + (j + b) * 32);
+                            const uint64_t csxy = *reinterpret_cast<const uint64_t *>(mysc + (j + b) * 32 + 4);
                             const uint32_t a[4] = {wv[b][0] & 0x0F0F0F0Fu, wv[b][1] & 0x0F0F0F0Fu, (wv[b][0] >> 4) & 0x0F0F0F0Fu,
                                                    (wv[b][1] >> 4) & 0x0F0F0F0Fu};
                             int sh[4], sl[4];
                             mma_u8s8(sh, a, bh[j + b][0], bh[j + b][1], 0, 0, 0, 0);
-                            mma_u8s8(sl, a, bl[j + b][0], bl[j + b][1], s0, s1, s0, s1);
-                            acc[0] = fmaf(dw[b][0] * cs.x, __int_as_float(sh[0] * 128 + sl[0]) - kMagic, acc[0]);
-                            acc[1] = fmaf(dw[b][0] * cs.y, __int_as_float(sh[1] * 128 + sl[1]) - kMagic, acc[1]);
-                            acc[2] = fmaf(dw[b][1] * cs.x, __int_as_float(sh[2] * 128 + sl[2]) - kMagic, acc[2]);
-                            acc[3] = fmaf(dw[b][1] * cs.y, __int_as_float(sh[3] * 128 + sl[3]) - kMagic, acc[3]);
+                            mma_u8s8(sl, a, bl[j + b][0], bl[j + b][1], sd.x, sd.y, sd.z, sd.w);
+                            // two results per instruction (packed f32): (T - magic) * (activation scales), then * weight scale
+                            const uint64_t u01 = mul2(add2(pack2(__int_as_float(sh[0] * 128 + sl[0]), __int_as_float(sh[1] * 128 + sl[1])), neg_magic), csxy);
+                            const uint64_t u23 = mul2(add2(pack2(__int_as_float(sh[2] * 128 + sl[2]), __int_as_float(sh[3] * 128 + sl[3])), neg_magic), csxy);
+                            acc01 = fma2(dw[b][0], u01, acc01);
+                            acc23 = fma2(dw[b][1], u23, acc23);
                         }
                     }
                 }
             }
+            float acc[4];
+            unpack2(acc01, acc[0], acc[1]);
+            unpack2(acc23, acc[2], acc[3]);
             // The tile of pass ps - 2 has left this buffer once the reducer says so.  The partial tile depends on every
             // word read from the stage, so the stage can be released once it is parked.
             if (ps >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + buf), "n"(MM_WARPS * 32 + 32) : "memory");
@@ -287,49 +322,13 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
     }
 }
 
-template <int BPW, int ORDER>
-cq_status run_mma_o(cq_ctx *ctx, const MmaGemvParams &p, int grid, size_t smem) {
-    auto kern = gemv_mma_kernel<BPW, ORDER>;
-    static thread_local size_t configured = 0;
-    static thread_local int configured_dev = -1;
-    if (configured < smem || configured_dev != ctx->device) {
-        CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem, configured_dev = ctx->device;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(MM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (p.ks > 1) {
-        attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)p.ks, attr[na].val.clusterDim.y = 1, attr[na].val.clusterDim.z = 1;
-        ++na;
-    }
-    if (ctx->tune.pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
-    return CQ_OK;
-}
-
-template <int BPW>
-cq_status run_mma(cq_ctx *ctx, const MmaGemvParams &p, int grid, size_t smem) {
-    return p.order == 0 ? run_mma_o<BPW, 0>(ctx, p, grid, smem) : run_mma_o<BPW, 1>(ctx, p, grid, smem);
-}
-
 struct MmaPlan {
     int ks, bpw, ranges, stages, pitch, stage_bytes, ypart_off;
     size_t smem;
 };
 
-bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, MmaPlan &pl) {
+// ranges = 0: one row range per group of ks SMs; otherwise that many row ranges.
+bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, int ranges, MmaPlan &pl) {
     const int nb = (int)(k / kQK), units = nb / 8;
     for (int ks = 1; ks <= 8; ks *= 2) {
         if (ks > units) return false;
@@ -337,7 +336,7 @@ bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, MmaPlan &pl) {
         if (max_blocks > MM_WARPS * 8) continue;
         int bpw = (max_blocks + MM_WARPS - 1) / MM_WARPS;
         bpw += bpw & 1;
-        const int ranges = ctx->sm_count / ks;
+        if (ranges <= 0) ranges = ctx->sm_count / ks;
         if (ranges < 1) return false;
         // eight rows read at once must fall in different banks: pitch = 16 (mod 32) bytes
         const int slice = max_blocks * kQ4Bytes;
@@ -357,30 +356,79 @@ bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, MmaPlan &pl) {
     return false;
 }
 
+template <int BPW, int ORDER>
+cq_status run_mma_o(cq_ctx *ctx, MmaGemvParams p, MmaPlan pl, int64_t k) {
+    auto kern = gemv_mma_kernel<BPW, ORDER>;
+    static thread_local size_t configured = 0;
+    static thread_local int configured_dev = -1;
+    static thread_local std::map<std::pair<int, size_t>, int> resident;  // (cluster size, shared memory) -> clusters resident at once
+    if (configured_dev != ctx->device) configured = 0, resident.clear(), configured_dev = ctx->device;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[2];
+    for (int round = 0; round < 3; ++round) {
+        if (configured < pl.smem) {
+            CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+            configured = pl.smem;
+        }
+        cfg.gridDim = dim3((unsigned)(pl.ranges * pl.ks));
+        cfg.blockDim = dim3(MM_THREADS);
+        cfg.dynamicSmemBytes = pl.smem;
+        cfg.stream = ctx->stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = 0;
+        if (pl.ks == 1) break;
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)pl.ks, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+        cfg.numAttrs = 1;
+        // Every cluster must be resident at once: the SMs of a GPC do not always divide by the cluster size, and a second
+        // wave of a few clusters would double the time.  Fewer, longer row ranges instead.
+        const auto key = std::make_pair(pl.ks, pl.smem);
+        auto it = resident.find(key);
+        if (it == resident.end()) {
+            int nc = 0;
+            CQ_CUDA(ctx, cudaOccupancyMaxActiveClusters(&nc, kern, &cfg));
+            it = resident.emplace(key, nc).first;
+        }
+        if (it->second >= pl.ranges) break;
+        if (it->second < 1 || !plan_mma(ctx, k, p.n, it->second, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: clusters do not fit");
+    }
+    p.ks = pl.ks, p.ranges = pl.ranges, p.stages = pl.stages, p.pitch = pl.pitch, p.stage_bytes = pl.stage_bytes, p.ypart_off = pl.ypart_off;
+    if (ctx->tune.pdl) {
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        ++cfg.numAttrs;
+    }
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+    return CQ_OK;
+}
+
+template <int BPW>
+cq_status run_mma(cq_ctx *ctx, const MmaGemvParams &p, const MmaPlan &pl, int64_t k) {
+    return p.order == 0 ? run_mma_o<BPW, 0>(ctx, p, pl, k) : run_mma_o<BPW, 1>(ctx, p, pl, k);
+}
+
 }  // namespace
 
 bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx) {
     MmaPlan pl;
     return qtype == CQ_Q4_0 && m >= 2 && m <= 8 && k % 256 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
-           (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 4 == 0 && plan_mma(ctx, k, n, pl);
+           (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 4 == 0 && plan_mma(ctx, k, n, 0, pl);
 }
 
 cq_status launch_gemv_mma(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
                           float *y, int64_t ldy) {
     MmaPlan pl;
-    if (!plan_mma(ctx, k, n, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: shape not supported");
-    MmaGemvParams p;
+    if (!plan_mma(ctx, k, n, 0, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: shape not supported");
+    MmaGemvParams p = {};
     p.w = static_cast<const uint8_t *>(w);
     p.x = x, p.y = y, p.bias = bias;
     p.ldx = ldx, p.ldy = ldy, p.n = n;
-    p.nb = (int)(k / kQK), p.m = (int)m, p.ks = pl.ks, p.ranges = pl.ranges, p.order = order == CQ_ORDER_GGML_SPLIT ? 1 : 0;
-    p.stages = pl.stages, p.pitch = pl.pitch, p.stage_bytes = pl.stage_bytes, p.ypart_off = pl.ypart_off;
+    p.nb = (int)(k / kQK), p.m = (int)m, p.order = order == CQ_ORDER_GGML_SPLIT ? 1 : 0;
     p.err = ctx->dev_err_devptr;
-    const int grid = pl.ranges * pl.ks;
-    switch (pl.bpw) {
-    case 2: return run_mma<2>(ctx, p, grid, pl.smem);
-    case 4: return run_mma<4>(ctx, p, grid, pl.smem);
-    case 6: return run_mma<6>(ctx, p, grid, pl.smem);
-    default: return run_mma<8>(ctx, p, grid, pl.smem);
+    switch (pl.bpw) {  // the plan may still change its row ranges and stages, never its k slices
+    case 2: return run_mma<2>(ctx, p, pl, k);
+    case 4: return run_mma<4>(ctx, p, pl, k);
+    case 6: return run_mma<6>(ctx, p, pl, k);
+    default: return run_mma<8>(ctx, p, pl, k);
     }
 }
