@@ -138,8 +138,8 @@ def small_batch(dev, peak_gbs: float, ms_rows=(1, 2, 4, 8), n: int = 11008, k: i
     """Decode-side batches (m = 1 .. 8 activation rows against one Q4_0 weight, n = 11008, k = 4096) in the two
     decode numerics, CQ_ACT_F32 and CQ_ACT_Q8_1: the whole cq_qmatmul call, timed as replays of a CUDA graph of
     `calls` calls that cycle through eight copies of the weight.  One pass over the weights serves every row:
-    m = 1 the streaming GEMV, m = 2 its two-row form; m = 3..8 in CQ_ACT_F32 the single-launch kernel with mma.sync block
-    dots, in CQ_ACT_Q8_1 the int8 tensor-core kernel (Q8_1 columns)."""
+    m = 1 the streaming GEMV, m = 2 its two-row form; m = 3..8 the single-launch kernel with mma.sync block dots
+    (plane or Q8_1 columns)."""
     from .backend import QStorage
     lib, ctx = dev._lib, dev.ctx
     rng = np.random.default_rng(seed)
@@ -181,7 +181,8 @@ def small_batch(dev, peak_gbs: float, ms_rows=(1, 2, 4, 8), n: int = 11008, k: i
             out.append({"actmode": actname, "m": m, "us": round(t * 1e6, 2), "algorithmic_gbs": round(nbytes / t / 1e9, 1),
                         "frac_of_hbm_peak": round(nbytes / t / 1e9 / peak_gbs, 4),
                         "path": "streaming GEMV" if m == 1 else (
-                            "streaming kernel with mma.sync block dots, one launch" if act == 0 and (m >= 3 or n * k >= 40 << 20) and m <= 8 and k % 256 == 0
+                            "streaming kernel with mma.sync block dots, one launch" if m <= 8 and k % 256 == 0 and (
+                                m >= 3 or (n * k >= 40 << 20 if act == 0 else (k >= 8192 or n * k >= 100 << 20)))
                             else ("two-row streaming GEMV" if m == 2 else "int8 tcgen05 kernel"))})
             del x, y
     del ring, first

@@ -337,11 +337,12 @@ cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float
     CQ_ENTER(ctx);
     cq_status s = check_matmul_args(ctx, qtype, order, actmode, x_dev, m, k, ldx, w_blocks_dev, n, y_dev, ldy);
     if (s != CQ_OK) return s;
-    // Two to eight rows of CQ_ACT_F32 against Q4_0: the streaming kernel with tensor-core block dots, one launch.
-    // (two rows only against large weights: below about 20 MB the two-row form of the one-row kernel is quicker)
-    if (actmode == CQ_ACT_F32 && ctx->tune.gemv_mma > 0 && (m >= ctx->tune.gemv_mma || (m == 2 && n * k >= (int64_t(40) << 20))) && m <= 8 && !ctx->fuse.on && ctx->push.world == 0 &&
-        ctx->tune.gemv_variant == 0 && !ctx->tune.force_simple && gemv_mma_supported(ctx, qtype, m, k, n, w_blocks_dev, x_dev, ldx)) {
-        s = launch_gemv_mma(ctx, order, x_dev, m, k, ldx, w_blocks_dev, n, ctx->bias, y_dev, ldy);
+    // Two to eight rows against Q4_0 in CQ_ACT_F32 or CQ_ACT_Q8_1: the streaming kernel with tensor-core block dots, one launch
+    // (two rows only against large weights, or in CQ_ACT_Q8_1 long rows: elsewhere the two-row form of the one-row kernel is quicker)
+    if (actmode != CQ_ACT_F16 && ctx->tune.gemv_mma > 0 && (m >= ctx->tune.gemv_mma || (m == 2 && (actmode == CQ_ACT_Q8_1 ? (k >= 8192 || n * k >= (int64_t(100) << 20)) : n * k >= (int64_t(40) << 20)))) && m <= 8 &&
+        !ctx->fuse.on && ctx->push.world == 0 && ctx->tune.gemv_variant == 0 && !ctx->tune.force_simple &&
+        gemv_mma_supported(ctx, qtype, m, k, n, w_blocks_dev, x_dev, ldx)) {
+        s = launch_gemv_mma(ctx, order, actmode == CQ_ACT_Q8_1, x_dev, m, k, ldx, w_blocks_dev, n, ctx->bias, y_dev, ldy);
         if (s == CQ_OK && ctx->bias) ctx->bias_done = true;
         return s;
     }

@@ -154,9 +154,10 @@ cq_status launch_qgemm_dequant_tmem(cq_ctx *ctx, int qtype, int order, const flo
                                     float *y, int64_t ldy);
 // Integer-dot GEMM on tcgen05.mma kind::i8 (gemm_i8_tmem.cu): mode 1 = Q8_1 activation columns, mode 0 = 15-bit planes.
 bool qgemm_i8_supported(int qtype, int64_t k, const void *w, const float *x, int64_t ldx);
-// Q4_0, 2..8 activation rows, CQ_ACT_F32 numerics of small batches: one launch, one weight pass (gemv_mma.cu).
+// Q4_0, 2..8 activation rows, one launch, one weight pass (gemv_mma.cu): CQ_ACT_F32 numerics of small batches, or with
+// q8_1 set those of CQ_ACT_Q8_1.
 bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx);
-cq_status launch_gemv_mma(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
+cq_status launch_gemv_mma(cq_ctx *ctx, int order, int q8_1, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
                           float *y, int64_t ldy);
 cq_status launch_qgemm_i8(cq_ctx *ctx, int qtype, int order, int mode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
                           float *y, int64_t ldy);

@@ -55,6 +55,7 @@ struct MmaGemvParams {
     int ks;        // CTAs per cluster = k slices
     int ranges;    // row ranges = clusters
     int order;     // 0: interleaved nibbles (elements 2j, 2j+1 in byte j), 1: split (elements j, j+16)
+    int act;       // 0: 15-bit plane columns (CQ_ACT_F32), 1: Q8_1 columns (CQ_ACT_Q8_1); host-side dispatch only
     int stages, pitch, stage_bytes;
     int ypart_off;  // byte offset of the cluster-reduction buffer in dynamic shared memory
     int *err;
@@ -90,7 +91,7 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     return d;
 }
 
-template <int BPW, int ORDER>
+template <int BPW, int ORDER, int ACT>
 __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t bar_full[MM_MAX_STAGES];
@@ -176,8 +177,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
 
         // B fragments of this warp's blocks for activation row g, in registers; the scale and the accumulator seed of
         // every (block, activation row) go to shared memory, where the lane that owns result columns 2q, 2q+1 finds them.
-        uint32_t bh[BPW][2], bl[BPW][2];
-        {
+        uint32_t bh[BPW][2], bl[BPW][2];  // ACT 1: bh holds the single int8 plane, bl is unused
+        if (ACT == 0) {
             float v[BPW][8];  // 0..3: the elements under the low nibbles of the lane's four bytes, 4..7: under the high nibbles
 #pragma unroll
             for (int j = 0; j < BPW; ++j) {  // every load first: one trip to L2 for the whole warp's share
@@ -233,6 +234,100 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                 }
             }
         }
+        else {
+            // Q8_1 columns, exactly quantize_q8_1 (tensor/internal/cuda/kernels/quantized.cu:3521-3558): eight lanes per
+            // (block, activation row) in natural element order, d = amax / 127 and q = round(x / d) by true division, d and
+            // the block's f32 sum (the reference's xor butterfly: offsets 16, 8, 4 across the lanes here, 2 and 1 inside a
+            // lane) rounded to f16.  The bytes go through this warp's kilobyte of the reduction buffer (not yet in use), from
+            // where every lane picks the eight that match its weight bytes.
+            uint8_t *stg = reinterpret_cast<uint8_t *>(red) + (size_t)warp * 1024;  // [block of the chunk][row][32 positions]
+            float *sc = reinterpret_cast<float *>(colsc) + (size_t)warp * BPW * 32;
+            const int l8 = lane & 7;
+#pragma unroll
+            for (int c0 = 0; c0 < BPW; c0 += 4) {
+                constexpr int kChunkMax = 4;
+                const int cb = BPW - c0 < kChunkMax ? BPW - c0 : kChunkMax;  // blocks in this chunk
+                // up to four rows: rows 4..7 take no turns, their entries and bytes are zeroed first (the MMA still reads them)
+                const int rsh = p.m <= 4 ? 2 : 3, mrows = 1 << rsh;
+                if (mrows < 8) {
+                    for (int i = lane; i < cb * 8 * 8; i += 32) reinterpret_cast<uint32_t *>(stg)[i] = 0u;
+                    for (int i = lane; i < cb * 4 * 4; i += 32) sc[(c0 * 4 + (i >> 2)) * 8 + (i & 3)] = 0.0f;
+                    __syncwarp();
+                }
+                const int turns = (cb * mrows + 3) >> 2;
+                float4 vin[kChunkMax * 2];
+#pragma unroll
+                for (int it = 0; it < kChunkMax * 2; ++it) {  // every load of the chunk first: one trip to L2
+                    const int pairi = it * 4 + (lane >> 3);
+                    const int bj = pairi >> rsh, row = pairi & (mrows - 1);
+                    const int lb = warp * BPW + c0 + bj;
+                    vin[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (it < turns && bj < cb && lb < sblocks && row < p.m)
+                        vin[it] = __ldg(reinterpret_cast<const float4 *>(p.x + (int64_t)row * p.ldx + (int64_t)(u0 * 8 + lb) * kQK) + l8);
+                }
+#pragma unroll
+                for (int it = 0; it < kChunkMax * 2; ++it) {
+                    if (it >= turns) break;
+                    const int pairi = it * 4 + (lane >> 3);  // (block of the chunk, activation row)
+                    const int bj = pairi >> rsh, row = pairi & (mrows - 1);
+                    const float4 v = vin[it];
+                    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                    float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
+#pragma unroll
+                    for (int o = 4; o > 0; o >>= 1) {
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
+                        s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o, 8));
+                        s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o, 8));
+                        s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, o, 8));
+                        s3 = __fadd_rn(s3, __shfl_xor_sync(0xffffffffu, s3, o, 8));
+                    }
+                    const float sum = __fadd_rn(__fadd_rn(s0, s2), __fadd_rn(s1, s3));
+                    const float d = __fdiv_rn(amax, 127.0f);
+                    // round(x / d) by true division only where the quick quotient lies within 1e-3 of a tie: elsewhere both
+                    // round to the same integer (the quick quotient is off by less than 127 * 2^-21)
+                    const float rd = amax == 0.0f ? 0.0f : __frcp_rn(d);
+                    auto q8 = [&](float xv) -> uint32_t {
+                        const float t = xv * rd;
+                        float r = roundf(t);
+                        if (!(fabsf(fabsf(t - r) - 0.5f) >= 1e-3f)) r = roundf(__fdiv_rn(xv, d));  // also when the quick quotient is not finite
+                        return (uint32_t)((int)r & 0xFF);
+                    };
+                    uint32_t byte[4];
+                    byte[0] = amax == 0.0f ? 0u : q8(v.x);
+                    byte[1] = amax == 0.0f ? 0u : q8(v.y);
+                    byte[2] = amax == 0.0f ? 0u : q8(v.z);
+                    byte[3] = amax == 0.0f ? 0u : q8(v.w);
+                    // positions 0..15: the elements under the low nibbles of bytes 0..15, positions 16..31: under the high nibbles
+                    uint8_t *dst = stg + ((bj < cb ? bj : 0) * 8 + row) * 32;
+                    if (bj >= cb) {
+                    } else if (ORDER == 0) {  // elements 4l, 4l+2 are the low nibbles of bytes 2l, 2l+1; elements 4l+1, 4l+3 the high ones
+                        *reinterpret_cast<uint16_t *>(dst + 2 * l8) = (uint16_t)(byte[0] | (byte[2] << 8));
+                        *reinterpret_cast<uint16_t *>(dst + 16 + 2 * l8) = (uint16_t)(byte[1] | (byte[3] << 8));
+                    } else {           // element e is the low nibble of byte e (e < 16) or the high nibble of byte e - 16
+                        *reinterpret_cast<uint32_t *>(dst + 4 * l8) = byte[0] | (byte[1] << 8) | (byte[2] << 16) | (byte[3] << 24);
+                    }
+                    // entry (block, q') = (d8 of rows 2q', 2q'+1, then -8 * s8 of the same rows)
+                    if (l8 == 0 && bj < cb) {
+                        float *e = sc + ((c0 + bj) * 4 + (row >> 1)) * 8 + (row & 1);
+                        e[0] = __half2float(__float2half_rn(d));
+                        e[2] = -8.0f * __half2float(__float2half_rn(sum));
+                    }
+                }
+                __syncwarp();
+#pragma unroll
+                for (int bj = 0; bj < cb; ++bj) {
+                    const int j = c0 + bj;
+                    const int b0 = (j & 1) ? 4 * q : (q < 3 ? 2 + 4 * q : 0), b1 = (j & 1) ? 4 * q + 2 : (q < 3 ? 4 + 4 * q : 14);
+                    const uint8_t *src = stg + (bj * 8 + g) * 32;
+                    bh[j][0] = (uint32_t)*reinterpret_cast<const uint16_t *>(src + b0) | ((uint32_t)*reinterpret_cast<const uint16_t *>(src + b1) << 16);
+                    bh[j][1] = (uint32_t)*reinterpret_cast<const uint16_t *>(src + 16 + b0) | ((uint32_t)*reinterpret_cast<const uint16_t *>(src + 16 + b1) << 16);
+                    bl[j][0] = bl[j][1] = 0;
+                }
+                __syncwarp();
+            }
+            // the staging bytes lie where other warps will park their partial tiles
+            asm volatile("bar.sync 1, %0;" ::"n"(MM_WARPS * 32) : "memory");
+        }
         __syncwarp();
 
         const uint64_t neg_magic = dup2(-kMagic);
@@ -272,18 +367,30 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                                                     dup2(__high2float(*reinterpret_cast<const __half2 *>(&t1)))}};
 #pragma unroll
                         for (int b = 0; b < 2; ++b) {
-                            const int4 sd = *reinterpret_cast<const int4 *>(mysc + (j + b) * 32);
-                            const uint64_t csxy = *reinterpret_cast<const uint64_t *>(mysc + (j + b) * 32 + 4);
                             const uint32_t a[4] = {wv[b][0] & 0x0F0F0F0Fu, wv[b][1] & 0x0F0F0F0Fu, (wv[b][0] >> 4) & 0x0F0F0F0Fu,
                                                    (wv[b][1] >> 4) & 0x0F0F0F0Fu};
-                            int sh[4], sl[4];
-                            mma_u8s8(sh, a, bh[j + b][0], bh[j + b][1], 0, 0, 0, 0);
-                            mma_u8s8(sl, a, bl[j + b][0], bl[j + b][1], sd.x, sd.y, sd.z, sd.w);
-                            // two results per instruction (packed f32): (T - magic) * (activation scales), then * weight scale
-                            const uint64_t u01 = mul2(add2(pack2(__int_as_float(sh[0] * 128 + sl[0]), __int_as_float(sh[1] * 128 + sl[1])), neg_magic), csxy);
-                            const uint64_t u23 = mul2(add2(pack2(__int_as_float(sh[2] * 128 + sl[2]), __int_as_float(sh[3] * 128 + sl[3])), neg_magic), csxy);
-                            acc01 = fma2(dw[b][0], u01, acc01);
-                            acc23 = fma2(dw[b][1], u23, acc23);
+                            if (ACT == 0) {
+                                const int4 sd = *reinterpret_cast<const int4 *>(mysc + (j + b) * 32);
+                                const uint64_t csxy = *reinterpret_cast<const uint64_t *>(mysc + (j + b) * 32 + 4);
+                                int sh[4], sl[4];
+                                mma_u8s8(sh, a, bh[j + b][0], bh[j + b][1], 0, 0, 0, 0);
+                                mma_u8s8(sl, a, bl[j + b][0], bl[j + b][1], sd.x, sd.y, sd.z, sd.w);
+                                // two results per instruction (packed f32): (T - magic) * (activation scales), then * weight scale
+                                const uint64_t u01 = mul2(add2(pack2(__int_as_float(sh[0] * 128 + sl[0]), __int_as_float(sh[1] * 128 + sl[1])), neg_magic), csxy);
+                                const uint64_t u23 = mul2(add2(pack2(__int_as_float(sh[2] * 128 + sl[2]), __int_as_float(sh[3] * 128 + sl[3])), neg_magic), csxy);
+                                acc01 = fma2(dw[b][0], u01, acc01);
+                                acc23 = fma2(dw[b][1], u23, acc23);
+                            } else {
+                                // vec_dot_q4_0_q8_1 (quantized.cu:1919-1941) with the block scale applied as at :4434-4453:
+                                // acc += d4 * (sumi * d8 - 8 * s8), each step a fused multiply-add
+                                const ulonglong2 cs = *reinterpret_cast<const ulonglong2 *>(mysc + (j + b) * 32);  // (d8, d8'), (-8 s8, -8 s8')
+                                int si[4];
+                                mma_u8s8(si, a, bh[j + b][0], bh[j + b][1], kMagicBits, kMagicBits, kMagicBits, kMagicBits);
+                                const uint64_t f01 = add2(pack2(__int_as_float(si[0]), __int_as_float(si[1])), neg_magic);
+                                const uint64_t f23 = add2(pack2(__int_as_float(si[2]), __int_as_float(si[3])), neg_magic);
+                                acc01 = fma2(dw[b][0], fma2(f01, cs.x, cs.y), acc01);
+                                acc23 = fma2(dw[b][1], fma2(f23, cs.x, cs.y), acc23);
+                            }
                         }
                     }
                 }
@@ -356,9 +463,9 @@ bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, int ranges, MmaPlan &pl) {
     return false;
 }
 
-template <int BPW, int ORDER>
+template <int BPW, int ORDER, int ACT>
 cq_status run_mma_o(cq_ctx *ctx, MmaGemvParams p, MmaPlan pl, int64_t k) {
-    auto kern = gemv_mma_kernel<BPW, ORDER>;
+    auto kern = gemv_mma_kernel<BPW, ORDER, ACT>;
     static thread_local size_t configured = 0;
     static thread_local int configured_dev = -1;
     static thread_local std::map<std::pair<int, size_t>, int> resident;  // (cluster size, shared memory) -> clusters resident at once
@@ -404,7 +511,8 @@ cq_status run_mma_o(cq_ctx *ctx, MmaGemvParams p, MmaPlan pl, int64_t k) {
 
 template <int BPW>
 cq_status run_mma(cq_ctx *ctx, const MmaGemvParams &p, const MmaPlan &pl, int64_t k) {
-    return p.order == 0 ? run_mma_o<BPW, 0>(ctx, p, pl, k) : run_mma_o<BPW, 1>(ctx, p, pl, k);
+    if (p.act == 0) return p.order == 0 ? run_mma_o<BPW, 0, 0>(ctx, p, pl, k) : run_mma_o<BPW, 1, 0>(ctx, p, pl, k);
+    return p.order == 0 ? run_mma_o<BPW, 0, 1>(ctx, p, pl, k) : run_mma_o<BPW, 1, 1>(ctx, p, pl, k);
 }
 
 }  // namespace
@@ -415,7 +523,7 @@ bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n,
            (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 4 == 0 && plan_mma(ctx, k, n, 0, pl);
 }
 
-cq_status launch_gemv_mma(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
+cq_status launch_gemv_mma(cq_ctx *ctx, int order, int q8_1, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
                           float *y, int64_t ldy) {
     MmaPlan pl;
     if (!plan_mma(ctx, k, n, 0, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: shape not supported");
@@ -423,7 +531,7 @@ cq_status launch_gemv_mma(cq_ctx *ctx, int order, const float *x, int64_t m, int
     p.w = static_cast<const uint8_t *>(w);
     p.x = x, p.y = y, p.bias = bias;
     p.ldx = ldx, p.ldy = ldy, p.n = n;
-    p.nb = (int)(k / kQK), p.m = (int)m, p.order = order == CQ_ORDER_GGML_SPLIT ? 1 : 0;
+    p.nb = (int)(k / kQK), p.m = (int)m, p.order = order == CQ_ORDER_GGML_SPLIT ? 1 : 0, p.act = q8_1 ? 1 : 0;
     p.err = ctx->dev_err_devptr;
     switch (pl.bpw) {  // the plan may still change its row ranges and stages, never its k slices
     case 2: return run_mma<2>(ctx, p, pl, k);
