@@ -3,11 +3,15 @@
 // activation rows are one pair of integer tensor-core instructions (mma.sync m16n8k32, u8 x s8 -> s32) instead of
 // 32 x 8 multiply-adds on the CUDA cores, so the kernel stays bound by HBM at eight rows as it is at one.
 //
-// Numerics are those of the int8 tensor-core GEMM's plane columns (gemm_i8_tmem.cu): every activation block is
+// CQ_ACT_F32 numerics (ACT = 0) are those of the int8 tensor-core GEMM's plane columns (gemm_i8_tmem.cu): every activation block is
 // 15-bit block fixed point, X = rint(x * 16383 / amax) = 128 * hi + lo (hi in [-128, 127], lo in [0, 127]); with the
 // unsigned nibbles n of a weight block the block's term is (d_w * amax / 16383) * (128 * sum(n * hi) + sum(n * lo)
 // - 8 * sum(X)), integer sums exact.  The reference path is QMatMul's dequantize + f32 matmul
 // (tensor/cpu_backend.go:419-481); this lands about 2e-5 of max|y| from it.
+//
+// With ACT = 1 the same kernel runs CQ_ACT_Q8_1: one int8 plane quantized exactly as quantize_q8_1
+// (tensor/internal/cuda/kernels/quantized.cu:3521-3558), block terms d4 * (sumi * d8 - 8 * s8) as vec_dot_q4_0_q8_1
+// (quantized.cu:1919-1941), each step a fused multiply-add.
 //
 // Shape of the work:
 //   * the CTAs of a cluster of `ks` (1, 2, 4 or 8) share a range of weight rows and split k between them, so that a
