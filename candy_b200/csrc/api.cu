@@ -346,6 +346,13 @@ cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float
         if (s == CQ_OK && ctx->bias) ctx->bias_done = true;
         return s;
     }
+    // Up to eight rows of CQ_ACT_F16 against Q4_0: the same streaming kernel with f16 operands, one launch.
+    if (actmode == CQ_ACT_F16 && ctx->tune.gemv_mma > 0 && m <= 8 && !ctx->fuse.on && ctx->push.world == 0 &&
+        gemv_mma_f16_supported(ctx, qtype, m, k, n, w_blocks_dev, x_dev, ldx)) {
+        s = launch_gemv_mma_f16(ctx, order, x_dev, m, k, ldx, w_blocks_dev, n, ctx->bias, y_dev, ldy);
+        if (s == CQ_OK && ctx->bias) ctx->bias_done = true;
+        return s;
+    }
     // Integer dots on the tensor cores: one weight pass for the whole batch, in the activation mode's own numerics.
     if (actmode != CQ_ACT_F16 && ctx->tune.gemm_int8 && !ctx->fuse.on && ctx->push.world == 0 && ctx->tune.gemv_variant == 0 &&
         m >= (actmode == CQ_ACT_Q8_1 ? ctx->tune.i8_min_rows_q8_1 : ctx->tune.i8_min_rows_f32) &&

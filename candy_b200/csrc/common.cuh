@@ -159,6 +159,10 @@ bool qgemm_i8_supported(int qtype, int64_t k, const void *w, const float *x, int
 bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx);
 cq_status launch_gemv_mma(cq_ctx *ctx, int order, int q8_1, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
                           float *y, int64_t ldy);
+// Q4_0, 1..8 activation rows, CQ_ACT_F16 numerics: one launch, one weight pass (gemv_mma_f16.cu).
+bool gemv_mma_f16_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx);
+cq_status launch_gemv_mma_f16(cq_ctx *ctx, int order, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
+                              float *y, int64_t ldy);
 cq_status launch_qgemm_i8(cq_ctx *ctx, int qtype, int order, int mode, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n,
                           float *y, int64_t ldy);
 cq_status launch_gemm(cq_ctx *ctx, int qtype, int order, int actmode, const float *x, int64_t m, int64_t k,

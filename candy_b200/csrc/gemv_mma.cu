@@ -30,40 +30,14 @@
 //     own (deterministic; the workers only arrive at a named barrier and go on with the next stage), the cluster's
 //     k slices in rank order through distributed shared memory at the end.
 // Every wait is bounded and records an error word.
-#include <cooperative_groups.h>
-#include <cuda_fp16.h>
+#include "gemv_mma.cuh"
 
-#include "common.cuh"
-
-namespace cg = cooperative_groups;
+using namespace mma_gemv;
 
 namespace {
 
-constexpr int MM_WARPS = 16;       // consumer warps
-constexpr int MM_ROWS = 16;        // weight rows per stage
-constexpr int MM_MAX_STAGES = 8;
-constexpr int MM_RED_BYTES = 2 * MM_WARPS * 128 * 4;
-constexpr int MM_COLSC_BYTES = MM_WARPS * 8 * 4 * 32;  // per (warp, block, q): the accumulator seeds as a ready quad, then the two scales
-constexpr int MM_THREADS = (MM_WARPS + 2) * 32;   // workers, the producer warp, the reducer warp
 constexpr int kMagicBits = 0x4B400000;  // 1.5 * 2^23 as a float
 constexpr float kMagic = 12582912.0f;
-
-struct MmaGemvParams {
-    const uint8_t *w;
-    const float *x;
-    float *y;
-    const float *bias;
-    int64_t ldx, ldy, n;
-    int nb;        // blocks per weight row
-    int m;         // activation rows (<= 8)
-    int ks;        // CTAs per cluster = k slices
-    int ranges;    // row ranges = clusters
-    int order;     // 0: interleaved nibbles (elements 2j, 2j+1 in byte j), 1: split (elements j, j+16)
-    int act;       // 0: 15-bit plane columns (CQ_ACT_F32), 1: Q8_1 columns (CQ_ACT_Q8_1); host-side dispatch only
-    int stages, pitch, stage_bytes;
-    int ypart_off;  // byte offset of the cluster-reduction buffer in dynamic shared memory
-    int *err;
-};
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int c0, int c1, int c2, int c3) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
@@ -102,78 +76,20 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
     __shared__ uint64_t bar_empty[MM_MAX_STAGES];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int ks = p.ks > 1 ? (int)(blockIdx.x % p.ks) : 0;  // rank in the cluster (clusters are consecutive CTAs)
-    const int range = (int)(blockIdx.x / p.ks);
-    const int64_t row_begin = p.n * range / p.ranges, row_end = p.n * (range + 1) / p.ranges;
-    const int nrows = (int)(row_end - row_begin);
-    const int npass = (nrows + MM_ROWS - 1) / MM_ROWS;
-    const int units = p.nb >> 3;  // slices are cut in units of eight blocks (144 bytes: copies stay 16-byte aligned)
-    const int u0 = units * ks / p.ks, u1 = units * (ks + 1) / p.ks;
-    const int sblocks = (u1 - u0) * 8;
-    const uint32_t slice_bytes = (uint32_t)sblocks * kQ4Bytes;
-    const int64_t row_bytes = (int64_t)p.nb * kQ4Bytes;
+    const Geometry geo = geometry(p);
+    const int nrows = geo.nrows, npass = geo.npass, u0 = geo.u0, sblocks = geo.sblocks;
     float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);
-    float4 *colsc = reinterpret_cast<float4 *>(smem + (size_t)p.stages * p.stage_bytes + MM_RED_BYTES);  // [warp][block][q] entries of 32 bytes
+    float4 *colsc = reinterpret_cast<float4 *>(smem + p.aux_off);  // [warp][block][q] entries of 32 bytes
     float *ypart = reinterpret_cast<float *>(smem + p.ypart_off);
+    (void)nrows;
 
     pdl_launch_dependents();
-    if (tid == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(smem_u32(&bar_full[s]), 1);
-            mbar_init(smem_u32(&bar_empty[s]), MM_WARPS);
-        }
-        fence_mbar_init();
-        fence_proxy_async();
-    }
-    __syncthreads();
+    init_ring(p, bar_full, bar_empty);
 
     if (warp == MM_WARPS) {
-        // ---- producer: the weights do not depend on the previous kernel, so the ring fills at once ----
-        const uint64_t policy = make_l2_policy_evict_first();
-        const uint8_t *src0 = p.w + row_begin * row_bytes + (int64_t)u0 * (8 * kQ4Bytes);
-        int issued = 0;
-        for (int ps = 0; ps < npass; ++ps) {
-            const int s = ps % p.stages;
-            if (ps >= p.stages && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ((ps / p.stages) - 1) & 1)) {
-                if (lane == 0) atomicExch(p.err, kDevErrEmptyWait);
-                break;
-            }
-            const int rows = min(MM_ROWS, nrows - ps * MM_ROWS);
-            if (lane == 0) mbar_expect_tx(smem_u32(&bar_full[s]), (uint32_t)rows * slice_bytes);
-            __syncwarp();
-            if (lane < rows)
-                bulk_g2s_hint(smem_u32(smem + (size_t)s * p.stage_bytes + (size_t)lane * p.pitch), src0 + (int64_t)(ps * MM_ROWS + lane) * row_bytes,
-                              slice_bytes, smem_u32(&bar_full[s]), policy);
-            issued = ps + 1;
-        }
-        // never leave with copies in flight into this CTA's shared memory
-        for (int ps = issued > p.stages ? issued - p.stages : 0; ps < issued; ++ps) {
-            if (!mbar_wait_bounded(smem_u32(&bar_full[ps % p.stages]), (ps / p.stages) & 1)) {
-                if (lane == 0) atomicExch(p.err, kDevErrDrain);
-                break;
-            }
-        }
+        produce(p, geo, smem, bar_full, bar_empty);
     } else if (warp == MM_WARPS + 1) {
-        // ---- reducer: adds the sixteen partial tiles of a pass in warp order while the others work on the next ----
-        pdl_wait_prior();
-        for (int ps = 0; ps < npass; ++ps) {
-            const int buf = ps & 1;
-            asm volatile("bar.sync %0, %1;" ::"r"(2 + buf), "n"(MM_WARPS * 32 + 32) : "memory");  // the tile is parked
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int t = e * 32 + lane;  // value t of the tile: lane t / 4 of the fragment, register t % 4
-                float tot = 0.0f;
-#pragma unroll
-                for (int w = 0; w < MM_WARPS; ++w) tot += red[(buf * MM_WARPS + w) * 128 + t];
-                const int l = t >> 2, c = t & 3;
-                const int wrow = ps * MM_ROWS + (l >> 2) + ((c >> 1) << 3), col = 2 * (l & 3) + (c & 1);
-                if (wrow < nrows && col < p.m) {
-                    if (p.ks > 1) ypart[wrow * 8 + col] = tot;
-                    else p.y[(int64_t)col * p.ldy + row_begin + wrow] = p.bias ? tot + p.bias[row_begin + wrow] : tot;
-                }
-            }
-            if (ps + 2 < npass) asm volatile("bar.arrive %0, %1;" ::"r"(4 + buf), "n"(MM_WARPS * 32 + 32) : "memory");  // the buffer is free again
-        }
+        reduce<1>(p, geo, red, ypart);
     } else {
         // ---- workers ----
         const int g = lane >> 2, q = lane & 3;
@@ -343,7 +259,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
         uint32_t phase = 0;
         bool dead = false;
         for (int ps = 0; ps < npass; ++ps) {
-            const int buf = ps & 1;
             // a warp whose wait gave up keeps walking the loop so that the reducer's barriers still fill up
             if (!dead && !mbar_wait_bounded(full0 + 8 * stage, phase)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
@@ -399,16 +314,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
                     }
                 }
             }
-            float acc[4];
-            unpack2(acc01, acc[0], acc[1]);
-            unpack2(acc23, acc[2], acc[3]);
-            // The tile of pass ps - 2 has left this buffer once the reducer says so.  The partial tile depends on every
-            // word read from the stage, so the stage can be released once it is parked.
-            if (ps >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + buf), "n"(MM_WARPS * 32 + 32) : "memory");
-            reinterpret_cast<float4 *>(red)[(buf * MM_WARPS + warp) * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
-            asm volatile("bar.arrive %0, %1;" ::"r"(2 + buf), "n"(MM_WARPS * 32 + 32) : "memory");
+            float acc[1][4];
+            unpack2(acc01, acc[0][0], acc[0][1]);
+            unpack2(acc23, acc[0][2], acc[0][3]);
+            park<1>(red, ps, warp, lane, acc, empty0 + 8 * stage);
             if (++stage == p.stages) {
                 stage = 0;
                 phase ^= 1;
@@ -416,107 +325,17 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
         }
     }
 
-    if (p.ks > 1) {
-        // add the cluster's k slices in rank order; every rank finishes the rows r with r % ks == its rank
-        cg::cluster_group cluster = cg::this_cluster();
-        pdl_wait_prior();  // the producer warp writes results below and has not waited yet
-        cluster.sync();
-        for (int i = tid; i < nrows * 8; i += MM_THREADS) {
-            const int wrow = i >> 3, col = i & 7;
-            if (col < p.m && wrow % p.ks == ks) {
-                float tot = 0.0f;
-                for (int r = 0; r < p.ks; ++r) tot += cluster.map_shared_rank(ypart, r)[i];
-                p.y[(int64_t)col * p.ldy + row_begin + wrow] = p.bias ? tot + p.bias[row_begin + wrow] : tot;
-            }
-        }
-        cluster.sync();  // nobody leaves while its shared memory may still be read
-    }
-}
-
-struct MmaPlan {
-    int ks, bpw, ranges, stages, pitch, stage_bytes, ypart_off;
-    size_t smem;
-};
-
-// ranges = 0: one row range per group of ks SMs; otherwise that many row ranges.
-bool plan_mma(cq_ctx *ctx, int64_t k, int64_t n, int ranges, MmaPlan &pl) {
-    const int nb = (int)(k / kQK), units = nb / 8;
-    for (int ks = 1; ks <= 8; ks *= 2) {
-        if (ks > units) return false;
-        const int max_blocks = ((units + ks - 1) / ks) * 8;
-        if (max_blocks > MM_WARPS * 8) continue;
-        int bpw = (max_blocks + MM_WARPS - 1) / MM_WARPS;
-        bpw += bpw & 1;
-        if (ranges <= 0) ranges = ctx->sm_count / ks;
-        if (ranges < 1) return false;
-        // eight rows read at once must fall in different banks: pitch = 16 (mod 32) bytes
-        const int slice = max_blocks * kQ4Bytes;
-        const int pitch = (slice % 32 == 16) ? slice : slice + 16;
-        const int stage_bytes = MM_ROWS * pitch;
-        const int rows_max = (int)((n + ranges - 1) / ranges);
-        const int ypart = ks > 1 ? ((rows_max + MM_ROWS) * 8 * 4) : 0;
-        const int budget = 225 * 1024 - MM_RED_BYTES - MM_COLSC_BYTES - ypart;
-        int stages = budget / stage_bytes;
-        if (stages > MM_MAX_STAGES) stages = MM_MAX_STAGES;
-        if (stages < 2) return false;
-        pl.ks = ks, pl.bpw = bpw, pl.ranges = ranges, pl.stages = stages, pl.pitch = pitch, pl.stage_bytes = stage_bytes;
-        pl.ypart_off = stages * stage_bytes + MM_RED_BYTES + MM_COLSC_BYTES;
-        pl.smem = (size_t)pl.ypart_off + ypart;
-        return true;
-    }
-    return false;
-}
-
-template <int BPW, int ORDER, int ACT>
-cq_status run_mma_o(cq_ctx *ctx, MmaGemvParams p, MmaPlan pl, int64_t k) {
-    auto kern = gemv_mma_kernel<BPW, ORDER, ACT>;
-    static thread_local size_t configured = 0;
-    static thread_local int configured_dev = -1;
-    static thread_local std::map<std::pair<int, size_t>, int> resident;  // (cluster size, shared memory) -> clusters resident at once
-    if (configured_dev != ctx->device) configured = 0, resident.clear(), configured_dev = ctx->device;
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[2];
-    for (int round = 0; round < 3; ++round) {
-        if (configured < pl.smem) {
-            CQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-            configured = pl.smem;
-        }
-        cfg.gridDim = dim3((unsigned)(pl.ranges * pl.ks));
-        cfg.blockDim = dim3(MM_THREADS);
-        cfg.dynamicSmemBytes = pl.smem;
-        cfg.stream = ctx->stream;
-        cfg.attrs = attr;
-        cfg.numAttrs = 0;
-        if (pl.ks == 1) break;
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)pl.ks, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-        cfg.numAttrs = 1;
-        // Every cluster must be resident at once: the SMs of a GPC do not always divide by the cluster size, and a second
-        // wave of a few clusters would double the time.  Fewer, longer row ranges instead.
-        const auto key = std::make_pair(pl.ks, pl.smem);
-        auto it = resident.find(key);
-        if (it == resident.end()) {
-            int nc = 0;
-            CQ_CUDA(ctx, cudaOccupancyMaxActiveClusters(&nc, kern, &cfg));
-            it = resident.emplace(key, nc).first;
-        }
-        if (it->second >= pl.ranges) break;
-        if (it->second < 1 || !plan_mma(ctx, k, p.n, it->second, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: clusters do not fit");
-    }
-    p.ks = pl.ks, p.ranges = pl.ranges, p.stages = pl.stages, p.pitch = pl.pitch, p.stage_bytes = pl.stage_bytes, p.ypart_off = pl.ypart_off;
-    if (ctx->tune.pdl) {
-        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
-        ++cfg.numAttrs;
-    }
-    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
-    return CQ_OK;
+    if (p.ks > 1) cluster_sum<1>(p, geo, ypart);
 }
 
 template <int BPW>
 cq_status run_mma(cq_ctx *ctx, const MmaGemvParams &p, const MmaPlan &pl, int64_t k) {
-    if (p.act == 0) return p.order == 0 ? run_mma_o<BPW, 0, 0>(ctx, p, pl, k) : run_mma_o<BPW, 1, 0>(ctx, p, pl, k);
-    return p.order == 0 ? run_mma_o<BPW, 0, 1>(ctx, p, pl, k) : run_mma_o<BPW, 1, 1>(ctx, p, pl, k);
+    if (p.act == 0) {
+        if (p.order == 0) return launch_planned(ctx, gemv_mma_kernel<BPW, 0, 0>, p, pl, k, 1, 8);
+        return launch_planned(ctx, gemv_mma_kernel<BPW, 1, 0>, p, pl, k, 1, 8);
+    }
+    if (p.order == 0) return launch_planned(ctx, gemv_mma_kernel<BPW, 0, 1>, p, pl, k, 1, 8);
+    return launch_planned(ctx, gemv_mma_kernel<BPW, 1, 1>, p, pl, k, 1, 8);
 }
 
 }  // namespace
@@ -524,13 +343,13 @@ cq_status run_mma(cq_ctx *ctx, const MmaGemvParams &p, const MmaPlan &pl, int64_
 bool gemv_mma_supported(cq_ctx *ctx, int qtype, int64_t m, int64_t k, int64_t n, const void *w, const float *x, int64_t ldx) {
     MmaPlan pl;
     return qtype == CQ_Q4_0 && m >= 2 && m <= 8 && k % 256 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
-           (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 4 == 0 && plan_mma(ctx, k, n, 0, pl);
+           (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 4 == 0 && plan_mma(ctx, k, n, 0, 1, 8, pl);
 }
 
 cq_status launch_gemv_mma(cq_ctx *ctx, int order, int q8_1, const float *x, int64_t m, int64_t k, int64_t ldx, const void *w, int64_t n, const float *bias,
                           float *y, int64_t ldy) {
     MmaPlan pl;
-    if (!plan_mma(ctx, k, n, 0, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: shape not supported");
+    if (!plan_mma(ctx, k, n, 0, 1, 8, pl)) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "small-batch kernel: shape not supported");
     MmaGemvParams p = {};
     p.w = static_cast<const uint8_t *>(w);
     p.x = x, p.y = y, p.bias = bias;
