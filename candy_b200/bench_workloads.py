@@ -136,7 +136,7 @@ def prefill_gemm(dev, peak_gbs: float, peak_tflops: float, ms_rows=(16, 128, 256
 
 def small_batch(dev, peak_gbs: float, ms_rows=(1, 2, 4, 8), n: int = 11008, k: int = 4096, seed: int = 3, calls: int = 40):
     """Decode-side batches (m = 1 .. 8 activation rows against one Q4_0 weight, n = 11008, k = 4096) in the two
-    decode numerics, CQ_ACT_F32 and CQ_ACT_Q8_1: the whole cq_qmatmul call, timed as replays of a CUDA graph of
+    decode numerics, CQ_ACT_F32 and CQ_ACT_Q8_1, and in CQ_ACT_F16: the whole cq_qmatmul call, timed as replays of a CUDA graph of
     `calls` calls that cycle through eight copies of the weight.  One pass over the weights serves every row:
     m = 1 the streaming GEMV, m = 2 its two-row form; m = 3..8 the single-launch kernel with mma.sync block dots
     (plane or Q8_1 columns)."""
@@ -147,7 +147,7 @@ def small_batch(dev, peak_gbs: float, ms_rows=(1, 2, 4, 8), n: int = 11008, k: i
     first = QStorage.quantize(dev, 2, 0, w)
     ring = [first] + [RawCopy(dev, first) for _ in range(7)]
     out = []
-    for act, actname in ((0, "f32"), (1, "q8_1")):
+    for act, actname in ((0, "f32"), (1, "q8_1"), (2, "f16")):
         for m in ms_rows:
             x = dev.storage_from_slice(rng.standard_normal((m, k), dtype=np.float32))
             y = dev.alloc(m * n)
@@ -180,7 +180,8 @@ def small_batch(dev, peak_gbs: float, ms_rows=(1, 2, 4, 8), n: int = 11008, k: i
             nbytes = n * (k // 32) * 18 + 4 * m * k + 4 * m * n
             out.append({"actmode": actname, "m": m, "us": round(t * 1e6, 2), "algorithmic_gbs": round(nbytes / t / 1e9, 1),
                         "frac_of_hbm_peak": round(nbytes / t / 1e9 / peak_gbs, 4),
-                        "path": "streaming GEMV" if m == 1 else (
+                        "path": ("streaming kernel with mma.sync f16 operands dequantized in registers, one launch" if m <= 8 and k % 256 == 0
+                                 else "narrow tensor-memory GEMM") if act == 2 else "streaming GEMV" if m == 1 else (
                             "streaming kernel with mma.sync block dots, one launch" if m <= 8 and k % 256 == 0 and (
                                 m >= 3 or (n * k >= 40 << 20 if act == 0 else (k >= 8192 or n * k >= 100 << 20)))
                             else ("two-row streaming GEMV" if m == 2 else "int8 tcgen05 kernel"))})

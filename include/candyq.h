@@ -103,7 +103,8 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
 /* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl, gemv_early (launch geometry of the
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
  * row); gemv_mma (3, default: CQ_ACT_F32 and CQ_ACT_Q8_1 batches of this many rows up to eight against Q4_0 run the
- * single-launch kernel with mma.sync block dots; two rows too against large weights; 0: never); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
+ * single-launch kernel with mma.sync block dots, two rows too against large weights, and CQ_ACT_F16 batches of up to
+ * eight rows its f16 form; 0: never); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
  * GEMM has seen: the weights must then stay unchanged, or be rewritten only through cq_* entry points, or
  * cq_invalidate_weight_cache must be called); gemm_pair (1, default: CQ_ACT_F16 batches beyond 384 rows run 256 x 256
  * tiles on CTA pairs; 0: 128 x 256 tiles per CTA); gemm_fused_dequant (1, default: Q4_0 batches of 129..384 rows in
@@ -174,7 +175,8 @@ cq_status cq_quantize_q8_1(cq_ctx *ctx, const float *x_dev, int64_t m, int64_t k
  * the tensor cores, scaled per block as the mode says (CQ_ACT_F32 batches hold each activation block as 15-bit
  * block fixed point, about 2e-5 of max|y| from the CPU path; CQ_ACT_Q8_1 batches quantize exactly as quantize_q8_1
  * does; up to eight rows against Q4_0 run in a single-launch streaming kernel, larger batches in the int8 GEMM);
- * CQ_ACT_F16 runs the f16 tensor-core GEMMs.
+ * CQ_ACT_F16 runs the f16 tensor-core GEMMs (up to eight rows against Q4_0: the single-launch streaming kernel with
+ * f16 operands, same rounding of the operands).
  * Preconditions: k % 32 == 0, k >= 32, m, n >= 1, ldx >= k, ldy >= n. */
 cq_status cq_qmatmul(cq_ctx *ctx, int qtype, int order, int actmode, const float *x_dev,
                      int64_t m, int64_t k, int64_t ldx, const void *w_blocks_dev, int64_t n,
