@@ -53,11 +53,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) gemv_mma_kernel(const MmaGemvPa
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const Geometry geo = geometry(p);
-    const int nrows = geo.nrows, npass = geo.npass, u0 = geo.u0, sblocks = geo.sblocks;
+    const int npass = geo.npass, u0 = geo.u0, sblocks = geo.sblocks;
     float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);
     float4 *colsc = reinterpret_cast<float4 *>(smem + p.aux_off);  // [warp][block][q] entries of 32 bytes
     float *ypart = reinterpret_cast<float *>(smem + p.ypart_off);
-    (void)nrows;
 
     pdl_launch_dependents();
     init_ring(p, bar_full, bar_empty);
