@@ -630,6 +630,86 @@ struct DecQ81 {
     }
 };
 
+// The same numerics straight from f32 activations: quantize_q8_1's arithmetic (quantized.cu:3521-3558) runs in the
+// kernel's cooperative set-up instead of a launch of its own.  Four adjacent lanes hold a block, eight values each:
+// d = amax / 127 and q = round(x / d) by true division (taken only where the quick quotient x * rcp(d) lies within
+// 1e-3 of a rounding tie or is not finite: elsewhere both round to the same integer), d and the block's f32 sum rounded
+// to f16; the sum follows the reference's xor butterfly over the 32 values (offsets 16 and 8 across the lanes here,
+// 4, 2, 1 inside a lane), so its bits agree with the reference kernel's.  All 32 lanes call the staging together.
+template <int QT, int ORDER>
+struct DecQ81F : DecQ81<QT, ORDER> {
+    using Base = DecQ81<QT, ORDER>;
+    static constexpr bool kSplitStage = true;
+    __device__ __forceinline__ static void load_quarter(const float *x, int item, bool valid, float (&r)[8]) {
+        if (valid) {
+            const float4 a = reinterpret_cast<const float4 *>(x)[2 * item];
+            const float4 b = reinterpret_cast<const float4 *>(x)[2 * item + 1];
+            r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = 0.0f;
+        }
+    }
+    __device__ __forceinline__ static void stage_quarter_regs(const float (&r)[8], int item, bool valid, uint32_t *area) {
+        const int blk = item >> 2, qd = item & 3;
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(r[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1, 32));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2, 32));
+        float s[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s[i] = __fadd_rn(r[i], __shfl_xor_sync(0xffffffffu, r[i], 2, 32));   // values 16 apart
+            s[i] = __fadd_rn(s[i], __shfl_xor_sync(0xffffffffu, s[i], 1, 32));   // values 8 apart
+        }
+        const float c0 = __fadd_rn(s[0], s[4]), c1 = __fadd_rn(s[1], s[5]), c2 = __fadd_rn(s[2], s[6]), c3 = __fadd_rn(s[3], s[7]);
+        const float sum = __fadd_rn(__fadd_rn(c0, c2), __fadd_rn(c1, c3));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float rd = amax == 0.0f ? 0.0f : __frcp_rn(d);
+        uint32_t w01[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float t = r[i] * rd;
+            float q = roundf(t);
+            if (!(fabsf(fabsf(t - q) - 0.5f) >= 1e-3f)) q = roundf(__fdiv_rn(r[i], d));
+            const uint32_t byte = amax == 0.0f ? 0u : (uint32_t)((int)q & 0xFF);
+            w01[i >> 2] |= byte << (8 * (i & 3));
+        }
+        if (!valid) return;
+        const uint32_t w0 = w01[0], w1 = w01[1];  // values 8qd .. 8qd+3, 8qd+4 .. 8qd+7
+        uint32_t wa, wb;
+        int idxA, idxB;
+        if (QT == CQ_Q4_0 && ORDER == CQ_ORDER_GO_INTERLEAVED) {
+            wa = __byte_perm(w0, w1, 0x6420), wb = __byte_perm(w0, w1, 0x7531);  // low nibbles meet the even values
+            idxA = 2 * qd, idxB = 2 * qd + 1;
+        } else if (QT == CQ_Q4_0) {
+            wa = w0, wb = w1;
+            idxA = (qd < 2) ? 4 * qd : 4 * (qd - 2) + 1, idxB = idxA + 2;
+        } else {
+            wa = w0, wb = w1;
+            idxA = 2 * qd, idxB = 2 * qd + 1;
+        }
+        uint32_t *dst = area + blk * Base::kStateWordsPerBlock;
+        dst[idxA] = wa;
+        dst[idxB] = wb;
+        if (qd == 0) {
+            dst[8] = __float_as_uint(__half2float(__float2half_rn(d)));
+            dst[9] = __float_as_uint(__half2float(__float2half_rn(sum)));
+        }
+    }
+    __device__ __forceinline__ static void stage_quarter(const float *x, int item, bool valid, uint32_t *area) {
+        float r[8];
+        load_quarter(x, item, valid, r);
+        stage_quarter_regs(r, item, valid, area);
+    }
+    struct QRegs {
+        float r[8];
+    };
+    __device__ __forceinline__ static void qload(const float *x, int item, bool valid, QRegs &q) { load_quarter(x, item, valid, q.r); }
+    __device__ __forceinline__ static void qstage(const QRegs &q, int item, bool valid, uint32_t *area) { stage_quarter_regs(q.r, item, valid, area); }
+};
+
 // MAXT / MINB are launch bounds only: geometries of at most 288 threads are compiled to fit two
 // CTAs per SM, so that under programmatic dependent launch the next GEMV of the stream can be
 // resident (and prefetching its weights) while this one is still computing.
@@ -1448,10 +1528,12 @@ cq_status run_stream_mr(cq_ctx *ctx, const GemvParams &p, int grid, int threads,
 // most 4 rows of state per thread, two warp groups for 5..8 rows when the row is short enough) or rows of
 // Q8_1 blocks (Q81 state, up to 8 rows per thread).  Returns how many leading rows were launched (0 when
 // the shape does not fit; a single left-over row is left to the one-row kernel).
-template <int QT, int ORDER, bool Q81>
+// DECK: 0 = f32 rows, Q16 state; 1 = rows of Q8_1 blocks; 2 = f32 rows quantized to Q8_1 in the set-up (two rows a pass only).
+template <int QT, int ORDER, int DECK>
 int64_t try_stream_mr(cq_ctx *ctx, const void *x, int64_t x_row_bytes, int64_t m, int64_t k, const uint8_t *w, int64_t n, float *y, int64_t ldy,
                       cq_status &s) {
-    using Dec = typename std::conditional<Q81, DecQ81<QT, ORDER>, DecQ16<QT, ORDER>>::type;
+    constexpr bool Q81 = DECK == 1;
+    using Dec = typename std::conditional<DECK == 2, DecQ81F<QT, ORDER>, typename std::conditional<DECK == 1, DecQ81<QT, ORDER>, DecQ16<QT, ORDER>>::type>::type;
     s = CQ_OK;
     if (ctx->tune.force_simple || ctx->tune.gemv_multirow == 0 || m < 2 || m > 8 || (x_row_bytes & 15) != 0) return 0;
     int64_t r0 = 0;
@@ -1461,6 +1543,7 @@ int64_t try_stream_mr(cq_ctx *ctx, const void *x, int64_t x_row_bytes, int64_t m
         size_t smem = 0;
         const uint8_t *xr = static_cast<const uint8_t *>(x) + r0 * x_row_bytes;
         int rows = (int)(m - r0);
+        if (DECK == 2 && rows > 2) rows = 2;
         const int mr = Q81 ? (rows <= 2 ? 2 : (rows <= 4 ? 4 : 8)) : (rows <= 2 ? 2 : 4);
         bool ok = plan_stream_mr(ctx, QT, w, xr, n, k, rows, mr, Dec::kStateWordsPerBlock, p, grid, threads, smem);
         if (!ok && rows > mr) {  // not enough warps for two activation-row groups: mr rows now, the rest in another pass
@@ -1475,9 +1558,9 @@ int64_t try_stream_mr(cq_ctx *ctx, const void *x, int64_t x_row_bytes, int64_t m
         p.ldy = ldy;
         p.err = ctx->dev_err_devptr;
         p.bias = ctx->bias;
-        if (mr == 2) s = run_stream_mr<Dec, 2>(ctx, p, grid, threads, smem);
-        else if (mr == 4) s = run_stream_mr<Dec, 4>(ctx, p, grid, threads, smem);
-        else s = run_stream_mr<Dec, Q81 ? 8 : 4>(ctx, p, grid, threads, smem);
+        if (mr == 2 || DECK == 2) s = run_stream_mr<Dec, 2>(ctx, p, grid, threads, smem);
+        else if (mr == 4) s = run_stream_mr<Dec, DECK == 2 ? 2 : 4>(ctx, p, grid, threads, smem);
+        else s = run_stream_mr<Dec, DECK == 2 ? 2 : (Q81 ? 8 : 4)>(ctx, p, grid, threads, smem);
         if (s != CQ_OK) return r0 + rows;
         r0 += rows;
     }
@@ -1567,7 +1650,7 @@ cq_status q8_1_on_blocks(cq_ctx *ctx, const void *act_blocks, int64_t m, int64_t
         p.bias = ctx->bias;
         ctx->bias_done = true;
         cq_status s = CQ_OK;
-        const int64_t done = try_stream_mr<QT, ORDER, true>(ctx, act_blocks, (int64_t)nb * kQ81Bytes, m, k, w, n, y, ldy, s);
+        const int64_t done = try_stream_mr<QT, ORDER, 1>(ctx, act_blocks, (int64_t)nb * kQ81Bytes, m, k, w, n, y, ldy, s);
         if (s != CQ_OK) return s;
         for (int64_t i = done; i < m; ++i) {
             p.x = reinterpret_cast<const float *>(static_cast<const uint8_t *>(act_blocks) + (size_t)i * nb * kQ81Bytes);
@@ -1585,6 +1668,29 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
                         int64_t n, float *y, int64_t ldy) {
     const int nb = (int)(k / kQK);
     if (actmode == CQ_ACT_Q8_1) {
+        // One or two rows: the activations are quantized inside the GEMV's set-up, no launch of their own.
+        if (m <= 2 && ctx->tune.gemv_q81_inline && !ctx->tune.force_simple && ctx->push.world == 0 && !ctx->fuse.on && ldx % 4 == 0 &&
+            (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            GemvParams p{};
+            int rpt = 1, grid = 0, threads = 0;
+            size_t smem = 0;
+            if (plan_stream(ctx, QT, w, x, n, k, p, rpt, grid, threads, smem) && p.coop_off >= 0) {
+                p.w = w;
+                p.err = ctx->dev_err_devptr;
+                p.bias = ctx->bias;
+                ctx->bias_done = true;
+                cq_status s = CQ_OK;
+                const int64_t done = try_stream_mr<QT, ORDER, 2>(ctx, x, ldx * (int64_t)sizeof(float), m, k, w, n, y, ldy, s);
+                if (s != CQ_OK) return s;
+                for (int64_t i = done; i < m; ++i) {
+                    p.x = x + i * ldx;
+                    p.y = y + i * ldy;
+                    s = run_stream<DecQ81F<QT, ORDER>>(ctx, p, rpt, grid, threads, smem);
+                    if (s != CQ_OK) return s;
+                }
+                return CQ_OK;
+            }
+        }
         const size_t bytes = (size_t)m * nb * kQ81Bytes;
         cq_status s = cq_reserve_scratch(ctx, bytes);
         if (s != CQ_OK) return s;
@@ -1610,7 +1716,7 @@ cq_status gemv_dispatch(cq_ctx *ctx, int actmode, const float *x, int64_t m, int
         int64_t done = 0;
         if (!f.on && ctx->push.world == 0 && ctx->tune.gemv_variant == 0) {  // two or more plain rows: one weight pass for up to 4 (8) of them
             cq_status s = CQ_OK;
-            done = try_stream_mr<QT, ORDER, false>(ctx, x, ldx * (int64_t)sizeof(float), m, k, w, n, y, ldy, s);
+            done = try_stream_mr<QT, ORDER, 0>(ctx, x, ldx * (int64_t)sizeof(float), m, k, w, n, y, ldy, s);
             if (s != CQ_OK) return s;
         }
         for (int64_t i = done; i < m; ++i) {  // one pass over the weights per remaining activation row

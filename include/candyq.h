@@ -102,7 +102,8 @@ cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream);
 cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
 /* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl, gemv_early (launch geometry of the
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
- * row); gemv_mma (3, default: CQ_ACT_F32 and CQ_ACT_Q8_1 batches of this many rows up to eight against Q4_0 run the
+ * row); gemv_q81_inline (1, default: one or two rows in CQ_ACT_Q8_1 quantize their activations inside the GEMV's
+ * set-up; 0: in a launch of their own first; the same bits either way); gemv_mma (3, default: CQ_ACT_F32 and CQ_ACT_Q8_1 batches of this many rows up to eight against Q4_0 run the
  * single-launch kernel with mma.sync block dots, two rows too against large weights, and CQ_ACT_F16 batches of up to
  * eight rows its f16 form; 0: never); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide
  * GEMM has seen: the weights must then stay unchanged, or be rewritten only through cq_* entry points, or

@@ -105,3 +105,27 @@ def test_bias_on_the_tensor_core_route(device):
     bias = np.random.default_rng(2).standard_normal(n).astype(np.float32)
     want = oc.qmatmul(oc.Q4_0, 0, x, blocks, n, nthreads=8) + bias
     assert rel_err(run(device, oc.Q4_0, 0, x, blocks, n, 2, bias=bias), want) < 1e-3
+
+
+@pytest.mark.parametrize("qt,order", QT_ORDERS)
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("n,k", [(600, 4096), (257, 11008), (96, 256)])
+def test_q8_1_activations_quantized_inside_the_gemv_give_the_same_bits(device, qt, order, m, n, k):
+    """One and two rows in CQ_ACT_Q8_1: the quantizer runs in the GEMV's set-up.  Its integers, scales and block sums
+    must be those of the separate quantize launch bit for bit, so the results are equal, including on rounding ties
+    (x / d = n + 0.5 exactly), all-zero blocks and subnormal scales."""
+    w, x = make_case(9300 + m + n + k, n, k, m)
+    x[0, :32] = (np.arange(32) - 16) + 0.5
+    x[0, 0] = 127.0
+    x[0, 32:64] = 0.0
+    x[m - 1, 64:96] = 1e-41
+    x[m - 1, 70] = -3e-41
+    blocks = oc.quantize(qt, order, w)
+    got = run(device, qt, order, x, blocks, n, 1)
+    device.set_option("gemv_q81_inline", 0)
+    try:
+        two_launches = run(device, qt, order, x, blocks, n, 1)
+    finally:
+        device.set_option("gemv_q81_inline", 1)
+    assert np.array_equal(got, two_launches)
+    assert rel_err(got, oc.qmatmul(qt, order, x, blocks, n, nthreads=8, q8_1=True)) < 2e-5
