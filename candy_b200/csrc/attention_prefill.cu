@@ -46,7 +46,7 @@ struct FaParams {
     void *o;
     float *lse;             // [b][h][seqlen_q] or null
     int64_t o_batch_stride, o_row_stride, o_head_stride;
-    int h, h_k, seqlen_q, seqlen_k;
+    int b, h, h_k, seqlen_q, seqlen_k;
     int causal;
     float scale_log2;       // softmax_scale * log2(e)
     float scale;            // softmax_scale
@@ -140,26 +140,39 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     float *sm_mx = reinterpret_cast<float *>(sm_v + (size_t)VS * Cfg::kVBytes);  // [2 tile parities][2 halves][128]: maxima of half rows
     float *sm_l = sm_mx + 4 * FA_M;                              // [2 halves][128] final sums
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm_l + 2 * FA_M);
-    uint64_t *q_full = bars, *k_full = q_full + 1, *k_empty = k_full + KS, *v_full = k_empty + KS, *s_full = v_full + VS, *s_empty = s_full + 1, *p_full = s_empty + 1,
+    uint64_t *q_full = bars, *q_empty = q_full + 1, *k_full = q_empty + 1, *k_empty = k_full + KS, *v_full = k_empty + KS, *s_full = v_full + VS, *s_empty = s_full + 1, *p_full = s_empty + 1,
              *o_full = p_full + 2, *o_empty = o_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heavy tiles (late query rows under a causal mask) first
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-    const int q0 = qt * FA_M;
+    // A CTA stays on its SM and takes one work item per round: an item is one tile of 128 query rows of one (head, batch).
+    // Items are numbered heavy first (late query rows under a causal mask have the most key tiles) and dealt out in
+    // alternating directions, which gives every CTA a similar load.  Between items nothing is torn down: the next
+    // item's Q and first K tiles are loaded, and its first score tile computed, while the compute warps still normalize
+    // and store the previous item's rows.  Every role walks the same list and keeps a running tile count g: stage
+    // indices and barrier phases follow g, not the tile's number inside its item.
     const int off = p.seqlen_k - p.seqlen_q;  // causal: key j is visible to row i iff j <= i + off
-    int ntiles = (p.seqlen_k + FA_N - 1) / FA_N;
-    if (p.causal) {
-        const int lim = q0 + FA_M + off;      // keys >= lim are masked for every row of this tile
-        const int t = lim <= 0 ? 0 : (lim + FA_N - 1) / FA_N;
-        ntiles = t < ntiles ? t : ntiles;
-    }
-    const int kv_head = head / (p.h / p.h_k);
+    const int nq = (p.seqlen_q + FA_M - 1) / FA_M, hb = p.h * p.b, items = nq * hb;
+    auto item_at = [&](int w, int &q0, int &head, int &batch, int &ntiles) {
+        const int qt = nq - 1 - w / hb, rem = w % hb;
+        head = rem % p.h, batch = rem / p.h;
+        q0 = qt * FA_M;
+        ntiles = (p.seqlen_k + FA_N - 1) / FA_N;
+        if (p.causal) {
+            const int lim = q0 + FA_M + off;  // keys >= lim are masked for every row of this tile
+            const int t = lim <= 0 ? 0 : (lim + FA_N - 1) / FA_N;
+            ntiles = t < ntiles ? t : ntiles;
+        }
+    };
+    const int kv_group = p.h / p.h_k;
+    // round rd hands out items rd * G .. rd * G + G - 1, forwards on even rounds and backwards on odd ones: the CTA that
+    // got the heaviest item of a round gets the lightest of the next
+    auto item_of_round = [&](int rd) { return (rd & 1) ? (rd + 1) * (int)gridDim.x - 1 - (int)blockIdx.x : rd * (int)gridDim.x + (int)blockIdx.x; };
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(q_full), 1);
+        mbar_init(smem_u32(q_empty), 1);
         for (int s = 0; s < KS; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
             mbar_init(smem_u32(&k_empty[s]), 1);
@@ -186,51 +199,68 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     if (warp == 0) {
         if (lane == 0) {
             pdl_wait_prior();  // Q, K come from earlier kernels, V^T from the transpose just before this one
-            mbar_expect_tx(smem_u32(q_full), Cfg::kQBytes);
-#pragma unroll
-            for (int c = 0; c < SLABS; ++c) tma_load_4d(smem_u32(sm_q + c * (FA_M * 128)), &tmQ, c * 64, head, q0, batch, smem_u32(q_full));
             bool ok = true;
-            auto load_k = [&](int t) {
-                const int s = t % KS;
-                if (t >= KS && !mbar_wait_sleep(smem_u32(&k_empty[s]), ((t / KS) - 1) & 1, 100)) {
+            int g = 0, qi = 0;  // key tiles and (non-empty) items loaded so far
+            for (int rd = 0; rd * (int)gridDim.x < items && ok; ++rd) {
+                const int w = item_of_round(rd);
+                if (w >= items) continue;
+                int q0, head, batch, ntiles;
+                item_at(w, q0, head, batch, ntiles);
+                if (ntiles == 0) continue;
+                const int kv_head = head / kv_group;
+                // Q has one buffer: free once the previous item's last score tile has been computed
+                if (qi >= 1 && !mbar_wait_sleep(smem_u32(q_empty), (qi - 1) & 1, 100)) {
                     atomicExch(p.err, kDevErrEmptyWait);
                     ok = false;
-                    return;
+                    break;
                 }
-                mbar_expect_tx(smem_u32(&k_full[s]), Cfg::kKBytes);
+                mbar_expect_tx(smem_u32(q_full), Cfg::kQBytes);
 #pragma unroll
-                for (int c = 0; c < SLABS; ++c)
-                    tma_load_4d(smem_u32(sm_k + (size_t)s * Cfg::kKBytes + c * (FA_N * 128)), &tmK, c * 64, kv_head, t * FA_N, batch, smem_u32(&k_full[s]));
-            };
-            auto load_v = [&](int t) {
-                const int s = t % VS;
-                // a V^T stage is free when the product that read it has finished: the barrier the compute warps wait on
-                // for that product (one commit per tile serves all three uses; VS == 2 == the number of product slots)
-                if (t >= VS && !mbar_wait_sleep(smem_u32(&o_full[s]), ((t / VS) - 1) & 1, 100)) {
-                    atomicExch(p.err, kDevErrEmptyWait);
-                    ok = false;
-                    return;
+                for (int c = 0; c < SLABS; ++c) tma_load_4d(smem_u32(sm_q + c * (FA_M * 128)), &tmQ, c * 64, head, q0, batch, smem_u32(q_full));
+                auto load_k = [&](int t) {  // t: tile of this item; its stage and phase follow g + t
+                    const int gt = g + t, s = gt % KS;
+                    if (gt >= KS && !mbar_wait_sleep(smem_u32(&k_empty[s]), ((gt / KS) - 1) & 1, 100)) {
+                        atomicExch(p.err, kDevErrEmptyWait);
+                        ok = false;
+                        return;
+                    }
+                    mbar_expect_tx(smem_u32(&k_full[s]), Cfg::kKBytes);
+#pragma unroll
+                    for (int c = 0; c < SLABS; ++c)
+                        tma_load_4d(smem_u32(sm_k + (size_t)s * Cfg::kKBytes + c * (FA_N * 128)), &tmK, c * 64, kv_head, t * FA_N, batch, smem_u32(&k_full[s]));
+                };
+                auto load_v = [&](int t) {
+                    const int gt = g + t, s = gt % VS;
+                    // a V^T stage is free when the product that read it has finished: the barrier the compute warps wait on
+                    // for that product (one commit per tile serves all three uses; VS == 2 == the number of product slots)
+                    if (gt >= VS && !mbar_wait_sleep(smem_u32(&o_full[s]), ((gt / VS) - 1) & 1, 100)) {
+                        atomicExch(p.err, kDevErrEmptyWait);
+                        ok = false;
+                        return;
+                    }
+                    mbar_expect_tx(smem_u32(&v_full[s]), Cfg::kVBytes);
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf)
+                        tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, t * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
+                                    smem_u32(&v_full[s]));
+                };
+                // K runs one tile ahead of V^T: K(0), K(1), V(0), K(2), V(1), ...
+                load_k(0);
+                for (int j = 0; j < ntiles && ok; ++j) {
+                    if (j + 1 < ntiles) load_k(j + 1);
+                    if (ok) load_v(j);
                 }
-                mbar_expect_tx(smem_u32(&v_full[s]), Cfg::kVBytes);
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf)
-                    tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, t * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
-                                smem_u32(&v_full[s]));
-            };
-            // K runs one tile ahead of V^T: K(0), K(1), V(0), K(2), V(1), ...
-            if (ntiles > 0) load_k(0);
-            for (int j = 0; j < ntiles && ok; ++j) {
-                if (j + 1 < ntiles) load_k(j + 1);
-                if (ok) load_v(j);
+                g += ntiles;
+                ++qi;
             }
-            if (ok) {  // leave only when nothing is in flight into this CTA's shared memory
-                if (!mbar_wait_sleep(smem_u32(q_full), 0, 100)) atomicExch(p.err, kDevErrDrain);
-                for (int j = ntiles > KS ? ntiles - KS : 0; j < ntiles && ok; ++j)
+            if (ok && qi > 0) {  // leave only when nothing is in flight into this CTA's shared memory
+                if (!mbar_wait_sleep(smem_u32(q_full), (qi - 1) & 1, 100)) atomicExch(p.err, kDevErrDrain);
+                for (int j = g > KS ? g - KS : 0; j < g && ok; ++j)
                     if (!mbar_wait_sleep(smem_u32(&k_full[j % KS]), (j / KS) & 1, 100)) {
                         atomicExch(p.err, kDevErrDrain);
                         ok = false;
                     }
-                for (int j = ntiles > VS ? ntiles - VS : 0; j < ntiles && ok; ++j)
+                for (int j = g > VS ? g - VS : 0; j < g && ok; ++j)
                     if (!mbar_wait_sleep(smem_u32(&v_full[j % VS]), (j / VS) & 1, 100)) {
                         atomicExch(p.err, kDevErrDrain);
                         ok = false;
@@ -238,51 +268,65 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && ntiles > 0) {
+        if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_16(FA_M, FA_N, BF16), idesc_o = idesc_16(FA_M, D, BF16);
-            bool ok = mbar_wait_bounded(smem_u32(q_full), 0);
-            if (!ok) atomicExch(p.err, kDevErrFullWait);
             const uint32_t q_addr = smem_u32(sm_q);
-            // S(j) = Q K(j)^T (one slot: the softmax warps free it as soon as they hold the scores in registers)
-            auto issue_qk = [&](int j) -> bool {
-                const int s = j % KS;
-                if (!mbar_wait_bounded(smem_u32(&k_full[s]), (j / KS) & 1)) return false;
-                if (j >= 1 && !mbar_wait_bounded(smem_u32(s_empty), (j - 1) & 1)) return false;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(sm_k + (size_t)s * Cfg::kKBytes);
-#pragma unroll
-                for (int c = 0; c < SLABS; ++c)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        tc_mma_f16(tmem_base + Cfg::kColS, smem_desc_k128(q_addr + c * (FA_M * 128) + kk * 32),
-                                   smem_desc_k128(k_addr + c * (FA_N * 128) + kk * 32), idesc_s, (c | kk) != 0);
-                tc_commit(smem_u32(s_full));
-                tc_commit(smem_u32(&k_empty[s]));  // the K tile is free once these MMAs have read it
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < ntiles && ok; ++j) {
-                if (j + 1 < ntiles) ok = issue_qk(j + 1);  // the next tile's scores are computed while this tile's softmax runs
-                if (!ok) break;
-                const int s = j % VS;
-                if (!mbar_wait_bounded(smem_u32(&v_full[s]), (j / VS) & 1)) {
+            bool ok = true;
+            int g = 0, qi = 0;
+            for (int rd = 0; rd * (int)gridDim.x < items && ok; ++rd) {
+                const int w = item_of_round(rd);
+                if (w >= items) continue;
+                int q0, head, batch, ntiles;
+                item_at(w, q0, head, batch, ntiles);
+                if (ntiles == 0) continue;
+                if (!mbar_wait_bounded(smem_u32(q_full), qi & 1)) {
                     ok = false;
                     break;
                 }
-                // P(j) in place, and the product slot free (the accumulate warps have folded tile j - 2)
-                if (!mbar_wait_bounded(smem_u32(&p_full[j & 1]), (j >> 1) & 1) || (j >= 2 && !mbar_wait_bounded(smem_u32(&o_empty[j & 1]), ((j >> 1) - 1) & 1))) {
-                    ok = false;
-                    break;
+                // S(t) = Q K(t)^T (one slot: the softmax warps free it as soon as they hold the scores in registers)
+                auto issue_qk = [&](int t) -> bool {
+                    const int gt = g + t, s = gt % KS;
+                    if (!mbar_wait_bounded(smem_u32(&k_full[s]), (gt / KS) & 1)) return false;
+                    if (gt >= 1 && !mbar_wait_bounded(smem_u32(s_empty), (gt - 1) & 1)) return false;
+                    tc_fence_after();
+                    const uint32_t k_addr = smem_u32(sm_k + (size_t)s * Cfg::kKBytes);
+#pragma unroll
+                    for (int c = 0; c < SLABS; ++c)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            tc_mma_f16(tmem_base + Cfg::kColS, smem_desc_k128(q_addr + c * (FA_M * 128) + kk * 32),
+                                       smem_desc_k128(k_addr + c * (FA_N * 128) + kk * 32), idesc_s, (c | kk) != 0);
+                    tc_commit(smem_u32(s_full));
+                    tc_commit(smem_u32(&k_empty[s]));  // the K tile is free once these MMAs have read it
+                    if (t == ntiles - 1) tc_commit(smem_u32(q_empty));  // and so is Q after the item's last score tile
+                    return true;
+                };
+                ok = issue_qk(0);
+                for (int j = 0; j < ntiles && ok; ++j) {
+                    if (j + 1 < ntiles) ok = issue_qk(j + 1);  // the next tile's scores are computed while this tile's softmax runs
+                    if (!ok) break;
+                    const int gj = g + j, s = gj % VS, slot = gj & 1;
+                    if (!mbar_wait_bounded(smem_u32(&v_full[s]), (gj / VS) & 1)) {
+                        ok = false;
+                        break;
+                    }
+                    // P in place, and the product slot free (the accumulate warps have folded the tile two back)
+                    if (!mbar_wait_bounded(smem_u32(&p_full[slot]), (gj >> 1) & 1) || (gj >= 2 && !mbar_wait_bounded(smem_u32(&o_empty[slot]), ((gj >> 1) - 1) & 1))) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t v_addr = smem_u32(sm_v + (size_t)s * Cfg::kVBytes);
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)  // 16 keys per step: 8 tensor-memory columns of P, 32 bytes of a V^T row
+                            tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)(slot * D), tmem_base + Cfg::kColP + (uint32_t)(slot * 64 + (hf * 4 + kk) * 8),
+                                          smem_desc_k128(v_addr + hf * (D * 128) + kk * 32), idesc_o, (hf | kk) != 0);
+                    tc_commit(smem_u32(&o_full[slot]));  // product ready; its P slot and V^T stage free
                 }
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(sm_v + (size_t)s * Cfg::kVBytes);
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)  // 16 keys per step: 8 tensor-memory columns of P, 32 bytes of a V^T row
-                        tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)((j & 1) * D), tmem_base + Cfg::kColP + (uint32_t)((j & 1) * 64 + (hf * 4 + kk) * 8),
-                                      smem_desc_k128(v_addr + hf * (D * 128) + kk * 32), idesc_o, (hf | kk) != 0);
-                tc_commit(smem_u32(&o_full[j & 1]));  // product ready; its P slot and V^T stage free
+                g += ntiles;
+                ++qi;
             }
             if (!ok) atomicExch(p.err, kDevErrMma);
         }
@@ -296,22 +340,16 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         // factor never leaves the thread that computed it.
         constexpr int HC = FA_N / 2, HD = D / 2;
         const int quarter = warp & 3, half = (warp - 2) >> 2, r = quarter * 32 + lane;
-        const int row = q0 + r;                                    // global query index
-        const int causal_lim = p.causal ? row + off : 0x7FFFFFFF;  // last visible key
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float m_run = -INFINITY, l_run = 0.0f;  // running max of the raw scores (whole row), running sum (this half)
-        float alpha_prev = 0.0f;                // the factor of the tile whose product is folded next
-        float acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
-        bool ok = true;
-        auto fold = [&](int jt, float alpha) -> bool {  // acc = acc * alpha + (P V)(jt), this thread's half of the columns
-            if (!mbar_wait_bounded(smem_u32(&o_full[jt & 1]), (jt >> 1) & 1)) {
+        bool ok = true, waited_prior = false;
+        int g = 0;
+        auto fold = [&](int gt, float alpha, float (&acc)[HD]) -> bool {  // acc = acc * alpha + (P V)(gt), this thread's half of the columns
+            if (!mbar_wait_bounded(smem_u32(&o_full[gt & 1]), (gt >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.err, kDevErrFullWait);
                 return false;
             }
             tc_fence_after();
-            const uint32_t o_addr = lane_addr + Cfg::kColO + (uint32_t)((jt & 1) * D + half * HD);
+            const uint32_t o_addr = lane_addr + Cfg::kColO + (uint32_t)((gt & 1) * D + half * HD);
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t v[32];
@@ -321,105 +359,124 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&o_empty[jt & 1]));
+            if (lane == 0) mbar_arrive(smem_u32(&o_empty[gt & 1]));
             return true;
         };
-        for (int j = 0; j < ntiles; ++j) {
-            const int buf = j & 1;
-            // A warp whose wait gave up keeps walking the tiles without waiting or computing, so that its partner
-            // (the other half of the rows' columns) still finds it at the named barrier below.
-            if (ok && !mbar_wait_bounded(smem_u32(s_full), j & 1)) {
-                if (lane == 0) atomicExch(p.err, kDevErrFullWait);
-                ok = false;
-            }
-            if (!ok) {
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-                continue;
-            }
-            tc_fence_after();
-            const int kmax = min(p.seqlen_k - 1, causal_lim) - j * FA_N - half * HC;  // columns > kmax of this half are masked
-            // this half of the row's scores: read out of tensor memory once, kept in registers for both steps
-            uint32_t sv[HC];
+        for (int rd = 0; rd * (int)gridDim.x < items; ++rd) {
+            const int w = item_of_round(rd);
+            if (w >= items) continue;
+            int q0, head, batch, ntiles;
+            item_at(w, q0, head, batch, ntiles);
+            const int row = q0 + r;                                    // global query index
+            const int causal_lim = p.causal ? row + off : 0x7FFFFFFF;  // last visible key
+            float m_run = -INFINITY, l_run = 0.0f;  // running max of the raw scores (whole row), running sum (this half)
+            float alpha_prev = 0.0f;                // the factor of the tile whose product is folded next
+            float acc[HD];
 #pragma unroll
-            for (int c = 0; c < HC / 32; ++c) tmem_ld32_async(lane_addr + Cfg::kColS + (uint32_t)(half * HC + c * 32), sv + c * 32);
-            tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(s_empty));  // the scores are in registers: the next tile's may be computed
-            const bool cut = kmax < HC - 1;  // only a tile that the causal diagonal or the end of the keys cuts needs the mask
-            float m_half = -INFINITY;
-            if (!cut) {
-                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int i = 0; i < HC; i += 4) {
-                    m4[0] = fmaxf(m4[0], __uint_as_float(sv[i])), m4[1] = fmaxf(m4[1], __uint_as_float(sv[i + 1]));
-                    m4[2] = fmaxf(m4[2], __uint_as_float(sv[i + 2])), m4[3] = fmaxf(m4[3], __uint_as_float(sv[i + 3]));
+            for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
+            for (int j = 0; j < ntiles; ++j) {
+                const int gj = g + j, buf = gj & 1;
+                // A warp whose wait gave up keeps walking the tiles without waiting or computing, so that its partner
+                // (the other half of the rows' columns) still finds it at the named barrier below.
+                if (ok && !mbar_wait_bounded(smem_u32(s_full), gj & 1)) {
+                    if (lane == 0) atomicExch(p.err, kDevErrFullWait);
+                    ok = false;
                 }
-                m_half = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            } else {
+                if (!ok) {
+                    asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+                    continue;
+                }
+                tc_fence_after();
+                const int kmax = min(p.seqlen_k - 1, causal_lim) - j * FA_N - half * HC;  // columns > kmax of this half are masked
+                // this half of the row's scores: read out of tensor memory once, kept in registers for both steps
+                uint32_t sv[HC];
 #pragma unroll
-                for (int i = 0; i < HC; ++i)
-                    if (i <= kmax) m_half = fmaxf(m_half, __uint_as_float(sv[i]));
-            }
-            // the row's maximum over both halves
-            sm_mx[(buf * 2 + half) * FA_M + r] = m_half;
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-            const float m_tile = fmaxf(m_half, sm_mx[(buf * 2 + (half ^ 1)) * FA_M + r]);
-            const float m_new = fmaxf(m_run, m_tile);
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // a row with no visible key yet: every p is 0
-            const float alpha = fast_ex2((m_run - m_use) * p.scale_log2);  // m_run = -inf gives 0: nothing accumulated yet
-            const float mb = m_use * p.scale_log2;
-            // P has two slots: the product that read this one (two tiles back) has finished -- this warp folded it
-            // at the end of the previous iteration.
-            // p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
-            float l2[2] = {0.0f, 0.0f};
+                for (int c = 0; c < HC / 32; ++c) tmem_ld32_async(lane_addr + Cfg::kColS + (uint32_t)(half * HC + c * 32), sv + c * 32);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(s_empty));  // the scores are in registers: the next tile's may be computed
+                const bool cut = kmax < HC - 1;  // only a tile that the causal diagonal or the end of the keys cuts needs the mask
+                float m_half = -INFINITY;
+                if (!cut) {
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int c0 = c * 32 + 2 * i;
-                    float p0 = fast_ex2(fmaf(__uint_as_float(sv[c0]), p.scale_log2, -mb));
-                    float p1 = fast_ex2(fmaf(__uint_as_float(sv[c0 + 1]), p.scale_log2, -mb));
-                    if (cut) {
-                        p0 = c0 <= kmax ? p0 : 0.0f;
-                        p1 = c0 + 1 <= kmax ? p1 : 0.0f;
+                    for (int i = 0; i < HC; i += 4) {
+                        m4[0] = fmaxf(m4[0], __uint_as_float(sv[i])), m4[1] = fmaxf(m4[1], __uint_as_float(sv[i + 1]));
+                        m4[2] = fmaxf(m4[2], __uint_as_float(sv[i + 2])), m4[3] = fmaxf(m4[3], __uint_as_float(sv[i + 3]));
                     }
-                    l2[0] += p0, l2[1] += p1;
-                    pk[i] = pack2<BF16>(p0, p1);
-                }
-                tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(buf * (FA_N / 2) + half * (HC / 2) + c * 16), pk);
-            }
-            tmem_wait_st();
-            l_run = l_run * alpha + (l2[0] + l2[1]);
-            m_run = m_new;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));  // this warp's part of P is in place
-            // the previous tile's product, while the tensor core works on this tile's
-            if (j >= 1) ok = fold(j - 1, alpha_prev);
-            alpha_prev = alpha;
-        }
-        if (ok && ntiles > 0) ok = fold(ntiles - 1, alpha_prev);
-        // the row's sum over both halves (both used the same maxima)
-        sm_l[half * FA_M + r] = l_run;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-        const float l = l_run + sm_l[(half ^ 1) * FA_M + r];
-        if (half == 0 && p.lse && row < p.seqlen_q)  // kernels/softmax.h:206: max * scale + log(sum); +inf for a row with nothing to attend to
-            p.lse[((int64_t)batch * p.h + head) * p.seqlen_q + row] = (l == 0.0f || l != l) ? INFINITY : m_run * p.scale + logf(l);
-        if (ok && row < p.seqlen_q) {
-            pdl_wait_prior();  // the output buffer may still be read by an earlier kernel
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // nothing to attend to: zeros, as the reference writes
-            uint16_t *dst = reinterpret_cast<uint16_t *>(p.o) + (int64_t)batch * p.o_batch_stride + (int64_t)row * p.o_row_stride + (int64_t)head * p.o_head_stride +
-                            half * HD;
+                    m_half = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                } else {
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                uint4 w;
-                w.x = pack2<BF16>(acc[8 * c] * inv, acc[8 * c + 1] * inv);
-                w.y = pack2<BF16>(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
-                w.z = pack2<BF16>(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
-                w.w = pack2<BF16>(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
-                reinterpret_cast<uint4 *>(dst)[c] = w;
+                    for (int i = 0; i < HC; ++i)
+                        if (i <= kmax) m_half = fmaxf(m_half, __uint_as_float(sv[i]));
+                }
+                // the row's maximum over both halves
+                sm_mx[(buf * 2 + half) * FA_M + r] = m_half;
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+                const float m_tile = fmaxf(m_half, sm_mx[(buf * 2 + (half ^ 1)) * FA_M + r]);
+                const float m_new = fmaxf(m_run, m_tile);
+                const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // a row with no visible key yet: every p is 0
+                const float alpha = fast_ex2((m_run - m_use) * p.scale_log2);  // m_run = -inf gives 0: nothing accumulated yet
+                const float mb = m_use * p.scale_log2;
+                // P has two slots: the product that read this one (two tiles back) has finished -- this warp folded it
+                // at the end of the previous iteration (the last tile of the previous item right after its loop).
+                // p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
+                float l2[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int c = 0; c < HC / 32; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int c0 = c * 32 + 2 * i;
+                        float p0 = fast_ex2(fmaf(__uint_as_float(sv[c0]), p.scale_log2, -mb));
+                        float p1 = fast_ex2(fmaf(__uint_as_float(sv[c0 + 1]), p.scale_log2, -mb));
+                        if (cut) {
+                            p0 = c0 <= kmax ? p0 : 0.0f;
+                            p1 = c0 + 1 <= kmax ? p1 : 0.0f;
+                        }
+                        l2[0] += p0, l2[1] += p1;
+                        pk[i] = pack2<BF16>(p0, p1);
+                    }
+                    tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(buf * (FA_N / 2) + half * (HC / 2) + c * 16), pk);
+                }
+                tmem_wait_st();
+                l_run = l_run * alpha + (l2[0] + l2[1]);
+                m_run = m_new;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));  // this warp's part of P is in place
+                // the previous tile's product, while the tensor core works on this tile's
+                if (j >= 1) ok = fold(gj - 1, alpha_prev, acc);
+                alpha_prev = alpha;
+            }
+            if (ok && ntiles > 0) ok = fold(g + ntiles - 1, alpha_prev, acc);
+            g += ntiles;
+            // the row's sum over both halves (both used the same maxima); the second barrier keeps the next item's sums
+            // out of the buffer until the partner has read this item's
+            sm_l[half * FA_M + r] = l_run;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            const float l = l_run + sm_l[(half ^ 1) * FA_M + r];
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            if (!waited_prior) {
+                pdl_wait_prior();  // the output buffers may still be read by an earlier kernel
+                waited_prior = true;
+            }
+            if (half == 0 && p.lse && row < p.seqlen_q)  // kernels/softmax.h:206: max * scale + log(sum); +inf for a row with nothing to attend to
+                p.lse[((int64_t)batch * p.h + head) * p.seqlen_q + row] = (l == 0.0f || l != l) ? INFINITY : m_run * p.scale + logf(l);
+            if (ok && row < p.seqlen_q) {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // nothing to attend to: zeros, as the reference writes
+                uint16_t *dst = reinterpret_cast<uint16_t *>(p.o) + (int64_t)batch * p.o_batch_stride + (int64_t)row * p.o_row_stride + (int64_t)head * p.o_head_stride +
+                                half * HD;
+#pragma unroll
+                for (int c = 0; c < HD / 8; ++c) {
+                    uint4 wv;
+                    wv.x = pack2<BF16>(acc[8 * c] * inv, acc[8 * c + 1] * inv);
+                    wv.y = pack2<BF16>(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
+                    wv.z = pack2<BF16>(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
+                    wv.w = pack2<BF16>(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
+                    reinterpret_cast<uint4 *>(dst)[c] = wv;
+                }
             }
         }
     }
@@ -528,10 +585,12 @@ cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr,
     FaParams p;
     p.o = o_ptr, p.lse = static_cast<float *>(softmax_lse_ptr);
     p.o_batch_stride = o_batch_stride, p.o_row_stride = o_row_stride, p.o_head_stride = o_head_stride;
-    p.h = (int)h, p.h_k = (int)h_k, p.seqlen_q = (int)seqlen_q, p.seqlen_k = (int)seqlen_k, p.causal = is_causal ? 1 : 0;
+    p.b = (int)b, p.h = (int)h, p.h_k = (int)h_k, p.seqlen_q = (int)seqlen_q, p.seqlen_k = (int)seqlen_k, p.causal = is_causal ? 1 : 0;
     p.scale = softmax_scale, p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.err = ctx->dev_err_devptr;
-    const dim3 grid((seqlen_q + FA_M - 1) / FA_M, h, b);
+    // persistent CTAs, one per SM (the kernel's shared memory allows no more), each walking its share of the work items
+    const int64_t items = (int64_t)((seqlen_q + FA_M - 1) / FA_M) * h * b;
+    const dim3 grid((unsigned)(items < ctx->sm_count ? items : ctx->sm_count));
     if (d == 128) return bf ? run_fa<128, true>(ctx, tq, tk, tv, p, grid) : run_fa<128, false>(ctx, tq, tk, tv, p, grid);
     return bf ? run_fa<64, true>(ctx, tq, tk, tv, p, grid) : run_fa<64, false>(ctx, tq, tk, tv, p, grid);
 }

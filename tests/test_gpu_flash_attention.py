@@ -89,6 +89,20 @@ def test_long_causal_sequence(device):
     assert err <= 2e-3 and lse_err <= 2e-3
 
 
+@pytest.mark.parametrize("b,h,hk,sq,sk,d,causal,bf16", [
+    (2, 20, 4, 1024, 1024, 128, True, False),   # 320 work items: up to three per CTA, dealt out in alternating directions
+    (1, 40, 40, 640, 384, 64, False, False),    # 200 items, all of the same length
+    (1, 48, 8, 600, 200, 128, True, False),     # 240 items, those of the first 400 rows see no key at all (zero key tiles)
+    (3, 25, 5, 500, 500, 128, True, True),      # 300 items, ragged last tiles, bf16
+])
+def test_more_work_items_than_ctas(device, b, h, hk, sq, sk, d, causal, bf16):
+    """The kernel's CTAs are persistent: with more (query tile, head, batch) items than SMs a CTA runs several in a row,
+    re-using its Q buffer, its key / value stages and its tensor memory with phases that carry on across items."""
+    err, lse_err = run_case(device, b, h, hk, sq, sk, d, causal, bf16)
+    assert err <= (1.5e-2 if bf16 else 2e-3), err
+    assert lse_err <= 2e-3, lse_err
+
+
 def test_packed_qkv_strides_and_the_reference_symbol(device):
     err, lse_err = run_case(device, 2, 4, 2, 256, 256, 128, True, False, packed=True)
     assert err <= 2e-3 and lse_err <= 2e-3
