@@ -5,8 +5,12 @@
 // FlashAttention-2 for sm_80 built on CUTLASS (a submodule that is absent from the checkout); this is a from-scratch
 // sm_100a kernel with the same contract for the cases a decoder's prompt phase needs.
 //
-// One CTA per (128 query rows, head, batch); keys and values stream through in tiles of 128 keys.
-//   warp 0        TMA: the Q tile once, then K tiles into a three-stage ring and V^T tiles into a two-stage ring of
+// A work item is (128 query rows, head, batch); keys and values stream through in tiles of 128 keys.  One persistent CTA
+// per SM walks its share of the items (heavy first, dealt out in alternating directions): the rings, the barriers'
+// phases and the tensor memory carry on from one item to the next, so the next item's Q, first keys and first score
+// tile overlap the previous item's normalization and store (measured against one CTA per item: 32 heads x 2048 causal
+// 95.8 -> 79.6 us, 2 x 64 heads x 4096 858 -> 760 us; a plain round-robin instead of alternating directions: 89.8 us).
+//   warp 0        TMA: the item's Q tile, then K tiles into a three-stage ring and V^T tiles into a two-stage ring of
 //                 its own (128-byte swizzle); a K tile is free as soon as its scores exist, long before its V^T
 //   warp 1        tcgen05.mma issue: S = Q K^T into a 128-column f32 slot of tensor memory (one slot: the compute
 //                 warps release it once the scores sit in their registers), O_tile = P V with P read from tensor
