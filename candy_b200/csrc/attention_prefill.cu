@@ -10,8 +10,8 @@
 // phases and the tensor memory carry on from one item to the next, so the next item's Q, first keys and first score
 // tile overlap the previous item's normalization and store (measured against one CTA per item: 32 heads x 2048 causal
 // 95.8 -> 79.6 us, 2 x 64 heads x 4096 858 -> 760 us; a plain round-robin instead of alternating directions: 89.8 us).
-//   warp 0        TMA: the item's Q tile, then K tiles into a three-stage ring and V^T tiles into a two-stage ring of
-//                 its own (128-byte swizzle); a K tile is free as soon as its scores exist, long before its V^T
+//   warp 0        TMA: the item's Q tile, then K tiles into a three-stage ring and V tiles into a two-stage ring of
+//                 its own (128-byte swizzle); a K tile is free as soon as its scores exist, long before its V
 //   warp 1        tcgen05.mma issue: S = Q K^T into a 128-column f32 slot of tensor memory (one slot: the compute
 //                 warps release it once the scores sit in their registers), O_tile = P V with P read from tensor
 //                 memory as the A operand into one of two product slots; one commit per product
@@ -30,8 +30,10 @@
 // Keeping Q in tensor memory as the A operand of S, so that only K is read from shared memory, changed nothing
 // (measured, not kept), and so did two S slots with one product slot: the MMAs are neither starved for operands
 // nor held back by the S slot.
-// V is [key][d] in memory but the P V product wants it K-major, i.e. [d][key]: a small kernel transposes it into
-// context scratch first (2 x the V bytes of traffic against O(seq^2 d) of compute).
+// V is [key][d] in memory, i.e. N-major for the P V product: the tile is loaded like a K tile and handed to the tensor
+// core with an N-major operand descriptor (8-row groups along the keys, 64-wide slabs of d a tile's 16 KB apart).  A V
+// the tensor maps cannot address (rows not 16-byte aligned) is transposed into context scratch by a small kernel first
+// and read as a K-major V^T (the first form of this kernel did that always: 79.6 us against 58.5 at 32 heads x 2048).
 // Every wait is bounded; tensor memory is always freed.
 #include <cuda_bf16.h>
 
@@ -131,7 +133,7 @@ struct FaCfg {
     static_assert(kColO + 2 * D <= 512, "tensor memory");
 };
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool VT>
 __global__ void __launch_bounds__(FA_THREADS, 1)
     fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmVt, const FaParams p) {
     using Cfg = FaCfg<D, BF16>;
@@ -243,10 +245,16 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                         return;
                     }
                     mbar_expect_tx(smem_u32(&v_full[s]), Cfg::kVBytes);
+                    if (VT) {
 #pragma unroll
-                    for (int hf = 0; hf < 2; ++hf)
-                        tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, t * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
-                                    smem_u32(&v_full[s]));
+                        for (int hf = 0; hf < 2; ++hf)
+                            tma_load_3d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + hf * (D * 128)), &tmVt, t * FA_N + hf * 64, 0, batch * p.h_k + kv_head,
+                                        smem_u32(&v_full[s]));
+                    } else {  // the V tile as it lies in memory, [key][d], loaded like a K tile
+#pragma unroll
+                        for (int c = 0; c < SLABS; ++c)
+                            tma_load_4d(smem_u32(sm_v + (size_t)s * Cfg::kVBytes + c * (FA_N * 128)), &tmVt, c * 64, kv_head, t * FA_N, batch, smem_u32(&v_full[s]));
+                    }
                 };
                 // K runs one tile ahead of V^T: K(0), K(1), V(0), K(2), V(1), ...
                 load_k(0);
@@ -324,9 +332,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)  // 16 keys per step: 8 tensor-memory columns of P, 32 bytes of a V^T row
-                            tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)(slot * D), tmem_base + Cfg::kColP + (uint32_t)(slot * 64 + (hf * 4 + kk) * 8),
-                                          smem_desc_k128(v_addr + hf * (D * 128) + kk * 32), idesc_o, (hf | kk) != 0);
+                        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step: 8 tensor-memory columns of P
+                            // V^T: 32 bytes further along a row of 64 keys (K-major operand).  V itself: 16 rows of 128 bytes further
+                            // down (the operand is N-major: d runs along a row, 64-wide slabs of d lie FA_N * 128 bytes apart)
+                            const uint64_t bdesc = VT ? smem_desc_k128(v_addr + hf * (D * 128) + kk * 32) : smem_desc_mn128(v_addr + (hf * 4 + kk) * 2048, FA_N * 128);
+                            tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)(slot * D), tmem_base + Cfg::kColP + (uint32_t)(slot * 64 + (hf * 4 + kk) * 8), bdesc,
+                                          VT ? idesc_o : (idesc_o | (1u << 16)), (hf | kk) != 0);
+                        }
                     tc_commit(smem_u32(&o_full[slot]));  // product ready; its P slot and V^T stage free
                 }
                 g += ntiles;
@@ -512,11 +524,11 @@ bool make_vt_map(CUtensorMap *map, const void *base, bool bf16, int d, int sk, i
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool VT>
 cq_status run_fa(cq_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const FaParams &p, dim3 grid) {
     static thread_local int configured = -1;
     if (configured != ctx->device) {
-        CQ_CUDA(ctx, cudaFuncSetAttribute(fmha_fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FaCfg<D, BF16>::kSmem));
+        CQ_CUDA(ctx, cudaFuncSetAttribute(fmha_fwd_kernel<D, BF16, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FaCfg<D, BF16>::kSmem));
         configured = ctx->device;
     }
     cudaLaunchConfig_t cfg = {};
@@ -529,7 +541,7 @@ cq_status run_fa(cq_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, cons
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
-    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, fmha_fwd_kernel<D, BF16>, tq, tk, tv, p));
+    CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, fmha_fwd_kernel<D, BF16, VT>, tq, tk, tv, p));
     return CQ_OK;
 }
 
@@ -561,13 +573,18 @@ cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr,
         if (reinterpret_cast<uintptr_t>(ptr) & 15) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: q, k, o must be 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(v_ptr) & 1) return cq_fail(ctx, CQ_ERR_INVALID_ARG, "flash attention: v must be 2-byte aligned");
     if (seqlen_q > (1u << 24) || seqlen_k > (1u << 24) || (uint64_t)b * h > 65535u * 65535ull) return cq_fail(ctx, CQ_ERR_TOO_LARGE, "flash attention: sequence beyond 2^24");
-    // V^T in context scratch
-    const int sk_pad = (int)((seqlen_k + 7) & ~7u);
-    const size_t vt_bytes = (size_t)b * h_k * d * sk_pad * 2;
-    cq_status s = cq_reserve_scratch(ctx, vt_bytes);
-    if (s != CQ_OK) return s;
-    uint16_t *vt = static_cast<uint16_t *>(ctx->scratch);
-    {
+    // V tiles are read where they lie when the tensor maps can address them (16-byte rows); otherwise, or on request
+    // (option fa_transpose_v), V is transposed into context scratch first and read as V^T
+    const bool v_direct = !ctx->tune.fa_transpose_v && v_batch_stride % 8 == 0 && v_row_stride % 8 == 0 && v_head_stride % 8 == 0 &&
+                          (reinterpret_cast<uintptr_t>(v_ptr) & 15) == 0;
+    CUtensorMap tq, tk, tv;
+    const bool bf = is_bf16 != 0;
+    if (!v_direct) {
+        const int sk_pad = (int)((seqlen_k + 7) & ~7u);
+        const size_t vt_bytes = (size_t)b * h_k * d * sk_pad * 2;
+        cq_status s = cq_reserve_scratch(ctx, vt_bytes);
+        if (s != CQ_OK) return s;
+        uint16_t *vt = static_cast<uint16_t *>(ctx->scratch);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)((sk_pad + 31) / 32), (unsigned)((d + 31) / 32), (unsigned)(b * h_k));
         cfg.blockDim = dim3(256);
@@ -579,12 +596,13 @@ cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr,
         cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
         CQ_CUDA(ctx, cudaLaunchKernelEx(&cfg, fa_transpose_v_kernel, (const uint16_t *)v_ptr, (int64_t)v_batch_stride, (int64_t)v_row_stride,
                                         (int64_t)v_head_stride, (int)h_k, (int)d, (int)seqlen_k, sk_pad, vt));
+        if (!make_vt_map(&tv, vt, bf, (int)d, (int)seqlen_k, sk_pad, (int)(b * h_k)))
+            return cq_fail(ctx, CQ_ERR_CUDA, "flash attention: cuTensorMapEncodeTiled failed or is unavailable");
+    } else if (!make_qk_map(&tv, v_ptr, bf, (int)d, (int)h_k, (int)seqlen_k, (int)b, v_head_stride, v_row_stride, v_batch_stride)) {
+        return cq_fail(ctx, CQ_ERR_CUDA, "flash attention: cuTensorMapEncodeTiled failed or is unavailable");
     }
-    CUtensorMap tq, tk, tv;
-    const bool bf = is_bf16 != 0;
     if (!make_qk_map(&tq, q_ptr, bf, (int)d, (int)h, (int)seqlen_q, (int)b, q_head_stride, q_row_stride, q_batch_stride) ||
-        !make_qk_map(&tk, k_ptr, bf, (int)d, (int)h_k, (int)seqlen_k, (int)b, k_head_stride, k_row_stride, k_batch_stride) ||
-        !make_vt_map(&tv, vt, bf, (int)d, (int)seqlen_k, sk_pad, (int)(b * h_k)))
+        !make_qk_map(&tk, k_ptr, bf, (int)d, (int)h_k, (int)seqlen_k, (int)b, k_head_stride, k_row_stride, k_batch_stride))
         return cq_fail(ctx, CQ_ERR_CUDA, "flash attention: cuTensorMapEncodeTiled failed or is unavailable");
     FaParams p;
     p.o = o_ptr, p.lse = static_cast<float *>(softmax_lse_ptr);
@@ -595,8 +613,12 @@ cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr,
     // persistent CTAs, one per SM (the kernel's shared memory allows no more), each walking its share of the work items
     const int64_t items = (int64_t)((seqlen_q + FA_M - 1) / FA_M) * h * b;
     const dim3 grid((unsigned)(items < ctx->sm_count ? items : ctx->sm_count));
-    if (d == 128) return bf ? run_fa<128, true>(ctx, tq, tk, tv, p, grid) : run_fa<128, false>(ctx, tq, tk, tv, p, grid);
-    return bf ? run_fa<64, true>(ctx, tq, tk, tv, p, grid) : run_fa<64, false>(ctx, tq, tk, tv, p, grid);
+    if (v_direct) {
+        if (d == 128) return bf ? run_fa<128, true, false>(ctx, tq, tk, tv, p, grid) : run_fa<128, false, false>(ctx, tq, tk, tv, p, grid);
+        return bf ? run_fa<64, true, false>(ctx, tq, tk, tv, p, grid) : run_fa<64, false, false>(ctx, tq, tk, tv, p, grid);
+    }
+    if (d == 128) return bf ? run_fa<128, true, true>(ctx, tq, tk, tv, p, grid) : run_fa<128, false, true>(ctx, tq, tk, tv, p, grid);
+    return bf ? run_fa<64, true, true>(ctx, tq, tk, tv, p, grid) : run_fa<64, false, true>(ctx, tq, tk, tv, p, grid);
 }
 
 // The reference's own entry point, same symbol and signature (flash_api.h:71-117): a host that binds run_mha

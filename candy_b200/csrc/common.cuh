@@ -46,6 +46,7 @@ struct GemvTuning {
     int i8_min_rows_f32 = 3;
     int i8_min_rows_q8_1 = 3;
     int gemv_mma = 3;       // CQ_ACT_F32, Q4_0: batches of this many rows up to 8 take the single-launch mma.sync kernel (0: never)
+    int fa_transpose_v = 0;   // prefill attention: 1 = always transpose V into scratch first (0: read V tiles in place when their strides allow)
     int gemv_q81_inline = 1;  // CQ_ACT_Q8_1, one or two rows: quantize the activations inside the GEMV's set-up (0: a launch of its own first)
     int gemv_multirow = 1;  // 0: one launch (one weight pass) per activation row even for m = 2..8
     int gemv_variant = 0;   // 0: 16-bit block fixed point (default), 1: f32 FMA, 2 / 3: two / three int8 slices

@@ -42,6 +42,13 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
+// Descriptor of an MN-major operand tile ([k rows][128 bytes of consecutive m / n], 128-byte swizzle, as a TMA load of a
+// row-major [k][n] matrix writes it): 8-row groups 1024 bytes apart along k, 64-element slabs `slab_bytes` apart along
+// m / n.  The instruction descriptor must mark the operand as MN-major (bit 15 for A, bit 16 for B).
+__device__ __forceinline__ uint64_t smem_desc_mn128(uint32_t smem_addr, uint32_t slab_bytes) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((slab_bytes >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
 // kind::f16 instruction descriptor: D f32, A/B f16, both K-major, M x N.
 __host__ __device__ constexpr uint32_t idesc_f16(int mm, int nn) {
     return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(nn >> 3) << 17) | ((uint32_t)(mm >> 4) << 24);

@@ -115,7 +115,8 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
  * weight pass per batch; 0: the decode kernels, up to eight rows a pass); attn_variant (decode attention: 1 = one CTA per 32-key chunk for grouped heads instead of split contexts, 2 = never the
  * single-launch cluster kernel of short contexts); comm_poll_limit (polls before the reducing
  * norm gives up on a peer's data, default about one second's worth); comm_cluster; host_zero_copy (see
- * cq_qmatmul_host). */
+ * cq_qmatmul_host); fa_transpose_v (1: cq_flash_attention always transposes V into scratch first; 0, default: V tiles
+ * are read in place when V is 16-byte aligned with strides that are multiples of 8 elements). */
 /* Grows the context's scratch memory to at least `bytes` now, so that no later call has to (scratch cannot
  * grow while the stream is being captured: such a call fails with CQ_ERR_INVALID_ARG and leaves the capture
  * intact).  A block outgrown while graphs made by cq_capture_end exist is kept until the last of them is

@@ -103,6 +103,23 @@ def test_more_work_items_than_ctas(device, b, h, hk, sq, sk, d, causal, bf16):
     assert lse_err <= 2e-3, lse_err
 
 
+@pytest.mark.parametrize("b,h,hk,sq,sk,d,causal,bf16", [
+    (1, 8, 2, 200, 333, 128, True, False),
+    (1, 2, 1, 64, 300, 64, False, True),
+    (2, 20, 4, 1024, 1024, 128, True, False),
+])
+def test_value_tiles_through_the_transposed_copy(device, b, h, hk, sq, sk, d, causal, bf16):
+    """By default the kernel reads V tiles where they lie (an N-major tensor-core operand); a V whose strides the tensor
+    maps cannot address is transposed into scratch first and read as V^T.  The option forces that second route."""
+    device.set_option("fa_transpose_v", 1)
+    try:
+        err, lse_err = run_case(device, b, h, hk, sq, sk, d, causal, bf16)
+    finally:
+        device.set_option("fa_transpose_v", 0)
+    assert err <= (1.5e-2 if bf16 else 2e-3), err
+    assert lse_err <= 2e-3, lse_err
+
+
 def test_packed_qkv_strides_and_the_reference_symbol(device):
     err, lse_err = run_case(device, 2, 4, 2, 256, 256, 128, True, False, packed=True)
     assert err <= 2e-3 and lse_err <= 2e-3
