@@ -366,8 +366,9 @@ cq_status cq_decoder_destroy(cq_ctx *ctx, cq_decoder *dec);
  * [batch][h][seqlen_q] f32 = max * scale + log(sum) (kernels/softmax.h:206).  Built: head dimensions 64 and
  * 128, strides that are multiples of 8 elements.  Not built (CQ_ERR_UNSUPPORTED): other head dimensions,
  * ALiBi, cu_seqlens (variable-length batches), sliding windows, soft-capping, the unpadded LSE layout.
- * V is transposed into context scratch first (cq_reserve(b * h_k * d * roundup(seqlen_k, 8) * 2) up front
- * when capturing).  cq_flash_attention returns a status and runs on the context's stream; run_mha is the
+ * V is read in place when it is 16-byte aligned with strides that are multiples of 8 elements; any other V is
+ * transposed into context scratch first (then cq_reserve(b * h_k * d * roundup(seqlen_k, 8) * 2) up front when
+ * capturing).  cq_flash_attention returns a status and runs on the context's stream; run_mha is the
  * reference's own symbol and signature (void, default stream), for hosts that already bind it, with
  * cq_run_mha_last_status() to read the outcome. */
 cq_status cq_flash_attention(cq_ctx *ctx, void *q_ptr, void *k_ptr, void *v_ptr, void *o_ptr, void *softmax_lse_ptr, void *alibi_slopes_ptr,
