@@ -217,7 +217,7 @@ def prefill_attention(dev, peak_tflops: float, cases=((1, 32, 32, 128), (1, 32, 
         flops = 4.0 * s * s * h * d * b / 2
         out.append({"batch": b, "heads": h, "kv_heads": hk, "seq": s, "head_dim": d, "causal": True, "dtype": "f16", "us": round(t * 1e6, 1),
                     "tflops": round(flops / t / 1e12, 1), "frac_of_tensor_peak": round(flops / t / 1e12 / peak_tflops, 4),
-                    "includes": "V transpose pre-pass + attention kernel"})
+                    "includes": "the whole cq_flash_attention call: one persistent kernel, V tiles read in place"})
     return {"peak_tflops": peak_tflops, "cases": out}
 
 
