@@ -12,9 +12,12 @@
 // 95.8 -> 79.6 us, 2 x 64 heads x 4096 858 -> 760 us; a plain round-robin instead of alternating directions: 89.8 us).
 //   warp 0        TMA: the item's Q tile, then K tiles into a three-stage ring and V tiles into a two-stage ring of
 //                 its own (128-byte swizzle); a K tile is free as soon as its scores exist, long before its V
-//   warp 1        tcgen05.mma issue: S = Q K^T into a 128-column f32 slot of tensor memory (one slot: the compute
-//                 warps release it once the scores sit in their registers), O_tile = P V with P read from tensor
-//                 memory as the A operand into one of two product slots; one commit per product
+//   warp 1        tcgen05.mma issue of S = Q K^T into a 128-column f32 slot of tensor memory (one slot: the compute
+//                 warps release it once the scores sit in their registers)
+//   warp 10       tcgen05.mma issue of O_tile = P V, with P read from tensor memory as the A operand, into one of two
+//                 product slots; one commit per product.  Two issuing threads because one thread issues an
+//                 M 128 x N 128 x K 16 instruction every ~100 cycles while the tensor pipe needs 64: with both products on
+//                 one thread the issue was the longest role of a tile (2 x 64/8 heads x 4096: 732 -> 659 us)
 //   warps 2-9     compute: thread = (query row, half of the columns): warps 2-5 take keys 0-63 of a tile and the first
 //                 half of the output row, warps 6-9 the other halves (two warps per tensor-memory lane quarter, two per
 //                 scheduler).  Softmax of the half: scores read once (tcgen05.ld, loads in flight together), masked
@@ -25,8 +28,9 @@
 //                 previous tile's product is folded into f32 registers, acc = acc * factor + tile, so nothing in
 //                 tensor memory is ever rescaled in place and the factor never leaves its thread; at the end
 //                 acc / (sum of both halves) goes out as f16 / bf16
-// Measured per tile (clock64 counters in an instrumented build): the MMA lane is busy ~2400 of ~3600 cycles (the
-// tensor pipe itself ~1450 by the profiler's count) and the compute warps wait for scores a third of the time.
+// Measured per tile with ONE issuing thread (clock64 counters in an instrumented build): the MMA lane busy ~2400 of
+// ~3600 cycles (the tensor pipe itself ~1450 by the profiler's count), the compute warps waiting for scores a third of
+// the time; that is what the second issuer removed (a tile now takes ~2800 cycles at 4096 keys).
 // Keeping Q in tensor memory as the A operand of S, so that only K is read from shared memory, changed nothing
 // (measured, not kept), and so did two S slots with one product slot: the MMAs are neither starved for operands
 // nor held back by the S slot.
@@ -46,7 +50,7 @@ namespace {
 
 constexpr int FA_M = 128;   // query rows per CTA
 constexpr int FA_N = 128;   // keys per tile
-constexpr int FA_THREADS = 320;
+constexpr int FA_THREADS = 352;  // TMA warp, first MMA issuer, eight compute warps, second MMA issuer
 
 struct FaParams {
     void *o;
@@ -280,8 +284,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             }
         }
     } else if (warp == 1) {
+        // ---- first MMA issuer: S(t) = Q K(t)^T, as far ahead as the K ring and the score slot allow ----------------------
+        // (one thread issues an M 128 x N 128 x K 16 instruction every ~100 cycles, the tensor pipe needs 64: with the two
+        // products on one thread the issue was the tile's longest role, with a thread each they run side by side)
         if (lane == 0) {
-            constexpr uint32_t idesc_s = idesc_16(FA_M, FA_N, BF16), idesc_o = idesc_16(FA_M, D, BF16);
+            constexpr uint32_t idesc_s = idesc_16(FA_M, FA_N, BF16);
             const uint32_t q_addr = smem_u32(sm_q);
             bool ok = true;
             int g = 0, qi = 0;
@@ -295,11 +302,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                     ok = false;
                     break;
                 }
-                // S(t) = Q K(t)^T (one slot: the softmax warps free it as soon as they hold the scores in registers)
-                auto issue_qk = [&](int t) -> bool {
+                for (int t = 0; t < ntiles && ok; ++t) {
                     const int gt = g + t, s = gt % KS;
-                    if (!mbar_wait_bounded(smem_u32(&k_full[s]), (gt / KS) & 1)) return false;
-                    if (gt >= 1 && !mbar_wait_bounded(smem_u32(s_empty), (gt - 1) & 1)) return false;
+                    // the K tile has landed; the score slot is free (one slot: the softmax warps free it as soon as they hold
+                    // the previous tile's scores in registers)
+                    if (!mbar_wait_bounded(smem_u32(&k_full[s]), (gt / KS) & 1) || (gt >= 1 && !mbar_wait_bounded(smem_u32(s_empty), (gt - 1) & 1))) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
                     const uint32_t k_addr = smem_u32(sm_k + (size_t)s * Cfg::kKBytes);
 #pragma unroll
@@ -311,19 +321,28 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                     tc_commit(smem_u32(s_full));
                     tc_commit(smem_u32(&k_empty[s]));  // the K tile is free once these MMAs have read it
                     if (t == ntiles - 1) tc_commit(smem_u32(q_empty));  // and so is Q after the item's last score tile
-                    return true;
-                };
-                ok = issue_qk(0);
+                }
+                g += ntiles;
+                ++qi;
+            }
+            if (!ok) atomicExch(p.err, kDevErrMma);
+        }
+    } else if (warp == FA_THREADS / 32 - 1) {
+        // ---- second MMA issuer: O_tile(t) = P(t) V(t), P from tensor memory as the A operand ----------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = idesc_16(FA_M, D, BF16);
+            bool ok = true;
+            int g = 0;
+            for (int rd = 0; rd * (int)gridDim.x < items && ok; ++rd) {
+                const int w = item_of_round(rd);
+                if (w >= items) continue;
+                int q0, head, batch, ntiles;
+                item_at(w, q0, head, batch, ntiles);
                 for (int j = 0; j < ntiles && ok; ++j) {
-                    if (j + 1 < ntiles) ok = issue_qk(j + 1);  // the next tile's scores are computed while this tile's softmax runs
-                    if (!ok) break;
                     const int gj = g + j, s = gj % VS, slot = gj & 1;
-                    if (!mbar_wait_bounded(smem_u32(&v_full[s]), (gj / VS) & 1)) {
-                        ok = false;
-                        break;
-                    }
-                    // P in place, and the product slot free (the accumulate warps have folded the tile two back)
-                    if (!mbar_wait_bounded(smem_u32(&p_full[slot]), (gj >> 1) & 1) || (gj >= 2 && !mbar_wait_bounded(smem_u32(&o_empty[slot]), ((gj >> 1) - 1) & 1))) {
+                    // V and P in place, and the product slot free (the compute warps have folded the tile two back)
+                    if (!mbar_wait_bounded(smem_u32(&v_full[s]), (gj / VS) & 1) || !mbar_wait_bounded(smem_u32(&p_full[slot]), (gj >> 1) & 1) ||
+                        (gj >= 2 && !mbar_wait_bounded(smem_u32(&o_empty[slot]), ((gj >> 1) - 1) & 1))) {
                         ok = false;
                         break;
                     }
@@ -339,10 +358,9 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                             tc_mma_f16_ts(tmem_base + Cfg::kColO + (uint32_t)(slot * D), tmem_base + Cfg::kColP + (uint32_t)(slot * 64 + (hf * 4 + kk) * 8), bdesc,
                                           VT ? idesc_o : (idesc_o | (1u << 16)), (hf | kk) != 0);
                         }
-                    tc_commit(smem_u32(&o_full[slot]));  // product ready; its P slot and V^T stage free
+                    tc_commit(smem_u32(&o_full[slot]));  // product ready; its P slot and V stage free
                 }
                 g += ntiles;
-                ++qi;
             }
             if (!ok) atomicExch(p.err, kDevErrMma);
         }
