@@ -509,6 +509,7 @@ def run_ours(args):
                 line[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
         if world == 1:
             extra("small_batch", lambda: bw.small_batch(dev, peak))
+            extra("independent_gemvs", lambda: bw.independent_gemvs(dev, peak))
             extra("prefill_gemm", lambda: bw.prefill_gemm(dev, peak, measured_peak_tflops()))
             extra("prefill_attention", lambda: bw.prefill_attention(dev, measured_peak_tflops()))
             extra("decode_7b", lambda: bw.decode_7b(dev, peak))

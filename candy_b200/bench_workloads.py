@@ -221,6 +221,78 @@ def prefill_attention(dev, peak_tflops: float, cases=((1, 32, 32, 128), (1, 32, 
     return {"peak_tflops": peak_tflops, "cases": out}
 
 
+def independent_gemvs(dev, peak_gbs: float, shapes=((4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)), sweeps: int = 50, reps: int = 10):
+    """The headline sweep once more with the caller's promise that consecutive GEMVs do not depend on one another
+    (option gemv_independent: a decoder's q / k / v, or gate / up, projections of one x are such launches).  The
+    kernels then skip the wait on the previous launch, whose last rows overlap the next launch's set-up.  Reported
+    next to the default, dependent, figures; results are the same bits (checked).  Weights cycle through eight copies
+    per shape, the results alternate between two buffers."""
+    from .backend import RawBuffer
+    lib, ctx = dev._lib, dev.ctx
+    rng = np.random.default_rng(11)
+    rings, xs, ys = [], [], []
+
+    def device_copy(src):
+        dst = RawBuffer(dev, src.nbytes)
+        dev._check(lib.cq_memcpy_d2d(ctx, dst.ptr, src.ptr, src.nbytes), "copy")
+        return dst
+
+    for n, k in shapes:
+        raw = rng.integers(0, 256, size=(n * (k // 32), 18), dtype=np.uint8)
+        raw[:, 1] = (raw[:, 1] & 0x3F) | 0x20  # finite f16 scales of moderate size
+        first = dev.upload_bytes(raw.reshape(-1))
+        rings.append([first] + [device_copy(first) for _ in range(7)])
+        xs.append(dev.storage_from_slice(rng.standard_normal((1, k), dtype=np.float32)))
+        ys.append([dev.alloc(n), dev.alloc(n)])
+
+    def timed(which):
+        cur = [0]
+
+        def sweep():
+            for i in which:
+                n, k = shapes[i]
+                dev._check(lib.cq_qmatmul(ctx, 2, 0, 0, xs[i].ptr, 1, k, k, rings[i][cur[0] % 8].ptr, n, ys[i][cur[0] & 1].ptr, n), "qmatmul")
+            cur[0] += 1
+
+        sweep()
+        dev.synchronize()
+        lib.cq_capture_begin(ctx)
+        for _ in range(sweeps):
+            sweep()
+        g = C.c_void_p()
+        dev._check(lib.cq_capture_end(ctx, C.byref(g)), "capture end")
+        for _ in range(2):
+            dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+        dev.synchronize()
+        ms = C.c_float()
+        lib.cq_timer_start(ctx)
+        for _ in range(reps):
+            dev._check(lib.cq_graph_launch(ctx, g), "graph launch")
+        lib.cq_timer_stop(ctx, C.byref(ms))
+        dev.synchronize()
+        lib.cq_graph_destroy(ctx, g)
+        us = ms.value * 1e3 / (reps * sweeps)
+        nbytes = sum(shapes[i][0] * (shapes[i][1] // 32) * 18 + 4 * shapes[i][1] + 4 * shapes[i][0] for i in which)
+        return us, nbytes / us / 1e3
+
+    dom = max(range(len(shapes)), key=lambda i: shapes[i][0] * shapes[i][1])
+    out = {"shapes": [list(s) for s in shapes], "l2_defeat": "ring of 8 weight copies per shape"}
+    results = {}
+    for opt in (0, 1):
+        dev.set_option("gemv_independent", opt)
+        try:
+            us_sweep, gbs_sweep = timed(range(len(shapes)))
+            us_dom, gbs_dom = timed([dom])
+            results[opt] = ys[dom][0].data().copy()
+        finally:
+            dev.set_option("gemv_independent", 0)
+        out["independent" if opt else "dependent"] = {
+            "sweep_us": round(us_sweep, 2), "sweep_gbs": round(gbs_sweep, 1), "dominant_shape_us": round(us_dom, 2),
+            "dominant_shape_gbs": round(gbs_dom, 1), "dominant_shape_frac_of_hbm_peak": round(gbs_dom / peak_gbs, 4)}
+    out["same_bits"] = bool(np.array_equal(results[0], results[1]))
+    return out
+
+
 class RawCopy:
     """A device copy of a QStorage's blocks (ring element)."""
 

@@ -30,6 +30,10 @@ struct GemvTuning {
     // ring fill delays the last loads of the previous kernel's CTAs still running (sweep of four shapes 40.3 us
     // against 37.7), although the same shape back to back gains 0.1-0.2 us per launch.
     int early = 0;
+    // 1: the one-row streaming GEMVs launched while this is set neither read nor overwrite anything that an earlier
+    // launch on the stream still in flight writes (q / k / v, or gate / up, of one x): they skip the wait on the
+    // previous kernel and overlap it.  The caller's promise; results are undefined if it does not hold.
+    int gemv_independent = 0;
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;

@@ -84,6 +84,7 @@ struct GemvParams {
     const float *bias;   // added to every output row in the epilogue (nn.Linear's bias), or null
     int *err;
     int early;           // 1: the producer fills the ring before the CTA's first barrier
+    int independent;     // 1: the caller promises that this launch reads and overwrites nothing an earlier launch still in flight writes
 };
 
 // ---- compile-time description of where each value of a thread's two blocks sits --------
@@ -816,8 +817,9 @@ __global__ void __launch_bounds__(MAXT, MINB) gemv_stream_kernel(const GemvParam
     const int pair = wir * 32 + (lane % p.lanes_per_row);
     const bool active = pair < p.tpr;
 
-    // Activations depend on the previous kernel in the stream.
-    pdl_wait_prior();
+    // Activations depend on the previous kernel in the stream, unless the caller has said otherwise (option
+    // gemv_independent): then this launch's set-up and first rows overlap the previous launch's last ones.
+    if (!p.independent) pdl_wait_prior();
 
     // Fused prologue: x' = x + delta (CTA 0 also stores it to x_out: the caller ping-pongs two residual
     // buffers, every other CTA keeps reading the old one), x'' = x' / sqrt(mean(x'^2) + eps) * alpha.
@@ -1419,6 +1421,7 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
     if ((size_t)stage_bytes * 2 > budget) return false;
     while ((size_t)stage_bytes * stages > budget) --stages;
     p.early = ctx->tune.early;
+    p.independent = (ctx->tune.gemv_independent && !ctx->fuse.on && ctx->push.world == 0) ? 1 : 0;
     p.n = n;
     p.nb = (int)nb;
     p.row_bytes = (int)row_bytes;

@@ -102,7 +102,10 @@ cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream);
 cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
 /* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl, gemv_early (launch geometry of the
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
- * row); gemv_q81_inline (1, default: one or two rows in CQ_ACT_Q8_1 quantize their activations inside the GEMV's
+ * row); gemv_independent (0, default; 1: the caller promises that the one-row GEMVs launched while it is set neither
+ * read nor overwrite anything an earlier launch still in flight writes -- q / k / v or gate / up projections of one x --
+ * so they skip the wait on the previous kernel and overlap its last rows; undefined results if the promise does not
+ * hold); gemv_q81_inline (1, default: one or two rows in CQ_ACT_Q8_1 quantize their activations inside the GEMV's
  * set-up; 0: in a launch of their own first; the same bits either way); gemv_mma (3, default: CQ_ACT_F32 and CQ_ACT_Q8_1 batches of this many rows up to eight against Q4_0 run the
  * single-launch kernel with mma.sync block dots, two rows too against large weights, and CQ_ACT_F16 batches of up to
  * eight rows its f16 form; 0: never); gemv_force_simple; gemm_variant, gemm_cache_weights (keep an f16 copy of each weight matrix the wide

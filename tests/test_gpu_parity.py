@@ -341,3 +341,30 @@ def test_argument_errors_come_back_as_status_codes(device):
     assert lib.cq_dequantize(ctx, 2, 0, p, -1, p) == abi.ERR_INVALID_ARG
     assert lib.cq_quantize_rows(ctx, 2, 0, p, 4, 40, p) == abi.ERR_INVALID_ARG
     device.synchronize()  # the context is still usable after rejected calls
+
+
+def test_independent_gemv_launches_give_the_same_bits(device):
+    """Option gemv_independent: launches that do not depend on one another skip the wait on the previous kernel and
+    overlap it.  Three projections of one x into three buffers, with and without the option: equal results."""
+    lib, ctx = device._lib, device.ctx
+    k, ns = 4096, (4096, 1024, 11008)
+    rng = np.random.default_rng(31)
+    x = device.storage_from_slice(rng.standard_normal((1, k), dtype=np.float32))
+    ws, ys = [], []
+    for i, n in enumerate(ns):
+        w, _ = make_case(700 + i, n, k, 1)
+        ws.append(device.upload_bytes(oc.quantize(oc.Q4_0, 0, w)))
+        ys.append(device.zeros(n))
+    outs = {}
+    for opt in (0, 1):
+        device.set_option("gemv_independent", opt)
+        try:
+            for rep in range(3):
+                for w, y, n in zip(ws, ys, ns):
+                    assert lib.cq_qmatmul(ctx, oc.Q4_0, 0, 0, x.ptr, 1, k, k, w.ptr, n, y.ptr, n) == 0
+            device.synchronize()
+        finally:
+            device.set_option("gemv_independent", 0)
+        outs[opt] = [y.data().copy() for y in ys]
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
