@@ -161,6 +161,7 @@ cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "i8_min_rows_q8_1")) t.i8_min_rows_q8_1 = (int)value;
     else if (!strcmp(key, "gemv_mma")) t.gemv_mma = (int)value;
     else if (!strcmp(key, "fa_transpose_v")) t.fa_transpose_v = (int)value;
+    else if (!strcmp(key, "gemv_chain")) t.gemv_chain = value ? 1 : 0;
     else if (!strcmp(key, "gemv_independent")) t.gemv_independent = value ? 1 : 0;
     else if (!strcmp(key, "gemv_q81_inline")) t.gemv_q81_inline = (int)value;
     else if (!strcmp(key, "gemv_multirow")) t.gemv_multirow = (int)value;

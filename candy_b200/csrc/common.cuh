@@ -34,6 +34,7 @@ struct GemvTuning {
     // launch on the stream still in flight writes (q / k / v, or gate / up, of one x): they skip the wait on the
     // previous kernel and overlap it.  The caller's promise; results are undefined if it does not hold.
     int gemv_independent = 0;
+    int gemv_chain = 0;     // 1: the GEMVs launched while this is set are links of a chain with small kernels in between (a decode step)
     int force_simple = 0;   // 1: always use the plain one-warp-per-row kernel
     int pdl = 1;            // programmatic dependent launch on the streaming kernel
     int gemm_variant = 0;

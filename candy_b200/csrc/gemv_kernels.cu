@@ -1386,7 +1386,11 @@ bool plan_stream(const cq_ctx *ctx, int qtype, const void *w, const float *x, in
         wpr = 1;
     }
     if (wpr > 15) return false;  // 15 consumer warps + the producer warp = 512 threads
-    const int target = ctx->tune.target_warps < 1 ? 1 : (ctx->tune.target_warps > 15 ? 15 : ctx->tune.target_warps);
+    int target = ctx->tune.target_warps < 1 ? 1 : (ctx->tune.target_warps > 15 ? 15 : ctx->tune.target_warps);
+    // In a chain of GEMVs with small kernels in between (a decode step; the caller says so) one CTA of twelve warps per
+    // SM beats two of eight (7B-shape step: 1154 -> 1194 tok/s at 16 layers), while GEMVs back to back prefer the latter
+    // (74 MB shape: 15.1 against 16.7 us).  An explicit gemv_warps setting wins.
+    if (ctx->tune.gemv_chain && ctx->tune.target_warps == 8) target = 12;
     int row_groups = (target + wpr - 1) / wpr;  // warp groups, each covering 32/lanes rows
     if (row_groups < 1) row_groups = 1;
     while (row_groups > 1 && row_groups * wpr > 15) --row_groups;

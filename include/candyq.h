@@ -102,7 +102,9 @@ cq_status cq_ctx_set_stream(cq_ctx *ctx, void *cuda_stream);
 cq_status cq_ctx_set_option(cq_ctx *ctx, const char *key, int64_t value);
 /* Options: gemv_warps, gemv_stages, gemv_ctas_per_sm, gemv_rpt, gemv_coop, gemv_pdl, gemv_early (launch geometry of the
  * decode GEMV); gemv_variant (0 default, see CQ_ACT_F32); gemv_multirow (0: one weight pass per activation
- * row); gemv_independent (0, default; 1: the caller promises that the one-row GEMVs launched while it is set neither
+ * row); gemv_chain (0, default; 1: the GEMVs launched while it is set are links of a chain with small kernels in
+ * between, as in a decode step: unless gemv_warps was set explicitly they run as one CTA of twelve warps per SM);
+ * gemv_independent (0, default; 1: the caller promises that the one-row GEMVs launched while it is set neither
  * read nor overwrite anything an earlier launch still in flight writes -- q / k / v or gate / up projections of one x --
  * so they skip the wait on the previous kernel and overlap its last rows; undefined results if the promise does not
  * hold); gemv_q81_inline (1, default: one or two rows in CQ_ACT_Q8_1 quantize their activations inside the GEMV's
