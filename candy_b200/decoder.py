@@ -238,7 +238,8 @@ class QuantDecoder:
                 self.guard.need(1)
             return self._step_persistent(advance)
         # A decode step is a chain of GEMVs with small kernels in between: the library's planner then prefers one CTA
-        # of twelve warps per SM over two of eight (measured on the single-GPU, batch-1 step only; +3 %).
+        # of twelve warps per SM over two of eight (single-GPU, batch-1 step: +3 %; the sharded layers of a tensor-parallel
+        # step were measured slightly slower with it, 0.706 against 0.693 ms on two GPUs, and keep the default).
         chain = self.world == 1 and self.batch == 1
         if chain:
             self._check(self.lib.cq_ctx_set_option(self.ctx, b"gemv_chain", 1), "set option")
