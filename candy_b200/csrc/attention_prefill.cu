@@ -433,13 +433,15 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 const bool cut = kmax < HC - 1;  // only a tile that the causal diagonal or the end of the keys cuts needs the mask
                 float m_half = -INFINITY;
                 if (!cut) {
-                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    float m8[8];  // eight independent chains
 #pragma unroll
-                    for (int i = 0; i < HC; i += 4) {
-                        m4[0] = fmaxf(m4[0], __uint_as_float(sv[i])), m4[1] = fmaxf(m4[1], __uint_as_float(sv[i + 1]));
-                        m4[2] = fmaxf(m4[2], __uint_as_float(sv[i + 2])), m4[3] = fmaxf(m4[3], __uint_as_float(sv[i + 3]));
+                    for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(sv[i]);
+#pragma unroll
+                    for (int i = 8; i < HC; i += 8) {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) m8[u] = fmaxf(m8[u], __uint_as_float(sv[i + u]));
                     }
-                    m_half = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                    m_half = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
                 } else {
 #pragma unroll
                     for (int i = 0; i < HC; ++i)
@@ -456,7 +458,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 // P has two slots: the product that read this one (two tiles back) has finished -- this warp folded it
                 // at the end of the previous iteration (the last tile of the previous item right after its loop).
                 // p = exp2(s * scale_log2 - max * scale_log2), summed in f32, stored as 16-bit pairs
-                float l2[2] = {0.0f, 0.0f};
+                float l2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int c = 0; c < HC / 32; ++c) {
                     uint32_t pk[16];
@@ -469,13 +471,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                             p0 = c0 <= kmax ? p0 : 0.0f;
                             p1 = c0 + 1 <= kmax ? p1 : 0.0f;
                         }
-                        l2[0] += p0, l2[1] += p1;
+                        l2[(i & 1) * 2] += p0, l2[(i & 1) * 2 + 1] += p1;
                         pk[i] = pack2<BF16>(p0, p1);
                     }
                     tmem_st16(lane_addr + Cfg::kColP + (uint32_t)(buf * (FA_N / 2) + half * (HC / 2) + c * 16), pk);
                 }
                 tmem_wait_st();
-                l_run = l_run * alpha + (l2[0] + l2[1]);
+                l_run = l_run * alpha + ((l2[0] + l2[1]) + (l2[2] + l2[3]));
                 m_run = m_new;
                 tc_fence_before();
                 __syncwarp();
